@@ -1,0 +1,258 @@
+"""TEST INFRASTRUCTURE: numpy-facing bindings of the checker.
+
+Two back ends, same call shapes:
+
+* ``restated``  -> oracle/libmegcc_oracle.so, our C restatement (oracle/megcc_oracle.c)
+* ``reference`` -> oracle/_ref/libmegcc_ref_kernels.so, the reference's own generated
+  x86 kernels (built by oracle/Makefile from the reference sources; only the kernels
+  listed in oracle/ref_specs.txt exist)
+
+Only tests/, the smoke check and the CPU-baseline leg of bench.py import this module.
+The product package never does.
+
+All tensors are the reference's model-visible layouts: activations NCHW, dense filter
+OIHW, grouped filter [G, OCpg, ICpg, KH, KW], bias [OC] int32.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ACT = {"IDENTITY": 0, "RELU": 1, "H_SWISH": 2}
+POOL = {"MAX": 0, "AVERAGE": 1, "AVERAGE_COUNT_EXCLUDE_PADDING": 2}
+QELEM = {"QADD": 0, "QFUSE_ADD_RELU": 1, "QMUL": 2, "QRELU": 3}
+
+_i8p = np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS")
+_i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+
+
+def build(with_reference=True):
+    """Compile the checker (and, when the reference tree is present, oracle/_ref)."""
+    targets = ["oracle"] + (["ref"] if with_reference else [])
+    subprocess.run(["make", "-s", "-j8", "-C", HERE] + targets, check=True)
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(HERE, "libmegcc_oracle.so")
+        if not os.path.exists(path):
+            build(with_reference=False)
+        L = C.CDLL(path)
+        L.oracle_conv_bias_qs8.restype = C.c_int
+        L.oracle_conv_bias_qs8.argtypes = (
+            [_i8p, _i8p, C.c_void_p, _i8p, C.c_void_p] + [C.c_int] * 14
+            + [C.c_float, _f32p, C.c_int, C.c_float, C.c_int])
+        L.oracle_pooling_qs8.restype = None
+        L.oracle_pooling_qs8.argtypes = [_i8p, _i8p] + [C.c_int] * 11
+        L.oracle_qelemwise.restype = None
+        L.oracle_qelemwise.argtypes = [
+            _i8p, C.c_void_p, _i8p, C.c_int, C.c_size_t, C.c_int, C.c_int, C.c_int,
+            C.c_float, C.c_float, C.c_float]
+        L.oracle_typecvt_qs32_qs8.restype = None
+        L.oracle_typecvt_qs32_qs8.argtypes = [_i32p, _i8p, C.c_size_t, C.c_float, C.c_float]
+        L.oracle_matmul_s8_s32.restype = None
+        L.oracle_matmul_s8_s32.argtypes = [_i8p, _i8p, _i32p, C.c_int, C.c_int, C.c_int]
+        _lib = L
+    return _lib
+
+
+def out_extent(i, k, s, p, d=1):
+    return (i + 2 * p - d * (k - 1) - 1) // s + 1
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+def conv_bias_qs8(src, flt, bias, stride, pad, s_src, s_flt, s_dst, act="IDENTITY",
+                  groups=1, dilate=1, return_acc=False):
+    """qint8 ConvBias; ``s_flt`` a float (per tensor) or an [OC] array (per channel)."""
+    src, flt = _c(src, np.int8), _c(flt, np.int8)
+    n, ic, ih, iw = src.shape
+    kh, kw = flt.shape[-2:]
+    oc = flt.shape[0] if flt.ndim == 4 else flt.shape[0] * flt.shape[1]
+    oh, ow = out_extent(ih, kh, stride, pad, dilate), out_extent(iw, kw, stride, pad, dilate)
+    dst = np.empty((n, oc, oh, ow), np.int8)
+    acc = np.empty((n, oc, oh, ow), np.int32) if return_acc else None
+    per_channel = int(np.ndim(s_flt) > 0)
+    fs = _c(np.atleast_1d(s_flt), np.float32)
+    b = None if bias is None else _c(np.asarray(bias).reshape(-1), np.int32)
+    rc = lib().oracle_conv_bias_qs8(
+        src, flt, None if b is None else b.ctypes.data, dst,
+        None if acc is None else acc.ctypes.data, n, ic, ih, iw, oc, kh, kw, stride, stride,
+        pad, pad, dilate, dilate, groups, np.float32(s_src), fs, per_channel,
+        np.float32(s_dst), ACT[act])
+    assert rc == 0
+    return (dst, acc) if return_acc else dst
+
+
+def pooling_qs8(src, mode, window, stride, pad):
+    src = _c(src, np.int8)
+    n, c, ih, iw = src.shape
+    oh, ow = (ih + 2 * pad - window) // stride + 1, (iw + 2 * pad - window) // stride + 1
+    dst = np.empty((n, c, oh, ow), np.int8)
+    lib().oracle_pooling_qs8(src, dst, POOL[mode], n, c, ih, iw, window, window, stride,
+                             stride, pad, pad)
+    return dst
+
+
+def _bcast(a, b):
+    if b is None or a.shape == b.shape:
+        return 0, 1, 1
+    if b.size == 1:
+        return 1, 1, 1
+    assert b.size == a.shape[1], "only same-shape, scalar or per-channel operands"
+    return 2, a.shape[1], int(np.prod(a.shape[2:]))
+
+
+def qelemwise(mode, a, b, s0, s1, s_dst):
+    a = _c(a, np.int8)
+    b = None if b is None else _c(b, np.int8)
+    bc, ch, inner = _bcast(a, b)
+    dst = np.empty(a.shape, np.int8)
+    lib().oracle_qelemwise(a, None if b is None else b.ctypes.data, dst, QELEM[mode], a.size,
+                           bc, ch, inner, np.float32(s0), np.float32(s1), np.float32(s_dst))
+    return dst
+
+
+def typecvt_qs32_qs8(src, s_src, s_dst):
+    src = _c(src, np.int32)
+    dst = np.empty(src.shape, np.int8)
+    lib().oracle_typecvt_qs32_qs8(src, dst, src.size, np.float32(s_src), np.float32(s_dst))
+    return dst
+
+
+def matmul_s8_s32(a, b):
+    a, b = _c(a, np.int8), _c(b, np.int8)
+    m, k = a.shape
+    k2, n = b.shape
+    assert k == k2
+    c = np.empty((m, n), np.int32)
+    lib().oracle_matmul_s8_s32(a, b, c, m, n, k)
+    return c
+
+
+# ----------------------------------------------------------------------------------------
+# the reference's own kernels
+# ----------------------------------------------------------------------------------------
+class _RefOperand(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("dtype", C.c_int), ("scale", C.c_float),
+                ("ndim", C.c_int), ("dims", C.c_int * 7)]
+
+
+_DT = {np.dtype(np.int8): 100, np.dtype(np.int32): 101, np.dtype(np.float32): 0}
+_ref = None
+
+
+def ref_lib():
+    """The reference-kernel library, or None when it was never built."""
+    global _ref
+    if _ref is None:
+        path = os.path.join(HERE, "_ref", "libmegcc_ref_kernels.so")
+        if not os.path.exists(path):
+            return None
+        L = C.CDLL(path)
+        L.megcc_ref_call.restype = C.c_int
+        L.megcc_ref_call.argtypes = [C.c_char_p, C.POINTER(_RefOperand), C.c_int,
+                                     C.POINTER(_RefOperand), C.c_int]
+        L.megcc_ref_has.restype = C.c_int
+        L.megcc_ref_has.argtypes = [C.c_char_p]
+        _ref = L
+    return _ref
+
+
+def ref_has(symbol):
+    L = ref_lib()
+    return bool(L and L.megcc_ref_has(symbol.encode()))
+
+
+def _operand(a, scale):
+    o = _RefOperand()
+    o.ptr = a.ctypes.data
+    o.dtype = _DT[a.dtype]
+    o.scale = scale
+    o.ndim = a.ndim
+    for i, d in enumerate(a.shape):
+        o.dims[i] = d
+    return o
+
+
+def ref_call(symbol, ins, outs):
+    """ins/outs: lists of (contiguous ndarray, scale)."""
+    L = ref_lib()
+    if L is None:
+        raise RuntimeError("oracle/_ref was not built (reference tree absent at build time)")
+    ia = (_RefOperand * len(ins))(*[_operand(a, s) for a, s in ins])
+    oa = (_RefOperand * len(outs))(*[_operand(a, s) for a, s in outs])
+    rc = L.megcc_ref_call(symbol.encode(), ia, len(ins), oa, len(outs))
+    if rc != 0:
+        raise RuntimeError(f"reference kernel {symbol}: status {rc}")
+
+
+def conv_symbol(k, stride, pad, groups, act, bias=True):
+    """Symbol naming of compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:144-176."""
+    sparse = "DENSE" if groups == 1 else "GROUP"
+    s = (f"kernel_conv2d_{k}x{k}_NCHW_{sparse}_p{pad}x{pad}_s{stride}x{stride}_d1x1_"
+         f"qsi8qsi8qsi32qsi8")
+    if bias:
+        s += "_bias"
+    if act != "IDENTITY":
+        s += "_" + act
+    return s
+
+
+def ref_conv_bias_qs8(src, flt, bias, stride, pad, s_src, s_flt, s_dst, act="IDENTITY",
+                      groups=1):
+    src, flt = _c(src, np.int8), _c(flt, np.int8)
+    n, ic, ih, iw = src.shape
+    kh, kw = flt.shape[-2:]
+    if groups > 1 and flt.ndim == 4:
+        flt = flt.reshape(groups, flt.shape[0] // groups, flt.shape[1], kh, kw)
+    oc = flt.shape[0] if flt.ndim == 4 else flt.shape[0] * flt.shape[1]
+    oh, ow = out_extent(ih, kh, stride, pad), out_extent(iw, kw, stride, pad)
+    dst = np.empty((n, oc, oh, ow), np.int8)
+    if bias is None:
+        b = np.zeros((0,), np.int32)
+        ins = [(src, s_src), (flt, s_flt), (b, s_src * s_flt)]
+    else:
+        b = _c(np.asarray(bias).reshape(1, oc, 1, 1), np.int32)
+        ins = [(src, s_src), (flt, s_flt), (b, s_src * s_flt)]
+    ref_call(conv_symbol(kh, stride, pad, groups, act, bias is not None), ins, [(dst, s_dst)])
+    return dst
+
+
+def ref_pooling_qs8(src, mode, window, stride, pad, scale=1.0):
+    src = _c(src, np.int8)
+    n, c, ih, iw = src.shape
+    oh, ow = (ih + 2 * pad - window) // stride + 1, (iw + 2 * pad - window) // stride + 1
+    dst = np.empty((n, c, oh, ow), np.int8)
+    sym = (f"kernel_pooling_{mode}_NCHW_p{pad}x{pad}_s{stride}x{stride}_w{window}x{window}"
+           f"_qsi8qsi8")
+    ref_call(sym, [(src, scale)], [(dst, scale)])
+    return dst
+
+
+def ref_qelemwise(mode, a, b, s0, s1, s_dst):
+    a = _c(a, np.int8)
+    dst = np.empty(a.shape, np.int8)
+    if mode == "QRELU":
+        ref_call("kernel_elementwise_multitype_QRELU_qsi8qsi8", [(a, s0)], [(dst, s_dst)])
+    else:
+        b = _c(b, np.int8)
+        ref_call(f"kernel_elementwise_multitype_{mode}_qsi8qsi8qsi8", [(a, s0), (b, s1)],
+                 [(dst, s_dst)])
+    return dst
+
+
+def ref_typecvt_qs32_qs8(src, s_src, s_dst):
+    src = _c(src, np.int32)
+    dst = np.empty(src.shape, np.int8)
+    ref_call("kernel_typecvt_qsi32qsi8", [(src, s_src)], [(dst, s_dst)])
+    return dst

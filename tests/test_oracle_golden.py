@@ -1,0 +1,65 @@
+"""The CPU restatement (oracle/megcc_oracle.c) against the committed golden vectors, which
+were produced by the reference's own generated x86 kernels (tests/golden/make_golden.py)."""
+import numpy as np
+import pytest
+
+import cases
+import golden_util as G
+
+
+def _conv(oracle, c):
+    src, flt, bias = cases.conv_inputs(c)
+    s0, s1, s2 = c["scales"]
+    dst = oracle.conv_bias_qs8(src, flt, bias, c["stride"], c["pad"], s0, s1, s2, c["act"],
+                               c["groups"])
+    G.check("conv_bias_qs8", c["name"], dst, src, flt, bias)
+
+
+def test_conv_naive_catalogue(oracle):
+    for c in cases.conv_naive_catalogue():
+        _conv(oracle, c)
+
+
+def test_conv_im2col_catalogue(oracle):
+    for c in cases.conv_im2col_catalogue():
+        _conv(oracle, c)
+
+
+@pytest.mark.parametrize("dst_scale", [0.1, 5.0])
+def test_conv_cfg1(oracle, dst_scale):
+    _conv(oracle, cases.conv_cfg1(dst_scale))
+
+
+def test_conv_model_shapes(oracle):
+    for c in cases.conv_model_shapes():
+        _conv(oracle, c)
+
+
+def test_pooling(oracle):
+    for c in cases.pool_catalogue():
+        x = cases.pool_input(c)
+        G.check("pooling_qs8", c["name"],
+                oracle.pooling_qs8(x, c["mode"], c["window"], c["stride"], c["pad"]), x)
+
+
+def test_qelemwise(oracle):
+    for c in cases.qelem_catalogue():
+        a, b = cases.qelem_inputs(c)
+        s0, s1, s2 = c["scales"]
+        G.check("qelemwise", c["name"], oracle.qelemwise(c["mode"], a, b, s0, s1, s2), a, b)
+
+
+def test_typecvt(oracle):
+    for c in cases.typecvt_catalogue():
+        x = cases.typecvt_input(c)
+        G.check("typecvt_qs32_qs8", c["name"],
+                oracle.typecvt_qs32_qs8(x, c["s_src"], c["s_dst"]), x)
+
+
+def test_matmul_is_exact_integer_gemm(oracle):
+    r = cases.rng_for("matmul")
+    for m, n, k in ((4, 3, 4), (16, 15, 16), (64, 56, 64), (33, 17, 129)):
+        a = r.integers(-127, 128, (m, k), dtype=np.int8)
+        b = r.integers(-127, 128, (k, n), dtype=np.int8)
+        want = a.astype(np.int64) @ b.astype(np.int64)
+        assert (oracle.matmul_s8_s32(a, b) == want).all()
