@@ -1,0 +1,115 @@
+/*
+ * megcc_b200 operator-level C ABI (libmegcc_b200.so).
+ *
+ * These are the entry points that the host stubs emitted by the CUDA KernelGen arch
+ * (GetKernelBody) call, one per reference kernel family. Every pointer is a DEVICE
+ * pointer unless its name says host; `stream` is a cudaStream_t passed as void*.
+ * All functions return a TinyNNStatus value (0 = TinyNN_SUCCESS,
+ * runtime/src/tinynn.h:9-24 in the reference) and never throw or trap.
+ *
+ * Internal activation layout is NHWC int8 (channels innermost) so that one pixel's
+ * channels are one contiguous TMA row; the model-visible layout stays the reference's
+ * NCHW (compiler/lib/KernelGen/BareMetal/FormatHelper.cpp:18-22) and the *_nchw entry
+ * points convert on the way in and out.
+ */
+#ifndef MEGCC_B200_H_
+#define MEGCC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MB200_API __attribute__((visibility("default")))
+
+/* nonlineMode values of ConvBias (compiler/lib/KernelGen/BareMetal/Activation.cpp:9-42) */
+enum { MB200_IDENTITY = 0, MB200_RELU = 1, MB200_H_SWISH = 2 };
+/* Pooling modes (compiler/lib/KernelGen/BareMetal/Pooling.cpp:66-150) */
+enum { MB200_POOL_MAX = 0, MB200_POOL_AVERAGE = 1, MB200_POOL_AVERAGE_COUNT_EXCLUDE_PADDING = 2 };
+/* ElemwiseMultiType modes (compiler/lib/KernelGen/BareMetal/ElemwiseMultiType.cpp:26-56) */
+enum { MB200_QADD = 0, MB200_QFUSE_ADD_RELU = 1, MB200_QMUL = 2, MB200_QRELU = 3 };
+/* kernel choice for ConvBias */
+enum { MB200_ALGO_AUTO = 0, MB200_ALGO_DIRECT = 1, MB200_ALGO_UMMA = 2 };
+
+/* The attributes the reference passes through TContext for a ConvBias
+ * (kernel_h/w, stride_h/w, pad_h/w, dilate_h/w, sparse, nonlineMode:
+ * compiler/lib/Conversion/MGBToKernel/MGBToKernelHelper.h:98-124) plus the extents its
+ * kernel reads from the Tensor layouts (BareMetal/ConvKernel.cpp:287-301). */
+typedef struct mb200_conv_param {
+    int n, ic, ih, iw;
+    int oc, kh, kw;
+    int stride_h, stride_w, pad_h, pad_w, dilate_h, dilate_w;
+    int groups;   /* 1 = DENSE, else GROUP (ic and oc are totals) */
+    int nonline;  /* MB200_IDENTITY / MB200_RELU / MB200_H_SWISH */
+    float src_scale, flt_scale, dst_scale;
+} mb200_conv_param;
+
+/* ---- library ---- */
+MB200_API const char* mb200_version(void);
+/* text of the last error raised on the calling thread ("" if none) */
+MB200_API const char* mb200_last_error(void);
+/* Reads and clears the device status word that kernels set when a bounded wait ran out
+ * (0 = healthy). Synchronises `stream`. */
+MB200_API int mb200_device_status(void* stream, int* status_host);
+
+/* ---- ConvBias, qint8 x qint8 -> int32 -> qint8 ------------------------------------
+ * Replaces kernel_conv2d_<k>x<k>_NCHW_{DENSE,GROUP}_p.._s.._d.._qsi8qsi8qsi32qsi8[_bias][_ACT]
+ * (compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:144-176, body :178-389). */
+
+/* bytes of the K-major packed filter [OC][KH][KW][ICpg] that the kernels read */
+MB200_API size_t mb200_conv_packed_filter_bytes(const mb200_conv_param* p);
+/* OIHW / [G][OCpg][ICpg][KH][KW] -> packed. This is the Init step of the kernel
+ * (the 3-phase init protocol of runtime/src/data_struct.h:135-142). */
+MB200_API int mb200_conv_pack_filter(
+        const mb200_conv_param* p, const int8_t* flt_oihw, int8_t* flt_packed, void* stream);
+/* src/dst NHWC. bias may be NULL. flt_scales: NULL = per-tensor p->flt_scale (all the
+ * reference can express), else one float per output channel (extension).
+ * src_is_nchw != 0 lets the first layer read the model input in place. */
+MB200_API int mb200_conv_bias_qs8_nhwc(
+        const mb200_conv_param* p, const int8_t* src, int src_is_nchw,
+        const int8_t* flt_packed, const int32_t* bias, const float* flt_scales, int8_t* dst,
+        int algo, void* stream);
+/* Same operator in the reference's own layouts: src/dst NCHW, filter OIHW. Needs
+ * mb200_conv_bias_qs8_nchw_workspace(p) bytes of device scratch (256-byte aligned). */
+MB200_API size_t mb200_conv_bias_qs8_nchw_workspace(const mb200_conv_param* p);
+MB200_API int mb200_conv_bias_qs8_nchw(
+        const mb200_conv_param* p, const int8_t* src, const int8_t* flt_oihw,
+        const int32_t* bias, const float* flt_scales, int8_t* dst, void* workspace,
+        size_t workspace_bytes, int algo, void* stream);
+/* int32 accumulators (bias added, before requantisation), NHWC; for accumulator parity */
+MB200_API int mb200_conv_acc_qs8_nhwc(
+        const mb200_conv_param* p, const int8_t* src, const int8_t* flt_packed,
+        const int32_t* bias, int32_t* acc, void* stream);
+
+/* ---- Pooling qint8 (kernel_pooling_<MODE>_NCHW_p.._s.._w.._qsi8qsi8,
+ * compiler/lib/KernelGen/BareMetal/Pooling.cpp:166-273), NHWC in/out ---- */
+MB200_API int mb200_pooling_qs8_nhwc(
+        const int8_t* src, int8_t* dst, int mode, int n, int c, int ih, int iw, int window_h,
+        int window_w, int stride_h, int stride_w, int pad_h, int pad_w, void* stream);
+
+/* ---- Quantised elementwise (kernel_elementwise_multitype_<MODE>_qsi8qsi8qsi8,
+ * compiler/lib/KernelGen/BareMetal/ElemwiseMultiType.cpp:102-213), same-shape operands.
+ * b is ignored for MB200_QRELU. ---- */
+MB200_API int mb200_qelemwise_qs8(
+        const int8_t* a, const int8_t* b, int8_t* dst, int mode, size_t nr_elem, float scale_a,
+        float scale_b, float scale_dst, void* stream);
+
+/* ---- TypeCvt qsi32 -> qsi8 (kernel_typecvt_qsi32qsi8,
+ * compiler/lib/KernelGen/BareMetal/Typecvt.cpp:43-106) ---- */
+MB200_API int mb200_typecvt_qs32_qs8(
+        const int32_t* src, int8_t* dst, size_t nr_elem, float src_scale, float dst_scale,
+        void* stream);
+
+/* ---- Layout transforms between the model-visible NCHW and the internal NHWC
+ * (the reference's Relayout/Dimshuffle, compiler/lib/KernelGen/BareMetal/Relayout.cpp:13-23) */
+MB200_API int mb200_relayout_nchw_to_nhwc_s8(
+        const int8_t* src, int8_t* dst, int n, int c, int h, int w, void* stream);
+MB200_API int mb200_relayout_nhwc_to_nchw_s8(
+        const int8_t* src, int8_t* dst, int n, int c, int h, int w, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MEGCC_B200_H_ */

@@ -1,0 +1,67 @@
+"""Loads libmegcc_b200.so. There is no fallback: without the built CUDA library every
+operator call raises."""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmegcc_b200.so")
+
+
+class ConvParam(C.Structure):
+    """Mirror of ``mb200_conv_param`` (include/megcc_b200.h)."""
+    _fields_ = [(k, C.c_int) for k in (
+        "n", "ic", "ih", "iw", "oc", "kh", "kw", "stride_h", "stride_w", "pad_h", "pad_w",
+        "dilate_h", "dilate_w", "groups", "nonline")] + [
+        ("src_scale", C.c_float), ("flt_scale", C.c_float), ("dst_scale", C.c_float)]
+
+
+_lib = None
+
+# name -> (restype, argtypes); every symbol declared in include/megcc_b200.h
+_P = C.c_void_p
+SIGNATURES = {
+    "mb200_version": (C.c_char_p, []),
+    "mb200_last_error": (C.c_char_p, []),
+    "mb200_device_status": (C.c_int, [_P, C.POINTER(C.c_int)]),
+    "mb200_conv_packed_filter_bytes": (C.c_size_t, [C.POINTER(ConvParam)]),
+    "mb200_conv_pack_filter": (C.c_int, [C.POINTER(ConvParam), _P, _P, _P]),
+    "mb200_conv_bias_qs8_nhwc": (C.c_int, [C.POINTER(ConvParam), _P, C.c_int, _P, _P, _P, _P,
+                                           C.c_int, _P]),
+    "mb200_conv_bias_qs8_nchw_workspace": (C.c_size_t, [C.POINTER(ConvParam)]),
+    "mb200_conv_bias_qs8_nchw": (C.c_int, [C.POINTER(ConvParam), _P, _P, _P, _P, _P, _P,
+                                           C.c_size_t, C.c_int, _P]),
+    "mb200_conv_acc_qs8_nhwc": (C.c_int, [C.POINTER(ConvParam), _P, _P, _P, _P, _P]),
+    "mb200_pooling_qs8_nhwc": (C.c_int, [_P, _P] + [C.c_int] * 11 + [_P]),
+    "mb200_qelemwise_qs8": (C.c_int, [_P, _P, _P, C.c_int, C.c_size_t, C.c_float, C.c_float,
+                                      C.c_float, _P]),
+    "mb200_typecvt_qs32_qs8": (C.c_int, [_P, _P, C.c_size_t, C.c_float, C.c_float, _P]),
+    "mb200_relayout_nchw_to_nhwc_s8": (C.c_int, [_P, _P] + [C.c_int] * 4 + [_P]),
+    "mb200_relayout_nhwc_to_nchw_s8": (C.c_int, [_P, _P] + [C.c_int] * 4 + [_P]),
+}
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m megcc_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+class MegccError(RuntimeError):
+    def __init__(self, status, msg):
+        super().__init__(f"TinyNNStatus {status}: {msg}")
+        self.status = status
+
+
+def check(status):
+    if status != 0:
+        raise MegccError(status, lib().mb200_last_error().decode())

@@ -1,0 +1,274 @@
+// extern "C" operator-level entry points declared in include/megcc_b200.h.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/megcc_b200.h"
+#include "internal.h"
+
+namespace mb200 {
+
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return set_error(ST_RUNTIME, "%s: %s", what, cudaGetErrorString(e));
+    return ST_SUCCESS;
+}
+
+int* device_status_word() {
+    // one word per device, allocated on first use and kept for the life of the process
+    static int* words[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        set_error(ST_RUNTIME, "no current CUDA device");
+        return nullptr;
+    }
+    if (!words[dev]) {
+        int* p = nullptr;
+        if (cudaMalloc(&p, 256) != cudaSuccess || cudaMemset(p, 0, 256) != cudaSuccess) {
+            set_error(ST_MALLOC, "cannot allocate the device status word");
+            return nullptr;
+        }
+        words[dev] = p;
+    }
+    return words[dev];
+}
+
+static int out_extent(int in, int k, int s, int p, int d) {
+    return (in + 2 * p - d * (k - 1) - 1) / s + 1;
+}
+
+static int make_args(const mb200_conv_param* p, int src_is_nchw, ConvArgs* a) {
+    if (!p)
+        return set_error(ST_NULL_PTR, "conv param is NULL");
+    if (p->n <= 0 || p->ic <= 0 || p->oc <= 0 || p->ih <= 0 || p->iw <= 0 || p->kh <= 0 ||
+        p->kw <= 0 || p->stride_h <= 0 || p->stride_w <= 0 || p->pad_h < 0 || p->pad_w < 0 ||
+        p->dilate_h <= 0 || p->dilate_w <= 0 || p->groups <= 0)
+        return set_error(ST_INVALID_LAYOUT, "conv param has a non-positive extent");
+    if (p->ic % p->groups || p->oc % p->groups)
+        return set_error(ST_INVALID_LAYOUT, "channels %d/%d not divisible by groups %d", p->ic,
+                         p->oc, p->groups);
+    if (p->nonline < 0 || p->nonline > 2)
+        return set_error(ST_NO_IMPLEMENT, "nonlineMode %d not supported", p->nonline);
+    a->n = p->n;
+    a->ic = p->ic;
+    a->ih = p->ih;
+    a->iw = p->iw;
+    a->oc = p->oc;
+    a->kh = p->kh;
+    a->kw = p->kw;
+    a->sh = p->stride_h;
+    a->sw = p->stride_w;
+    a->ph = p->pad_h;
+    a->pw = p->pad_w;
+    a->dh = p->dilate_h;
+    a->dw = p->dilate_w;
+    a->groups = p->groups;
+    a->oh = out_extent(p->ih, p->kh, p->stride_h, p->pad_h, p->dilate_h);
+    a->ow = out_extent(p->iw, p->kw, p->stride_w, p->pad_w, p->dilate_w);
+    if (a->oh <= 0 || a->ow <= 0)
+        return set_error(ST_INVALID_LAYOUT, "filter larger than the padded input");
+    const long long m = (long long)p->n * a->oh * a->ow;
+    if (m > 0x7fffffffLL)
+        return set_error(ST_OUT_OF_RANGE, "too many output pixels");
+    a->m = (int)m;
+    a->act = p->nonline;
+    a->src_is_nchw = src_is_nchw;
+    a->s_src = p->src_scale;
+    a->s_flt = p->flt_scale;
+    a->s_dst = p->dst_scale;
+    return ST_SUCCESS;
+}
+
+static size_t align_up(size_t v, size_t a) {
+    return (v + a - 1) / a * a;
+}
+
+}  // namespace mb200
+
+using namespace mb200;
+
+extern "C" {
+
+const char* mb200_version(void) {
+    return "megcc_b200 0.1 (sm_100a)";
+}
+
+const char* mb200_last_error(void) {
+    return g_err;
+}
+
+int mb200_device_status(void* stream, int* status_host) {
+    if (!status_host)
+        return set_error(ST_NULL_PTR, "status_host is NULL");
+    int* w = device_status_word();
+    if (!w)
+        return ST_MALLOC;
+    cudaStream_t st = (cudaStream_t)stream;
+    int v = 0;
+    if (cudaMemcpyAsync(&v, w, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+        return set_error(ST_RUNTIME, "reading the device status word failed: %s",
+                         cudaGetErrorString(cudaGetLastError()));
+    if (v != 0)
+        cudaMemsetAsync(w, 0, sizeof(int), st);
+    *status_host = v;
+    return ST_SUCCESS;
+}
+
+size_t mb200_conv_packed_filter_bytes(const mb200_conv_param* p) {
+    if (!p || p->groups <= 0)
+        return 0;
+    return (size_t)p->oc * (p->ic / p->groups) * p->kh * p->kw;
+}
+
+int mb200_conv_pack_filter(
+        const mb200_conv_param* p, const int8_t* flt_oihw, int8_t* flt_packed, void* stream) {
+    ConvArgs a{};
+    int rc = make_args(p, 0, &a);
+    if (rc)
+        return rc;
+    if (!flt_oihw || !flt_packed)
+        return set_error(ST_NULL_PTR, "filter pointer is NULL");
+    return launch_pack_filter(a, flt_oihw, flt_packed, (cudaStream_t)stream);
+}
+
+int mb200_conv_bias_qs8_nhwc(
+        const mb200_conv_param* p, const int8_t* src, int src_is_nchw, const int8_t* flt_packed,
+        const int32_t* bias, const float* flt_scales, int8_t* dst, int algo, void* stream) {
+    ConvArgs a{};
+    int rc = make_args(p, src_is_nchw, &a);
+    if (rc)
+        return rc;
+    if (!src || !flt_packed || !dst)
+        return set_error(ST_NULL_PTR, "conv tensor pointer is NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool umma_ok = conv_umma_supported(a, src, flt_packed, dst);
+    if (algo == MB200_ALGO_UMMA && !umma_ok)
+        return set_error(ST_NO_IMPLEMENT,
+                         "tensor-core ConvBias needs dense, NHWC, ic %% 64 == 0, oc %% 8 == 0, "
+                         "16-byte aligned tensors and >= 128 KiB of input");
+    if (algo == MB200_ALGO_UMMA || (algo == MB200_ALGO_AUTO && umma_ok))
+        return launch_conv_umma(a, src, flt_packed, bias, flt_scales, dst, st);
+    if (algo != MB200_ALGO_AUTO && algo != MB200_ALGO_DIRECT)
+        return set_error(ST_OUT_OF_RANGE, "unknown algo %d", algo);
+    return launch_conv_direct(a, src, flt_packed, bias, flt_scales, dst, nullptr, st);
+}
+
+int mb200_conv_acc_qs8_nhwc(
+        const mb200_conv_param* p, const int8_t* src, const int8_t* flt_packed,
+        const int32_t* bias, int32_t* acc, void* stream) {
+    ConvArgs a{};
+    int rc = make_args(p, 0, &a);
+    if (rc)
+        return rc;
+    if (!src || !flt_packed || !acc)
+        return set_error(ST_NULL_PTR, "conv tensor pointer is NULL");
+    return launch_conv_direct(
+            a, src, flt_packed, bias, nullptr, nullptr, acc, (cudaStream_t)stream);
+}
+
+size_t mb200_conv_bias_qs8_nchw_workspace(const mb200_conv_param* p) {
+    ConvArgs a{};
+    if (make_args(p, 0, &a))
+        return 0;
+    const size_t src = align_up((size_t)a.n * a.ih * a.iw * a.ic, 256);
+    const size_t dst = align_up((size_t)a.m * a.oc, 256);
+    const size_t flt = align_up(mb200_conv_packed_filter_bytes(p), 256);
+    return src + dst + flt;
+}
+
+int mb200_conv_bias_qs8_nchw(
+        const mb200_conv_param* p, const int8_t* src, const int8_t* flt_oihw,
+        const int32_t* bias, const float* flt_scales, int8_t* dst, void* workspace,
+        size_t workspace_bytes, int algo, void* stream) {
+    ConvArgs a{};
+    int rc = make_args(p, 0, &a);
+    if (rc)
+        return rc;
+    if (!src || !flt_oihw || !dst || !workspace)
+        return set_error(ST_NULL_PTR, "conv tensor or workspace pointer is NULL");
+    if (workspace_bytes < mb200_conv_bias_qs8_nchw_workspace(p))
+        return set_error(ST_OUT_OF_RANGE, "workspace of %zu bytes is too small", workspace_bytes);
+    if ((uintptr_t)workspace & 255)
+        return set_error(ST_INVALID_LAYOUT, "workspace must be 256-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    int8_t* ws_src = (int8_t*)workspace;
+    int8_t* ws_dst = ws_src + align_up((size_t)a.n * a.ih * a.iw * a.ic, 256);
+    int8_t* ws_flt = ws_dst + align_up((size_t)a.m * a.oc, 256);
+    // NCHW -> NHWC is a [C][HW] -> [HW][C] transpose per image
+    if ((rc = launch_transpose_s8(src, ws_src, a.n, a.ic, a.ih * a.iw, st)))
+        return rc;
+    if ((rc = launch_pack_filter(a, flt_oihw, ws_flt, st)))
+        return rc;
+    if ((rc = mb200_conv_bias_qs8_nhwc(p, ws_src, 0, ws_flt, bias, flt_scales, ws_dst, algo, st)))
+        return rc;
+    return launch_transpose_s8(ws_dst, dst, a.n, a.oh * a.ow, a.oc, st);
+}
+
+int mb200_pooling_qs8_nhwc(
+        const int8_t* src, int8_t* dst, int mode, int n, int c, int ih, int iw, int window_h,
+        int window_w, int stride_h, int stride_w, int pad_h, int pad_w, void* stream) {
+    if (!src || !dst)
+        return set_error(ST_NULL_PTR, "pooling tensor pointer is NULL");
+    if (mode < 0 || mode > 2)
+        return set_error(ST_NO_IMPLEMENT, "pooling mode %d not supported", mode);
+    if (n <= 0 || c <= 0 || ih <= 0 || iw <= 0 || window_h <= 0 || window_w <= 0 ||
+        stride_h <= 0 || stride_w <= 0 || pad_h < 0 || pad_w < 0 ||
+        ih + 2 * pad_h < window_h || iw + 2 * pad_w < window_w)
+        return set_error(ST_INVALID_LAYOUT, "pooling extents are invalid");
+    return launch_pooling(
+            src, dst, mode, n, c, ih, iw, window_h, window_w, stride_h, stride_w, pad_h, pad_w,
+            (cudaStream_t)stream);
+}
+
+int mb200_qelemwise_qs8(
+        const int8_t* a, const int8_t* b, int8_t* dst, int mode, size_t nr_elem, float scale_a,
+        float scale_b, float scale_dst, void* stream) {
+    if (mode < 0 || mode > 3)
+        return set_error(ST_NO_IMPLEMENT, "elemwise mode %d not supported", mode);
+    if (!a || !dst || (mode != MB200_QRELU && !b))
+        return set_error(ST_NULL_PTR, "elemwise tensor pointer is NULL");
+    if (nr_elem == 0)
+        return ST_SUCCESS;
+    return launch_qelemwise(
+            a, mode == MB200_QRELU ? a : b, dst, mode, nr_elem, scale_a, scale_b, scale_dst,
+            (cudaStream_t)stream);
+}
+
+int mb200_typecvt_qs32_qs8(
+        const int32_t* src, int8_t* dst, size_t nr_elem, float src_scale, float dst_scale,
+        void* stream) {
+    if (!src || !dst)
+        return set_error(ST_NULL_PTR, "typecvt tensor pointer is NULL");
+    if (nr_elem == 0)
+        return ST_SUCCESS;
+    return launch_typecvt_qs32_qs8(
+            src, dst, nr_elem, src_scale, dst_scale, (cudaStream_t)stream);
+}
+
+int mb200_relayout_nchw_to_nhwc_s8(
+        const int8_t* src, int8_t* dst, int n, int c, int h, int w, void* stream) {
+    if (!src || !dst)
+        return set_error(ST_NULL_PTR, "relayout tensor pointer is NULL");
+    return launch_transpose_s8(src, dst, n, c, h * w, (cudaStream_t)stream);
+}
+
+int mb200_relayout_nhwc_to_nchw_s8(
+        const int8_t* src, int8_t* dst, int n, int c, int h, int w, void* stream) {
+    if (!src || !dst)
+        return set_error(ST_NULL_PTR, "relayout tensor pointer is NULL");
+    return launch_transpose_s8(src, dst, n, h * w, c, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,65 @@
+// Internal declarations shared by the kernel translation units and the C ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace mb200 {
+
+// TinyNNStatus values used by this library (runtime/src/tinynn.h:9-24 in the reference)
+enum Status : int {
+    ST_SUCCESS = 0,
+    ST_NULL_PTR = 1,
+    ST_RUNTIME = 3,
+    ST_OUT_OF_RANGE = 4,
+    ST_NO_IMPLEMENT = 6,
+    ST_MODEL_PARSE = 7,
+    ST_OPEN_FILE = 8,
+    ST_MALLOC = 9,
+    ST_UNSUPPORTED_INST = 10,
+    ST_UNSUPPORTED_DTYPE = 11,
+    ST_INVALID_LAYOUT = 12,
+    ST_ERROR = 13,
+};
+
+// Everything a conv kernel needs, by value.
+struct ConvArgs {
+    int n, ic, ih, iw, oc, oh, ow;
+    int kh, kw, sh, sw, ph, pw, dh, dw, groups;
+    int m;  // n * oh * ow
+    int act;
+    int src_is_nchw;
+    float s_src, s_flt, s_dst;
+};
+
+// records a message for mb200_last_error() and returns `code`
+int set_error(int code, const char* fmt, ...);
+// cudaGetLastError() after a launch -> status
+int check_launch(const char* what);
+// the per-device int that kernels set when a bounded wait runs out
+int* device_status_word();
+
+int launch_pack_filter(const ConvArgs& a, const int8_t* src, int8_t* dst, cudaStream_t st);
+int launch_conv_direct(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
+        const float* flt_scales, int8_t* dst, int32_t* acc, cudaStream_t st);
+// tensor-core implicit GEMM; conv_umma_supported() says whether the shape qualifies
+bool conv_umma_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst);
+int launch_conv_umma(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
+        const float* flt_scales, int8_t* dst, cudaStream_t st);
+int launch_pooling(
+        const int8_t* src, int8_t* dst, int mode, int n, int c, int ih, int iw, int wh, int ww,
+        int sh, int sw, int ph, int pw, cudaStream_t st);
+int launch_qelemwise(
+        const int8_t* a, const int8_t* b, int8_t* dst, int mode, size_t nr_elem, float s0,
+        float s1, float s_dst, cudaStream_t st);
+int launch_typecvt_qs32_qs8(
+        const int32_t* src, int8_t* dst, size_t nr_elem, float s_src, float s_dst,
+        cudaStream_t st);
+int launch_transpose_s8(
+        const int8_t* src, int8_t* dst, int batch, int rows, int cols, cudaStream_t st);
+
+}  // namespace mb200

@@ -1,0 +1,298 @@
+// CUDA-core kernels of the hot path: the general (any shape) ConvBias, filter packing,
+// pooling, quantised elementwise, type conversion and layout transforms. The tensor-core
+// ConvBias lives in conv_umma.cu; everything here is bandwidth- or latency-bound work.
+#include "internal.h"
+
+namespace mb200 {
+
+// ------------------------------------------------------------------------------------------
+// filter packing: OIHW (dense) or [G][OCpg][ICpg][KH][KW] (group) -> [OC][KH][KW][ICpg]
+// ------------------------------------------------------------------------------------------
+__global__ void pack_filter_kernel(
+        const int8_t* __restrict__ src, int8_t* __restrict__ dst, int oc, int icpg, int kh,
+        int kw) {
+    const size_t total = (size_t)oc * icpg * kh * kw;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        // i indexes dst: [o][fy][fx][c]
+        int c = (int)(i % icpg);
+        size_t t = i / icpg;
+        int fx = (int)(t % kw);
+        t /= kw;
+        int fy = (int)(t % kh);
+        int o = (int)(t / kh);
+        dst[i] = src[(((size_t)o * icpg + c) * kh + fy) * kw + fx];
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// general direct ConvBias. One thread per (output pixel, output channel), channel fastest,
+// so a warp shares one input window (broadcast loads) and writes 32 contiguous bytes.
+// ------------------------------------------------------------------------------------------
+template <bool kRequant>
+__global__ void __launch_bounds__(256) conv_direct_kernel(
+        ConvArgs a, const int8_t* __restrict__ src, const int8_t* __restrict__ flt,
+        const int32_t* __restrict__ bias, const float* __restrict__ flt_scales,
+        int8_t* __restrict__ dst, int32_t* __restrict__ acc_out) {
+    const size_t total = (size_t)a.m * a.oc;
+    const int icpg = a.ic / a.groups, ocpg = a.oc / a.groups;
+    const bool vec4 = !a.src_is_nchw && (icpg % 4 == 0);
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int o = (int)(idx % a.oc);
+        const int m = (int)(idx / a.oc);
+        const int ow_ = m % a.ow;
+        const int t = m / a.ow;
+        const int oh_ = t % a.oh;
+        const int n = t / a.oh;
+        const int g = o / ocpg;
+        const int8_t* w = flt + (size_t)o * a.kh * a.kw * icpg;
+        int acc = 0;
+        for (int fy = 0; fy < a.kh; ++fy) {
+            const int iy = oh_ * a.sh + fy * a.dh - a.ph;
+            if ((unsigned)iy >= (unsigned)a.ih)
+                continue;
+            for (int fx = 0; fx < a.kw; ++fx) {
+                const int ix = ow_ * a.sw + fx * a.dw - a.pw;
+                if ((unsigned)ix >= (unsigned)a.iw)
+                    continue;
+                const int8_t* wk = w + (size_t)(fy * a.kw + fx) * icpg;
+                if (vec4) {
+                    const int8_t* s =
+                            src + (((size_t)n * a.ih + iy) * a.iw + ix) * a.ic + g * icpg;
+                    const int* s4 = reinterpret_cast<const int*>(s);
+                    const int* w4 = reinterpret_cast<const int*>(wk);
+                    for (int c = 0; c < icpg / 4; ++c)
+                        acc = __dp4a(__ldg(s4 + c), __ldg(w4 + c), acc);
+                } else if (!a.src_is_nchw) {
+                    const int8_t* s =
+                            src + (((size_t)n * a.ih + iy) * a.iw + ix) * a.ic + g * icpg;
+                    for (int c = 0; c < icpg; ++c)
+                        acc += (int)s[c] * (int)wk[c];
+                } else {
+                    const size_t plane = (size_t)a.ih * a.iw;
+                    const int8_t* s = src + ((size_t)n * a.ic + g * icpg) * plane +
+                                      (size_t)iy * a.iw + ix;
+                    for (int c = 0; c < icpg; ++c)
+                        acc += (int)s[c * plane] * (int)wk[c];
+                }
+            }
+        }
+        if (bias)
+            acc += bias[o];
+        if (kRequant) {
+            const float sf = flt_scales ? flt_scales[o] : a.s_flt;
+            dst[idx] = (int8_t)requant_conv(acc, a.s_src, sf, a.s_dst, a.act);
+        } else {
+            acc_out[idx] = acc;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// pooling, NHWC, one thread per output element (channel fastest -> coalesced)
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) pooling_kernel(
+        const int8_t* __restrict__ src, int8_t* __restrict__ dst, int mode, int n, int c, int ih,
+        int iw, int oh, int ow, int wh, int ww, int sh, int sw, int ph, int pw) {
+    const size_t total = (size_t)n * oh * ow * c;
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int ch = (int)(idx % c);
+        size_t t = idx / c;
+        const int x = (int)(t % ow);
+        t /= ow;
+        const int y = (int)(t % oh);
+        const int b = (int)(t / oh);
+        int mx = -128, sum = 0, count = 0;
+        for (int fy = 0; fy < wh; ++fy) {
+            const int iy = y * sh + fy - ph;
+            if ((unsigned)iy >= (unsigned)ih)
+                continue;
+            for (int fx = 0; fx < ww; ++fx) {
+                const int ix = x * sw + fx - pw;
+                if ((unsigned)ix >= (unsigned)iw)
+                    continue;
+                const int v = src[(((size_t)b * ih + iy) * iw + ix) * c + ch];
+                mx = v > mx ? v : mx;
+                sum += v;
+                ++count;
+            }
+        }
+        int r;
+        if (mode == 0) {
+            r = mx;
+        } else {
+            // roundf((float)sum / count), stored through an int (Pooling.cpp:131-146)
+            const float d = (mode == 1) ? (float)(wh * ww) : (float)count;
+            r = f32_to_i32_x86(roundf(__fdiv_rn(__int2float_rn(sum), d)));
+        }
+        dst[idx] = (int8_t)r;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// quantised elementwise, same-shape operands, 16 bytes per thread
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ int qelem_one(
+        int mode, int v0, int v1, float s0, float s1, float scale_div, float scale_mul) {
+    if (mode == 0) {  // QADD: (s0*v0 + s1*v1) * scale_div
+        float x = __fmul_rn(
+                __fadd_rn(__fmul_rn(s0, __int2float_rn(v0)), __fmul_rn(s1, __int2float_rn(v1))),
+                scale_div);
+        return fp32_to_int8(x);
+    } else if (mode == 1) {  // QFUSE_ADD_RELU
+        float t = __fadd_rn(__fmul_rn(s0, __int2float_rn(v0)), __fmul_rn(s1, __int2float_rn(v1)));
+        t = t > 0.f ? t : 0.f;
+        return fp32_to_int8(__fmul_rn(t, scale_div));
+    } else if (mode == 2) {  // QMUL: v0*v1*scale_mul, the product formed in int first
+        return fp32_to_int8(__fmul_rn(__int2float_rn(v0 * v1), scale_mul));
+    } else {  // QRELU
+        float t = __fmul_rn(s0, __int2float_rn(v0));
+        t = t > 0.f ? t : 0.f;
+        return fp32_to_int8(__fmul_rn(t, scale_div));
+    }
+}
+
+__global__ void __launch_bounds__(256) qelemwise_kernel(
+        const int8_t* __restrict__ a, const int8_t* __restrict__ b, int8_t* __restrict__ dst,
+        int mode, size_t nr_elem, float s0, float s1, float scale_div, float scale_mul,
+        int vec_ok) {
+    const size_t nvec = vec_ok ? nr_elem / 16 : 0;
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    const size_t nthr = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = tid; i < nvec; i += nthr) {
+        const int4 va = __ldg(reinterpret_cast<const int4*>(a) + i);
+        int4 vb = make_int4(0, 0, 0, 0);
+        if (mode != 3)
+            vb = __ldg(reinterpret_cast<const int4*>(b) + i);
+        const int wa[4] = {va.x, va.y, va.z, va.w};
+        const int wb[4] = {vb.x, vb.y, vb.z, vb.w};
+        int wo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int q[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int v0 = (int)(int8_t)(wa[j] >> (8 * k));
+                const int v1 = (int)(int8_t)(wb[j] >> (8 * k));
+                q[k] = qelem_one(mode, v0, v1, s0, s1, scale_div, scale_mul);
+            }
+            wo[j] = (int)pack4(q[0], q[1], q[2], q[3]);
+        }
+        reinterpret_cast<int4*>(dst)[i] = make_int4(wo[0], wo[1], wo[2], wo[3]);
+    }
+    for (size_t i = nvec * 16 + tid; i < nr_elem; i += nthr) {
+        const int v1 = (mode != 3) ? (int)b[i] : 0;
+        dst[i] = (int8_t)qelem_one(mode, (int)a[i], v1, s0, s1, scale_div, scale_mul);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// typecvt qsi32 -> qsi8: saturate(roundf(val * src_scale / dst_scale))
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) typecvt_qs32_qs8_kernel(
+        const int32_t* __restrict__ src, int8_t* __restrict__ dst, size_t nr_elem, float s_src,
+        float s_dst) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nr_elem;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const float x = __fdiv_rn(__fmul_rn(__int2float_rn(src[i]), s_src), s_dst);
+        dst[i] = (int8_t)fp32_to_int8(x);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// [R][C] -> [C][R] byte transpose per batch item, 32x32 tiles through shared memory
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) transpose_s8_kernel(
+        const int8_t* __restrict__ src, int8_t* __restrict__ dst, int rows, int cols) {
+    __shared__ int8_t tile[32][33];
+    const size_t base = (size_t)blockIdx.z * rows * cols;
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int r = r0 + j, c = c0 + threadIdx.x;
+        if (r < rows && c < cols)
+            tile[j][threadIdx.x] = src[base + (size_t)r * cols + c];
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int c = c0 + j, r = r0 + threadIdx.x;
+        if (r < rows && c < cols)
+            dst[base + (size_t)c * rows + r] = tile[threadIdx.x][j];
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// host launchers
+// ------------------------------------------------------------------------------------------
+static int grid_for(size_t work, int block) {
+    size_t g = (work + block - 1) / block;
+    const size_t cap = (size_t)148 * 16;
+    return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+int launch_pack_filter(
+        const ConvArgs& a, const int8_t* src, int8_t* dst, cudaStream_t st) {
+    const int icpg = a.ic / a.groups;
+    const size_t total = (size_t)a.oc * icpg * a.kh * a.kw;
+    pack_filter_kernel<<<grid_for(total, 256), 256, 0, st>>>(src, dst, a.oc, icpg, a.kh, a.kw);
+    return check_launch("pack_filter");
+}
+
+int launch_conv_direct(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
+        const float* flt_scales, int8_t* dst, int32_t* acc, cudaStream_t st) {
+    const size_t total = (size_t)a.m * a.oc;
+    const int grid = grid_for(total, 256);
+    if (acc)
+        conv_direct_kernel<false><<<grid, 256, 0, st>>>(a, src, flt, bias, flt_scales, dst, acc);
+    else
+        conv_direct_kernel<true><<<grid, 256, 0, st>>>(a, src, flt, bias, flt_scales, dst, acc);
+    return check_launch("conv_direct");
+}
+
+int launch_pooling(
+        const int8_t* src, int8_t* dst, int mode, int n, int c, int ih, int iw, int wh, int ww,
+        int sh, int sw, int ph, int pw, cudaStream_t st) {
+    const int oh = (ih + 2 * ph - wh) / sh + 1, ow = (iw + 2 * pw - ww) / sw + 1;
+    const size_t total = (size_t)n * oh * ow * c;
+    pooling_kernel<<<grid_for(total, 256), 256, 0, st>>>(
+            src, dst, mode, n, c, ih, iw, oh, ow, wh, ww, sh, sw, ph, pw);
+    return check_launch("pooling");
+}
+
+int launch_qelemwise(
+        const int8_t* a, const int8_t* b, int8_t* dst, int mode, size_t nr_elem, float s0,
+        float s1, float s_dst, cudaStream_t st) {
+    // scale_div = 1.f / scale_dst; scale_mul = s0 * s1 * scale_div, computed on the host in
+    // float exactly like the reference's generated C (ElemwiseMultiType.cpp:158-159)
+    volatile float scale_div = 1.f / s_dst;
+    volatile float t = s0 * s1;
+    volatile float scale_mul = t * scale_div;
+    const int vec_ok = (((uintptr_t)a | (uintptr_t)b | (uintptr_t)dst) & 15) == 0;
+    const size_t work = nr_elem / 16 + 1;
+    qelemwise_kernel<<<grid_for(work, 256), 256, 0, st>>>(
+            a, b, dst, mode, nr_elem, s0, s1, scale_div, scale_mul, vec_ok);
+    return check_launch("qelemwise");
+}
+
+int launch_typecvt_qs32_qs8(
+        const int32_t* src, int8_t* dst, size_t nr_elem, float s_src, float s_dst,
+        cudaStream_t st) {
+    typecvt_qs32_qs8_kernel<<<grid_for(nr_elem, 256), 256, 0, st>>>(
+            src, dst, nr_elem, s_src, s_dst);
+    return check_launch("typecvt_qs32_qs8");
+}
+
+int launch_transpose_s8(
+        const int8_t* src, int8_t* dst, int batch, int rows, int cols, cudaStream_t st) {
+    if (batch <= 0 || rows <= 0 || cols <= 0)
+        return 0;
+    if (batch > 65535)
+        return set_error(4, "transpose: batch %d exceeds the grid z limit", batch);
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch), block(32, 8);
+    transpose_s8_kernel<<<grid, block, 0, st>>>(src, dst, rows, cols);
+    return check_launch("transpose_s8");
+}
+
+}  // namespace mb200

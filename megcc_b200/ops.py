@@ -1,0 +1,124 @@
+"""Operator calls over device buffers (torch tensors are used only as device memory).
+
+Each function mirrors one kernel family of the reference's KernelGen and calls straight
+into the C ABI of libmegcc_b200.so on the current torch CUDA stream.
+"""
+import ctypes as C
+
+import torch
+
+from ._lib import ConvParam, check, lib
+
+ACT = {"IDENTITY": 0, "RELU": 1, "H_SWISH": 2}
+POOL = {"MAX": 0, "AVERAGE": 1, "AVERAGE_COUNT_EXCLUDE_PADDING": 2}
+QELEM = {"QADD": 0, "QFUSE_ADD_RELU": 1, "QMUL": 2, "QRELU": 3}
+ALGO = {"auto": 0, "direct": 1, "umma": 2}
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def conv_param(n, ic, ih, iw, oc, kh, kw, stride, pad, groups, act, s_src, s_flt, s_dst,
+               dilate=1):
+    p = ConvParam()
+    p.n, p.ic, p.ih, p.iw, p.oc, p.kh, p.kw = n, ic, ih, iw, oc, kh, kw
+    p.stride_h = p.stride_w = stride
+    p.pad_h = p.pad_w = pad
+    p.dilate_h = p.dilate_w = dilate
+    p.groups = groups
+    p.nonline = ACT[act]
+    p.src_scale, p.flt_scale, p.dst_scale = s_src, s_flt, s_dst
+    return p
+
+
+def out_hw(p):
+    oh = (p.ih + 2 * p.pad_h - p.dilate_h * (p.kh - 1) - 1) // p.stride_h + 1
+    ow = (p.iw + 2 * p.pad_w - p.dilate_w * (p.kw - 1) - 1) // p.stride_w + 1
+    return oh, ow
+
+
+def pack_filter(p, flt_oihw):
+    """OIHW / [G,OCpg,ICpg,KH,KW] int8 device tensor -> K-major packed filter."""
+    packed = torch.empty(lib().mb200_conv_packed_filter_bytes(C.byref(p)), dtype=torch.int8,
+                         device=flt_oihw.device)
+    check(lib().mb200_conv_pack_filter(C.byref(p), _ptr(flt_oihw), _ptr(packed), _stream()))
+    return packed
+
+
+def conv_bias_qs8_nhwc(p, src, flt_packed, bias, dst=None, flt_scales=None, algo="auto",
+                       src_is_nchw=False):
+    oh, ow = out_hw(p)
+    if dst is None:
+        dst = torch.empty((p.n, oh, ow, p.oc), dtype=torch.int8, device=src.device)
+    check(lib().mb200_conv_bias_qs8_nhwc(
+        C.byref(p), _ptr(src), int(src_is_nchw), _ptr(flt_packed), _ptr(bias), _ptr(flt_scales),
+        _ptr(dst), ALGO[algo], _stream()))
+    return dst
+
+
+def conv_acc_qs8_nhwc(p, src, flt_packed, bias):
+    oh, ow = out_hw(p)
+    acc = torch.empty((p.n, oh, ow, p.oc), dtype=torch.int32, device=src.device)
+    check(lib().mb200_conv_acc_qs8_nhwc(C.byref(p), _ptr(src), _ptr(flt_packed), _ptr(bias),
+                                        _ptr(acc), _stream()))
+    return acc
+
+
+def conv_bias_qs8_nchw(p, src, flt_oihw, bias, flt_scales=None, algo="auto"):
+    """ConvBias in the reference's own layouts (NCHW activations, OIHW filter)."""
+    oh, ow = out_hw(p)
+    dst = torch.empty((p.n, p.oc, oh, ow), dtype=torch.int8, device=src.device)
+    nbytes = lib().mb200_conv_bias_qs8_nchw_workspace(C.byref(p))
+    ws = torch.empty(nbytes + 256, dtype=torch.int8, device=src.device)
+    off = (-ws.data_ptr()) % 256
+    check(lib().mb200_conv_bias_qs8_nchw(
+        C.byref(p), _ptr(src), _ptr(flt_oihw), _ptr(bias), _ptr(flt_scales), _ptr(dst),
+        C.c_void_p(ws.data_ptr() + off), nbytes, ALGO[algo], _stream()))
+    return dst
+
+
+def pooling_qs8_nhwc(src, mode, window, stride, pad):
+    n, ih, iw, c = src.shape
+    oh, ow = (ih + 2 * pad - window) // stride + 1, (iw + 2 * pad - window) // stride + 1
+    dst = torch.empty((n, oh, ow, c), dtype=torch.int8, device=src.device)
+    check(lib().mb200_pooling_qs8_nhwc(_ptr(src), _ptr(dst), POOL[mode], n, c, ih, iw, window,
+                                       window, stride, stride, pad, pad, _stream()))
+    return dst
+
+
+def qelemwise_qs8(mode, a, b, s0, s1, s_dst):
+    dst = torch.empty_like(a)
+    check(lib().mb200_qelemwise_qs8(_ptr(a), _ptr(b), _ptr(dst), QELEM[mode], a.numel(), s0, s1,
+                                    s_dst, _stream()))
+    return dst
+
+
+def typecvt_qs32_qs8(src, s_src, s_dst):
+    dst = torch.empty(src.shape, dtype=torch.int8, device=src.device)
+    check(lib().mb200_typecvt_qs32_qs8(_ptr(src), _ptr(dst), src.numel(), s_src, s_dst, _stream()))
+    return dst
+
+
+def nchw_to_nhwc(src):
+    n, c, h, w = src.shape
+    dst = torch.empty((n, h, w, c), dtype=torch.int8, device=src.device)
+    check(lib().mb200_relayout_nchw_to_nhwc_s8(_ptr(src), _ptr(dst), n, c, h, w, _stream()))
+    return dst
+
+
+def nhwc_to_nchw(src):
+    n, h, w, c = src.shape
+    dst = torch.empty((n, c, h, w), dtype=torch.int8, device=src.device)
+    check(lib().mb200_relayout_nhwc_to_nchw_s8(_ptr(src), _ptr(dst), n, c, h, w, _stream()))
+    return dst
+
+
+def device_status():
+    s = C.c_int(0)
+    check(lib().mb200_device_status(_stream(), C.byref(s)))
+    return s.value

@@ -1,0 +1,181 @@
+"""Parity of the CUDA operators, called through the C ABI, with the CPU oracle and with the
+golden vectors produced by the reference's own x86 kernels. Bit-exact everywhere."""
+import numpy as np
+import pytest
+
+import cases
+import golden_util as G
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from megcc_b200 import ops as O
+    return O
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def run_conv_nchw(ops, c, algo="auto", flt_scales=None):
+    src, flt, bias = cases.conv_inputs(c)
+    s0, s1, s2 = c["scales"]
+    p = ops.conv_param(c["n"], c["ic"], c["h"], c["w"], c["oc"], c["k"], c["k"], c["stride"],
+                       c["pad"], c["groups"], c["act"], s0, s1, s2)
+    out = ops.conv_bias_qs8_nchw(p, dev(src), dev(flt), None if bias is None else dev(bias),
+                                 None if flt_scales is None else dev(flt_scales), algo=algo)
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), (src, flt, bias)
+
+
+def test_conv_naive_catalogue_golden(ops):
+    for c in cases.conv_naive_catalogue():
+        out, ins = run_conv_nchw(ops, c)
+        G.check("conv_bias_qs8", c["name"], out, *ins)
+
+
+def test_conv_im2col_catalogue_golden(ops):
+    for c in cases.conv_im2col_catalogue():
+        out, ins = run_conv_nchw(ops, c)
+        G.check("conv_bias_qs8", c["name"], out, *ins)
+
+
+def test_conv_model_shapes_golden(ops):
+    for c in cases.conv_model_shapes():
+        out, ins = run_conv_nchw(ops, c)
+        G.check("conv_bias_qs8", c["name"], out, *ins)
+
+
+@pytest.mark.parametrize("algo", ["direct", "umma"])
+@pytest.mark.parametrize("dst_scale", [0.1, 5.0])
+def test_conv_cfg1_golden(ops, algo, dst_scale):
+    c = cases.conv_cfg1(dst_scale)
+    out, ins = run_conv_nchw(ops, c, algo=algo)
+    G.check("conv_bias_qs8", c["name"], out, *ins)
+    assert ops.device_status() == 0
+
+
+UMMA_CASES = [
+    # name, n, ic, oc, h, w, k, stride, pad, act
+    ("s1_64", 2, 64, 64, 32, 32, 3, 1, 1, "RELU"),
+    ("s1_64_identity", 1, 64, 64, 56, 56, 3, 1, 1, "IDENTITY"),
+    ("s1_64_hswish", 1, 64, 64, 56, 56, 3, 1, 1, "H_SWISH"),
+    ("ragged_m", 3, 64, 64, 27, 29, 3, 1, 1, "RELU"),
+    ("s2_64_128", 2, 64, 128, 56, 56, 3, 2, 1, "RELU"),
+    ("proj_64_128", 2, 64, 128, 56, 56, 1, 2, 0, "IDENTITY"),
+    ("s1_128", 2, 128, 128, 28, 28, 3, 1, 1, "RELU"),
+    ("s2_128_256", 2, 128, 256, 28, 28, 3, 2, 1, "RELU"),
+    ("s1_256", 4, 256, 256, 14, 14, 3, 1, 1, "RELU"),
+    ("s1_512", 6, 512, 512, 7, 7, 3, 1, 1, "RELU"),
+    ("fc_512_1000", 256, 512, 1000, 1, 1, 1, 1, 0, "IDENTITY"),
+    ("pw_1024", 3, 1024, 1024, 7, 7, 1, 1, 0, "RELU"),
+    ("k5_s1", 1, 64, 72, 40, 40, 5, 1, 2, "RELU"),
+    ("k7_s2_p3", 1, 64, 64, 48, 48, 7, 2, 3, "RELU"),
+    ("nopad_k3", 1, 64, 64, 50, 50, 3, 1, 0, "RELU"),
+    ("s3", 1, 64, 64, 50, 47, 3, 3, 1, "RELU"),
+]
+
+
+@pytest.mark.parametrize("case", UMMA_CASES, ids=[c[0] for c in UMMA_CASES])
+def test_conv_umma_matches_oracle(ops, oracle, case):
+    name, n, ic, oc, h, w, k, stride, pad, act = case
+    c = dict(name="umma_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=stride, pad=pad,
+             groups=1, act=act, range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.37 * (ic * k * k / 576.0) ** 0.5 + 0.4))
+    out, (src, flt, bias) = run_conv_nchw(ops, c, algo="umma")
+    s0, s1, s2 = c["scales"]
+    want = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, s1, s2, act)
+    bad = int((out != want).sum())
+    assert bad == 0, f"{bad}/{want.size} differ; first at {np.argwhere(out != want)[:4].tolist()}"
+    assert ops.device_status() == 0
+    # the result must exercise the requantisation, not sit on the clamps
+    assert (np.abs(want.astype(int)) < 127).mean() > 0.3
+
+
+def test_conv_umma_per_channel_scales(ops, oracle):
+    c = dict(name="umma_perchannel", n=2, ic=64, oc=128, h=32, w=32, k=3, stride=1, pad=1,
+             groups=1, act="RELU", range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.8))
+    sf = cases.rng_for("umma_perchannel_scales").uniform(0.005, 0.02, 128).astype(np.float32)
+    out, (src, flt, bias) = run_conv_nchw(ops, c, algo="umma", flt_scales=sf)
+    want = oracle.conv_bias_qs8(src, flt, bias, 1, 1, 0.05, sf, 0.8, "RELU")
+    assert (out == want).all()
+
+
+def test_conv_accumulators_match_oracle(ops, oracle):
+    c = dict(name="acc_parity", n=1, ic=20, oc=20, h=10, w=10, k=3, stride=1, pad=0, groups=1,
+             act="IDENTITY", range=(30, 50), scales=(1.0, 2.0, 4.0))
+    src, flt, bias = cases.conv_inputs(c)
+    p = ops.conv_param(1, 20, 10, 10, 20, 3, 3, 1, 0, 1, "IDENTITY", 1.0, 2.0, 4.0)
+    packed = ops.pack_filter(p, dev(flt))
+    acc = ops.conv_acc_qs8_nhwc(p, ops.nchw_to_nhwc(dev(src)), packed, dev(bias))
+    want = oracle.conv_bias_qs8(src, flt, bias, 1, 0, 1.0, 2.0, 4.0, return_acc=True)[1]
+    assert (acc.cpu().numpy().transpose(0, 3, 1, 2) == want).all()
+
+
+def test_first_layer_reads_nchw_in_place(ops, oracle):
+    c = dict(name="stem_nchw", n=2, ic=3, oc=64, h=64, w=64, k=7, stride=2, pad=3, groups=1,
+             act="RELU", range=(-128, 127), bias_range=(-1000, 1000), scales=(0.05, 0.01, 0.9))
+    src, flt, bias = cases.conv_inputs(c)
+    p = ops.conv_param(2, 3, 64, 64, 64, 7, 7, 2, 3, 1, "RELU", 0.05, 0.01, 0.9)
+    packed = ops.pack_filter(p, dev(flt))
+    out = ops.conv_bias_qs8_nhwc(p, dev(src), packed, dev(bias), src_is_nchw=True)
+    want = oracle.conv_bias_qs8(src, flt, bias, 2, 3, 0.05, 0.01, 0.9, "RELU")
+    assert (out.cpu().numpy().transpose(0, 3, 1, 2) == want).all()
+
+
+def test_pooling_golden(ops):
+    for c in cases.pool_catalogue():
+        x = cases.pool_input(c)
+        y = ops.pooling_qs8_nhwc(ops.nchw_to_nhwc(dev(x)), c["mode"], c["window"], c["stride"],
+                                 c["pad"])
+        out = ops.nhwc_to_nchw(y).cpu().numpy()
+        G.check("pooling_qs8", c["name"], out, x)
+
+
+def test_qelemwise_golden(ops):
+    for c in cases.qelem_catalogue():
+        if c["a"] != c["b"]:
+            continue  # broadcast forms are not on the model path
+        a, b = cases.qelem_inputs(c)
+        s0, s1, s2 = c["scales"]
+        out = ops.qelemwise_qs8(c["mode"], dev(a), dev(b), s0, s1, s2).cpu().numpy()
+        G.check("qelemwise", c["name"], out, a, b)
+
+
+def test_qrelu_matches_oracle(ops, oracle):
+    a = cases.rng_for("qrelu").integers(-128, 128, (3, 5, 7, 11), dtype=np.int8)
+    out = ops.qelemwise_qs8("QRELU", dev(a), None, 0.3, 1.0, 0.7).cpu().numpy()
+    assert (out == oracle.qelemwise("QRELU", a, None, 0.3, 1.0, 0.7)).all()
+
+
+def test_typecvt_golden(ops):
+    for c in cases.typecvt_catalogue():
+        x = cases.typecvt_input(c)
+        out = ops.typecvt_qs32_qs8(dev(x), c["s_src"], c["s_dst"]).cpu().numpy()
+        G.check("typecvt_qs32_qs8", c["name"], out, x)
+
+
+def test_relayout_round_trip(ops):
+    x = cases.rng_for("relayout").integers(-128, 128, (3, 37, 19, 23), dtype=np.int8)
+    y = ops.nchw_to_nhwc(dev(x))
+    assert (y.cpu().numpy() == x.transpose(0, 2, 3, 1)).all()
+    assert (ops.nhwc_to_nchw(y).cpu().numpy() == x).all()
+
+
+def test_bad_arguments_return_status_not_trap(ops):
+    from megcc_b200._lib import MegccError
+    p = ops.conv_param(1, 6, 8, 8, 4, 3, 3, 1, 1, 4, "RELU", 1, 1, 1)  # 6 % 4 != 0
+    with pytest.raises(MegccError) as e:
+        ops.pack_filter(p, torch.zeros(10, dtype=torch.int8, device="cuda"))
+    assert e.value.status == 12
+    p = ops.conv_param(1, 3, 8, 8, 8, 3, 3, 1, 1, 1, "RELU", 1, 1, 1)
+    with pytest.raises(MegccError) as e:
+        ops.conv_bias_qs8_nhwc(p, torch.zeros(192, dtype=torch.int8, device="cuda"),
+                               torch.zeros(216, dtype=torch.int8, device="cuda"), None,
+                               algo="umma")
+    assert e.value.status == 6
