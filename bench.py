@@ -1,0 +1,303 @@
+#!/usr/bin/env python
+"""Headline benchmark: ResNet-18 int8, batch 256 per GPU, img/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One process per GPU (the driver starts N of them with torch.distributed.run). A step is
+one forward of a 256-image batch through the compiled model:
+
+  value     img/s with the input batch already in device memory and the logits left there
+            (CUDA-graph replay through LITE_forward / LITE_wait), timed with CUDA events on
+            the network's stream, max over ranks
+  e2e       the same through the host-buffer boundary a LITE_* user sees: pinned host input
+            copied in and logits copied out inside every timed step
+  roofline  the tcgen05 ConvBias kernel: algorithmic int8 ops of every launch / its CUDA
+            event time, against 2 x the measured bf16 tensor peak
+  cpu_baseline  the reference's own generated x86 kernels (oracle/_ref) walking the same
+            network on the host cores, one image per thread (a bounded sample)
+
+--impl reference times only that CPU path and prints it in the same JSON shape.
+All data is synthetic (seeded uniform int8) and weights are random-init.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCH = 256
+METRIC = "resnet18_int8_images_per_second"
+UNIT = "img/s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_burst=p["bf16_tflops"],
+                    bf16_sustained=p["bf16_tflops_sustained"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_burst=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
+                stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower() == "active":
+                    reasons.add(n)
+        sm.sort()
+        return dict(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    samples=len(sm), reasons=sorted(reasons))
+
+
+def cpu_reference_run(spec, steps, warmup, threads):
+    """The reference's own x86 kernels on the host: each step walks the network once per
+    thread on one image, all threads in parallel. Returns (img/s, seconds per step)."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import netwalk
+    from oracle import oracle as O
+
+    if O.ref_lib() is None:
+        kind, use_ref = "port", False
+        O.lib()
+    else:
+        kind, use_ref = "reference", True
+    rng = np.random.default_rng(1234)
+    xs = [rng.integers(-128, 128, (1, 3, 224, 224), dtype=np.int8) for _ in range(threads)]
+
+    def one_step():
+        ts = [threading.Thread(target=netwalk.run, args=(spec, xs[i], O, use_ref))
+              for i in range(threads)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+
+    for _ in range(warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    dt = time.perf_counter() - t0
+    return threads * steps / dt, dt / steps, kind
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="megcc_b200", choices=["megcc_b200", "reference"])
+    ap.add_argument("--cpu-threads", type=int, default=0)
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    from megcc_b200 import zoo
+    spec = zoo.resnet18()
+    threads = args.cpu_threads or min(os.cpu_count() or 1, 64)
+    config = dict(workload="resnet18_int8_b256", per_gpu_batch=BATCH, global_batch=BATCH * world,
+                  input="3x224x224 int8", classes=1000, scales="per-tensor",
+                  parallelism=f"batch-sharded x{world}, no collective",
+                  l2="working set per step 1.7 GB, far larger than the 126 MB L2",
+                  macs_per_image=spec.macs_per_image())
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
+        ips, sec, kind = cpu_reference_run(spec, steps, warmup, threads)
+        sample = (f"{steps} steps x {threads} images (one per thread) of the same network, "
+                  f"{warmup} warm-up; the {BATCH}-image batch is not run in full on the CPU")
+        print(json.dumps(dict(
+            impl="reference", metric=METRIC, value=ips, unit=UNIT, n_gpus=args.gpus,
+            steps=steps, warmup=warmup, ms_per_step=sec * 1e3, higher_is_better=True,
+            scaling="weak", vs_baseline=None, dtype="int8", data="synthetic", config=config,
+            cpu_baseline=dict(value=ips, unit=UNIT, cores=threads, kind=kind, sample=sample),
+            e2e=dict(value=ips, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))))
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    from megcc_b200 import lite
+
+    model = spec.to_graph().compile([BATCH])
+    rng = np.random.default_rng(1000 + rank)
+    x_host = torch.from_numpy(
+        rng.integers(-128, 128, (BATCH, 3, 224, 224), dtype=np.int8)).pin_memory()
+    x_dev = x_host.cuda()
+    in_bytes = x_host.numel()
+
+    # ---- device-resident arm: input in HBM, logits stay in HBM ----
+    net = lite.Network(model, device_id=local_rank, device_io=("fc:out",))
+    stream = torch.cuda.ExternalStream(net.stream())
+    ops_per_step = len([l for l in spec.layers])
+    net.set_input_ptr("data", x_dev.data_ptr(), in_bytes)
+    for _ in range(max(args.warmup, 3)):
+        net.forward()
+    net.wait()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        net.forward()
+    e1.record(stream)
+    net.wait()
+    barrier()
+    ms_dev = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop()
+
+    # ---- end-to-end arm: pinned host input in, logits out, every step ----
+    net2 = lite.Network(model, device_id=local_rank)
+    out_bytes = net2.tensor_bytes("fc:out", lite.LITE_OUTPUT)
+    net2.set_input_ptr("data", x_host.data_ptr(), in_bytes)
+    stream2 = torch.cuda.ExternalStream(net2.stream())
+    for _ in range(max(args.warmup, 3)):
+        net2.forward()
+        net2.wait()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    checksum = 0
+    f0.record(stream2)
+    for _ in range(args.steps):
+        net2.forward()
+        net2.wait()
+        checksum ^= int(np.frombuffer(
+            (lite.C.c_int8 * 8).from_address(net2.output_ptr("fc:out")), dtype=np.int8)[0])
+    f1.record(stream2)
+    f1.synchronize()
+    barrier()
+    ms_e2e = max_over_ranks(f0.elapsed_time(f1))
+
+    # ---- per-kernel pass for the roofline of the dominant kernel ----
+    roofline = None
+    cpu_baseline = None
+    if rank == 0:
+        peaks = load_peaks()
+        net.set_profile(True)
+        for _ in range(5):
+            net.forward()
+            net.wait()
+        rows = net.profile()
+        net.set_profile(False)
+        shapes = spec.shapes
+        conv_ops = {}
+        for l in spec.layers:
+            if l["op"] == "conv":
+                oc, oh, ow = shapes[l["name"]]
+                ic = shapes[l["src"]][0]
+                k = l["flt"].shape[-1]
+                conv_ops[l["name"]] = 2.0 * BATCH * oc * oh * ow * (ic // l["groups"]) * k * k
+        total_ms = sum(r[2] for r in rows)
+        # the tensor-core kernel handles every dense conv whose input channels are a
+        # multiple of 64: all of them except the 3-channel stem
+        umma = [(n, ms) for n, s, ms, c in rows if n in conv_ops and n != "stem" and c]
+        umma_ops = sum(conv_ops[n] for n, _ in umma)
+        umma_ms = sum(ms for _, ms in umma)
+        peak = 2.0 * peaks["bf16_sustained"]
+        achieved = umma_ops / (umma_ms * 1e-3) / 1e12 if umma_ms > 0 else 0.0
+        roofline = dict(
+            bound="tensor", kernel="conv_umma_kernel (tcgen05 kind::i8 implicit GEMM)",
+            achieved=achieved, peak=peak, unit="TOP/s", frac=achieved / peak, traffic=None,
+            launches_per_step=len(umma), share_of_step=umma_ms / total_ms if total_ms else None,
+            peak_note=f"2 x bf16 sustained ({peaks['source']}); int8 dense peak is not in "
+                      "MEASURED_PEAKS.json",
+            per_kernel_ms={n: round(ms, 4) for n, s, ms, c in rows})
+        ips_cpu, sec, kind = cpu_reference_run(spec, 2, 1, threads)
+        cpu_baseline = dict(
+            value=ips_cpu, unit=UNIT, cores=threads, kind=kind,
+            sample=f"2 steps x {threads} images (one per thread), 1 warm-up step")
+    net.close()
+    net2.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    images = BATCH * world * args.steps
+    value = images / (ms_dev * 1e-3)
+    line = dict(
+        metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps,
+        warmup=max(args.warmup, 3), ms_per_step=ms_dev / args.steps, higher_is_better=True,
+        scaling="weak", vs_baseline=None, dtype="int8", data="synthetic", config=config,
+        clocks=clocks, gpu_launches=ops_per_step * args.steps,
+        e2e=dict(value=images / (ms_e2e * 1e-3), unit=UNIT, ms_per_step=ms_e2e / args.steps,
+                 h2d_bytes_per_step=in_bytes, d2h_bytes_per_step=out_bytes),
+        roofline=roofline, cpu_baseline=cpu_baseline)
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

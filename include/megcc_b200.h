@@ -54,6 +54,11 @@ MB200_API const char* mb200_last_error(void);
  * (0 = healthy). Synchronises `stream`. */
 MB200_API int mb200_device_status(void* stream, int* status_host);
 
+/* Parses a tinynn model (root table MegCC.Model, runtime/schema/model.fbs) the way the
+ * runtime's loader does, without using a GPU, and writes a text summary into out.
+ * Returns TinyNN_ERROR_MODEL_PARSE (7) for a truncated or malformed buffer. */
+MB200_API int mb200_tinynn_describe(const void* model_mem, size_t size, char* out, size_t cap);
+
 /* ---- ConvBias, qint8 x qint8 -> int32 -> qint8 ------------------------------------
  * Replaces kernel_conv2d_<k>x<k>_NCHW_{DENSE,GROUP}_p.._s.._d.._qsi8qsi8qsi32qsi8[_bias][_ACT]
  * (compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:144-176, body :178-389). */

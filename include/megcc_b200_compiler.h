@@ -1,0 +1,84 @@
+/*
+ * Compile side of megcc_b200 (libmegcc_b200_compiler.so): describes a static-shape
+ * quantised network, asks the CUDA KernelGen pack for a kernel per operator, plans every
+ * tensor into one device arena and writes the tinynn model.
+ *
+ * It stands in for the part of the reference's mgb-to-tinynn pipeline that follows the
+ * importer: KernelMaterialization (compiler/lib/Dialect/Kernel/Transforms/
+ * KernelMaterialization.cpp:136-158,212-276: operator -> TContext -> first available
+ * KernelFunc), StaticMemoryPlanning (.../StaticMemoryPlanning.cpp:34-99: liveness ->
+ * offsets into one buffer) and the tinynn exporter (compiler/lib/Target/TinyNN/
+ * exporter.cpp:345-396,957-1001 and KernelExporter.cpp:15-66). The importer itself needs
+ * MegEngine and is out of scope; operators are added through the calls below instead.
+ *
+ * All functions return a tensor id (>= 0) or a negative value on error;
+ * mb200c_last_error() describes the failure. Host pointers throughout.
+ */
+#ifndef MEGCC_B200_COMPILER_H_
+#define MEGCC_B200_COMPILER_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MB200C_API __attribute__((visibility("default")))
+
+typedef struct mb200c_graph mb200c_graph;
+
+MB200C_API mb200c_graph* mb200c_graph_create(const char* model_name);
+MB200C_API void mb200c_graph_destroy(mb200c_graph* g);
+MB200C_API const char* mb200c_last_error(void);
+
+/* network input, qint8, model-visible layout NCHW; c/h/w are per image */
+MB200C_API int mb200c_add_input(mb200c_graph* g, const char* name, int c, int h, int w, float scale);
+
+/* ConvBias: operands src, filter, [bias], dst and attributes as
+ * compiler/lib/Conversion/MGBToKernel/MGBToKernel.cpp:236-283 passes them.
+ * flt: OIHW (groups == 1) or [G][OCpg][ICpg][KH][KW] int8; bias: [OC] int32 or NULL;
+ * channel_scales: NULL (per-tensor flt_scale) or [OC] floats (extension).
+ * nonline: "IDENTITY" | "RELU" | "H_SWISH". */
+MB200C_API int mb200c_add_conv_bias(
+        mb200c_graph* g, const char* name, int src, int oc, int kh, int kw, int stride, int pad,
+        int groups, const char* nonline, const int8_t* flt, float flt_scale,
+        const int32_t* bias, const float* channel_scales, float dst_scale);
+
+/* mode: "MAX" | "AVERAGE" | "AVERAGE_COUNT_EXCLUDE_PADDING" */
+MB200C_API int mb200c_add_pooling(
+        mb200c_graph* g, const char* name, int src, const char* mode, int window, int stride,
+        int pad);
+
+/* mode: "QADD" | "QFUSE_ADD_RELU" | "QMUL" | "QRELU" (b < 0 for QRELU) */
+MB200C_API int mb200c_add_qelemwise(
+        mb200c_graph* g, const char* name, const char* mode, int a, int b, float dst_scale);
+
+MB200C_API int mb200c_mark_output(mb200c_graph* g, int tensor);
+
+/* Compiles one DeviceModel (device CUDA_SM100) per batch size into a tinynn model.
+ * The returned bytes belong to the graph and stay valid until it is destroyed or
+ * compiled again. */
+MB200C_API int mb200c_compile(
+        mb200c_graph* g, const int* batches, int nr_batches, const uint8_t** bytes, size_t* len);
+
+/* after mb200c_compile: newline-separated kernel symbols in kernel_id order */
+MB200C_API const char* mb200c_kernel_symbols(mb200c_graph* g);
+/* arena bytes the planner needed for batches[i], and the sum of tensor sizes it would
+ * take without reuse */
+MB200C_API size_t mb200c_arena_bytes(mb200c_graph* g, int batch_index);
+MB200C_API size_t mb200c_unplanned_bytes(mb200c_graph* g, int batch_index);
+/* Writes the generated sources the reference's exporter would: kernels.h, kernels.c
+ * (tables + load_kernel_init_function) and one <symbol>.c per kernel. */
+MB200C_API int mb200c_export_kernels(mb200c_graph* g, const char* dir);
+
+/* KernelFunc probe used by the tests: 1 if the CUDA pack has an available ConvBias kernel
+ * for this description, and its symbol. */
+MB200C_API int mb200c_probe_conv_symbol(
+        int ic, int oc, int h, int w, int k, int stride, int pad, int groups, const char* nonline,
+        int with_bias, const char* format, char* symbol_out, size_t symbol_cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MEGCC_B200_COMPILER_H_ */

@@ -19,9 +19,36 @@ NVCC_FLAGS = [
 ]
 
 
+COMPILER_DIR = os.path.join(HERE, "compiler")
+COMPILER_LIB = os.path.join(HERE, "libmegcc_b200_compiler.so")
+
+
 def _sources():
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC)
                   if f.endswith((".cu", ".cpp")))
+
+
+def build_compiler(verbose=False, force=False):
+    """The compile-side library (KernelGen CUDA pack, planner, tinynn writer): host C++ only."""
+    srcs = sorted(os.path.join(COMPILER_DIR, f) for f in os.listdir(COMPILER_DIR)
+                  if f.endswith(".cpp"))
+    deps = srcs + [os.path.join(COMPILER_DIR, f) for f in os.listdir(COMPILER_DIR)
+                   if f.endswith(".h")]
+    deps += [os.path.join(CSRC, "tinynn_format.h"),
+             os.path.join(os.path.dirname(HERE), "include", "megcc_b200_compiler.h")]
+    if not force and not _stale(COMPILER_LIB, deps):
+        return COMPILER_LIB
+    # the distribution compiler: a g++ that links libstdc++ statically into a shared object
+    # yields a library that crashes when loaded next to another C++ runtime
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else os.environ.get("CXX", "g++")
+    cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall",
+           "-o", COMPILER_LIB] + srcs
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if verbose or r.returncode:
+        sys.stderr.write(r.stdout)
+    if r.returncode:
+        raise RuntimeError("building the compiler library failed")
+    return COMPILER_LIB
 
 
 def _stale(target, deps):
@@ -32,6 +59,7 @@ def _stale(target, deps):
 
 
 def build(verbose=False, force=False):
+    build_compiler(verbose, force)
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     srcs = _sources()
     deps = srcs + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]

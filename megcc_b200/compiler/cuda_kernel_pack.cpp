@@ -1,0 +1,396 @@
+#include "cuda_kernel_pack.h"
+
+#include <cmath>
+#include <sstream>
+
+using namespace megcc;
+using namespace megcc::KernelGen;
+using namespace megcc::KernelGen::Cuda;
+
+namespace {
+
+bool is_quant(const std::string& dtype, int bits) {
+    const std::string prefix = "qsi" + std::to_string(bits);
+    return dtype.compare(0, prefix.size(), prefix) == 0 &&
+           (dtype.size() == prefix.size() || dtype[prefix.size()] == '<');
+}
+
+// dtype string without its "<...>" parameter, as the reference's symbols spell it
+// (compiler/lib/KernelGen/Utils/SymbolHelper.h:9-24)
+std::string bare_dtype(const std::string& dtype) {
+    const auto p = dtype.find('<');
+    return p == std::string::npos ? dtype : dtype.substr(0, p);
+}
+
+std::string io_str(TContext* ctx) {
+    std::string s;
+    const int n = ctx->getAttrInt("nr_operands");
+    for (int i = 0; i < n; ++i)
+        s += bare_dtype(ctx->getAttrOprand("operand:" + std::to_string(i)).dtype);
+    return s;
+}
+
+CCOperand last_operand(TContext* ctx) {
+    return ctx->getAttrOprand("operand:" + std::to_string(ctx->getAttrInt("nr_operands") - 1));
+}
+
+// bias present iff there are more than 3 operands and operand 2 has a shape
+// (compiler/lib/KernelGen/Common/ConvKernel.h:10-21)
+bool has_bias(TContext* ctx) {
+    return ctx->getAttrInt("nr_operands") > 3 &&
+           ctx->getAttrOprand("operand:2").shape.size() > 0;
+}
+
+bool channel_broadcast_bias(TContext* ctx) {
+    const CCOperand b = ctx->getAttrOprand("operand:2");
+    if (b.shape.size() == 1)
+        return true;
+    return b.shape.size() == 4 && b.shape[0] == 1 && b.shape[2] == 1 && b.shape[3] == 1;
+}
+
+std::string nonline(TContext* ctx) {
+    return ctx->haveAttr("nonlineMode") ? ctx->getAttrStr("nonlineMode") : "IDENTITY";
+}
+
+int nonline_code(const std::string& m) {
+    return m == "RELU" ? 1 : m == "H_SWISH" ? 2 : 0;
+}
+
+struct Subst {
+    std::string text;
+    Subst& set(const std::string& key, const std::string& value) {
+        const std::string pat = "${" + key + "}";
+        for (size_t p = text.find(pat); p != std::string::npos; p = text.find(pat, p))
+            text.replace(p, pat.size(), value), p += value.size();
+        return *this;
+    }
+    Subst& set(const std::string& key, long long v) { return set(key, std::to_string(v)); }
+};
+
+}  // namespace
+
+std::string Cuda::GenStubPrologue() {
+    return "#include \"megcc_b200_runtime.h\"\n#include \"megcc_b200.h\"\n";
+}
+
+// ------------------------------------------------------------------------------------------
+// ConvBias
+// ------------------------------------------------------------------------------------------
+bool ConvBiasQS8::IsAvailable(TContext* ctx) const {
+    if (ctx->getAttrStr("format") != "NCHW" || ctx->getAttrStr("mode") != "CROSS_CORRELATION")
+        return false;
+    if (ctx->getAttrInt("nr_operands") < 3)
+        return false;
+    const CCOperand src = ctx->getAttrOprand("operand:0");
+    const CCOperand flt = ctx->getAttrOprand("operand:1");
+    const CCOperand dst = last_operand(ctx);
+    if (!is_quant(src.dtype, 8) || !is_quant(flt.dtype, 8) || !is_quant(dst.dtype, 8))
+        return false;
+    if (src.shape.size() != 4)
+        return false;
+    const std::string sparse = ctx->getAttrStr("sparse");
+    if (sparse != "DENSE" && sparse != "GROUP")
+        return false;
+    const std::string act = nonline(ctx);
+    if (act != "IDENTITY" && act != "RELU" && act != "H_SWISH")
+        return false;
+    if (has_bias(ctx)) {
+        const CCOperand bias = ctx->getAttrOprand("operand:2");
+        if (!is_quant(bias.dtype, 32) || !channel_broadcast_bias(ctx))
+            return false;
+        // same scale consistency rule as the reference (ConvKernel.cpp:37-42)
+        if (std::fabs(src.scale * flt.scale - bias.scale) >= 1e-5)
+            return false;
+    }
+    return true;
+}
+
+std::string ConvBiasQS8::GetKernelSymbol(TContext* ctx) const {
+    if (!ctx)  // the dispatcher probes symbols with a null context (KernelGen.cpp:49,108)
+        return "cuda_sm100_conv2d";
+    std::stringstream ss;
+    ss << "cuda_sm100_conv2d_" << ctx->getAttrUInt("kernel_h") << "x"
+       << ctx->getAttrUInt("kernel_w") << "_NHWC_" << ctx->getAttrStr("sparse") << "_p"
+       << ctx->getAttrUInt("pad_h") << "x" << ctx->getAttrUInt("pad_w") << "_s"
+       << ctx->getAttrUInt("stride_h") << "x" << ctx->getAttrUInt("stride_w") << "_d"
+       << ctx->getAttrUInt("dilate_h") << "x" << ctx->getAttrUInt("dilate_w") << "_"
+       << io_str(ctx);
+    if (has_bias(ctx))
+        ss << "_bias";
+    if (nonline(ctx) != "IDENTITY")
+        ss << "_" << nonline(ctx);
+    return ss.str();
+}
+
+std::string ConvBiasQS8::GetKernelBody(TContext* ctx) const {
+    Subst s{R"(
+${prologue}
+/* dims are the logical NCHW extents; strides say the buffer is NHWC */
+TinyNNStatus ${signature} {
+    const Tensor* src = inputs[0];
+    const Tensor* flt = inputs[1];
+    const Tensor* dst = outputs[0];
+    mb200_conv_param p;
+    p.n = src->layout.dims[0];
+    p.ic = src->layout.dims[1];
+    p.ih = src->layout.dims[2];
+    p.iw = src->layout.dims[3];
+    p.oc = dst->layout.dims[1];
+    p.kh = ${kh}; p.kw = ${kw};
+    p.stride_h = ${sh}; p.stride_w = ${sw};
+    p.pad_h = ${ph}; p.pad_w = ${pw};
+    p.dilate_h = ${dh}; p.dilate_w = ${dw};
+    p.groups = ${dense} ? 1 : (int)flt->layout.dims[0];
+    p.nonline = ${nonline};
+    p.src_scale = src->dtype.param.scale;
+    p.flt_scale = flt->dtype.param.scale;
+    p.dst_scale = dst->dtype.param.scale;
+    const int src_is_nchw = src->layout.format == TinyNN_NCHW;
+    const int32_t* bias = ${has_bias} ? (const int32_t*)inputs[2]->ptr : 0;
+    const float* ch_scales = nr_input > ${scale_idx} ? (const float*)inputs[${scale_idx}]->ptr : 0;
+    return (TinyNNStatus)mb200_conv_bias_qs8_nhwc(
+            &p, (const int8_t*)src->ptr, src_is_nchw, (const int8_t*)flt->ptr, bias, ch_scales,
+            (int8_t*)dst->ptr, MB200_ALGO_AUTO, mb200_opt_stream(opt));
+}
+)"};
+    const bool bias = has_bias(ctx);
+    s.set("prologue", GenStubPrologue())
+            .set("signature", GetKernelSignature(ctx))
+            .set("kh", ctx->getAttrUInt("kernel_h"))
+            .set("kw", ctx->getAttrUInt("kernel_w"))
+            .set("sh", ctx->getAttrUInt("stride_h"))
+            .set("sw", ctx->getAttrUInt("stride_w"))
+            .set("ph", ctx->getAttrUInt("pad_h"))
+            .set("pw", ctx->getAttrUInt("pad_w"))
+            .set("dh", ctx->getAttrUInt("dilate_h"))
+            .set("dw", ctx->getAttrUInt("dilate_w"))
+            .set("dense", ctx->getAttrStr("sparse") == "DENSE" ? 1 : 0)
+            .set("nonline", nonline_code(nonline(ctx)))
+            .set("has_bias", bias ? 1 : 0)
+            .set("scale_idx", bias ? 3 : 2);
+    return s.text;
+}
+
+// Init: the filter weight is re-laid from OIHW / [G][OCpg][ICpg][KH][KW] to the K-major
+// [OC][KH][KW][ICpg] the kernels read. Follows the 3-phase protocol of
+// runtime/src/data_struct.h:135-142 (count, describe, fill) and keeps the weight's name
+// pointer, which the runtime matches on (runtime/src/init.c:64,192).
+std::string ConvBiasQS8::GetInitBody(TContext* ctx) const {
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    Tensor* in_weights = inputs[1];
+    if (out_weights == 0 && nr_out_weight != 0) {
+        *nr_out_weight = 1;
+        return TinyNN_SUCCESS;
+    }
+    if (out_weights != 0 && nr_out_weight == 0) {
+        out_weights->layout = in_weights->layout;
+        out_weights->dtype = in_weights->dtype;
+        out_weights->name = in_weights->name;
+        return TinyNN_SUCCESS;
+    }
+    mb200_conv_param p;
+    const Layout* l = &in_weights->layout;
+    const int grouped = l->nr_dim == 5;
+    p.groups = grouped ? l->dims[0] : 1;
+    p.oc = grouped ? l->dims[0] * l->dims[1] : l->dims[0];
+    p.ic = grouped ? l->dims[0] * l->dims[2] : l->dims[1];
+    p.kh = l->dims[l->nr_dim - 2];
+    p.kw = l->dims[l->nr_dim - 1];
+    p.n = 1; p.ih = p.kh; p.iw = p.kw;
+    p.stride_h = p.stride_w = p.dilate_h = p.dilate_w = 1;
+    p.pad_h = p.pad_w = 0;
+    p.nonline = 0;
+    p.src_scale = p.flt_scale = p.dst_scale = 1.f;
+    return (TinyNNStatus)mb200_conv_pack_filter(
+            &p, (const int8_t*)in_weights->ptr, (int8_t*)out_weights->ptr, mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue()).set("signature", GetInitSignature(ctx));
+    return s.text;
+}
+
+// ------------------------------------------------------------------------------------------
+// Pooling
+// ------------------------------------------------------------------------------------------
+bool PoolingQS8::IsAvailable(TContext* ctx) const {
+    if (ctx->getAttrStr("format") != "NCHW")
+        return false;
+    const CCOperand src = ctx->getAttrOprand("operand:0");
+    const CCOperand dst = ctx->getAttrOprand("operand:1");
+    if (!is_quant(src.dtype, 8) || !is_quant(dst.dtype, 8))
+        return false;
+    // quantised pooling keeps the scale (compiler/lib/KernelGen/BareMetal/Pooling.cpp:22-27)
+    if (src.scale != dst.scale)
+        return false;
+    const std::string mode = ctx->getAttrStr("mode");
+    return mode == "MAX" || mode == "AVERAGE" || mode == "AVERAGE_COUNT_EXCLUDE_PADDING";
+}
+
+std::string PoolingQS8::GetKernelSymbol(TContext* ctx) const {
+    std::stringstream ss;
+    ss << "cuda_sm100_pooling_" << ctx->getAttrStr("mode") << "_NHWC_p" << ctx->getAttrInt("pad_h")
+       << "x" << ctx->getAttrInt("pad_w") << "_s" << ctx->getAttrInt("stride_h") << "x"
+       << ctx->getAttrInt("stride_w") << "_w" << ctx->getAttrInt("window_h") << "x"
+       << ctx->getAttrInt("window_w") << "_" << io_str(ctx);
+    return ss.str();
+}
+
+std::string PoolingQS8::GetKernelBody(TContext* ctx) const {
+    const std::string mode = ctx->getAttrStr("mode");
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    const Tensor* src = inputs[0];
+    return (TinyNNStatus)mb200_pooling_qs8_nhwc(
+            (const int8_t*)src->ptr, (int8_t*)outputs[0]->ptr, ${mode}, src->layout.dims[0],
+            src->layout.dims[1], src->layout.dims[2], src->layout.dims[3], ${wh}, ${ww}, ${sh},
+            ${sw}, ${ph}, ${pw}, mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue())
+            .set("signature", GetKernelSignature(ctx))
+            .set("mode", mode == "MAX" ? 0 : mode == "AVERAGE" ? 1 : 2)
+            .set("wh", ctx->getAttrInt("window_h"))
+            .set("ww", ctx->getAttrInt("window_w"))
+            .set("sh", ctx->getAttrInt("stride_h"))
+            .set("sw", ctx->getAttrInt("stride_w"))
+            .set("ph", ctx->getAttrInt("pad_h"))
+            .set("pw", ctx->getAttrInt("pad_w"));
+    return s.text;
+}
+
+// ------------------------------------------------------------------------------------------
+// ElemwiseMultiType
+// ------------------------------------------------------------------------------------------
+static int qelem_code(const std::string& m) {
+    return m == "QADD" ? 0 : m == "QFUSE_ADD_RELU" ? 1 : m == "QMUL" ? 2 : m == "QRELU" ? 3 : -1;
+}
+
+bool ElemwiseMultiTypeQS8::IsAvailable(TContext* ctx) const {
+    const std::string mode = ctx->getAttrStr("mode");
+    const int n = ctx->getAttrInt("nr_operands");
+    if (qelem_code(mode) < 0)
+        return false;
+    if ((mode == "QRELU") != (n == 2) || (n != 2 && n != 3))
+        return false;
+    for (int i = 0; i < n; ++i)
+        if (!is_quant(ctx->getAttrOprand("operand:" + std::to_string(i)).dtype, 8))
+            return false;
+    // same-shape operands only; the broadcast forms stay on the reference's CPU kernels
+    if (n == 3 && ctx->getAttrOprand("operand:0").shape != ctx->getAttrOprand("operand:1").shape)
+        return false;
+    return true;
+}
+
+std::string ElemwiseMultiTypeQS8::GetKernelSymbol(TContext* ctx) const {
+    return "cuda_sm100_elementwise_multitype_" + ctx->getAttrStr("mode") + "_" + io_str(ctx);
+}
+
+std::string ElemwiseMultiTypeQS8::GetKernelBody(TContext* ctx) const {
+    const bool unary = ctx->getAttrInt("nr_operands") == 2;
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    const Tensor* a = inputs[0];
+    const Tensor* b = ${unary} ? inputs[0] : inputs[1];
+    size_t nr_elem = 1;
+    for (int i = 0; i < a->layout.nr_dim; ++i) nr_elem *= a->layout.dims[i];
+    return (TinyNNStatus)mb200_qelemwise_qs8(
+            (const int8_t*)a->ptr, (const int8_t*)b->ptr, (int8_t*)outputs[0]->ptr, ${mode},
+            nr_elem, a->dtype.param.scale, b->dtype.param.scale, outputs[0]->dtype.param.scale,
+            mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue())
+            .set("signature", GetKernelSignature(ctx))
+            .set("unary", unary ? 1 : 0)
+            .set("mode", qelem_code(ctx->getAttrStr("mode")));
+    return s.text;
+}
+
+// ------------------------------------------------------------------------------------------
+// TypeCvt
+// ------------------------------------------------------------------------------------------
+bool TypeCvtQS32QS8::IsAvailable(TContext* ctx) const {
+    const CCOperand src = ctx->getAttrOprand("operand:0");
+    const CCOperand dst = ctx->getAttrOprand("operand:1");
+    return is_quant(src.dtype, 32) && is_quant(dst.dtype, 8) && src.scale > 0 && dst.scale > 0;
+}
+
+std::string TypeCvtQS32QS8::GetKernelSymbol(TContext* ctx) const {
+    return "cuda_sm100_typecvt_" + io_str(ctx);
+}
+
+std::string TypeCvtQS32QS8::GetKernelBody(TContext* ctx) const {
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    const Tensor* src = inputs[0];
+    size_t nr_elem = 1;
+    for (int i = 0; i < src->layout.nr_dim; ++i) nr_elem *= src->layout.dims[i];
+    return (TinyNNStatus)mb200_typecvt_qs32_qs8(
+            (const int32_t*)src->ptr, (int8_t*)outputs[0]->ptr, nr_elem, src->dtype.param.scale,
+            outputs[0]->dtype.param.scale, mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue()).set("signature", GetKernelSignature(ctx));
+    return s.text;
+}
+
+// ------------------------------------------------------------------------------------------
+// Relayout
+// ------------------------------------------------------------------------------------------
+bool RelayoutQS8::IsAvailable(TContext* ctx) const {
+    if (!ctx->haveAttr("relayout_mode"))
+        return false;
+    const std::string m = ctx->getAttrStr("relayout_mode");
+    const CCOperand src = ctx->getAttrOprand("operand:0");
+    return (m == "NCHW_NHWC" || m == "NHWC_NCHW") && src.shape.size() == 4 &&
+           (is_quant(src.dtype, 8) || src.dtype == "si8");
+}
+
+std::string RelayoutQS8::GetKernelSymbol(TContext* ctx) const {
+    return "cuda_sm100_relayout_" + ctx->getAttrStr("relayout_mode") + "_" + io_str(ctx);
+}
+
+std::string RelayoutQS8::GetKernelBody(TContext* ctx) const {
+    const bool to_nhwc = ctx->getAttrStr("relayout_mode") == "NCHW_NHWC";
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    const Tensor* src = inputs[0];
+    return (TinyNNStatus)${fn}(
+            (const int8_t*)src->ptr, (int8_t*)outputs[0]->ptr, src->layout.dims[0],
+            src->layout.dims[1], src->layout.dims[2], src->layout.dims[3], mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue())
+            .set("signature", GetKernelSignature(ctx))
+            .set("fn", to_nhwc ? "mb200_relayout_nchw_to_nhwc_s8" : "mb200_relayout_nhwc_to_nchw_s8");
+    return s.text;
+}
+
+// ------------------------------------------------------------------------------------------
+std::vector<const KernelFunc*> ArchKernelPack::GetKernel(KernelPack::KernType kernel_type) {
+    static ConvBiasQS8 conv;
+    static PoolingQS8 pooling;
+    static ElemwiseMultiTypeQS8 qelem;
+    static TypeCvtQS32QS8 typecvt;
+    static RelayoutQS8 relayout;
+    switch (kernel_type) {
+        case KernelPack::KernType::ConvKernel:
+            return {&conv};
+        case KernelPack::KernType::PoolingKernel:
+            return {&pooling};
+        case KernelPack::KernType::ElemwiseMultiKernel:
+            return {&qelem};
+        case KernelPack::KernType::TypeCvtKernel:
+            return {&typecvt};
+        case KernelPack::KernType::RelayoutKernel:
+            return {&relayout};
+        default:
+            return {};
+    }
+}

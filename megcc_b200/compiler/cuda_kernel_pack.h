@@ -1,0 +1,65 @@
+// The CUDA (sm_100a) architecture of KernelGen: KernelFunc implementations whose generated
+// "kernel body" is a small host C stub with the reference's uniform kernel signature that
+// launches the pre-built sm_100a kernel through the C ABI of libmegcc_b200.so.
+//
+// Mirrors the per-arch packs of the reference (compiler/lib/KernelGen/BareMetal/KernelPack.cpp
+// :38-116): static singletons, order in the returned vector = priority, first IsAvailable wins.
+#pragma once
+#include <string>
+#include <vector>
+
+#include "kernelgen_compat.h"
+
+namespace megcc {
+namespace KernelGen {
+namespace Cuda {
+
+// qint8 ConvBias, activations NHWC. Admits a subset of what BareMetal::ConvGeneral admits
+// (compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:16-46).
+class ConvBiasQS8 : public KernelFunc {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+    std::string GetInitBody(TContext* ctx) const override;
+};
+
+class PoolingQS8 : public KernelFunc {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+};
+
+class ElemwiseMultiTypeQS8 : public KernelFunc {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+};
+
+class TypeCvtQS32QS8 : public KernelFunc {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+};
+
+// NCHW <-> NHWC at the model boundary
+class RelayoutQS8 : public KernelFunc {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+};
+
+struct ArchKernelPack {
+    static std::vector<const KernelFunc*> GetKernel(KernelPack::KernType kernel_type);
+};
+
+// "#include" lines every generated stub starts with
+std::string GenStubPrologue();
+
+}  // namespace Cuda
+}  // namespace KernelGen
+}  // namespace megcc

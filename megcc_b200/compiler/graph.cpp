@@ -1,0 +1,744 @@
+// Network description -> kernel selection -> static memory plan -> tinynn model.
+// See include/megcc_b200_compiler.h for what each step replaces in the reference.
+#include <stdarg.h>
+#include <string.h>
+
+#include <algorithm>
+#include <fstream>
+#include <map>
+#include <memory>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../include/megcc_b200_compiler.h"
+#include "../csrc/tinynn_format.h"
+#include "cuda_kernel_pack.h"
+
+namespace fb = tinynn_fb;
+using namespace megcc;
+using KernType = KernelGen::KernelPack::KernType;
+
+namespace {
+
+thread_local char g_err[512] = "";
+int err(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return -1;
+}
+
+struct GTensor {
+    std::string name;
+    int c = 0, h = 0, w = 0;  // per image
+    float scale = 1.f;
+    bool nchw = false;  // physical layout of the buffer (model input / 1x1 outputs)
+    bool is_input = false, is_output = false;
+};
+
+struct GWeight {
+    std::string name;
+    fb::DTypeEnum dtype;
+    float scale;
+    std::vector<int> dims;
+    std::vector<uint8_t> data;
+    int use_count = 0;
+};
+
+enum class OpType { CONV, POOL, QELEM, RELAYOUT };
+
+struct GOp {
+    OpType type;
+    std::string name;
+    std::vector<int> inputs;   // tensor ids
+    std::vector<int> weights;  // weight ids, appended after the tensor inputs
+    int output = -1;
+    // conv / pooling
+    int kh = 0, kw = 0, stride = 1, pad = 0, groups = 1;
+    std::string mode;  // nonline / pooling mode / elemwise mode / relayout mode
+    bool has_bias = false;
+    float flt_scale = 1.f;
+};
+
+struct Compiled {
+    size_t arena = 0, unplanned = 0;
+};
+
+std::string qdtype(const char* base, float scale) {
+    uint32_t bits;
+    memcpy(&bits, &scale, 4);
+    std::stringstream ss;
+    ss << base << "<" << bits << ":" << scale << ">";
+    return ss.str();
+}
+
+CCOperand operand(const char* base, std::vector<size_t> shape, float scale) {
+    CCOperand o;
+    o.shape = std::move(shape);
+    o.dtype = qdtype(base, scale);
+    o.scale = scale;
+    return o;
+}
+
+#ifdef MEGCC_B200_IN_MEGCC_TREE
+void set_u32(CodeGenContext& c, const char* k, uint32_t v) { c.setAttr(k, CCAttr(v)); }
+void set_i32(CodeGenContext& c, const char* k, int32_t v) { c.setAttr(k, CCAttr(v)); }
+void set_str(CodeGenContext& c, const char* k, const std::string& v) { c.setAttr(k, CCAttr(v)); }
+void set_opr(CodeGenContext& c, const std::string& k, const CCOperand& v) { c.setAttr(k, CCAttr(v)); }
+#else
+void set_u32(CodeGenContext& c, const char* k, uint32_t v) { c.setInt(k, v); }
+void set_i32(CodeGenContext& c, const char* k, int32_t v) { c.setInt(k, v); }
+void set_str(CodeGenContext& c, const char* k, const std::string& v) { c.setStr(k, v); }
+void set_opr(CodeGenContext& c, const std::string& k, const CCOperand& v) { c.setOperand(k, v); }
+#endif
+
+int out_extent(int in, int k, int s, int p) {
+    return (in + 2 * p - (k - 1) - 1) / s + 1;
+}
+
+}  // namespace
+
+struct mb200c_graph {
+    std::string name;
+    std::vector<GTensor> tensors;
+    std::vector<GWeight> weights;
+    std::vector<GOp> ops;
+    // results of the last compile
+    std::vector<uint8_t> bytes;
+    std::vector<std::string> symbols;
+    std::map<std::string, const KernelGen::KernelFunc*> kernel_of;
+    std::map<std::string, std::shared_ptr<CodeGenContext>> ctx_of;
+    std::string symbols_joined;
+    std::vector<Compiled> compiled;
+
+    int add_tensor(const std::string& n, int c, int h, int w, float scale) {
+        GTensor t;
+        t.name = n;
+        t.c = c;
+        t.h = h;
+        t.w = w;
+        t.scale = scale;
+        tensors.push_back(t);
+        return (int)tensors.size() - 1;
+    }
+    bool valid(int id) const { return id >= 0 && (size_t)id < tensors.size(); }
+
+    // the attribute bag KernelMaterialization would build for this operator and batch
+    // (KernelMaterialization.cpp:136-158; attribute names of MGBToKernelHelper.h:98-124)
+    std::shared_ptr<CodeGenContext> context_for(const GOp& op, int batch) const {
+        auto ctx = std::make_shared<CodeGenContext>();
+        auto shape = [&](int id) {
+            const GTensor& t = tensors[id];
+            return std::vector<size_t>{(size_t)batch, (size_t)t.c, (size_t)t.h, (size_t)t.w};
+        };
+        switch (op.type) {
+            case OpType::CONV: {
+                const GTensor& src = tensors[op.inputs[0]];
+                const GTensor& dst = tensors[op.output];
+                set_u32(*ctx, "kernel_h", op.kh);
+                set_u32(*ctx, "kernel_w", op.kw);
+                set_u32(*ctx, "stride_h", op.stride);
+                set_u32(*ctx, "stride_w", op.stride);
+                set_u32(*ctx, "pad_h", op.pad);
+                set_u32(*ctx, "pad_w", op.pad);
+                set_u32(*ctx, "dilate_h", 1);
+                set_u32(*ctx, "dilate_w", 1);
+                set_str(*ctx, "sparse", op.groups == 1 ? "DENSE" : "GROUP");
+                set_str(*ctx, "format", "NCHW");
+                set_str(*ctx, "mode", "CROSS_CORRELATION");
+                set_str(*ctx, "nonlineMode", op.mode);
+                set_str(*ctx, "compute_mode", "DEFAULT");
+                set_opr(*ctx, "operand:0", operand("qsi8", shape(op.inputs[0]), src.scale));
+                std::vector<size_t> fs;
+                for (int d : weights[op.weights[0]].dims)
+                    fs.push_back(d);
+                set_opr(*ctx, "operand:1", operand("qsi8", fs, op.flt_scale));
+                if (op.has_bias)
+                    set_opr(*ctx, "operand:2",
+                            operand("qsi32", {1, (size_t)dst.c, 1, 1}, src.scale * op.flt_scale));
+                else
+                    set_opr(*ctx, "operand:2", operand("qsi32", {}, src.scale * op.flt_scale));
+                set_opr(*ctx, "operand:3", operand("qsi8", shape(op.output), dst.scale));
+                set_i32(*ctx, "nr_operands", 4);
+                break;
+            }
+            case OpType::POOL: {
+                set_str(*ctx, "mode", op.mode);
+                set_str(*ctx, "format", "NCHW");
+                set_i32(*ctx, "window_h", op.kh);
+                set_i32(*ctx, "window_w", op.kw);
+                set_i32(*ctx, "stride_h", op.stride);
+                set_i32(*ctx, "stride_w", op.stride);
+                set_i32(*ctx, "pad_h", op.pad);
+                set_i32(*ctx, "pad_w", op.pad);
+                set_opr(*ctx, "operand:0",
+                        operand("qsi8", shape(op.inputs[0]), tensors[op.inputs[0]].scale));
+                set_opr(*ctx, "operand:1", operand("qsi8", shape(op.output), tensors[op.output].scale));
+                set_i32(*ctx, "nr_operands", 2);
+                break;
+            }
+            case OpType::QELEM: {
+                set_str(*ctx, "mode", op.mode);
+                int k = 0;
+                for (int id : op.inputs)
+                    set_opr(*ctx, "operand:" + std::to_string(k++),
+                            operand("qsi8", shape(id), tensors[id].scale));
+                set_opr(*ctx, "operand:" + std::to_string(k++),
+                        operand("qsi8", shape(op.output), tensors[op.output].scale));
+                set_i32(*ctx, "nr_operands", k);
+                break;
+            }
+            case OpType::RELAYOUT: {
+                set_str(*ctx, "relayout_mode", op.mode);
+                set_opr(*ctx, "operand:0",
+                        operand("qsi8", shape(op.inputs[0]), tensors[op.inputs[0]].scale));
+                set_opr(*ctx, "operand:1", operand("qsi8", shape(op.output), tensors[op.output].scale));
+                set_i32(*ctx, "nr_operands", 2);
+                break;
+            }
+        }
+        return ctx;
+    }
+
+    static KernType kern_type(OpType t) {
+        switch (t) {
+            case OpType::CONV: return KernType::ConvKernel;
+            case OpType::POOL: return KernType::PoolingKernel;
+            case OpType::QELEM: return KernType::ElemwiseMultiKernel;
+            default: return KernType::RelayoutKernel;
+        }
+    }
+};
+
+namespace {
+
+size_t tensor_bytes(const GTensor& t, int batch) {
+    return (size_t)batch * t.c * t.h * t.w;
+}
+
+size_t align256(size_t v) {
+    return (v + 255) / 256 * 256;
+}
+
+// Static memory planning: every tensor lives from the instruction that writes it to the
+// last one that reads it (inputs from the start, outputs to the end); tensors are placed
+// largest first at the lowest 256-byte aligned offset that is free for their whole
+// lifetime. Returns the arena size.
+size_t plan_memory(
+        const mb200c_graph& g, const std::vector<GOp>& ops, int batch,
+        std::vector<size_t>* offsets, size_t* unplanned) {
+    const size_t n = g.tensors.size();
+    std::vector<int> first(n, -1), last(n, -1);
+    for (size_t i = 0; i < n; ++i)
+        if (g.tensors[i].is_input)
+            first[i] = 0;
+    for (size_t k = 0; k < ops.size(); ++k) {
+        for (int id : ops[k].inputs) {
+            if (first[id] < 0)
+                first[id] = (int)k;
+            last[id] = (int)k;
+        }
+        if (first[ops[k].output] < 0)
+            first[ops[k].output] = (int)k;
+        last[ops[k].output] = std::max(last[ops[k].output], (int)k);
+    }
+    for (size_t i = 0; i < n; ++i)
+        if (g.tensors[i].is_output)
+            last[i] = (int)ops.size();
+    std::vector<size_t> order;
+    for (size_t i = 0; i < n; ++i)
+        if (first[i] >= 0)
+            order.push_back(i);
+    std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) {
+        return tensor_bytes(g.tensors[a], batch) > tensor_bytes(g.tensors[b], batch);
+    });
+    offsets->assign(n, 0);
+    std::vector<size_t> placed;
+    size_t arena = 0;
+    *unplanned = 0;
+    for (size_t id : order) {
+        const size_t sz = align256(tensor_bytes(g.tensors[id], batch));
+        *unplanned += sz;
+        // gather busy intervals of tensors alive at the same time
+        std::vector<std::pair<size_t, size_t>> busy;
+        for (size_t o : placed)
+            if (!(last[o] < first[id] || last[id] < first[o]))
+                busy.push_back({(*offsets)[o],
+                                (*offsets)[o] + align256(tensor_bytes(g.tensors[o], batch))});
+        std::sort(busy.begin(), busy.end());
+        size_t off = 0;
+        for (auto& b : busy) {
+            if (off + sz <= b.first)
+                break;
+            off = std::max(off, b.second);
+        }
+        (*offsets)[id] = off;
+        arena = std::max(arena, off + sz);
+        placed.push_back(id);
+    }
+    return arena;
+}
+
+fb::NodeP dtype_node(fb::DTypeEnum t, float scale) {
+    auto p = fb::make_table();
+    p->add<float>(fb::field::DP_scale, scale);
+    auto d = fb::make_table();
+    d->add<int8_t>(fb::field::DT_type, (int8_t)t);
+    d->add_ref(fb::field::DT_param, p);
+    return d;
+}
+
+fb::NodeP layout_node(const std::vector<int>& dims, const std::vector<int>& stride, fb::Format f) {
+    auto l = fb::make_table();
+    l->add_ref(fb::field::L_dims, fb::make_vec<int32_t>(dims));
+    l->add_ref(fb::field::L_stride, fb::make_vec<int32_t>(stride));
+    l->add<int8_t>(fb::field::L_format, (int8_t)f);
+    return l;
+}
+
+std::vector<int> contiguous(const std::vector<int>& dims) {
+    std::vector<int> s(dims.size(), 1);
+    for (int i = (int)dims.size() - 2; i >= 0; --i)
+        s[i] = s[i + 1] * dims[i + 1];
+    return s;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+extern "C" {
+
+const char* mb200c_last_error(void) {
+    return g_err;
+}
+
+mb200c_graph* mb200c_graph_create(const char* model_name) {
+    auto* g = new mb200c_graph();
+    g->name = model_name ? model_name : "model";
+    return g;
+}
+
+void mb200c_graph_destroy(mb200c_graph* g) {
+    delete g;
+}
+
+int mb200c_add_input(mb200c_graph* g, const char* name, int c, int h, int w, float scale) {
+    if (!g || !name || c <= 0 || h <= 0 || w <= 0 || !(scale > 0))
+        return err("add_input: bad argument");
+    const int id = g->add_tensor(name, c, h, w, scale);
+    g->tensors[id].is_input = true;
+    g->tensors[id].nchw = true;
+    return id;
+}
+
+int mb200c_add_conv_bias(
+        mb200c_graph* g, const char* name, int src, int oc, int kh, int kw, int stride, int pad,
+        int groups, const char* nonline, const int8_t* flt, float flt_scale, const int32_t* bias,
+        const float* channel_scales, float dst_scale) {
+    if (!g || !name || !nonline || !flt || !g->valid(src))
+        return err("add_conv_bias: bad argument");
+    const GTensor s = g->tensors[src];
+    if (oc <= 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0 || groups <= 0 ||
+        s.c % groups || oc % groups)
+        return err("add_conv_bias %s: bad extents", name);
+    const int oh = out_extent(s.h, kh, stride, pad), ow = out_extent(s.w, kw, stride, pad);
+    if (oh <= 0 || ow <= 0)
+        return err("add_conv_bias %s: filter larger than padded input", name);
+    GOp op;
+    op.type = OpType::CONV;
+    op.name = name;
+    op.inputs = {src};
+    op.kh = kh;
+    op.kw = kw;
+    op.stride = stride;
+    op.pad = pad;
+    op.groups = groups;
+    op.mode = nonline;
+    op.flt_scale = flt_scale;
+    const int icpg = s.c / groups;
+    GWeight wf;
+    wf.name = std::string(name) + ":filter";
+    wf.dtype = fb::QInt8;
+    wf.scale = flt_scale;
+    wf.dims = groups == 1 ? std::vector<int>{oc, s.c, kh, kw}
+                          : std::vector<int>{groups, oc / groups, icpg, kh, kw};
+    wf.data.assign((const uint8_t*)flt, (const uint8_t*)flt + (size_t)oc * icpg * kh * kw);
+    wf.use_count = 1;
+    g->weights.push_back(std::move(wf));
+    op.weights.push_back((int)g->weights.size() - 1);
+    if (bias) {
+        GWeight wb;
+        wb.name = std::string(name) + ":bias";
+        wb.dtype = fb::QInt32;
+        wb.scale = s.scale * flt_scale;
+        wb.dims = {1, oc, 1, 1};
+        wb.data.assign((const uint8_t*)bias, (const uint8_t*)bias + (size_t)oc * 4);
+        wb.use_count = 1;
+        g->weights.push_back(std::move(wb));
+        op.weights.push_back((int)g->weights.size() - 1);
+        op.has_bias = true;
+    }
+    if (channel_scales) {
+        GWeight ws;
+        ws.name = std::string(name) + ":channel_scales";
+        ws.dtype = fb::Float32;
+        ws.scale = 1.f;
+        ws.dims = {oc};
+        ws.data.assign((const uint8_t*)channel_scales, (const uint8_t*)channel_scales + (size_t)oc * 4);
+        ws.use_count = 1;
+        g->weights.push_back(std::move(ws));
+        op.weights.push_back((int)g->weights.size() - 1);
+    }
+    op.output = g->add_tensor(std::string(name) + ":out", oc, oh, ow, dst_scale);
+    g->ops.push_back(op);
+    return op.output;
+}
+
+int mb200c_add_pooling(
+        mb200c_graph* g, const char* name, int src, const char* mode, int window, int stride,
+        int pad) {
+    if (!g || !name || !mode || !g->valid(src) || window <= 0 || stride <= 0 || pad < 0)
+        return err("add_pooling: bad argument");
+    const GTensor s = g->tensors[src];
+    const int oh = (s.h + 2 * pad - window) / stride + 1, ow = (s.w + 2 * pad - window) / stride + 1;
+    if (s.h + 2 * pad < window || s.w + 2 * pad < window)
+        return err("add_pooling %s: window larger than padded input", name);
+    GOp op;
+    op.type = OpType::POOL;
+    op.name = name;
+    op.inputs = {src};
+    op.kh = op.kw = window;
+    op.stride = stride;
+    op.pad = pad;
+    op.mode = mode;
+    op.output = g->add_tensor(std::string(name) + ":out", s.c, oh, ow, s.scale);
+    g->ops.push_back(op);
+    return op.output;
+}
+
+int mb200c_add_qelemwise(
+        mb200c_graph* g, const char* name, const char* mode, int a, int b, float dst_scale) {
+    if (!g || !name || !mode || !g->valid(a))
+        return err("add_qelemwise: bad argument");
+    const bool unary = strcmp(mode, "QRELU") == 0;
+    if (!unary && !g->valid(b))
+        return err("add_qelemwise %s: second operand missing", name);
+    const GTensor s = g->tensors[a];
+    if (!unary) {
+        const GTensor& t = g->tensors[b];
+        if (t.c != s.c || t.h != s.h || t.w != s.w)
+            return err("add_qelemwise %s: operand shapes differ", name);
+    }
+    GOp op;
+    op.type = OpType::QELEM;
+    op.name = name;
+    op.inputs = unary ? std::vector<int>{a} : std::vector<int>{a, b};
+    op.mode = mode;
+    op.output = g->add_tensor(std::string(name) + ":out", s.c, s.h, s.w, dst_scale);
+    g->ops.push_back(op);
+    return op.output;
+}
+
+int mb200c_mark_output(mb200c_graph* g, int tensor) {
+    if (!g || !g->valid(tensor))
+        return err("mark_output: bad tensor id");
+    g->tensors[tensor].is_output = true;
+    return 0;
+}
+
+int mb200c_compile(
+        mb200c_graph* g, const int* batches, int nr_batches, const uint8_t** bytes, size_t* len) {
+    if (!g || !batches || nr_batches <= 0 || !bytes || !len)
+        return err("compile: bad argument");
+    g->symbols.clear();
+    g->kernel_of.clear();
+    g->ctx_of.clear();
+    g->compiled.clear();
+
+    // ---- layout decisions: activations are NHWC inside the model; the model input is
+    // NCHW (read in place by a first ConvBias, else converted); outputs are handed back
+    // in NCHW, which is free for 1x1 maps and costs a Relayout otherwise ----
+    mb200c_graph work = *g;  // ops get relayouts inserted; the user's graph stays as is
+    {
+        std::vector<GOp> ops;
+        std::map<int, int> nhwc_of;  // NCHW input id -> converted tensor id
+        for (auto op : work.ops) {
+            for (size_t k = 0; k < op.inputs.size(); ++k) {
+                const int id = op.inputs[k];
+                if (!work.tensors[id].nchw)
+                    continue;
+                if (op.type == OpType::CONV && k == 0)
+                    continue;  // ConvBias reads NCHW directly
+                if (work.tensors[id].h == 1 && work.tensors[id].w == 1)
+                    continue;  // NCHW == NHWC
+                if (!nhwc_of.count(id)) {
+                    const GTensor t = work.tensors[id];
+                    const int nid = work.add_tensor(t.name + ":nhwc", t.c, t.h, t.w, t.scale);
+                    GOp r;
+                    r.type = OpType::RELAYOUT;
+                    r.name = t.name + ":to_nhwc";
+                    r.inputs = {id};
+                    r.mode = "NCHW_NHWC";
+                    r.output = nid;
+                    ops.push_back(r);
+                    nhwc_of[id] = nid;
+                }
+                op.inputs[k] = nhwc_of[id];
+            }
+            ops.push_back(op);
+        }
+        const size_t n_before = work.tensors.size();
+        for (size_t id = 0; id < n_before; ++id) {
+            GTensor& t = work.tensors[id];
+            if (!t.is_output || t.nchw)
+                continue;
+            if (t.h == 1 && t.w == 1) {
+                t.nchw = true;
+                continue;
+            }
+            const GTensor copy = t;
+            t.is_output = false;
+            const int nid = work.add_tensor(copy.name + ":nchw", copy.c, copy.h, copy.w, copy.scale);
+            work.tensors[nid].is_output = true;
+            work.tensors[nid].nchw = true;
+            std::swap(work.tensors[id].name, work.tensors[nid].name);  // keep the visible name
+            GOp r;
+            r.type = OpType::RELAYOUT;
+            r.name = copy.name + ":to_nchw";
+            r.inputs = {(int)id};
+            r.mode = "NHWC_NCHW";
+            r.output = nid;
+            ops.push_back(r);
+        }
+        work.ops = ops;
+    }
+
+    // ---- kernel selection (first available kernel of the CUDA pack wins) ----
+    std::vector<std::string> op_symbol(work.ops.size());
+    std::map<std::string, int> kernel_id;
+    for (size_t k = 0; k < work.ops.size(); ++k) {
+        const GOp& op = work.ops[k];
+        auto ctx = work.context_for(op, batches[0]);
+        const KernelGen::KernelFunc* chosen = nullptr;
+        for (auto* kf : KernelGen::Cuda::ArchKernelPack::GetKernel(mb200c_graph::kern_type(op.type)))
+            if (kf->IsAvailable(ctx.get())) {
+                chosen = kf;
+                break;
+            }
+        if (!chosen)
+            return err("no CUDA kernel is available for operator '%s'", op.name.c_str());
+        const std::string sym = chosen->GetKernelSymbol(ctx.get());
+        op_symbol[k] = sym;
+        if (!kernel_id.count(sym)) {
+            kernel_id[sym] = (int)g->symbols.size();
+            g->symbols.push_back(sym);
+            g->kernel_of[sym] = chosen;
+            g->ctx_of[sym] = ctx;
+        }
+    }
+
+    // ---- weights ----
+    std::vector<fb::NodeP> wnodes;
+    for (auto& w : work.weights) {
+        auto n = fb::make_table();
+        n->add_ref(fb::field::W_dtype, dtype_node(w.dtype, w.scale));
+        n->add_ref(fb::field::W_layout, layout_node(w.dims, contiguous(w.dims), fb::NCHW));
+        n->add<int32_t>(fb::field::W_use_count, w.use_count);
+        n->add_ref(fb::field::W_data, fb::make_bytes(w.data.data(), w.data.size()));
+        n->add_ref(fb::field::W_name, fb::make_string(w.name));
+        wnodes.push_back(n);
+    }
+
+    // ---- one DeviceModel per batch size ----
+    std::vector<fb::NodeP> dmodels;
+    for (int bi = 0; bi < nr_batches; ++bi) {
+        const int batch = batches[bi];
+        if (batch <= 0)
+            return err("compile: batch %d", batch);
+        std::vector<size_t> offsets;
+        Compiled c;
+        c.arena = plan_memory(work, work.ops, batch, &offsets, &c.unplanned);
+        g->compiled.push_back(c);
+
+        std::vector<fb::NodeP> tnodes;
+        std::vector<int> use_count(work.tensors.size(), 0);
+        for (auto& op : work.ops)
+            for (int id : op.inputs)
+                use_count[id]++;
+        for (size_t i = 0; i < work.tensors.size(); ++i) {
+            const GTensor& t = work.tensors[i];
+            const std::vector<int> dims = {batch, t.c, t.h, t.w};
+            const std::vector<int> stride =
+                    t.nchw ? contiguous(dims) : std::vector<int>{t.h * t.w * t.c, 1, t.w * t.c, t.c};
+            auto n = fb::make_table();
+            n->add_ref(fb::field::T_dtype, dtype_node(fb::QInt8, t.scale));
+            n->add_ref(fb::field::T_layout, layout_node(dims, stride, t.nchw ? fb::NCHW : fb::NHWC));
+            n->add<int64_t>(fb::field::T_offset, (int64_t)offsets[i]);
+            n->add<int32_t>(fb::field::T_use_count, use_count[i]);
+            n->add_ref(fb::field::T_name, fb::make_string(t.name));
+            tnodes.push_back(n);
+        }
+        std::vector<fb::NodeP> inodes;
+        std::vector<uint8_t> itags;
+        for (size_t k = 0; k < work.ops.size(); ++k) {
+            const GOp& op = work.ops[k];
+            std::vector<int32_t> in;
+            std::vector<int8_t> in_t;
+            for (int id : op.inputs) {
+                in.push_back(id);
+                in_t.push_back(fb::TENSOR);
+            }
+            // operand order src, filter, [bias], [scales]: the filter follows the source
+            for (int wid : op.weights) {
+                in.push_back(wid);
+                in_t.push_back(fb::WEIGHT);
+            }
+            auto ws = fb::make_table();
+            ws->add<int64_t>(fb::field::WS_size, 0);
+            ws->add<int64_t>(fb::field::WS_offset, 0);
+            auto n = fb::make_table();
+            n->add_ref(fb::field::O_name, fb::make_string(op.name));
+            n->add_ref(fb::field::O_type, fb::make_string(op_symbol[k]));
+            n->add_ref(fb::field::O_inputs, fb::make_vec<int32_t>(in));
+            n->add_ref(fb::field::O_input_types, fb::make_vec<int8_t>(in_t));
+            n->add_ref(fb::field::O_outputs, fb::make_vec<int32_t>({op.output}));
+            n->add_ref(fb::field::O_workspace, ws);
+            n->add<int32_t>(fb::field::O_init_id, kernel_id[op_symbol[k]]);
+            n->add<int32_t>(fb::field::O_kernel_id, kernel_id[op_symbol[k]]);
+            n->add<int32_t>(fb::field::O_workspace_id, kernel_id[op_symbol[k]]);
+            n->add<int32_t>(fb::field::O_deduce_id, -1);
+            inodes.push_back(n);
+            itags.push_back(fb::INST_OPR);
+        }
+        std::vector<int32_t> ins, outs;
+        for (size_t i = 0; i < work.tensors.size(); ++i) {
+            if (work.tensors[i].is_input)
+                ins.push_back((int)i);
+            if (work.tensors[i].is_output)
+                outs.push_back((int)i);
+        }
+        if (outs.empty())
+            return err("compile: the graph has no output");
+        auto dm = fb::make_table();
+        dm->add<int8_t>(fb::field::D_device, (int8_t)fb::CUDA_SM100);
+        dm->add_ref(fb::field::D_tensor_pool, fb::make_table_vec(tnodes));
+        dm->add_ref(fb::field::D_instructions_type, fb::make_vec<uint8_t>(itags));
+        dm->add_ref(fb::field::D_instructions, fb::make_table_vec(inodes));
+        dm->add<uint64_t>(fb::field::D_tensor_memory, (uint64_t)c.arena);
+        dm->add_ref(fb::field::D_inputs, fb::make_vec<int32_t>(ins));
+        dm->add_ref(fb::field::D_outputs, fb::make_vec<int32_t>(outs));
+        dmodels.push_back(dm);
+    }
+    auto model = fb::make_table();
+    model->add_ref(fb::field::M_weight_pool, fb::make_table_vec(wnodes));
+    model->add_ref(fb::field::M_device_models, fb::make_table_vec(dmodels));
+    model->add<uint8_t>(fb::field::M_const_shape, 1);
+    model->add_ref(fb::field::M_name, fb::make_string(g->name));
+    fb::Writer w;
+    g->bytes = w.finish(model);
+    g->symbols_joined.clear();
+    for (auto& s : g->symbols)
+        g->symbols_joined += s + "\n";
+    *bytes = g->bytes.data();
+    *len = g->bytes.size();
+    return 0;
+}
+
+const char* mb200c_kernel_symbols(mb200c_graph* g) {
+    return g ? g->symbols_joined.c_str() : "";
+}
+
+size_t mb200c_arena_bytes(mb200c_graph* g, int i) {
+    return g && i >= 0 && (size_t)i < g->compiled.size() ? g->compiled[i].arena : 0;
+}
+
+size_t mb200c_unplanned_bytes(mb200c_graph* g, int i) {
+    return g && i >= 0 && (size_t)i < g->compiled.size() ? g->compiled[i].unplanned : 0;
+}
+
+int mb200c_export_kernels(mb200c_graph* g, const char* dir) {
+    if (!g || !dir)
+        return err("export_kernels: bad argument");
+    if (g->symbols.empty())
+        return err("export_kernels: compile the graph first");
+    const std::string d = dir;
+    // kernels.h / kernels.c follow the shape of the reference exporter's output
+    // (compiler/lib/Target/TinyNN/KernelExporter.cpp:15-66): function tables indexed by
+    // kernel_id / init_id and a loader that fills them.
+    std::ofstream h(d + "/kernels.h"), c(d + "/kernels.c");
+    if (!h || !c)
+        return err("export_kernels: cannot write into %s", dir);
+    const size_t n = g->symbols.size();
+    h << "#ifndef KERNELS_H\n#define KERNELS_H\n#include \"megcc_b200_runtime.h\"\n"
+      << "#define NR_KERNELS (" << n << ")\n#define NR_INIT (" << n << ")\n"
+      << "extern KernelFunc kernels[NR_KERNELS];\nextern InitFunc init_kernels[NR_INIT];\n"
+      << "extern WorkspaceFunc workspace_func[NR_KERNELS];\n"
+      << "void load_kernel_init_function(void);\n";
+    c << "#include \"kernels.h\"\nKernelFunc kernels[NR_KERNELS];\nInitFunc init_kernels[NR_INIT];\n"
+      << "WorkspaceFunc workspace_func[NR_KERNELS];\n";
+    std::stringstream loader;
+    loader << "void load_kernel_init_function(void) {\n";
+    for (size_t i = 0; i < n; ++i) {
+        const std::string& sym = g->symbols[i];
+        const KernelGen::KernelFunc* kf = g->kernel_of[sym];
+        TContext* ctx = g->ctx_of[sym].get();
+        h << "TinyNNStatus " << kf->GetKernelSignature(ctx) << ";\n"
+          << "TinyNNStatus " << kf->GetInitSignature(ctx) << ";\n"
+          << "TinyNNStatus " << kf->GetWorkspaceSignature(ctx) << ";\n";
+        loader << "    kernels[" << i << "] = " << sym << ";\n    init_kernels[" << i
+               << "] = " << kf->GetInitSymbol(ctx) << ";\n    workspace_func[" << i
+               << "] = " << kf->GetWorkspaceSymbol(ctx) << ";\n";
+        std::ofstream k(d + "/" + sym + ".c");
+        if (!k)
+            return err("export_kernels: cannot write %s.c", sym.c_str());
+        const std::string body = kf->GetKernelBody(ctx);
+        std::string init = kf->GetInitBody(ctx);
+        k << kf->GetBodyGuardBegin(ctx) << "#include \"kernels.h\"\n" << body << "\n" << init
+          << "\n" << kf->GetWorkspaceBody(ctx) << "\n" << kf->GetBodyGuardEnd(ctx);
+    }
+    loader << "}\n";
+    c << loader.str();
+    h << "#endif\n";
+    return 0;
+}
+
+int mb200c_probe_conv_symbol(
+        int ic, int oc, int h, int w, int k, int stride, int pad, int groups, const char* nonline,
+        int with_bias, const char* format, char* symbol_out, size_t symbol_cap) {
+    CodeGenContext ctx;
+    set_u32(ctx, "kernel_h", k);
+    set_u32(ctx, "kernel_w", k);
+    set_u32(ctx, "stride_h", stride);
+    set_u32(ctx, "stride_w", stride);
+    set_u32(ctx, "pad_h", pad);
+    set_u32(ctx, "pad_w", pad);
+    set_u32(ctx, "dilate_h", 1);
+    set_u32(ctx, "dilate_w", 1);
+    set_str(ctx, "sparse", groups == 1 ? "DENSE" : "GROUP");
+    set_str(ctx, "format", format ? format : "NCHW");
+    set_str(ctx, "mode", "CROSS_CORRELATION");
+    set_str(ctx, "nonlineMode", nonline ? nonline : "IDENTITY");
+    set_opr(ctx, "operand:0", operand("qsi8", {1, (size_t)ic, (size_t)h, (size_t)w}, 1.f));
+    if (groups == 1)
+        set_opr(ctx, "operand:1", operand("qsi8", {(size_t)oc, (size_t)ic, (size_t)k, (size_t)k}, 1.f));
+    else
+        set_opr(ctx, "operand:1",
+                operand("qsi8", {(size_t)groups, (size_t)oc / groups, (size_t)ic / groups,
+                                 (size_t)k, (size_t)k}, 1.f));
+    set_opr(ctx, "operand:2",
+            with_bias ? operand("qsi32", {1, (size_t)oc, 1, 1}, 1.f) : operand("qsi32", {}, 1.f));
+    set_opr(ctx, "operand:3", operand("qsi8", {1, (size_t)oc, (size_t)h, (size_t)w}, 1.f));
+    set_i32(ctx, "nr_operands", 4);
+    for (auto* kf : KernelGen::Cuda::ArchKernelPack::GetKernel(KernType::ConvKernel))
+        if (kf->IsAvailable(&ctx)) {
+            const std::string s = kf->GetKernelSymbol(&ctx);
+            if (symbol_out && symbol_cap)
+                snprintf(symbol_out, symbol_cap, "%s", s.c_str());
+            return 1;
+        }
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,1267 @@
+// The runtime behind the LITE_* C API: loads a tinynn model whose DeviceModel targets
+// CUDA_SM100, lays every tensor into one device arena at the offsets the compile-time
+// planner chose, and replays the instruction list as one CUDA graph on one stream.
+//
+// It takes the place of the reference's parse.c / init.c / vm.c / vm/op.c / lite/*.c
+// (runtime/src): same model format, same structs handed to kernels, same status codes.
+// An Opr's `type` string is the kernel symbol chosen by KernelGen; the symbol selects the
+// pre-built sm_100a kernel here exactly as the generated stub of that symbol would.
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/megcc_b200.h"
+#include "../../include/megcc_b200_lite.h"
+#include "../../include/megcc_b200_runtime.h"
+#include "internal.h"
+#include "tinynn_format.h"
+
+namespace fb = tinynn_fb;
+using mb200::set_error;
+
+namespace {
+
+LiteLogLevel g_log_level = LITE_WARN;
+
+void log_at(LiteLogLevel lvl, const char* fmt, ...) {
+    if (lvl < g_log_level)
+        return;
+    static const char* tag[] = {"DEBUG", "INFO", "WARN", "ERROR"};
+    fprintf(stderr, "megcc_b200 %s: ", tag[lvl]);
+    va_list ap;
+    va_start(ap, fmt);
+    vfprintf(stderr, fmt, ap);
+    va_end(ap);
+}
+
+size_t dtype_bytes(TinyNNDType t) {
+    switch (t) {
+        case TinyNN_FLOAT:
+        case TinyNN_INT:
+        case TinyNN_QINT32:
+            return 4;
+        case TinyNN_FLOAT16:
+        case TinyNN_INT16:
+            return 2;
+        default:
+            return 1;
+    }
+}
+
+size_t tensor_bytes(const Tensor& t) {
+    size_t n = 1;
+    for (int i = 0; i < t.layout.nr_dim; ++i)
+        n *= t.layout.dims[i];
+    return n * dtype_bytes(t.dtype.type_enum);
+}
+
+enum OpKind { OP_CONV, OP_POOL, OP_QELEM, OP_TYPECVT, OP_RELAYOUT_TO_NHWC, OP_RELAYOUT_TO_NCHW };
+
+struct OpPlan {
+    OpKind kind;
+    std::string symbol, name;
+    // attributes baked into the symbol
+    int kh = 0, kw = 0, sh = 1, sw = 1, ph = 0, pw = 0, dh = 1, dw = 1;
+    bool dense = true, has_bias = false;
+    int mode = 0;  // nonline / pooling mode / elemwise mode
+    std::vector<Tensor*> inputs, outputs;
+    std::vector<int> weight_inputs;  // indices (into inputs) that are weights
+    Workspace ws{nullptr, 0, 0};
+    bool needs_init = false;
+    float ms_total = 0;
+    int ms_count = 0;
+};
+
+struct MemForwardPlan {
+    Tensor* in;
+    Tensor* out;
+    int offset;
+};
+
+struct Instr {
+    bool is_opr;
+    OpPlan op;
+    MemForwardPlan mf;
+};
+
+struct Arena {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    int device = 0;
+    ~Arena() {
+        if (ptr) {
+            cudaSetDevice(device);
+            cudaFree(ptr);
+        }
+    }
+};
+
+struct IoSlot {
+    Tensor* tensor = nullptr;
+    void* user_ptr = nullptr;   // what LITE_reset_tensor_memory was given (inputs)
+    bool user_is_device = false;
+    bool want_device = false;   // LiteIO.is_host == 0
+    void* host_stage = nullptr; // pinned copy of an output
+    size_t bytes = 0;
+};
+
+struct DevModel {
+    std::vector<Tensor> tensors;
+    std::vector<std::string> names;
+    std::vector<Instr> instrs;
+    std::vector<IoSlot> inputs, outputs;
+    size_t tensor_memory = 0;
+    cudaGraphExec_t exec = nullptr;
+    std::vector<void*> captured_inputs;
+    bool memory_ready = false;
+    bool ran_eager = false;
+};
+
+struct Network;
+
+struct IoHandle {
+    Network* net;
+    bool is_input;
+    int index;
+};
+
+struct Network {
+    LiteConfig config;
+    std::vector<std::string> io_device_names;  // outputs/inputs declared is_host == 0
+    int device_id = 0;
+    cudaStream_t stream = nullptr;
+    Device device{256, TinyNN_CUDA_SM100, nullptr, nullptr};
+    RuntimeOpt opt{nullptr, nullptr, 0};
+    std::vector<uint8_t> owned_model;  // LITE_load_model_from_path
+    std::vector<Tensor> weights;       // device-resident
+    std::vector<std::string> weight_names;
+    std::vector<const uint8_t*> weight_host;  // into the model buffer, until uploaded
+    std::vector<Tensor> processed;     // packed filters
+    void* weight_arena = nullptr;
+    std::vector<DevModel> models;
+    int active = 0;
+    std::shared_ptr<Arena> arena = std::make_shared<Arena>();
+    size_t arena_need = 0;
+    bool loaded = false, pending = false, use_graph = true, profile = false;
+    std::vector<std::unique_ptr<IoHandle>> handles;
+};
+
+thread_local char g_lite_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_lite_err, sizeof(g_lite_err), fmt, ap);
+    va_end(ap);
+    log_at(LITE_ERROR, "%s\n", g_lite_err);
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(TinyNN_ERROR_RUNTIME, "%s: %s", what, cudaGetErrorString(e));
+}
+
+// ---------------------------------------------------------------------------------------
+// symbol -> plan
+// ---------------------------------------------------------------------------------------
+bool ends_with(const std::string& s, const char* suf) {
+    const size_t n = strlen(suf);
+    return s.size() >= n && s.compare(s.size() - n, n, suf) == 0;
+}
+
+bool parse_symbol(const std::string& sym, OpPlan* op) {
+    op->symbol = sym;
+    if (sym.compare(0, 18, "cuda_sm100_conv2d_") == 0) {
+        char sparse[16] = {0};
+        int used = 0;
+        if (sscanf(sym.c_str(), "cuda_sm100_conv2d_%dx%d_NHWC_%15[A-Z]_p%dx%d_s%dx%d_d%dx%d_%n",
+                   &op->kh, &op->kw, sparse, &op->ph, &op->pw, &op->sh, &op->sw, &op->dh,
+                   &op->dw, &used) != 9 ||
+            used == 0)
+            return false;
+        op->kind = OP_CONV;
+        op->dense = strcmp(sparse, "DENSE") == 0;
+        if (!op->dense && strcmp(sparse, "GROUP") != 0)
+            return false;
+        const std::string rest = sym.substr(used);
+        if (rest.compare(0, 8, "qsi8qsi8") != 0)
+            return false;
+        op->has_bias = rest.find("_bias") != std::string::npos;
+        op->mode = ends_with(rest, "_H_SWISH") ? MB200_H_SWISH
+                   : ends_with(rest, "_RELU")  ? MB200_RELU
+                                               : MB200_IDENTITY;
+        op->needs_init = true;
+        return true;
+    }
+    if (sym.compare(0, 19, "cuda_sm100_pooling_") == 0) {
+        const size_t p = sym.find("_NHWC_p");
+        if (p == std::string::npos)
+            return false;
+        const std::string mode = sym.substr(19, p - 19);
+        op->mode = mode == "MAX" ? 0 : mode == "AVERAGE" ? 1
+                   : mode == "AVERAGE_COUNT_EXCLUDE_PADDING" ? 2 : -1;
+        if (op->mode < 0)
+            return false;
+        if (sscanf(sym.c_str() + p, "_NHWC_p%dx%d_s%dx%d_w%dx%d_", &op->ph, &op->pw, &op->sh,
+                   &op->sw, &op->kh, &op->kw) != 6)
+            return false;
+        op->kind = OP_POOL;
+        return true;
+    }
+    if (sym.compare(0, 33, "cuda_sm100_elementwise_multitype_") == 0) {
+        const size_t p = sym.find("_qsi8");
+        if (p == std::string::npos)
+            return false;
+        const std::string mode = sym.substr(33, p - 33);
+        op->mode = mode == "QADD" ? 0 : mode == "QFUSE_ADD_RELU" ? 1 : mode == "QMUL" ? 2
+                   : mode == "QRELU" ? 3 : -1;
+        op->kind = OP_QELEM;
+        return op->mode >= 0;
+    }
+    if (sym == "cuda_sm100_typecvt_qsi32qsi8") {
+        op->kind = OP_TYPECVT;
+        return true;
+    }
+    if (sym.compare(0, 30, "cuda_sm100_relayout_NCHW_NHWC_") == 0) {
+        op->kind = OP_RELAYOUT_TO_NHWC;
+        return true;
+    }
+    if (sym.compare(0, 30, "cuda_sm100_relayout_NHWC_NCHW_") == 0) {
+        op->kind = OP_RELAYOUT_TO_NCHW;
+        return true;
+    }
+    return false;
+}
+
+size_t nr_elems(const Tensor* t) {
+    size_t n = 1;
+    for (int i = 0; i < t->layout.nr_dim; ++i)
+        n *= t->layout.dims[i];
+    return n;
+}
+
+void fill_conv_param(const OpPlan& op, mb200_conv_param* p) {
+    const Tensor* src = op.inputs[0];
+    const Tensor* flt = op.inputs[1];
+    const Tensor* dst = op.outputs[0];
+    p->n = src->layout.dims[0];
+    p->ic = src->layout.dims[1];
+    p->ih = src->layout.dims[2];
+    p->iw = src->layout.dims[3];
+    p->oc = dst->layout.dims[1];
+    p->kh = op.kh;
+    p->kw = op.kw;
+    p->stride_h = op.sh;
+    p->stride_w = op.sw;
+    p->pad_h = op.ph;
+    p->pad_w = op.pw;
+    p->dilate_h = op.dh;
+    p->dilate_w = op.dw;
+    p->groups = op.dense ? 1 : (int)flt->layout.dims[0];
+    p->nonline = op.mode;
+    p->src_scale = src->dtype.param.scale;
+    p->flt_scale = flt->dtype.param.scale;
+    p->dst_scale = dst->dtype.param.scale;
+}
+
+// what the generated stub of op.symbol does (megcc_b200/compiler/cuda_kernel_pack.cpp)
+int run_op(const OpPlan& op, cudaStream_t st) {
+    switch (op.kind) {
+        case OP_CONV: {
+            mb200_conv_param p;
+            fill_conv_param(op, &p);
+            const Tensor* src = op.inputs[0];
+            const size_t scale_idx = op.has_bias ? 3 : 2;
+            const int32_t* bias = op.has_bias ? (const int32_t*)op.inputs[2]->ptr : nullptr;
+            const float* ch =
+                    op.inputs.size() > scale_idx ? (const float*)op.inputs[scale_idx]->ptr : nullptr;
+            return mb200_conv_bias_qs8_nhwc(
+                    &p, (const int8_t*)src->ptr, src->layout.format == TinyNN_NCHW,
+                    (const int8_t*)op.inputs[1]->ptr, bias, ch, (int8_t*)op.outputs[0]->ptr,
+                    MB200_ALGO_AUTO, st);
+        }
+        case OP_POOL: {
+            const Tensor* s = op.inputs[0];
+            return mb200_pooling_qs8_nhwc(
+                    (const int8_t*)s->ptr, (int8_t*)op.outputs[0]->ptr, op.mode, s->layout.dims[0],
+                    s->layout.dims[1], s->layout.dims[2], s->layout.dims[3], op.kh, op.kw, op.sh,
+                    op.sw, op.ph, op.pw, st);
+        }
+        case OP_QELEM: {
+            const Tensor* a = op.inputs[0];
+            const Tensor* b = op.inputs.size() > 1 ? op.inputs[1] : op.inputs[0];
+            return mb200_qelemwise_qs8(
+                    (const int8_t*)a->ptr, (const int8_t*)b->ptr, (int8_t*)op.outputs[0]->ptr,
+                    op.mode, nr_elems(a), a->dtype.param.scale, b->dtype.param.scale,
+                    op.outputs[0]->dtype.param.scale, st);
+        }
+        case OP_TYPECVT: {
+            const Tensor* s = op.inputs[0];
+            return mb200_typecvt_qs32_qs8(
+                    (const int32_t*)s->ptr, (int8_t*)op.outputs[0]->ptr, nr_elems(s),
+                    s->dtype.param.scale, op.outputs[0]->dtype.param.scale, st);
+        }
+        case OP_RELAYOUT_TO_NHWC:
+        case OP_RELAYOUT_TO_NCHW: {
+            const Tensor* s = op.inputs[0];
+            auto fn = op.kind == OP_RELAYOUT_TO_NHWC ? mb200_relayout_nchw_to_nhwc_s8
+                                                     : mb200_relayout_nhwc_to_nchw_s8;
+            return fn((const int8_t*)s->ptr, (int8_t*)op.outputs[0]->ptr, s->layout.dims[0],
+                      s->layout.dims[1], s->layout.dims[2], s->layout.dims[3], st);
+        }
+    }
+    return TinyNN_ERROR_NO_IMPLEMENT;
+}
+
+// ---------------------------------------------------------------------------------------
+// model parsing
+// ---------------------------------------------------------------------------------------
+bool read_dtype(const fb::Table& t, DType* out) {
+    if (!t)
+        return false;
+    out->type_enum = (TinyNNDType)(int)t.scalar<int8_t>(fb::field::DT_type, 0);
+    const fb::Table p = t.table(fb::field::DT_param);
+    out->param.scale = p ? p.scalar<float>(fb::field::DP_scale, 1.0f) : 1.0f;
+    out->param.zero_point = p ? p.scalar<uint8_t>(fb::field::DP_zero_point, 0) : 0;
+    switch (out->type_enum) {
+        case TinyNN_FLOAT: case TinyNN_FLOAT16: case TinyNN_INT: case TinyNN_INT8:
+        case TinyNN_INT16: case TinyNN_UINT8: case TinyNN_QINT8: case TinyNN_QINT32:
+        case TinyNN_QUINT8:
+            return true;
+        default:
+            return false;
+    }
+}
+
+bool read_layout(const fb::Table& t, Layout* out) {
+    if (!t)
+        return false;
+    const fb::Vec dims = t.vec(fb::field::L_dims, 4), stride = t.vec(fb::field::L_stride, 4);
+    if (!dims || !stride || dims.len != stride.len || dims.len > MAX_DIM)
+        return false;
+    memset(out, 0, sizeof(*out));
+    out->nr_dim = (int)dims.len;
+    for (uint32_t i = 0; i < dims.len; ++i) {
+        const int d = dims.at<int32_t>(i);
+        if (d < 0)
+            return false;
+        out->dims[i] = (uint32_t)d;
+        out->stride[i] = stride.at<int32_t>(i);
+    }
+    out->format = (TinyNNFormat)(int)t.scalar<int8_t>(fb::field::L_format, 0);
+    return true;
+}
+
+int parse_model(Network* net, const void* mem, size_t size) {
+    fb::Buffer buf;  // Tables keep a pointer to it; none outlives this call
+    buf.data = (const uint8_t*)mem;
+    buf.size = size;
+    buf.failed = false;
+    const fb::Table model = fb::root(buf);
+    if (!model)
+        return fail(TinyNN_ERROR_MODEL_PARSE, "model buffer of %zu bytes has no root table", size);
+    const fb::Vec wpool = model.vec(fb::field::M_weight_pool, 4);
+    const fb::Vec dmodels = model.vec(fb::field::M_device_models, 4);
+    if (!wpool || !dmodels)
+        return fail(TinyNN_ERROR_MODEL_PARSE, "model lacks weight_pool or device_models");
+
+    // ---- weights (host view; uploaded later) ----
+    net->weights.resize(wpool.len);
+    net->weight_names.resize(wpool.len);
+    net->weight_host.assign(wpool.len, nullptr);
+    std::vector<const uint8_t*>& host_data = net->weight_host;
+    for (uint32_t i = 0; i < wpool.len; ++i) {
+        const fb::Table w = fb::Table::elem(wpool, i);
+        Tensor& t = net->weights[i];
+        memset(&t, 0, sizeof(t));
+        if (!w || !read_dtype(w.table(fb::field::W_dtype), &t.dtype) ||
+            !read_layout(w.table(fb::field::W_layout), &t.layout))
+            return fail(TinyNN_ERROR_MODEL_PARSE, "weight %u is malformed", i);
+        if (w.scalar<uint8_t>(fb::field::W_compressed, 0))
+            return fail(TinyNN_ERROR_NO_IMPLEMENT, "compressed weights are not supported");
+        const fb::Vec data = w.vec(fb::field::W_data, 1);
+        t.size = tensor_bytes(t);
+        if (!data || data.len != t.size)
+            return fail(TinyNN_ERROR_MODEL_PARSE, "weight %u: %u data bytes for a %zu byte layout",
+                        i, data ? data.len : 0, t.size);
+        host_data[i] = data.bytes();
+        if (!w.str(fb::field::W_name, &net->weight_names[i]))
+            net->weight_names[i] = "weight:" + std::to_string(i);
+        t.use_count = w.scalar<int32_t>(fb::field::W_use_count, 0);
+        t.checksum = w.scalar<uint32_t>(fb::field::W_checksum, 0);
+        t.is_weight = 1;
+    }
+    for (size_t i = 0; i < net->weights.size(); ++i)
+        net->weights[i].name = (char*)net->weight_names[i].c_str();
+
+    // ---- device models: keep the ones for this device (parse.c:404-421 keeps those that
+    // pass valid_device_check) ----
+    for (uint32_t mi = 0; mi < dmodels.len; ++mi) {
+        const fb::Table dm = fb::Table::elem(dmodels, mi);
+        if (!dm)
+            return fail(TinyNN_ERROR_MODEL_PARSE, "device model %u is malformed", mi);
+        if (dm.scalar<int8_t>(fb::field::D_device, 0) != fb::CUDA_SM100)
+            continue;
+        net->models.emplace_back();
+        DevModel& m = net->models.back();
+        const fb::Vec tpool = dm.vec(fb::field::D_tensor_pool, 4);
+        if (!tpool)
+            return fail(TinyNN_ERROR_MODEL_PARSE, "device model %u has no tensor_pool", mi);
+        m.tensors.resize(tpool.len);
+        m.names.resize(tpool.len);
+        m.tensor_memory = (size_t)dm.scalar<uint64_t>(fb::field::D_tensor_memory, 0);
+        for (uint32_t i = 0; i < tpool.len; ++i) {
+            const fb::Table tt = fb::Table::elem(tpool, i);
+            Tensor& t = m.tensors[i];
+            memset(&t, 0, sizeof(t));
+            if (!tt || !read_dtype(tt.table(fb::field::T_dtype), &t.dtype) ||
+                !read_layout(tt.table(fb::field::T_layout), &t.layout))
+                return fail(TinyNN_ERROR_MODEL_PARSE, "tensor %u is malformed", i);
+            if (tt.scalar<uint8_t>(fb::field::T_dynamic, 0))
+                return fail(TinyNN_ERROR_NO_IMPLEMENT, "dynamic-shape tensors are not supported");
+            const int64_t off = tt.scalar<int64_t>(fb::field::T_offset, 0);
+            t.size = tensor_bytes(t);
+            if (off < 0 || (size_t)off + t.size > m.tensor_memory)
+                return fail(TinyNN_ERROR_MODEL_PARSE,
+                            "tensor %u at offset %lld (+%zu) lies outside the %zu byte arena", i,
+                            (long long)off, t.size, m.tensor_memory);
+            t.offset = (size_t)off;
+            t.use_count = tt.scalar<int32_t>(fb::field::T_use_count, 0);
+            if (!tt.str(fb::field::T_name, &m.names[i]) || m.names[i].empty())
+                m.names[i] = "tensor:" + std::to_string(i);
+        }
+        for (size_t i = 0; i < m.tensors.size(); ++i)
+            m.tensors[i].name = (char*)m.names[i].c_str();
+
+        auto io = [&](int fid, std::vector<IoSlot>* slots, bool input) -> bool {
+            const fb::Vec v = dm.vec(fid, 4);
+            if (!v)
+                return false;
+            for (uint32_t i = 0; i < v.len; ++i) {
+                const int idx = v.at<int32_t>(i);
+                if (idx < 0 || (size_t)idx >= m.tensors.size())
+                    return false;
+                IoSlot s;
+                s.tensor = &m.tensors[idx];
+                s.bytes = s.tensor->size;
+                if (input)
+                    s.tensor->is_input = 1;
+                for (auto& n : net->io_device_names)
+                    if (n == s.tensor->name)
+                        s.want_device = true;
+                slots->push_back(s);
+            }
+            return true;
+        };
+        if (!io(fb::field::D_inputs, &m.inputs, true) || !io(fb::field::D_outputs, &m.outputs, false))
+            return fail(TinyNN_ERROR_MODEL_PARSE, "device model %u: bad input/output index", mi);
+
+        const fb::Vec itypes = dm.vec(fb::field::D_instructions_type, 1);
+        const fb::Vec insts = dm.vec(fb::field::D_instructions, 4);
+        if (!itypes || !insts || itypes.len != insts.len)
+            return fail(TinyNN_ERROR_MODEL_PARSE, "device model %u: instruction vectors differ", mi);
+        m.instrs.reserve(insts.len);
+        for (uint32_t i = 0; i < insts.len; ++i) {
+            const uint8_t tag = itypes.at<uint8_t>(i);
+            const fb::Table it = fb::Table::elem(insts, i);
+            if (!it)
+                return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u is malformed", i);
+            Instr ins;
+            if (tag == fb::INST_OPR) {
+                ins.is_opr = true;
+                std::string type;
+                if (!it.str(fb::field::O_type, &type) || !parse_symbol(type, &ins.op))
+                    return fail(TinyNN_ERROR_NO_FOUND,
+                                "instruction %u: no sm_100a kernel for symbol '%s'", i,
+                                type.c_str());
+                it.str(fb::field::O_name, &ins.op.name);
+                const fb::Vec in = it.vec(fb::field::O_inputs, 4);
+                const fb::Vec in_t = it.vec(fb::field::O_input_types, 1);
+                const fb::Vec out = it.vec(fb::field::O_outputs, 4);
+                if (!in || !in_t || !out || in.len != in_t.len)
+                    return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: operand lists", i);
+                for (uint32_t k = 0; k < in.len; ++k) {
+                    const int idx = in.at<int32_t>(k);
+                    const bool is_w = in_t.at<int8_t>(k) == fb::WEIGHT;
+                    const size_t limit = is_w ? net->weights.size() : m.tensors.size();
+                    if (idx < 0 || (size_t)idx >= limit)
+                        return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: operand %u", i, k);
+                    if (is_w)
+                        ins.op.weight_inputs.push_back((int)k);
+                    ins.op.inputs.push_back(is_w ? &net->weights[idx] : &m.tensors[idx]);
+                }
+                for (uint32_t k = 0; k < out.len; ++k) {
+                    const int idx = out.at<int32_t>(k);
+                    if (idx < 0 || (size_t)idx >= m.tensors.size())
+                        return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: output %u", i, k);
+                    ins.op.outputs.push_back(&m.tensors[idx]);
+                }
+                // the workspace table is always present (runtime/src/vm/op.c:56-58)
+                const fb::Table ws = it.table(fb::field::O_workspace);
+                if (!ws)
+                    return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: no workspace", i);
+                ins.op.ws.size = (size_t)ws.scalar<int64_t>(fb::field::WS_size, 0);
+                ins.op.ws.offset = (size_t)ws.scalar<int64_t>(fb::field::WS_offset, 0);
+                if (ins.op.ws.size && ins.op.ws.offset + ins.op.ws.size > m.tensor_memory)
+                    return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: workspace outside arena",
+                                i);
+                const size_t need_in = ins.op.kind == OP_CONV ? 2 : 1;
+                if (ins.op.inputs.size() < need_in || ins.op.outputs.empty())
+                    return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: too few operands", i);
+                if (ins.op.kind == OP_CONV &&
+                    ins.op.inputs.size() < (size_t)(ins.op.has_bias ? 3 : 2))
+                    return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: bias operand missing", i);
+            } else if (tag == fb::INST_MEM_FORWARD) {
+                ins.is_opr = false;
+                const int a = it.scalar<int32_t>(fb::field::MF_input, 0);
+                const int b = it.scalar<int32_t>(fb::field::MF_output, 0);
+                if (a < 0 || b < 0 || (size_t)a >= m.tensors.size() || (size_t)b >= m.tensors.size())
+                    return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: memforward index", i);
+                ins.mf = {&m.tensors[a], &m.tensors[b], it.scalar<int32_t>(fb::field::MF_offset, 0)};
+            } else {
+                return fail(TinyNN_ERROR_UNSUPPORTED_INSTRUCTION_TYPE,
+                            "instruction %u: type %u is not supported on the CUDA device", i,
+                            (unsigned)tag);
+            }
+            m.instrs.push_back(std::move(ins));
+        }
+        if (m.tensor_memory > net->arena_need)
+            net->arena_need = m.tensor_memory;
+    }
+    if (buf.failed)
+        return fail(TinyNN_ERROR_MODEL_PARSE, "model buffer is truncated or corrupt");
+    if (net->models.empty())
+        return fail(TinyNN_ERROR_NO_FOUND, "model holds no DeviceModel for CUDA_SM100");
+
+    return TinyNN_SUCCESS;
+}
+
+// weights -> one device allocation, then the Init step of every ConvBias
+int upload_weights(Network* net) {
+    std::vector<const uint8_t*>& host_data = net->weight_host;
+    cudaError_t e = cudaSetDevice(net->device_id);
+    if (e != cudaSuccess)
+        return cuda_fail(e, "cudaSetDevice");
+    if (!net->stream && (e = cudaStreamCreateWithFlags(&net->stream, cudaStreamNonBlocking)) != cudaSuccess)
+        return cuda_fail(e, "cudaStreamCreate");
+    net->opt.device = &net->device;
+    net->opt.stream = net->stream;
+    net->opt.device_id = net->device_id;
+
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    size_t total = 0;
+    for (auto& w : net->weights)
+        total += up(w.size);
+    // packed copies of the conv filters (the Init step)
+    std::vector<std::pair<OpPlan*, int>> packs;  // op, filter index in weights
+    for (auto& m : net->models)
+        for (auto& ins : m.instrs)
+            if (ins.is_opr && ins.op.needs_init) {
+                Tensor* f = ins.op.inputs[1];
+                if (!f->is_weight)
+                    return fail(TinyNN_ERROR_NO_IMPLEMENT, "conv filter must be a weight");
+                packs.push_back({&ins.op, (int)(f - net->weights.data())});
+            }
+    std::vector<int> packed_of(net->weights.size(), -1);
+    for (auto& pk : packs)
+        if (packed_of[pk.second] < 0) {
+            packed_of[pk.second] = (int)net->processed.size();
+            net->processed.push_back(net->weights[pk.second]);
+            total += up(net->weights[pk.second].size);
+        }
+    if (total == 0)
+        total = 256;
+    if ((e = cudaMalloc(&net->weight_arena, total)) != cudaSuccess)
+        return cuda_fail(e, "cudaMalloc(weights)");
+    size_t off = 0;
+    for (size_t i = 0; i < net->weights.size(); ++i) {
+        Tensor& w = net->weights[i];
+        w.ptr = (uint8_t*)net->weight_arena + off;
+        off += up(w.size);
+        if (w.size &&
+            (e = cudaMemcpyAsync(w.ptr, host_data[i], w.size, cudaMemcpyHostToDevice, net->stream)) !=
+                    cudaSuccess)
+            return cuda_fail(e, "cudaMemcpy(weights)");
+    }
+    for (auto& pw : net->processed) {
+        pw.ptr = (uint8_t*)net->weight_arena + off;
+        off += up(pw.size);
+    }
+    // Init: pack each filter once, then point the Oprs at the processed weight
+    // (the swap the reference performs in runtime/src/init.c:59-92)
+    std::vector<char> done(net->processed.size(), 0);
+    for (auto& pk : packs) {
+        OpPlan* op = pk.first;
+        const int pi = packed_of[pk.second];
+        Tensor* src = &net->weights[pk.second];
+        Tensor* dst = &net->processed[pi];
+        if (!done[pi]) {
+            const Layout& l = src->layout;
+            const bool grouped = l.nr_dim == 5;
+            if (l.nr_dim != 4 && l.nr_dim != 5)
+                return fail(TinyNN_ERROR_INVALID_LAYOUT, "conv filter must have 4 or 5 dims");
+            mb200_conv_param p;
+            memset(&p, 0, sizeof(p));
+            p.groups = grouped ? l.dims[0] : 1;
+            p.oc = grouped ? l.dims[0] * l.dims[1] : l.dims[0];
+            p.ic = grouped ? l.dims[0] * l.dims[2] : l.dims[1];
+            p.kh = l.dims[l.nr_dim - 2];
+            p.kw = l.dims[l.nr_dim - 1];
+            p.n = 1;
+            p.ih = p.kh;
+            p.iw = p.kw;
+            p.stride_h = p.stride_w = p.dilate_h = p.dilate_w = 1;
+            p.src_scale = p.flt_scale = p.dst_scale = 1.f;
+            int rc = mb200_conv_pack_filter(&p, (const int8_t*)src->ptr, (int8_t*)dst->ptr, net->stream);
+            if (rc)
+                return fail(rc, "packing filter '%s': %s", src->name, mb200_last_error());
+            done[pi] = 1;
+        }
+        op->inputs[1] = dst;
+    }
+    if ((e = cudaStreamSynchronize(net->stream)) != cudaSuccess)
+        return cuda_fail(e, "weight upload");
+    if (!mb200::device_status_word())
+        return fail(TinyNN_ERROR_MEMORY_MALLOC, "%s", mb200_last_error());
+    net->loaded = true;
+    return TinyNN_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------------------
+// memory + execution
+// ---------------------------------------------------------------------------------------
+int init_model_memory(Network* net) {
+    DevModel& m = net->models[net->active];
+    if (m.memory_ready)
+        return TinyNN_SUCCESS;
+    cudaError_t e = cudaSetDevice(net->device_id);
+    if (e != cudaSuccess)
+        return cuda_fail(e, "cudaSetDevice");
+    Arena& a = *net->arena;
+    if (a.bytes < net->arena_need)
+        a.bytes = net->arena_need;
+    if (!a.ptr) {
+        // one allocation for every tensor and workspace of the model
+        a.device = net->device_id;
+        if ((e = cudaMalloc(&a.ptr, a.bytes ? a.bytes : 256)) != cudaSuccess)
+            return cuda_fail(e, "cudaMalloc(arena)");
+    }
+    for (auto& t : m.tensors)
+        t.ptr = (uint8_t*)a.ptr + t.offset;
+    for (auto& ins : m.instrs) {
+        if (ins.is_opr)
+            ins.op.ws.ptr = ins.op.ws.size ? (uint8_t*)a.ptr + ins.op.ws.offset : nullptr;
+        else
+            ins.mf.out->ptr = (uint8_t*)ins.mf.in->ptr + ins.mf.offset;
+    }
+    for (auto& o : m.outputs) {
+        if (!o.host_stage && !o.want_device &&
+            (e = cudaMallocHost(&o.host_stage, o.bytes ? o.bytes : 1)) != cudaSuccess)
+            return cuda_fail(e, "cudaMallocHost(output)");
+    }
+    m.memory_ready = true;
+    return TinyNN_SUCCESS;
+}
+
+int issue_instructions(Network* net, DevModel& m, bool timed) {
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    if (timed) {
+        cudaEventCreate(&ev0);
+        cudaEventCreate(&ev1);
+    }
+    for (auto& ins : m.instrs) {
+        if (!ins.is_opr)
+            continue;  // memforward is resolved when the arena is laid out
+        if (timed)
+            cudaEventRecord(ev0, net->stream);
+        const int rc = run_op(ins.op, net->stream);
+        if (rc)
+            return fail(rc, "kernel %s: %s", ins.op.symbol.c_str(), mb200_last_error());
+        if (timed) {
+            cudaEventRecord(ev1, net->stream);
+            cudaEventSynchronize(ev1);
+            float ms = 0;
+            cudaEventElapsedTime(&ms, ev0, ev1);
+            ins.op.ms_total += ms;
+            ins.op.ms_count++;
+        }
+    }
+    if (timed) {
+        cudaEventDestroy(ev0);
+        cudaEventDestroy(ev1);
+    }
+    return TinyNN_SUCCESS;
+}
+
+int forward(Network* net) {
+    if (!net->loaded)
+        return fail(TinyNN_ERROR, "LITE_forward before a model was loaded");
+    int rc = init_model_memory(net);
+    if (rc)
+        return rc;
+    DevModel& m = net->models[net->active];
+    cudaError_t e = cudaSetDevice(net->device_id);
+    if (e != cudaSuccess)
+        return cuda_fail(e, "cudaSetDevice");
+
+    // inputs: device pointers are used in place, host pointers are copied in
+    std::vector<void*> in_ptrs;
+    for (auto& s : m.inputs) {
+        if (!s.user_ptr)
+            return fail(TinyNN_ERROR_NULL_PTR,
+                        "input '%s' has no memory: call LITE_reset_tensor_memory first",
+                        s.tensor->name);
+        if (s.user_is_device) {
+            s.tensor->ptr = s.user_ptr;
+        } else {
+            s.tensor->ptr = (uint8_t*)net->arena->ptr + s.tensor->offset;
+            if ((e = cudaMemcpyAsync(s.tensor->ptr, s.user_ptr, s.bytes, cudaMemcpyHostToDevice,
+                                     net->stream)) != cudaSuccess)
+                return cuda_fail(e, "cudaMemcpyAsync(input)");
+        }
+        in_ptrs.push_back(s.tensor->ptr);
+    }
+
+    if (net->profile || !net->use_graph) {
+        if ((rc = issue_instructions(net, m, net->profile)))
+            return rc;
+    } else {
+        if (!m.ran_eager) {
+            // the first pass runs eagerly: it also performs one-time set-up that may not
+            // happen under stream capture
+            if ((rc = issue_instructions(net, m, false)))
+                return rc;
+            m.ran_eager = true;
+        } else {
+            if (m.exec && in_ptrs != m.captured_inputs) {
+                cudaGraphExecDestroy(m.exec);
+                m.exec = nullptr;
+            }
+            if (!m.exec) {
+                cudaGraph_t graph = nullptr;
+                if ((e = cudaStreamBeginCapture(net->stream, cudaStreamCaptureModeThreadLocal)) !=
+                    cudaSuccess)
+                    return cuda_fail(e, "cudaStreamBeginCapture");
+                rc = issue_instructions(net, m, false);
+                e = cudaStreamEndCapture(net->stream, &graph);
+                if (rc) {
+                    if (graph)
+                        cudaGraphDestroy(graph);
+                    return rc;
+                }
+                if (e != cudaSuccess)
+                    return cuda_fail(e, "cudaStreamEndCapture");
+                e = cudaGraphInstantiate(&m.exec, graph, 0);
+                cudaGraphDestroy(graph);
+                if (e != cudaSuccess)
+                    return cuda_fail(e, "cudaGraphInstantiate");
+                m.captured_inputs = in_ptrs;
+            }
+            if ((e = cudaGraphLaunch(m.exec, net->stream)) != cudaSuccess)
+                return cuda_fail(e, "cudaGraphLaunch");
+        }
+    }
+    for (auto& o : m.outputs) {
+        if (o.want_device)
+            continue;
+        if ((e = cudaMemcpyAsync(o.host_stage, o.tensor->ptr, o.bytes, cudaMemcpyDeviceToHost,
+                                 net->stream)) != cudaSuccess)
+            return cuda_fail(e, "cudaMemcpyAsync(output)");
+    }
+    net->pending = true;
+    return TinyNN_SUCCESS;
+}
+
+int wait(Network* net) {
+    if (!net->pending)
+        return TinyNN_SUCCESS;
+    net->pending = false;
+    cudaSetDevice(net->device_id);
+    int status = 0;
+    const int rc = mb200_device_status(net->stream, &status);  // synchronises the stream
+    if (rc)
+        return fail(rc, "%s", mb200_last_error());
+    if (status)
+        return fail(TinyNN_ERROR_RUNTIME, "a kernel gave up on a bounded wait (code 0x%x)", status);
+    return TinyNN_SUCCESS;
+}
+
+Network* as_net(LiteNetwork n) {
+    return (Network*)n;
+}
+IoHandle* as_io(LiteTensor t) {
+    return (IoHandle*)t;
+}
+IoSlot* slot_of(IoHandle* h) {
+    DevModel& m = h->net->models[h->net->active];
+    auto& v = h->is_input ? m.inputs : m.outputs;
+    return (size_t)h->index < v.size() ? &v[h->index] : nullptr;
+}
+
+LiteConfig g_default_config = {
+        0, -1, LITE_CPU, LITE_DEFAULT, nullptr,
+        {0, 0, 0, 1, 0, 0, 0, 0, 0, 0, 2, 1, 0, 0, 0, 0, 0, 0, 0}};
+LiteNetworkIO g_default_io = {nullptr, nullptr, 0, 0};
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// C API
+// ---------------------------------------------------------------------------------------
+extern "C" {
+
+LiteConfig* default_config(void) {
+    return &g_default_config;
+}
+LiteNetworkIO* default_network_io(void) {
+    return &g_default_io;
+}
+
+const char* LITE_get_last_error(void) {
+    return g_lite_err;
+}
+
+int LITE_set_log_level(LiteLogLevel level) {
+    g_log_level = level;
+    return 0;
+}
+int LITE_get_log_level(LiteLogLevel* level) {
+    if (!level)
+        return TinyNN_ERROR_NULL_PTR;
+    *level = g_log_level;
+    return 0;
+}
+
+// Parses a model exactly as LITE_load_model_from_mem does, without touching a GPU, and
+// writes a one-line-per-item text summary. For tools and tests.
+int mb200_tinynn_describe(const void* model_mem, size_t size, char* out, size_t cap) {
+    if (!model_mem || !out || !cap)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    Network net;
+    const int rc = parse_model(&net, model_mem, size);
+    if (rc)
+        return rc;
+    std::string s;
+    char line[512];
+    for (auto& w : net.weights) {
+        snprintf(line, sizeof(line), "weight %s dtype=%d scale=%.9g bytes=%zu dims=", w.name,
+                 (int)w.dtype.type_enum, w.dtype.param.scale, w.size);
+        s += line;
+        for (int i = 0; i < w.layout.nr_dim; ++i)
+            s += std::to_string(w.layout.dims[i]) + (i + 1 < w.layout.nr_dim ? "x" : "");
+        s += "\n";
+    }
+    for (size_t mi = 0; mi < net.models.size(); ++mi) {
+        DevModel& m = net.models[mi];
+        snprintf(line, sizeof(line), "device_model %zu tensor_memory=%zu tensors=%zu instructions=%zu\n",
+                 mi, m.tensor_memory, m.tensors.size(), m.instrs.size());
+        s += line;
+        for (auto& t : m.tensors) {
+            snprintf(line, sizeof(line), "tensor %s offset=%zu bytes=%zu format=%d scale=%.9g dims=",
+                     t.name, t.offset, t.size, (int)t.layout.format, t.dtype.param.scale);
+            s += line;
+            for (int i = 0; i < t.layout.nr_dim; ++i)
+                s += std::to_string(t.layout.dims[i]) + (i + 1 < t.layout.nr_dim ? "x" : "");
+            s += " stride=";
+            for (int i = 0; i < t.layout.nr_dim; ++i)
+                s += std::to_string(t.layout.stride[i]) + (i + 1 < t.layout.nr_dim ? "x" : "");
+            s += "\n";
+        }
+        for (auto& ins : m.instrs) {
+            if (!ins.is_opr)
+                continue;
+            s += "opr " + ins.op.symbol + " in=";
+            for (auto* t : ins.op.inputs)
+                s += std::string(t->name) + ",";
+            s += " out=";
+            for (auto* t : ins.op.outputs)
+                s += std::string(t->name) + ",";
+            s += "\n";
+        }
+        for (auto& io : m.inputs)
+            s += std::string("input ") + io.tensor->name + "\n";
+        for (auto& io : m.outputs)
+            s += std::string("output ") + io.tensor->name + "\n";
+    }
+    if (s.size() + 1 > cap)
+        return fail(TinyNN_ERROR_OUT_OF_RANGE, "summary needs %zu bytes", s.size() + 1);
+    memcpy(out, s.c_str(), s.size() + 1);
+    return TinyNN_SUCCESS;
+}
+
+int LITE_make_network(LiteNetwork* network, const LiteConfig config, const LiteNetworkIO io) {
+    if (!network)
+        return fail(TinyNN_ERROR_NULL_PTR, "network pointer is NULL");
+    Network* net = new (std::nothrow) Network();
+    if (!net)
+        return fail(TinyNN_ERROR_MEMORY_MALLOC, "out of host memory");
+    net->config = config;
+    net->device_id = config.device_id >= 0 ? config.device_id : 0;
+    for (size_t i = 0; i < io.input_size; ++i)
+        if (io.inputs && io.inputs[i].name && !io.inputs[i].is_host)
+            net->io_device_names.push_back(io.inputs[i].name);
+    for (size_t i = 0; i < io.output_size; ++i)
+        if (io.outputs && io.outputs[i].name && !io.outputs[i].is_host)
+            net->io_device_names.push_back(io.outputs[i].name);
+    const char* ng = getenv("MB200_NO_GRAPH");
+    net->use_graph = !(ng && ng[0] == '1');
+    const char* pf = getenv("MB200_PROFILE");
+    net->profile = pf && pf[0] == '1';
+    *network = net;
+    return TinyNN_SUCCESS;
+}
+
+int LITE_load_model_from_mem(LiteNetwork network, void* model_mem, size_t size) {
+    if (!network || !model_mem)
+        return fail(TinyNN_ERROR_NULL_PTR, "network or model pointer is NULL");
+    Network* net = as_net(network);
+    if (net->loaded)
+        return fail(TinyNN_ERROR, "this network already holds a model");
+    const int rc = parse_model(net, model_mem, size);
+    return rc ? rc : upload_weights(net);
+}
+
+int LITE_load_model_with_shared_mem(LiteNetwork network, void* model_mem, size_t size) {
+    // weights live in device memory either way, so sharing the host buffer changes nothing
+    return LITE_load_model_from_mem(network, model_mem, size);
+}
+
+int LITE_load_model_from_path(LiteNetwork network, const char* model_path) {
+    if (!network || !model_path)
+        return fail(TinyNN_ERROR_NULL_PTR, "network or path is NULL");
+    FILE* f = fopen(model_path, "rb");
+    if (!f)
+        return fail(TinyNN_ERROR_OPEN_FILE_ERROR, "cannot open %s", model_path);
+    fseek(f, 0, SEEK_END);
+    const long size = ftell(f);
+    fseek(f, 0, SEEK_SET);
+    Network* net = as_net(network);
+    net->owned_model.resize(size > 0 ? (size_t)size : 0);
+    const size_t got = size > 0 ? fread(net->owned_model.data(), 1, (size_t)size, f) : 0;
+    fclose(f);
+    if (size <= 0 || got != (size_t)size)
+        return fail(TinyNN_ERROR_OPEN_FILE_ERROR, "short read of %s", model_path);
+    return LITE_load_model_from_mem(network, net->owned_model.data(), net->owned_model.size());
+}
+
+int LITE_get_io_tensor(
+        LiteNetwork network, const char* io_name, LiteTensorPhase phase, LiteTensor* tensor) {
+    if (!network || !io_name || !tensor)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    Network* net = as_net(network);
+    if (!net->loaded)
+        return fail(TinyNN_ERROR, "no model loaded");
+    DevModel& m = net->models[net->active];
+    for (int pass = 0; pass < 2; ++pass) {
+        const bool input = pass == 0;
+        if (input && phase == LITE_OUTPUT)
+            continue;
+        if (!input && phase == LITE_INPUT)
+            continue;
+        auto& v = input ? m.inputs : m.outputs;
+        for (size_t i = 0; i < v.size(); ++i) {
+            if (strcmp(v[i].tensor->name, io_name) == 0) {
+                for (auto& h : net->handles)
+                    if (h->is_input == input && h->index == (int)i) {
+                        *tensor = h.get();
+                        return TinyNN_SUCCESS;
+                    }
+                net->handles.emplace_back(new IoHandle{net, input, (int)i});
+                *tensor = net->handles.back().get();
+                return TinyNN_SUCCESS;
+            }
+        }
+    }
+    return fail(TinyNN_ERROR_NO_FOUND, "no input/output tensor named '%s'", io_name);
+}
+
+int LITE_get_tensor_total_size_in_byte(const LiteTensor tensor, size_t* size) {
+    if (!tensor || !size)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    IoSlot* s = slot_of(as_io(tensor));
+    if (!s)
+        return fail(TinyNN_ERROR_OUT_OF_RANGE, "stale tensor handle");
+    *size = s->bytes;
+    return TinyNN_SUCCESS;
+}
+
+int LITE_reset_tensor_memory(LiteTensor tensor, void* prepared_data, size_t data_length_in_byte) {
+    if (!tensor || !prepared_data)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    IoHandle* h = as_io(tensor);
+    IoSlot* s = slot_of(h);
+    if (!s)
+        return fail(TinyNN_ERROR_OUT_OF_RANGE, "stale tensor handle");
+    if (data_length_in_byte != s->bytes)
+        return fail(TinyNN_ERROR, "reset tensor memory with not equal size %zu != %zu",
+                    data_length_in_byte, s->bytes);
+    if (!h->is_input)
+        return fail(TinyNN_ERROR_NO_IMPLEMENT, "only input tensors take user memory");
+    cudaPointerAttributes attr;
+    bool is_dev = false;
+    if (cudaPointerGetAttributes(&attr, prepared_data) == cudaSuccess)
+        is_dev = attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+    else
+        cudaGetLastError();
+    if (is_dev && ((uintptr_t)prepared_data & 15))
+        return fail(TinyNN_ERROR_INVALID_LAYOUT, "device input must be 16-byte aligned");
+    s->user_ptr = prepared_data;
+    s->user_is_device = is_dev;
+    return TinyNN_SUCCESS;
+}
+
+int LITE_get_tensor_memory(const LiteTensor tensor, void** data) {
+    if (!tensor || !data)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    IoHandle* h = as_io(tensor);
+    IoSlot* s = slot_of(h);
+    if (!s)
+        return fail(TinyNN_ERROR_OUT_OF_RANGE, "stale tensor handle");
+    if (h->is_input) {
+        if (!s->user_ptr)
+            return fail(TinyNN_ERROR_NULL_PTR,
+                        "the input tensor memory is NULL: call LITE_reset_tensor_memory first");
+        *data = s->user_ptr;
+        return TinyNN_SUCCESS;
+    }
+    int rc = init_model_memory(h->net);
+    if (rc)
+        return rc;
+    if ((rc = wait(h->net)))  // results must be complete before the caller reads them
+        return rc;
+    *data = s->want_device ? s->tensor->ptr : s->host_stage;
+    return TinyNN_SUCCESS;
+}
+
+static int lite_dtype(TinyNNDType t, LiteCDataType* out) {
+    switch (t) {
+        case TinyNN_FLOAT: *out = LITE_FLOAT; return 0;
+        case TinyNN_FLOAT16: *out = LITE_HALF; return 0;
+        case TinyNN_INT: *out = LITE_INT; return 0;
+        case TinyNN_INT8: *out = LITE_INT8; return 0;
+        case TinyNN_INT16: *out = LITE_INT16; return 0;
+        case TinyNN_UINT8: *out = LITE_UINT8; return 0;
+        default:
+            // quantised dtypes have no lite counterpart (runtime/src/lite/tensor.c:11-40)
+            return TinyNN_ERROR_OUT_OF_RANGE;
+    }
+}
+
+int LITE_get_tensor_layout(const LiteTensor tensor, LiteLayout* layout) {
+    if (!tensor || !layout)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    IoSlot* s = slot_of(as_io(tensor));
+    if (!s)
+        return fail(TinyNN_ERROR_OUT_OF_RANGE, "stale tensor handle");
+    const int rc = lite_dtype(s->tensor->dtype.type_enum, &layout->data_type);
+    if (rc)
+        return fail(rc, "failed convert tinynn dtype to lite");
+    layout->ndim = s->tensor->layout.nr_dim;
+    for (size_t i = 0; i < layout->ndim; ++i)
+        layout->shapes[i] = s->tensor->layout.dims[i];
+    return TinyNN_SUCCESS;
+}
+
+int LITE_set_tensor_layout(LiteTensor tensor, const LiteLayout layout) {
+    if (!tensor)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    IoHandle* h = as_io(tensor);
+    Network* net = h->net;
+    // pick the DeviceModel (shape variant) whose tensor matches (tensor.c:78-91)
+    for (size_t mi = 0; mi < net->models.size(); ++mi) {
+        auto& v = h->is_input ? net->models[mi].inputs : net->models[mi].outputs;
+        if ((size_t)h->index >= v.size())
+            continue;
+        const Tensor* t = v[h->index].tensor;
+        bool same = (size_t)t->layout.nr_dim == layout.ndim;
+        for (size_t i = 0; same && i < layout.ndim; ++i)
+            same = t->layout.dims[i] == layout.shapes[i];
+        if (same) {
+            if (wait(net))
+                return TinyNN_ERROR_RUNTIME;
+            net->active = (int)mi;
+            return TinyNN_SUCCESS;
+        }
+    }
+    return fail(TinyNN_ERROR_INVALID_LAYOUT, "no device model has this layout");
+}
+
+int LITE_destroy_tensor(LiteTensor) {
+    return TinyNN_SUCCESS;
+}
+
+int LITE_forward(const LiteNetwork network) {
+    if (!network)
+        return fail(TinyNN_ERROR_NULL_PTR, "network is NULL");
+    return forward(as_net(network));
+}
+
+int LITE_wait(const LiteNetwork network) {
+    if (!network)
+        return fail(TinyNN_ERROR_NULL_PTR, "network is NULL");
+    return wait(as_net(network));
+}
+
+static int io_name(const LiteNetwork network, size_t index, const char** name, bool input) {
+    if (!network || !name)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    Network* net = as_net(network);
+    if (!net->loaded)
+        return fail(TinyNN_ERROR, "no model loaded");
+    auto& v = input ? net->models[net->active].inputs : net->models[net->active].outputs;
+    if (index >= v.size())
+        return fail(TinyNN_ERROR_OUT_OF_RANGE, "index %zu out of range", index);
+    *name = v[index].tensor->name;
+    return TinyNN_SUCCESS;
+}
+int LITE_get_input_name(const LiteNetwork network, size_t index, const char** name) {
+    return io_name(network, index, name, true);
+}
+int LITE_get_output_name(const LiteNetwork network, size_t index, const char** name) {
+    return io_name(network, index, name, false);
+}
+
+static int all_names(const LiteNetwork network, size_t* size, const char** name, bool input) {
+    if (!network)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    Network* net = as_net(network);
+    if (!net->loaded)
+        return fail(TinyNN_ERROR, "no model loaded");
+    auto& v = input ? net->models[net->active].inputs : net->models[net->active].outputs;
+    if (size)
+        *size = v.size();
+    if (name)
+        for (size_t i = 0; i < v.size(); ++i)
+            name[i] = v[i].tensor->name;
+    return TinyNN_SUCCESS;
+}
+int LITE_get_all_input_name(const LiteNetwork network, size_t* size, const char** name) {
+    return all_names(network, size, name, true);
+}
+int LITE_get_all_output_name(const LiteNetwork network, size_t* size, const char** name) {
+    return all_names(network, size, name, false);
+}
+
+int LITE_share_runtime_memroy(LiteNetwork src_network, LiteNetwork dst_network) {
+    if (!src_network || !dst_network)
+        return fail(TinyNN_ERROR_NULL_PTR, "network is NULL");
+    Network* src = as_net(src_network);
+    Network* dst = as_net(dst_network);
+    if (src->arena->ptr || dst->arena->ptr)
+        return fail(TinyNN_ERROR, "shared runtime memory should be called before model run");
+    if (src->device_id != dst->device_id)
+        return fail(TinyNN_ERROR, "networks live on different devices");
+    // one arena sized for the larger of the two; both networks must then run on one
+    // stream's worth of ordering, which the caller gets by waiting between forwards
+    src->arena->bytes = src->arena_need > dst->arena_need ? src->arena_need : dst->arena_need;
+    dst->arena = src->arena;
+    return TinyNN_SUCCESS;
+}
+
+int LITE_destroy_network(LiteNetwork network) {
+    if (!network)
+        return TinyNN_ERROR_NULL_PTR;
+    Network* net = as_net(network);
+    cudaSetDevice(net->device_id);
+    if (net->stream)
+        cudaStreamSynchronize(net->stream);
+    for (auto& m : net->models) {
+        if (net->profile)
+            for (auto& ins : m.instrs)
+                if (ins.is_opr && ins.op.ms_count)
+                    log_at(LITE_WARN, "profile %-90s %8.4f ms\n", ins.op.symbol.c_str(),
+                           ins.op.ms_total / ins.op.ms_count);
+        if (m.exec)
+            cudaGraphExecDestroy(m.exec);
+        for (auto& o : m.outputs)
+            if (o.host_stage)
+                cudaFreeHost(o.host_stage);
+    }
+    if (net->weight_arena)
+        cudaFree(net->weight_arena);
+    if (net->stream)
+        cudaStreamDestroy(net->stream);
+    delete net;
+    return TinyNN_SUCCESS;
+}
+
+// ---- additions without a counterpart in the reference ----
+int mb200_lite_stream(const LiteNetwork network, void** stream) {
+    if (!network || !stream)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    *stream = as_net(network)->stream;
+    return TinyNN_SUCCESS;
+}
+
+int mb200_lite_set_profile(LiteNetwork network, int enable) {
+    if (!network)
+        return fail(TinyNN_ERROR_NULL_PTR, "network is NULL");
+    as_net(network)->profile = enable != 0;
+    return TinyNN_SUCCESS;
+}
+
+int mb200_lite_profile(const LiteNetwork network, char* out, size_t cap) {
+    if (!network || !out || !cap)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    Network* net = as_net(network);
+    if (!net->loaded)
+        return fail(TinyNN_ERROR, "no model loaded");
+    std::string s;
+    char line[512];
+    for (auto& ins : net->models[net->active].instrs) {
+        if (!ins.is_opr)
+            continue;
+        snprintf(line, sizeof(line), "%s %s %.6f %d\n", ins.op.name.c_str(), ins.op.symbol.c_str(),
+                 ins.op.ms_count ? ins.op.ms_total / ins.op.ms_count : 0.f, ins.op.ms_count);
+        s += line;
+    }
+    if (s.size() + 1 > cap)
+        return fail(TinyNN_ERROR_OUT_OF_RANGE, "profile needs %zu bytes", s.size() + 1);
+    memcpy(out, s.c_str(), s.size() + 1);
+    return TinyNN_SUCCESS;
+}
+
+int LITE_get_device_id(const LiteNetwork network, int* device_id) {
+    if (!network || !device_id)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    *device_id = as_net(network)->device_id;
+    return TinyNN_SUCCESS;
+}
+
+int LITE_set_device_id(LiteNetwork network, int device_id) {
+    if (!network)
+        return fail(TinyNN_ERROR_NULL_PTR, "network is NULL");
+    Network* net = as_net(network);
+    if (net->loaded)
+        return fail(TinyNN_ERROR, "the device must be chosen before the model is loaded");
+    if (device_id < 0)
+        return fail(TinyNN_ERROR_OUT_OF_RANGE, "device id %d", device_id);
+    net->device_id = device_id;
+    return TinyNN_SUCCESS;
+}
+
+int LITE_get_device_type(const LiteNetwork network, LiteDeviceType* device_type) {
+    if (!network || !device_type)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    *device_type = LITE_CUDA;
+    return TinyNN_SUCCESS;
+}
+
+int LITE_get_tensor_device_type(const LiteTensor tensor, LiteDeviceType* device_type) {
+    if (!tensor || !device_type)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    IoHandle* h = as_io(tensor);
+    IoSlot* s = slot_of(h);
+    if (!s)
+        return fail(TinyNN_ERROR_OUT_OF_RANGE, "stale tensor handle");
+    const bool dev = h->is_input ? s->user_is_device : s->want_device;
+    *device_type = dev ? LITE_CUDA : LITE_CPU;
+    return TinyNN_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,166 @@
+"""Compile side on CPU: kernel selection through the KernelFunc interface, the static
+memory plan, the tinynn writer (checked with our loader's parser AND with the reference's
+own flatcc reader) and the generated host stubs."""
+import ctypes as C
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def describe(model_bytes):
+    from megcc_b200 import _lib
+    buf = C.create_string_buffer(4 << 20)
+    rc = _lib.lib().mb200_tinynn_describe(model_bytes, len(model_bytes), buf, len(buf))
+    return rc, buf.value.decode()
+
+
+def test_kernel_pack_symbols_follow_reference_naming():
+    from megcc_b200.compiler import probe_conv_symbol
+    ok, sym = probe_conv_symbol(64, 64, 56, 56, 3, 1, 1, nonline="RELU")
+    assert ok
+    # the reference's x86 symbol for the same operator is
+    # kernel_conv2d_3x3_NCHW_DENSE_p1x1_s1x1_d1x1_qsi8qsi8qsi32qsi8_bias_RELU
+    assert sym == "cuda_sm100_conv2d_3x3_NHWC_DENSE_p1x1_s1x1_d1x1_qsi8qsi8qsi32qsi8_bias_RELU"
+    ok, sym = probe_conv_symbol(32, 32, 112, 112, 3, 2, 1, groups=32, nonline="H_SWISH", bias=False)
+    assert ok and sym == "cuda_sm100_conv2d_3x3_NHWC_GROUP_p1x1_s2x2_d1x1_qsi8qsi8qsi32qsi8_H_SWISH"
+    # admission is a subset of BareMetal::ConvGeneral::IsAvailable: other formats and
+    # activations are refused, so the registry would fall through to the CPU kernels
+    assert not probe_conv_symbol(64, 64, 56, 56, 3, 1, 1, fmt="NCHW44")[0]
+    assert not probe_conv_symbol(64, 64, 56, 56, 3, 1, 1, nonline="SIGMOID")[0]
+
+
+def test_symbols_match_the_reference_kernels_one_to_one(reference):
+    """Every CUDA symbol of the two models has a reference x86 kernel of the same family and
+    attributes (the one the checker runs)."""
+    from megcc_b200 import zoo
+    for spec in (zoo.resnet18(), zoo.mobilenet_v1()):
+        g = spec.to_graph()
+        g.compile([1])
+        for sym in g.kernel_symbols():
+            ref = sym.replace("cuda_sm100_", "kernel_").replace("_NHWC_", "_NCHW_")
+            assert reference.ref_has(ref), f"{sym}: no reference kernel {ref}"
+
+
+def _parse_plan(text, model=0):
+    tensors, oprs, cur = {}, [], -1
+    for line in text.splitlines():
+        if line.startswith("device_model"):
+            cur += 1
+        if cur != model:
+            continue
+        m = re.match(r"tensor (\S+) offset=(\d+) bytes=(\d+)", line)
+        if m:
+            tensors[m.group(1)] = (int(m.group(2)), int(m.group(3)))
+        m = re.match(r"opr (\S+) in=(\S*) out=(\S*)", line)
+        if m:
+            oprs.append((m.group(1), [x for x in m.group(2).split(",") if x],
+                         [x for x in m.group(3).split(",") if x]))
+    return tensors, oprs
+
+
+@pytest.mark.parametrize("net", ["resnet18", "mobilenet_v1"])
+def test_memory_plan_never_overlaps_live_tensors(net):
+    from megcc_b200 import zoo
+    spec = getattr(zoo, net)()
+    g = spec.to_graph()
+    model = g.compile([1, 8])
+    rc, text = describe(model)
+    assert rc == 0
+    for mi, batch in enumerate((1, 8)):
+        tensors, oprs = _parse_plan(text, mi)
+        first, last = {"data": 0}, {}
+        for k, (_, ins, outs) in enumerate(oprs):
+            for t in ins:
+                if t in tensors:
+                    last[t] = k
+            for t in outs:
+                first.setdefault(t, k)
+                last[t] = max(last.get(t, k), k)
+        last[oprs[-1][2][0]] = len(oprs)
+        names = [t for t in tensors if t in first]
+        for i, a in enumerate(names):
+            for b in names[i + 1:]:
+                if last[a] < first[b] or last[b] < first[a]:
+                    continue
+                (oa, sa), (ob, sb) = tensors[a], tensors[b]
+                assert oa + sa <= ob or ob + sb <= oa, f"{a} and {b} overlap while both live"
+        arena = g.arena_bytes(mi)
+        assert all(o % 256 == 0 and o + s <= arena for o, s in tensors.values())
+        assert arena < 0.5 * g.unplanned_bytes(mi), "the plan should reuse memory"
+
+
+def test_reference_reader_accepts_our_model(tmp_path):
+    """The reference's flatcc-generated reader sees the model we wrote."""
+    tool = os.path.join(ROOT, "oracle", "_ref", "ref_tinynn_dump")
+    if not os.path.exists(tool):
+        pytest.skip("oracle/_ref not built")
+    from megcc_b200 import zoo
+    spec = zoo.resnet18()
+    model = spec.to_graph().compile([2])
+    path = tmp_path / "r18.tiny"
+    path.write_bytes(model)
+    out = subprocess.run([tool, str(path)], capture_output=True, text=True, check=True).stdout
+    assert "model name=resnet18_int8" in out
+    assert "device=7" in out  # CUDA_SM100, appended to the Device enum
+    theirs = [l for l in out.splitlines() if l.startswith("tensor ")]
+    rc, ours = describe(model)
+    mine = [l for l in ours.splitlines() if l.startswith("tensor ")]
+    assert rc == 0 and len(theirs) == len(mine) == 32
+    for a, b in zip(theirs, mine):
+        assert a.split()[1] == b.split()[1]
+        assert re.search(r"offset=(\d+)", a).group(1) == re.search(r"offset=(\d+)", b).group(1)
+        assert re.search(r"dims=(\S+)", a).group(1) == re.search(r"dims=(\S+)", b).group(1)
+        assert re.search(r"stride=(\S+)", a).group(1) == re.search(r"stride=(\S+)", b).group(1)
+    # weights arrive byte for byte
+    w = [l for l in out.splitlines() if l.startswith("weight stem:filter")][0]
+    assert "bytes=9408" in w and "dims=64x3x7x7" in w
+    assert len([l for l in out.splitlines() if l.startswith("opr ")]) == 31
+
+
+def test_truncated_and_corrupt_models_are_rejected_not_crashed():
+    from megcc_b200 import zoo
+    model = zoo.single_conv().to_graph().compile([1])
+    assert describe(model)[0] == 0
+    for cut in (0, 3, 7, 64, len(model) // 2, len(model) - 64):
+        rc, _ = describe(model[:cut])
+        assert rc in (5, 7), f"cut at {cut}: status {rc}"
+    rng = np.random.default_rng(7)
+    for _ in range(200):
+        bad = bytearray(model)
+        for pos in rng.integers(0, min(len(bad), 2000), 8):
+            bad[pos] = int(rng.integers(0, 256))
+        assert describe(bytes(bad))[0] in (0, 4, 5, 6, 7, 10, 11, 12)
+
+
+def test_unknown_kernel_symbol_is_reported():
+    from megcc_b200 import zoo
+    model = zoo.single_conv().to_graph().compile([1])
+    bad = model.replace(b"cuda_sm100_conv2d_3x3", b"cuda_sm100_conv9d_3x3")
+    assert describe(bad)[0] == 5  # TinyNN_ERROR_NO_FOUND
+
+
+def test_exported_stubs_compile_against_public_headers(tmp_path):
+    """kernels.h / kernels.c / <symbol>.c, laid out like the reference exporter's output,
+    compile as C against include/ and link against libmegcc_b200.so."""
+    from megcc_b200 import zoo, _lib
+    g = zoo.resnet18().to_graph()
+    g.compile([1])
+    g.export_kernels(str(tmp_path))
+    files = sorted(os.listdir(tmp_path))
+    assert "kernels.h" in files and "kernels.c" in files
+    syms = g.kernel_symbols()
+    assert all(s + ".c" in files for s in syms)
+    srcs = [str(tmp_path / f) for f in files if f.endswith(".c")]
+    so = str(tmp_path / "libkernels.so")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-shared", "-fPIC",
+                    "-I" + os.path.join(ROOT, "include"), "-I" + str(tmp_path), "-o", so] + srcs
+                   + [_lib.LIB_PATH], check=True)
+    L = C.CDLL(so)
+    L.load_kernel_init_function()
+    tab = (C.c_void_p * len(syms)).in_dll(L, "kernels")
+    assert all(tab[i] for i in range(len(syms)))

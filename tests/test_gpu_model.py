@@ -1,0 +1,127 @@
+"""Whole compiled models through the LITE_* C API on the GPU, against the CPU checker
+walking the same layer list (bit-exact int8 outputs)."""
+import numpy as np
+import pytest
+
+import cases
+import golden_util as G
+import netwalk
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lite():
+    assert torch.cuda.is_available()
+    from megcc_b200 import lite as L
+    return L
+
+
+def run_model(lite, model, x, out_shape, forwards=1, device_io=()):
+    net = lite.Network(model, device_io=device_io)
+    name_in, name_out = net.input_names()[0], net.output_names()[0]
+    outs = []
+    for _ in range(forwards):
+        net.set_input(name_in, x)
+        net.forward()
+        net.wait()
+        outs.append(net.output(name_out).reshape(out_shape))
+    net.close()
+    return outs
+
+
+def test_single_conv_model_matches_golden(lite):
+    from megcc_b200 import zoo
+    for dst_scale in (0.1, 5.0):
+        c = cases.conv_cfg1(dst_scale)
+        src, flt, bias = cases.conv_inputs(c)
+        spec = zoo.single_conv(s_dst=dst_scale)
+        spec.layers[0]["flt"], spec.layers[0]["bias"] = flt, bias
+        model = spec.to_graph().compile([1])
+        out = run_model(lite, model, src, (1, 64, 56, 56))[0]
+        G.check("conv_bias_qs8", c["name"], out, src, flt, bias)
+
+
+@pytest.mark.parametrize("per_channel", [False, True])
+def test_resnet18_matches_oracle(lite, oracle, per_channel):
+    from megcc_b200 import zoo
+    spec = zoo.resnet18(per_channel=per_channel)
+    x = cases.rng_for("resnet18_input").integers(-128, 128, (4, 3, 224, 224), dtype=np.int8)
+    model = spec.to_graph().compile([4])
+    want = netwalk.run(spec, x, oracle)
+    # three forwards: eager pass, graph capture + launch, graph replay
+    outs = run_model(lite, model, x, want.shape, forwards=3)
+    for i, out in enumerate(outs):
+        bad = int((out != want).sum())
+        assert bad == 0, f"forward {i}: {bad}/{want.size} logits differ"
+    assert len(np.unique(want)) > 8
+
+
+def test_resnet18_reference_kernels_agree(lite, reference):
+    """Same check against the reference's own x86 kernels chained layer by layer."""
+    from megcc_b200 import zoo
+    spec = zoo.resnet18(seed=1)
+    x = cases.rng_for("resnet18_ref_input").integers(-128, 128, (1, 3, 224, 224), dtype=np.int8)
+    want = netwalk.run(spec, x, reference, use_reference=True)
+    out = run_model(lite, spec.to_graph().compile([1]), x, want.shape)[0]
+    assert (out == want).all()
+
+
+def test_mobilenet_v1_matches_oracle(lite, oracle):
+    from megcc_b200 import zoo
+    spec = zoo.mobilenet_v1()
+    x = cases.rng_for("mbv1_input").integers(-128, 128, (2, 3, 224, 224), dtype=np.int8)
+    want = netwalk.run(spec, x, oracle)
+    outs = run_model(lite, spec.to_graph().compile([2]), x, want.shape, forwards=2)
+    assert (outs[0] == want).all() and (outs[1] == want).all()
+
+
+def test_batch_variants_and_device_io(lite, oracle):
+    from megcc_b200 import zoo
+    spec = zoo.resnet18(hw=64, classes=100)
+    model = spec.to_graph().compile([1, 3])
+    net = lite.Network(model, device_io=("fc:out",))
+    x3 = cases.rng_for("variants").integers(-128, 128, (3, 3, 64, 64), dtype=np.int8)
+    want3 = netwalk.run(spec, x3, oracle)
+    # DeviceModel 0 is the batch-1 variant; selecting the batch-3 layout switches models
+    net.select_batch("data", (3, 3, 64, 64))
+    assert net.tensor_bytes("data") == x3.nbytes
+    xd = torch.from_numpy(x3).cuda()
+    for _ in range(3):
+        net.set_input_ptr("data", xd.data_ptr(), x3.nbytes)  # device memory, used in place
+        net.forward()
+        net.wait()
+    import ctypes
+    ptr = net.output_ptr("fc:out")  # device pointer: declared with is_host = 0
+    rt = ctypes.CDLL("/usr/local/cuda/lib64/libcudart.so")
+    host = np.empty(want3.size, np.int8)
+    # kind 2 = device to host: fails if ptr were host memory
+    rc = rt.cudaMemcpy(ctypes.c_void_p(host.ctypes.data), ctypes.c_void_p(ptr),
+                       ctypes.c_size_t(want3.size), 2)
+    assert rc == 0
+    assert (host.reshape(want3.shape) == want3).all()
+    net.select_batch("data", (1, 3, 64, 64))
+    net.set_input("data", x3[:1])
+    net.forward()
+    net.wait()
+    net.close()
+
+
+def test_api_errors(lite):
+    from megcc_b200 import zoo
+    model = zoo.single_conv(hw=16).to_graph().compile([1])
+    with pytest.raises(lite.LiteError) as e:
+        lite.Network(model[:100])
+    assert e.value.status == 7
+    net = lite.Network(model)
+    with pytest.raises(lite.LiteError) as e:
+        net.forward()  # no input memory yet
+    assert e.value.status == 1
+    with pytest.raises(lite.LiteError) as e:
+        net.set_input("data", np.zeros(5, np.int8))  # wrong byte count
+    assert e.value.status == 13
+    with pytest.raises(lite.LiteError) as e:
+        net.tensor("nonexistent")
+    assert e.value.status == 5
+    net.close()

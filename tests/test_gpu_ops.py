@@ -73,7 +73,7 @@ UMMA_CASES = [
     ("s1_512", 6, 512, 512, 7, 7, 3, 1, 1, "RELU"),
     ("fc_512_1000", 256, 512, 1000, 1, 1, 1, 1, 0, "IDENTITY"),
     ("pw_1024", 3, 1024, 1024, 7, 7, 1, 1, 0, "RELU"),
-    ("k5_s1", 1, 64, 72, 40, 40, 5, 1, 2, "RELU"),
+    ("k5_s1", 2, 64, 72, 40, 40, 5, 1, 2, "RELU"),
     ("k7_s2_p3", 1, 64, 64, 48, 48, 7, 2, 3, "RELU"),
     ("nopad_k3", 1, 64, 64, 50, 50, 3, 1, 0, "RELU"),
     ("s3", 1, 64, 64, 50, 47, 3, 3, 1, "RELU"),
