@@ -76,6 +76,21 @@ MB200_API int mb200_conv_bias_qs8_nhwc(
         const mb200_conv_param* p, const int8_t* src, int src_is_nchw,
         const int8_t* flt_packed, const int32_t* bias, const float* flt_scales, int8_t* dst,
         int algo, void* stream);
+/* First-layer form: stride 2 and at most 4 input channels run on the tensor cores after a
+ * 2x2 space-to-depth step into `workspace` (device scratch, 16-byte aligned, at least
+ * mb200_conv_s2d_workspace_bytes(p)). The filter must have been packed by
+ * mb200_conv_s2d_pack_filter (mb200_conv_s2d_filter_bytes(p) bytes). Same operator and
+ * results as mb200_conv_bias_qs8_nhwc. mb200_conv_s2d_supported(p) != 0 says the path
+ * applies to p. */
+MB200_API int mb200_conv_s2d_supported(const mb200_conv_param* p);
+MB200_API size_t mb200_conv_s2d_filter_bytes(const mb200_conv_param* p);
+MB200_API size_t mb200_conv_s2d_workspace_bytes(const mb200_conv_param* p);
+MB200_API int mb200_conv_s2d_pack_filter(
+        const mb200_conv_param* p, const int8_t* flt_oihw, int8_t* flt_s2d, void* stream);
+MB200_API int mb200_conv_bias_qs8_s2d(
+        const mb200_conv_param* p, const int8_t* src, int src_is_nchw, const int8_t* flt_s2d,
+        const int32_t* bias, const float* flt_scales, int8_t* dst, void* workspace,
+        size_t workspace_bytes, void* stream);
 /* Same operator in the reference's own layouts: src/dst NCHW, filter OIHW. Needs
  * mb200_conv_bias_qs8_nchw_workspace(p) bytes of device scratch (256-byte aligned). */
 MB200_API size_t mb200_conv_bias_qs8_nchw_workspace(const mb200_conv_param* p);

@@ -1,5 +1,7 @@
 #include "cuda_kernel_pack.h"
 
+#include "../csrc/conv_s2d_geom.h"
+
 #include <cmath>
 #include <sstream>
 
@@ -148,6 +150,12 @@ TinyNNStatus ${signature} {
     const int src_is_nchw = src->layout.format == TinyNN_NCHW;
     const int32_t* bias = ${has_bias} ? (const int32_t*)inputs[2]->ptr : 0;
     const float* ch_scales = nr_input > ${scale_idx} ? (const float*)inputs[${scale_idx}]->ptr : 0;
+    if (mb200_conv_s2d_supported(&p)) {
+        /* first-layer form; the filter was packed for it by the init function below */
+        return (TinyNNStatus)mb200_conv_bias_qs8_s2d(
+                &p, (const int8_t*)src->ptr, src_is_nchw, (const int8_t*)flt->ptr, bias, ch_scales,
+                (int8_t*)dst->ptr, workspace->ptr, workspace->size, mb200_opt_stream(opt));
+    }
     return (TinyNNStatus)mb200_conv_bias_qs8_nhwc(
             &p, (const int8_t*)src->ptr, src_is_nchw, (const int8_t*)flt->ptr, bias, ch_scales,
             (int8_t*)dst->ptr, MB200_ALGO_AUTO, mb200_opt_stream(opt));
@@ -178,37 +186,95 @@ TinyNNStatus ${signature} {
 std::string ConvBiasQS8::GetInitBody(TContext* ctx) const {
     Subst s{R"(
 ${prologue}
+static void ${symbol}_param(Tensor** inputs, mb200_conv_param* p) {
+    const Tensor* src = inputs[0];
+    const Layout* l = &inputs[1]->layout;
+    const int grouped = l->nr_dim == 5;
+    p->n = src->layout.dims[0];
+    p->ic = src->layout.dims[1];
+    p->ih = src->layout.dims[2];
+    p->iw = src->layout.dims[3];
+    p->groups = grouped ? (int)l->dims[0] : 1;
+    p->oc = grouped ? (int)(l->dims[0] * l->dims[1]) : (int)l->dims[0];
+    p->kh = ${kh}; p->kw = ${kw};
+    p->stride_h = ${sh}; p->stride_w = ${sw};
+    p->pad_h = ${ph}; p->pad_w = ${pw};
+    p->dilate_h = ${dh}; p->dilate_w = ${dw};
+    p->nonline = 0;
+    p->src_scale = p->flt_scale = p->dst_scale = 1.f;
+}
 TinyNNStatus ${signature} {
     Tensor* in_weights = inputs[1];
+    mb200_conv_param p;
+    ${symbol}_param(inputs, &p);
+    const int s2d = mb200_conv_s2d_supported(&p);
     if (out_weights == 0 && nr_out_weight != 0) {
         *nr_out_weight = 1;
         return TinyNN_SUCCESS;
     }
     if (out_weights != 0 && nr_out_weight == 0) {
         out_weights->layout = in_weights->layout;
+        if (s2d) { /* a flat byte buffer of the space-to-depth packing */
+            out_weights->layout.nr_dim = 1;
+            out_weights->layout.dims[0] = (uint32_t)mb200_conv_s2d_filter_bytes(&p);
+            out_weights->layout.stride[0] = 1;
+        }
         out_weights->dtype = in_weights->dtype;
         out_weights->name = in_weights->name;
         return TinyNN_SUCCESS;
     }
-    mb200_conv_param p;
-    const Layout* l = &in_weights->layout;
-    const int grouped = l->nr_dim == 5;
-    p.groups = grouped ? l->dims[0] : 1;
-    p.oc = grouped ? l->dims[0] * l->dims[1] : l->dims[0];
-    p.ic = grouped ? l->dims[0] * l->dims[2] : l->dims[1];
-    p.kh = l->dims[l->nr_dim - 2];
-    p.kw = l->dims[l->nr_dim - 1];
-    p.n = 1; p.ih = p.kh; p.iw = p.kw;
-    p.stride_h = p.stride_w = p.dilate_h = p.dilate_w = 1;
-    p.pad_h = p.pad_w = 0;
-    p.nonline = 0;
-    p.src_scale = p.flt_scale = p.dst_scale = 1.f;
+    if (s2d)
+        return (TinyNNStatus)mb200_conv_s2d_pack_filter(
+                &p, (const int8_t*)in_weights->ptr, (int8_t*)out_weights->ptr,
+                mb200_opt_stream(opt));
     return (TinyNNStatus)mb200_conv_pack_filter(
             &p, (const int8_t*)in_weights->ptr, (int8_t*)out_weights->ptr, mb200_opt_stream(opt));
 }
 )"};
-    s.set("prologue", GenStubPrologue()).set("signature", GetInitSignature(ctx));
+    s.set("prologue", GenStubPrologue())
+            .set("signature", GetInitSignature(ctx))
+            .set("symbol", GetKernelSymbol(ctx))
+            .set("kh", ctx->getAttrUInt("kernel_h"))
+            .set("kw", ctx->getAttrUInt("kernel_w"))
+            .set("sh", ctx->getAttrUInt("stride_h"))
+            .set("sw", ctx->getAttrUInt("stride_w"))
+            .set("ph", ctx->getAttrUInt("pad_h"))
+            .set("pw", ctx->getAttrUInt("pad_w"))
+            .set("dh", ctx->getAttrUInt("dilate_h"))
+            .set("dw", ctx->getAttrUInt("dilate_w"));
     return s.text;
+}
+
+// Workspace: the space-to-depth tensor of the first-layer form, nothing otherwise. The
+// reference sizes workspaces by running this function at compile time (JIT); the CUDA
+// pack also answers directly through WorkspaceBytes().
+std::string ConvBiasQS8::GetWorkspaceBody(TContext* ctx) const {
+    Subst s{R"(
+TinyNNStatus ${signature} {
+    mb200_conv_param p;
+    ${symbol}_param(inputs, &p);
+    *workspace = mb200_conv_s2d_supported(&p) ? mb200_conv_s2d_workspace_bytes(&p) : 0;
+    return TinyNN_SUCCESS;
+}
+)"};
+    s.set("signature", GetWorkspaceSignature(ctx)).set("symbol", GetKernelSymbol(ctx));
+    return s.text;
+}
+
+size_t ConvBiasQS8::WorkspaceBytes(TContext* ctx) const {
+    const CCOperand src = ctx->getAttrOprand("operand:0");
+    const CCOperand flt = ctx->getAttrOprand("operand:1");
+    const CCOperand dst = last_operand(ctx);
+    if (src.shape.size() != 4 || dst.shape.size() != 4)
+        return 0;
+    const int groups = ctx->getAttrStr("sparse") == "DENSE" ? 1 : (int)flt.shape[0];
+    const mb200::S2dGeom g = mb200::s2d_geometry(
+            (int)src.shape[0], (int)src.shape[1], (int)src.shape[2], (int)src.shape[3],
+            (int)dst.shape[1], (int)ctx->getAttrUInt("kernel_h"), (int)ctx->getAttrUInt("kernel_w"),
+            (int)ctx->getAttrUInt("stride_h"), (int)ctx->getAttrUInt("stride_w"),
+            (int)ctx->getAttrUInt("pad_h"), (int)ctx->getAttrUInt("pad_w"),
+            (int)ctx->getAttrUInt("dilate_h"), (int)ctx->getAttrUInt("dilate_w"), groups);
+    return g.ok ? g.workspace_bytes : 0;
 }
 
 // ------------------------------------------------------------------------------------------

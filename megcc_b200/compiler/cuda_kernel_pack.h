@@ -22,6 +22,9 @@ public:
     std::string GetKernelSymbol(TContext* ctx) const override;
     std::string GetKernelBody(TContext* ctx) const override;
     std::string GetInitBody(TContext* ctx) const override;
+    std::string GetWorkspaceBody(TContext* ctx) const override;
+    // bytes of device scratch the kernel needs for the operator `ctx` describes
+    size_t WorkspaceBytes(TContext* ctx) const;
 };
 
 class PoolingQS8 : public KernelFunc {

@@ -228,7 +228,8 @@ size_t align256(size_t v) {
 // lifetime. Returns the arena size.
 size_t plan_memory(
         const mb200c_graph& g, const std::vector<GOp>& ops, int batch,
-        std::vector<size_t>* offsets, size_t* unplanned) {
+        const std::vector<size_t>& ws_bytes, std::vector<size_t>* offsets,
+        std::vector<size_t>* ws_offsets, size_t* unplanned) {
     const size_t n = g.tensors.size();
     std::vector<int> first(n, -1), last(n, -1);
     for (size_t i = 0; i < n; ++i)
@@ -254,19 +255,35 @@ size_t plan_memory(
     std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) {
         return tensor_bytes(g.tensors[a], batch) > tensor_bytes(g.tensors[b], batch);
     });
-    offsets->assign(n, 0);
+    // workspaces are planned as extra buffers that live for exactly one instruction
+    struct Item {
+        size_t bytes;
+        int first, last;
+        size_t offset;
+    };
+    std::vector<Item> items;
+    for (size_t i = 0; i < n; ++i)
+        items.push_back({first[i] >= 0 ? align256(tensor_bytes(g.tensors[i], batch)) : 0, first[i],
+                         last[i], 0});
+    for (size_t k = 0; k < ops.size(); ++k)
+        items.push_back({align256(ws_bytes[k]), ws_bytes[k] ? (int)k : -1, (int)k, 0});
+    order.clear();
+    for (size_t i = 0; i < items.size(); ++i)
+        if (items[i].first >= 0 && items[i].bytes)
+            order.push_back(i);
+    std::stable_sort(order.begin(), order.end(),
+                     [&](size_t a, size_t b) { return items[a].bytes > items[b].bytes; });
     std::vector<size_t> placed;
     size_t arena = 0;
     *unplanned = 0;
     for (size_t id : order) {
-        const size_t sz = align256(tensor_bytes(g.tensors[id], batch));
+        const size_t sz = items[id].bytes;
         *unplanned += sz;
-        // gather busy intervals of tensors alive at the same time
+        // gather busy intervals of buffers alive at the same time
         std::vector<std::pair<size_t, size_t>> busy;
         for (size_t o : placed)
-            if (!(last[o] < first[id] || last[id] < first[o]))
-                busy.push_back({(*offsets)[o],
-                                (*offsets)[o] + align256(tensor_bytes(g.tensors[o], batch))});
+            if (!(items[o].last < items[id].first || items[id].last < items[o].first))
+                busy.push_back({items[o].offset, items[o].offset + items[o].bytes});
         std::sort(busy.begin(), busy.end());
         size_t off = 0;
         for (auto& b : busy) {
@@ -274,10 +291,16 @@ size_t plan_memory(
                 break;
             off = std::max(off, b.second);
         }
-        (*offsets)[id] = off;
+        items[id].offset = off;
         arena = std::max(arena, off + sz);
         placed.push_back(id);
     }
+    offsets->assign(n, 0);
+    for (size_t i = 0; i < n; ++i)
+        (*offsets)[i] = items[i].offset;
+    ws_offsets->assign(ops.size(), 0);
+    for (size_t k = 0; k < ops.size(); ++k)
+        (*ws_offsets)[k] = items[n + k].offset;
     return arena;
 }
 
@@ -557,9 +580,19 @@ int mb200c_compile(
         const int batch = batches[bi];
         if (batch <= 0)
             return err("compile: batch %d", batch);
+        // workspace bytes per operator, as the kernel that was selected reports them
+        std::vector<size_t> ws_bytes(work.ops.size(), 0), ws_offsets;
+        for (size_t k = 0; k < work.ops.size(); ++k) {
+            if (work.ops[k].type != OpType::CONV)
+                continue;
+            auto ctx = work.context_for(work.ops[k], batch);
+            auto* conv = dynamic_cast<const KernelGen::Cuda::ConvBiasQS8*>(g->kernel_of[op_symbol[k]]);
+            if (conv)
+                ws_bytes[k] = conv->WorkspaceBytes(ctx.get());
+        }
         std::vector<size_t> offsets;
         Compiled c;
-        c.arena = plan_memory(work, work.ops, batch, &offsets, &c.unplanned);
+        c.arena = plan_memory(work, work.ops, batch, ws_bytes, &offsets, &ws_offsets, &c.unplanned);
         g->compiled.push_back(c);
 
         std::vector<fb::NodeP> tnodes;
@@ -596,8 +629,8 @@ int mb200c_compile(
                 in_t.push_back(fb::WEIGHT);
             }
             auto ws = fb::make_table();
-            ws->add<int64_t>(fb::field::WS_size, 0);
-            ws->add<int64_t>(fb::field::WS_offset, 0);
+            ws->add<int64_t>(fb::field::WS_size, (int64_t)ws_bytes[k]);
+            ws->add<int64_t>(fb::field::WS_offset, (int64_t)ws_offsets[k]);
             auto n = fb::make_table();
             n->add_ref(fb::field::O_name, fb::make_string(op.name));
             n->add_ref(fb::field::O_type, fb::make_string(op_symbol[k]));

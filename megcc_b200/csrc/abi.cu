@@ -178,12 +178,67 @@ int mb200_conv_acc_qs8_nhwc(
             a, src, flt_packed, bias, nullptr, nullptr, acc, (cudaStream_t)stream);
 }
 
+int mb200_conv_s2d_supported(const mb200_conv_param* p) {
+    ConvArgs a{};
+    if (make_args(p, 0, &a))
+        return 0;
+    return conv_s2d_supported(a) ? 1 : 0;
+}
+
+size_t mb200_conv_s2d_filter_bytes(const mb200_conv_param* p) {
+    ConvArgs a{};
+    if (make_args(p, 0, &a))
+        return 0;
+    return conv_s2d_filter_bytes(a);
+}
+
+size_t mb200_conv_s2d_workspace_bytes(const mb200_conv_param* p) {
+    ConvArgs a{};
+    if (make_args(p, 0, &a))
+        return 0;
+    return conv_s2d_workspace_bytes(a);
+}
+
+int mb200_conv_s2d_pack_filter(
+        const mb200_conv_param* p, const int8_t* flt_oihw, int8_t* flt_s2d, void* stream) {
+    ConvArgs a{};
+    int rc = make_args(p, 0, &a);
+    if (rc)
+        return rc;
+    if (!flt_oihw || !flt_s2d)
+        return set_error(ST_NULL_PTR, "filter pointer is NULL");
+    if (!conv_s2d_supported(a))
+        return set_error(ST_NO_IMPLEMENT, "the space-to-depth path does not apply to this conv");
+    return launch_conv_s2d_pack_filter(a, flt_oihw, flt_s2d, (cudaStream_t)stream);
+}
+
+int mb200_conv_bias_qs8_s2d(
+        const mb200_conv_param* p, const int8_t* src, int src_is_nchw, const int8_t* flt_s2d,
+        const int32_t* bias, const float* flt_scales, int8_t* dst, void* workspace,
+        size_t workspace_bytes, void* stream) {
+    ConvArgs a{};
+    int rc = make_args(p, src_is_nchw, &a);
+    if (rc)
+        return rc;
+    if (!src || !flt_s2d || !dst || !workspace)
+        return set_error(ST_NULL_PTR, "conv tensor or workspace pointer is NULL");
+    if (!conv_s2d_supported(a))
+        return set_error(ST_NO_IMPLEMENT, "the space-to-depth path does not apply to this conv");
+    if (workspace_bytes < conv_s2d_workspace_bytes(a))
+        return set_error(ST_OUT_OF_RANGE, "workspace of %zu bytes is too small", workspace_bytes);
+    if (((uintptr_t)workspace | (uintptr_t)flt_s2d | (uintptr_t)dst) & 15)
+        return set_error(ST_INVALID_LAYOUT, "workspace, filter and dst must be 16-byte aligned");
+    return launch_conv_s2d(a, src, flt_s2d, bias, flt_scales, dst, workspace, (cudaStream_t)stream);
+}
+
 size_t mb200_conv_bias_qs8_nchw_workspace(const mb200_conv_param* p) {
     ConvArgs a{};
     if (make_args(p, 0, &a))
         return 0;
-    const size_t src = align_up((size_t)a.n * a.ih * a.iw * a.ic, 256);
     const size_t dst = align_up((size_t)a.m * a.oc, 256);
+    if (conv_s2d_supported(a))
+        return dst + align_up(conv_s2d_filter_bytes(a), 256) + conv_s2d_workspace_bytes(a);
+    const size_t src = align_up((size_t)a.n * a.ih * a.iw * a.ic, 256);
     const size_t flt = align_up(mb200_conv_packed_filter_bytes(p), 256);
     return src + dst + flt;
 }
@@ -203,6 +258,27 @@ int mb200_conv_bias_qs8_nchw(
     if ((uintptr_t)workspace & 255)
         return set_error(ST_INVALID_LAYOUT, "workspace must be 256-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
+    if (conv_s2d_supported(a) && algo != MB200_ALGO_DIRECT) {
+        // first-layer form: the input is read in place, only the output needs a transpose
+        int8_t* ws_dst = (int8_t*)workspace;
+        int8_t* ws_flt = ws_dst + align_up((size_t)a.m * a.oc, 256);
+        int8_t* ws_s2d = ws_flt + align_up(conv_s2d_filter_bytes(a), 256);
+        a.src_is_nchw = 1;
+        if ((rc = launch_conv_s2d_pack_filter(a, flt_oihw, ws_flt, st)))
+            return rc;
+        if ((rc = launch_conv_s2d(a, src, ws_flt, bias, flt_scales, ws_dst, ws_s2d, st)))
+            return rc;
+        return launch_transpose_s8(ws_dst, dst, a.n, a.oh * a.ow, a.oc, st);
+    }
+    if (conv_s2d_supported(a)) {
+        // the general kernel on this shape: same scratch budget, standard packing
+        const size_t need = align_up((size_t)a.n * a.ih * a.iw * a.ic, 256) +
+                            align_up((size_t)a.m * a.oc, 256) +
+                            align_up(mb200_conv_packed_filter_bytes(p), 256);
+        if (workspace_bytes < need)
+            return set_error(ST_OUT_OF_RANGE, "workspace of %zu bytes is too small",
+                             workspace_bytes);
+    }
     int8_t* ws_src = (int8_t*)workspace;
     int8_t* ws_dst = ws_src + align_up((size_t)a.n * a.ih * a.iw * a.ic, 256);
     int8_t* ws_flt = ws_dst + align_up((size_t)a.m * a.oc, 256);

@@ -47,6 +47,35 @@ __device__ __forceinline__ int requant_conv(
     return fp32_to_int8(apply_act(act, x));
 }
 
+// ---- the same arithmetic in fewer instructions, still bit-exact ----
+//
+// Division: with r = RN(1/d) (computed on the host), q0 = RN(t*r), rem = t - q0*d (exact in
+// one FMA) and q = RN(q0 + rem*r) equals RN(t/d) for every normal t; checked exhaustively
+// over all numerators for the divisors in tests/requant_math_check.c. Three instructions
+// instead of the general division routine.
+__device__ __forceinline__ float div_rn_by_const(float t, float d, float r) {
+    const float q0 = __fmul_rn(t, r);
+    const float rem = __fmaf_rn(-q0, d, t);
+    return __fmaf_rn(rem, r, q0);
+}
+
+// roundf (half away from zero) followed by the x86 float->int conversion and the int8
+// clamp. trunc(x + copysign(0.49999997f, x)) == roundf(x) for every float below 2^31 in
+// magnitude (0.49999997f is the largest float below one half); larger magnitudes convert
+// to INT_MIN on x86 and therefore clamp to -128.
+__device__ __forceinline__ int round_clamp_s8(float x) {
+    const float y = __fadd_rn(x, copysignf(0.49999997f, x));
+    int q = __float2int_rz(y);
+    q = min(max(q, -128), 127);
+    return (fabsf(x) < 2147483648.f) ? q : -128;
+}
+
+__device__ __forceinline__ int requant_conv_fast(
+        int acc, float s_src, float s_flt, float s_dst, float inv_dst, int act) {
+    const float t = __fmul_rn(__fmul_rn(__int2float_rn(acc), s_src), s_flt);
+    return round_clamp_s8(apply_act(act, div_rn_by_const(t, s_dst, inv_dst)));
+}
+
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
     return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
            ((uint32_t)(d & 0xff) << 24);

@@ -2,20 +2,25 @@
 //
 //   D[m, oc] = sum_{fy,fx,c} A[m, (fy,fx,c)] * W[oc, (fy,fx,c)],   m = (n, oh, ow) linearised
 //
-// * activations NHWC int8; one TMA im2col load per (filter tap, 64-channel block) brings the
-//   128 consecutive output pixels of the tile straight into a 64B-swizzled K-major tile
-//   (padding and stride are resolved by the im2col bounding box / traversal stride);
-// * filter pre-packed [OC][KH][KW][IC], fetched by a tiled 2D TMA into the same swizzle;
-// * tcgen05.mma kind::i8, M=128 x N=BN x K=32 per instruction, int32 accumulators in TMEM;
-// * warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM alloc), warps 2..5 =
-//   epilogue (tcgen05.ld -> +bias -> fp32 requant in the reference's operation order ->
-//   activation -> int8 -> 16-byte stores);
+// * activations NHWC int8. One TMA im2col load brings, for one filter tap, the channels of
+//   the 128 consecutive output pixels of a tile straight into a K-major shared-memory tile;
+//   padding and stride are resolved by the im2col bounding box and traversal stride.
+// * filter pre-packed K-major [OC][taps][channels], fetched by tiled 2D TMA.
+// * tcgen05.mma kind::i8, M=128 x N=BN x K=32 per instruction, int32 accumulators in TMEM,
+//   two accumulator buffers so the epilogue of one tile overlaps the MMAs of the next.
+// * persistent CTAs walk the tile list; warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM
+//   alloc), warps 2..5 = epilogue (tcgen05.ld -> +bias -> fp32 requantisation in the
+//   reference's operation order -> activation -> int8 -> 16-byte stores).
 // * every wait is bounded: when it runs out the kernel records a code in the device status
 //   word, drains what it started, frees its TMEM and returns.
 //
+// Two operand geometries:
+//   WIDE  one tap x 64 channels per pipeline stage, 64-byte swizzle (input channels % 64 == 0)
+//   TAP16 four taps x 16 channels per stage, no swizzle: the form a stride-2 convolution with
+//         at most 4 input channels takes after a 2x2 space-to-depth step (see conv_s2d.cu)
+//
 // Replaces the loop nest of compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:305-344 and
-// its epilogue (:374-382, BareMetal/Activation.cpp:105-113) for dense convolutions whose
-// input channel count is a multiple of 64.
+// its epilogue (:374-382, BareMetal/Activation.cpp:105-113).
 #include <cuda.h>
 
 #include "internal.h"
@@ -24,11 +29,12 @@ namespace mb200 {
 
 namespace {
 
-constexpr int kBM = 128;         // output pixels per tile (UMMA M)
-constexpr int kBK = 64;          // K bytes per pipeline stage = channels per TMA row
-constexpr int kUmmaK = 32;       // K per tcgen05.mma kind::i8
+constexpr int kBM = 128;     // output pixels per tile (UMMA M)
+constexpr int kBK = 64;      // K bytes per pipeline stage
+constexpr int kUmmaK = 32;   // K per tcgen05.mma kind::i8
 constexpr int kStages = 6;
 constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
 constexpr long long kWaitCycles = 1LL << 31;  // ~1 s: only a lost barrier gets there
 
 enum : int {
@@ -36,6 +42,7 @@ enum : int {
     ERR_MMA_WAIT = 0x102,
     ERR_EPILOGUE_WAIT = 0x103,
     ERR_DRAIN_WAIT = 0x104,
+    ERR_MMA_ACC_WAIT = 0x105,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -50,6 +57,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                  "r"(bytes)
                  : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
@@ -102,14 +113,18 @@ __device__ __forceinline__ void tma_load_im2col_4d(
             : "memory");
 }
 
-// K-major operand tile with 64-byte swizzle: rows of 64 bytes, 8-row groups 512 bytes apart.
-__device__ __forceinline__ uint64_t umma_smem_desc_sw64(uint32_t saddr) {
+// Shared-memory matrix descriptor of a K-major operand tile.
+//   swizzled (64 B): rows of 64 bytes, 8-row groups `sbo` bytes apart, `lbo` unused
+//   plain:           8x16-byte core matrices; `lbo` = distance between the two 16-byte K
+//                    halves of one MMA, `sbo` = distance between 8-row groups
+__device__ __forceinline__ uint64_t umma_smem_desc(
+        uint32_t saddr, uint32_t lbo, uint32_t sbo, uint32_t layout_type) {
     uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);  // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                    // leading byte offset: unused with swizzle
-    d |= (uint64_t)(512 >> 4) << 32;           // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                    // descriptor version of sm_100
-    d |= (uint64_t)4 << 61;                    // layout type SWIZZLE_64B
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version of sm_100
+    d |= (uint64_t)layout_type << 61;
     return d;
 }
 
@@ -153,12 +168,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+enum Geometry : int { GEOM_WIDE = 0, GEOM_TAP16 = 1 };
+
 struct UmmaConvParams {
-    int m_total, oc, oh, ow, ic;
-    int kh, kw, sh, sw, ph, pw, dh, dw;
-    int n_tiles;
+    int m_total, oc, oh, ow;
+    int cblocks;        // WIDE: 64-channel blocks per tap
+    int taps_w;         // filter taps along W (TAP16: taps of the space-to-depth filter)
+    int k_iters;        // pipeline stages per tile
+    int sh, sw;         // output -> base pixel scaling
+    int base_h, base_w; // coordinate of output (0,0)'s first tap (= -pad)
+    int dh, dw;
+    int m_tiles, n_tiles;
     int act;
-    float s_src, s_flt, s_dst;
+    float s_src, s_flt, s_dst, inv_dst;
     const int32_t* bias;
     const float* flt_scales;
     int8_t* dst;
@@ -170,15 +192,61 @@ struct SmemLayout {
     static constexpr int kABytes = kBM * kBK;
     static constexpr int kBBytes = BN * kBK;
     static constexpr int kTiles = kStages * (kABytes + kBBytes);
-    // after the tiles: full[kStages], empty[kStages], accum, drain barriers, bias, scales
+    // after the tiles: full[kStages], empty[kStages], acc_full[2], acc_empty[2], drain
     static constexpr int kBarOff = kTiles;
-    static constexpr int kBiasOff = kBarOff + (2 * kStages + 2) * 8 + 16;
-    static constexpr int kScaleOff = kBiasOff + BN * 4;
-    static constexpr int kTotal = kScaleOff + BN * 4;
+    static constexpr int kTotal = kBarOff + (2 * kStages + 5) * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;  // room to align the tiles to 1024 bytes
 };
 
-template <int BN>
+__device__ __forceinline__ uint32_t pack4_prmt(int a, int b, int c, int d) {
+    const uint32_t ab = __byte_perm((uint32_t)a, (uint32_t)b, 0x0040);
+    const uint32_t cd = __byte_perm((uint32_t)c, (uint32_t)d, 0x0040);
+    return __byte_perm(ab, cd, 0x5410);
+}
+
+// 32 accumulators of one output pixel -> 32 int8, stored as two 16-byte vectors
+template <int ACT, bool PER_CHANNEL>
+__device__ __forceinline__ void epilogue_chunk(
+        const uint32_t (&v)[32], const UmmaConvParams& p, int m, int ch0) {
+    int8_t* out = p.dst + (size_t)m * p.oc + ch0;
+    const bool full = ch0 + 32 <= p.oc;
+    if (full && (p.oc % 16) == 0) {
+        uint32_t packed[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int4 b = make_int4(0, 0, 0, 0);
+            if (p.bias)
+                b = __ldg(reinterpret_cast<const int4*>(p.bias + ch0) + j);
+            float4 s = make_float4(p.s_flt, p.s_flt, p.s_flt, p.s_flt);
+            if (PER_CHANNEL)
+                s = __ldg(reinterpret_cast<const float4*>(p.flt_scales + ch0) + j);
+            const int r0 = requant_conv_fast((int)v[j * 4 + 0] + b.x, p.s_src, s.x, p.s_dst,
+                                             p.inv_dst, ACT);
+            const int r1 = requant_conv_fast((int)v[j * 4 + 1] + b.y, p.s_src, s.y, p.s_dst,
+                                             p.inv_dst, ACT);
+            const int r2 = requant_conv_fast((int)v[j * 4 + 2] + b.z, p.s_src, s.z, p.s_dst,
+                                             p.inv_dst, ACT);
+            const int r3 = requant_conv_fast((int)v[j * 4 + 3] + b.w, p.s_src, s.w, p.s_dst,
+                                             p.inv_dst, ACT);
+            packed[j] = pack4_prmt(r0, r1, r2, r3);
+        }
+        reinterpret_cast<uint4*>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        reinterpret_cast<uint4*>(out)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    } else {
+        // ragged channel tail (or a channel count that rules out vector stores)
+        // (fully unrolled with a predicate so the accumulators stay in registers)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (ch0 + i < p.oc) {
+                const int acc = (int)v[i] + (p.bias ? p.bias[ch0 + i] : 0);
+                const float s = PER_CHANNEL ? p.flt_scales[ch0 + i] : p.s_flt;
+                out[i] = (int8_t)requant_conv_fast(acc, p.s_src, s, p.s_dst, p.inv_dst, ACT);
+            }
+        }
+    }
+}
+
+template <int BN, int GEOM>
 __global__ void __launch_bounds__(kThreads) conv_umma_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const UmmaConvParams p) {
@@ -189,25 +257,24 @@ __global__ void __launch_bounds__(kThreads) conv_umma_kernel(
     uint8_t* tiles_b = smem + kStages * L::kABytes;
     uint64_t* full_bar = (uint64_t*)(smem + L::kBarOff);
     uint64_t* empty_bar = full_bar + kStages;
-    uint64_t* accum_bar = empty_bar + kStages;
-    uint64_t* drain_bar = accum_bar + 1;
+    uint64_t* acc_full = empty_bar + kStages;  // [2]
+    uint64_t* acc_empty = acc_full + 2;        // [2]
+    uint64_t* drain_bar = acc_empty + 2;
     uint32_t* tmem_slot = (uint32_t*)(drain_bar + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    int32_t* s_bias = (int32_t*)(smem + L::kBiasOff);
-    float* s_scale = (float*)(smem + L::kScaleOff);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_n = blockIdx.x % p.n_tiles, tile_m = blockIdx.x / p.n_tiles;
-    const int m0 = tile_m * kBM, n0 = tile_n * BN;
-    const int cblocks = p.ic / kBK;
-    const int k_iters = p.kh * p.kw * cblocks;
+    const int total_tiles = p.m_tiles * p.n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], kEpilogueThreads);
+        }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -216,15 +283,9 @@ __global__ void __launch_bounds__(kThreads) conv_umma_kernel(
         asm volatile(
                 "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                         smem_u32(tmem_slot)),
-                "r"(BN)
+                "r"(2 * BN)
                 : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    // bias / per-channel scales of this tile's channels
-    for (int i = threadIdx.x; i < BN; i += kThreads) {
-        const int ch = n0 + i;
-        s_bias[i] = (p.bias && ch < p.oc) ? p.bias[ch] : 0;
-        s_scale[i] = (p.flt_scales && ch < p.oc) ? p.flt_scales[ch] : p.s_flt;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -234,100 +295,142 @@ __global__ void __launch_bounds__(kThreads) conv_umma_kernel(
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            const int img = m0 / (p.oh * p.ow);
-            const int rem = m0 - img * (p.oh * p.ow);
-            const int oy = rem / p.ow, ox = rem - oy * p.ow;
-            const int base_w = ox * p.sw - p.pw, base_h = oy * p.sh - p.ph;
-            for (int it = 0; it < k_iters; ++it) {
-                const int s = it % kStages;
-                const uint32_t phase = (uint32_t)(it / kStages) & 1u;
-                if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) {
-                    if (!*abort_flag) {
-                        *abort_flag = 1;
-                        atomicExch(p.status, ERR_PRODUCER_WAIT);
+            int it_global = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int tile_n = tile % p.n_tiles, tile_m = tile / p.n_tiles;
+                const int m0 = tile_m * kBM, n0 = tile_n * BN;
+                const int img = m0 / (p.oh * p.ow);
+                const int rem = m0 - img * (p.oh * p.ow);
+                const int oy = rem / p.ow, ox = rem - oy * p.ow;
+                const int base_w = ox * p.sw + p.base_w, base_h = oy * p.sh + p.base_h;
+                for (int it = 0; it < p.k_iters; ++it, ++it_global) {
+                    const int s = it_global % kStages;
+                    const uint32_t phase = (uint32_t)(it_global / kStages) & 1u;
+                    if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) {
+                        if (!*abort_flag) {
+                            *abort_flag = 1;
+                            atomicExch(p.status, ERR_PRODUCER_WAIT);
+                        }
+                        ok = false;
+                        break;
                     }
-                    break;
+                    mbar_expect_tx(&full_bar[s], (uint32_t)(L::kABytes + L::kBBytes));
+                    uint8_t* sa = tiles_a + s * L::kABytes;
+                    uint8_t* sb = tiles_b + s * L::kBBytes;
+                    if (GEOM == GEOM_WIDE) {
+                        const int tap = it / p.cblocks, cb = it - tap * p.cblocks;
+                        const int fy = tap / p.taps_w, fx = tap - fy * p.taps_w;
+                        tma_load_im2col_4d(sa, &map_a, &full_bar[s], cb * kBK, base_w, base_h, img,
+                                           (uint16_t)(fx * p.dw), (uint16_t)(fy * p.dh));
+                        tma_load_2d(sb, &map_b, &full_bar[s], it * kBK, n0);
+                    } else {
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            const int tap = it * 4 + t;
+                            const int fy = tap / p.taps_w, fx = tap - fy * p.taps_w;
+                            tma_load_im2col_4d(sa + t * (kBM * 16), &map_a, &full_bar[s], 0, base_w,
+                                               base_h, img, (uint16_t)fx, (uint16_t)fy);
+                            tma_load_2d(sb + t * (BN * 16), &map_b, &full_bar[s], tap * 16, n0);
+                        }
+                    }
                 }
-                const int tap = it / cblocks, cb = it - tap * cblocks;
-                const int fy = tap / p.kw, fx = tap - fy * p.kw;
-                mbar_expect_tx(&full_bar[s], (uint32_t)(L::kABytes + L::kBBytes));
-                tma_load_im2col_4d(
-                        tiles_a + s * L::kABytes, &map_a, &full_bar[s], cb * kBK, base_w, base_h,
-                        img, (uint16_t)(fx * p.dw), (uint16_t)(fy * p.dh));
-                tma_load_2d(tiles_b + s * L::kBBytes, &map_b, &full_bar[s], it * kBK, n0);
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_s8(kBM, BN);
+            int it_global = 0, local = 0;
             bool ok = true;
-            for (int it = 0; it < k_iters && ok; ++it) {
-                const int s = it % kStages;
-                const uint32_t phase = (uint32_t)(it / kStages) & 1u;
-                if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                // the epilogue must have drained this accumulator buffer
+                if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
                     if (!*abort_flag) {
                         *abort_flag = 1;
-                        atomicExch(p.status, ERR_MMA_WAIT);
+                        atomicExch(p.status, ERR_MMA_ACC_WAIT);
                     }
                     ok = false;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t adesc = umma_smem_desc_sw64(smem_u32(tiles_a + s * L::kABytes));
-                const uint64_t bdesc = umma_smem_desc_sw64(smem_u32(tiles_b + s * L::kBBytes));
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                for (int it = 0; it < p.k_iters; ++it, ++it_global) {
+                    const int s = it_global % kStages;
+                    const uint32_t phase = (uint32_t)(it_global / kStages) & 1u;
+                    if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
+                        if (!*abort_flag) {
+                            *abort_flag = 1;
+                            atomicExch(p.status, ERR_MMA_WAIT);
+                        }
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(tiles_a + s * L::kABytes);
+                    const uint32_t b_addr = smem_u32(tiles_b + s * L::kBBytes);
 #pragma unroll
-                for (int k = 0; k < kBK / kUmmaK; ++k) {
-                    // +32 bytes along K inside the swizzle row = +2 in the address field
-                    umma_s8(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
-                            idesc, (it | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        uint64_t adesc, bdesc;
+                        if (GEOM == GEOM_WIDE) {
+                            // 64-byte swizzle; +32 bytes along K inside the swizzled row
+                            adesc = umma_smem_desc(a_addr + k * 32, 16, 512, 4);
+                            bdesc = umma_smem_desc(b_addr + k * 32, 16, 512, 4);
+                        } else {
+                            // two 16-byte taps form one K=32 step
+                            adesc = umma_smem_desc(a_addr + k * 2 * (kBM * 16), kBM * 16, 128, 0);
+                            bdesc = umma_smem_desc(b_addr + k * 2 * (BN * 16), BN * 16, 128, 0);
+                        }
+                        umma_s8(tmem_d, adesc, bdesc, idesc, (it | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[s]);  // frees the stage once these MMAs retire
                 }
-                umma_commit(&empty_bar[s]);  // frees the stage once these MMAs retire
+                if (ok)
+                    umma_commit(&acc_full[buf]);
             }
-            if (ok)
-                umma_commit(accum_bar);
         }
     } else {
         // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp%4).. ----------------
         const int q = warp & 3;
         const int row = q * 32 + lane;
-        const int m = m0 + row;
-        bool ok = mbar_wait(accum_bar, 0, abort_flag);
-        if (!ok && !*abort_flag) {
-            *abort_flag = 1;
-            atomicExch(p.status, ERR_EPILOGUE_WAIT);
-        }
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
+        int local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            const int tile_n = tile % p.n_tiles, tile_m = tile / p.n_tiles;
+            const int m = tile_m * kBM + row, n0 = tile_n * BN;
+            ok = mbar_wait(&acc_full[buf], acc_phase, abort_flag);
+            if (!ok && !*abort_flag) {
+                *abort_flag = 1;
+                atomicExch(p.status, ERR_EPILOGUE_WAIT);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const bool vec_ok = (p.oc % 16) == 0;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+                tmem_ld32(taddr + (uint32_t)(c * 32), v);
+                if (c == BN / 32 - 1) {
+                    // all of this thread's accumulators are in registers: hand the buffer back
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbar_arrive(&acc_empty[buf]);
+                }
                 const int ch0 = n0 + c * 32;
                 if (m < p.m_total && ch0 < p.oc) {
-                    uint32_t packed[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        int r[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int i = c * 32 + j * 4 + e;
-                            const int acc = (int)v[j * 4 + e] + s_bias[i];
-                            r[e] = requant_conv(acc, p.s_src, s_scale[i], p.s_dst, p.act);
-                        }
-                        packed[j] = pack4(r[0], r[1], r[2], r[3]);
-                    }
-                    int8_t* out = p.dst + (size_t)m * p.oc + ch0;
-                    if (vec_ok && ch0 + 32 <= p.oc) {
-                        reinterpret_cast<uint4*>(out)[0] =
-                                make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        reinterpret_cast<uint4*>(out)[1] =
-                                make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    } else {
-                        for (int i = 0; i < 32 && ch0 + i < p.oc; ++i)
-                            out[i] = (int8_t)(packed[i >> 2] >> (8 * (i & 3)));
+                    const bool pc = p.flt_scales != nullptr;
+                    switch (p.act * 2 + (pc ? 1 : 0)) {
+                        case 0: epilogue_chunk<ACT_IDENTITY, false>(v, p, m, ch0); break;
+                        case 1: epilogue_chunk<ACT_IDENTITY, true>(v, p, m, ch0); break;
+                        case 2: epilogue_chunk<ACT_RELU, false>(v, p, m, ch0); break;
+                        case 3: epilogue_chunk<ACT_RELU, true>(v, p, m, ch0); break;
+                        case 4: epilogue_chunk<ACT_H_SWISH, false>(v, p, m, ch0); break;
+                        default: epilogue_chunk<ACT_H_SWISH, true>(v, p, m, ch0); break;
                     }
                 }
             }
@@ -356,7 +459,7 @@ __global__ void __launch_bounds__(kThreads) conv_umma_kernel(
     }
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                     "r"(BN)
+                     "r"(2 * BN)
                      : "memory");
     }
 }
@@ -400,23 +503,39 @@ const DriverApi& driver_api() {
     return api;
 }
 
-int pick_bn(int oc) {
-    return oc <= 64 ? 64 : 128;
+int sm_count() {
+    static int sms[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64)
+        return 148;
+    if (!sms[dev]) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+            v = 148;
+        sms[dev] = v;
+    }
+    return sms[dev];
 }
 
-template <int BN>
-int launch_bn(
-        const CUtensorMap& ma, const CUtensorMap& mb, const UmmaConvParams& p, int grid,
-        cudaStream_t st) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(
-                    conv_umma_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                    SmemLayout<BN>::kDynamic) != cudaSuccess)
-            return check_launch("conv_umma smem attribute");
-        attr_set = true;
-    }
-    conv_umma_kernel<BN><<<grid, kThreads, SmemLayout<BN>::kDynamic, st>>>(ma, mb, p);
+template <int BN, int GEOM>
+int launch_kernel(
+        const CUtensorMap& ma, const CUtensorMap& mb, const UmmaConvParams& p, cudaStream_t st) {
+    if (cudaFuncSetAttribute(
+                conv_umma_kernel<BN, GEOM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                SmemLayout<BN>::kDynamic) != cudaSuccess)
+        return check_launch("conv_umma smem attribute");
+    // persistent CTAs: as many as fit per SM (shared memory and 2*BN TMEM columns each)
+    const int per_sm_smem = (227 * 1024) / (SmemLayout<BN>::kDynamic + 1024);
+    const int per_sm_tmem = 512 / (2 * BN);
+    int per_sm = per_sm_smem < per_sm_tmem ? per_sm_smem : per_sm_tmem;
+    if (per_sm < 1)
+        per_sm = 1;
+    const int total = p.m_tiles * p.n_tiles;
+    int grid = sm_count() * per_sm;
+    if (grid > total)
+        grid = total;
+    conv_umma_kernel<BN, GEOM><<<grid, kThreads, SmemLayout<BN>::kDynamic, st>>>(ma, mb, p);
     return check_launch("conv_umma");
 }
 
@@ -426,7 +545,7 @@ bool conv_umma_supported(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst) {
     if (a.groups != 1 || a.src_is_nchw)
         return false;
-    if (a.ic % kBK != 0 || a.oc % 8 != 0)
+    if (a.ic % kBK != 0)
         return false;
     if (a.kh * a.kw > 49 || a.dh != 1 || a.dw != 1)
         return false;
@@ -442,40 +561,53 @@ bool conv_umma_supported(
     return true;
 }
 
-int launch_conv_umma(
-        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
+// geom: 0 = WIDE (src NHWC with ic % 64 == 0, filter [OC][KH][KW][IC]);
+//       1 = TAP16 (src NHWC with exactly 16 channels, stride 1, filter [OC][taps][16] with the
+//           tap count a multiple of 4; `a` then describes that transformed convolution, with
+//           a.ph/a.pw the LOW padding and a.oh/a.ow the output extent)
+int launch_conv_umma_geom(
+        const ConvArgs& a, int geom, const int8_t* src, const int8_t* flt, const int32_t* bias,
         const float* flt_scales, int8_t* dst, cudaStream_t st) {
     const DriverApi& api = driver_api();
     if (!api.ok)
         return set_error(ST_RUNTIME, "cuTensorMapEncode* entry points not found in the driver");
-    const int bn = pick_bn(a.oc);
+    const int bn = a.oc <= 64 ? 64 : 128;
+    const int taps = a.kh * a.kw;
+    if (geom == GEOM_TAP16 && (a.ic != 16 || taps % 4 != 0 || a.sh != 1 || a.sw != 1))
+        return set_error(ST_INVALID_LAYOUT, "TAP16 geometry needs 16 channels and 4k taps");
+    if (((uintptr_t)bias & 15) || ((uintptr_t)flt_scales & 15))
+        return set_error(ST_INVALID_LAYOUT, "bias and channel scales must be 16-byte aligned");
 
+    const int chans = geom == GEOM_WIDE ? kBK : 16;
+    const CUtensorMapSwizzle swz =
+            geom == GEOM_WIDE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE;
     CUtensorMap map_a, map_b;
     {
         cuuint64_t dims[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw, (cuuint64_t)a.ih,
                               (cuuint64_t)a.n};
         cuuint64_t strides[3] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw * a.ic,
                                  (cuuint64_t)a.ih * a.iw * a.ic};
+        // bounding box of the first-tap positions: from -pad to the last output's position
         int lower[2] = {-a.pw, -a.ph};
-        int upper[2] = {a.pw - (a.kw - 1) * a.dw, a.ph - (a.kh - 1) * a.dh};
+        int upper[2] = {(a.ow - 1) * a.sw - a.pw - (a.iw - 1), (a.oh - 1) * a.sh - a.ph - (a.ih - 1)};
         cuuint32_t estr[4] = {1, (cuuint32_t)a.sw, (cuuint32_t)a.sh, 1};
         CUresult r = api.im2col(
                 &map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)src, dims, strides, lower, upper,
-                kBK, kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                chans, kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS)
             return set_error(ST_RUNTIME, "cuTensorMapEncodeIm2col failed: %d", (int)r);
     }
     {
-        const cuuint64_t k_total = (cuuint64_t)a.kh * a.kw * a.ic;
+        const cuuint64_t k_total = (cuuint64_t)taps * a.ic;
         cuuint64_t dims[2] = {k_total, (cuuint64_t)a.oc};
         cuuint64_t strides[1] = {k_total};
-        cuuint32_t box[2] = {kBK, (cuuint32_t)bn};
+        cuuint32_t box[2] = {(cuuint32_t)chans, (cuuint32_t)bn};
         cuuint32_t estr[2] = {1, 1};
         CUresult r = api.tiled(
                 &map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)flt, dims, strides, box, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
-                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS)
             return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled failed: %d", (int)r);
     }
@@ -485,30 +617,39 @@ int launch_conv_umma(
     p.oc = a.oc;
     p.oh = a.oh;
     p.ow = a.ow;
-    p.ic = a.ic;
-    p.kh = a.kh;
-    p.kw = a.kw;
+    p.cblocks = geom == GEOM_WIDE ? a.ic / kBK : 1;
+    p.taps_w = a.kw;
+    p.k_iters = geom == GEOM_WIDE ? taps * p.cblocks : taps / 4;
     p.sh = a.sh;
     p.sw = a.sw;
-    p.ph = a.ph;
-    p.pw = a.pw;
+    p.base_h = -a.ph;
+    p.base_w = -a.pw;
     p.dh = a.dh;
     p.dw = a.dw;
+    p.m_tiles = (a.m + kBM - 1) / kBM;
     p.n_tiles = (a.oc + bn - 1) / bn;
     p.act = a.act;
     p.s_src = a.s_src;
     p.s_flt = a.s_flt;
     p.s_dst = a.s_dst;
+    p.inv_dst = 1.0f / a.s_dst;  // correctly rounded on the host
     p.bias = bias;
     p.flt_scales = flt_scales;
     p.dst = dst;
     p.status = device_status_word();
     if (!p.status)
         return ST_MALLOC;
-    const int m_tiles = (a.m + kBM - 1) / kBM;
-    const int grid = m_tiles * p.n_tiles;
-    return bn == 64 ? launch_bn<64>(map_a, map_b, p, grid, st)
-                    : launch_bn<128>(map_a, map_b, p, grid, st);
+    if (geom == GEOM_WIDE)
+        return bn == 64 ? launch_kernel<64, GEOM_WIDE>(map_a, map_b, p, st)
+                        : launch_kernel<128, GEOM_WIDE>(map_a, map_b, p, st);
+    return bn == 64 ? launch_kernel<64, GEOM_TAP16>(map_a, map_b, p, st)
+                    : launch_kernel<128, GEOM_TAP16>(map_a, map_b, p, st);
+}
+
+int launch_conv_umma(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
+        const float* flt_scales, int8_t* dst, cudaStream_t st) {
+    return launch_conv_umma_geom(a, GEOM_WIDE, src, flt, bias, flt_scales, dst, st);
 }
 
 }  // namespace mb200

@@ -50,6 +50,15 @@ bool conv_umma_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt
 int launch_conv_umma(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
         const float* flt_scales, int8_t* dst, cudaStream_t st);
+// stride-2 ConvBias with <= 4 input channels via 2x2 space-to-depth (conv_s2d.cu)
+bool conv_s2d_supported(const ConvArgs& a);
+size_t conv_s2d_filter_bytes(const ConvArgs& a);
+size_t conv_s2d_workspace_bytes(const ConvArgs& a);
+int launch_conv_s2d_pack_filter(
+        const ConvArgs& a, const int8_t* flt_oihw, int8_t* out, cudaStream_t st);
+int launch_conv_s2d(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt_s2d, const int32_t* bias,
+        const float* flt_scales, int8_t* dst, void* workspace, cudaStream_t st);
 int launch_pooling(
         const int8_t* src, int8_t* dst, int mode, int n, int c, int ih, int iw, int wh, int ww,
         int sh, int sw, int ph, int pw, cudaStream_t st);

@@ -73,6 +73,7 @@ struct OpPlan {
     std::vector<int> weight_inputs;  // indices (into inputs) that are weights
     Workspace ws{nullptr, 0, 0};
     bool needs_init = false;
+    bool use_s2d = false;  // first-layer form: space-to-depth + tensor cores
     float ms_total = 0;
     int ms_count = 0;
 };
@@ -280,6 +281,11 @@ int run_op(const OpPlan& op, cudaStream_t st) {
             const int32_t* bias = op.has_bias ? (const int32_t*)op.inputs[2]->ptr : nullptr;
             const float* ch =
                     op.inputs.size() > scale_idx ? (const float*)op.inputs[scale_idx]->ptr : nullptr;
+            if (op.use_s2d)
+                return mb200_conv_bias_qs8_s2d(
+                        &p, (const int8_t*)src->ptr, src->layout.format == TinyNN_NCHW,
+                        (const int8_t*)op.inputs[1]->ptr, bias, ch, (int8_t*)op.outputs[0]->ptr,
+                        op.ws.ptr, op.ws.size, st);
             return mb200_conv_bias_qs8_nhwc(
                     &p, (const int8_t*)src->ptr, src->layout.format == TinyNN_NCHW,
                     (const int8_t*)op.inputs[1]->ptr, bias, ch, (int8_t*)op.outputs[0]->ptr,
@@ -567,13 +573,27 @@ int upload_weights(Network* net) {
                     return fail(TinyNN_ERROR_NO_IMPLEMENT, "conv filter must be a weight");
                 packs.push_back({&ins.op, (int)(f - net->weights.data())});
             }
-    std::vector<int> packed_of(net->weights.size(), -1);
-    for (auto& pk : packs)
-        if (packed_of[pk.second] < 0) {
-            packed_of[pk.second] = (int)net->processed.size();
-            net->processed.push_back(net->weights[pk.second]);
-            total += up(net->weights[pk.second].size);
+    // one processed copy per (filter, packing): the standard K-major packing, or the
+    // space-to-depth packing when the Opr qualifies and the compiler gave it a workspace
+    std::vector<int> packed_of(net->weights.size() * 2, -1);
+    std::vector<int> pack_mode;  // per entry of `packs`
+    for (auto& pk : packs) {
+        mb200_conv_param cp;
+        fill_conv_param(*pk.first, &cp);
+        const bool s2d = mb200_conv_s2d_supported(&cp) &&
+                         pk.first->ws.size >= mb200_conv_s2d_workspace_bytes(&cp);
+        pk.first->use_s2d = s2d;
+        pack_mode.push_back(s2d ? 1 : 0);
+        const size_t key = (size_t)pk.second * 2 + (s2d ? 1 : 0);
+        if (packed_of[key] < 0) {
+            packed_of[key] = (int)net->processed.size();
+            Tensor t = net->weights[pk.second];
+            if (s2d)
+                t.size = mb200_conv_s2d_filter_bytes(&cp);
+            net->processed.push_back(t);
+            total += up(t.size);
         }
+    }
     if (total == 0)
         total = 256;
     if ((e = cudaMalloc(&net->weight_arena, total)) != cudaSuccess)
@@ -595,29 +615,24 @@ int upload_weights(Network* net) {
     // Init: pack each filter once, then point the Oprs at the processed weight
     // (the swap the reference performs in runtime/src/init.c:59-92)
     std::vector<char> done(net->processed.size(), 0);
-    for (auto& pk : packs) {
-        OpPlan* op = pk.first;
-        const int pi = packed_of[pk.second];
-        Tensor* src = &net->weights[pk.second];
+    for (size_t k = 0; k < packs.size(); ++k) {
+        OpPlan* op = packs[k].first;
+        const int wi = packs[k].second;
+        const int pi = packed_of[(size_t)wi * 2 + pack_mode[k]];
+        Tensor* src = &net->weights[wi];
         Tensor* dst = &net->processed[pi];
         if (!done[pi]) {
             const Layout& l = src->layout;
-            const bool grouped = l.nr_dim == 5;
             if (l.nr_dim != 4 && l.nr_dim != 5)
                 return fail(TinyNN_ERROR_INVALID_LAYOUT, "conv filter must have 4 or 5 dims");
             mb200_conv_param p;
-            memset(&p, 0, sizeof(p));
-            p.groups = grouped ? l.dims[0] : 1;
-            p.oc = grouped ? l.dims[0] * l.dims[1] : l.dims[0];
-            p.ic = grouped ? l.dims[0] * l.dims[2] : l.dims[1];
-            p.kh = l.dims[l.nr_dim - 2];
-            p.kw = l.dims[l.nr_dim - 1];
-            p.n = 1;
-            p.ih = p.kh;
-            p.iw = p.kw;
-            p.stride_h = p.stride_w = p.dilate_h = p.dilate_w = 1;
-            p.src_scale = p.flt_scale = p.dst_scale = 1.f;
-            int rc = mb200_conv_pack_filter(&p, (const int8_t*)src->ptr, (int8_t*)dst->ptr, net->stream);
+            fill_conv_param(*op, &p);
+            const int rc =
+                    pack_mode[k]
+                            ? mb200_conv_s2d_pack_filter(&p, (const int8_t*)src->ptr,
+                                                         (int8_t*)dst->ptr, net->stream)
+                            : mb200_conv_pack_filter(&p, (const int8_t*)src->ptr,
+                                                     (int8_t*)dst->ptr, net->stream);
             if (rc)
                 return fail(rc, "packing filter '%s': %s", src->name, mb200_last_error());
             done[pi] = 1;
@@ -881,6 +896,7 @@ int mb200_tinynn_describe(const void* model_mem, size_t size, char* out, size_t 
             s += " out=";
             for (auto* t : ins.op.outputs)
                 s += std::string(t->name) + ",";
+            s += " ws=" + std::to_string(ins.op.ws.offset) + "+" + std::to_string(ins.op.ws.size);
             s += "\n";
         }
         for (auto& io : m.inputs)

@@ -37,6 +37,7 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
     const size_t total = (size_t)a.m * a.oc;
     const int icpg = a.ic / a.groups, ocpg = a.oc / a.groups;
     const bool vec4 = !a.src_is_nchw && (icpg % 4 == 0);
+    const float inv_dst = __fdiv_rn(1.f, a.s_dst);  // RN(1/d), as the fast division needs
     for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const int o = (int)(idx % a.oc);
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
             acc += bias[o];
         if (kRequant) {
             const float sf = flt_scales ? flt_scales[o] : a.s_flt;
-            dst[idx] = (int8_t)requant_conv(acc, a.s_src, sf, a.s_dst, a.act);
+            dst[idx] = (int8_t)requant_conv_fast(acc, a.s_src, sf, a.s_dst, inv_dst, a.act);
         } else {
             acc_out[idx] = acc;
         }
@@ -128,6 +129,39 @@ __global__ void __launch_bounds__(256) pooling_kernel(
             r = f32_to_i32_x86(roundf(__fdiv_rn(__int2float_rn(sum), d)));
         }
         dst[idx] = (int8_t)r;
+    }
+}
+
+// MAX pooling, 16 channels (one 16-byte vector) per thread; per-byte signed max in SIMD
+__global__ void __launch_bounds__(256) pooling_max_vec16_kernel(
+        const uint4* __restrict__ src, uint4* __restrict__ dst, int n, int c16, int ih, int iw,
+        int oh, int ow, int wh, int ww, int sh, int sw, int ph, int pw) {
+    const size_t total = (size_t)n * oh * ow * c16;
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int cv = (int)(idx % c16);
+        size_t t = idx / c16;
+        const int x = (int)(t % ow);
+        t /= ow;
+        const int y = (int)(t % oh);
+        const int b = (int)(t / oh);
+        uint4 m = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // -128
+        for (int fy = 0; fy < wh; ++fy) {
+            const int iy = y * sh + fy - ph;
+            if ((unsigned)iy >= (unsigned)ih)
+                continue;
+            for (int fx = 0; fx < ww; ++fx) {
+                const int ix = x * sw + fx - pw;
+                if ((unsigned)ix >= (unsigned)iw)
+                    continue;
+                const uint4 v = __ldg(src + (((size_t)b * ih + iy) * iw + ix) * c16 + cv);
+                m.x = __vmaxs4(m.x, v.x);
+                m.y = __vmaxs4(m.y, v.y);
+                m.z = __vmaxs4(m.z, v.z);
+                m.w = __vmaxs4(m.w, v.w);
+            }
+        }
+        dst[idx] = m;
     }
 }
 
@@ -256,6 +290,11 @@ int launch_pooling(
         int sh, int sw, int ph, int pw, cudaStream_t st) {
     const int oh = (ih + 2 * ph - wh) / sh + 1, ow = (iw + 2 * pw - ww) / sw + 1;
     const size_t total = (size_t)n * oh * ow * c;
+    if (mode == 0 && c % 16 == 0 && ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0)) {
+        pooling_max_vec16_kernel<<<grid_for(total / 16, 256), 256, 0, st>>>(
+                (const uint4*)src, (uint4*)dst, n, c / 16, ih, iw, oh, ow, wh, ww, sh, sw, ph, pw);
+        return check_launch("pooling_max_vec16");
+    }
     pooling_kernel<<<grid_for(total, 256), 256, 0, st>>>(
             src, dst, mode, n, c, ih, iw, oh, ow, wh, ww, sh, sw, ph, pw);
     return check_launch("pooling");

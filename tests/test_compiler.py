@@ -56,10 +56,14 @@ def _parse_plan(text, model=0):
         m = re.match(r"tensor (\S+) offset=(\d+) bytes=(\d+)", line)
         if m:
             tensors[m.group(1)] = (int(m.group(2)), int(m.group(3)))
-        m = re.match(r"opr (\S+) in=(\S*) out=(\S*)", line)
+        m = re.match(r"opr (\S+) in=(\S*) out=(\S*) ws=(\d+)\+(\d+)", line)
         if m:
+            k = len(oprs)
             oprs.append((m.group(1), [x for x in m.group(2).split(",") if x],
                          [x for x in m.group(3).split(",") if x]))
+            if int(m.group(5)):  # a workspace is a buffer that lives for this instruction only
+                tensors[f"ws:{k}"] = (int(m.group(4)), int(m.group(5)))
+                oprs[-1][1].append(f"ws:{k}")
     return tensors, oprs
 
 
@@ -77,6 +81,7 @@ def test_memory_plan_never_overlaps_live_tensors(net):
         for k, (_, ins, outs) in enumerate(oprs):
             for t in ins:
                 if t in tensors:
+                    first.setdefault(t, k)
                     last[t] = k
             for t in outs:
                 first.setdefault(t, k)
@@ -91,6 +96,9 @@ def test_memory_plan_never_overlaps_live_tensors(net):
                 assert oa + sa <= ob or ob + sb <= oa, f"{a} and {b} overlap while both live"
         arena = g.arena_bytes(mi)
         assert all(o % 256 == 0 and o + s <= arena for o, s in tensors.values())
+        # the first layer (stride 2, 3 input channels) gets scratch for its space-to-depth
+        # tensor: N x 112 x 112 x 16 bytes
+        assert tensors["ws:0"][1] == batch * 112 * 112 * 16
         assert arena < 0.5 * g.unplanned_bytes(mi), "the plan should reuse memory"
 
 

@@ -96,6 +96,39 @@ def test_conv_umma_matches_oracle(ops, oracle, case):
     assert (np.abs(want.astype(int)) < 127).mean() > 0.3
 
 
+S2D_CASES = [
+    # name, n, ic, oc, h, w, k, pad, act  (all stride 2)
+    ("r18_stem", 2, 3, 64, 224, 224, 7, 3, "RELU"),
+    ("mbv1_stem", 2, 3, 32, 224, 224, 3, 1, "RELU"),
+    ("odd_hw", 3, 3, 64, 225, 223, 7, 3, "IDENTITY"),
+    ("ic1_k5", 4, 1, 40, 120, 120, 5, 2, "RELU"),
+    ("ic4_k3_nopad", 4, 4, 136, 96, 100, 3, 0, "H_SWISH"),
+    ("ic2_k2", 4, 2, 64, 128, 128, 2, 0, "RELU"),
+    ("k1", 8, 3, 64, 128, 128, 1, 0, "RELU"),
+]
+
+
+@pytest.mark.parametrize("case", S2D_CASES, ids=[c[0] for c in S2D_CASES])
+def test_conv_first_layer_space_to_depth_matches_oracle(ops, oracle, case):
+    import ctypes
+    from megcc_b200._lib import lib
+    name, n, ic, oc, h, w, k, pad, act = case
+    c = dict(name="s2d_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=2, pad=pad, groups=1,
+             act=act, range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.05 * (ic * k * k) ** 0.5 + 0.05))
+    s0, s1, s2 = c["scales"]
+    p = ops.conv_param(n, ic, h, w, oc, k, k, 2, pad, 1, act, s0, s1, s2)
+    assert lib().mb200_conv_s2d_supported(ctypes.byref(p)) == 1
+    out, (src, flt, bias) = run_conv_nchw(ops, c)  # auto: takes the space-to-depth path
+    want = oracle.conv_bias_qs8(src, flt, bias, 2, pad, s0, s1, s2, act)
+    bad = int((out != want).sum())
+    assert bad == 0, f"{bad}/{want.size} differ; first at {np.argwhere(out != want)[:4].tolist()}"
+    assert ops.device_status() == 0
+    assert (np.abs(want.astype(int)) < 127).mean() > 0.3
+    direct, _ = run_conv_nchw(ops, c, algo="direct")
+    assert (direct == want).all()
+
+
 def test_conv_umma_per_channel_scales(ops, oracle):
     c = dict(name="umma_perchannel", n=2, ic=64, oc=128, h=32, w=32, k=3, stride=1, pad=1,
              groups=1, act="RELU", range=(-128, 127), bias_range=(-1000, 1000),
