@@ -1,0 +1,64 @@
+"""Launches three representative qint8 ConvBias kernels twice each (first layer 3->64 7x7/2,
+64->64 3x3 at 56x56, 256->256 3x3 at 14x14) on a small batch and prints their times.
+
+Meant to be run under a profiler, capturing the second round:
+
+    ncu --set full --clock-control none -k regex:conv_umma -s 3 -c 3 \
+        python -m megcc_b200.profile_conv 32
+"""
+import ctypes
+import sys
+
+import numpy as np
+import torch
+
+from . import ops
+from ._lib import check, lib
+
+
+def main(batch=32):
+    rng = np.random.default_rng(0)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    cases = []
+
+    p = ops.conv_param(batch, 3, 224, 224, 64, 7, 7, 2, 3, 1, "RELU", 0.02, 0.01, 0.5)
+    src = dev(rng.integers(-128, 128, (batch, 3, 224, 224), dtype=np.int8))
+    flt = dev(rng.integers(-127, 128, (64, 3, 7, 7), dtype=np.int8))
+    bias = dev(rng.integers(-1000, 1000, (64,), dtype=np.int32))
+    packed = torch.empty(lib().mb200_conv_s2d_filter_bytes(ctypes.byref(p)), dtype=torch.int8,
+                         device="cuda")
+    check(lib().mb200_conv_s2d_pack_filter(ctypes.byref(p), ptr(flt), ptr(packed), st))
+    ws = torch.empty(lib().mb200_conv_s2d_workspace_bytes(ctypes.byref(p)), dtype=torch.int8,
+                     device="cuda")
+    dst = torch.empty((batch, 112, 112, 64), dtype=torch.int8, device="cuda")
+
+    def first_layer():
+        check(lib().mb200_conv_bias_qs8_s2d(ctypes.byref(p), ptr(src), 1, ptr(packed), ptr(bias),
+                                            None, ptr(dst), ptr(ws), ws.numel(), st))
+
+    cases.append(("first_layer_3_64_7x7s2", first_layer, 2.0 * batch * 64 * 112 * 112 * 147))
+    for name, c, hw in (("conv_64_64_3x3_56", 64, 56), ("conv_256_256_3x3_14", 256, 14)):
+        pp = ops.conv_param(batch, c, hw, hw, c, 3, 3, 1, 1, 1, "RELU", 0.05, 0.01, 2.0)
+        s = dev(rng.integers(-128, 128, (batch, hw, hw, c), dtype=np.int8))
+        f = ops.pack_filter(pp, dev(rng.integers(-127, 128, (c, c, 3, 3), dtype=np.int8)))
+        b = dev(rng.integers(-1000, 1000, (c,), dtype=np.int32))
+        d = torch.empty((batch, hw, hw, c), dtype=torch.int8, device="cuda")
+        cases.append((name, (lambda pp=pp, s=s, f=f, b=b, d=d: ops.conv_bias_qs8_nhwc(
+            pp, s, f, b, dst=d, algo="umma")), 2.0 * batch * c * hw * hw * c * 9))
+    for rnd in range(2):
+        for name, fn, work in cases:
+            e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if rnd:
+                ms = e0.elapsed_time(e1)
+                print(f"{name}: {ms * 1e3:.1f} us incl. launch, {work / ms / 1e9:.0f} TOP/s")
+    print("device status", ops.device_status())
+
+
+if __name__ == "__main__":
+    main(int(sys.argv[1]) if len(sys.argv) > 1 else 32)
