@@ -26,6 +26,21 @@ def test_ops_library_exports_header_symbols():
     assert b"sm_100a" in _lib.lib().mb200_version()
 
 
+def test_lite_and_compiler_libraries_export_header_symbols():
+    from megcc_b200 import _lib, compiler, lite
+    L = ctypes.CDLL(_lib.LIB_PATH)
+    names = declared("megcc_b200_lite.h", "LITE_API")
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in include/megcc_b200_lite.h but not exported"
+    assert sorted(lite.SIGNATURES) == names
+    Lc = ctypes.CDLL(compiler.LIB_PATH)
+    cnames = declared("megcc_b200_compiler.h", "MB200C_API")
+    for n in cnames:
+        assert hasattr(Lc, n), f"{n} declared in include/megcc_b200_compiler.h but not exported"
+    assert sorted(compiler.SIGNATURES) == cnames
+
+
 def test_missing_library_fails_loudly(monkeypatch):
     from megcc_b200 import _lib
     monkeypatch.setattr(_lib, "_lib", None)

@@ -172,3 +172,29 @@ def test_exported_stubs_compile_against_public_headers(tmp_path):
     L.load_kernel_init_function()
     tab = (C.c_void_p * len(syms)).in_dll(L, "kernels")
     assert all(tab[i] for i in range(len(syms)))
+
+
+def test_compile_side_builds_inside_the_reference_kernelgen(tmp_path):
+    """The CUDA kernel pack and graph compiler, compiled against the reference's own
+    KernelGen.h / TContext.h and linked with its registry (oracle/Makefile), emit byte for
+    byte the model the stand-alone build emits."""
+    tool = os.path.join(ROOT, "oracle", "_ref", "intree_compile_check")
+    if not os.path.exists(tool):
+        pytest.skip("oracle/_ref/intree_compile_check not built (needs the reference tree)")
+    out = tmp_path / "intree.tiny"
+    r = subprocess.run([tool, str(out)], capture_output=True, text=True, check=True)
+    assert "reference_pooling_candidates" in r.stdout
+    from megcc_b200.compiler import Graph
+    g = Graph("intree")
+    x = g.input("data", 3, 64, 64, 0.02)
+    f1 = ((np.arange(64 * 3 * 7 * 7) * 37) % 255 - 127).astype(np.int8).reshape(64, 3, 7, 7)
+    f2 = ((np.arange(64 * 64 * 9) * 53) % 255 - 127).astype(np.int8).reshape(64, 64, 3, 3)
+    b = (np.arange(64) * 17 - 500).astype(np.int32)
+    y = g.conv_bias("stem", x, f1, b, 2, 3, 0.01, 0.5, "RELU")
+    y = g.pooling("pool", y, "MAX", 3, 2, 1)
+    z = g.conv_bias("conv", y, f2, b, 1, 1, 0.01, 2.0, "IDENTITY")
+    z = g.qelemwise("add", "QFUSE_ADD_RELU", z, y, 2.0)
+    g.mark_output(z)
+    mine = g.compile([1, 32])
+    assert out.read_bytes() == mine
+    assert r.stdout.split()[:5] == g.kernel_symbols()
