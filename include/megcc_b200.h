@@ -98,6 +98,25 @@ MB200_API int mb200_conv_bias_qs8_nchw(
         const mb200_conv_param* p, const int8_t* src, const int8_t* flt_oihw,
         const int32_t* bias, const float* flt_scales, int8_t* dst, void* workspace,
         size_t workspace_bytes, int algo, void* stream);
+/* The same operator for callers that cannot allocate device memory (a process whose own
+ * pool already owns the whole device, or a loop that cannot afford the device-wide
+ * synchronisation of cudaMalloc): this entry point has no counterpart in the reference.
+ * The scratch mb200_conv_bias_qs8_nchw asks its caller for comes from a fixed array of
+ * MB200_NOALLOC_SCRATCH_BYTES inside the library instead; the call makes no cudaMalloc,
+ * cudaFree or other allocating call. Problems that need more scratch are refused with
+ * TinyNN_ERROR_OUT_OF_RANGE (4) and a message naming both sizes. It runs the general
+ * CUDA-core ConvBias kernel; results are identical to the other entry points.
+ *  - The first call on each device resolves the array's device address; make that first call
+ *    before any stream capture begins.
+ *  - All calls on a device share the one array: two calls whose kernels overlap on the GPU
+ *    (different streams without ordering between them) race. Calls on one stream are safe.
+ *  - The array keeps the previous call's bytes; nothing depends on them, every byte read is
+ *    written first within the same call. */
+#define MB200_NOALLOC_SCRATCH_BYTES ((size_t)8 << 20)
+MB200_API size_t mb200_conv_bias_qs8_nchw_noalloc_max_scratch(void);
+MB200_API int mb200_conv_bias_qs8_nchw_noalloc(
+        const mb200_conv_param* p, const int8_t* src, const int8_t* flt_oihw,
+        const int32_t* bias, const float* flt_scales, int8_t* dst, void* stream);
 /* int32 accumulators (bias added, before requantisation), NHWC; for accumulator parity */
 MB200_API int mb200_conv_acc_qs8_nhwc(
         const mb200_conv_param* p, const int8_t* src, const int8_t* flt_packed,
