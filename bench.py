@@ -138,9 +138,8 @@ def main():
     ap.add_argument("--cpu-threads", type=int, default=0)
     args = ap.parse_args()
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
+    from megcc_b200 import shard
+    rank, local_rank, world = shard.env_rank()
 
     from megcc_b200 import zoo
     spec = zoo.resnet18()
@@ -168,25 +167,16 @@ def main():
 
     import numpy as np
     import torch
-    import torch.distributed as dist
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
     torch.cuda.set_device(local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    group = shard.Group("nccl", torch.device("cuda", local_rank))
 
     def barrier():
-        if world > 1:
-            dist.barrier()
+        group.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    max_over_ranks = group.max
 
     from megcc_b200 import lite
 
@@ -281,9 +271,7 @@ def main():
             sample=f"2 steps x {threads} images (one per thread), 1 warm-up step")
     net.close()
     net2.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    group.close()
     if rank != 0:
         return
     images = BATCH * world * args.steps
