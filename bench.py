@@ -45,31 +45,40 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    """nvidia-smi SM clock and throttle reasons, sampled every 20 ms from before the warm-up
+    until after the timed regions. Samples are time-stamped on arrival so that the ones
+    that fall inside the timed region can be told apart from the rest of the run."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.samples = index, None, []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
-                stderr=subprocess.DEVNULL, text=True)
+                 "-i", str(self.index), "-lms", "20"], stdout=subprocess.PIPE,
+                stderr=subprocess.DEVNULL, text=True, bufsize=1)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.samples.append((time.perf_counter(), line.strip()))
 
-    def stop(self):
+    def wait_first(self, timeout=5.0):
+        t0 = time.perf_counter()
+        while self.proc and not self.samples and time.perf_counter() - t0 < timeout:
+            time.sleep(0.01)
+
+    def stop(self, windows):
+        """windows: [(t_begin, t_end)] of the timed regions (perf_counter seconds)."""
         if not self.proc:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
         self.proc.terminate()
@@ -77,23 +86,36 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for l in self.lines:
-            f = [x.strip() for x in l.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for n, v in zip(names, f[5:9]):
-                if v.lower() == "active":
-                    reasons.add(n)
-        sm.sort()
+
+        def digest(rows):
+            sm, mx, reasons = [], [], set()
+            for _, l in rows:
+                f = [x.strip() for x in l.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, f[5:9]):
+                    if v.lower() == "active":
+                        reasons.add(n)
+            sm.sort()
+            return sm, mx, sorted(reasons)
+
+        inside = [r for r in self.samples
+                  if any(b - 0.02 <= r[0] <= e + 0.02 for b, e in windows)]
+        window = "timed regions"
+        if len(inside) < 3:  # a very short timed region: fall back to the loaded run around it
+            lo = min(b for b, _ in windows) - 1.0
+            hi = max(e for _, e in windows) + 0.2
+            inside = [r for r in self.samples if lo <= r[0] <= hi]
+            window = "timed regions and the warm-up before them"
+        sm, mx, reasons = digest(inside)
         return dict(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=max(mx) if mx else None,
-                    samples=len(sm), reasons=sorted(reasons))
+                    samples=len(sm), window=window, reasons=reasons)
 
 
 def cpu_reference_run(spec, steps, warmup, threads):
@@ -192,22 +214,27 @@ def main():
     stream = torch.cuda.ExternalStream(net.stream())
     ops_per_step = len([l for l in spec.layers])
     net.set_input_ptr("data", x_dev.data_ptr(), in_bytes)
+    sampler = ClockSampler(local_rank).start()
+    sampler.wait_first()
     for _ in range(max(args.warmup, 3)):
         net.forward()
     net.wait()
-    barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    # keep the GPU under the same load for a moment so the clock samples mean something
+    t_load = time.perf_counter()
+    while time.perf_counter() - t_load < 0.3:
+        net.forward()
+        net.wait()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    w0 = time.perf_counter()
     e0.record(stream)
     for _ in range(args.steps):
         net.forward()
     e1.record(stream)
     net.wait()
+    w1 = time.perf_counter()
     barrier()
     ms_dev = max_over_ranks(e0.elapsed_time(e1))
-    clocks = sampler.stop()
 
     # ---- end-to-end arm: pinned host input in, logits out, every step ----
     net2 = lite.Network(model, device_id=local_rank)
@@ -220,6 +247,7 @@ def main():
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     checksum = 0
+    w2 = time.perf_counter()
     f0.record(stream2)
     for _ in range(args.steps):
         net2.forward()
@@ -228,8 +256,10 @@ def main():
             (lite.C.c_int8 * 8).from_address(net2.output_ptr("fc:out")), dtype=np.int8)[0])
     f1.record(stream2)
     f1.synchronize()
+    w3 = time.perf_counter()
     barrier()
     ms_e2e = max_over_ranks(f0.elapsed_time(f1))
+    clocks = sampler.stop([(w0, w1), (w2, w3)])
 
     # ---- per-kernel pass for the roofline of the dominant kernel ----
     roofline = None

@@ -31,7 +31,7 @@ enum { MB200_POOL_MAX = 0, MB200_POOL_AVERAGE = 1, MB200_POOL_AVERAGE_COUNT_EXCL
 /* ElemwiseMultiType modes (compiler/lib/KernelGen/BareMetal/ElemwiseMultiType.cpp:26-56) */
 enum { MB200_QADD = 0, MB200_QFUSE_ADD_RELU = 1, MB200_QMUL = 2, MB200_QRELU = 3 };
 /* kernel choice for ConvBias */
-enum { MB200_ALGO_AUTO = 0, MB200_ALGO_DIRECT = 1, MB200_ALGO_UMMA = 2 };
+enum { MB200_ALGO_AUTO = 0, MB200_ALGO_DIRECT = 1, MB200_ALGO_UMMA = 2, MB200_ALGO_PATCH = 3 };
 
 /* The attributes the reference passes through TContext for a ConvBias
  * (kernel_h/w, stride_h/w, pad_h/w, dilate_h/w, sparse, nonlineMode:

@@ -153,6 +153,15 @@ int mb200_conv_bias_qs8_nhwc(
     if (!src || !flt_packed || !dst)
         return set_error(ST_NULL_PTR, "conv tensor pointer is NULL");
     cudaStream_t st = (cudaStream_t)stream;
+    const bool patch_ok = conv_patch_supported(a, src, flt_packed, dst);
+    if (algo == MB200_ALGO_PATCH && !patch_ok)
+        return set_error(ST_NO_IMPLEMENT,
+                         "halo-patch ConvBias needs dense, stride 1, NHWC, ic in {16, 32k <= 128}, "
+                         "16-byte aligned tensors and >= 128 KiB of input");
+    // the patch kernel pays for partial 16x8 patches; below 3/4 useful rows im2col wins
+    if (algo == MB200_ALGO_PATCH ||
+        (algo == MB200_ALGO_AUTO && patch_ok && conv_patch_efficiency(a) >= 0.75f))
+        return launch_conv_patch(a, src, flt_packed, bias, flt_scales, dst, st);
     const bool umma_ok = conv_umma_supported(a, src, flt_packed, dst);
     if (algo == MB200_ALGO_UMMA && !umma_ok)
         return set_error(ST_NO_IMPLEMENT,

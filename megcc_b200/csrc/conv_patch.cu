@@ -1,0 +1,480 @@
+// qint8 ConvBias, stride 1, on the tensor cores with halo-patch input tiles and a filter that
+// stays in shared memory.
+//
+// conv_umma.cu fetches the input once per filter tap (TMA im2col); for a 3x3 filter every
+// pixel is requested nine times and the filter tile again for every output tile, and the
+// request rate of the TMA unit becomes the limit. Here an output tile is a 16 (rows) x 8
+// (columns) patch of one image, and its whole input neighbourhood, (16+KH-1) x (8+KW-1)
+// pixels of all input channels, is brought in ONCE as planes of 16-channel chunks:
+//
+//     A stage  = [chunk = C/16][patch row][patch column][16 bytes]
+//
+// In the plain (unswizzled) K-major operand layout a core matrix is 8 rows x 16 bytes, rows
+// 16 bytes apart: 8 horizontally adjacent pixels of one chunk plane are exactly that, and
+// the next output row is PW*16 bytes further (the stride between 8-row groups). The operand
+// of tap (fy, fx) is therefore the same planes addressed from pixel (fy, fx): every tap is
+// a shifted view, nothing is copied or fetched again. The CTA's filter slice
+// [BN][KH*KW*C] is loaded once and stays resident; persistent CTAs walk the patch list.
+//
+// Accumulators: int32 in TMEM, two buffers; epilogue identical in arithmetic to conv_umma.cu
+// (reference order of compiler/lib/KernelGen/BareMetal/Activation.cpp:105-113).
+#include "internal.h"
+#include "umma_ptx.cuh"
+
+namespace mb200 {
+
+using namespace umma;
+
+namespace {
+
+constexpr int kTH = 16, kTW = 8;  // output patch; kTW = 8 makes a patch row one core matrix
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr int kMaxStages = 4;
+
+struct PatchParams {
+    int n, oh, ow, oc;
+    int chunks;      // C / 16
+    int kh, kw, ph, pw;
+    int pph, ppw;    // input patch extent: kTH + kh - 1, kTW + kw - 1
+    int tiles_y, tiles_x, m_tiles, n_tiles;
+    int stages;
+    int a_stage_bytes, a_tx_bytes, b_bytes;
+    int mma_per_tap;  // k-steps per tap (C/32), or 0 when C == 16 (two taps per k-step)
+    int act;
+    float s_src, s_flt, s_dst, inv_dst;
+    const int32_t* bias;
+    const float* flt_scales;
+    int8_t* dst;
+    int* status;
+};
+
+template <int ACT, bool PER_CHANNEL>
+__device__ __forceinline__ void store_chunk(
+        const uint32_t (&v)[32], const PatchParams& p, int8_t* out, int ch0) {
+    if (ch0 + 32 <= p.oc && (p.oc % 16) == 0) {
+        uint32_t packed[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int4 b = make_int4(0, 0, 0, 0);
+            if (p.bias)
+                b = __ldg(reinterpret_cast<const int4*>(p.bias + ch0) + j);
+            float4 s = make_float4(p.s_flt, p.s_flt, p.s_flt, p.s_flt);
+            if (PER_CHANNEL)
+                s = __ldg(reinterpret_cast<const float4*>(p.flt_scales + ch0) + j);
+            const int r0 = requant_conv_fast((int)v[j * 4 + 0] + b.x, p.s_src, s.x, p.s_dst,
+                                             p.inv_dst, ACT);
+            const int r1 = requant_conv_fast((int)v[j * 4 + 1] + b.y, p.s_src, s.y, p.s_dst,
+                                             p.inv_dst, ACT);
+            const int r2 = requant_conv_fast((int)v[j * 4 + 2] + b.z, p.s_src, s.z, p.s_dst,
+                                             p.inv_dst, ACT);
+            const int r3 = requant_conv_fast((int)v[j * 4 + 3] + b.w, p.s_src, s.w, p.s_dst,
+                                             p.inv_dst, ACT);
+            packed[j] = pack4_prmt(r0, r1, r2, r3);
+        }
+        reinterpret_cast<uint4*>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        reinterpret_cast<uint4*>(out)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (ch0 + i < p.oc) {
+                const int acc = (int)v[i] + (p.bias ? p.bias[ch0 + i] : 0);
+                const float s = PER_CHANNEL ? p.flt_scales[ch0 + i] : p.s_flt;
+                out[i] = (int8_t)requant_conv_fast(acc, p.s_src, s, p.s_dst, p.inv_dst, ACT);
+            }
+        }
+    }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads) conv_patch_kernel(
+        const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+        const PatchParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_b = smem;
+    uint8_t* smem_a = smem + p.b_bytes;
+    uint64_t* bars = (uint64_t*)(smem_a + p.stages * p.a_stage_bytes);
+    uint64_t* a_full = bars;                    // [kMaxStages]
+    uint64_t* a_empty = a_full + kMaxStages;    // [kMaxStages]
+    uint64_t* acc_full = a_empty + kMaxStages;  // [2]
+    uint64_t* acc_empty = acc_full + 2;         // [2]
+    uint64_t* b_full = acc_empty + 2;
+    uint64_t* drain_bar = b_full + 1;
+    uint32_t* tmem_slot = (uint32_t*)(drain_bar + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // each CTA owns one slice of output channels and walks the patches with a fixed stride
+    const int tile_n = blockIdx.x % p.n_tiles;
+    const int m_first = blockIdx.x / p.n_tiles;
+    const int m_step = gridDim.x / p.n_tiles;
+    const int n0 = tile_n * BN;
+    const int tiles_per_image = p.tiles_y * p.tiles_x;
+    const int plane = p.pph * p.ppw * 16;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMaxStages; ++s) {
+            mbar_init(&a_full[s], 1);
+            mbar_init(&a_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], kEpilogueThreads);
+        }
+        mbar_init(b_full, 1);
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile(
+                "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                        smem_u32(tmem_slot)),
+                "r"(2 * BN)
+                : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            // the filter slice, once: one [BN][16-byte] block per 16 bytes of K
+            const int kchunks = p.kh * p.kw * p.chunks;
+            mbar_expect_tx(b_full, (uint32_t)p.b_bytes);
+            for (int kc = 0; kc < kchunks; ++kc)
+                tma_load_2d(smem_b + kc * (BN * 16), &map_b, b_full, kc * 16, n0);
+            int local = 0;
+            for (int mt = m_first; mt < p.m_tiles; mt += m_step, ++local) {
+                const int s = local % p.stages;
+                const uint32_t phase = (uint32_t)(local / p.stages) & 1u;
+                if (!mbar_wait(&a_empty[s], phase ^ 1u, abort_flag)) {
+                    if (!*abort_flag) {
+                        *abort_flag = 1;
+                        atomicExch(p.status, ERR_PRODUCER_WAIT);
+                    }
+                    break;
+                }
+                const int img = mt / tiles_per_image;
+                const int rem = mt - img * tiles_per_image;
+                const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
+                const int x0 = tx * kTW - p.pw, y0 = ty * kTH - p.ph;
+                mbar_expect_tx(&a_full[s], (uint32_t)p.a_tx_bytes);
+                uint8_t* sa = smem_a + s * p.a_stage_bytes;
+                for (int c = 0; c < p.chunks; ++c)
+                    tma_load_4d(sa + c * plane, &map_a, &a_full[s], c * 16, x0, y0, img);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_s8(128, BN);
+            bool ok = mbar_wait(b_full, 0, abort_flag);
+            if (!ok && !*abort_flag) {
+                *abort_flag = 1;
+                atomicExch(p.status, ERR_MMA_WAIT);
+            }
+            const uint32_t b_addr = smem_u32(smem_b);
+            const uint32_t sbo_a = (uint32_t)p.ppw * 16;
+            int local = 0;
+            for (int mt = m_first; mt < p.m_tiles && ok; mt += m_step, ++local) {
+                const int buf = local & 1;
+                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
+                    if (!*abort_flag) {
+                        *abort_flag = 1;
+                        atomicExch(p.status, ERR_MMA_ACC_WAIT);
+                    }
+                    break;
+                }
+                const int s = local % p.stages;
+                const uint32_t phase = (uint32_t)(local / p.stages) & 1u;
+                if (!mbar_wait(&a_full[s], phase, abort_flag)) {
+                    if (!*abort_flag) {
+                        *abort_flag = 1;
+                        atomicExch(p.status, ERR_MMA_WAIT);
+                    }
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(smem_a + s * p.a_stage_bytes);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                uint32_t first = 1;
+                if (p.mma_per_tap > 0) {
+                    for (int fy = 0; fy < p.kh; ++fy) {
+                        for (int fx = 0; fx < p.kw; ++fx) {
+                            const uint32_t a_tap = a_addr + (uint32_t)(fy * p.ppw + fx) * 16;
+                            const uint32_t b_tap =
+                                    b_addr + (uint32_t)((fy * p.kw + fx) * p.chunks) * (BN * 16);
+                            for (int j = 0; j < p.mma_per_tap; ++j) {
+                                // chunks 2j, 2j+1 are the two 16-byte K halves of this step
+                                const uint64_t adesc = umma_smem_desc(
+                                        a_tap + (uint32_t)(2 * j) * plane, plane, sbo_a, 0);
+                                const uint64_t bdesc = umma_smem_desc(
+                                        b_tap + (uint32_t)(2 * j) * (BN * 16), BN * 16, 128, 0);
+                                umma_s8(tmem_d, adesc, bdesc, idesc, first ? 0u : 1u);
+                                first = 0;
+                            }
+                        }
+                    }
+                } else {
+                    // 16 channels: taps (fx, fx+1) are the two K halves; the second half is
+                    // the same plane one pixel (16 bytes) to the right
+                    for (int fy = 0; fy < p.kh; ++fy) {
+                        for (int fx = 0; fx < p.kw; fx += 2) {
+                            const uint64_t adesc = umma_smem_desc(
+                                    a_addr + (uint32_t)(fy * p.ppw + fx) * 16, 16, sbo_a, 0);
+                            const uint64_t bdesc = umma_smem_desc(
+                                    b_addr + (uint32_t)(fy * p.kw + fx) * (BN * 16), BN * 16, 128, 0);
+                            umma_s8(tmem_d, adesc, bdesc, idesc, first ? 0u : 1u);
+                            first = 0;
+                        }
+                    }
+                }
+                umma_commit(&a_empty[s]);
+                umma_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const int py = row >> 3, px = row & 7;
+        int local = 0;
+        bool ok = true;
+        for (int mt = m_first; mt < p.m_tiles && ok; mt += m_step, ++local) {
+            const int buf = local & 1;
+            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            ok = mbar_wait(&acc_full[buf], acc_phase, abort_flag);
+            if (!ok && !*abort_flag) {
+                *abort_flag = 1;
+                atomicExch(p.status, ERR_EPILOGUE_WAIT);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int img = mt / tiles_per_image;
+            const int rem = mt - img * tiles_per_image;
+            const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
+            const int oy = ty * kTH + py, ox = tx * kTW + px;
+            const bool valid = oy < p.oh && ox < p.ow;
+            int8_t* out_px = p.dst + (((size_t)img * p.oh + oy) * p.ow + ox) * p.oc;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(taddr + (uint32_t)(c * 32), v);
+                if (c == BN / 32 - 1) {
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbar_arrive(&acc_empty[buf]);
+                }
+                const int ch0 = n0 + c * 32;
+                if (valid && ch0 < p.oc) {
+                    const bool pc = p.flt_scales != nullptr;
+                    switch (p.act * 2 + (pc ? 1 : 0)) {
+                        case 0: store_chunk<ACT_IDENTITY, false>(v, p, out_px + ch0, ch0); break;
+                        case 1: store_chunk<ACT_IDENTITY, true>(v, p, out_px + ch0, ch0); break;
+                        case 2: store_chunk<ACT_RELU, false>(v, p, out_px + ch0, ch0); break;
+                        case 3: store_chunk<ACT_RELU, true>(v, p, out_px + ch0, ch0); break;
+                        case 4: store_chunk<ACT_H_SWISH, false>(v, p, out_px + ch0, ch0); break;
+                        default: store_chunk<ACT_H_SWISH, true>(v, p, out_px + ch0, ch0); break;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {
+        if (warp == 1 && lane == 0) {
+            umma_commit(drain_bar);
+            const long long t0 = clock64();
+            while (!mbar_try_wait(drain_bar, 0)) {
+                if (clock64() - t0 > kWaitCycles) {
+                    atomicExch(p.status, ERR_DRAIN_WAIT);
+                    break;
+                }
+            }
+        }
+        for (int i = 0; i < 200; ++i)
+            __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(2 * BN)
+                     : "memory");
+    }
+}
+
+struct PatchPlan {
+    bool ok;
+    int bn, stages, ctas_per_sm;
+    int a_stage_bytes, b_bytes, smem_bytes;
+};
+
+PatchPlan plan_patch(const ConvArgs& a) {
+    PatchPlan pl{};
+    if (a.groups != 1 || a.src_is_nchw || a.sh != 1 || a.sw != 1 || a.dh != 1 || a.dw != 1)
+        return pl;
+    if (a.ic % 16 != 0 || a.ic > 128 || (a.ic != 16 && a.ic % 32 != 0))
+        return pl;
+    if (a.ic == 16 && a.kw % 2 != 0)
+        return pl;
+    if (a.kh > 8 || a.kw > 8 || a.ph > 8 || a.pw > 8)
+        return pl;
+    const int pph = kTH + a.kh - 1, ppw = kTW + a.kw - 1;
+    if (pph > 256 || ppw > 256)
+        return pl;
+    pl.bn = a.oc <= 64 ? 64 : 128;
+    pl.a_stage_bytes = (a.ic / 16) * pph * ppw * 16;
+    // every A stage starts 128-byte aligned
+    pl.a_stage_bytes = (pl.a_stage_bytes + 127) / 128 * 128;
+    pl.b_bytes = pl.bn * a.kh * a.kw * a.ic;
+    const int fixed = pl.b_bytes + (2 * kMaxStages + 6) * 8 + 64 + 1024;
+    const int budget = 227 * 1024;
+    // prefer two CTAs per SM (epilogue of one overlaps the MMAs of the other)
+    for (int per_sm = 2; per_sm >= 1; --per_sm) {
+        const int avail = budget / per_sm - 1024 - fixed;
+        int st = avail / pl.a_stage_bytes;
+        if (st > kMaxStages)
+            st = kMaxStages;
+        if (st >= 2 && 2 * pl.bn * per_sm <= 512) {
+            pl.ok = true;
+            pl.stages = st;
+            pl.ctas_per_sm = per_sm;
+            pl.smem_bytes = fixed + st * pl.a_stage_bytes;
+            return pl;
+        }
+    }
+    return pl;
+}
+
+template <int BN>
+int launch_patch(
+        const CUtensorMap& ma, const CUtensorMap& mb, const PatchParams& p, int smem, int grid,
+        cudaStream_t st) {
+    if (cudaFuncSetAttribute(
+                conv_patch_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess)
+        return check_launch("conv_patch smem attribute");
+    conv_patch_kernel<BN><<<grid, kThreads, smem, st>>>(ma, mb, p);
+    return check_launch("conv_patch");
+}
+
+}  // namespace
+
+// Fraction of the MMA rows that land on real output pixels; the caller weighs it against
+// the im2col kernel, which has no such loss.
+float conv_patch_efficiency(const ConvArgs& a) {
+    const int ty = (a.oh + kTH - 1) / kTH, tx = (a.ow + kTW - 1) / kTW;
+    return (float)(a.oh * a.ow) / (float)(ty * kTH * tx * kTW);
+}
+
+bool conv_patch_supported(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst) {
+    if (!plan_patch(a).ok)
+        return false;
+    if ((size_t)a.n * a.ih * a.iw * a.ic < 131072)
+        return false;
+    if (((uintptr_t)src | (uintptr_t)flt | (uintptr_t)dst) & 15)
+        return false;
+    return true;
+}
+
+// `a`: stride-1 dense convolution over an NHWC source; a.ph / a.pw are the LOW paddings and
+// a.oh / a.ow the output extent (the upper padding is whatever those imply).
+int launch_conv_patch(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
+        const float* flt_scales, int8_t* dst, cudaStream_t st) {
+    const DriverApi& api = driver_api();
+    if (!api.ok)
+        return set_error(ST_RUNTIME, "cuTensorMapEncode* entry points not found in the driver");
+    const PatchPlan pl = plan_patch(a);
+    if (!pl.ok)
+        return set_error(ST_NO_IMPLEMENT, "halo-patch ConvBias does not apply to this shape");
+    if (((uintptr_t)bias & 15) || ((uintptr_t)flt_scales & 15))
+        return set_error(ST_INVALID_LAYOUT, "bias and channel scales must be 16-byte aligned");
+
+    const int pph = kTH + a.kh - 1, ppw = kTW + a.kw - 1;
+    CUtensorMap map_a, map_b;
+    {
+        cuuint64_t dims[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw, (cuuint64_t)a.ih,
+                              (cuuint64_t)a.n};
+        cuuint64_t strides[3] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw * a.ic,
+                                 (cuuint64_t)a.ih * a.iw * a.ic};
+        cuuint32_t box[4] = {16, (cuuint32_t)ppw, (cuuint32_t)pph, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = api.tiled(
+                &map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)src, dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(activation) failed: %d", (int)r);
+    }
+    {
+        const cuuint64_t k_total = (cuuint64_t)a.kh * a.kw * a.ic;
+        cuuint64_t dims[2] = {k_total, (cuuint64_t)a.oc};
+        cuuint64_t strides[1] = {k_total};
+        cuuint32_t box[2] = {16, (cuuint32_t)pl.bn};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = api.tiled(
+                &map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)flt, dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(filter) failed: %d", (int)r);
+    }
+
+    PatchParams p;
+    p.n = a.n;
+    p.oh = a.oh;
+    p.ow = a.ow;
+    p.oc = a.oc;
+    p.chunks = a.ic / 16;
+    p.kh = a.kh;
+    p.kw = a.kw;
+    p.ph = a.ph;
+    p.pw = a.pw;
+    p.pph = pph;
+    p.ppw = ppw;
+    p.tiles_y = (a.oh + kTH - 1) / kTH;
+    p.tiles_x = (a.ow + kTW - 1) / kTW;
+    p.m_tiles = a.n * p.tiles_y * p.tiles_x;
+    p.n_tiles = (a.oc + pl.bn - 1) / pl.bn;
+    p.stages = pl.stages;
+    p.a_stage_bytes = pl.a_stage_bytes;
+    p.a_tx_bytes = p.chunks * pph * ppw * 16;
+    p.b_bytes = pl.b_bytes;
+    p.mma_per_tap = a.ic == 16 ? 0 : a.ic / 32;
+    p.act = a.act;
+    p.s_src = a.s_src;
+    p.s_flt = a.s_flt;
+    p.s_dst = a.s_dst;
+    p.inv_dst = 1.0f / a.s_dst;
+    p.bias = bias;
+    p.flt_scales = flt_scales;
+    p.dst = dst;
+    p.status = device_status_word();
+    if (!p.status)
+        return ST_MALLOC;
+    // persistent grid: a multiple of the channel-slice count, at most what fits on the GPU
+    int grid = sm_count() * pl.ctas_per_sm;
+    grid = grid / p.n_tiles * p.n_tiles;
+    if (grid < p.n_tiles)
+        grid = p.n_tiles;
+    const long long total = (long long)p.m_tiles * p.n_tiles;
+    if (grid > total)
+        grid = (int)total;
+    return pl.bn == 64 ? launch_patch<64>(map_a, map_b, p, pl.smem_bytes, grid, st)
+                       : launch_patch<128>(map_a, map_b, p, pl.smem_bytes, grid, st);
+}
+
+}  // namespace mb200

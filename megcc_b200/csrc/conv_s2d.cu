@@ -143,6 +143,8 @@ int launch_conv_s2d(
     t.pw = -g.a_min_w;
     t.src_is_nchw = 0;
     // oh / ow / m stay those of the original convolution
+    if (conv_patch_supported(t, (const int8_t*)workspace, flt_s2d, dst))
+        return launch_conv_patch(t, (const int8_t*)workspace, flt_s2d, bias, flt_scales, dst, st);
     return launch_conv_umma_geom(t, 1, (const int8_t*)workspace, flt_s2d, bias, flt_scales, dst, st);
 }
 

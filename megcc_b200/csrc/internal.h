@@ -50,6 +50,12 @@ bool conv_umma_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt
 int launch_conv_umma(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
         const float* flt_scales, int8_t* dst, cudaStream_t st);
+// stride-1 tensor-core ConvBias with halo-patch tiles and a resident filter (conv_patch.cu)
+bool conv_patch_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst);
+float conv_patch_efficiency(const ConvArgs& a);
+int launch_conv_patch(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
+        const float* flt_scales, int8_t* dst, cudaStream_t st);
 // stride-2 ConvBias with <= 4 input channels via 2x2 space-to-depth (conv_s2d.cu)
 bool conv_s2d_supported(const ConvArgs& a);
 size_t conv_s2d_filter_bytes(const ConvArgs& a);

@@ -12,7 +12,7 @@ from ._lib import ConvParam, check, lib
 ACT = {"IDENTITY": 0, "RELU": 1, "H_SWISH": 2}
 POOL = {"MAX": 0, "AVERAGE": 1, "AVERAGE_COUNT_EXCLUDE_PADDING": 2}
 QELEM = {"QADD": 0, "QFUSE_ADD_RELU": 1, "QMUL": 2, "QRELU": 3}
-ALGO = {"auto": 0, "direct": 1, "umma": 2}
+ALGO = {"auto": 0, "direct": 1, "umma": 2, "patch": 3}
 
 
 def _stream():

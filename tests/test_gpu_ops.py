@@ -96,6 +96,34 @@ def test_conv_umma_matches_oracle(ops, oracle, case):
     assert (np.abs(want.astype(int)) < 127).mean() > 0.3
 
 
+PATCH_CASES = [
+    # name, n, ic, oc, h, w, k, pad, act  (all stride 1)
+    ("c64_56", 2, 64, 64, 56, 56, 3, 1, "RELU"),
+    ("c64_ragged", 3, 64, 64, 27, 29, 3, 1, "IDENTITY"),
+    ("c64_oc128", 2, 64, 128, 40, 40, 3, 1, "RELU"),
+    ("c128_28", 2, 128, 128, 28, 28, 3, 1, "RELU"),
+    ("c32_k5", 2, 32, 72, 50, 50, 5, 2, "H_SWISH"),
+    ("c16_k2x4", 8, 16, 64, 40, 40, 4, 2, "RELU"),
+    ("c96_k1", 4, 96, 200, 33, 31, 1, 0, "RELU"),
+    ("c64_nopad", 2, 64, 64, 40, 44, 3, 0, "RELU"),
+]
+
+
+@pytest.mark.parametrize("case", PATCH_CASES, ids=[c[0] for c in PATCH_CASES])
+def test_conv_patch_matches_oracle(ops, oracle, case):
+    name, n, ic, oc, h, w, k, pad, act = case
+    c = dict(name="patch_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=1, pad=pad, groups=1,
+             act=act, range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.37 * (ic * k * k / 576.0) ** 0.5 + 0.4))
+    out, (src, flt, bias) = run_conv_nchw(ops, c, algo="patch")
+    s0, s1, s2 = c["scales"]
+    want = oracle.conv_bias_qs8(src, flt, bias, 1, pad, s0, s1, s2, act)
+    bad = int((out != want).sum())
+    assert bad == 0, f"{bad}/{want.size} differ; first at {np.argwhere(out != want)[:4].tolist()}"
+    assert ops.device_status() == 0
+    assert (np.abs(want.astype(int)) < 127).mean() > 0.3
+
+
 S2D_CASES = [
     # name, n, ic, oc, h, w, k, pad, act  (all stride 2)
     ("r18_stem", 2, 3, 64, 224, 224, 7, 3, "RELU"),
