@@ -39,7 +39,7 @@ struct PatchParams {
     int pph, ppw;    // input patch extent: kTH + kh - 1, kTW + kw - 1
     int tiles_y, tiles_x, m_tiles, n_tiles;
     int stages;
-    int a_stage_bytes, a_tx_bytes, b_bytes;
+    int a_stage_bytes, a_tx_bytes, b_bytes, plane_stride;
     int mma_per_tap;  // k-steps per tap (C/32), or 0 when C == 16 (two taps per k-step)
     int act;
     float s_src, s_flt, s_dst, inv_dst;
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(kThreads) conv_patch_kernel(
     const int m_step = gridDim.x / p.n_tiles;
     const int n0 = tile_n * BN;
     const int tiles_per_image = p.tiles_y * p.tiles_x;
-    const int plane = p.pph * p.ppw * 16;
+    const int plane = p.plane_stride;  // chunk planes start 128-byte aligned (TMA destination rule)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(kThreads) conv_patch_kernel(
 struct PatchPlan {
     bool ok;
     int bn, stages, ctas_per_sm;
-    int a_stage_bytes, b_bytes, smem_bytes;
+    int a_stage_bytes, b_bytes, smem_bytes, plane_stride;
 };
 
 PatchPlan plan_patch(const ConvArgs& a) {
@@ -334,9 +334,9 @@ PatchPlan plan_patch(const ConvArgs& a) {
     if (pph > 256 || ppw > 256)
         return pl;
     pl.bn = a.oc <= 64 ? 64 : 128;
-    pl.a_stage_bytes = (a.ic / 16) * pph * ppw * 16;
-    // every A stage starts 128-byte aligned
-    pl.a_stage_bytes = (pl.a_stage_bytes + 127) / 128 * 128;
+    // a TMA destination in shared memory must be 128-byte aligned: pad every chunk plane
+    pl.plane_stride = (pph * ppw * 16 + 127) / 128 * 128;
+    pl.a_stage_bytes = (a.ic / 16) * pl.plane_stride;
     pl.b_bytes = pl.bn * a.kh * a.kw * a.ic;
     const int fixed = pl.b_bytes + (2 * kMaxStages + 6) * 8 + 64 + 1024;
     const int budget = 227 * 1024;
@@ -452,6 +452,7 @@ int launch_conv_patch(
     p.stages = pl.stages;
     p.a_stage_bytes = pl.a_stage_bytes;
     p.a_tx_bytes = p.chunks * pph * ppw * 16;
+    p.plane_stride = pl.plane_stride;
     p.b_bytes = pl.b_bytes;
     p.mma_per_tap = a.ic == 16 ? 0 : a.ic / 32;
     p.act = a.act;
