@@ -18,6 +18,7 @@
 //
 // Accumulators: int32 in TMEM, two buffers; epilogue identical in arithmetic to conv_umma.cu
 // (reference order of compiler/lib/KernelGen/BareMetal/Activation.cpp:105-113).
+#include "conv_epilogue.cuh"
 #include "internal.h"
 #include "umma_ptx.cuh"
 
@@ -41,53 +42,13 @@ struct PatchParams {
     int stages;
     int a_stage_bytes, a_tx_bytes, b_bytes, plane_stride;
     int mma_per_tap;  // k-steps per tap (C/32), or 0 when C == 16 (two taps per k-step)
-    int act;
-    float s_src, s_flt, s_dst, inv_dst;
-    const int32_t* bias;
-    const float* flt_scales;
+    EpilogueParams ep;
     int8_t* dst;
     int* status;
 };
 
-template <int ACT, bool PER_CHANNEL>
-__device__ __forceinline__ void store_chunk(
-        const uint32_t (&v)[32], const PatchParams& p, int8_t* out, int ch0) {
-    if (ch0 + 32 <= p.oc && (p.oc % 16) == 0) {
-        uint32_t packed[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            int4 b = make_int4(0, 0, 0, 0);
-            if (p.bias)
-                b = __ldg(reinterpret_cast<const int4*>(p.bias + ch0) + j);
-            float4 s = make_float4(p.s_flt, p.s_flt, p.s_flt, p.s_flt);
-            if (PER_CHANNEL)
-                s = __ldg(reinterpret_cast<const float4*>(p.flt_scales + ch0) + j);
-            const int r0 = requant_conv_fast((int)v[j * 4 + 0] + b.x, p.s_src, s.x, p.s_dst,
-                                             p.inv_dst, ACT);
-            const int r1 = requant_conv_fast((int)v[j * 4 + 1] + b.y, p.s_src, s.y, p.s_dst,
-                                             p.inv_dst, ACT);
-            const int r2 = requant_conv_fast((int)v[j * 4 + 2] + b.z, p.s_src, s.z, p.s_dst,
-                                             p.inv_dst, ACT);
-            const int r3 = requant_conv_fast((int)v[j * 4 + 3] + b.w, p.s_src, s.w, p.s_dst,
-                                             p.inv_dst, ACT);
-            packed[j] = pack4_prmt(r0, r1, r2, r3);
-        }
-        reinterpret_cast<uint4*>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        reinterpret_cast<uint4*>(out)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            if (ch0 + i < p.oc) {
-                const int acc = (int)v[i] + (p.bias ? p.bias[ch0 + i] : 0);
-                const float s = PER_CHANNEL ? p.flt_scales[ch0 + i] : p.s_flt;
-                out[i] = (int8_t)requant_conv_fast(acc, p.s_src, s, p.s_dst, p.inv_dst, ACT);
-            }
-        }
-    }
-}
-
 template <int BN>
-__global__ void __launch_bounds__(kThreads) conv_patch_kernel(
+__global__ void __launch_bounds__(kThreads, 2) conv_patch_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const PatchParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -274,17 +235,8 @@ __global__ void __launch_bounds__(kThreads) conv_patch_kernel(
                     mbar_arrive(&acc_empty[buf]);
                 }
                 const int ch0 = n0 + c * 32;
-                if (valid && ch0 < p.oc) {
-                    const bool pc = p.flt_scales != nullptr;
-                    switch (p.act * 2 + (pc ? 1 : 0)) {
-                        case 0: store_chunk<ACT_IDENTITY, false>(v, p, out_px + ch0, ch0); break;
-                        case 1: store_chunk<ACT_IDENTITY, true>(v, p, out_px + ch0, ch0); break;
-                        case 2: store_chunk<ACT_RELU, false>(v, p, out_px + ch0, ch0); break;
-                        case 3: store_chunk<ACT_RELU, true>(v, p, out_px + ch0, ch0); break;
-                        case 4: store_chunk<ACT_H_SWISH, false>(v, p, out_px + ch0, ch0); break;
-                        default: store_chunk<ACT_H_SWISH, true>(v, p, out_px + ch0, ch0); break;
-                    }
-                }
+                if (valid && ch0 < p.oc)
+                    epilogue_store32(v, p.ep, out_px + ch0, ch0);
             }
         }
     }
@@ -365,6 +317,16 @@ int launch_patch(
                 conv_patch_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
         return check_launch("conv_patch smem attribute");
+    // never more CTAs than are resident at once: a persistent CTA that starts late would
+    // leave its share of the patches to the end
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, conv_patch_kernel<BN>, kThreads,
+                                                      smem) == cudaSuccess &&
+        per_sm >= 1) {
+        int cap = sm_count() * per_sm / p.n_tiles * p.n_tiles;
+        if (cap >= p.n_tiles && grid > cap)
+            grid = cap;
+    }
     conv_patch_kernel<BN><<<grid, kThreads, smem, st>>>(ma, mb, p);
     return check_launch("conv_patch");
 }
@@ -374,6 +336,10 @@ int launch_patch(
 // Fraction of the MMA rows that land on real output pixels; the caller weighs it against
 // the im2col kernel, which has no such loss.
 float conv_patch_efficiency(const ConvArgs& a) {
+    // with a filter slice so large that only one CTA fits per SM, nothing overlaps the
+    // epilogue and the im2col kernel measured faster: report no benefit
+    if (plan_patch(a).ctas_per_sm < 2)
+        return 0.f;
     const int ty = (a.oh + kTH - 1) / kTH, tx = (a.ow + kTW - 1) / kTW;
     return (float)(a.oh * a.ow) / (float)(ty * kTH * tx * kTW);
 }
@@ -455,13 +421,15 @@ int launch_conv_patch(
     p.plane_stride = pl.plane_stride;
     p.b_bytes = pl.b_bytes;
     p.mma_per_tap = a.ic == 16 ? 0 : a.ic / 32;
-    p.act = a.act;
-    p.s_src = a.s_src;
-    p.s_flt = a.s_flt;
-    p.s_dst = a.s_dst;
-    p.inv_dst = 1.0f / a.s_dst;
-    p.bias = bias;
-    p.flt_scales = flt_scales;
+    p.ep.oc = a.oc;
+    p.ep.act = a.act;
+    p.ep.bounded = requant_is_bounded(a.s_src, a.s_flt, a.s_dst) ? 1 : 0;
+    p.ep.s_src = a.s_src;
+    p.ep.s_flt = a.s_flt;
+    p.ep.s_dst = a.s_dst;
+    p.ep.inv_dst = 1.0f / a.s_dst;  // correctly rounded on the host
+    p.ep.bias = bias;
+    p.ep.flt_scales = flt_scales;
     p.dst = dst;
     p.status = device_status_word();
     if (!p.status)

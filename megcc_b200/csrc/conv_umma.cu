@@ -21,6 +21,7 @@
 //
 // Replaces the loop nest of compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:305-344 and
 // its epilogue (:374-382, BareMetal/Activation.cpp:105-113).
+#include "conv_epilogue.cuh"
 #include "internal.h"
 #include "umma_ptx.cuh"
 
@@ -47,10 +48,7 @@ struct UmmaConvParams {
     int base_h, base_w; // coordinate of output (0,0)'s first tap (= -pad)
     int dh, dw;
     int m_tiles, n_tiles;
-    int act;
-    float s_src, s_flt, s_dst, inv_dst;
-    const int32_t* bias;
-    const float* flt_scales;
+    EpilogueParams ep;
     int8_t* dst;
     int* status;
 };
@@ -66,50 +64,8 @@ struct SmemLayout {
     static constexpr int kDynamic = kTotal + 1024;  // room to align the tiles to 1024 bytes
 };
 
-// 32 accumulators of one output pixel -> 32 int8, stored as two 16-byte vectors
-template <int ACT, bool PER_CHANNEL>
-__device__ __forceinline__ void epilogue_chunk(
-        const uint32_t (&v)[32], const UmmaConvParams& p, int m, int ch0) {
-    int8_t* out = p.dst + (size_t)m * p.oc + ch0;
-    const bool full = ch0 + 32 <= p.oc;
-    if (full && (p.oc % 16) == 0) {
-        uint32_t packed[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            int4 b = make_int4(0, 0, 0, 0);
-            if (p.bias)
-                b = __ldg(reinterpret_cast<const int4*>(p.bias + ch0) + j);
-            float4 s = make_float4(p.s_flt, p.s_flt, p.s_flt, p.s_flt);
-            if (PER_CHANNEL)
-                s = __ldg(reinterpret_cast<const float4*>(p.flt_scales + ch0) + j);
-            const int r0 = requant_conv_fast((int)v[j * 4 + 0] + b.x, p.s_src, s.x, p.s_dst,
-                                             p.inv_dst, ACT);
-            const int r1 = requant_conv_fast((int)v[j * 4 + 1] + b.y, p.s_src, s.y, p.s_dst,
-                                             p.inv_dst, ACT);
-            const int r2 = requant_conv_fast((int)v[j * 4 + 2] + b.z, p.s_src, s.z, p.s_dst,
-                                             p.inv_dst, ACT);
-            const int r3 = requant_conv_fast((int)v[j * 4 + 3] + b.w, p.s_src, s.w, p.s_dst,
-                                             p.inv_dst, ACT);
-            packed[j] = pack4_prmt(r0, r1, r2, r3);
-        }
-        reinterpret_cast<uint4*>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        reinterpret_cast<uint4*>(out)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-    } else {
-        // ragged channel tail (or a channel count that rules out vector stores)
-        // (fully unrolled with a predicate so the accumulators stay in registers)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            if (ch0 + i < p.oc) {
-                const int acc = (int)v[i] + (p.bias ? p.bias[ch0 + i] : 0);
-                const float s = PER_CHANNEL ? p.flt_scales[ch0 + i] : p.s_flt;
-                out[i] = (int8_t)requant_conv_fast(acc, p.s_src, s, p.s_dst, p.inv_dst, ACT);
-            }
-        }
-    }
-}
-
 template <int BN, int GEOM>
-__global__ void __launch_bounds__(kThreads) conv_umma_kernel(
+__global__ void __launch_bounds__(kThreads, 2) conv_umma_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const UmmaConvParams p) {
     using L = SmemLayout<BN>;
@@ -284,17 +240,8 @@ __global__ void __launch_bounds__(kThreads) conv_umma_kernel(
                     mbar_arrive(&acc_empty[buf]);
                 }
                 const int ch0 = n0 + c * 32;
-                if (m < p.m_total && ch0 < p.oc) {
-                    const bool pc = p.flt_scales != nullptr;
-                    switch (p.act * 2 + (pc ? 1 : 0)) {
-                        case 0: epilogue_chunk<ACT_IDENTITY, false>(v, p, m, ch0); break;
-                        case 1: epilogue_chunk<ACT_IDENTITY, true>(v, p, m, ch0); break;
-                        case 2: epilogue_chunk<ACT_RELU, false>(v, p, m, ch0); break;
-                        case 3: epilogue_chunk<ACT_RELU, true>(v, p, m, ch0); break;
-                        case 4: epilogue_chunk<ACT_H_SWISH, false>(v, p, m, ch0); break;
-                        default: epilogue_chunk<ACT_H_SWISH, true>(v, p, m, ch0); break;
-                    }
-                }
+                if (m < p.m_total && ch0 < p.oc)
+                    epilogue_store32(v, p.ep, p.dst + (size_t)m * p.oc + ch0, ch0);
             }
         }
     }
@@ -336,12 +283,17 @@ int launch_kernel(
                 conv_umma_kernel<BN, GEOM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                 SmemLayout<BN>::kDynamic) != cudaSuccess)
         return check_launch("conv_umma smem attribute");
-    // persistent CTAs: as many as fit per SM (shared memory and 2*BN TMEM columns each)
-    const int per_sm_smem = (227 * 1024) / (SmemLayout<BN>::kDynamic + 1024);
-    const int per_sm_tmem = 512 / (2 * BN);
-    int per_sm = per_sm_smem < per_sm_tmem ? per_sm_smem : per_sm_tmem;
-    if (per_sm < 1)
+    // persistent CTAs: as many as the SM holds at once (registers, shared memory), and no
+    // more than the 512 TMEM columns allow at 2*BN columns each
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                &per_sm, conv_umma_kernel<BN, GEOM>, kThreads, SmemLayout<BN>::kDynamic) !=
+                cudaSuccess ||
+        per_sm < 1)
         per_sm = 1;
+    const int per_sm_tmem = 512 / (2 * BN);
+    if (per_sm > per_sm_tmem)
+        per_sm = per_sm_tmem;
     const int total = p.m_tiles * p.n_tiles;
     int grid = sm_count() * per_sm;
     if (grid > total)
@@ -439,13 +391,15 @@ int launch_conv_umma_geom(
     p.dw = a.dw;
     p.m_tiles = (a.m + kBM - 1) / kBM;
     p.n_tiles = (a.oc + bn - 1) / bn;
-    p.act = a.act;
-    p.s_src = a.s_src;
-    p.s_flt = a.s_flt;
-    p.s_dst = a.s_dst;
-    p.inv_dst = 1.0f / a.s_dst;  // correctly rounded on the host
-    p.bias = bias;
-    p.flt_scales = flt_scales;
+    p.ep.oc = a.oc;
+    p.ep.act = a.act;
+    p.ep.bounded = requant_is_bounded(a.s_src, a.s_flt, a.s_dst) ? 1 : 0;
+    p.ep.s_src = a.s_src;
+    p.ep.s_flt = a.s_flt;
+    p.ep.s_dst = a.s_dst;
+    p.ep.inv_dst = 1.0f / a.s_dst;  // correctly rounded on the host
+    p.ep.bias = bias;
+    p.ep.flt_scales = flt_scales;
     p.dst = dst;
     p.status = device_status_word();
     if (!p.status)
