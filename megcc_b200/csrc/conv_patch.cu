@@ -18,6 +18,9 @@
 //
 // Accumulators: int32 in TMEM, two buffers; epilogue identical in arithmetic to conv_umma.cu
 // (reference order of compiler/lib/KernelGen/BareMetal/Activation.cpp:105-113).
+#include <stdio.h>
+#include <stdlib.h>
+
 #include "conv_epilogue.cuh"
 #include "internal.h"
 #include "umma_ptx.cuh"
@@ -29,9 +32,10 @@ using namespace umma;
 namespace {
 
 constexpr int kTH = 16, kTW = 8;  // output patch; kTW = 8 makes a patch row one core matrix
-constexpr int kThreads = 192;
-constexpr int kEpilogueThreads = 128;
-constexpr int kMaxStages = 4;
+constexpr int kEpilogueWarps = 8;  // two per TMEM lane quarter, splitting the column chunks
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kEpilogueThreads = 32 * kEpilogueWarps;
+constexpr int kMaxStages = 3;
 
 struct PatchParams {
     int n, oh, ow, oc;
@@ -48,7 +52,7 @@ struct PatchParams {
 };
 
 template <int BN>
-__global__ void __launch_bounds__(kThreads, 2) conv_patch_kernel(
+__global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const PatchParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -226,11 +230,14 @@ __global__ void __launch_bounds__(kThreads, 2) conv_patch_kernel(
             const bool valid = oy < p.oh && ox < p.ow;
             int8_t* out_px = p.dst + (((size_t)img * p.oh + oy) * p.ow + ox) * p.oc;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+            // warps 2..5 take the even column chunks of their quarter, warps 6..9 the odd ones
+            const int half = (warp - 2) >> 2;
+            constexpr int kChunkStep = kEpilogueWarps / 4;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = half; c < BN / 32; c += kChunkStep) {
                 uint32_t v[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), v);
-                if (c == BN / 32 - 1) {
+                if (c + kChunkStep >= BN / 32) {
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     mbar_arrive(&acc_empty[buf]);
                 }
@@ -292,8 +299,9 @@ PatchPlan plan_patch(const ConvArgs& a) {
     pl.b_bytes = pl.bn * a.kh * a.kw * a.ic;
     const int fixed = pl.b_bytes + (2 * kMaxStages + 6) * 8 + 64 + 1024;
     const int budget = 227 * 1024;
-    // prefer two CTAs per SM (epilogue of one overlaps the MMAs of the other)
-    for (int per_sm = 2; per_sm >= 1; --per_sm) {
+    // more CTAs per SM hide more latency; one stage is a whole tile, so two stages already
+    // keep the loads a tile ahead
+    for (int per_sm = 3; per_sm >= 1; --per_sm) {
         const int avail = budget / per_sm - 1024 - fixed;
         int st = avail / pl.a_stage_bytes;
         if (st > kMaxStages)
@@ -319,14 +327,15 @@ int launch_patch(
         return check_launch("conv_patch smem attribute");
     // never more CTAs than are resident at once: a persistent CTA that starts late would
     // leave its share of the patches to the end
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, conv_patch_kernel<BN>, kThreads,
-                                                      smem) == cudaSuccess &&
-        per_sm >= 1) {
+    const int per_sm = resident_ctas_per_sm(conv_patch_kernel<BN>, kThreads, smem, 2 * BN);
+    {
         int cap = sm_count() * per_sm / p.n_tiles * p.n_tiles;
         if (cap >= p.n_tiles && grid > cap)
             grid = cap;
     }
+    if (getenv("MB200_DEBUG"))
+        fprintf(stderr, "conv_patch<%d>: per_sm %d grid %d m_tiles %d n_tiles %d smem %d stages %d\n", BN,
+                per_sm, grid, p.m_tiles, p.n_tiles, smem, p.stages);
     conv_patch_kernel<BN><<<grid, kThreads, smem, st>>>(ma, mb, p);
     return check_launch("conv_patch");
 }

@@ -9,7 +9,7 @@
 // * tcgen05.mma kind::i8, M=128 x N=BN x K=32 per instruction, int32 accumulators in TMEM,
 //   two accumulator buffers so the epilogue of one tile overlaps the MMAs of the next.
 // * persistent CTAs walk the tile list; warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM
-//   alloc), warps 2..5 = epilogue (tcgen05.ld -> +bias -> fp32 requantisation in the
+//   alloc), warps 2..9 = epilogue (tcgen05.ld -> +bias -> fp32 requantisation in the
 //   reference's operation order -> activation -> int8 -> 16-byte stores).
 // * every wait is bounded: when it runs out the kernel records a code in the device status
 //   word, drains what it started, frees its TMEM and returns.
@@ -21,6 +21,9 @@
 //
 // Replaces the loop nest of compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:305-344 and
 // its epilogue (:374-382, BareMetal/Activation.cpp:105-113).
+#include <stdio.h>
+#include <stdlib.h>
+
 #include "conv_epilogue.cuh"
 #include "internal.h"
 #include "umma_ptx.cuh"
@@ -35,8 +38,9 @@ constexpr int kBM = 128;     // output pixels per tile (UMMA M)
 constexpr int kBK = 64;      // K bytes per pipeline stage
 constexpr int kUmmaK = 32;   // K per tcgen05.mma kind::i8
 constexpr int kStages = 6;
-constexpr int kThreads = 192;
-constexpr int kEpilogueThreads = 128;
+constexpr int kEpilogueWarps = 8;  // two per TMEM lane quarter, splitting the column chunks
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kEpilogueThreads = 32 * kEpilogueWarps;
 enum Geometry : int { GEOM_WIDE = 0, GEOM_TAP16 = 1 };
 
 struct UmmaConvParams {
@@ -65,7 +69,7 @@ struct SmemLayout {
 };
 
 template <int BN, int GEOM>
-__global__ void __launch_bounds__(kThreads, 2) conv_umma_kernel(
+__global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const UmmaConvParams p) {
     using L = SmemLayout<BN>;
@@ -210,7 +214,7 @@ __global__ void __launch_bounds__(kThreads, 2) conv_umma_kernel(
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp%4).. ----------------
+        // ---------------- epilogue: warps 2..9, TMEM lanes 32*(warp%4).. ----------------
         const int q = warp & 3;
         const int row = q * 32 + lane;
         int local = 0;
@@ -230,11 +234,14 @@ __global__ void __launch_bounds__(kThreads, 2) conv_umma_kernel(
                 break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+            // warps 2..5 take the even column chunks of their quarter, warps 6..9 the odd ones
+            const int half = (warp - 2) >> 2;
+            constexpr int kChunkStep = kEpilogueWarps / 4;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = half; c < BN / 32; c += kChunkStep) {
                 uint32_t v[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), v);
-                if (c == BN / 32 - 1) {
+                if (c + kChunkStep >= BN / 32) {
                     // all of this thread's accumulators are in registers: hand the buffer back
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     mbar_arrive(&acc_empty[buf]);
@@ -283,21 +290,16 @@ int launch_kernel(
                 conv_umma_kernel<BN, GEOM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                 SmemLayout<BN>::kDynamic) != cudaSuccess)
         return check_launch("conv_umma smem attribute");
-    // persistent CTAs: as many as the SM holds at once (registers, shared memory), and no
-    // more than the 512 TMEM columns allow at 2*BN columns each
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-                &per_sm, conv_umma_kernel<BN, GEOM>, kThreads, SmemLayout<BN>::kDynamic) !=
-                cudaSuccess ||
-        per_sm < 1)
-        per_sm = 1;
-    const int per_sm_tmem = 512 / (2 * BN);
-    if (per_sm > per_sm_tmem)
-        per_sm = per_sm_tmem;
+    // persistent CTAs: as many as the SM holds at once
+    const int per_sm = resident_ctas_per_sm(
+            conv_umma_kernel<BN, GEOM>, kThreads, SmemLayout<BN>::kDynamic, 2 * BN);
     const int total = p.m_tiles * p.n_tiles;
     int grid = sm_count() * per_sm;
     if (grid > total)
         grid = total;
+    if (getenv("MB200_DEBUG"))
+        fprintf(stderr, "conv_umma<%d,%d>: per_sm %d grid %d tiles %d smem %d\n", BN, GEOM, per_sm, grid,
+                total, SmemLayout<BN>::kDynamic);
     conv_umma_kernel<BN, GEOM><<<grid, kThreads, SmemLayout<BN>::kDynamic, st>>>(ma, mb, p);
     return check_launch("conv_umma");
 }

@@ -210,5 +210,24 @@ inline int sm_count() {
     return sms[dev];
 }
 
+// CTAs of `threads` threads that one SM holds at once, from the kernel's register count,
+// its dynamic shared memory and its TMEM columns. (The runtime's occupancy query answers 1
+// for these kernels whatever their footprint, so the arithmetic is done here.)
+template <class Kernel>
+inline int resident_ctas_per_sm(Kernel kernel, int threads, int dynamic_smem, int tmem_cols) {
+    cudaFuncAttributes fa;
+    int regs = 128;
+    if (cudaFuncGetAttributes(&fa, kernel) == cudaSuccess && fa.numRegs > 0)
+        regs = fa.numRegs;
+    const int regs_per_warp = (regs * 32 + 511) / 512 * 512;  // allocation granularity
+    const int warps = (threads + 31) / 32;
+    int by_regs = 65536 / (regs_per_warp * warps);
+    int by_smem = (227 * 1024) / (dynamic_smem + 1024);
+    int by_tmem = tmem_cols > 0 ? 512 / tmem_cols : 32;
+    int n = by_regs < by_smem ? by_regs : by_smem;
+    n = n < by_tmem ? n : by_tmem;
+    return n < 1 ? 1 : n;
+}
+
 }  // namespace umma
 }  // namespace mb200
