@@ -46,6 +46,18 @@ typedef struct mb200_conv_param {
     float src_scale, flt_scale, dst_scale;
 } mb200_conv_param;
 
+/* An ElemwiseMultiType step fused behind a ConvBias without activation: the int8 result of
+ * the ConvBias (scale p->dst_scale, exactly what the stand-alone kernel would store) and the
+ * int8 tensor z of the same NHWC shape go through kernel_elementwise_multitype_<MODE>
+ * (compiler/lib/KernelGen/BareMetal/ElemwiseMultiType.cpp:38-46,158) with output scale
+ * out_scale. Bit-identical to running the two kernels one after the other. */
+typedef struct mb200_conv_fuse {
+    const int8_t* z;
+    int mode;        /* MB200_QADD or MB200_QFUSE_ADD_RELU */
+    float z_scale;   /* scale of z */
+    float out_scale; /* scale of the fused output */
+} mb200_conv_fuse;
+
 /* ---- library ---- */
 MB200_API const char* mb200_version(void);
 /* text of the last error raised on the calling thread ("" if none) */
@@ -76,6 +88,11 @@ MB200_API int mb200_conv_bias_qs8_nhwc(
         const mb200_conv_param* p, const int8_t* src, int src_is_nchw,
         const int8_t* flt_packed, const int32_t* bias, const float* flt_scales, int8_t* dst,
         int algo, void* stream);
+/* mb200_conv_bias_qs8_nhwc with a fused elementwise step (fuse may be NULL: plain ConvBias) */
+MB200_API int mb200_conv_bias_qs8_nhwc_fused(
+        const mb200_conv_param* p, const int8_t* src, int src_is_nchw,
+        const int8_t* flt_packed, const int32_t* bias, const float* flt_scales,
+        const mb200_conv_fuse* fuse, int8_t* dst, int algo, void* stream);
 /* First-layer form: stride 2 and at most 4 input channels run on the tensor cores after a
  * 2x2 space-to-depth step into `workspace` (device scratch, 16-byte aligned, at least
  * mb200_conv_s2d_workspace_bytes(p)). The filter must have been packed by

@@ -56,6 +56,14 @@ MB200C_API int mb200c_add_qelemwise(
 
 MB200C_API int mb200c_mark_output(mb200c_graph* g, int tensor);
 
+/* Options (all on by default):
+ *   "fuse_conv_elemwise"  a ConvBias without activation whose only consumer is a QADD /
+ *                         QFUSE_ADD_RELU becomes one instruction (the z operand slot of the
+ *                         reference's Conv2DKernel); results are bit-identical to the two
+ *                         separate kernels (the MGB-level counterpart in the reference is
+ *                         compiler/lib/Dialect/MGB/Transforms/KernelFuse.cpp:41-80). */
+MB200C_API int mb200c_set_option(mb200c_graph* g, const char* name, int value);
+
 /* Compiles one DeviceModel (device CUDA_SM100) per batch size into a tinynn model.
  * The returned bytes belong to the graph and stay valid until it is destroyed or
  * compiled again. */

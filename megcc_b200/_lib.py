@@ -15,6 +15,12 @@ class ConvParam(C.Structure):
         ("src_scale", C.c_float), ("flt_scale", C.c_float), ("dst_scale", C.c_float)]
 
 
+class ConvFuse(C.Structure):
+    """Mirror of ``mb200_conv_fuse``."""
+    _fields_ = [("z", C.c_void_p), ("mode", C.c_int), ("z_scale", C.c_float),
+                ("out_scale", C.c_float)]
+
+
 _lib = None
 
 # name -> (restype, argtypes); every symbol declared in include/megcc_b200.h
@@ -28,6 +34,8 @@ SIGNATURES = {
     "mb200_conv_pack_filter": (C.c_int, [C.POINTER(ConvParam), _P, _P, _P]),
     "mb200_conv_bias_qs8_nhwc": (C.c_int, [C.POINTER(ConvParam), _P, C.c_int, _P, _P, _P, _P,
                                            C.c_int, _P]),
+    "mb200_conv_bias_qs8_nhwc_fused": (C.c_int, [C.POINTER(ConvParam), _P, C.c_int, _P, _P, _P, _P,
+                                                 _P, C.c_int, _P]),
     "mb200_conv_s2d_supported": (C.c_int, [C.POINTER(ConvParam)]),
     "mb200_conv_s2d_filter_bytes": (C.c_size_t, [C.POINTER(ConvParam)]),
     "mb200_conv_s2d_workspace_bytes": (C.c_size_t, [C.POINTER(ConvParam)]),

@@ -19,6 +19,7 @@ SIGNATURES = {
     "mb200c_add_pooling": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_char_p] + [C.c_int] * 3),
     "mb200c_add_qelemwise": (C.c_int, [_P, C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_float]),
     "mb200c_mark_output": (C.c_int, [_P, C.c_int]),
+    "mb200c_set_option": (C.c_int, [_P, C.c_char_p, C.c_int]),
     "mb200c_compile": (C.c_int, [_P, C.POINTER(C.c_int), C.c_int, C.POINTER(_P),
                                  C.POINTER(C.c_size_t)]),
     "mb200c_kernel_symbols": (C.c_char_p, [_P]),
@@ -90,6 +91,9 @@ class Graph:
     def qelemwise(self, name, mode, a, b, dst_scale):
         return _check(lib().mb200c_add_qelemwise(self._g, name.encode(), mode.encode(), a,
                                                  -1 if b is None else b, dst_scale))
+
+    def set_option(self, name, value):
+        _check(lib().mb200c_set_option(self._g, name.encode(), int(value)))
 
     def mark_output(self, t):
         _check(lib().mb200c_mark_output(self._g, t))

@@ -3,6 +3,7 @@
 #include "../csrc/conv_s2d_geom.h"
 
 #include <cmath>
+#include <cstdio>
 #include <sstream>
 
 using namespace megcc;
@@ -48,6 +49,12 @@ bool channel_broadcast_bias(TContext* ctx) {
     if (b.shape.size() == 1)
         return true;
     return b.shape.size() == 4 && b.shape[0] == 1 && b.shape[2] == 1 && b.shape[3] == 1;
+}
+
+// "" unless the operator carries a fused ElemwiseMultiType step (5 operands: src, filter,
+// bias, z, dst)
+std::string fuse_mode(TContext* ctx) {
+    return ctx->haveAttr("fuse_elemwise_mode") ? ctx->getAttrStr("fuse_elemwise_mode") : "";
 }
 
 std::string nonline(TContext* ctx) {
@@ -96,6 +103,18 @@ bool ConvBiasQS8::IsAvailable(TContext* ctx) const {
     const std::string act = nonline(ctx);
     if (act != "IDENTITY" && act != "RELU" && act != "H_SWISH")
         return false;
+    const std::string fm = fuse_mode(ctx);
+    if (!fm.empty()) {
+        // fused residual step: needs the z operand, no activation on the ConvBias itself
+        if (ctx->getAttrInt("nr_operands") != 5 || act != "IDENTITY" ||
+            (fm != "QADD" && fm != "QFUSE_ADD_RELU"))
+            return false;
+        const CCOperand z = ctx->getAttrOprand("operand:3");
+        if (!is_quant(z.dtype, 8) || z.shape != dst.shape)
+            return false;
+    } else if (ctx->getAttrInt("nr_operands") > 4) {
+        return false;
+    }
     if (has_bias(ctx)) {
         const CCOperand bias = ctx->getAttrOprand("operand:2");
         if (!is_quant(bias.dtype, 32) || !channel_broadcast_bias(ctx))
@@ -121,6 +140,8 @@ std::string ConvBiasQS8::GetKernelSymbol(TContext* ctx) const {
         ss << "_bias";
     if (nonline(ctx) != "IDENTITY")
         ss << "_" << nonline(ctx);
+    if (!fuse_mode(ctx).empty())
+        ss << "_z_" << fuse_mode(ctx);
     return ss.str();
 }
 
@@ -149,7 +170,22 @@ TinyNNStatus ${signature} {
     p.dst_scale = dst->dtype.param.scale;
     const int src_is_nchw = src->layout.format == TinyNN_NCHW;
     const int32_t* bias = ${has_bias} ? (const int32_t*)inputs[2]->ptr : 0;
-    const float* ch_scales = nr_input > ${scale_idx} ? (const float*)inputs[${scale_idx}]->ptr : 0;
+    /* inputs: src, filter, [bias], [channel scales], [z, mid scale] */
+    const int nr_plain = nr_input - ${fused} * 2;
+    const float* ch_scales = nr_plain > ${scale_idx} ? (const float*)inputs[${scale_idx}]->ptr : 0;
+    if (${fused}) {
+        mb200_conv_fuse fuse;
+        fuse.z = (const int8_t*)inputs[nr_input - 2]->ptr;
+        fuse.mode = ${fuse_code};
+        fuse.z_scale = inputs[nr_input - 2]->dtype.param.scale;
+        fuse.out_scale = dst->dtype.param.scale;
+        /* the ConvBias result keeps its own scale; it travels as the dtype scale of a
+         * 1-element weight, the last input */
+        p.dst_scale = inputs[nr_input - 1]->dtype.param.scale;
+        return (TinyNNStatus)mb200_conv_bias_qs8_nhwc_fused(
+                &p, (const int8_t*)src->ptr, src_is_nchw, (const int8_t*)flt->ptr, bias, ch_scales,
+                &fuse, (int8_t*)dst->ptr, MB200_ALGO_AUTO, mb200_opt_stream(opt));
+    }
     if (mb200_conv_s2d_supported(&p)) {
         /* first-layer form; the filter was packed for it by the init function below */
         return (TinyNNStatus)mb200_conv_bias_qs8_s2d(
@@ -176,6 +212,8 @@ TinyNNStatus ${signature} {
             .set("nonline", nonline_code(nonline(ctx)))
             .set("has_bias", bias ? 1 : 0)
             .set("scale_idx", bias ? 3 : 2);
+    const std::string fm = fuse_mode(ctx);
+    s.set("fused", fm.empty() ? 0 : 1).set("fuse_code", fm == "QADD" ? 0 : 1);
     return s.text;
 }
 

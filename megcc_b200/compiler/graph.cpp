@@ -60,6 +60,10 @@ struct GOp {
     std::string mode;  // nonline / pooling mode / elemwise mode / relayout mode
     bool has_bias = false;
     float flt_scale = 1.f;
+    // a fused ElemwiseMultiType step behind a ConvBias: inputs = {src, z}
+    std::string fuse_mode;  // "" | "QADD" | "QFUSE_ADD_RELU"
+    float mid_scale = 1.f;  // scale of the ConvBias result that the fused step consumes
+    int mid_weight = -1;    // 1-element float weight carrying mid_scale to the runtime
 };
 
 struct Compiled {
@@ -112,6 +116,7 @@ struct mb200c_graph {
     std::map<std::string, std::shared_ptr<CodeGenContext>> ctx_of;
     std::string symbols_joined;
     std::vector<Compiled> compiled;
+    bool fuse_conv_elemwise = true;
 
     int add_tensor(const std::string& n, int c, int h, int w, float scale) {
         GTensor t;
@@ -160,8 +165,23 @@ struct mb200c_graph {
                             operand("qsi32", {1, (size_t)dst.c, 1, 1}, src.scale * op.flt_scale));
                 else
                     set_opr(*ctx, "operand:2", operand("qsi32", {}, src.scale * op.flt_scale));
-                set_opr(*ctx, "operand:3", operand("qsi8", shape(op.output), dst.scale));
-                set_i32(*ctx, "nr_operands", 4);
+                if (op.fuse_mode.empty()) {
+                    set_opr(*ctx, "operand:3", operand("qsi8", shape(op.output), dst.scale));
+                    set_i32(*ctx, "nr_operands", 4);
+                } else {
+                    // operand order src, filter, bias, z, dst: the z slot of the reference's
+                    // Conv2DKernel (include/compiler/Dialect/Kernel/IR/AbstractKernels.td:113-118)
+                    set_opr(*ctx, "operand:3",
+                            operand("qsi8", shape(op.inputs[1]), tensors[op.inputs[1]].scale));
+                    set_opr(*ctx, "operand:4", operand("qsi8", shape(op.output), dst.scale));
+                    set_i32(*ctx, "nr_operands", 5);
+                    set_str(*ctx, "fuse_elemwise_mode", op.fuse_mode);
+#ifdef MEGCC_B200_IN_MEGCC_TREE
+                    ctx->setAttr("fuse_mid_scale", CCAttr(op.mid_scale));
+#else
+                    ctx->setFloat("fuse_mid_scale", op.mid_scale);
+#endif
+                }
                 break;
             }
             case OpType::POOL: {
@@ -464,6 +484,16 @@ int mb200c_add_qelemwise(
     return op.output;
 }
 
+int mb200c_set_option(mb200c_graph* g, const char* name, int value) {
+    if (!g || !name)
+        return err("set_option: bad argument");
+    if (strcmp(name, "fuse_conv_elemwise") == 0) {
+        g->fuse_conv_elemwise = value != 0;
+        return 0;
+    }
+    return err("set_option: unknown option '%s'", name);
+}
+
 int mb200c_mark_output(mb200c_graph* g, int tensor) {
     if (!g || !g->valid(tensor))
         return err("mark_output: bad tensor id");
@@ -536,6 +566,55 @@ int mb200c_compile(
             ops.push_back(r);
         }
         work.ops = ops;
+    }
+
+    // ---- fusion: ConvBias (no activation) whose only consumer is a QADD / QFUSE_ADD_RELU
+    // becomes one instruction at the consumer's position; the other operand is z ----
+    if (g->fuse_conv_elemwise) {
+        std::vector<int> uses(work.tensors.size(), 0), producer(work.tensors.size(), -1);
+        for (size_t k = 0; k < work.ops.size(); ++k) {
+            for (int id : work.ops[k].inputs)
+                uses[id]++;
+            producer[work.ops[k].output] = (int)k;
+        }
+        std::vector<char> dead(work.ops.size(), 0);
+        for (size_t k = 0; k < work.ops.size(); ++k) {
+            const GOp q = work.ops[k];
+            if (q.type != OpType::QELEM || q.inputs.size() != 2 ||
+                (q.mode != "QADD" && q.mode != "QFUSE_ADD_RELU"))
+                continue;
+            for (int side = 0; side < 2; ++side) {
+                const int t = q.inputs[side];
+                const int j = producer[t];
+                if (j < 0 || dead[j] || work.ops[j].type != OpType::CONV ||
+                    work.ops[j].mode != "IDENTITY" || !work.ops[j].fuse_mode.empty() ||
+                    uses[t] != 1 || work.tensors[t].is_output)
+                    continue;
+                GOp f = work.ops[j];
+                f.name = work.ops[j].name + "+" + q.name;
+                f.fuse_mode = q.mode;
+                f.mid_scale = work.tensors[t].scale;
+                f.inputs = {work.ops[j].inputs[0], q.inputs[1 - side]};
+                f.output = q.output;
+                GWeight wm;
+                wm.name = f.name + ":mid_scale";
+                wm.dtype = fb::Float32;
+                wm.scale = f.mid_scale;  // read by the kernel stub from the tensor struct
+                wm.dims = {1};
+                wm.data.assign((const uint8_t*)&f.mid_scale, (const uint8_t*)&f.mid_scale + 4);
+                wm.use_count = 1;
+                work.weights.push_back(std::move(wm));
+                f.mid_weight = (int)work.weights.size() - 1;
+                work.ops[k] = f;
+                dead[j] = 1;
+                break;
+            }
+        }
+        std::vector<GOp> kept;
+        for (size_t k = 0; k < work.ops.size(); ++k)
+            if (!dead[k])
+                kept.push_back(work.ops[k]);
+        work.ops = kept;
     }
 
     // ---- kernel selection (first available kernel of the CUDA pack wins) ----
@@ -619,14 +698,25 @@ int mb200c_compile(
             const GOp& op = work.ops[k];
             std::vector<int32_t> in;
             std::vector<int8_t> in_t;
-            for (int id : op.inputs) {
-                in.push_back(id);
+            if (op.type == OpType::CONV) {
+                // operand order src, filter, [bias], [channel scales], [z, mid scale]
+                in.push_back(op.inputs[0]);
                 in_t.push_back(fb::TENSOR);
-            }
-            // operand order src, filter, [bias], [scales]: the filter follows the source
-            for (int wid : op.weights) {
-                in.push_back(wid);
-                in_t.push_back(fb::WEIGHT);
+                for (int wid : op.weights) {
+                    in.push_back(wid);
+                    in_t.push_back(fb::WEIGHT);
+                }
+                if (!op.fuse_mode.empty()) {
+                    in.push_back(op.inputs[1]);
+                    in_t.push_back(fb::TENSOR);
+                    in.push_back(op.mid_weight);
+                    in_t.push_back(fb::WEIGHT);
+                }
+            } else {
+                for (int id : op.inputs) {
+                    in.push_back(id);
+                    in_t.push_back(fb::TENSOR);
+                }
             }
             auto ws = fb::make_table();
             ws->add<int64_t>(fb::field::WS_size, (int64_t)ws_bytes[k]);

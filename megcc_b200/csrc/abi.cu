@@ -87,6 +87,10 @@ static int make_args(const mb200_conv_param* p, int src_is_nchw, ConvArgs* a) {
     a->s_src = p->src_scale;
     a->s_flt = p->flt_scale;
     a->s_dst = p->dst_scale;
+    a->z = nullptr;
+    a->z_mode = 0;
+    a->z_scale = 1.f;
+    a->z_out_scale = 1.f;
     return ST_SUCCESS;
 }
 
@@ -146,10 +150,33 @@ int mb200_conv_pack_filter(
 int mb200_conv_bias_qs8_nhwc(
         const mb200_conv_param* p, const int8_t* src, int src_is_nchw, const int8_t* flt_packed,
         const int32_t* bias, const float* flt_scales, int8_t* dst, int algo, void* stream) {
+    return mb200_conv_bias_qs8_nhwc_fused(
+            p, src, src_is_nchw, flt_packed, bias, flt_scales, nullptr, dst, algo, stream);
+}
+
+int mb200_conv_bias_qs8_nhwc_fused(
+        const mb200_conv_param* p, const int8_t* src, int src_is_nchw, const int8_t* flt_packed,
+        const int32_t* bias, const float* flt_scales, const mb200_conv_fuse* fuse, int8_t* dst,
+        int algo, void* stream) {
     ConvArgs a{};
     int rc = make_args(p, src_is_nchw, &a);
     if (rc)
         return rc;
+    if (fuse) {
+        if (!fuse->z)
+            return set_error(ST_NULL_PTR, "fused operand z is NULL");
+        if (fuse->mode != MB200_QADD && fuse->mode != MB200_QFUSE_ADD_RELU)
+            return set_error(ST_NO_IMPLEMENT, "fused elemwise mode %d not supported", fuse->mode);
+        if (p->nonline != MB200_IDENTITY)
+            return set_error(ST_NO_IMPLEMENT, "a fused elemwise step needs a ConvBias without "
+                                              "activation");
+        if ((uintptr_t)fuse->z & 15)
+            return set_error(ST_INVALID_LAYOUT, "fused operand z must be 16-byte aligned");
+        a.z = fuse->z;
+        a.z_mode = fuse->mode == MB200_QADD ? 1 : 2;
+        a.z_scale = fuse->z_scale;
+        a.z_out_scale = fuse->out_scale;
+    }
     if (!src || !flt_packed || !dst)
         return set_error(ST_NULL_PTR, "conv tensor pointer is NULL");
     cudaStream_t st = (cudaStream_t)stream;

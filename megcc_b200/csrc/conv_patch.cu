@@ -45,6 +45,7 @@ struct PatchParams {
     int tiles_y, tiles_x, m_tiles, n_tiles;
     int stages;
     int a_stage_bytes, a_tx_bytes, b_bytes, plane_stride;
+    int b_single_load;  // the filter map is the 3-D view (one load) rather than 2-D blocks
     int mma_per_tap;  // k-steps per tap (C/32), or 0 when C == 16 (two taps per k-step)
     EpilogueParams ep;
     int8_t* dst;
@@ -111,8 +112,13 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
             // the filter slice, once: one [BN][16-byte] block per 16 bytes of K
             const int kchunks = p.kh * p.kw * p.chunks;
             mbar_expect_tx(b_full, (uint32_t)p.b_bytes);
-            for (int kc = 0; kc < kchunks; ++kc)
-                tma_load_2d(smem_b + kc * (BN * 16), &map_b, b_full, kc * 16, n0);
+            if (p.b_single_load) {
+                // 3-D view {16 bytes, rows, K/16}: one request lays down every block
+                tma_load_3d(smem_b, &map_b, b_full, 0, n0, 0);
+            } else {
+                for (int kc = 0; kc < kchunks; ++kc)
+                    tma_load_2d(smem_b + kc * (BN * 16), &map_b, b_full, kc * 16, n0);
+            }
             int local = 0;
             for (int mt = m_first; mt < p.m_tiles; mt += m_step, ++local) {
                 const int s = local % p.stages;
@@ -228,7 +234,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
             const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
             const int oy = ty * kTH + py, ox = tx * kTW + px;
             const bool valid = oy < p.oh && ox < p.ow;
-            int8_t* out_px = p.dst + (((size_t)img * p.oh + oy) * p.ow + ox) * p.oc;
+            const size_t px_off = (((size_t)img * p.oh + oy) * p.ow + ox) * p.oc;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             // warps 2..5 take the even column chunks of their quarter, warps 6..9 the odd ones
             const int half = (warp - 2) >> 2;
@@ -243,7 +249,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
                 }
                 const int ch0 = n0 + c * 32;
                 if (valid && ch0 < p.oc)
-                    epilogue_store32(v, p.ep, out_px + ch0, ch0);
+                    epilogue_store32(v, p.ep, p.dst, px_off + ch0, ch0);
             }
         }
     }
@@ -334,8 +340,9 @@ int launch_patch(
             grid = cap;
     }
     if (getenv("MB200_DEBUG"))
-        fprintf(stderr, "conv_patch<%d>: per_sm %d grid %d m_tiles %d n_tiles %d smem %d stages %d\n", BN,
-                per_sm, grid, p.m_tiles, p.n_tiles, smem, p.stages);
+        fprintf(stderr, "conv_patch<%d>: per_sm %d grid %d m_tiles %d n_tiles %d smem %d stages %d "
+                "b_single_load %d\n", BN, per_sm, grid, p.m_tiles, p.n_tiles, smem, p.stages,
+                p.b_single_load);
     conv_patch_kernel<BN><<<grid, kThreads, smem, st>>>(ma, mb, p);
     return check_launch("conv_patch");
 }
@@ -394,16 +401,34 @@ int launch_conv_patch(
         if (r != CUDA_SUCCESS)
             return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(activation) failed: %d", (int)r);
     }
+    int b_single_load = 0;
     {
         const cuuint64_t k_total = (cuuint64_t)a.kh * a.kw * a.ic;
-        cuuint64_t dims[2] = {k_total, (cuuint64_t)a.oc};
-        cuuint64_t strides[1] = {k_total};
-        cuuint32_t box[2] = {16, (cuuint32_t)pl.bn};
-        cuuint32_t estr[2] = {1, 1};
-        CUresult r = api.tiled(
-                &map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)flt, dims, strides, box, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const cuuint64_t kchunks = k_total / 16;
+        CUresult r = CUDA_ERROR_INVALID_VALUE;
+        if (kchunks <= 256) {
+            // the packed filter [OC][K] seen as {16 bytes, OC rows (pitch K), K/16 blocks (pitch
+            // 16)}: a box over all blocks arrives as [block][row][16 bytes], the operand layout
+            cuuint64_t dims[3] = {16, (cuuint64_t)a.oc, kchunks};
+            cuuint64_t strides[2] = {k_total, 16};
+            cuuint32_t box[3] = {16, (cuuint32_t)pl.bn, (cuuint32_t)kchunks};
+            cuuint32_t estr[3] = {1, 1, 1};
+            r = api.tiled(
+                    &map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, (void*)flt, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            b_single_load = r == CUDA_SUCCESS;
+        }
+        if (r != CUDA_SUCCESS) {
+            cuuint64_t dims[2] = {k_total, (cuuint64_t)a.oc};
+            cuuint64_t strides[1] = {k_total};
+            cuuint32_t box[2] = {16, (cuuint32_t)pl.bn};
+            cuuint32_t estr[2] = {1, 1};
+            r = api.tiled(
+                    &map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)flt, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        }
         if (r != CUDA_SUCCESS)
             return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(filter) failed: %d", (int)r);
     }
@@ -429,6 +454,7 @@ int launch_conv_patch(
     p.a_tx_bytes = p.chunks * pph * ppw * 16;
     p.plane_stride = pl.plane_stride;
     p.b_bytes = pl.b_bytes;
+    p.b_single_load = b_single_load;
     p.mma_per_tap = a.ic == 16 ? 0 : a.ic / 32;
     p.ep.oc = a.oc;
     p.ep.act = a.act;
@@ -439,6 +465,10 @@ int launch_conv_patch(
     p.ep.inv_dst = 1.0f / a.s_dst;  // correctly rounded on the host
     p.ep.bias = bias;
     p.ep.flt_scales = flt_scales;
+    p.ep.z = a.z;
+    p.ep.z_mode = a.z ? a.z_mode : 0;
+    p.ep.z_scale = a.z_scale;
+    p.ep.z_div = 1.0f / a.z_out_scale;  // the reference's scale_div = 1.f / scale_dst
     p.dst = dst;
     p.status = device_status_word();
     if (!p.status)

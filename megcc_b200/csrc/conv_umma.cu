@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                 }
                 const int ch0 = n0 + c * 32;
                 if (m < p.m_total && ch0 < p.oc)
-                    epilogue_store32(v, p.ep, p.dst + (size_t)m * p.oc + ch0, ch0);
+                    epilogue_store32(v, p.ep, p.dst, (size_t)m * p.oc + ch0, ch0);
             }
         }
     }
@@ -402,6 +402,10 @@ int launch_conv_umma_geom(
     p.ep.inv_dst = 1.0f / a.s_dst;  // correctly rounded on the host
     p.ep.bias = bias;
     p.ep.flt_scales = flt_scales;
+    p.ep.z = a.z;
+    p.ep.z_mode = a.z ? a.z_mode : 0;
+    p.ep.z_scale = a.z_scale;
+    p.ep.z_div = 1.0f / a.z_out_scale;  // the reference's scale_div = 1.f / scale_dst
     p.dst = dst;
     p.status = device_status_word();
     if (!p.status)

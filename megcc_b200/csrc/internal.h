@@ -32,6 +32,11 @@ struct ConvArgs {
     int act;
     int src_is_nchw;
     float s_src, s_flt, s_dst;
+    // optional fused ElemwiseMultiType step after the ConvBias (see conv_epilogue.cuh):
+    // s_dst is then the scale of the ConvBias result, z_out_scale that of the final output
+    const int8_t* z;
+    int z_mode;  // 0 none, 1 QADD, 2 QFUSE_ADD_RELU
+    float z_scale, z_out_scale;
 };
 
 // records a message for mb200_last_error() and returns `code`

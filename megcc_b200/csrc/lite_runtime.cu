@@ -74,6 +74,7 @@ struct OpPlan {
     Workspace ws{nullptr, 0, 0};
     bool needs_init = false;
     bool use_s2d = false;  // first-layer form: space-to-depth + tensor cores
+    int z_mode = 0;        // fused elemwise step: 0 none, else MB200_QADD + 1 / MB200_QFUSE_ADD_RELU + 1
     float ms_total = 0;
     int ms_count = 0;
 };
@@ -189,9 +190,17 @@ bool parse_symbol(const std::string& sym, OpPlan* op) {
         op->dense = strcmp(sparse, "DENSE") == 0;
         if (!op->dense && strcmp(sparse, "GROUP") != 0)
             return false;
-        const std::string rest = sym.substr(used);
+        std::string rest = sym.substr(used);
         if (rest.compare(0, 8, "qsi8qsi8") != 0)
             return false;
+        // a fused elemwise step is spelled last: ..._z_QADD / ..._z_QFUSE_ADD_RELU
+        if (ends_with(rest, "_z_QFUSE_ADD_RELU")) {
+            op->z_mode = MB200_QFUSE_ADD_RELU + 1;
+            rest.resize(rest.size() - strlen("_z_QFUSE_ADD_RELU"));
+        } else if (ends_with(rest, "_z_QADD")) {
+            op->z_mode = MB200_QADD + 1;
+            rest.resize(rest.size() - strlen("_z_QADD"));
+        }
         op->has_bias = rest.find("_bias") != std::string::npos;
         op->mode = ends_with(rest, "_H_SWISH") ? MB200_H_SWISH
                    : ends_with(rest, "_RELU")  ? MB200_RELU
@@ -277,10 +286,25 @@ int run_op(const OpPlan& op, cudaStream_t st) {
             mb200_conv_param p;
             fill_conv_param(op, &p);
             const Tensor* src = op.inputs[0];
+            // inputs: src, filter, [bias], [channel scales], [z, mid scale]
             const size_t scale_idx = op.has_bias ? 3 : 2;
+            const size_t nr_plain = op.inputs.size() - (op.z_mode ? 2 : 0);
             const int32_t* bias = op.has_bias ? (const int32_t*)op.inputs[2]->ptr : nullptr;
             const float* ch =
-                    op.inputs.size() > scale_idx ? (const float*)op.inputs[scale_idx]->ptr : nullptr;
+                    nr_plain > scale_idx ? (const float*)op.inputs[scale_idx]->ptr : nullptr;
+            if (op.z_mode) {
+                const Tensor* z = op.inputs[op.inputs.size() - 2];
+                mb200_conv_fuse fuse;
+                fuse.z = (const int8_t*)z->ptr;
+                fuse.mode = op.z_mode - 1;
+                fuse.z_scale = z->dtype.param.scale;
+                fuse.out_scale = op.outputs[0]->dtype.param.scale;
+                p.dst_scale = op.inputs.back()->dtype.param.scale;  // scale of the ConvBias result
+                return mb200_conv_bias_qs8_nhwc_fused(
+                        &p, (const int8_t*)src->ptr, src->layout.format == TinyNN_NCHW,
+                        (const int8_t*)op.inputs[1]->ptr, bias, ch, &fuse,
+                        (int8_t*)op.outputs[0]->ptr, MB200_ALGO_AUTO, st);
+            }
             if (op.use_s2d)
                 return mb200_conv_bias_qs8_s2d(
                         &p, (const int8_t*)src->ptr, src->layout.format == TinyNN_NCHW,
@@ -520,8 +544,15 @@ int parse_model(Network* net, const void* mem, size_t size) {
                 if (ins.op.inputs.size() < need_in || ins.op.outputs.empty())
                     return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: too few operands", i);
                 if (ins.op.kind == OP_CONV &&
-                    ins.op.inputs.size() < (size_t)(ins.op.has_bias ? 3 : 2))
-                    return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: bias operand missing", i);
+                    ins.op.inputs.size() < (size_t)(ins.op.has_bias ? 3 : 2) + (ins.op.z_mode ? 2 : 0))
+                    return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: conv operand missing", i);
+                if (ins.op.kind == OP_CONV && ins.op.z_mode) {
+                    const Tensor* z = ins.op.inputs[ins.op.inputs.size() - 2];
+                    const Tensor* o = ins.op.outputs[0];
+                    if (z->is_weight || z->size != o->size || !ins.op.inputs.back()->is_weight)
+                        return fail(TinyNN_ERROR_MODEL_PARSE,
+                                    "instruction %u: fused operand does not match the output", i);
+                }
             } else if (tag == fb::INST_MEM_FORWARD) {
                 ins.is_opr = false;
                 const int a = it.scalar<int32_t>(fb::field::MF_input, 0);
@@ -580,7 +611,7 @@ int upload_weights(Network* net) {
     for (auto& pk : packs) {
         mb200_conv_param cp;
         fill_conv_param(*pk.first, &cp);
-        const bool s2d = mb200_conv_s2d_supported(&cp) &&
+        const bool s2d = !pk.first->z_mode && mb200_conv_s2d_supported(&cp) &&
                          pk.first->ws.size >= mb200_conv_s2d_workspace_bytes(&cp);
         pk.first->use_s2d = s2d;
         pack_mode.push_back(s2d ? 1 : 0);

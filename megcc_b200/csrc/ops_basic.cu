@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
     const int icpg = a.ic / a.groups, ocpg = a.oc / a.groups;
     const bool vec4 = !a.src_is_nchw && (icpg % 4 == 0);
     const float inv_dst = __fdiv_rn(1.f, a.s_dst);  // RN(1/d), as the fast division needs
+    const float z_div = __fdiv_rn(1.f, a.z_out_scale);
     for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const int o = (int)(idx % a.oc);
@@ -83,7 +84,16 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
             acc += bias[o];
         if (kRequant) {
             const float sf = flt_scales ? flt_scales[o] : a.s_flt;
-            dst[idx] = (int8_t)requant_conv_fast(acc, a.s_src, sf, a.s_dst, inv_dst, a.act);
+            int q = requant_conv_fast(acc, a.s_src, sf, a.s_dst, inv_dst, a.act);
+            if (a.z_mode != 0 && a.z) {
+                // fused ElemwiseMultiType step (ElemwiseMultiType.cpp:38-46,158)
+                float t = __fadd_rn(__fmul_rn(a.s_dst, __int2float_rn(q)),
+                                    __fmul_rn(a.z_scale, __int2float_rn((int)a.z[idx])));
+                if (a.z_mode == 2)
+                    t = t > 0.f ? t : 0.f;
+                q = fp32_to_int8(__fmul_rn(t, z_div));
+            }
+            dst[idx] = (int8_t)q;
         } else {
             acc_out[idx] = acc;
         }

@@ -41,10 +41,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            // the hint lets the hardware park the thread until the phase completes (or the
+            // time passes) instead of burning issue slots in a software spin
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(smem_u32(bar)), "r"(parity)
+            : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)
             : "memory");
     return ok != 0;
 }
@@ -73,6 +75,15 @@ __device__ __forceinline__ void tma_load_2d(
             "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
             " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem)),
             "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+            : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(
+        void* smem, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem)),
+            "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
             : "memory");
 }
 

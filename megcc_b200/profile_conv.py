@@ -3,7 +3,7 @@
 
 Meant to be run under a profiler, capturing the second round:
 
-    ncu --set full --clock-control none -k regex:conv_umma -s 3 -c 3 \
+    ncu --set full --clock-control none -k regex:conv_ -s 3 -c 3 \
         python -m megcc_b200.profile_conv 32
 """
 import ctypes
@@ -46,7 +46,7 @@ def main(batch=32):
         b = dev(rng.integers(-1000, 1000, (c,), dtype=np.int32))
         d = torch.empty((batch, hw, hw, c), dtype=torch.int8, device="cuda")
         cases.append((name, (lambda pp=pp, s=s, f=f, b=b, d=d: ops.conv_bias_qs8_nhwc(
-            pp, s, f, b, dst=d, algo="umma")), 2.0 * batch * c * hw * hw * c * 9))
+            pp, s, f, b, dst=d, algo="auto")), 2.0 * batch * c * hw * hw * c * 9))
     for rnd in range(2):
         for name, fn, work in cases:
             e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)

@@ -58,6 +58,18 @@ def test_resnet18_matches_oracle(lite, oracle, per_channel):
     assert len(np.unique(want)) > 8
 
 
+def test_resnet18_without_fusion_matches_oracle(lite, oracle):
+    """One instruction per operator (the residual adds as separate kernels)."""
+    from megcc_b200 import zoo
+    spec = zoo.resnet18(seed=2)
+    x = cases.rng_for("resnet18_nofuse").integers(-128, 128, (4, 3, 224, 224), dtype=np.int8)
+    g = spec.to_graph()
+    g.set_option("fuse_conv_elemwise", 0)
+    want = netwalk.run(spec, x, oracle)
+    out = run_model(lite, g.compile([4]), x, want.shape, forwards=2)[1]
+    assert (out == want).all()
+
+
 def test_resnet18_reference_kernels_agree(lite, reference):
     """Same check against the reference's own x86 kernels chained layer by layer."""
     from megcc_b200 import zoo
