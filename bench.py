@@ -212,8 +212,11 @@ def main():
     # ---- device-resident arm: input in HBM, logits stay in HBM ----
     net = lite.Network(model, device_id=local_rank, device_io=("fc:out",))
     stream = torch.cuda.ExternalStream(net.stream())
-    ops_per_step = len([l for l in spec.layers])
+    ops_per_step = None  # counted from the loaded model below
     net.set_input_ptr("data", x_dev.data_ptr(), in_bytes)
+    # kernel launches per step = instructions of the model (+1: the first layer's
+    # space-to-depth kernel), all inside one CUDA graph launch
+    ops_per_step = len(net.profile()) + 1
     sampler = ClockSampler(local_rank).start()
     sampler.wait_first()
     for _ in range(max(args.warmup, 3)):
@@ -281,15 +284,18 @@ def main():
                 k = l["flt"].shape[-1]
                 conv_ops[l["name"]] = 2.0 * BATCH * oc * oh * ow * (ic // l["groups"]) * k * k
         total_ms = sum(r[2] for r in rows)
-        # the tensor-core kernel handles every dense conv whose input channels are a
-        # multiple of 64: all of them except the 3-channel stem
-        umma = [(n, ms) for n, s, ms, c in rows if n in conv_ops and n != "stem" and c]
+        # every ConvBias of this network runs on the tcgen05 kernels (the 3-channel first layer
+        # after its space-to-depth step)
+        # an instruction named "a+b" is ConvBias a with the elementwise b fused behind it
+        conv_of = lambda n: n.split("+")[0]
+        umma = [(conv_of(n), ms) for n, s, ms, c in rows if conv_of(n) in conv_ops and c]
         umma_ops = sum(conv_ops[n] for n, _ in umma)
         umma_ms = sum(ms for _, ms in umma)
         peak = 2.0 * peaks["bf16_sustained"]
         achieved = umma_ops / (umma_ms * 1e-3) / 1e12 if umma_ms > 0 else 0.0
         roofline = dict(
-            bound="tensor", kernel="conv_umma_kernel (tcgen05 kind::i8 implicit GEMM)",
+            bound="tensor",
+            kernel="conv_umma_kernel / conv_patch_kernel (tcgen05 kind::i8 implicit GEMM)",
             achieved=achieved, peak=peak, unit="TOP/s", frac=achieved / peak, traffic=None,
             launches_per_step=len(umma), share_of_step=umma_ms / total_ms if total_ms else None,
             peak_note=f"2 x bf16 sustained ({peaks['source']}); int8 dense peak is not in "
