@@ -35,13 +35,21 @@ using namespace umma;
 namespace {
 
 constexpr int kBM = 128;     // output pixels per tile (UMMA M)
-constexpr int kBK = 64;      // K bytes per pipeline stage
+constexpr int kBK = 64;      // K bytes per pipeline stage of the 64-byte geometries
 constexpr int kUmmaK = 32;   // K per tcgen05.mma kind::i8
 constexpr int kStages = 6;
 constexpr int kEpilogueWarps = 8;  // two per TMEM lane quarter, splitting the column chunks
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kEpilogueThreads = 32 * kEpilogueWarps;
-enum Geometry : int { GEOM_WIDE = 0, GEOM_TAP16 = 1 };
+enum Geometry : int { GEOM_WIDE = 0, GEOM_TAP16 = 1, GEOM_WIDE128 = 2 };
+
+// K bytes and pipeline depth per geometry. WIDE128 moves 128-channel rows (128-byte swizzle):
+// half as many TMA requests and barrier round trips per byte as WIDE.
+template <int GEOM>
+struct Geom {
+    static constexpr int kBKg = GEOM == GEOM_WIDE128 ? 128 : 64;
+    static constexpr int kStagesG = GEOM == GEOM_WIDE128 ? 3 : kStages;
+};
 
 struct UmmaConvParams {
     int m_total, oc, oh, ow;
@@ -57,11 +65,11 @@ struct UmmaConvParams {
     int* status;
 };
 
-template <int BN>
+template <int BN, int GEOM>
 struct SmemLayout {
-    static constexpr int kABytes = kBM * kBK;
-    static constexpr int kBBytes = BN * kBK;
-    static constexpr int kTiles = kStages * (kABytes + kBBytes);
+    static constexpr int kABytes = kBM * Geom<GEOM>::kBKg;
+    static constexpr int kBBytes = BN * Geom<GEOM>::kBKg;
+    static constexpr int kTiles = Geom<GEOM>::kStagesG * (kABytes + kBBytes);
     // after the tiles: full[kStages], empty[kStages], acc_full[2], acc_empty[2], drain
     static constexpr int kBarOff = kTiles;
     static constexpr int kTotal = kBarOff + (2 * kStages + 5) * 8 + 16;
@@ -72,11 +80,13 @@ template <int BN, int GEOM>
 __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const UmmaConvParams p) {
-    using L = SmemLayout<BN>;
+    using L = SmemLayout<BN, GEOM>;
+    constexpr int kBKc = Geom<GEOM>::kBKg;
+    constexpr int kSt = Geom<GEOM>::kStagesG;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles_a = smem;
-    uint8_t* tiles_b = smem + kStages * L::kABytes;
+    uint8_t* tiles_b = smem + kSt * L::kABytes;
     uint64_t* full_bar = (uint64_t*)(smem + L::kBarOff);
     uint64_t* empty_bar = full_bar + kStages;
     uint64_t* acc_full = empty_bar + kStages;  // [2]
@@ -127,8 +137,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                 const int oy = rem / p.ow, ox = rem - oy * p.ow;
                 const int base_w = ox * p.sw + p.base_w, base_h = oy * p.sh + p.base_h;
                 for (int it = 0; it < p.k_iters; ++it, ++it_global) {
-                    const int s = it_global % kStages;
-                    const uint32_t phase = (uint32_t)(it_global / kStages) & 1u;
+                    const int s = it_global % kSt;
+                    const uint32_t phase = (uint32_t)(it_global / kSt) & 1u;
                     if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) {
                         if (!*abort_flag) {
                             *abort_flag = 1;
@@ -140,12 +150,12 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                     mbar_expect_tx(&full_bar[s], (uint32_t)(L::kABytes + L::kBBytes));
                     uint8_t* sa = tiles_a + s * L::kABytes;
                     uint8_t* sb = tiles_b + s * L::kBBytes;
-                    if (GEOM == GEOM_WIDE) {
+                    if (GEOM != GEOM_TAP16) {
                         const int tap = it / p.cblocks, cb = it - tap * p.cblocks;
                         const int fy = tap / p.taps_w, fx = tap - fy * p.taps_w;
-                        tma_load_im2col_4d(sa, &map_a, &full_bar[s], cb * kBK, base_w, base_h, img,
+                        tma_load_im2col_4d(sa, &map_a, &full_bar[s], cb * kBKc, base_w, base_h, img,
                                            (uint16_t)(fx * p.dw), (uint16_t)(fy * p.dh));
-                        tma_load_2d(sb, &map_b, &full_bar[s], it * kBK, n0);
+                        tma_load_2d(sb, &map_b, &full_bar[s], it * kBKc, n0);
                     } else {
 #pragma unroll
                         for (int t = 0; t < 4; ++t) {
@@ -180,8 +190,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
                 for (int it = 0; it < p.k_iters; ++it, ++it_global) {
-                    const int s = it_global % kStages;
-                    const uint32_t phase = (uint32_t)(it_global / kStages) & 1u;
+                    const int s = it_global % kSt;
+                    const uint32_t phase = (uint32_t)(it_global / kSt) & 1u;
                     if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
                         if (!*abort_flag) {
                             *abort_flag = 1;
@@ -194,9 +204,13 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                     const uint32_t a_addr = smem_u32(tiles_a + s * L::kABytes);
                     const uint32_t b_addr = smem_u32(tiles_b + s * L::kBBytes);
 #pragma unroll
-                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                    for (int k = 0; k < kBKc / kUmmaK; ++k) {
                         uint64_t adesc, bdesc;
-                        if (GEOM == GEOM_WIDE) {
+                        if (GEOM == GEOM_WIDE128) {
+                            // 128-byte swizzle: 8-row groups 1024 bytes apart
+                            adesc = umma_smem_desc(a_addr + k * 32, 16, 1024, 2);
+                            bdesc = umma_smem_desc(b_addr + k * 32, 16, 1024, 2);
+                        } else if (GEOM == GEOM_WIDE) {
                             // 64-byte swizzle; +32 bytes along K inside the swizzled row
                             adesc = umma_smem_desc(a_addr + k * 32, 16, 512, 4);
                             bdesc = umma_smem_desc(b_addr + k * 32, 16, 512, 4);
@@ -288,19 +302,19 @@ int launch_kernel(
         const CUtensorMap& ma, const CUtensorMap& mb, const UmmaConvParams& p, cudaStream_t st) {
     if (cudaFuncSetAttribute(
                 conv_umma_kernel<BN, GEOM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                SmemLayout<BN>::kDynamic) != cudaSuccess)
+                SmemLayout<BN, GEOM>::kDynamic) != cudaSuccess)
         return check_launch("conv_umma smem attribute");
     // persistent CTAs: as many as the SM holds at once
     const int per_sm = resident_ctas_per_sm(
-            conv_umma_kernel<BN, GEOM>, kThreads, SmemLayout<BN>::kDynamic, 2 * BN);
+            conv_umma_kernel<BN, GEOM>, kThreads, SmemLayout<BN, GEOM>::kDynamic, 2 * BN);
     const int total = p.m_tiles * p.n_tiles;
     int grid = sm_count() * per_sm;
     if (grid > total)
         grid = total;
     if (getenv("MB200_DEBUG"))
         fprintf(stderr, "conv_umma<%d,%d>: per_sm %d grid %d tiles %d smem %d\n", BN, GEOM, per_sm, grid,
-                total, SmemLayout<BN>::kDynamic);
-    conv_umma_kernel<BN, GEOM><<<grid, kThreads, SmemLayout<BN>::kDynamic, st>>>(ma, mb, p);
+                total, SmemLayout<BN, GEOM>::kDynamic);
+    conv_umma_kernel<BN, GEOM><<<grid, kThreads, SmemLayout<BN, GEOM>::kDynamic, st>>>(ma, mb, p);
     return check_launch("conv_umma");
 }
 
@@ -331,8 +345,9 @@ bool conv_umma_supported(
 //           tap count a multiple of 4; `a` then describes that transformed convolution, with
 //           a.ph/a.pw the LOW padding and a.oh/a.ow the output extent)
 int launch_conv_umma_geom(
-        const ConvArgs& a, int geom, const int8_t* src, const int8_t* flt, const int32_t* bias,
+        const ConvArgs& a, int geom_in, const int8_t* src, const int8_t* flt, const int32_t* bias,
         const float* flt_scales, int8_t* dst, cudaStream_t st) {
+    int geom = geom_in;
     const DriverApi& api = driver_api();
     if (!api.ok)
         return set_error(ST_RUNTIME, "cuTensorMapEncode* entry points not found in the driver");
@@ -343,9 +358,13 @@ int launch_conv_umma_geom(
     if (((uintptr_t)bias & 15) || ((uintptr_t)flt_scales & 15))
         return set_error(ST_INVALID_LAYOUT, "bias and channel scales must be 16-byte aligned");
 
-    const int chans = geom == GEOM_WIDE ? kBK : 16;
-    const CUtensorMapSwizzle swz =
-            geom == GEOM_WIDE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE;
+    // 128-channel rows whenever the channel count allows: fewer, larger TMA requests
+    if (geom == GEOM_WIDE && a.ic % 128 == 0 && !getenv("MB200_NO_WIDE128"))
+        geom = GEOM_WIDE128;
+    const int chans = geom == GEOM_WIDE128 ? 128 : geom == GEOM_WIDE ? kBK : 16;
+    const CUtensorMapSwizzle swz = geom == GEOM_WIDE128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                   : geom == GEOM_WIDE  ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                        : CU_TENSOR_MAP_SWIZZLE_NONE;
     CUtensorMap map_a, map_b;
     {
         cuuint64_t dims[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw, (cuuint64_t)a.ih,
@@ -382,9 +401,9 @@ int launch_conv_umma_geom(
     p.oc = a.oc;
     p.oh = a.oh;
     p.ow = a.ow;
-    p.cblocks = geom == GEOM_WIDE ? a.ic / kBK : 1;
+    p.cblocks = geom == GEOM_TAP16 ? 1 : a.ic / chans;
     p.taps_w = a.kw;
-    p.k_iters = geom == GEOM_WIDE ? taps * p.cblocks : taps / 4;
+    p.k_iters = geom == GEOM_TAP16 ? taps / 4 : taps * p.cblocks;
     p.sh = a.sh;
     p.sw = a.sw;
     p.base_h = -a.ph;
@@ -410,6 +429,9 @@ int launch_conv_umma_geom(
     p.status = device_status_word();
     if (!p.status)
         return ST_MALLOC;
+    if (geom == GEOM_WIDE128)
+        return bn == 64 ? launch_kernel<64, GEOM_WIDE128>(map_a, map_b, p, st)
+                        : launch_kernel<128, GEOM_WIDE128>(map_a, map_b, p, st);
     if (geom == GEOM_WIDE)
         return bn == 64 ? launch_kernel<64, GEOM_WIDE>(map_a, map_b, p, st)
                         : launch_kernel<128, GEOM_WIDE>(map_a, map_b, p, st);
