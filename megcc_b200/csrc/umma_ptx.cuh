@@ -52,15 +52,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait. Returns false when the limit ran out or another role already gave up.
+// After a few immediate retries the thread sleeps between polls (64 ns doubling to 512 ns):
+// a role that waits for most of the kernel (the producer and the MMA issuer when the
+// epilogue is the slow stage) would otherwise spend the SM's issue slots on its polling loop.
 __device__ __forceinline__ bool mbar_wait(
         uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity))
-        return true;
+#pragma unroll 1
+    for (int i = 0; i < 4; ++i)
+        if (mbar_try_wait(bar, parity))
+            return true;
     const long long t0 = clock64();
+    unsigned ns = 64;
     for (int spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity))
             return true;
-        if ((spin & 255) == 255) {
+        __nanosleep(ns);
+        if (ns < 512)
+            ns *= 2;
+        if ((spin & 63) == 63) {
             if (*abort_flag)
                 return false;
             if (clock64() - t0 > kWaitCycles)
