@@ -139,6 +139,21 @@ MB200_API int mb200_conv_acc_qs8_nhwc(
         const mb200_conv_param* p, const int8_t* src, const int8_t* flt_packed,
         const int32_t* bias, int32_t* acc, void* stream);
 
+/* ---- MatrixMul int8 x int8 -> int32 (C = A[M][K] * B[K][N], row-major), and the same with
+ * the int32 product requantised to qint8 by the TypeCvt rule val * acc_scale / dst_scale
+ * (compiler/lib/KernelGen/BareMetal/Typecvt.cpp:91-96). The reference has an int8 MatrixMul
+ * only for Arm (compiler/lib/KernelGen/Arm/Arm64/MatMulKernel/Int8DotMatMulM8N12K4.cpp:20-31)
+ * and none for x86 (BareMetal/MatrixMul.cpp:13-23 admits f32/f16), so the arithmetic follows
+ * the exact integer definition. B is re-laid once to K-major rows (k*n bytes) by
+ * mb200_matmul_pack_b, as a weight's Init step would. Runs on the tensor cores when
+ * k % 64 == 0 and A holds at least 128 KiB. ---- */
+MB200_API int mb200_matmul_pack_b(int k, int n, const int8_t* b, int8_t* b_packed, void* stream);
+MB200_API int mb200_matmul_s8_s32(
+        int m, int n, int k, const int8_t* a, const int8_t* b_packed, int32_t* c, void* stream);
+MB200_API int mb200_matmul_s8_qs8(
+        int m, int n, int k, const int8_t* a, const int8_t* b_packed, int8_t* c, float acc_scale,
+        float dst_scale, void* stream);
+
 /* ---- Pooling qint8 (kernel_pooling_<MODE>_NCHW_p.._s.._w.._qsi8qsi8,
  * compiler/lib/KernelGen/BareMetal/Pooling.cpp:166-273), NHWC in/out ---- */
 MB200_API int mb200_pooling_qs8_nhwc(

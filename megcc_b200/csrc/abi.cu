@@ -91,6 +91,7 @@ static int make_args(const mb200_conv_param* p, int src_is_nchw, ConvArgs* a) {
     a->z_mode = 0;
     a->z_scale = 1.f;
     a->z_out_scale = 1.f;
+    a->acc_out = nullptr;
     return ST_SUCCESS;
 }
 
@@ -326,6 +327,70 @@ int mb200_conv_bias_qs8_nchw(
     if ((rc = mb200_conv_bias_qs8_nhwc(p, ws_src, 0, ws_flt, bias, flt_scales, ws_dst, algo, st)))
         return rc;
     return launch_transpose_s8(ws_dst, dst, a.n, a.oh * a.ow, a.oc, st);
+}
+
+// ---- int8 matrix product: a 1x1 ConvBias over M "pixels" with K channels ----
+static int matmul_args(int m, int n, int k, ConvArgs* a) {
+    if (m <= 0 || n <= 0 || k <= 0)
+        return set_error(ST_INVALID_LAYOUT, "matmul extents must be positive");
+    mb200_conv_param p;
+    memset(&p, 0, sizeof(p));
+    p.n = m;
+    p.ic = k;
+    p.ih = p.iw = 1;
+    p.oc = n;
+    p.kh = p.kw = 1;
+    p.stride_h = p.stride_w = p.dilate_h = p.dilate_w = 1;
+    p.groups = 1;
+    p.nonline = MB200_IDENTITY;
+    p.src_scale = p.flt_scale = p.dst_scale = 1.f;
+    return make_args(&p, 0, a);
+}
+
+int mb200_matmul_pack_b(int k, int n, const int8_t* b, int8_t* b_packed, void* stream) {
+    if (!b || !b_packed)
+        return set_error(ST_NULL_PTR, "matmul operand pointer is NULL");
+    if (k <= 0 || n <= 0)
+        return set_error(ST_INVALID_LAYOUT, "matmul extents must be positive");
+    // [K][N] row-major -> [N][K]: K-major rows, the layout the filter of a 1x1 conv has
+    return launch_transpose_s8(b, b_packed, 1, k, n, (cudaStream_t)stream);
+}
+
+int mb200_matmul_s8_s32(
+        int m, int n, int k, const int8_t* a, const int8_t* b_packed, int32_t* c, void* stream) {
+    ConvArgs args{};
+    int rc = matmul_args(m, n, k, &args);
+    if (rc)
+        return rc;
+    if (!a || !b_packed || !c)
+        return set_error(ST_NULL_PTR, "matmul operand pointer is NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (conv_umma_supported(args, a, b_packed, (const int8_t*)c)) {
+        args.acc_out = c;
+        return launch_conv_umma(args, a, b_packed, nullptr, nullptr, (int8_t*)c, st);
+    }
+    return launch_conv_direct(args, a, b_packed, nullptr, nullptr, nullptr, c, st);
+}
+
+int mb200_matmul_s8_qs8(
+        int m, int n, int k, const int8_t* a, const int8_t* b_packed, int8_t* c, float acc_scale,
+        float dst_scale, void* stream) {
+    ConvArgs args{};
+    int rc = matmul_args(m, n, k, &args);
+    if (rc)
+        return rc;
+    if (!a || !b_packed || !c)
+        return set_error(ST_NULL_PTR, "matmul operand pointer is NULL");
+    // requantisation of the int32 product by the TypeCvt rule val * src_scale / dst_scale:
+    // the ConvBias form acc * s_src * s_flt / s_dst with s_flt = 1 (a multiplication by 1.0f
+    // is exact), so both are the same float operations in the same order
+    args.s_src = acc_scale;
+    args.s_flt = 1.f;
+    args.s_dst = dst_scale;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (conv_umma_supported(args, a, b_packed, c))
+        return launch_conv_umma(args, a, b_packed, nullptr, nullptr, c, st);
+    return launch_conv_direct(args, a, b_packed, nullptr, nullptr, c, nullptr, st);
 }
 
 int mb200_pooling_qs8_nhwc(

@@ -25,6 +25,9 @@ struct EpilogueParams {
     const int8_t* z;
     int z_mode;  // 0 none, 1 QADD, 2 QFUSE_ADD_RELU
     float z_scale, z_div;
+    // when set, the int32 accumulators (+ bias) are stored here instead of the int8 result
+    // (same [pixel][channel] indexing); used by the int8 -> int32 matrix product
+    int32_t* acc_out;
 };
 
 // host: is |(float)acc * s_src * s_flt / s_dst| < 2^30 for every int32 acc?
@@ -53,6 +56,78 @@ __device__ __forceinline__ int requant_one(
     return q;
 }
 
+// ---- two floats per instruction (sm_100 f32x2 forms; each half is the IEEE RN operation) ----
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// the constants of one requantisation, each duplicated into both halves
+struct RequantPair {
+    uint64_t s_src, s_flt, neg_dst, inv_dst, half;
+    __device__ __forceinline__ explicit RequantPair(const EpilogueParams& e)
+            : s_src(f2_pack(e.s_src, e.s_src)),
+              s_flt(f2_pack(e.s_flt, e.s_flt)),
+              neg_dst(f2_pack(-e.s_dst, -e.s_dst)),
+              inv_dst(f2_pack(e.inv_dst, e.inv_dst)),
+              half(f2_pack(0.49999997f, 0.49999997f)) {}
+};
+
+// Bounded, per-tensor requantisation of two accumulators: the float operations of
+// requant_one<ACT, true> on both halves at once. With RELU the max is NOT applied here: the
+// caller clears negative bytes after packing (a value below zero rounds to something <= 0
+// either way, and max(., 0) commutes with the monotonic round-and-saturate).
+template <int ACT>
+__device__ __forceinline__ void requant_pair(
+        int acc0, int acc1, const RequantPair& c, int& q0, int& q1) {
+    const uint64_t f = f2_pack(__int2float_rn(acc0), __int2float_rn(acc1));
+    const uint64_t t = f2_mul(f2_mul(f, c.s_src), c.s_flt);
+    // t / s_dst correctly rounded (div_rn_by_const); fma(-q, d, t) == fma(q, -d, t)
+    const uint64_t qa = f2_mul(t, c.inv_dst);
+    const uint64_t rem = f2_fma(qa, c.neg_dst, t);
+    const uint64_t x = f2_fma(rem, c.inv_dst, qa);
+    uint64_t y;
+    if (ACT == ACT_RELU) {
+        y = f2_add(x, c.half);
+    } else {
+        float x0, x1;
+        f2_unpack(x, x0, x1);
+        y = f2_add(x, f2_pack(copysignf(0.49999997f, x0), copysignf(0.49999997f, x1)));
+    }
+    float y0, y1;
+    f2_unpack(y, y0, y1);
+    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(y0));
+    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(y1));
+}
+
+// four packed int8: bytes below zero become zero (byte-wise sign masks from PRMT)
+__device__ __forceinline__ uint32_t relu_s8x4(uint32_t p) {
+    // selector nibbles 8..B: bytes 0..3 with bit 3 set, which replicates the byte's sign bit
+    // (the __byte_perm intrinsic masks that bit off, hence the instruction itself)
+    uint32_t neg;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(neg) : "r"(p), "r"(0u), "r"(0xBA98u));
+    return p & ~neg;
+}
+
 // conv (already int8, as int) combined with one z value
 template <int ZMODE>
 __device__ __forceinline__ int fuse_z(int conv_q, int zv, const EpilogueParams& e) {
@@ -70,24 +145,72 @@ __device__ __forceinline__ int fuse_z(int conv_q, int zv, const EpilogueParams& 
     return q;
 }
 
-template <int ACT, bool PER_CHANNEL, bool BOUNDED, int ZMODE>
-__device__ __forceinline__ void epilogue_store32_t(
-        const uint32_t (&v)[32], const EpilogueParams& e, int8_t* out, const int8_t* zin,
+// fuse_z on two values at once (same float operations, both halves)
+template <int ZMODE>
+__device__ __forceinline__ void fuse_z_pair(
+        int& q0, int& q1, int z0, int z1, uint64_t s_dst2, uint64_t z_scale2, uint64_t z_div2) {
+    const uint64_t a = f2_mul(s_dst2, f2_pack(__int2float_rn(q0), __int2float_rn(q1)));
+    const uint64_t b = f2_mul(z_scale2, f2_pack(__int2float_rn(z0), __int2float_rn(z1)));
+    uint64_t t = f2_add(a, b);
+    if (ZMODE == 2) {
+        float t0, t1;
+        f2_unpack(t, t0, t1);
+        t = f2_pack(t0 > 0.f ? t0 : 0.f, t1 > 0.f ? t1 : 0.f);
+    }
+    const uint64_t x = f2_mul(t, z_div2);
+    float x0, x1;
+    f2_unpack(x, x0, x1);
+    const uint64_t y =
+            f2_add(x, f2_pack(copysignf(0.49999997f, x0), copysignf(0.49999997f, x1)));
+    float y0, y1;
+    f2_unpack(y, y0, y1);
+    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(y0));
+    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(y1));
+}
+
+// NV = 16 or 32 accumulators (consecutive channels from ch0) of one output pixel
+template <int NV, int ACT, bool PER_CHANNEL, bool BOUNDED, int ZMODE>
+__device__ __forceinline__ void epilogue_store_t(
+        const uint32_t (&v)[NV], const EpilogueParams& e, int8_t* out, const int8_t* zin,
         int ch0) {
-    if (ch0 + 32 <= e.oc && (e.oc % 16) == 0) {
-        uint32_t packed[8];
-        uint32_t zw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (ZMODE != 0) {
-            const uint4 z0 = __ldg(reinterpret_cast<const uint4*>(zin));
-            const uint4 z1 = __ldg(reinterpret_cast<const uint4*>(zin) + 1);
-            zw[0] = z0.x; zw[1] = z0.y; zw[2] = z0.z; zw[3] = z0.w;
-            zw[4] = z1.x; zw[5] = z1.y; zw[6] = z1.z; zw[7] = z1.w;
-        }
+    static_assert(NV == 16 || NV == 32, "16 or 32 channels per call");
+    if (ch0 + NV <= e.oc && (e.oc % 16) == 0) {
+        uint32_t packed[NV / 4];
+        uint32_t zw[NV / 4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < NV / 4; ++j)
+            zw[j] = 0;
+        if (ZMODE != 0) {
+#pragma unroll
+            for (int h = 0; h < NV / 16; ++h) {
+                const uint4 z0 = __ldg(reinterpret_cast<const uint4*>(zin) + h);
+                zw[h * 4 + 0] = z0.x; zw[h * 4 + 1] = z0.y; zw[h * 4 + 2] = z0.z; zw[h * 4 + 3] = z0.w;
+            }
+        }
+        constexpr bool kPaired = BOUNDED && !PER_CHANNEL && ACT != ACT_H_SWISH;
+        static_assert(ZMODE == 0 || ACT == ACT_IDENTITY, "the fused step follows a plain ConvBias");
+        const RequantPair rp(e);
+        const uint64_t s_dst2 = f2_pack(e.s_dst, e.s_dst), z_scale2 = f2_pack(e.z_scale, e.z_scale),
+                       z_div2 = f2_pack(e.z_div, e.z_div);
+#pragma unroll
+        for (int j = 0; j < NV / 4; ++j) {
             int4 b = make_int4(0, 0, 0, 0);
             if (e.bias)
                 b = __ldg(reinterpret_cast<const int4*>(e.bias + ch0) + j);
+            if (kPaired) {
+                int r0, r1, r2, r3;
+                requant_pair<ACT>((int)v[j * 4 + 0] + b.x, (int)v[j * 4 + 1] + b.y, rp, r0, r1);
+                requant_pair<ACT>((int)v[j * 4 + 2] + b.z, (int)v[j * 4 + 3] + b.w, rp, r2, r3);
+                if (ZMODE != 0) {
+                    fuse_z_pair<ZMODE>(r0, r1, (int)(int8_t)(zw[j]), (int)(int8_t)(zw[j] >> 8),
+                                       s_dst2, z_scale2, z_div2);
+                    fuse_z_pair<ZMODE>(r2, r3, (int)(int8_t)(zw[j] >> 16),
+                                       (int)(int8_t)(zw[j] >> 24), s_dst2, z_scale2, z_div2);
+                }
+                const uint32_t pk = umma::pack4_prmt(r0, r1, r2, r3);
+                packed[j] = (ACT == ACT_RELU && ZMODE == 0) ? relu_s8x4(pk) : pk;
+                continue;
+            }
             float4 s = make_float4(e.s_flt, e.s_flt, e.s_flt, e.s_flt);
             if (PER_CHANNEL)
                 s = __ldg(reinterpret_cast<const float4*>(e.flt_scales + ch0) + j);
@@ -107,13 +230,15 @@ __device__ __forceinline__ void epilogue_store32_t(
             }
             packed[j] = umma::pack4_prmt(r0, r1, r2, r3);
         }
-        reinterpret_cast<uint4*>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        reinterpret_cast<uint4*>(out)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+#pragma unroll
+        for (int h = 0; h < NV / 16; ++h)
+            reinterpret_cast<uint4*>(out)[h] = make_uint4(
+                    packed[h * 4 + 0], packed[h * 4 + 1], packed[h * 4 + 2], packed[h * 4 + 3]);
     } else {
         // ragged channel tail, or a channel count that rules out vector stores (fully
         // unrolled with a predicate so the accumulators stay in registers)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < NV; ++i) {
             if (ch0 + i < e.oc) {
                 const int acc = (int)v[i] + (e.bias ? e.bias[ch0 + i] : 0);
                 const float s = PER_CHANNEL ? e.flt_scales[ch0 + i] : e.s_flt;
@@ -129,8 +254,29 @@ __device__ __forceinline__ void epilogue_store32_t(
 // run-time dispatch on (activation, per-channel scales, bounded, fused step); uniform across
 // the CTA. `off` is the element offset of the pixel's first channel of this chunk in the
 // output tensor (and in z, which has the same shape).
-__device__ __forceinline__ void epilogue_store32(
-        const uint32_t (&v)[32], const EpilogueParams& e, int8_t* dst, size_t off, int ch0) {
+template <int NV>
+__device__ __forceinline__ void epilogue_store(
+        const uint32_t (&v)[NV], const EpilogueParams& e, int8_t* dst, size_t off, int ch0) {
+    if (e.acc_out) {
+        int32_t* o = e.acc_out + off;
+        if (ch0 + NV <= e.oc && (e.oc % 4) == 0) {
+#pragma unroll
+            for (int j = 0; j < NV / 4; ++j) {
+                int4 b = make_int4(0, 0, 0, 0);
+                if (e.bias)
+                    b = __ldg(reinterpret_cast<const int4*>(e.bias + ch0) + j);
+                reinterpret_cast<int4*>(o)[j] =
+                        make_int4((int)v[j * 4 + 0] + b.x, (int)v[j * 4 + 1] + b.y,
+                                  (int)v[j * 4 + 2] + b.z, (int)v[j * 4 + 3] + b.w);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                if (ch0 + i < e.oc)
+                    o[i] = (int)v[i] + (e.bias ? e.bias[ch0 + i] : 0);
+        }
+        return;
+    }
     int8_t* out = dst + off;
     const bool pc = e.flt_scales != nullptr;
     if (e.z_mode != 0) {
@@ -138,42 +284,42 @@ __device__ __forceinline__ void epilogue_store32(
         const int8_t* zin = e.z + off;
         if (e.z_mode == 1) {
             if (pc)
-                epilogue_store32_t<ACT_IDENTITY, true, false, 1>(v, e, out, zin, ch0);
+                epilogue_store_t<NV, ACT_IDENTITY, true, false, 1>(v, e, out, zin, ch0);
             else if (e.bounded)
-                epilogue_store32_t<ACT_IDENTITY, false, true, 1>(v, e, out, zin, ch0);
+                epilogue_store_t<NV, ACT_IDENTITY, false, true, 1>(v, e, out, zin, ch0);
             else
-                epilogue_store32_t<ACT_IDENTITY, false, false, 1>(v, e, out, zin, ch0);
+                epilogue_store_t<NV, ACT_IDENTITY, false, false, 1>(v, e, out, zin, ch0);
         } else {
             if (pc)
-                epilogue_store32_t<ACT_IDENTITY, true, false, 2>(v, e, out, zin, ch0);
+                epilogue_store_t<NV, ACT_IDENTITY, true, false, 2>(v, e, out, zin, ch0);
             else if (e.bounded)
-                epilogue_store32_t<ACT_IDENTITY, false, true, 2>(v, e, out, zin, ch0);
+                epilogue_store_t<NV, ACT_IDENTITY, false, true, 2>(v, e, out, zin, ch0);
             else
-                epilogue_store32_t<ACT_IDENTITY, false, false, 2>(v, e, out, zin, ch0);
+                epilogue_store_t<NV, ACT_IDENTITY, false, false, 2>(v, e, out, zin, ch0);
         }
         return;
     }
     if (e.bounded && !pc) {
         switch (e.act) {
             case ACT_IDENTITY:
-                epilogue_store32_t<ACT_IDENTITY, false, true, 0>(v, e, out, nullptr, ch0);
+                epilogue_store_t<NV, ACT_IDENTITY, false, true, 0>(v, e, out, nullptr, ch0);
                 break;
             case ACT_RELU:
-                epilogue_store32_t<ACT_RELU, false, true, 0>(v, e, out, nullptr, ch0);
+                epilogue_store_t<NV, ACT_RELU, false, true, 0>(v, e, out, nullptr, ch0);
                 break;
             default:
-                epilogue_store32_t<ACT_H_SWISH, false, true, 0>(v, e, out, nullptr, ch0);
+                epilogue_store_t<NV, ACT_H_SWISH, false, true, 0>(v, e, out, nullptr, ch0);
                 break;
         }
         return;
     }
     switch (e.act * 2 + (pc ? 1 : 0)) {
-        case 0: epilogue_store32_t<ACT_IDENTITY, false, false, 0>(v, e, out, nullptr, ch0); break;
-        case 1: epilogue_store32_t<ACT_IDENTITY, true, false, 0>(v, e, out, nullptr, ch0); break;
-        case 2: epilogue_store32_t<ACT_RELU, false, false, 0>(v, e, out, nullptr, ch0); break;
-        case 3: epilogue_store32_t<ACT_RELU, true, false, 0>(v, e, out, nullptr, ch0); break;
-        case 4: epilogue_store32_t<ACT_H_SWISH, false, false, 0>(v, e, out, nullptr, ch0); break;
-        default: epilogue_store32_t<ACT_H_SWISH, true, false, 0>(v, e, out, nullptr, ch0); break;
+        case 0: epilogue_store_t<NV, ACT_IDENTITY, false, false, 0>(v, e, out, nullptr, ch0); break;
+        case 1: epilogue_store_t<NV, ACT_IDENTITY, true, false, 0>(v, e, out, nullptr, ch0); break;
+        case 2: epilogue_store_t<NV, ACT_RELU, false, false, 0>(v, e, out, nullptr, ch0); break;
+        case 3: epilogue_store_t<NV, ACT_RELU, true, false, 0>(v, e, out, nullptr, ch0); break;
+        case 4: epilogue_store_t<NV, ACT_H_SWISH, false, false, 0>(v, e, out, nullptr, ch0); break;
+        default: epilogue_store_t<NV, ACT_H_SWISH, true, false, 0>(v, e, out, nullptr, ch0); break;
     }
 }
 

@@ -5,7 +5,8 @@
 // pixel is requested nine times and the filter tile again for every output tile, and the
 // request rate of the TMA unit becomes the limit. Here an output tile is a 16 (rows) x 8
 // (columns) patch of one image, and its whole input neighbourhood, (16+KH-1) x (8+KW-1)
-// pixels of all input channels, is brought in ONCE as planes of 16-channel chunks:
+// pixels of all input channels, is brought in ONCE, by one TMA request, as planes of
+// 16-channel chunks:
 //
 //     A stage  = [chunk = C/16][patch row][patch column][16 bytes]
 //
@@ -13,8 +14,10 @@
 // 16 bytes apart: 8 horizontally adjacent pixels of one chunk plane are exactly that, and
 // the next output row is PW*16 bytes further (the stride between 8-row groups). The operand
 // of tap (fy, fx) is therefore the same planes addressed from pixel (fy, fx): every tap is
-// a shifted view, nothing is copied or fetched again. The CTA's filter slice
-// [BN][KH*KW*C] is loaded once and stays resident; persistent CTAs walk the patch list.
+// a shifted view, nothing is copied or fetched again. (Core matrices that do not start on a
+// 128-byte boundary cost the MMA nothing: a variant with one aligned copy per horizontal
+// offset issued its MMAs at the same rate.) The CTA's filter slice [BN][KH*KW*C] is loaded
+// once and stays resident; persistent CTAs walk the patch list.
 //
 // Accumulators: int32 in TMEM, two buffers; epilogue identical in arithmetic to conv_umma.cu
 // (reference order of compiler/lib/KernelGen/BareMetal/Activation.cpp:105-113).
@@ -44,15 +47,84 @@ struct PatchParams {
     int pph, ppw;    // input patch extent: kTH + kh - 1, kTW + kw - 1
     int tiles_y, tiles_x, m_tiles, n_tiles;
     int stages;
-    int a_stage_bytes, a_tx_bytes, b_bytes, plane_stride;
+    int a_stage_bytes, a_tx_bytes, b_bytes;
+    int plane_stride;  // one chunk plane: pph x ppw pixels of 16 bytes
     int b_single_load;  // the filter map is the 3-D view (one load) rather than 2-D blocks
     int mma_per_tap;  // k-steps per tap (C/32), or 0 when C == 16 (two taps per k-step)
+    int a_lbo;        // distance between the two 16-byte K halves of one A operand
     EpilogueParams ep;
     int8_t* dst;
     int* status;
+    // optional timeline of CTA 0 (clock64 stamps), for performance work: see MB200_TRACE
+    long long* trace;
 };
 
-template <int BN>
+// One tile's MMAs. The issuing thread runs alone in its warp and every instruction of its
+// loop costs it several cycles, so the hot filter shapes get their own instantiation
+// (KH > 0) where every operand offset is a compile-time constant: two adds per MMA. Looking
+// the offsets up in a shared-memory table measured slower than the MMAs themselves.
+template <int BN, int KH, int KW, int CHUNKS>
+__device__ __forceinline__ void issue_tile_mmas(
+        const PatchParams& p, uint64_t a0, uint64_t b0, uint32_t tmem_d) {
+    constexpr uint32_t idesc = umma_idesc_s8(128, BN);
+    // all offsets in descriptor address units (16 bytes = one pixel of one chunk plane)
+    if constexpr (KH > 0) {
+        constexpr uint32_t ppw = kTW + KW - 1;
+        constexpr uint32_t plane16 = (kTH + KH - 1) * ppw;
+        if constexpr (CHUNKS == 1) {
+            // 16 channels: taps (fx, fx+1) are the two K halves; the second half is the
+            // same plane one pixel to the right
+#pragma unroll
+            for (int fy = 0; fy < KH; ++fy) {
+#pragma unroll
+                for (int fx = 0; fx < KW; fx += 2) {
+                    umma_s8(tmem_d, a0 + (fy * ppw + fx), b0 + (uint32_t)((fy * KW + fx) * BN),
+                            idesc, (fy | fx) ? 1u : 0u);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int fy = 0; fy < KH; ++fy) {
+#pragma unroll
+                for (int fx = 0; fx < KW; ++fx) {
+#pragma unroll
+                    for (int j = 0; j < CHUNKS / 2; ++j) {
+                        // chunks 2j, 2j+1 are the two 16-byte K halves of this step
+                        umma_s8(tmem_d, a0 + (fy * ppw + fx + 2 * j * plane16),
+                                b0 + (uint32_t)(((fy * KW + fx) * CHUNKS + 2 * j) * BN), idesc,
+                                (fy | fx | j) ? 1u : 0u);
+                    }
+                }
+            }
+        }
+    } else {
+        const uint32_t plane16 = (uint32_t)p.plane_stride >> 4;
+        uint32_t acc = 0;
+        uint64_t b_desc = b0;
+        if (p.mma_per_tap > 0) {
+            for (int fy = 0; fy < p.kh; ++fy) {
+                uint64_t a_tap = a0 + (uint32_t)(fy * p.ppw);
+                for (int fx = 0; fx < p.kw; ++fx, ++a_tap) {
+                    uint64_t a_desc = a_tap;
+                    for (int j = 0; j < p.mma_per_tap; ++j, a_desc += 2 * plane16, b_desc += 2 * BN) {
+                        umma_s8(tmem_d, a_desc, b_desc, idesc, acc);
+                        acc = 1;
+                    }
+                }
+            }
+        } else {
+            for (int fy = 0; fy < p.kh; ++fy) {
+                uint64_t a_desc = a0 + (uint32_t)(fy * p.ppw);
+                for (int fx = 0; fx < p.kw; fx += 2, a_desc += 2, b_desc += 2 * BN) {
+                    umma_s8(tmem_d, a_desc, b_desc, idesc, acc);
+                    acc = 1;
+                }
+            }
+        }
+    }
+}
+
+template <int BN, int KH, int KW, int CHUNKS>
 __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const PatchParams p) {
@@ -69,7 +141,6 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
     uint64_t* drain_bar = b_full + 1;
     uint32_t* tmem_slot = (uint32_t*)(drain_bar + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // each CTA owns one slice of output channels and walks the patches with a fixed stride
     const int tile_n = blockIdx.x % p.n_tiles;
@@ -77,7 +148,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
     const int m_step = gridDim.x / p.n_tiles;
     const int n0 = tile_n * BN;
     const int tiles_per_image = p.tiles_y * p.tiles_x;
-    const int plane = p.plane_stride;  // chunk planes start 128-byte aligned (TMA destination rule)
+    const int plane = p.plane_stride;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
@@ -119,10 +190,9 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
                 for (int kc = 0; kc < kchunks; ++kc)
                     tma_load_2d(smem_b + kc * (BN * 16), &map_b, b_full, kc * 16, n0);
             }
-            int local = 0;
-            for (int mt = m_first; mt < p.m_tiles; mt += m_step, ++local) {
-                const int s = local % p.stages;
-                const uint32_t phase = (uint32_t)(local / p.stages) & 1u;
+            int s = 0;
+            uint32_t phase = 0;
+            for (int mt = m_first; mt < p.m_tiles; mt += m_step) {
                 if (!mbar_wait(&a_empty[s], phase ^ 1u, abort_flag)) {
                     if (!*abort_flag) {
                         *abort_flag = 1;
@@ -135,26 +205,32 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
                 const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
                 const int x0 = tx * kTW - p.pw, y0 = ty * kTH - p.ph;
                 mbar_expect_tx(&a_full[s], (uint32_t)p.a_tx_bytes);
-                uint8_t* sa = smem_a + s * p.a_stage_bytes;
-                for (int c = 0; c < p.chunks; ++c)
-                    tma_load_4d(sa + c * plane, &map_a, &a_full[s], c * 16, x0, y0, img);
+                // one request: box {16 B, patch columns, patch rows, 1 image, all chunks}
+                tma_load_5d(smem_a + s * p.a_stage_bytes, &map_a, &a_full[s], 0, x0, y0, img, 0);
+                if (++s == p.stages) {
+                    s = 0;
+                    phase ^= 1u;
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_s8(128, BN);
             bool ok = mbar_wait(b_full, 0, abort_flag);
             if (!ok && !*abort_flag) {
                 *abort_flag = 1;
                 atomicExch(p.status, ERR_MMA_WAIT);
             }
-            const uint32_t b_addr = smem_u32(smem_b);
-            const uint32_t sbo_a = (uint32_t)p.ppw * 16;
-            int local = 0;
+            const uint32_t sbo_a = (uint32_t)p.ppw * 16;  // the next patch row
+            const uint64_t b0 = umma_smem_desc(smem_u32(smem_b), BN * 16, 128, 0);
+            int local = 0, s = 0;
+            uint32_t phase = 0;
             for (int mt = m_first; mt < p.m_tiles && ok; mt += m_step, ++local) {
                 const int buf = local & 1;
                 const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                const bool tr = p.trace && blockIdx.x == 0 && local < 64;
+                if (tr)
+                    p.trace[local * 8 + 4] = clock64();
                 if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
                     if (!*abort_flag) {
                         *abort_flag = 1;
@@ -162,8 +238,6 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
                     }
                     break;
                 }
-                const int s = local % p.stages;
-                const uint32_t phase = (uint32_t)(local / p.stages) & 1u;
                 if (!mbar_wait(&a_full[s], phase, abort_flag)) {
                     if (!*abort_flag) {
                         *abort_flag = 1;
@@ -172,42 +246,20 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (tr)
+                    p.trace[local * 8 + 5] = clock64();
                 const uint32_t a_addr = smem_u32(smem_a + s * p.a_stage_bytes);
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                uint32_t first = 1;
-                if (p.mma_per_tap > 0) {
-                    for (int fy = 0; fy < p.kh; ++fy) {
-                        for (int fx = 0; fx < p.kw; ++fx) {
-                            const uint32_t a_tap = a_addr + (uint32_t)(fy * p.ppw + fx) * 16;
-                            const uint32_t b_tap =
-                                    b_addr + (uint32_t)((fy * p.kw + fx) * p.chunks) * (BN * 16);
-                            for (int j = 0; j < p.mma_per_tap; ++j) {
-                                // chunks 2j, 2j+1 are the two 16-byte K halves of this step
-                                const uint64_t adesc = umma_smem_desc(
-                                        a_tap + (uint32_t)(2 * j) * plane, plane, sbo_a, 0);
-                                const uint64_t bdesc = umma_smem_desc(
-                                        b_tap + (uint32_t)(2 * j) * (BN * 16), BN * 16, 128, 0);
-                                umma_s8(tmem_d, adesc, bdesc, idesc, first ? 0u : 1u);
-                                first = 0;
-                            }
-                        }
-                    }
-                } else {
-                    // 16 channels: taps (fx, fx+1) are the two K halves; the second half is
-                    // the same plane one pixel (16 bytes) to the right
-                    for (int fy = 0; fy < p.kh; ++fy) {
-                        for (int fx = 0; fx < p.kw; fx += 2) {
-                            const uint64_t adesc = umma_smem_desc(
-                                    a_addr + (uint32_t)(fy * p.ppw + fx) * 16, 16, sbo_a, 0);
-                            const uint64_t bdesc = umma_smem_desc(
-                                    b_addr + (uint32_t)(fy * p.kw + fx) * (BN * 16), BN * 16, 128, 0);
-                            umma_s8(tmem_d, adesc, bdesc, idesc, first ? 0u : 1u);
-                            first = 0;
-                        }
-                    }
-                }
+                const uint64_t a0 = umma_smem_desc(a_addr, (uint32_t)p.a_lbo, sbo_a, 0);
+                issue_tile_mmas<BN, KH, KW, CHUNKS>(p, a0, b0, tmem_d);
                 umma_commit(&a_empty[s]);
                 umma_commit(&acc_full[buf]);
+                if (tr)
+                    p.trace[local * 8 + 6] = clock64();
+                if (++s == p.stages) {
+                    s = 0;
+                    phase ^= 1u;
+                }
             }
         }
     } else {
@@ -220,7 +272,12 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
         for (int mt = m_first; mt < p.m_tiles && ok; mt += m_step, ++local) {
             const int buf = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            const bool tr = p.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && local < 64;
+            if (tr)
+                p.trace[local * 8 + 0] = clock64();
             ok = mbar_wait(&acc_full[buf], acc_phase, abort_flag);
+            if (tr)
+                p.trace[local * 8 + 1] = clock64();
             if (!ok && !*abort_flag) {
                 *abort_flag = 1;
                 atomicExch(p.status, ERR_EPILOGUE_WAIT);
@@ -243,13 +300,17 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
             for (int c = half; c < BN / 32; c += kChunkStep) {
                 uint32_t v[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), v);
+                if (tr)
+                    p.trace[local * 8 + 2] = clock64();
                 if (c + kChunkStep >= BN / 32) {
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     mbar_arrive(&acc_empty[buf]);
                 }
                 const int ch0 = n0 + c * 32;
                 if (valid && ch0 < p.oc)
-                    epilogue_store32(v, p.ep, p.dst, px_off + ch0, ch0);
+                    epilogue_store<32>(v, p.ep, p.dst, px_off + ch0, ch0);
+                if (tr)
+                    p.trace[local * 8 + 3] = clock64();
             }
         }
     }
@@ -285,6 +346,13 @@ struct PatchPlan {
     int a_stage_bytes, b_bytes, smem_bytes, plane_stride;
 };
 
+// CTAs per SM to try first; MB200_PATCH_CTAS overrides (performance experiments)
+int patch_first_ctas() {
+    const char* e = getenv("MB200_PATCH_CTAS");
+    const int v = e ? atoi(e) : 0;
+    return v >= 1 && v <= 3 ? v : 3;
+}
+
 PatchPlan plan_patch(const ConvArgs& a) {
     PatchPlan pl{};
     if (a.groups != 1 || a.src_is_nchw || a.sh != 1 || a.sw != 1 || a.dh != 1 || a.dw != 1)
@@ -299,20 +367,22 @@ PatchPlan plan_patch(const ConvArgs& a) {
     if (pph > 256 || ppw > 256)
         return pl;
     pl.bn = a.oc <= 64 ? 64 : 128;
-    // a TMA destination in shared memory must be 128-byte aligned: pad every chunk plane
-    pl.plane_stride = (pph * ppw * 16 + 127) / 128 * 128;
-    pl.a_stage_bytes = (a.ic / 16) * pl.plane_stride;
+    pl.plane_stride = pph * ppw * 16;
+    // a TMA destination in shared memory must be 128-byte aligned: pad the stage
+    pl.a_stage_bytes = ((a.ic / 16) * pl.plane_stride + 127) / 128 * 128;
     pl.b_bytes = pl.bn * a.kh * a.kw * a.ic;
     const int fixed = pl.b_bytes + (2 * kMaxStages + 6) * 8 + 64 + 1024;
     const int budget = 227 * 1024;
     // more CTAs per SM hide more latency; one stage is a whole tile, so two stages already
     // keep the loads a tile ahead
-    for (int per_sm = 3; per_sm >= 1; --per_sm) {
+    const char* one = getenv("MB200_PATCH_MIN_STAGES");
+    const int min_stages = one && atoi(one) == 1 ? 1 : 2;
+    for (int per_sm = patch_first_ctas(); per_sm >= 1; --per_sm) {
         const int avail = budget / per_sm - 1024 - fixed;
         int st = avail / pl.a_stage_bytes;
         if (st > kMaxStages)
             st = kMaxStages;
-        if (st >= 2 && 2 * pl.bn * per_sm <= 512) {
+        if (st >= min_stages && 2 * pl.bn * per_sm <= 512) {
             pl.ok = true;
             pl.stages = st;
             pl.ctas_per_sm = per_sm;
@@ -323,17 +393,17 @@ PatchPlan plan_patch(const ConvArgs& a) {
     return pl;
 }
 
-template <int BN>
+template <int BN, int KH, int KW, int CHUNKS>
 int launch_patch(
         const CUtensorMap& ma, const CUtensorMap& mb, const PatchParams& p, int smem, int grid,
         cudaStream_t st) {
     if (cudaFuncSetAttribute(
-                conv_patch_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+                conv_patch_kernel<BN, KH, KW, CHUNKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
         return check_launch("conv_patch smem attribute");
     // never more CTAs than are resident at once: a persistent CTA that starts late would
     // leave its share of the patches to the end
-    const int per_sm = resident_ctas_per_sm(conv_patch_kernel<BN>, kThreads, smem, 2 * BN);
+    const int per_sm = resident_ctas_per_sm(conv_patch_kernel<BN, KH, KW, CHUNKS>, kThreads, smem, 2 * BN);
     {
         int cap = sm_count() * per_sm / p.n_tiles * p.n_tiles;
         if (cap >= p.n_tiles && grid > cap)
@@ -343,7 +413,7 @@ int launch_patch(
         fprintf(stderr, "conv_patch<%d>: per_sm %d grid %d m_tiles %d n_tiles %d smem %d stages %d "
                 "b_single_load %d\n", BN, per_sm, grid, p.m_tiles, p.n_tiles, smem, p.stages,
                 p.b_single_load);
-    conv_patch_kernel<BN><<<grid, kThreads, smem, st>>>(ma, mb, p);
+    conv_patch_kernel<BN, KH, KW, CHUNKS><<<grid, kThreads, smem, st>>>(ma, mb, p);
     return check_launch("conv_patch");
 }
 
@@ -388,14 +458,16 @@ int launch_conv_patch(
     const int pph = kTH + a.kh - 1, ppw = kTW + a.kw - 1;
     CUtensorMap map_a, map_b;
     {
-        cuuint64_t dims[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw, (cuuint64_t)a.ih,
-                              (cuuint64_t)a.n};
-        cuuint64_t strides[3] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw * a.ic,
-                                 (cuuint64_t)a.ih * a.iw * a.ic};
-        cuuint32_t box[4] = {16, (cuuint32_t)ppw, (cuuint32_t)pph, 1};
-        cuuint32_t estr[4] = {1, 1, 1, 1};
+        // NHWC seen as {16 channel bytes, W, H, N, C/16}: a box over all chunks arrives as
+        // [chunk][row][column][16 bytes]
+        cuuint64_t dims[5] = {16, (cuuint64_t)a.iw, (cuuint64_t)a.ih, (cuuint64_t)a.n,
+                              (cuuint64_t)(a.ic / 16)};
+        cuuint64_t strides[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw * a.ic,
+                                 (cuuint64_t)a.ih * a.iw * a.ic, 16};
+        cuuint32_t box[5] = {16, (cuuint32_t)ppw, (cuuint32_t)pph, 1, (cuuint32_t)(a.ic / 16)};
+        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
         CUresult r = api.tiled(
-                &map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)src, dims, strides, box, estr,
+                &map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, (void*)src, dims, strides, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS)
@@ -451,11 +523,12 @@ int launch_conv_patch(
     p.n_tiles = (a.oc + pl.bn - 1) / pl.bn;
     p.stages = pl.stages;
     p.a_stage_bytes = pl.a_stage_bytes;
-    p.a_tx_bytes = p.chunks * pph * ppw * 16;
     p.plane_stride = pl.plane_stride;
+    p.a_tx_bytes = p.chunks * pl.plane_stride;
     p.b_bytes = pl.b_bytes;
     p.b_single_load = b_single_load;
     p.mma_per_tap = a.ic == 16 ? 0 : a.ic / 32;
+    p.a_lbo = a.ic == 16 ? 16 : p.plane_stride;
     p.ep.oc = a.oc;
     p.ep.act = a.act;
     p.ep.bounded = requant_is_bounded(a.s_src, a.s_flt, a.s_dst) ? 1 : 0;
@@ -469,10 +542,23 @@ int launch_conv_patch(
     p.ep.z_mode = a.z ? a.z_mode : 0;
     p.ep.z_scale = a.z_scale;
     p.ep.z_div = 1.0f / a.z_out_scale;  // the reference's scale_div = 1.f / scale_dst
+    p.ep.acc_out = a.acc_out;
     p.dst = dst;
     p.status = device_status_word();
     if (!p.status)
         return ST_MALLOC;
+    // MB200_TRACE=1: CTA 0 stamps clock64() at the hand-over points of its first 64 tiles and
+    // the launcher prints them (synchronises; for performance work only)
+    static long long* trace_buf = nullptr;
+    p.trace = nullptr;
+    if (getenv("MB200_TRACE")) {
+        if (!trace_buf)
+            cudaMalloc(&trace_buf, (64 * 8 + 64) * sizeof(long long));
+        if (trace_buf) {
+            cudaMemsetAsync(trace_buf, 0, (64 * 8 + 64) * sizeof(long long), st);
+            p.trace = trace_buf;
+        }
+    }
     // persistent grid: a multiple of the channel-slice count, at most what fits on the GPU
     int grid = sm_count() * pl.ctas_per_sm;
     grid = grid / p.n_tiles * p.n_tiles;
@@ -481,8 +567,30 @@ int launch_conv_patch(
     const long long total = (long long)p.m_tiles * p.n_tiles;
     if (grid > total)
         grid = (int)total;
-    return pl.bn == 64 ? launch_patch<64>(map_a, map_b, p, pl.smem_bytes, grid, st)
-                       : launch_patch<128>(map_a, map_b, p, pl.smem_bytes, grid, st);
+    int rc;
+    if (pl.bn == 64 && a.kh == 3 && a.kw == 3 && a.ic == 64)
+        rc = launch_patch<64, 3, 3, 4>(map_a, map_b, p, pl.smem_bytes, grid, st);
+    else if (pl.bn == 64 && a.kh == 4 && a.kw == 4 && a.ic == 16)
+        rc = launch_patch<64, 4, 4, 1>(map_a, map_b, p, pl.smem_bytes, grid, st);
+    else if (pl.bn == 64)
+        rc = launch_patch<64, 0, 0, 0>(map_a, map_b, p, pl.smem_bytes, grid, st);
+    else
+        rc = launch_patch<128, 0, 0, 0>(map_a, map_b, p, pl.smem_bytes, grid, st);
+    if (p.trace && rc == 0) {
+        static long long host[64 * 8 + 64];
+        cudaStreamSynchronize(st);
+        cudaMemcpy(host, p.trace, sizeof(host), cudaMemcpyDeviceToHost);
+        const long long t0 = host[4];
+        fprintf(stderr, "trace conv_patch ic=%d oc=%d %dx%d: per tile [epi wait begin, acc full, tmem "
+                        "loaded, stored | mma wait begin, operands ready, issued] cycles since start\n",
+                a.ic, a.oc, a.oh, a.ow);
+        for (int i = 0; i < 64 && host[i * 8 + 1]; ++i)
+            fprintf(stderr, "  tile %2d: %7lld %7lld %7lld %7lld | %7lld %7lld %7lld\n", i,
+                    host[i * 8 + 0] - t0, host[i * 8 + 1] - t0, host[i * 8 + 2] - t0,
+                    host[i * 8 + 3] - t0, host[i * 8 + 4] - t0, host[i * 8 + 5] - t0,
+                    host[i * 8 + 6] - t0);
+    }
+    return rc;
 }
 
 }  // namespace mb200

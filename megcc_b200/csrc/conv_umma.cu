@@ -127,7 +127,10 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            int it_global = 0;
+            // this thread runs alone in its warp and every instruction costs it several
+            // cycles: stage, phase and filter tap are running counters, no division per step
+            int s = 0;
+            uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int tile_n = tile % p.n_tiles, tile_m = tile / p.n_tiles;
@@ -136,9 +139,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                 const int rem = m0 - img * (p.oh * p.ow);
                 const int oy = rem / p.ow, ox = rem - oy * p.ow;
                 const int base_w = ox * p.sw + p.base_w, base_h = oy * p.sh + p.base_h;
-                for (int it = 0; it < p.k_iters; ++it, ++it_global) {
-                    const int s = it_global % kSt;
-                    const uint32_t phase = (uint32_t)(it_global / kSt) & 1u;
+                int cb = 0, fx = 0, fy = 0;
+                for (int it = 0; it < p.k_iters; ++it) {
                     if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) {
                         if (!*abort_flag) {
                             *abort_flag = 1;
@@ -151,20 +153,32 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                     uint8_t* sa = tiles_a + s * L::kABytes;
                     uint8_t* sb = tiles_b + s * L::kBBytes;
                     if (GEOM != GEOM_TAP16) {
-                        const int tap = it / p.cblocks, cb = it - tap * p.cblocks;
-                        const int fy = tap / p.taps_w, fx = tap - fy * p.taps_w;
                         tma_load_im2col_4d(sa, &map_a, &full_bar[s], cb * kBKc, base_w, base_h, img,
                                            (uint16_t)(fx * p.dw), (uint16_t)(fy * p.dh));
                         tma_load_2d(sb, &map_b, &full_bar[s], it * kBKc, n0);
+                        if (++cb == p.cblocks) {
+                            cb = 0;
+                            if (++fx == p.taps_w) {
+                                fx = 0;
+                                ++fy;
+                            }
+                        }
                     } else {
 #pragma unroll
                         for (int t = 0; t < 4; ++t) {
-                            const int tap = it * 4 + t;
-                            const int fy = tap / p.taps_w, fx = tap - fy * p.taps_w;
                             tma_load_im2col_4d(sa + t * (kBM * 16), &map_a, &full_bar[s], 0, base_w,
                                                base_h, img, (uint16_t)fx, (uint16_t)fy);
-                            tma_load_2d(sb + t * (BN * 16), &map_b, &full_bar[s], tap * 16, n0);
+                            tma_load_2d(sb + t * (BN * 16), &map_b, &full_bar[s], (it * 4 + t) * 16,
+                                        n0);
+                            if (++fx == p.taps_w) {
+                                fx = 0;
+                                ++fy;
+                            }
                         }
+                    }
+                    if (++s == kSt) {
+                        s = 0;
+                        phase ^= 1u;
                     }
                 }
             }
@@ -173,7 +187,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_s8(kBM, BN);
-            int it_global = 0, local = 0;
+            int local = 0, s = 0;
+            uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
                 const int buf = local & 1;
@@ -189,9 +204,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                for (int it = 0; it < p.k_iters; ++it, ++it_global) {
-                    const int s = it_global % kSt;
-                    const uint32_t phase = (uint32_t)(it_global / kSt) & 1u;
+                for (int it = 0; it < p.k_iters; ++it) {
                     if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
                         if (!*abort_flag) {
                             *abort_flag = 1;
@@ -203,25 +216,35 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a_addr = smem_u32(tiles_a + s * L::kABytes);
                     const uint32_t b_addr = smem_u32(tiles_b + s * L::kBBytes);
-#pragma unroll
-                    for (int k = 0; k < kBKc / kUmmaK; ++k) {
-                        uint64_t adesc, bdesc;
-                        if (GEOM == GEOM_WIDE128) {
-                            // 128-byte swizzle: 8-row groups 1024 bytes apart
-                            adesc = umma_smem_desc(a_addr + k * 32, 16, 1024, 2);
-                            bdesc = umma_smem_desc(b_addr + k * 32, 16, 1024, 2);
-                        } else if (GEOM == GEOM_WIDE) {
-                            // 64-byte swizzle; +32 bytes along K inside the swizzled row
-                            adesc = umma_smem_desc(a_addr + k * 32, 16, 512, 4);
-                            bdesc = umma_smem_desc(b_addr + k * 32, 16, 512, 4);
-                        } else {
-                            // two 16-byte taps form one K=32 step
-                            adesc = umma_smem_desc(a_addr + k * 2 * (kBM * 16), kBM * 16, 128, 0);
-                            bdesc = umma_smem_desc(b_addr + k * 2 * (BN * 16), BN * 16, 128, 0);
-                        }
-                        umma_s8(tmem_d, adesc, bdesc, idesc, (it | k) != 0 ? 1u : 0u);
+                    // one descriptor per operand and stage; a K step only moves the address
+                    // field (16-byte units): +32 bytes inside the swizzled row, or two 16-byte
+                    // tap blocks in the plain layout
+                    uint64_t adesc, bdesc;
+                    uint32_t a_step, b_step;
+                    if (GEOM == GEOM_WIDE128) {
+                        // 128-byte swizzle: 8-row groups 1024 bytes apart
+                        adesc = umma_smem_desc(a_addr, 16, 1024, 2);
+                        bdesc = umma_smem_desc(b_addr, 16, 1024, 2);
+                        a_step = b_step = 32 / 16;
+                    } else if (GEOM == GEOM_WIDE) {
+                        adesc = umma_smem_desc(a_addr, 16, 512, 4);
+                        bdesc = umma_smem_desc(b_addr, 16, 512, 4);
+                        a_step = b_step = 32 / 16;
+                    } else {
+                        adesc = umma_smem_desc(a_addr, kBM * 16, 128, 0);
+                        bdesc = umma_smem_desc(b_addr, BN * 16, 128, 0);
+                        a_step = 2 * (kBM * 16) / 16;
+                        b_step = 2 * (BN * 16) / 16;
                     }
+#pragma unroll
+                    for (int k = 0; k < kBKc / kUmmaK; ++k)
+                        umma_s8(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc,
+                                (it | k) != 0 ? 1u : 0u);
                     umma_commit(&empty_bar[s]);  // frees the stage once these MMAs retire
+                    if (++s == kSt) {
+                        s = 0;
+                        phase ^= 1u;
+                    }
                 }
                 if (ok)
                     umma_commit(&acc_full[buf]);
@@ -262,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                 }
                 const int ch0 = n0 + c * 32;
                 if (m < p.m_total && ch0 < p.oc)
-                    epilogue_store32(v, p.ep, p.dst, (size_t)m * p.oc + ch0, ch0);
+                    epilogue_store<32>(v, p.ep, p.dst, (size_t)m * p.oc + ch0, ch0);
             }
         }
     }
@@ -425,6 +448,7 @@ int launch_conv_umma_geom(
     p.ep.z_mode = a.z ? a.z_mode : 0;
     p.ep.z_scale = a.z_scale;
     p.ep.z_div = 1.0f / a.z_out_scale;  // the reference's scale_div = 1.f / scale_dst
+    p.ep.acc_out = a.acc_out;
     p.dst = dst;
     p.status = device_status_word();
     if (!p.status)

@@ -37,6 +37,8 @@ struct ConvArgs {
     const int8_t* z;
     int z_mode;  // 0 none, 1 QADD, 2 QFUSE_ADD_RELU
     float z_scale, z_out_scale;
+    // tensor-core kernels only: store the int32 accumulators here instead of int8 results
+    int32_t* acc_out;
 };
 
 // records a message for mb200_last_error() and returns `code`

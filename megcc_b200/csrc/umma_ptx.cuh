@@ -52,23 +52,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait. Returns false when the limit ran out or another role already gave up.
-// After a few immediate retries the thread sleeps between polls (64 ns doubling to 512 ns):
-// a role that waits for most of the kernel (the producer and the MMA issuer when the
-// epilogue is the slow stage) would otherwise spend the SM's issue slots on its polling loop.
+// try_wait itself parks the thread for a while, so the loop costs few issue slots; a sleep
+// between polls would add up to its length to every hand-over, and the hand-overs (operands
+// ready, accumulator full, accumulator drained) are on the critical path of each tile. Only
+// a wait that has already lasted long (a role idle for most of the kernel) starts sleeping.
 __device__ __forceinline__ bool mbar_wait(
         uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
 #pragma unroll 1
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity))
             return true;
     const long long t0 = clock64();
-    unsigned ns = 64;
     for (int spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity))
             return true;
-        __nanosleep(ns);
-        if (ns < 512)
-            ns *= 2;
+        if (spin > 256)
+            __nanosleep(128);
         if ((spin & 63) == 63) {
             if (*abort_flag)
                 return false;
@@ -102,6 +101,15 @@ __device__ __forceinline__ void tma_load_4d(
             "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
             " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(smem)),
             "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+            : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(
+        void* smem, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile(
+            "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(smem_u32(smem)),
+            "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
             : "memory");
 }
 
@@ -171,6 +179,29 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+
+// 16 columns, WITHOUT waiting: the registers may be read only after tmem_ld_wait16(v)
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+              "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]),
+              "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+            : "r"(taddr)
+            : "memory");
+}
+
+// Waits for this thread's TMEM loads. The registers are named as in/out operands so that
+// the compiler cannot move a use of them above the wait.
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&v)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]),
+                   "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]),
+                   "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :
+                 : "memory");
+}
 
 __device__ __forceinline__ uint32_t pack4_prmt(int a, int b, int c, int d) {
     const uint32_t ab = __byte_perm((uint32_t)a, (uint32_t)b, 0x0040);

@@ -82,6 +82,31 @@ def conv_bias_qs8_nchw(p, src, flt_oihw, bias, flt_scales=None, algo="auto"):
     return dst
 
 
+def matmul_pack_b(b):
+    """[K, N] int8 device tensor -> K-major [N, K] copy for the matrix product."""
+    k, n = b.shape
+    out = torch.empty((n, k), dtype=torch.int8, device=b.device)
+    check(lib().mb200_matmul_pack_b(k, n, _ptr(b), _ptr(out), _stream()))
+    return out
+
+
+def matmul_s8_s32(a, b_packed):
+    m, k = a.shape
+    n = b_packed.shape[0]
+    c = torch.empty((m, n), dtype=torch.int32, device=a.device)
+    check(lib().mb200_matmul_s8_s32(m, n, k, _ptr(a), _ptr(b_packed), _ptr(c), _stream()))
+    return c
+
+
+def matmul_s8_qs8(a, b_packed, acc_scale, dst_scale):
+    m, k = a.shape
+    n = b_packed.shape[0]
+    c = torch.empty((m, n), dtype=torch.int8, device=a.device)
+    check(lib().mb200_matmul_s8_qs8(m, n, k, _ptr(a), _ptr(b_packed), _ptr(c), acc_scale,
+                                    dst_scale, _stream()))
+    return c
+
+
 def pooling_qs8_nhwc(src, mode, window, stride, pad):
     n, ih, iw, c = src.shape
     oh, ow = (ih + 2 * pad - window) // stride + 1, (iw + 2 * pad - window) // stride + 1

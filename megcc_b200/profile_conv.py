@@ -1,9 +1,10 @@
-"""Launches three representative qint8 ConvBias kernels twice each (first layer 3->64 7x7/2,
-64->64 3x3 at 56x56, 256->256 3x3 at 14x14) on a small batch and prints their times.
+"""Launches three representative qint8 ConvBias kernels (first layer 3->64 7x7/2, 64->64 3x3
+at 56x56, 256->256 3x3 at 14x14) on a small batch: once each, then ten times each between
+two events, and prints the mean time of the ten.
 
-Meant to be run under a profiler, capturing the second round:
+Meant to be run under a profiler, capturing the first three launches:
 
-    ncu --set full --clock-control none -k regex:conv_ -s 3 -c 3 \
+    ncu --set full --clock-control none -k regex:conv_ -c 3 \
         python -m megcc_b200.profile_conv 32
 """
 import ctypes
@@ -50,13 +51,15 @@ def main(batch=32):
     for rnd in range(2):
         for name, fn, work in cases:
             e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+            reps = 10 if rnd else 1
             e0.record()
-            fn()
+            for _ in range(reps):
+                fn()
             e1.record()
             torch.cuda.synchronize()
             if rnd:
-                ms = e0.elapsed_time(e1)
-                print(f"{name}: {ms * 1e3:.1f} us incl. launch, {work / ms / 1e9:.0f} TOP/s")
+                ms = e0.elapsed_time(e1) / reps
+                print(f"{name}: {ms * 1e3:.1f} us, {work / ms / 1e9:.0f} TOP/s")
     print("device status", ops.device_status())
 
 

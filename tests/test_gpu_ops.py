@@ -101,7 +101,7 @@ PATCH_CASES = [
     ("c64_56", 2, 64, 64, 56, 56, 3, 1, "RELU"),
     ("c64_ragged", 3, 64, 64, 27, 29, 3, 1, "IDENTITY"),
     ("c64_oc128", 2, 64, 128, 40, 40, 3, 1, "RELU"),
-    ("c128_28", 2, 128, 128, 28, 28, 3, 1, "RELU"),
+    ("c128_oc64", 2, 128, 64, 28, 28, 3, 1, "RELU"),
     ("c32_k5", 2, 32, 72, 50, 50, 5, 2, "H_SWISH"),
     ("c16_k2x4", 8, 16, 64, 40, 40, 4, 2, "RELU"),
     ("c96_k1", 4, 96, 200, 33, 31, 1, 0, "RELU"),
@@ -187,6 +187,29 @@ def test_first_layer_reads_nchw_in_place(ops, oracle):
     out = ops.conv_bias_qs8_nhwc(p, dev(src), packed, dev(bias), src_is_nchw=True)
     want = oracle.conv_bias_qs8(src, flt, bias, 2, 3, 0.05, 0.01, 0.9, "RELU")
     assert (out.cpu().numpy().transpose(0, 3, 1, 2) == want).all()
+
+
+MATMUL_SHAPES = [(512, 512, 512), (1024, 1000, 2048), (300, 72, 640), (64, 15, 64),
+                 (16, 56, 16), (2048, 2048, 2048)]
+
+
+@pytest.mark.parametrize("shape", MATMUL_SHAPES, ids=["x".join(map(str, s)) for s in MATMUL_SHAPES])
+def test_matmul_int8_matches_oracle(ops, oracle, shape):
+    """int8 x int8 -> int32 exactly, and requantised to int8 (x 0.002) by the TypeCvt rule.
+    Small shapes are the reference's Arm int8 GEMM test family (m, n, k in 4..64)."""
+    m, n, k = shape
+    r = cases.rng_for("matmul_%dx%dx%d" % shape)
+    a = r.integers(-127, 128, (m, k), dtype=np.int8)
+    b = r.integers(-127, 128, (k, n), dtype=np.int8)
+    want = oracle.matmul_s8_s32(a, b)
+    bp = ops.matmul_pack_b(dev(b))
+    got = ops.matmul_s8_s32(dev(a), bp).cpu().numpy()
+    assert (got == want).all()
+    scale = 0.002 if k <= 512 else 0.0002
+    q = ops.matmul_s8_qs8(dev(a), bp, scale, 1.0).cpu().numpy()
+    want_q = oracle.typecvt_qs32_qs8(want, scale, 1.0)
+    assert (q == want_q).all()
+    assert ops.device_status() == 0
 
 
 def test_pooling_golden(ops):
