@@ -35,9 +35,10 @@ using namespace umma;
 namespace {
 
 constexpr int kTH = 16, kTW = 8;  // output patch; kTW = 8 makes a patch row one core matrix
-constexpr int kEpilogueWarps = 8;  // two per TMEM lane quarter, splitting the column chunks
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
-constexpr int kEpilogueThreads = 32 * kEpilogueWarps;
+// Epilogue warps per CTA (EW): 8 (two per TMEM lane quarter) when several CTAs share an SM,
+// 16 when the resident filter slice leaves room for one CTA only: that CTA then has the SM's
+// registers and issue slots to itself, and a single CTA's eight warps cannot keep up with
+// its own MMAs.
 constexpr int kMaxStages = 3;
 
 struct PatchParams {
@@ -124,10 +125,12 @@ __device__ __forceinline__ void issue_tile_mmas(
     }
 }
 
-template <int BN, int KH, int KW, int CHUNKS>
-__global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
+template <int BN, int KH, int KW, int CHUNKS, int EW>
+__global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const PatchParams p) {
+    constexpr int kEpilogueWarps = EW;
+    constexpr int kEpilogueThreads = 32 * EW;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_b = smem;
@@ -293,7 +296,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_patch_kernel(
             const bool valid = oy < p.oh && ox < p.ow;
             const size_t px_off = (((size_t)img * p.oh + oy) * p.ow + ox) * p.oc;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-            // warps 2..5 take the even column chunks of their quarter, warps 6..9 the odd ones
+            // the warps of one lane quarter interleave over its 32-column chunks
             const int half = (warp - 2) >> 2;
             constexpr int kChunkStep = kEpilogueWarps / 4;
 #pragma unroll 1
@@ -375,8 +378,7 @@ PatchPlan plan_patch(const ConvArgs& a) {
     const int budget = 227 * 1024;
     // more CTAs per SM hide more latency; one stage is a whole tile, so two stages already
     // keep the loads a tile ahead
-    const char* one = getenv("MB200_PATCH_MIN_STAGES");
-    const int min_stages = one && atoi(one) == 1 ? 1 : 2;
+    const int min_stages = 2;
     for (int per_sm = patch_first_ctas(); per_sm >= 1; --per_sm) {
         const int avail = budget / per_sm - 1024 - fixed;
         int st = avail / pl.a_stage_bytes;
@@ -393,27 +395,28 @@ PatchPlan plan_patch(const ConvArgs& a) {
     return pl;
 }
 
-template <int BN, int KH, int KW, int CHUNKS>
+template <int BN, int KH, int KW, int CHUNKS, int EW>
 int launch_patch(
         const CUtensorMap& ma, const CUtensorMap& mb, const PatchParams& p, int smem, int grid,
         cudaStream_t st) {
+    constexpr int kThreads = 64 + 32 * EW;
     if (cudaFuncSetAttribute(
-                conv_patch_kernel<BN, KH, KW, CHUNKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-        cudaSuccess)
+                conv_patch_kernel<BN, KH, KW, CHUNKS, EW>,
+                cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return check_launch("conv_patch smem attribute");
     // never more CTAs than are resident at once: a persistent CTA that starts late would
     // leave its share of the patches to the end
-    const int per_sm = resident_ctas_per_sm(conv_patch_kernel<BN, KH, KW, CHUNKS>, kThreads, smem, 2 * BN);
+    const int per_sm = resident_ctas_per_sm(conv_patch_kernel<BN, KH, KW, CHUNKS, EW>, kThreads, smem, 2 * BN);
     {
         int cap = sm_count() * per_sm / p.n_tiles * p.n_tiles;
         if (cap >= p.n_tiles && grid > cap)
             grid = cap;
     }
     if (getenv("MB200_DEBUG"))
-        fprintf(stderr, "conv_patch<%d>: per_sm %d grid %d m_tiles %d n_tiles %d smem %d stages %d "
-                "b_single_load %d\n", BN, per_sm, grid, p.m_tiles, p.n_tiles, smem, p.stages,
-                p.b_single_load);
-    conv_patch_kernel<BN, KH, KW, CHUNKS><<<grid, kThreads, smem, st>>>(ma, mb, p);
+        fprintf(stderr, "conv_patch<%d,%d,%d,%d,%d>: per_sm %d grid %d m_tiles %d n_tiles %d smem %d "
+                "stages %d b_single_load %d\n", BN, KH, KW, CHUNKS, EW, per_sm, grid, p.m_tiles,
+                p.n_tiles, smem, p.stages, p.b_single_load);
+    conv_patch_kernel<BN, KH, KW, CHUNKS, EW><<<grid, kThreads, smem, st>>>(ma, mb, p);
     return check_launch("conv_patch");
 }
 
@@ -422,9 +425,10 @@ int launch_patch(
 // Fraction of the MMA rows that land on real output pixels; the caller weighs it against
 // the im2col kernel, which has no such loss.
 float conv_patch_efficiency(const ConvArgs& a) {
-    // with a filter slice so large that only one CTA fits per SM, nothing overlaps the
-    // epilogue and the im2col kernel measured faster: report no benefit
-    if (plan_patch(a).ctas_per_sm < 2)
+    // MB200_PATCH_ALONE=0 keeps shapes whose filter slice leaves room for one CTA per SM
+    // on the im2col kernel (performance experiments)
+    const char* alone = getenv("MB200_PATCH_ALONE");
+    if (alone && atoi(alone) == 0 && plan_patch(a).ctas_per_sm < 2)
         return 0.f;
     const int ty = (a.oh + kTH - 1) / kTH, tx = (a.ow + kTW - 1) / kTW;
     return (float)(a.oh * a.ow) / (float)(ty * kTH * tx * kTW);
@@ -568,14 +572,19 @@ int launch_conv_patch(
     if (grid > total)
         grid = (int)total;
     int rc;
-    if (pl.bn == 64 && a.kh == 3 && a.kw == 3 && a.ic == 64)
-        rc = launch_patch<64, 3, 3, 4>(map_a, map_b, p, pl.smem_bytes, grid, st);
-    else if (pl.bn == 64 && a.kh == 4 && a.kw == 4 && a.ic == 16)
-        rc = launch_patch<64, 4, 4, 1>(map_a, map_b, p, pl.smem_bytes, grid, st);
+    const bool alone = pl.ctas_per_sm == 1;  // one CTA per SM: sixteen epilogue warps
+    if (pl.bn == 64 && a.kh == 3 && a.kw == 3 && a.ic == 64 && !alone)
+        rc = launch_patch<64, 3, 3, 4, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);
+    else if (pl.bn == 64 && a.kh == 4 && a.kw == 4 && a.ic == 16 && !alone)
+        rc = launch_patch<64, 4, 4, 1, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);
+    else if (pl.bn == 128 && a.kh == 3 && a.kw == 3 && a.ic == 128 && alone)
+        rc = launch_patch<128, 3, 3, 8, 16>(map_a, map_b, p, pl.smem_bytes, grid, st);
     else if (pl.bn == 64)
-        rc = launch_patch<64, 0, 0, 0>(map_a, map_b, p, pl.smem_bytes, grid, st);
+        rc = alone ? launch_patch<64, 0, 0, 0, 16>(map_a, map_b, p, pl.smem_bytes, grid, st)
+                   : launch_patch<64, 0, 0, 0, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);
     else
-        rc = launch_patch<128, 0, 0, 0>(map_a, map_b, p, pl.smem_bytes, grid, st);
+        rc = alone ? launch_patch<128, 0, 0, 0, 16>(map_a, map_b, p, pl.smem_bytes, grid, st)
+                   : launch_patch<128, 0, 0, 0, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);
     if (p.trace && rc == 0) {
         static long long host[64 * 8 + 64];
         cudaStreamSynchronize(st);

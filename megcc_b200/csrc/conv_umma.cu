@@ -37,18 +37,29 @@ namespace {
 constexpr int kBM = 128;     // output pixels per tile (UMMA M)
 constexpr int kBK = 64;      // K bytes per pipeline stage of the 64-byte geometries
 constexpr int kUmmaK = 32;   // K per tcgen05.mma kind::i8
-constexpr int kStages = 6;
-constexpr int kEpilogueWarps = 8;  // two per TMEM lane quarter, splitting the column chunks
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
-constexpr int kEpilogueThreads = 32 * kEpilogueWarps;
+constexpr int kStages = 6;         // most stages any variant uses (sizes the barrier arrays)
 enum Geometry : int { GEOM_WIDE = 0, GEOM_TAP16 = 1, GEOM_WIDE128 = 2 };
+
+// Per output-channel tile width. BN = 64 / 128: two accumulator buffers of BN columns, up
+// to three CTAs per SM, two epilogue warps per TMEM lane quarter. BN = 256 (only with
+// 128-byte rows): the two buffers fill the SM's 512 TMEM columns, so one CTA per SM, which
+// then gets four epilogue warps per lane quarter and a larger register budget. The wide
+// tile exists because the operands come from L2 at well under 100 bytes per clock and SM:
+// a 128 x 128 tile needs 32 KB per 256 MMA cycles, a 128 x 256 tile 48 KB per 512.
+template <int BN>
+struct Shape {
+    static constexpr int kEpilogueWarps = BN == 256 ? 16 : 8;
+    static constexpr int kEpilogueThreads = 32 * kEpilogueWarps;
+    static constexpr int kThreads = 64 + kEpilogueThreads;
+    static constexpr int kMinCtas = BN == 256 ? 1 : 3;
+};
 
 // K bytes and pipeline depth per geometry. WIDE128 moves 128-channel rows (128-byte swizzle):
 // half as many TMA requests and barrier round trips per byte as WIDE.
-template <int GEOM>
+template <int BN, int GEOM>
 struct Geom {
     static constexpr int kBKg = GEOM == GEOM_WIDE128 ? 128 : 64;
-    static constexpr int kStagesG = GEOM == GEOM_WIDE128 ? 3 : kStages;
+    static constexpr int kStagesG = GEOM == GEOM_WIDE128 ? (BN == 256 ? 4 : 3) : kStages;
 };
 
 struct UmmaConvParams {
@@ -63,13 +74,14 @@ struct UmmaConvParams {
     EpilogueParams ep;
     int8_t* dst;
     int* status;
+    long long* trace;  // optional per-step timeline of CTA 0's second tile (MB200_TRACE)
 };
 
 template <int BN, int GEOM>
 struct SmemLayout {
-    static constexpr int kABytes = kBM * Geom<GEOM>::kBKg;
-    static constexpr int kBBytes = BN * Geom<GEOM>::kBKg;
-    static constexpr int kTiles = Geom<GEOM>::kStagesG * (kABytes + kBBytes);
+    static constexpr int kABytes = kBM * Geom<BN, GEOM>::kBKg;
+    static constexpr int kBBytes = BN * Geom<BN, GEOM>::kBKg;
+    static constexpr int kTiles = Geom<BN, GEOM>::kStagesG * (kABytes + kBBytes);
     // after the tiles: full[kStages], empty[kStages], acc_full[2], acc_empty[2], drain
     static constexpr int kBarOff = kTiles;
     static constexpr int kTotal = kBarOff + (2 * kStages + 5) * 8 + 16;
@@ -77,12 +89,14 @@ struct SmemLayout {
 };
 
 template <int BN, int GEOM>
-__global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
+__global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv_umma_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const UmmaConvParams p) {
     using L = SmemLayout<BN, GEOM>;
-    constexpr int kBKc = Geom<GEOM>::kBKg;
-    constexpr int kSt = Geom<GEOM>::kStagesG;
+    constexpr int kBKc = Geom<BN, GEOM>::kBKg;
+    constexpr int kSt = Geom<BN, GEOM>::kStagesG;
+    constexpr int kEpilogueWarps = Shape<BN>::kEpilogueWarps;
+    constexpr int kEpilogueThreads = Shape<BN>::kEpilogueThreads;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles_a = smem;
@@ -149,6 +163,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                         ok = false;
                         break;
                     }
+                    if (p.trace && blockIdx.x == 0 && tile == blockIdx.x + gridDim.x && it < 64)
+                        p.trace[it * 4 + 3] = clock64();
                     mbar_expect_tx(&full_bar[s], (uint32_t)(L::kABytes + L::kBBytes));
                     uint8_t* sa = tiles_a + s * L::kABytes;
                     uint8_t* sb = tiles_b + s * L::kBBytes;
@@ -193,6 +209,9 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
                 const int buf = local & 1;
                 const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                const bool trt = p.trace && blockIdx.x == 0 && local < 16;
+                if (trt)
+                    p.trace[256 + local * 8 + 0] = clock64();
                 // the epilogue must have drained this accumulator buffer
                 if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
                     if (!*abort_flag) {
@@ -204,7 +223,12 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                if (trt)
+                    p.trace[256 + local * 8 + 1] = clock64();
                 for (int it = 0; it < p.k_iters; ++it) {
+                    const bool tr = p.trace && blockIdx.x == 0 && local == 1 && it < 64;
+                    if (tr)
+                        p.trace[it * 4 + 0] = clock64();
                     if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
                         if (!*abort_flag) {
                             *abort_flag = 1;
@@ -214,6 +238,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (tr)
+                        p.trace[it * 4 + 1] = clock64();
                     const uint32_t a_addr = smem_u32(tiles_a + s * L::kABytes);
                     const uint32_t b_addr = smem_u32(tiles_b + s * L::kBBytes);
                     // one descriptor per operand and stage; a K step only moves the address
@@ -241,6 +267,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                         umma_s8(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc,
                                 (it | k) != 0 ? 1u : 0u);
                     umma_commit(&empty_bar[s]);  // frees the stage once these MMAs retire
+                    if (tr)
+                        p.trace[it * 4 + 2] = clock64();
                     if (++s == kSt) {
                         s = 0;
                         phase ^= 1u;
@@ -248,6 +276,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                 }
                 if (ok)
                     umma_commit(&acc_full[buf]);
+                if (trt)
+                    p.trace[256 + local * 8 + 2] = clock64();
             }
         }
     } else {
@@ -261,7 +291,12 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             const int tile_n = tile % p.n_tiles, tile_m = tile / p.n_tiles;
             const int m = tile_m * kBM + row, n0 = tile_n * BN;
+            const bool tre = p.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && local < 16;
+            if (tre)
+                p.trace[256 + local * 8 + 4] = clock64();
             ok = mbar_wait(&acc_full[buf], acc_phase, abort_flag);
+            if (tre)
+                p.trace[256 + local * 8 + 5] = clock64();
             if (!ok && !*abort_flag) {
                 *abort_flag = 1;
                 atomicExch(p.status, ERR_EPILOGUE_WAIT);
@@ -271,7 +306,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                 break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-            // warps 2..5 take the even column chunks of their quarter, warps 6..9 the odd ones
+            // the warps of one lane quarter interleave over its 32-column chunks
             const int half = (warp - 2) >> 2;
             constexpr int kChunkStep = kEpilogueWarps / 4;
 #pragma unroll 1
@@ -287,6 +322,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_umma_kernel(
                 if (m < p.m_total && ch0 < p.oc)
                     epilogue_store<32>(v, p.ep, p.dst, (size_t)m * p.oc + ch0, ch0);
             }
+            if (tre)
+                p.trace[256 + local * 8 + 6] = clock64();
         }
     }
 
@@ -328,6 +365,7 @@ int launch_kernel(
                 SmemLayout<BN, GEOM>::kDynamic) != cudaSuccess)
         return check_launch("conv_umma smem attribute");
     // persistent CTAs: as many as the SM holds at once
+    constexpr int kThreads = Shape<BN>::kThreads;
     const int per_sm = resident_ctas_per_sm(
             conv_umma_kernel<BN, GEOM>, kThreads, SmemLayout<BN, GEOM>::kDynamic, 2 * BN);
     const int total = p.m_tiles * p.n_tiles;
@@ -338,6 +376,25 @@ int launch_kernel(
         fprintf(stderr, "conv_umma<%d,%d>: per_sm %d grid %d tiles %d smem %d\n", BN, GEOM, per_sm, grid,
                 total, SmemLayout<BN, GEOM>::kDynamic);
     conv_umma_kernel<BN, GEOM><<<grid, kThreads, SmemLayout<BN, GEOM>::kDynamic, st>>>(ma, mb, p);
+    if (p.trace) {
+        static long long host[384];
+        cudaStreamSynchronize(st);
+        cudaMemcpy(host, p.trace, sizeof(host), cudaMemcpyDeviceToHost);
+        const long long t0 = host[0];
+        fprintf(stderr, "trace conv_umma<%d,%d> k_iters %d: per step [mma wait begin, operands "
+                        "ready, issued | producer issued the loads]\n", BN, GEOM, p.k_iters);
+        for (int i = 0; i < 64 && i < p.k_iters; ++i)
+            fprintf(stderr, "  step %2d: %7lld %7lld %7lld | %7lld\n", i, host[i * 4] - t0,
+                    host[i * 4 + 1] - t0, host[i * 4 + 2] - t0, host[i * 4 + 3] - t0);
+        const long long t1 = host[256];
+        fprintf(stderr, "  per tile [mma: wait for the buffer, got it, all issued | epilogue: wait "
+                        "begin, accumulator full, stored]\n");
+        for (int i = 0; i < 16 && host[256 + i * 8 + 1]; ++i)
+            fprintf(stderr, "  tile %2d: %7lld %7lld %7lld | %7lld %7lld %7lld\n", i,
+                    host[256 + i * 8] - t1, host[256 + i * 8 + 1] - t1, host[256 + i * 8 + 2] - t1,
+                    host[256 + i * 8 + 4] - t1, host[256 + i * 8 + 5] - t1,
+                    host[256 + i * 8 + 6] - t1);
+    }
     return check_launch("conv_umma");
 }
 
@@ -374,7 +431,6 @@ int launch_conv_umma_geom(
     const DriverApi& api = driver_api();
     if (!api.ok)
         return set_error(ST_RUNTIME, "cuTensorMapEncode* entry points not found in the driver");
-    const int bn = a.oc <= 64 ? 64 : 128;
     const int taps = a.kh * a.kw;
     if (geom == GEOM_TAP16 && (a.ic != 16 || taps % 4 != 0 || a.sh != 1 || a.sw != 1))
         return set_error(ST_INVALID_LAYOUT, "TAP16 geometry needs 16 channels and 4k taps");
@@ -384,7 +440,30 @@ int launch_conv_umma_geom(
     // 128-channel rows whenever the channel count allows: fewer, larger TMA requests
     if (geom == GEOM_WIDE && a.ic % 128 == 0 && !getenv("MB200_NO_WIDE128"))
         geom = GEOM_WIDE128;
+    // MB200_CONV_PAIR=1: one 256 x 256 tile per pair of SMs (conv_pair.cu) wherever it applies.
+    // Off by default: both kernels are bound by shared-memory bandwidth (operand reads of
+    // the MMAs plus the TMA writes), and on the ResNet layers the pair measured no faster
+    // than the 128 x 256 tile of a single SM.
+    if (geom == GEOM_WIDE128 && conv_pair_supported(a, src, flt, dst)) {
+        const char* pair = getenv("MB200_CONV_PAIR");
+        if (pair && atoi(pair) != 0)
+            return launch_conv_pair(a, src, flt, bias, flt_scales, dst, st);
+    }
     const int chans = geom == GEOM_WIDE128 ? 128 : geom == GEOM_WIDE ? kBK : 16;
+    int bn = a.oc <= 64 ? 64 : 128;
+    {
+        // 256 output channels per tile when the K loop is long enough to hide the epilogue
+        // of a single CTA per SM and there are tiles for every SM
+        const long long k_bytes = (long long)taps * a.ic;
+        const long long tiles256 = (long long)((a.m + kBM - 1) / kBM) * ((a.oc + 255) / 256);
+        const char* force = getenv("MB200_CONV_BN");
+        if (geom == GEOM_WIDE128 && a.oc > 128 && k_bytes >= 1024 && tiles256 >= sm_count())
+            bn = 256;
+        if (force && geom == GEOM_WIDE128 && atoi(force) == 256 && a.oc > 128)
+            bn = 256;
+        if (force && atoi(force) == 128 && a.oc > 64)
+            bn = 128;
+    }
     const CUtensorMapSwizzle swz = geom == GEOM_WIDE128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                    : geom == GEOM_WIDE  ? CU_TENSOR_MAP_SWIZZLE_64B
                                                         : CU_TENSOR_MAP_SWIZZLE_NONE;
@@ -453,9 +532,22 @@ int launch_conv_umma_geom(
     p.status = device_status_word();
     if (!p.status)
         return ST_MALLOC;
-    if (geom == GEOM_WIDE128)
+    static long long* trace_buf = nullptr;
+    p.trace = nullptr;
+    if (getenv("MB200_TRACE")) {
+        if (!trace_buf)
+            cudaMalloc(&trace_buf, 384 * sizeof(long long));
+        if (trace_buf) {
+            cudaMemsetAsync(trace_buf, 0, 384 * sizeof(long long), st);
+            p.trace = trace_buf;
+        }
+    }
+    if (geom == GEOM_WIDE128) {
+        if (bn == 256)
+            return launch_kernel<256, GEOM_WIDE128>(map_a, map_b, p, st);
         return bn == 64 ? launch_kernel<64, GEOM_WIDE128>(map_a, map_b, p, st)
                         : launch_kernel<128, GEOM_WIDE128>(map_a, map_b, p, st);
+    }
     if (geom == GEOM_WIDE)
         return bn == 64 ? launch_kernel<64, GEOM_WIDE>(map_a, map_b, p, st)
                         : launch_kernel<128, GEOM_WIDE>(map_a, map_b, p, st);

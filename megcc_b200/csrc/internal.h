@@ -54,6 +54,11 @@ int launch_conv_direct(
         const float* flt_scales, int8_t* dst, int32_t* acc, cudaStream_t st);
 // tensor-core implicit GEMM; conv_umma_supported() says whether the shape qualifies
 bool conv_umma_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst);
+// the same implicit GEMM on a pair of SMs (cta_group::2), 256 x 256 tiles: wide layers
+bool conv_pair_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst);
+int launch_conv_pair(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
+        const float* flt_scales, int8_t* dst, cudaStream_t st);
 int launch_conv_umma(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
         const float* flt_scales, int8_t* dst, cudaStream_t st);

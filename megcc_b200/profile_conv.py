@@ -1,8 +1,9 @@
-"""Launches three representative qint8 ConvBias kernels (first layer 3->64 7x7/2, 64->64 3x3
-at 56x56, 256->256 3x3 at 14x14) on a small batch: once each, then ten times each between
+"""Launches representative qint8 ConvBias kernels (first layer 3->64 7x7/2, and the 3x3
+convolutions of the four ResNet-18 stages: 64 channels at 56x56, 128 at 28x28, 256 at 14x14,
+512 at 7x7) on a small batch: once each, then ten times each between
 two events, and prints the mean time of the ten.
 
-Meant to be run under a profiler, capturing the first three launches:
+Meant to be run under a profiler, capturing the first launches:
 
     ncu --set full --clock-control none -k regex:conv_ -c 3 \
         python -m megcc_b200.profile_conv 32
@@ -40,7 +41,8 @@ def main(batch=32):
                                             None, ptr(dst), ptr(ws), ws.numel(), st))
 
     cases.append(("first_layer_3_64_7x7s2", first_layer, 2.0 * batch * 64 * 112 * 112 * 147))
-    for name, c, hw in (("conv_64_64_3x3_56", 64, 56), ("conv_256_256_3x3_14", 256, 14)):
+    for name, c, hw in (("conv_64_64_3x3_56", 64, 56), ("conv_128_128_3x3_28", 128, 28),
+                        ("conv_256_256_3x3_14", 256, 14), ("conv_512_512_3x3_7", 512, 7)):
         pp = ops.conv_param(batch, c, hw, hw, c, 3, 3, 1, 1, 1, "RELU", 0.05, 0.01, 2.0)
         s = dev(rng.integers(-128, 128, (batch, hw, hw, c), dtype=np.int8))
         f = ops.pack_filter(pp, dev(rng.integers(-127, 128, (c, c, 3, 3), dtype=np.int8)))

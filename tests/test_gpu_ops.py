@@ -96,12 +96,70 @@ def test_conv_umma_matches_oracle(ops, oracle, case):
     assert (np.abs(want.astype(int)) < 127).mean() > 0.3
 
 
+BN256_CASES = [
+    # name, n, ic, oc, h, w, k, stride, pad, act, forced
+    ("s1_256", 4, 256, 256, 14, 14, 3, 1, 1, "RELU", True),
+    ("s1_512", 6, 512, 512, 7, 7, 3, 1, 1, "RELU", True),
+    ("s2_128_256", 2, 128, 256, 28, 28, 3, 2, 1, "IDENTITY", True),
+    ("ragged_oc320", 4, 128, 320, 20, 20, 3, 1, 1, "RELU", True),
+    ("pw_1024", 3, 1024, 1024, 7, 7, 1, 1, 0, "H_SWISH", True),
+    ("auto_256_n100", 100, 256, 256, 14, 14, 3, 1, 1, "RELU", False),
+]
+
+
+@pytest.mark.parametrize("case", BN256_CASES, ids=[c[0] for c in BN256_CASES])
+def test_conv_umma_256_wide_tiles_match_oracle(ops, oracle, case, monkeypatch):
+    """The 128 x 256 output tile (one CTA per SM, sixteen epilogue warps): forced through the
+    tuning variable on small shapes, and chosen by the launcher itself on one large enough."""
+    name, n, ic, oc, h, w, k, stride, pad, act, forced = case
+    if forced:
+        monkeypatch.setenv("MB200_CONV_BN", "256")
+    c = dict(name="bn256_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=stride, pad=pad,
+             groups=1, act=act, range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.37 * (ic * k * k / 576.0) ** 0.5 + 0.4))
+    out, (src, flt, bias) = run_conv_nchw(ops, c, algo="umma")
+    s0, s1, s2 = c["scales"]
+    want = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, s1, s2, act)
+    bad = int((out != want).sum())
+    assert bad == 0, f"{bad}/{want.size} differ; first at {np.argwhere(out != want)[:4].tolist()}"
+    assert ops.device_status() == 0
+
+
+PAIR_CASES = [
+    # name, n, ic, oc, h, w, k, stride, pad, act
+    ("s1_256", 4, 256, 256, 14, 14, 3, 1, 1, "RELU"),            # 784 pixels: 3 full pairs + tail
+    ("s1_512", 6, 512, 512, 7, 7, 3, 1, 1, "RELU"),              # 294 pixels, two channel tiles
+    ("s2_128_256", 2, 128, 256, 28, 28, 3, 2, 1, "IDENTITY"),
+    ("ragged_oc320", 4, 128, 320, 20, 20, 3, 1, 1, "RELU"),      # second channel tile: 64 of 256
+    ("peer_empty", 11, 128, 256, 10, 10, 3, 1, 1, "H_SWISH"),    # 1100 pixels: the last pair's peer is idle
+    ("pw_1024", 3, 1024, 1024, 7, 7, 1, 1, 0, "RELU"),
+]
+
+
+@pytest.mark.parametrize("case", PAIR_CASES, ids=[c[0] for c in PAIR_CASES])
+def test_conv_pair_of_sms_matches_oracle(ops, oracle, case, monkeypatch):
+    """256 x 256 tiles computed by two CTAs on two SMs (tcgen05 cta_group::2)."""
+    name, n, ic, oc, h, w, k, stride, pad, act = case
+    monkeypatch.setenv("MB200_CONV_PAIR", "1")
+    c = dict(name="pair_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=stride, pad=pad,
+             groups=1, act=act, range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.37 * (ic * k * k / 576.0) ** 0.5 + 0.4))
+    out, (src, flt, bias) = run_conv_nchw(ops, c, algo="umma")
+    s0, s1, s2 = c["scales"]
+    want = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, s1, s2, act)
+    bad = int((out != want).sum())
+    assert bad == 0, f"{bad}/{want.size} differ; first at {np.argwhere(out != want)[:4].tolist()}"
+    assert ops.device_status() == 0
+
+
 PATCH_CASES = [
     # name, n, ic, oc, h, w, k, pad, act  (all stride 1)
     ("c64_56", 2, 64, 64, 56, 56, 3, 1, "RELU"),
     ("c64_ragged", 3, 64, 64, 27, 29, 3, 1, "IDENTITY"),
     ("c64_oc128", 2, 64, 128, 40, 40, 3, 1, "RELU"),
     ("c128_oc64", 2, 128, 64, 28, 28, 3, 1, "RELU"),
+    ("c128_28", 2, 128, 128, 28, 28, 3, 1, "RELU"),
+    ("c96_oc128_k3", 2, 96, 128, 30, 30, 3, 1, "IDENTITY"),
     ("c32_k5", 2, 32, 72, 50, 50, 5, 2, "H_SWISH"),
     ("c16_k2x4", 8, 16, 64, 40, 40, 4, 2, "RELU"),
     ("c96_k1", 4, 96, 200, 33, 31, 1, 0, "RELU"),
