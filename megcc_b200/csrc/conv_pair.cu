@@ -48,7 +48,6 @@ struct PairParams {
     EpilogueParams ep;
     int8_t* dst;
     int* status;
-    long long* trace;  // optional timeline of cluster 0 (MB200_TRACE)
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -232,8 +231,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) conv_pa
                         ok = false;
                         break;
                     }
-                    if (p.trace && first_tile == 0 && tile == tile_step && it < 64)
-                        p.trace[it * 4 + 2 + (int)rank] = clock64();
                     const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[s]), 0);
                     if (leader)
                         mbar_expect_tx(&full_bar[s], 2u * (uint32_t)(kABytes + kBBytes));
@@ -265,9 +262,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) conv_pa
             for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++local) {
                 const int buf = local & 1;
                 const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-                const bool trt = p.trace && first_tile == 0 && local < 8;
-                if (trt)
-                    p.trace[128 + local * 16 + 0] = clock64();
                 // both CTAs' epilogues must have drained this accumulator buffer
                 if (!mbar_wait_cluster(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
                     give_up(ERR_MMA_ACC_WAIT);
@@ -275,20 +269,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) conv_pa
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kBN);
-                if (trt)
-                    p.trace[128 + local * 16 + 1] = clock64();
                 for (int it = 0; it < p.k_iters; ++it) {
-                    const bool tr = p.trace && first_tile == 0 && local == 1 && it < 64;
-                    if (tr)
-                        p.trace[it * 4 + 0] = clock64();
                     if (!mbar_wait_cluster(&full_bar[s], phase, abort_flag)) {
                         give_up(ERR_MMA_WAIT);
                         ok = false;
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (tr)
-                        p.trace[it * 4 + 1] = clock64();
                     // offsets inside the CTA's window: the same in both CTAs of the pair
                     const uint64_t adesc =
                             umma_smem_desc(smem_u32(tiles_a + s * kABytes), 16, 1024, 2);
@@ -312,8 +299,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) conv_pa
                     umma_pair_commit(f_local);
                     umma_pair_commit(map_to_cta(f_local, 1));
                 }
-                if (trt)
-                    p.trace[128 + local * 16 + 2] = clock64();
             }
         }
     } else {
@@ -327,12 +312,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) conv_pa
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             const int tile_n = tile % p.n_tiles, tile_m = tile / p.n_tiles;
             const int m = tile_m * (2 * kBM) + (int)rank * kBM + row, n0 = tile_n * kBN;
-            const bool tre = p.trace && first_tile == 0 && warp == 2 && lane == 0 && local < 8;
-            if (tre)
-                p.trace[128 + local * 16 + 4 + 4 * (int)rank] = clock64();
             ok = mbar_wait_cluster(&acc_full[buf], acc_phase, abort_flag);
-            if (tre)
-                p.trace[128 + local * 16 + 5 + 4 * (int)rank] = clock64();
             if (!ok)
                 give_up(ERR_EPILOGUE_WAIT);
             ok = __all_sync(0xffffffffu, ok);
@@ -359,8 +339,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) conv_pa
                 if (m < p.m_total && ch0 < p.oc)
                     epilogue_store<32>(v, p.ep, p.dst, (size_t)m * p.oc + ch0, ch0);
             }
-            if (tre)
-                p.trace[128 + local * 16 + 6 + 4 * (int)rank] = clock64();
         }
     }
 
@@ -518,37 +496,7 @@ int launch_conv_pair(
     if (getenv("MB200_DEBUG"))
         fprintf(stderr, "conv_pair: clusters %d tiles %d k_iters %d smem %d\n", clusters, total,
                 p.k_iters, kDynamic);
-    static long long* trace_buf = nullptr;
-    p.trace = nullptr;
-    if (getenv("MB200_TRACE")) {
-        if (!trace_buf)
-            cudaMalloc(&trace_buf, 256 * sizeof(long long));
-        if (trace_buf) {
-            cudaMemsetAsync(trace_buf, 0, 256 * sizeof(long long), st);
-            p.trace = trace_buf;
-        }
-    }
     conv_pair_kernel<<<2 * clusters, kThreads, kDynamic, st>>>(map_a, map_b, p);
-    if (p.trace) {
-        static long long host[256];
-        cudaStreamSynchronize(st);
-        cudaMemcpy(host, p.trace, sizeof(host), cudaMemcpyDeviceToHost);
-        const long long t0 = host[0];
-        fprintf(stderr, "trace conv_pair k_iters %d: per step [mma wait begin, operands ready | "
-                        "leader / peer producer issued the loads]\n", p.k_iters);
-        for (int i = 0; i < 64 && i < p.k_iters; ++i)
-            fprintf(stderr, "  step %2d: %7lld %7lld | %7lld %7lld\n", i, host[i * 4] - t0,
-                    host[i * 4 + 1] - t0, host[i * 4 + 2] - t0, host[i * 4 + 3] - t0);
-        const long long t1 = host[128];
-        fprintf(stderr, "  per tile [mma: wait for the buffer, got it, all issued | leader epilogue: "
-                        "wait begin, accumulator full, stored | peer epilogue: same (its own clock)]\n");
-        for (int i = 0; i < 8 && host[128 + i * 16 + 1]; ++i) {
-            const long long* h = host + 128 + i * 16;
-            fprintf(stderr, "  tile %2d: %7lld %7lld %7lld | %7lld %7lld %7lld | %7lld %7lld %7lld\n", i,
-                    h[0] - t1, h[1] - t1, h[2] - t1, h[4] - t1, h[5] - t1, h[6] - t1,
-                    h[8] - h[8 - 16 * i], h[9] - h[8 - 16 * i], h[10] - h[8 - 16 * i]);
-        }
-    }
     return check_launch("conv_pair");
 }
 

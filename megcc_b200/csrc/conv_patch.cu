@@ -56,8 +56,6 @@ struct PatchParams {
     EpilogueParams ep;
     int8_t* dst;
     int* status;
-    // optional timeline of CTA 0 (clock64 stamps), for performance work: see MB200_TRACE
-    long long* trace;
 };
 
 // One tile's MMAs. The issuing thread runs alone in its warp and every instruction of its
@@ -79,8 +77,11 @@ __device__ __forceinline__ void issue_tile_mmas(
             for (int fy = 0; fy < KH; ++fy) {
 #pragma unroll
                 for (int fx = 0; fx < KW; fx += 2) {
-                    umma_s8(tmem_d, a0 + (fy * ppw + fx), b0 + (uint32_t)((fy * KW + fx) * BN),
-                            idesc, (fy | fx) ? 1u : 0u);
+                    const uint64_t ad = a0 + (fy * ppw + fx), bd = b0 + (uint32_t)((fy * KW + fx) * BN);
+                    if ((fy | fx) == 0)
+                        umma_s8_c<false>(tmem_d, ad, bd, idesc);
+                    else
+                        umma_s8_c<true>(tmem_d, ad, bd, idesc);
                 }
             }
         } else {
@@ -91,9 +92,12 @@ __device__ __forceinline__ void issue_tile_mmas(
 #pragma unroll
                     for (int j = 0; j < CHUNKS / 2; ++j) {
                         // chunks 2j, 2j+1 are the two 16-byte K halves of this step
-                        umma_s8(tmem_d, a0 + (fy * ppw + fx + 2 * j * plane16),
-                                b0 + (uint32_t)(((fy * KW + fx) * CHUNKS + 2 * j) * BN), idesc,
-                                (fy | fx | j) ? 1u : 0u);
+                        const uint64_t ad = a0 + (fy * ppw + fx + 2 * j * plane16);
+                        const uint64_t bd = b0 + (uint32_t)(((fy * KW + fx) * CHUNKS + 2 * j) * BN);
+                        if ((fy | fx | j) == 0)
+                            umma_s8_c<false>(tmem_d, ad, bd, idesc);
+                        else
+                            umma_s8_c<true>(tmem_d, ad, bd, idesc);
                     }
                 }
             }
@@ -231,9 +235,6 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
             for (int mt = m_first; mt < p.m_tiles && ok; mt += m_step, ++local) {
                 const int buf = local & 1;
                 const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-                const bool tr = p.trace && blockIdx.x == 0 && local < 64;
-                if (tr)
-                    p.trace[local * 8 + 4] = clock64();
                 if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
                     if (!*abort_flag) {
                         *abort_flag = 1;
@@ -249,16 +250,12 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (tr)
-                    p.trace[local * 8 + 5] = clock64();
                 const uint32_t a_addr = smem_u32(smem_a + s * p.a_stage_bytes);
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
                 const uint64_t a0 = umma_smem_desc(a_addr, (uint32_t)p.a_lbo, sbo_a, 0);
                 issue_tile_mmas<BN, KH, KW, CHUNKS>(p, a0, b0, tmem_d);
                 umma_commit(&a_empty[s]);
                 umma_commit(&acc_full[buf]);
-                if (tr)
-                    p.trace[local * 8 + 6] = clock64();
                 if (++s == p.stages) {
                     s = 0;
                     phase ^= 1u;
@@ -275,12 +272,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
         for (int mt = m_first; mt < p.m_tiles && ok; mt += m_step, ++local) {
             const int buf = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-            const bool tr = p.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && local < 64;
-            if (tr)
-                p.trace[local * 8 + 0] = clock64();
             ok = mbar_wait(&acc_full[buf], acc_phase, abort_flag);
-            if (tr)
-                p.trace[local * 8 + 1] = clock64();
             if (!ok && !*abort_flag) {
                 *abort_flag = 1;
                 atomicExch(p.status, ERR_EPILOGUE_WAIT);
@@ -303,8 +295,6 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
             for (int c = half; c < BN / 32; c += kChunkStep) {
                 uint32_t v[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), v);
-                if (tr)
-                    p.trace[local * 8 + 2] = clock64();
                 if (c + kChunkStep >= BN / 32) {
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     mbar_arrive(&acc_empty[buf]);
@@ -312,8 +302,6 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
                 const int ch0 = n0 + c * 32;
                 if (valid && ch0 < p.oc)
                     epilogue_store<32>(v, p.ep, p.dst, px_off + ch0, ch0);
-                if (tr)
-                    p.trace[local * 8 + 3] = clock64();
             }
         }
     }
@@ -425,11 +413,15 @@ int launch_patch(
 // Fraction of the MMA rows that land on real output pixels; the caller weighs it against
 // the im2col kernel, which has no such loss.
 float conv_patch_efficiency(const ConvArgs& a) {
-    // MB200_PATCH_ALONE=0 keeps shapes whose filter slice leaves room for one CTA per SM
-    // on the im2col kernel (performance experiments)
-    const char* alone = getenv("MB200_PATCH_ALONE");
-    if (alone && atoi(alone) == 0 && plan_patch(a).ctas_per_sm < 2)
-        return 0.f;
+    // A filter slice so large that one CTA has the SM to itself leaves a single thread to
+    // issue every MMA of the SM, and with 128-column MMAs (64 cycles each) that thread, which
+    // shares its scheduler with epilogue warps, is the limit: the im2col kernel with two CTAs
+    // per SM measured faster. MB200_PATCH_ALONE=1 uses the patch kernel all the same.
+    if (plan_patch(a).ctas_per_sm < 2) {
+        const char* alone = getenv("MB200_PATCH_ALONE");
+        if (!(alone && atoi(alone) != 0))
+            return 0.f;
+    }
     const int ty = (a.oh + kTH - 1) / kTH, tx = (a.ow + kTW - 1) / kTW;
     return (float)(a.oh * a.ow) / (float)(ty * kTH * tx * kTW);
 }
@@ -551,18 +543,6 @@ int launch_conv_patch(
     p.status = device_status_word();
     if (!p.status)
         return ST_MALLOC;
-    // MB200_TRACE=1: CTA 0 stamps clock64() at the hand-over points of its first 64 tiles and
-    // the launcher prints them (synchronises; for performance work only)
-    static long long* trace_buf = nullptr;
-    p.trace = nullptr;
-    if (getenv("MB200_TRACE")) {
-        if (!trace_buf)
-            cudaMalloc(&trace_buf, (64 * 8 + 64) * sizeof(long long));
-        if (trace_buf) {
-            cudaMemsetAsync(trace_buf, 0, (64 * 8 + 64) * sizeof(long long), st);
-            p.trace = trace_buf;
-        }
-    }
     // persistent grid: a multiple of the channel-slice count, at most what fits on the GPU
     int grid = sm_count() * pl.ctas_per_sm;
     grid = grid / p.n_tiles * p.n_tiles;
@@ -585,20 +565,6 @@ int launch_conv_patch(
     else
         rc = alone ? launch_patch<128, 0, 0, 0, 16>(map_a, map_b, p, pl.smem_bytes, grid, st)
                    : launch_patch<128, 0, 0, 0, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);
-    if (p.trace && rc == 0) {
-        static long long host[64 * 8 + 64];
-        cudaStreamSynchronize(st);
-        cudaMemcpy(host, p.trace, sizeof(host), cudaMemcpyDeviceToHost);
-        const long long t0 = host[4];
-        fprintf(stderr, "trace conv_patch ic=%d oc=%d %dx%d: per tile [epi wait begin, acc full, tmem "
-                        "loaded, stored | mma wait begin, operands ready, issued] cycles since start\n",
-                a.ic, a.oc, a.oh, a.ow);
-        for (int i = 0; i < 64 && host[i * 8 + 1]; ++i)
-            fprintf(stderr, "  tile %2d: %7lld %7lld %7lld %7lld | %7lld %7lld %7lld\n", i,
-                    host[i * 8 + 0] - t0, host[i * 8 + 1] - t0, host[i * 8 + 2] - t0,
-                    host[i * 8 + 3] - t0, host[i * 8 + 4] - t0, host[i * 8 + 5] - t0,
-                    host[i * 8 + 6] - t0);
-    }
     return rc;
 }
 

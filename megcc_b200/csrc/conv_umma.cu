@@ -74,7 +74,6 @@ struct UmmaConvParams {
     EpilogueParams ep;
     int8_t* dst;
     int* status;
-    long long* trace;  // optional per-step timeline of CTA 0's second tile (MB200_TRACE)
 };
 
 template <int BN, int GEOM>
@@ -163,8 +162,6 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                         ok = false;
                         break;
                     }
-                    if (p.trace && blockIdx.x == 0 && tile == blockIdx.x + gridDim.x && it < 64)
-                        p.trace[it * 4 + 3] = clock64();
                     mbar_expect_tx(&full_bar[s], (uint32_t)(L::kABytes + L::kBBytes));
                     uint8_t* sa = tiles_a + s * L::kABytes;
                     uint8_t* sb = tiles_b + s * L::kBBytes;
@@ -209,9 +206,6 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
                 const int buf = local & 1;
                 const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-                const bool trt = p.trace && blockIdx.x == 0 && local < 16;
-                if (trt)
-                    p.trace[256 + local * 8 + 0] = clock64();
                 // the epilogue must have drained this accumulator buffer
                 if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
                     if (!*abort_flag) {
@@ -223,12 +217,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                if (trt)
-                    p.trace[256 + local * 8 + 1] = clock64();
                 for (int it = 0; it < p.k_iters; ++it) {
-                    const bool tr = p.trace && blockIdx.x == 0 && local == 1 && it < 64;
-                    if (tr)
-                        p.trace[it * 4 + 0] = clock64();
                     if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
                         if (!*abort_flag) {
                             *abort_flag = 1;
@@ -238,8 +227,6 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (tr)
-                        p.trace[it * 4 + 1] = clock64();
                     const uint32_t a_addr = smem_u32(tiles_a + s * L::kABytes);
                     const uint32_t b_addr = smem_u32(tiles_b + s * L::kBBytes);
                     // one descriptor per operand and stage; a K step only moves the address
@@ -262,13 +249,11 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                         a_step = 2 * (kBM * 16) / 16;
                         b_step = 2 * (BN * 16) / 16;
                     }
+                    umma_s8(tmem_d, adesc, bdesc, idesc, it != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k = 0; k < kBKc / kUmmaK; ++k)
-                        umma_s8(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc,
-                                (it | k) != 0 ? 1u : 0u);
+                    for (int k = 1; k < kBKc / kUmmaK; ++k)
+                        umma_s8_c<true>(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc);
                     umma_commit(&empty_bar[s]);  // frees the stage once these MMAs retire
-                    if (tr)
-                        p.trace[it * 4 + 2] = clock64();
                     if (++s == kSt) {
                         s = 0;
                         phase ^= 1u;
@@ -276,8 +261,6 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                 }
                 if (ok)
                     umma_commit(&acc_full[buf]);
-                if (trt)
-                    p.trace[256 + local * 8 + 2] = clock64();
             }
         }
     } else {
@@ -291,12 +274,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             const int tile_n = tile % p.n_tiles, tile_m = tile / p.n_tiles;
             const int m = tile_m * kBM + row, n0 = tile_n * BN;
-            const bool tre = p.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && local < 16;
-            if (tre)
-                p.trace[256 + local * 8 + 4] = clock64();
             ok = mbar_wait(&acc_full[buf], acc_phase, abort_flag);
-            if (tre)
-                p.trace[256 + local * 8 + 5] = clock64();
             if (!ok && !*abort_flag) {
                 *abort_flag = 1;
                 atomicExch(p.status, ERR_EPILOGUE_WAIT);
@@ -322,8 +300,6 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                 if (m < p.m_total && ch0 < p.oc)
                     epilogue_store<32>(v, p.ep, p.dst, (size_t)m * p.oc + ch0, ch0);
             }
-            if (tre)
-                p.trace[256 + local * 8 + 6] = clock64();
         }
     }
 
@@ -376,25 +352,6 @@ int launch_kernel(
         fprintf(stderr, "conv_umma<%d,%d>: per_sm %d grid %d tiles %d smem %d\n", BN, GEOM, per_sm, grid,
                 total, SmemLayout<BN, GEOM>::kDynamic);
     conv_umma_kernel<BN, GEOM><<<grid, kThreads, SmemLayout<BN, GEOM>::kDynamic, st>>>(ma, mb, p);
-    if (p.trace) {
-        static long long host[384];
-        cudaStreamSynchronize(st);
-        cudaMemcpy(host, p.trace, sizeof(host), cudaMemcpyDeviceToHost);
-        const long long t0 = host[0];
-        fprintf(stderr, "trace conv_umma<%d,%d> k_iters %d: per step [mma wait begin, operands "
-                        "ready, issued | producer issued the loads]\n", BN, GEOM, p.k_iters);
-        for (int i = 0; i < 64 && i < p.k_iters; ++i)
-            fprintf(stderr, "  step %2d: %7lld %7lld %7lld | %7lld\n", i, host[i * 4] - t0,
-                    host[i * 4 + 1] - t0, host[i * 4 + 2] - t0, host[i * 4 + 3] - t0);
-        const long long t1 = host[256];
-        fprintf(stderr, "  per tile [mma: wait for the buffer, got it, all issued | epilogue: wait "
-                        "begin, accumulator full, stored]\n");
-        for (int i = 0; i < 16 && host[256 + i * 8 + 1]; ++i)
-            fprintf(stderr, "  tile %2d: %7lld %7lld %7lld | %7lld %7lld %7lld\n", i,
-                    host[256 + i * 8] - t1, host[256 + i * 8 + 1] - t1, host[256 + i * 8 + 2] - t1,
-                    host[256 + i * 8 + 4] - t1, host[256 + i * 8 + 5] - t1,
-                    host[256 + i * 8 + 6] - t1);
-    }
     return check_launch("conv_umma");
 }
 
@@ -532,16 +489,6 @@ int launch_conv_umma_geom(
     p.status = device_status_word();
     if (!p.status)
         return ST_MALLOC;
-    static long long* trace_buf = nullptr;
-    p.trace = nullptr;
-    if (getenv("MB200_TRACE")) {
-        if (!trace_buf)
-            cudaMalloc(&trace_buf, 384 * sizeof(long long));
-        if (trace_buf) {
-            cudaMemsetAsync(trace_buf, 0, 384 * sizeof(long long), st);
-            p.trace = trace_buf;
-        }
-    }
     if (geom == GEOM_WIDE128) {
         if (bn == 256)
             return launch_kernel<256, GEOM_WIDE128>(map_a, map_b, p, st);

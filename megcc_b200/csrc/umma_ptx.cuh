@@ -155,6 +155,18 @@ __device__ __forceinline__ void umma_s8(
             : "memory");
 }
 
+// The same with the accumulate flag known at compile time: no register, no compare.
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_s8_c(
+        uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACCUMULATE ? 1 : 0)
+            : "memory");
+}
+
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile(
             "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
