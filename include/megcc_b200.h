@@ -139,6 +139,17 @@ MB200_API int mb200_conv_acc_qs8_nhwc(
         const mb200_conv_param* p, const int8_t* src, const int8_t* flt_packed,
         const int32_t* bias, int32_t* acc, void* stream);
 
+/* Host only, no GPU needed. The tensor-core ConvBias epilogue may replace the reference's
+ * three rounded float operations acc * src_scale * flt_scale / dst_scale
+ * (compiler/lib/KernelGen/BareMetal/Activation.cpp:105-113) by ONE fused multiply-add trunc(fma(acc, c, +-0.49999997)), but
+ * only with a constant c for which the library has compared the final int8 of both forms
+ * on every accumulator value between the two saturation points (beyond them both forms are
+ * saturated, by monotonicity). Returns that c, or 0 when no candidate passed, the range is
+ * too long to walk, a scale is not positive or the activation is H_SWISH; the kernels then
+ * keep the three-step form. Results are cached per scale triple. */
+MB200_API float mb200_requant_fast_constant(
+        float src_scale, float flt_scale, float dst_scale, int nonline);
+
 /* ---- MatrixMul int8 x int8 -> int32 (C = A[M][K] * B[K][N], row-major), and the same with
  * the int32 product requantised to qint8 by the TypeCvt rule val * acc_scale / dst_scale
  * (compiler/lib/KernelGen/BareMetal/Typecvt.cpp:91-96). The reference has an int8 MatrixMul

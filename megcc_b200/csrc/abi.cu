@@ -329,6 +329,10 @@ int mb200_conv_bias_qs8_nchw(
     return launch_transpose_s8(ws_dst, dst, a.n, a.oh * a.ow, a.oc, st);
 }
 
+float mb200_requant_fast_constant(float src_scale, float flt_scale, float dst_scale, int nonline) {
+    return requant_fast_constant(src_scale, flt_scale, dst_scale, nonline);
+}
+
 // ---- int8 matrix product: a 1x1 ConvBias over M "pixels" with K channels ----
 static int matmul_args(int m, int n, int k, ConvArgs* a) {
     if (m <= 0 || n <= 0 || k <= 0)

@@ -15,6 +15,10 @@ struct EpilogueParams {
     // one saturating conversion does round-to-int and clamp together
     int bounded;
     float s_src, s_flt, s_dst, inv_dst;
+    // non-zero: a single multiplier that the host has checked, accumulator value by value,
+    // to give the same int8 as the three-step chain (requant_verify.cu); per-tensor scales,
+    // IDENTITY / RELU only
+    float fast_mul;
     const int32_t* bias;
     const float* flt_scales;
     // Optional fused quantised elementwise step (the residual add of a ResNet block): the
@@ -57,6 +61,11 @@ __device__ __forceinline__ int requant_one(
 }
 
 // ---- two floats per instruction (sm_100 f32x2 forms; each half is the IEEE RN operation) ----
+// CAUTION: unlike the scalar intrinsics, a packed multiply whose result feeds a packed add IS
+// contracted into a fused multiply-add by the assembler (explicit .rn and -fmad=false
+// notwithstanding). Sequences here are multiply -> multiply, multiply -> fma, fma -> add,
+// none of which can be contracted; where a product must be rounded before it is added, the
+// scalar intrinsics are used.
 __device__ __forceinline__ uint64_t f2_pack(float a, float b) {
     uint64_t r;
     asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
@@ -119,6 +128,27 @@ __device__ __forceinline__ void requant_pair(
     asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(y1));
 }
 
+// The verified form (EpilogueParams::fast_mul) on two accumulators: ONE fused multiply-add,
+// trunc(fma((float)acc, c, +-0.49999997)), saturated. It is written as an explicit fma because
+// the assembler contracts a packed multiply followed by a packed add into one anyway (seen on
+// a tie: 15000 * 1e-4f + 0.49999997f is 2.0 in two steps and 1.9999999 fused), and the host's
+// value-by-value check (requant_verify.cu) evaluates exactly this fused form.
+template <int ACT>
+__device__ __forceinline__ void requant_pair_fast(
+        int acc0, int acc1, uint64_t mul2, uint64_t half2, int& q0, int& q1) {
+    const float f0 = __int2float_rn(acc0), f1 = __int2float_rn(acc1);
+    const uint64_t f = f2_pack(f0, f1);
+    const uint64_t y =
+            ACT == ACT_RELU
+                    ? f2_fma(f, mul2, half2)
+                    : f2_fma(f, mul2,
+                             f2_pack(copysignf(0.49999997f, f0), copysignf(0.49999997f, f1)));
+    float y0, y1;
+    f2_unpack(y, y0, y1);
+    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(y0));
+    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(y1));
+}
+
 // four packed int8: bytes below zero become zero (byte-wise sign masks from PRMT)
 __device__ __forceinline__ uint32_t relu_s8x4(uint32_t p) {
     // selector nibbles 8..B: bytes 0..3 with bit 3 set, which replicates the byte's sign bit
@@ -145,31 +175,8 @@ __device__ __forceinline__ int fuse_z(int conv_q, int zv, const EpilogueParams& 
     return q;
 }
 
-// fuse_z on two values at once (same float operations, both halves)
-template <int ZMODE>
-__device__ __forceinline__ void fuse_z_pair(
-        int& q0, int& q1, int z0, int z1, uint64_t s_dst2, uint64_t z_scale2, uint64_t z_div2) {
-    const uint64_t a = f2_mul(s_dst2, f2_pack(__int2float_rn(q0), __int2float_rn(q1)));
-    const uint64_t b = f2_mul(z_scale2, f2_pack(__int2float_rn(z0), __int2float_rn(z1)));
-    uint64_t t = f2_add(a, b);
-    if (ZMODE == 2) {
-        float t0, t1;
-        f2_unpack(t, t0, t1);
-        t = f2_pack(t0 > 0.f ? t0 : 0.f, t1 > 0.f ? t1 : 0.f);
-    }
-    const uint64_t x = f2_mul(t, z_div2);
-    float x0, x1;
-    f2_unpack(x, x0, x1);
-    const uint64_t y =
-            f2_add(x, f2_pack(copysignf(0.49999997f, x0), copysignf(0.49999997f, x1)));
-    float y0, y1;
-    f2_unpack(y, y0, y1);
-    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(y0));
-    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(y1));
-}
-
 // NV = 16 or 32 accumulators (consecutive channels from ch0) of one output pixel
-template <int NV, int ACT, bool PER_CHANNEL, bool BOUNDED, int ZMODE>
+template <int NV, int ACT, bool PER_CHANNEL, bool BOUNDED, int ZMODE, bool FAST = false>
 __device__ __forceinline__ void epilogue_store_t(
         const uint32_t (&v)[NV], const EpilogueParams& e, int8_t* out, const int8_t* zin,
         int ch0) {
@@ -188,10 +195,10 @@ __device__ __forceinline__ void epilogue_store_t(
             }
         }
         constexpr bool kPaired = BOUNDED && !PER_CHANNEL && ACT != ACT_H_SWISH;
+        static_assert(!FAST || kPaired, "the verified form exists for the paired path only");
+        const uint64_t fast2 = f2_pack(e.fast_mul, e.fast_mul);
         static_assert(ZMODE == 0 || ACT == ACT_IDENTITY, "the fused step follows a plain ConvBias");
         const RequantPair rp(e);
-        const uint64_t s_dst2 = f2_pack(e.s_dst, e.s_dst), z_scale2 = f2_pack(e.z_scale, e.z_scale),
-                       z_div2 = f2_pack(e.z_div, e.z_div);
 #pragma unroll
         for (int j = 0; j < NV / 4; ++j) {
             int4 b = make_int4(0, 0, 0, 0);
@@ -199,13 +206,22 @@ __device__ __forceinline__ void epilogue_store_t(
                 b = __ldg(reinterpret_cast<const int4*>(e.bias + ch0) + j);
             if (kPaired) {
                 int r0, r1, r2, r3;
-                requant_pair<ACT>((int)v[j * 4 + 0] + b.x, (int)v[j * 4 + 1] + b.y, rp, r0, r1);
-                requant_pair<ACT>((int)v[j * 4 + 2] + b.z, (int)v[j * 4 + 3] + b.w, rp, r2, r3);
+                if (FAST) {
+                    requant_pair_fast<ACT>((int)v[j * 4 + 0] + b.x, (int)v[j * 4 + 1] + b.y, fast2,
+                                           rp.half, r0, r1);
+                    requant_pair_fast<ACT>((int)v[j * 4 + 2] + b.z, (int)v[j * 4 + 3] + b.w, fast2,
+                                           rp.half, r2, r3);
+                } else {
+                    requant_pair<ACT>((int)v[j * 4 + 0] + b.x, (int)v[j * 4 + 1] + b.y, rp, r0, r1);
+                    requant_pair<ACT>((int)v[j * 4 + 2] + b.z, (int)v[j * 4 + 3] + b.w, rp, r2, r3);
+                }
                 if (ZMODE != 0) {
-                    fuse_z_pair<ZMODE>(r0, r1, (int)(int8_t)(zw[j]), (int)(int8_t)(zw[j] >> 8),
-                                       s_dst2, z_scale2, z_div2);
-                    fuse_z_pair<ZMODE>(r2, r3, (int)(int8_t)(zw[j] >> 16),
-                                       (int)(int8_t)(zw[j] >> 24), s_dst2, z_scale2, z_div2);
+                    // scalar operations with explicit rounding: a packed multiply feeding a
+                    // packed add would be contracted, and this sum must not be
+                    r0 = fuse_z<ZMODE>(r0, (int)(int8_t)(zw[j]), e);
+                    r1 = fuse_z<ZMODE>(r1, (int)(int8_t)(zw[j] >> 8), e);
+                    r2 = fuse_z<ZMODE>(r2, (int)(int8_t)(zw[j] >> 16), e);
+                    r3 = fuse_z<ZMODE>(r3, (int)(int8_t)(zw[j] >> 24), e);
                 }
                 const uint32_t pk = umma::pack4_prmt(r0, r1, r2, r3);
                 packed[j] = (ACT == ACT_RELU && ZMODE == 0) ? relu_s8x4(pk) : pk;
@@ -279,6 +295,19 @@ __device__ __forceinline__ void epilogue_store(
     }
     int8_t* out = dst + off;
     const bool pc = e.flt_scales != nullptr;
+    if (e.fast_mul != 0.f) {
+        // set by the host only together with `bounded`, per-tensor scales, IDENTITY / RELU
+        const int8_t* zin = e.z_mode != 0 ? e.z + off : nullptr;
+        if (e.z_mode == 1)
+            epilogue_store_t<NV, ACT_IDENTITY, false, true, 1, true>(v, e, out, zin, ch0);
+        else if (e.z_mode == 2)
+            epilogue_store_t<NV, ACT_IDENTITY, false, true, 2, true>(v, e, out, zin, ch0);
+        else if (e.act == ACT_RELU)
+            epilogue_store_t<NV, ACT_RELU, false, true, 0, true>(v, e, out, nullptr, ch0);
+        else
+            epilogue_store_t<NV, ACT_IDENTITY, false, true, 0, true>(v, e, out, nullptr, ch0);
+        return;
+    }
     if (e.z_mode != 0) {
         // the fused form follows a ConvBias without activation
         const int8_t* zin = e.z + off;

@@ -532,6 +532,11 @@ int launch_conv_patch(
     p.ep.s_flt = a.s_flt;
     p.ep.s_dst = a.s_dst;
     p.ep.inv_dst = 1.0f / a.s_dst;  // correctly rounded on the host
+    // a fused step follows a ConvBias without activation
+    p.ep.fast_mul = (p.ep.bounded && !flt_scales)
+                            ? requant_fast_constant(a.s_src, a.s_flt, a.s_dst,
+                                                    (a.z && a.z_mode) ? ACT_IDENTITY : a.act)
+                            : 0.f;
     p.ep.bias = bias;
     p.ep.flt_scales = flt_scales;
     p.ep.z = a.z;

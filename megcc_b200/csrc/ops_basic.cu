@@ -175,6 +175,56 @@ __global__ void __launch_bounds__(256) pooling_max_vec16_kernel(
     }
 }
 
+// MAX pooling with a 3x3 window and stride 2 (the ResNet stem's pool), 16 channels per
+// thread and TWO horizontally adjacent outputs per thread: their windows share a column, so
+// 15 loads serve both (instead of 18), all issued before the first use. 32-bit index
+// arithmetic (the launcher checks the sizes). The kernel is bound by HBM: every input byte
+// is read once from DRAM, the re-reads between neighbouring threads hit L1 / L2.
+__device__ __forceinline__ uint4 vmax16(uint4 a, uint4 b) {
+    return make_uint4(__vmaxs4(a.x, b.x), __vmaxs4(a.y, b.y), __vmaxs4(a.z, b.z),
+                      __vmaxs4(a.w, b.w));
+}
+
+__global__ void __launch_bounds__(256) pooling_max_3x3s2_vec16_kernel(
+        const uint4* __restrict__ src, uint4* __restrict__ dst, int n, int c16, int ih, int iw,
+        int oh, int ow, int ph, int pw) {
+    const int owp = (ow + 1) / 2;  // output pairs per row
+    const unsigned total = (unsigned)n * oh * owp * c16;
+    const uint4 lowest = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // -128
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += gridDim.x * blockDim.x) {
+        const unsigned cv = idx % c16;
+        unsigned t = idx / c16;
+        const int xp = (int)(t % owp);
+        t /= owp;
+        const int y = (int)(t % oh);
+        const int b = (int)(t / oh);
+        const int x0 = 2 * xp;
+        const int ix0 = 2 * x0 - pw, iy0 = 2 * y - ph;
+        uint4 v[3][5];
+#pragma unroll
+        for (int fy = 0; fy < 3; ++fy) {
+            const int iy = iy0 + fy;
+            const bool row_ok = (unsigned)iy < (unsigned)ih;
+            const uint4* row = src + ((size_t)((unsigned)b * ih + (row_ok ? iy : 0)) * iw) * c16 + cv;
+#pragma unroll
+            for (int fx = 0; fx < 5; ++fx) {
+                const int ix = ix0 + fx;
+                v[fy][fx] = (row_ok && (unsigned)ix < (unsigned)iw) ? __ldg(row + (size_t)ix * c16)
+                                                                     : lowest;
+            }
+        }
+        uint4 col[5];
+#pragma unroll
+        for (int fx = 0; fx < 5; ++fx)
+            col[fx] = vmax16(vmax16(v[0][fx], v[1][fx]), v[2][fx]);
+        uint4* out = dst + ((size_t)((unsigned)b * oh + y) * ow + x0) * c16 + cv;
+        out[0] = vmax16(vmax16(col[0], col[1]), col[2]);
+        if (x0 + 1 < ow)
+            out[c16] = vmax16(vmax16(col[2], col[3]), col[4]);
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // quantised elementwise, same-shape operands, 16 bytes per thread
 // ------------------------------------------------------------------------------------------
@@ -300,7 +350,16 @@ int launch_pooling(
         int sh, int sw, int ph, int pw, cudaStream_t st) {
     const int oh = (ih + 2 * ph - wh) / sh + 1, ow = (iw + 2 * pw - ww) / sw + 1;
     const size_t total = (size_t)n * oh * ow * c;
-    if (mode == 0 && c % 16 == 0 && ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0)) {
+    const bool vec16 = mode == 0 && c % 16 == 0 && ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0);
+    if (vec16 && wh == 3 && ww == 3 && sh == 2 && sw == 2 && ph <= 2 && pw <= 2 &&
+        (size_t)n * ih * iw * (c / 16) < (1u << 30) && oh > 0 && ow > 0) {
+        // a window with no valid element cannot occur: padding is below the window size
+        const size_t pairs = (size_t)n * oh * ((ow + 1) / 2) * (c / 16);
+        pooling_max_3x3s2_vec16_kernel<<<grid_for(pairs, 256), 256, 0, st>>>(
+                (const uint4*)src, (uint4*)dst, n, c / 16, ih, iw, oh, ow, ph, pw);
+        return check_launch("pooling_max_3x3s2_vec16");
+    }
+    if (vec16) {
         pooling_max_vec16_kernel<<<grid_for(total / 16, 256), 256, 0, st>>>(
                 (const uint4*)src, (uint4*)dst, n, c / 16, ih, iw, oh, ow, wh, ww, sh, sw, ph, pw);
         return check_launch("pooling_max_vec16");

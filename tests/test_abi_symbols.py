@@ -47,3 +47,53 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libmegcc_b200.so")
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.lib()
+
+
+def test_verified_requant_constant_agrees_with_the_reference_chain():
+    """mb200_requant_fast_constant (host only): the one-FMA requantisation it licenses must
+    give the reference's int8 on every accumulator; checked here independently, with exact
+    rational arithmetic for the fused multiply-add, on all near-tie accumulators (those whose
+    scaled value lies within 1e-4 of a half-integer), a dense band around zero, and the
+    saturation edges."""
+    import ctypes
+    from fractions import Fraction
+    import numpy as np
+    from megcc_b200._lib import lib
+    f32 = np.float32
+
+    def to_f32(fr):  # correctly rounded Fraction -> float32 (via float64 is exact enough here:
+        # the values are sums of a 48-bit product and a 24-bit constant, far from float64 ties)
+        return f32(float(fr))
+
+    found = 0
+    for s_src, s_flt, s_dst, act in [(0.05, 0.01, 2.0, 1), (0.05, 0.01, 5.0, 1),
+                                     (0.0473, 0.00731, 0.1931, 1), (0.02, 0.01, 0.5, 0),
+                                     (0.05, 0.01, 0.77, 0), (0.3, 0.2, 0.01, 1)]:
+        c = lib().mb200_requant_fast_constant(s_src, s_flt, s_dst, act)
+        if c == 0.0:
+            continue
+        found += 1
+        ratio = float(f32(s_src)) * float(f32(s_flt)) / float(f32(s_dst))
+        r = int(130 / ratio) + 4
+        acc = np.arange(-r, r + 1, dtype=np.int64)
+        frac = np.abs((acc * ratio) % 1.0 - 0.5)
+        pick = np.unique(np.concatenate([acc[frac < 1e-4], np.arange(-3000, 3001),
+                                         acc[:50], acc[-50:], np.array([-2**31, 2**31 - 1])]))
+        a = pick.astype(np.float32)
+        t = (a * f32(s_src)).astype(np.float32) * f32(s_flt)
+        x = (t.astype(np.float32) / f32(s_dst)).astype(np.float32)
+        if act == 1:
+            x = np.maximum(x, f32(0))
+        want = np.clip(np.sign(x) * np.floor(np.abs(x.astype(np.float64)) + 0.5), -128, 127)
+        half = Fraction(float(f32(0.49999997)))
+        got = []
+        for v in a:
+            h = half if (act == 1 or v >= 0) else -half
+            y = to_f32(Fraction(float(v)) * Fraction(float(f32(c))) + h)
+            q = int(np.clip(np.trunc(y), -128, 127))
+            got.append(max(q, 0) if act == 1 else q)
+        assert (np.array(got) == want).all(), (s_src, s_flt, s_dst, act)
+    assert found >= 3
+    # no licence without positive scales, nor for H_SWISH
+    assert lib().mb200_requant_fast_constant(0.05, -0.01, 2.0, 1) == 0.0
+    assert lib().mb200_requant_fast_constant(0.05, 0.01, 2.0, 2) == 0.0

@@ -279,6 +279,20 @@ def test_pooling_golden(ops):
         G.check("pooling_qs8", c["name"], out, x)
 
 
+@pytest.mark.parametrize("shape", [(3, 32, 13, 13, 1), (2, 16, 15, 9, 0), (1, 48, 6, 31, 1),
+                                   (2, 64, 112, 112, 1)],
+                         ids=["odd_out_pad1", "nopad", "wide_row", "stem"])
+def test_max_pool_3x3_stride2_matches_oracle(ops, oracle, shape):
+    """The two-outputs-per-thread kernel of the ResNet stem's pool: odd output widths (a last
+    pair with one output), windows that hang over every border."""
+    n, c, h, w, pad = shape
+    x = cases.rng_for("pool3x3s2_%d_%d_%d_%d_%d" % shape).integers(-128, 128, (n, c, h, w),
+                                                                  dtype=np.int8)
+    y = ops.pooling_qs8_nhwc(ops.nchw_to_nhwc(dev(x)), "MAX", 3, 2, pad)
+    out = ops.nhwc_to_nchw(y).cpu().numpy()
+    assert (out == oracle.pooling_qs8(x, "MAX", 3, 2, pad)).all()
+
+
 def test_qelemwise_golden(ops):
     for c in cases.qelem_catalogue():
         if c["a"] != c["b"]:
