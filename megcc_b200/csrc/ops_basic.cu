@@ -225,6 +225,40 @@ __global__ void __launch_bounds__(256) pooling_max_3x3s2_vec16_kernel(
     }
 }
 
+// AVERAGE pooling over the whole image (the classifier's global pool), 16 channels per thread:
+// wh * ww vector loads, sixteen int sums, then roundf((float)sum / count) as pooling_kernel.
+__global__ void __launch_bounds__(128) pooling_global_avg_vec16_kernel(
+        const uint4* __restrict__ src, uint4* __restrict__ dst, int n, int c16, int pixels) {
+    const unsigned total = (unsigned)n * c16;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += gridDim.x * blockDim.x) {
+        const unsigned cv = idx % c16, b = idx / c16;
+        const uint4* p = src + (size_t)b * pixels * c16 + cv;
+        int sum[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            sum[i] = 0;
+        for (int px = 0; px < pixels; ++px) {
+            const uint4 v = __ldg(p + (size_t)px * c16);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                sum[i] += (int)(int8_t)(w[i >> 2] >> (8 * (i & 3)));
+        }
+        const float d = (float)pixels;
+        uint32_t o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            int r[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                r[i] = f32_to_i32_x86(roundf(__fdiv_rn(__int2float_rn(sum[k * 4 + i]), d)));
+            o[k] = pack4(r[0], r[1], r[2], r[3]);
+        }
+        dst[idx] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // quantised elementwise, same-shape operands, 16 bytes per thread
 // ------------------------------------------------------------------------------------------
@@ -358,6 +392,14 @@ int launch_pooling(
         pooling_max_3x3s2_vec16_kernel<<<grid_for(pairs, 256), 256, 0, st>>>(
                 (const uint4*)src, (uint4*)dst, n, c / 16, ih, iw, oh, ow, ph, pw);
         return check_launch("pooling_max_3x3s2_vec16");
+    }
+    if (mode != 0 && c % 16 == 0 && ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0) && wh == ih &&
+        ww == iw && ph == 0 && pw == 0 && (size_t)n * (c / 16) < (1u << 31)) {
+        // one window per image and no padding: both AVERAGE modes divide by wh * ww
+        const size_t work = (size_t)n * (c / 16);
+        pooling_global_avg_vec16_kernel<<<grid_for(work, 128), 128, 0, st>>>(
+                (const uint4*)src, (uint4*)dst, n, c / 16, ih * iw);
+        return check_launch("pooling_global_avg_vec16");
     }
     if (vec16) {
         pooling_max_vec16_kernel<<<grid_for(total / 16, 256), 256, 0, st>>>(

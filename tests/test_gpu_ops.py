@@ -293,6 +293,18 @@ def test_max_pool_3x3_stride2_matches_oracle(ops, oracle, shape):
     assert (out == oracle.pooling_qs8(x, "MAX", 3, 2, pad)).all()
 
 
+@pytest.mark.parametrize("mode", ["AVERAGE", "AVERAGE_COUNT_EXCLUDE_PADDING"])
+def test_global_average_pool_matches_oracle(ops, oracle, mode):
+    """One window per image (the classifier's pool): sums of 25 int8 values whose mean hits
+    many .5 ties, which must round away from zero as the reference's roundf does."""
+    x = cases.rng_for("gap_" + mode).integers(-128, 128, (5, 48, 5, 5), dtype=np.int8)
+    x[0, :, :, :] = 127
+    x[1, :, :, :] = -128
+    y = ops.pooling_qs8_nhwc(ops.nchw_to_nhwc(dev(x)), mode, 5, 5, 0)
+    out = ops.nhwc_to_nchw(y).cpu().numpy()
+    assert (out == oracle.pooling_qs8(x, mode, 5, 5, 0)).all()
+
+
 def test_qelemwise_golden(ops):
     for c in cases.qelem_catalogue():
         if c["a"] != c["b"]:
