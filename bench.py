@@ -10,7 +10,8 @@ one forward of a 256-image batch through the compiled model:
             (CUDA-graph replay through LITE_forward / LITE_wait), timed with CUDA events on
             the network's stream, max over ranks
   e2e       the same through the host-buffer boundary a LITE_* user sees: pinned host input
-            copied in and logits copied out inside every timed step
+            copied in and logits copied out inside every timed step; two LiteNetworks
+            alternate so that one step's input copy overlaps the previous step's compute
   roofline  the tcgen05 ConvBias kernel: algorithmic int8 ops of every launch / its CUDA
             event time, against 2 x the measured bf16 tensor peak
   cpu_baseline  the reference's own generated x86 kernels (oracle/_ref) walking the same
@@ -240,28 +241,48 @@ def main():
     ms_dev = max_over_ranks(e0.elapsed_time(e1))
 
     # ---- end-to-end arm: pinned host input in, logits out, every step ----
-    net2 = lite.Network(model, device_id=local_rank)
-    out_bytes = net2.tensor_bytes("fc:out", lite.LITE_OUTPUT)
-    net2.set_input_ptr("data", x_host.data_ptr(), in_bytes)
-    stream2 = torch.cuda.ExternalStream(net2.stream())
-    for _ in range(max(args.warmup, 3)):
-        net2.forward()
-        net2.wait()
+    # Two LiteNetworks of the same model alternate, each with its own stream, arena and pinned
+    # input buffer: LITE_forward only enqueues (copy in, graph, copy out), so the host-to-device
+    # copy of step i+1 runs while step i computes. Every step still copies its 38.5 MB in and
+    # its logits out inside the timed region, and the host reads each step's result.
+    nets = [lite.Network(model, device_id=local_rank) for _ in range(2)]
+    out_bytes = nets[0].tensor_bytes("fc:out", lite.LITE_OUTPUT)
+    x_hosts = [x_host, x_host.clone().pin_memory()]
+    for n, xh in zip(nets, x_hosts):
+        n.set_input_ptr("data", xh.data_ptr(), in_bytes)
+    streams2 = [torch.cuda.ExternalStream(n.stream()) for n in nets]
+    for n in nets:
+        for _ in range(max(args.warmup, 3)):
+            n.forward()
+            n.wait()
     barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0 = torch.cuda.Event(enable_timing=True)
+    f_end = [torch.cuda.Event(enable_timing=True) for _ in nets]
     checksum = 0
+
+    def collect(n):
+        n.wait()
+        return int(np.frombuffer(
+            (lite.C.c_int8 * 8).from_address(n.output_ptr("fc:out")), dtype=np.int8)[0])
+
     w2 = time.perf_counter()
-    f0.record(stream2)
-    for _ in range(args.steps):
-        net2.forward()
-        net2.wait()
-        checksum ^= int(np.frombuffer(
-            (lite.C.c_int8 * 8).from_address(net2.output_ptr("fc:out")), dtype=np.int8)[0])
-    f1.record(stream2)
-    f1.synchronize()
+    f0.record(streams2[0])
+    pending = None
+    for i in range(args.steps):
+        n = nets[i % 2]
+        n.forward()
+        if pending is not None:
+            checksum ^= collect(pending)
+        pending = n
+    for ev, st in zip(f_end, streams2):
+        ev.record(st)
+    checksum ^= collect(pending)
+    for ev in f_end:
+        ev.synchronize()
     w3 = time.perf_counter()
     barrier()
-    ms_e2e = max_over_ranks(f0.elapsed_time(f1))
+    f1_ms = max(f0.elapsed_time(ev) for ev in f_end)
+    ms_e2e = max_over_ranks(f1_ms)
     clocks = sampler.stop([(w0, w1), (w2, w3)])
 
     # ---- per-kernel pass for the roofline of the dominant kernel ----
@@ -306,7 +327,8 @@ def main():
             value=ips_cpu, unit=UNIT, cores=threads, kind=kind,
             sample=f"2 steps x {threads} images (one per thread), 1 warm-up step")
     net.close()
-    net2.close()
+    for n in nets:
+        n.close()
     group.close()
     if rank != 0:
         return

@@ -135,16 +135,12 @@ __device__ __forceinline__ void requant_pair(
 // value-by-value check (requant_verify.cu) evaluates exactly this fused form.
 template <int ACT>
 __device__ __forceinline__ void requant_pair_fast(
-        int acc0, int acc1, uint64_t mul2, uint64_t half2, int& q0, int& q1) {
+        int acc0, int acc1, float mul, int& q0, int& q1) {
+    // scalar fused multiply-adds: the packed form would need the two converted values moved
+    // into a register pair and the results moved out again, which costs more than it saves
     const float f0 = __int2float_rn(acc0), f1 = __int2float_rn(acc1);
-    const uint64_t f = f2_pack(f0, f1);
-    const uint64_t y =
-            ACT == ACT_RELU
-                    ? f2_fma(f, mul2, half2)
-                    : f2_fma(f, mul2,
-                             f2_pack(copysignf(0.49999997f, f0), copysignf(0.49999997f, f1)));
-    float y0, y1;
-    f2_unpack(y, y0, y1);
+    const float y0 = __fmaf_rn(f0, mul, ACT == ACT_RELU ? 0.49999997f : copysignf(0.49999997f, f0));
+    const float y1 = __fmaf_rn(f1, mul, ACT == ACT_RELU ? 0.49999997f : copysignf(0.49999997f, f1));
     asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(y0));
     asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(y1));
 }
@@ -196,7 +192,6 @@ __device__ __forceinline__ void epilogue_store_t(
         }
         constexpr bool kPaired = BOUNDED && !PER_CHANNEL && ACT != ACT_H_SWISH;
         static_assert(!FAST || kPaired, "the verified form exists for the paired path only");
-        const uint64_t fast2 = f2_pack(e.fast_mul, e.fast_mul);
         static_assert(ZMODE == 0 || ACT == ACT_IDENTITY, "the fused step follows a plain ConvBias");
         const RequantPair rp(e);
 #pragma unroll
@@ -207,10 +202,10 @@ __device__ __forceinline__ void epilogue_store_t(
             if (kPaired) {
                 int r0, r1, r2, r3;
                 if (FAST) {
-                    requant_pair_fast<ACT>((int)v[j * 4 + 0] + b.x, (int)v[j * 4 + 1] + b.y, fast2,
-                                           rp.half, r0, r1);
-                    requant_pair_fast<ACT>((int)v[j * 4 + 2] + b.z, (int)v[j * 4 + 3] + b.w, fast2,
-                                           rp.half, r2, r3);
+                    requant_pair_fast<ACT>((int)v[j * 4 + 0] + b.x, (int)v[j * 4 + 1] + b.y,
+                                           e.fast_mul, r0, r1);
+                    requant_pair_fast<ACT>((int)v[j * 4 + 2] + b.z, (int)v[j * 4 + 3] + b.w,
+                                           e.fast_mul, r2, r3);
                 } else {
                     requant_pair<ACT>((int)v[j * 4 + 0] + b.x, (int)v[j * 4 + 1] + b.y, rp, r0, r1);
                     requant_pair<ACT>((int)v[j * 4 + 2] + b.z, (int)v[j * 4 + 3] + b.w, rp, r2, r3);

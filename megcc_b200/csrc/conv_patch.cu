@@ -58,6 +58,41 @@ struct PatchParams {
     int* status;
 };
 
+// Position of a CTA's current patch (image, patch row, patch column) and the step to its
+// next one, kept as three counters with carries: one division at the start, none per tile.
+// (With 64 output channels an epilogue warp does one 32-column chunk per tile, so whatever
+// the tile decode costs is paid per chunk.)
+struct PatchWalker {
+    int img, ty, tx;
+    int s_img, s_ty, s_tx;
+    int tiles_y, tiles_x;
+    __device__ __forceinline__ PatchWalker(int first, int step, int ty_n, int tx_n)
+            : tiles_y(ty_n), tiles_x(tx_n) {
+        const int per_image = ty_n * tx_n;
+        img = first / per_image;
+        int r = first - img * per_image;
+        ty = r / tx_n;
+        tx = r - ty * tx_n;
+        s_img = step / per_image;
+        r = step - s_img * per_image;
+        s_ty = r / tx_n;
+        s_tx = r - s_ty * tx_n;
+    }
+    __device__ __forceinline__ void next() {
+        tx += s_tx;
+        if (tx >= tiles_x) {
+            tx -= tiles_x;
+            ++ty;
+        }
+        ty += s_ty;
+        if (ty >= tiles_y) {
+            ty -= tiles_y;
+            ++img;
+        }
+        img += s_img;
+    }
+};
+
 // One tile's MMAs. The issuing thread runs alone in its warp and every instruction of its
 // loop costs it several cycles, so the hot filter shapes get their own instantiation
 // (KH > 0) where every operand offset is a compile-time constant: two adds per MMA. Looking
@@ -154,7 +189,6 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
     const int m_first = blockIdx.x / p.n_tiles;
     const int m_step = gridDim.x / p.n_tiles;
     const int n0 = tile_n * BN;
-    const int tiles_per_image = p.tiles_y * p.tiles_x;
     const int plane = p.plane_stride;
 
     if (threadIdx.x == 0) {
@@ -199,7 +233,8 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
             }
             int s = 0;
             uint32_t phase = 0;
-            for (int mt = m_first; mt < p.m_tiles; mt += m_step) {
+            PatchWalker at(m_first, m_step, p.tiles_y, p.tiles_x);
+            for (int mt = m_first; mt < p.m_tiles; mt += m_step, at.next()) {
                 if (!mbar_wait(&a_empty[s], phase ^ 1u, abort_flag)) {
                     if (!*abort_flag) {
                         *abort_flag = 1;
@@ -207,10 +242,8 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
                     }
                     break;
                 }
-                const int img = mt / tiles_per_image;
-                const int rem = mt - img * tiles_per_image;
-                const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
-                const int x0 = tx * kTW - p.pw, y0 = ty * kTH - p.ph;
+                const int img = at.img;
+                const int x0 = at.tx * kTW - p.pw, y0 = at.ty * kTH - p.ph;
                 mbar_expect_tx(&a_full[s], (uint32_t)p.a_tx_bytes);
                 // one request: box {16 B, patch columns, patch rows, 1 image, all chunks}
                 tma_load_5d(smem_a + s * p.a_stage_bytes, &map_a, &a_full[s], 0, x0, y0, img, 0);
@@ -269,7 +302,8 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
         const int py = row >> 3, px = row & 7;
         int local = 0;
         bool ok = true;
-        for (int mt = m_first; mt < p.m_tiles && ok; mt += m_step, ++local) {
+        PatchWalker at(m_first, m_step, p.tiles_y, p.tiles_x);
+        for (int mt = m_first; mt < p.m_tiles && ok; mt += m_step, ++local, at.next()) {
             const int buf = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             ok = mbar_wait(&acc_full[buf], acc_phase, abort_flag);
@@ -281,12 +315,11 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
             if (!ok)
                 break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int img = mt / tiles_per_image;
-            const int rem = mt - img * tiles_per_image;
-            const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
-            const int oy = ty * kTH + py, ox = tx * kTW + px;
+            const int oy = at.ty * kTH + py, ox = at.tx * kTW + px;
             const bool valid = oy < p.oh && ox < p.ow;
-            const size_t px_off = (((size_t)img * p.oh + oy) * p.ow + ox) * p.oc;
+            // the pixel index fits 32 bits (the launcher checks); one wide multiply
+            const uint32_t pixel = ((uint32_t)at.img * p.oh + oy) * p.ow + ox;
+            const size_t px_off = (size_t)pixel * p.oc;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             // the warps of one lane quarter interleave over its 32-column chunks
             const int half = (warp - 2) >> 2;
@@ -431,6 +464,8 @@ bool conv_patch_supported(
     if (!plan_patch(a).ok)
         return false;
     if ((size_t)a.n * a.ih * a.iw * a.ic < 131072)
+        return false;
+    if ((size_t)a.n * a.oh * a.ow >= (1ull << 31))
         return false;
     if (((uintptr_t)src | (uintptr_t)flt | (uintptr_t)dst) & 15)
         return false;

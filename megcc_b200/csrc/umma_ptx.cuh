@@ -59,15 +59,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(
         uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 8; ++i)
         if (mbar_try_wait(bar, parity))
             return true;
     const long long t0 = clock64();
+    unsigned ns = 20;
     for (int spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity))
             return true;
-        if (spin > 256)
-            __nanosleep(128);
+        __nanosleep(ns);
+        if (ns < 160)
+            ns *= 2;
         if ((spin & 63) == 63) {
             if (*abort_flag)
                 return false;
