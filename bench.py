@@ -193,6 +193,8 @@ def main():
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
     torch.cuda.set_device(local_rank)
+    # host staging next to the GPU: the end-to-end arm is bound by the input copy
+    affinity_before = shard.bind_to_gpu_cpus(local_rank)
     group = shard.Group("nccl", torch.device("cuda", local_rank))
 
     def barrier():
@@ -322,6 +324,8 @@ def main():
             peak_note=f"2 x bf16 sustained ({peaks['source']}); int8 dense peak is not in "
                       "MEASURED_PEAKS.json",
             per_kernel_ms={n: round(ms, 4) for n, s, ms, c in rows})
+        if affinity_before is not None:
+            os.sched_setaffinity(0, affinity_before)  # the CPU leg uses every host core
         ips_cpu, sec, kind = cpu_reference_run(spec, 2, 1, threads)
         cpu_baseline = dict(
             value=ips_cpu, unit=UNIT, cores=threads, kind=kind,

@@ -54,58 +54,48 @@ __global__ void __launch_bounds__(256) space_to_depth_kernel(
     }
 }
 
-// The same for an NCHW source whose rows are a multiple of 16 bytes and 16-byte aligned: one
-// thread per 8 half-resolution pixels. It loads 16 bytes of each of the (up to 4) channel
-// planes for both image rows with vector loads and writes 8 consecutive 16-byte vectors, so
-// a warp reads 512-byte row segments and writes 4 KB in one piece.
-__global__ void __launch_bounds__(256) space_to_depth_nchw16_kernel(
+// The same for an NCHW source with an even width and an even base address: one thread per
+// half-resolution pixel again, but the two horizontally adjacent bytes of a channel row come
+// in one 16-bit load, so a warp's loads are contiguous 64-byte runs and its stores one
+// contiguous 512 bytes. 32-bit index arithmetic.
+__global__ void __launch_bounds__(256) space_to_depth_nchw2_kernel(
         const int8_t* __restrict__ src, uint4* __restrict__ dst, int n, int c, int h, int w,
         int h2, int w2) {
-    const int groups = w / 16;  // 8 half-resolution pixels each; w2 == w / 2
-    const unsigned total = (unsigned)n * h2 * groups;
+    const unsigned total = (unsigned)n * h2 * w2;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += gridDim.x * blockDim.x) {
-        const int xg = (int)(idx % groups);
-        unsigned t = idx / groups;
+        const int x2 = (int)(idx % w2);
+        unsigned t = idx / w2;
         const int y2 = (int)(t % h2);
         const int b = (int)(t / h2);
-        // rows[dy][ch]: 16 input bytes (zero where the image or the channel ends)
-        uint4 rows[2][4];
+        uint32_t pair[2][4];  // [dy][ch]: bytes (x, x+1) of one channel row
 #pragma unroll
         for (int dy = 0; dy < 2; ++dy) {
             const int y = 2 * y2 + dy;
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
-                rows[dy][ch] = make_uint4(0, 0, 0, 0);
+                pair[dy][ch] = 0;
                 if (ch < c && y < h)
-                    rows[dy][ch] = __ldg(reinterpret_cast<const uint4*>(
-                            src + (((size_t)b * c + ch) * h + y) * w + 16 * xg));
+                    pair[dy][ch] = __ldg(reinterpret_cast<const unsigned short*>(
+                            src + (((size_t)b * c + ch) * h + y) * w + 2 * x2));
             }
         }
-        uint4* out = dst + ((size_t)b * h2 + y2) * w2 + 8 * xg;
+        uint32_t words[4] = {0, 0, 0, 0};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            // input columns 2j, 2j+1 are bytes (2j & 3), (2j & 3) + 1 of word j / 2
-            uint32_t words[4] = {0, 0, 0, 0};
+        for (int dy = 0; dy < 2; ++dy) {
 #pragma unroll
-            for (int dy = 0; dy < 2; ++dy) {
+            for (int dx = 0; dx < 2; ++dx) {
 #pragma unroll
-                for (int dx = 0; dx < 2; ++dx) {
-#pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        if (ch < c) {
-                            const uint4 r = rows[dy][ch];
-                            const uint32_t wsel = (j >> 1) == 0 ? r.x : (j >> 1) == 1 ? r.y
-                                                  : (j >> 1) == 2 ? r.z : r.w;
-                            const uint32_t v = (wsel >> (8 * (((2 * j) & 3) + dx))) & 0xffu;
-                            const int slot = (dy * 2 + dx) * c + ch;
-                            words[slot >> 2] |= v << (8 * (slot & 3));
-                        }
+                for (int ch = 0; ch < 4; ++ch) {
+                    if (ch < c) {
+                        const uint32_t v = (pair[dy][ch] >> (8 * dx)) & 0xffu;
+                        const int slot = (dy * 2 + dx) * c + ch;
+                        words[slot >> 2] |= v << (8 * (slot & 3));
                     }
                 }
             }
-            out[j] = make_uint4(words[0], words[1], words[2], words[3]);
         }
+        dst[idx] = make_uint4(words[0], words[1], words[2], words[3]);
     }
 }
 
@@ -182,9 +172,9 @@ int launch_conv_s2d(
         sy = (long long)a.iw * a.ic;
         sn = sy * a.ih;
     }
-    if (a.src_is_nchw && a.iw % 16 == 0 && ((uintptr_t)src & 15) == 0 && g.w2 == a.iw / 2 &&
-        (size_t)a.n * g.h2 * (a.iw / 16) < (1u << 31)) {
-        space_to_depth_nchw16_kernel<<<grid_for((size_t)a.n * g.h2 * (a.iw / 16)), 256, 0, st>>>(
+    if (a.src_is_nchw && a.iw % 2 == 0 && ((uintptr_t)src & 1) == 0 && g.w2 == a.iw / 2 &&
+        (size_t)a.n * g.h2 * g.w2 < (1u << 31)) {
+        space_to_depth_nchw2_kernel<<<grid_for((size_t)a.n * g.h2 * g.w2), 256, 0, st>>>(
                 src, (uint4*)workspace, a.n, a.ic, a.ih, a.iw, g.h2, g.w2);
     } else {
         space_to_depth_kernel<<<grid_for((size_t)a.n * g.h2 * g.w2), 256, 0, st>>>(

@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(256) pooling_max_3x3s2_vec16_kernel(
 
 // AVERAGE pooling over the whole image (the classifier's global pool), 16 channels per thread:
 // wh * ww vector loads, sixteen int sums, then roundf((float)sum / count) as pooling_kernel.
-__global__ void __launch_bounds__(128) pooling_global_avg_vec16_kernel(
+__global__ void __launch_bounds__(64) pooling_global_avg_vec16_kernel(
         const uint4* __restrict__ src, uint4* __restrict__ dst, int n, int c16, int pixels) {
     const unsigned total = (unsigned)n * c16;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -238,12 +238,19 @@ __global__ void __launch_bounds__(128) pooling_global_avg_vec16_kernel(
 #pragma unroll
         for (int i = 0; i < 16; ++i)
             sum[i] = 0;
-        for (int px = 0; px < pixels; ++px) {
-            const uint4 v = __ldg(p + (size_t)px * c16);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        // seven loads in flight at a time (the accumulation would otherwise serialise them)
+        for (int px0 = 0; px0 < pixels; px0 += 7) {
+            uint4 v[7];
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-                sum[i] += (int)(int8_t)(w[i >> 2] >> (8 * (i & 3)));
+            for (int k = 0; k < 7; ++k)
+                v[k] = px0 + k < pixels ? __ldg(p + (size_t)(px0 + k) * c16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int k = 0; k < 7; ++k) {
+                const uint32_t w[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    sum[i] += (int)(int8_t)(w[i >> 2] >> (8 * (i & 3)));
+            }
         }
         const float d = (float)pixels;
         uint32_t o[4];
@@ -397,7 +404,7 @@ int launch_pooling(
         ww == iw && ph == 0 && pw == 0 && (size_t)n * (c / 16) < (1u << 31)) {
         // one window per image and no padding: both AVERAGE modes divide by wh * ww
         const size_t work = (size_t)n * (c / 16);
-        pooling_global_avg_vec16_kernel<<<grid_for(work, 128), 128, 0, st>>>(
+        pooling_global_avg_vec16_kernel<<<grid_for(work, 64), 64, 0, st>>>(
                 (const uint4*)src, (uint4*)dst, n, c / 16, ih * iw);
         return check_launch("pooling_global_avg_vec16");
     }

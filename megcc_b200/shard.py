@@ -70,3 +70,31 @@ class Group:
             self.dist.barrier()
             self.dist.destroy_process_group()
             self.dist = None
+
+
+def bind_to_gpu_cpus(device_index):
+    """Restrict this process to the CPUs next to GPU ``device_index`` (the PCI device's
+    ``local_cpulist`` in sysfs), so that pinned staging buffers allocated afterwards land on
+    the GPU's NUMA node. Returns the previous affinity set for ``os.sched_setaffinity`` to
+    restore, or None when nothing was changed (no sysfs entry, an empty list, no permission)."""
+    import os
+    try:
+        import torch
+        pr = torch.cuda.get_device_properties(device_index)
+        bdf = "%04x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        with open("/sys/bus/pci/devices/%s/local_cpulist" % bdf) as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            if not part:
+                continue
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        before = os.sched_getaffinity(0)
+        cpus &= before
+        if not cpus or cpus == before:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return before
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return None
