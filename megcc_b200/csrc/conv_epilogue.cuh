@@ -177,17 +177,29 @@ __device__ __forceinline__ void epilogue_store_t(
         const uint32_t (&v)[NV], const EpilogueParams& e, int8_t* out, const int8_t* zin,
         int ch0) {
     static_assert(NV == 16 || NV == 32, "16 or 32 channels per call");
-    if (ch0 + NV <= e.oc && (e.oc % 16) == 0) {
+    // a pixel's channels start at a multiple of oc bytes: 16-byte vectors when oc allows,
+    // 8-byte ones for oc % 8 == 0 (a 1000-class classifier), bytes otherwise
+    if (ch0 + NV <= e.oc && (e.oc % 8) == 0) {
+        const bool wide = (e.oc % 16) == 0;
         uint32_t packed[NV / 4];
         uint32_t zw[NV / 4];
 #pragma unroll
         for (int j = 0; j < NV / 4; ++j)
             zw[j] = 0;
         if (ZMODE != 0) {
+            if (wide) {
 #pragma unroll
-            for (int h = 0; h < NV / 16; ++h) {
-                const uint4 z0 = __ldg(reinterpret_cast<const uint4*>(zin) + h);
-                zw[h * 4 + 0] = z0.x; zw[h * 4 + 1] = z0.y; zw[h * 4 + 2] = z0.z; zw[h * 4 + 3] = z0.w;
+                for (int h = 0; h < NV / 16; ++h) {
+                    const uint4 z0 = __ldg(reinterpret_cast<const uint4*>(zin) + h);
+                    zw[h * 4 + 0] = z0.x; zw[h * 4 + 1] = z0.y;
+                    zw[h * 4 + 2] = z0.z; zw[h * 4 + 3] = z0.w;
+                }
+            } else {
+#pragma unroll
+                for (int h = 0; h < NV / 8; ++h) {
+                    const uint2 z0 = __ldg(reinterpret_cast<const uint2*>(zin) + h);
+                    zw[h * 2 + 0] = z0.x; zw[h * 2 + 1] = z0.y;
+                }
             }
         }
         constexpr bool kPaired = BOUNDED && !PER_CHANNEL && ACT != ACT_H_SWISH;
@@ -241,10 +253,16 @@ __device__ __forceinline__ void epilogue_store_t(
             }
             packed[j] = umma::pack4_prmt(r0, r1, r2, r3);
         }
+        if (wide) {
 #pragma unroll
-        for (int h = 0; h < NV / 16; ++h)
-            reinterpret_cast<uint4*>(out)[h] = make_uint4(
-                    packed[h * 4 + 0], packed[h * 4 + 1], packed[h * 4 + 2], packed[h * 4 + 3]);
+            for (int h = 0; h < NV / 16; ++h)
+                reinterpret_cast<uint4*>(out)[h] = make_uint4(
+                        packed[h * 4 + 0], packed[h * 4 + 1], packed[h * 4 + 2], packed[h * 4 + 3]);
+        } else {
+#pragma unroll
+            for (int h = 0; h < NV / 8; ++h)
+                reinterpret_cast<uint2*>(out)[h] = make_uint2(packed[h * 2 + 0], packed[h * 2 + 1]);
+        }
     } else {
         // ragged channel tail, or a channel count that rules out vector stores (fully
         // unrolled with a predicate so the accumulators stay in registers)

@@ -61,6 +61,19 @@ def conv_bias_qs8_nhwc(p, src, flt_packed, bias, dst=None, flt_scales=None, algo
     return dst
 
 
+def conv_bias_qs8_nhwc_fused(p, src, flt_packed, bias, z, mode, z_scale, out_scale, algo="auto"):
+    """ConvBias (p.nonline must be IDENTITY) followed by QADD / QFUSE_ADD_RELU with the int8
+    tensor z of the output's NHWC shape, in one kernel."""
+    from ._lib import ConvFuse
+    oh, ow = out_hw(p)
+    dst = torch.empty((p.n, oh, ow, p.oc), dtype=torch.int8, device=src.device)
+    fuse = ConvFuse(z.data_ptr(), QELEM[mode], z_scale, out_scale)
+    check(lib().mb200_conv_bias_qs8_nhwc_fused(
+        C.byref(p), _ptr(src), 0, _ptr(flt_packed), _ptr(bias), None, C.byref(fuse), _ptr(dst),
+        ALGO[algo], _stream()))
+    return dst
+
+
 def conv_acc_qs8_nhwc(p, src, flt_packed, bias):
     oh, ow = out_hw(p)
     acc = torch.empty((p.n, oh, ow, p.oc), dtype=torch.int32, device=src.device)

@@ -77,6 +77,8 @@ UMMA_CASES = [
     ("k7_s2_p3", 1, 64, 64, 48, 48, 7, 2, 3, "RELU"),
     ("nopad_k3", 1, 64, 64, 50, 50, 3, 1, 0, "RELU"),
     ("s3", 1, 64, 64, 50, 47, 3, 3, 1, "RELU"),
+    ("oc76_bytes", 2, 64, 76, 40, 40, 3, 1, 1, "RELU"),
+    ("oc1000_8byte", 300, 512, 1000, 1, 1, 1, 1, 0, "RELU"),
 ]
 
 
@@ -149,6 +151,48 @@ def test_conv_pair_of_sms_matches_oracle(ops, oracle, case, monkeypatch):
     want = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, s1, s2, act)
     bad = int((out != want).sum())
     assert bad == 0, f"{bad}/{want.size} differ; first at {np.argwhere(out != want)[:4].tolist()}"
+    assert ops.device_status() == 0
+
+
+FUSED_CASES = [
+    # name, n, ic, oc, h, w, k, stride, pad, algo
+    ("patch_64", 2, 64, 64, 40, 40, 3, 1, 1, "patch"),
+    ("umma_128", 2, 128, 128, 28, 28, 3, 1, 1, "umma"),
+    ("umma_oc72", 2, 64, 72, 40, 40, 3, 1, 1, "umma"),    # 8-byte vectors
+    ("umma_oc76", 2, 64, 76, 40, 40, 3, 1, 1, "umma"),    # byte stores
+    ("umma_256_wide", 4, 256, 256, 14, 14, 3, 1, 1, "umma"),
+    ("direct_dw", 2, 32, 32, 20, 20, 3, 1, 1, "direct"),
+]
+
+
+@pytest.mark.parametrize("mode", ["QADD", "QFUSE_ADD_RELU"])
+@pytest.mark.parametrize("case", FUSED_CASES, ids=[c[0] for c in FUSED_CASES])
+def test_conv_with_fused_residual_step_matches_two_oracle_kernels(ops, oracle, case, mode,
+                                                                  monkeypatch):
+    """ConvBias + QADD / QFUSE_ADD_RELU in one launch == the reference's two kernels run one
+    after the other (ConvBias to int8 at its own scale, then ElemwiseMultiType)."""
+    name, n, ic, oc, h, w, k, stride, pad, algo = case
+    if name == "umma_256_wide":
+        monkeypatch.setenv("MB200_CONV_BN", "256")
+    groups = ic if name == "direct_dw" else 1
+    c = dict(name="fused_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=stride, pad=pad,
+             groups=groups, act="IDENTITY", range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.3 * (ic // groups * k * k / 576.0) ** 0.5 + 0.1))
+    src, flt, bias = cases.conv_inputs(c)
+    s0, s1, s2 = c["scales"]
+    p = ops.conv_param(n, ic, h, w, oc, k, k, stride, pad, groups, "IDENTITY", s0, s1, s2)
+    conv = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, s1, s2, "IDENTITY",
+                                groups=groups)
+    z = cases.rng_for("fused_z_" + name).integers(-128, 128, conv.shape, dtype=np.int8)
+    z_scale, out_scale = 0.7, 1.3
+    want = oracle.qelemwise(mode, conv, z, s2, z_scale, out_scale)
+    packed = ops.pack_filter(p, dev(flt))
+    out = ops.conv_bias_qs8_nhwc_fused(
+        p, ops.nchw_to_nhwc(dev(src)), packed, dev(bias), ops.nchw_to_nhwc(dev(z)), mode,
+        z_scale, out_scale, algo=algo)
+    got = ops.nhwc_to_nchw(out).cpu().numpy()
+    bad = int((got != want).sum())
+    assert bad == 0, f"{bad}/{want.size} differ; first at {np.argwhere(got != want)[:4].tolist()}"
     assert ops.device_status() == 0
 
 
@@ -267,6 +311,35 @@ def test_matmul_int8_matches_oracle(ops, oracle, shape):
     q = ops.matmul_s8_qs8(dev(a), bp, scale, 1.0).cpu().numpy()
     want_q = oracle.typecvt_qs32_qs8(want, scale, 1.0)
     assert (q == want_q).all()
+    assert ops.device_status() == 0
+
+
+SWEEP = [(512, 512, 512), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192),
+         (4096, 1000, 2048)]
+
+
+@pytest.mark.parametrize("shape", SWEEP, ids=["x".join(map(str, s)) for s in SWEEP])
+def test_matmul_sweep_shapes_requantised(ops, oracle, shape):
+    """The MatMul sweep: int8 x int8 -> int32 -> qint8 with scale 0.002, values in [-127, 127].
+    The oracle computes 48 sampled rows of A against the whole of B (the full product of
+    the largest shape would take the CPU minutes); a 32-bit checksum of the whole int8
+    result is compared between the int32 path + stand-alone TypeCvt and the fused path."""
+    m, n, k = shape
+    r = cases.rng_for("matmul_sweep_%dx%dx%d" % shape)
+    a = r.integers(-127, 128, (m, k), dtype=np.int8)
+    b = r.integers(-127, 128, (k, n), dtype=np.int8)
+    bp = ops.matmul_pack_b(dev(b))
+    a_dev = dev(a)
+    c32 = ops.matmul_s8_s32(a_dev, bp)
+    q = ops.matmul_s8_qs8(a_dev, bp, 0.002, 1.0)
+    rows = np.sort(r.choice(m, size=min(48, m), replace=False))
+    want32 = oracle.matmul_s8_s32(a[rows], b)
+    assert (c32[torch.from_numpy(rows).cuda()].cpu().numpy() == want32).all()
+    want_q = oracle.typecvt_qs32_qs8(want32, 0.002, 1.0)
+    assert (q[torch.from_numpy(rows).cuda()].cpu().numpy() == want_q).all()
+    # fused requantisation == int32 product followed by the stand-alone TypeCvt kernel
+    q2 = ops.typecvt_qs32_qs8(c32, 0.002, 1.0)
+    assert bool((q == q2).all())
     assert ops.device_status() == 0
 
 
