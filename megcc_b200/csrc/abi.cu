@@ -199,6 +199,9 @@ int mb200_conv_bias_qs8_nhwc_fused(
         return launch_conv_umma(a, src, flt_packed, bias, flt_scales, dst, st);
     if (algo != MB200_ALGO_AUTO && algo != MB200_ALGO_DIRECT)
         return set_error(ST_OUT_OF_RANGE, "unknown algo %d", algo);
+    // depthwise 3x3: bandwidth-bound, vector loads and dp4a over taps
+    if (algo == MB200_ALGO_AUTO && conv_dw_supported(a, src, flt_packed, dst))
+        return launch_conv_dw(a, src, flt_packed, bias, flt_scales, dst, st);
     return launch_conv_direct(a, src, flt_packed, bias, flt_scales, dst, nullptr, st);
 }
 

@@ -52,6 +52,11 @@ int launch_pack_filter(const ConvArgs& a, const int8_t* src, int8_t* dst, cudaSt
 int launch_conv_direct(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
         const float* flt_scales, int8_t* dst, int32_t* acc, cudaStream_t st);
+// depthwise 3x3 over NHWC with channels % 16 == 0 (conv_dw.cu)
+bool conv_dw_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst);
+int launch_conv_dw(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
+        const float* flt_scales, int8_t* dst, cudaStream_t st);
 // requant_verify.cu: the multiplier c for which clamp_s8(roundf(act((float)acc * c))) equals the
 // reference's three-step requantisation for EVERY int32 acc (checked value by value), or 0
 float requant_fast_constant(float s_src, float s_flt, float s_dst, int act);

@@ -154,6 +154,40 @@ def test_conv_pair_of_sms_matches_oracle(ops, oracle, case, monkeypatch):
     assert ops.device_status() == 0
 
 
+DW_CASES = [
+    # name, n, c, h, w, stride, pad, act, per_channel
+    ("mbv1_112_c32", 2, 32, 112, 112, 1, 1, "RELU", False),
+    ("mbv1_112_c64_s2", 2, 64, 112, 112, 2, 1, "RELU", True),
+    ("mbv1_14_c512", 3, 512, 14, 14, 1, 1, "RELU", True),
+    ("mbv1_7_c1024", 2, 1024, 7, 7, 1, 1, "IDENTITY", True),
+    ("odd_hw_nopad", 2, 48, 13, 17, 1, 0, "H_SWISH", False),
+    ("odd_hw_s2_pad2", 1, 16, 15, 11, 2, 2, "RELU", False),
+]
+
+
+@pytest.mark.parametrize("case", DW_CASES, ids=[c[0] for c in DW_CASES])
+def test_depthwise_3x3_matches_oracle(ops, oracle, case):
+    """The vectorised depthwise kernel (auto) against the oracle, and against the general
+    kernel (direct) on the same inputs."""
+    name, n, ch, h, w, stride, pad, act, per_channel = case
+    c = dict(name="dw_" + name, n=n, ic=ch, oc=ch, h=h, w=w, k=3, stride=stride, pad=pad,
+             groups=ch, act=act, range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.06))
+    src, flt, bias = cases.conv_inputs(c)
+    s0, s1, s2 = c["scales"]
+    scales = None
+    if per_channel:
+        scales = cases.rng_for("dw_scales_" + name).uniform(0.005, 0.02, ch).astype(np.float32)
+    out, _ = run_conv_nchw(ops, c, algo="auto", flt_scales=scales)
+    want = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, scales if per_channel else s1,
+                                s2, act, groups=ch)
+    bad = int((out != want).sum())
+    assert bad == 0, f"{bad}/{want.size} differ; first at {np.argwhere(out != want)[:4].tolist()}"
+    ref, _ = run_conv_nchw(ops, c, algo="direct", flt_scales=scales)
+    assert (ref == want).all()
+    assert (np.abs(want.astype(int)) < 127).mean() > 0.3
+
+
 FUSED_CASES = [
     # name, n, ic, oc, h, w, k, stride, pad, algo
     ("patch_64", 2, 64, 64, 40, 40, 3, 1, 1, "patch"),
