@@ -376,7 +376,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) conv_pa
 
 bool conv_pair_supported(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst) {
-    return conv_umma_supported(a, src, flt, dst) && a.ic % kBK == 0 && a.oc > kBNh;
+    // im2col maps only: the small-tensor limit of conv_umma.cu applies to every shape here
+    return conv_umma_supported(a, src, flt, dst) && a.ic % kBK == 0 && a.oc > kBNh &&
+           (size_t)a.n * a.ih * a.iw * a.ic >= 131072;
 }
 
 // Clusters of this kernel that the GPU holds at once (one CTA per SM, so at most half the SM

@@ -71,6 +71,7 @@ struct UmmaConvParams {
     int base_h, base_w; // coordinate of output (0,0)'s first tap (= -pad)
     int dh, dw;
     int m_tiles, n_tiles;
+    int a_tiled;        // 1x1, stride 1, no padding: A is the plain matrix [pixels][channels]
     EpilogueParams ep;
     int8_t* dst;
     int* status;
@@ -166,8 +167,11 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                     uint8_t* sa = tiles_a + s * L::kABytes;
                     uint8_t* sb = tiles_b + s * L::kBBytes;
                     if (GEOM != GEOM_TAP16) {
-                        tma_load_im2col_4d(sa, &map_a, &full_bar[s], cb * kBKc, base_w, base_h, img,
-                                           (uint16_t)(fx * p.dw), (uint16_t)(fy * p.dh));
+                        if (p.a_tiled)
+                            tma_load_2d(sa, &map_a, &full_bar[s], cb * kBKc, m0);
+                        else
+                            tma_load_im2col_4d(sa, &map_a, &full_bar[s], cb * kBKc, base_w, base_h,
+                                               img, (uint16_t)(fx * p.dw), (uint16_t)(fy * p.dh));
                         tma_load_2d(sb, &map_b, &full_bar[s], it * kBKc, n0);
                         if (++cb == p.cblocks) {
                             cb = 0;
@@ -357,6 +361,13 @@ int launch_kernel(
 
 }  // namespace
 
+// 1x1 filter, stride 1, no padding, NHWC: the convolution is a matrix product over the
+// activation as it lies in memory
+static bool conv_is_plain_matrix(const ConvArgs& a) {
+    return a.kh == 1 && a.kw == 1 && a.sh == 1 && a.sw == 1 && a.ph == 0 && a.pw == 0 &&
+           !a.src_is_nchw;
+}
+
 bool conv_umma_supported(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst) {
     if (a.groups != 1 || a.src_is_nchw)
@@ -369,8 +380,8 @@ bool conv_umma_supported(
     if (a.ph > 64 || a.pw > 64 || a.kh > 64 || a.kw > 64 || a.sh > 8 || a.sw > 8)
         return false;
     // the driver mis-encodes im2col maps of very small tensors; keep those on the
-    // general kernel
-    if ((size_t)a.n * a.ih * a.iw * a.ic < 131072)
+    // general kernel (a pointwise convolution uses a tiled map and has no such limit)
+    if ((size_t)a.n * a.ih * a.iw * a.ic < 131072 && !conv_is_plain_matrix(a))
         return false;
     if (((uintptr_t)src | (uintptr_t)flt | (uintptr_t)dst) & 15)
         return false;
@@ -425,7 +436,21 @@ int launch_conv_umma_geom(
                                    : geom == GEOM_WIDE  ? CU_TENSOR_MAP_SWIZZLE_64B
                                                         : CU_TENSOR_MAP_SWIZZLE_NONE;
     CUtensorMap map_a, map_b;
-    {
+    const bool a_tiled = geom != GEOM_TAP16 && conv_is_plain_matrix(a);
+    if (a_tiled) {
+        // a pointwise convolution reads the activation as the matrix [N*H*W][IC]: a tiled
+        // map, 128 rows per box (rows past the end are filled with zeros)
+        cuuint64_t dims[2] = {(cuuint64_t)a.ic, (cuuint64_t)a.m};
+        cuuint64_t strides[1] = {(cuuint64_t)a.ic};
+        cuuint32_t box[2] = {(cuuint32_t)chans, (cuuint32_t)kBM};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = api.tiled(
+                &map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)src, dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(activation) failed: %d", (int)r);
+    } else {
         cuuint64_t dims[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw, (cuuint64_t)a.ih,
                               (cuuint64_t)a.n};
         cuuint64_t strides[3] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw * a.ic,
@@ -471,6 +496,7 @@ int launch_conv_umma_geom(
     p.dw = a.dw;
     p.m_tiles = (a.m + kBM - 1) / kBM;
     p.n_tiles = (a.oc + bn - 1) / bn;
+    p.a_tiled = a_tiled ? 1 : 0;
     p.ep.oc = a.oc;
     p.ep.act = a.act;
     p.ep.bounded = requant_is_bounded(a.s_src, a.s_flt, a.s_dst) ? 1 : 0;
