@@ -141,14 +141,16 @@ MB200_API int mb200_conv_acc_qs8_nhwc(
 
 /* Host only, no GPU needed. The tensor-core ConvBias epilogue may replace the reference's
  * three rounded float operations acc * src_scale * flt_scale / dst_scale
- * (compiler/lib/KernelGen/BareMetal/Activation.cpp:105-113) by ONE fused multiply-add trunc(fma(acc, c, +-0.49999997)), but
- * only with a constant c for which the library has compared the final int8 of both forms
- * on every accumulator value between the two saturation points (beyond them both forms are
- * saturated, by monotonicity). Returns that c, or 0 when no candidate passed, the range is
- * too long to walk, a scale is not positive or the activation is H_SWISH; the kernels then
- * keep the three-step form. Results are cached per scale triple. */
-MB200_API float mb200_requant_fast_constant(
-        float src_scale, float flt_scale, float dst_scale, int nonline);
+ * (compiler/lib/KernelGen/BareMetal/Activation.cpp:105-113) by a shorter form that ends in
+ * one fused multiply-add: trunc(fma(f, mul, +-add)) with f = acc (1 operation), acc * src_scale
+ * (2) or acc * src_scale * flt_scale (3); but only with constants for which the library has
+ * shown that both are the same function of the int32 accumulator: both are monotonic
+ * staircases, and they are compared on either side of every step of the reference's.
+ * Returns the number of operations of the shortest form that passed, with its constants, or
+ * 0 (and zeros) when none did, a scale is not positive or the activation is H_SWISH; the
+ * kernels then keep the reference's operations. Cached per scale triple. */
+MB200_API int mb200_requant_fast_constants(
+        float src_scale, float flt_scale, float dst_scale, int nonline, float* mul, float* add);
 
 /* ---- MatrixMul int8 x int8 -> int32 (C = A[M][K] * B[K][N], row-major), and the same with
  * the int32 product requantised to qint8 by the TypeCvt rule val * acc_scale / dst_scale

@@ -48,7 +48,8 @@ SIGNATURES = {
     "mb200_conv_bias_qs8_nchw_noalloc_max_scratch": (C.c_size_t, []),
     "mb200_conv_bias_qs8_nchw_noalloc": (C.c_int, [C.POINTER(ConvParam), _P, _P, _P, _P, _P, _P]),
     "mb200_conv_acc_qs8_nhwc": (C.c_int, [C.POINTER(ConvParam), _P, _P, _P, _P, _P]),
-    "mb200_requant_fast_constant": (C.c_float, [C.c_float, C.c_float, C.c_float, C.c_int]),
+    "mb200_requant_fast_constants": (C.c_int, [C.c_float, C.c_float, C.c_float, C.c_int,
+                                               C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mb200_matmul_pack_b": (C.c_int, [C.c_int, C.c_int, _P, _P, _P]),
     "mb200_matmul_s8_s32": (C.c_int, [C.c_int, C.c_int, C.c_int, _P, _P, _P, _P]),
     "mb200_matmul_s8_qs8": (C.c_int, [C.c_int, C.c_int, C.c_int, _P, _P, _P, C.c_float, C.c_float,

@@ -332,8 +332,15 @@ int mb200_conv_bias_qs8_nchw(
     return launch_transpose_s8(ws_dst, dst, a.n, a.oh * a.ow, a.oc, st);
 }
 
-float mb200_requant_fast_constant(float src_scale, float flt_scale, float dst_scale, int nonline) {
-    return requant_fast_constant(src_scale, flt_scale, dst_scale, nonline);
+int mb200_requant_fast_constants(
+        float src_scale, float flt_scale, float dst_scale, int nonline, float* mul, float* add) {
+    float c = 0.f, d = 0.f;
+    const int ops = requant_fast_constants(src_scale, flt_scale, dst_scale, nonline, &c, &d);
+    if (mul)
+        *mul = c;
+    if (add)
+        *add = d;
+    return ops;
 }
 
 // ---- int8 matrix product: a 1x1 ConvBias over M "pixels" with K channels ----

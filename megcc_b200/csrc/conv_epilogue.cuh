@@ -15,10 +15,11 @@ struct EpilogueParams {
     // one saturating conversion does round-to-int and clamp together
     int bounded;
     float s_src, s_flt, s_dst, inv_dst;
-    // non-zero: a single multiplier that the host has checked, accumulator value by value,
-    // to give the same int8 as the three-step chain (requant_verify.cu); per-tensor scales,
-    // IDENTITY / RELU only
-    float fast_mul;
+    // non-zero: multiplier and rounding offset of the one-FMA form that the host has checked
+    // against the three-step chain on every step of its staircase (requant_verify.cu);
+    // per-tensor scales, IDENTITY / RELU only
+    float fast_mul, fast_add;
+    int fast_ops;  // 0: none; 1..3: float operations of the verified form (see requant_pair_fast)
     const int32_t* bias;
     const float* flt_scales;
     // Optional fused quantised elementwise step (the residual add of a ResNet block): the
@@ -29,6 +30,10 @@ struct EpilogueParams {
     const int8_t* z;
     int z_mode;  // 0 none, 1 QADD, 2 QFUSE_ADD_RELU
     float z_scale, z_div;
+    // non-zero: the fused step in its verified short form (requant_verify.cu): a and b with
+    // fma(z, b, conv * a) rounded as below equal to the reference's five float operations
+    // on all 65536 (conv, z) pairs
+    float z_fast_a, z_fast_b;
     // when set, the int32 accumulators (+ bias) are stored here instead of the int8 result
     // (same [pixel][channel] indexing); used by the int8 -> int32 matrix product
     int32_t* acc_out;
@@ -128,19 +133,28 @@ __device__ __forceinline__ void requant_pair(
     asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(y1));
 }
 
-// The verified form (EpilogueParams::fast_mul) on two accumulators: ONE fused multiply-add,
-// trunc(fma((float)acc, c, +-0.49999997)), saturated. It is written as an explicit fma because
+// The verified form (EpilogueParams::fast_mul / fast_add) on two accumulators: ONE fused
+// multiply-add, trunc(fma((float)acc, c, +-d)), saturated. It is written as an explicit fma because
 // the assembler contracts a packed multiply followed by a packed add into one anyway (seen on
 // a tie: 15000 * 1e-4f + 0.49999997f is 2.0 in two steps and 1.9999999 fused), and the host's
 // value-by-value check (requant_verify.cu) evaluates exactly this fused form.
-template <int ACT>
+template <int ACT, int OPS>
 __device__ __forceinline__ void requant_pair_fast(
-        int acc0, int acc1, float mul, int& q0, int& q1) {
-    // scalar fused multiply-adds: the packed form would need the two converted values moved
-    // into a register pair and the results moved out again, which costs more than it saves
-    const float f0 = __int2float_rn(acc0), f1 = __int2float_rn(acc1);
-    const float y0 = __fmaf_rn(f0, mul, ACT == ACT_RELU ? 0.49999997f : copysignf(0.49999997f, f0));
-    const float y1 = __fmaf_rn(f1, mul, ACT == ACT_RELU ? 0.49999997f : copysignf(0.49999997f, f1));
+        int acc0, int acc1, const EpilogueParams& e, int& q0, int& q1) {
+    // scalar operations: the packed form would need the two converted values moved into a
+    // register pair and the results moved out again, which costs what it saves. OPS - 1
+    // leading multiplications of the reference chain are kept, the rest is one fma.
+    float f0 = __int2float_rn(acc0), f1 = __int2float_rn(acc1);
+    if (OPS >= 2) {
+        f0 = __fmul_rn(f0, e.s_src);
+        f1 = __fmul_rn(f1, e.s_src);
+    }
+    if (OPS >= 3) {
+        f0 = __fmul_rn(f0, e.s_flt);
+        f1 = __fmul_rn(f1, e.s_flt);
+    }
+    const float y0 = __fmaf_rn(f0, e.fast_mul, ACT == ACT_RELU ? e.fast_add : copysignf(e.fast_add, f0));
+    const float y1 = __fmaf_rn(f1, e.fast_mul, ACT == ACT_RELU ? e.fast_add : copysignf(e.fast_add, f1));
     asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(y0));
     asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(y1));
 }
@@ -172,7 +186,27 @@ __device__ __forceinline__ int fuse_z(int conv_q, int zv, const EpilogueParams& 
 }
 
 // NV = 16 or 32 accumulators (consecutive channels from ch0) of one output pixel
-template <int NV, int ACT, bool PER_CHANNEL, bool BOUNDED, int ZMODE, bool FAST = false>
+// The verified short form of fuse_z (EpilogueParams::z_fast_a / z_fast_b). QFUSE_ADD_RELU:
+// trunc(fma(z, b, fma(conv, a, 0.49999997))) with negatives cleared afterwards; QADD: the
+// rounding offset takes the sign of the sum, so it is added last. Scalar intrinsics: none
+// of these may be contracted or reordered.
+template <int ZMODE>
+__device__ __forceinline__ int fuse_z_fast(int conv_q, int zv, float a, float b) {
+    const float qf = __int2float_rn(conv_q), zf = __int2float_rn(zv);
+    float y;
+    if (ZMODE == 2) {
+        y = __fmaf_rn(zf, b, __fmaf_rn(qf, a, 0.49999997f));
+    } else {
+        const float v = __fmaf_rn(zf, b, __fmul_rn(qf, a));
+        y = __fadd_rn(v, copysignf(0.49999997f, v));
+    }
+    int q;
+    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(y));
+    return q;
+}
+
+template <int NV, int ACT, bool PER_CHANNEL, bool BOUNDED, int ZMODE, int FAST = 0,
+          bool ZFAST = false>
 __device__ __forceinline__ void epilogue_store_t(
         const uint32_t (&v)[NV], const EpilogueParams& e, int8_t* out, const int8_t* zin,
         int ch0) {
@@ -203,7 +237,7 @@ __device__ __forceinline__ void epilogue_store_t(
             }
         }
         constexpr bool kPaired = BOUNDED && !PER_CHANNEL && ACT != ACT_H_SWISH;
-        static_assert(!FAST || kPaired, "the verified form exists for the paired path only");
+        static_assert(FAST == 0 || kPaired, "the verified form exists for the paired path only");
         static_assert(ZMODE == 0 || ACT == ACT_IDENTITY, "the fused step follows a plain ConvBias");
         const RequantPair rp(e);
 #pragma unroll
@@ -213,16 +247,21 @@ __device__ __forceinline__ void epilogue_store_t(
                 b = __ldg(reinterpret_cast<const int4*>(e.bias + ch0) + j);
             if (kPaired) {
                 int r0, r1, r2, r3;
-                if (FAST) {
-                    requant_pair_fast<ACT>((int)v[j * 4 + 0] + b.x, (int)v[j * 4 + 1] + b.y,
-                                           e.fast_mul, r0, r1);
-                    requant_pair_fast<ACT>((int)v[j * 4 + 2] + b.z, (int)v[j * 4 + 3] + b.w,
-                                           e.fast_mul, r2, r3);
+                if (FAST != 0) {
+                    requant_pair_fast<ACT, FAST>((int)v[j * 4 + 0] + b.x, (int)v[j * 4 + 1] + b.y, e,
+                                                 r0, r1);
+                    requant_pair_fast<ACT, FAST>((int)v[j * 4 + 2] + b.z, (int)v[j * 4 + 3] + b.w, e,
+                                                 r2, r3);
                 } else {
                     requant_pair<ACT>((int)v[j * 4 + 0] + b.x, (int)v[j * 4 + 1] + b.y, rp, r0, r1);
                     requant_pair<ACT>((int)v[j * 4 + 2] + b.z, (int)v[j * 4 + 3] + b.w, rp, r2, r3);
                 }
-                if (ZMODE != 0) {
+                if (ZMODE != 0 && ZFAST) {
+                    r0 = fuse_z_fast<ZMODE>(r0, (int)(int8_t)(zw[j]), e.z_fast_a, e.z_fast_b);
+                    r1 = fuse_z_fast<ZMODE>(r1, (int)(int8_t)(zw[j] >> 8), e.z_fast_a, e.z_fast_b);
+                    r2 = fuse_z_fast<ZMODE>(r2, (int)(int8_t)(zw[j] >> 16), e.z_fast_a, e.z_fast_b);
+                    r3 = fuse_z_fast<ZMODE>(r3, (int)(int8_t)(zw[j] >> 24), e.z_fast_a, e.z_fast_b);
+                } else if (ZMODE != 0) {
                     // scalar operations with explicit rounding: a packed multiply feeding a
                     // packed add would be contracted, and this sum must not be
                     r0 = fuse_z<ZMODE>(r0, (int)(int8_t)(zw[j]), e);
@@ -231,7 +270,10 @@ __device__ __forceinline__ void epilogue_store_t(
                     r3 = fuse_z<ZMODE>(r3, (int)(int8_t)(zw[j] >> 24), e);
                 }
                 const uint32_t pk = umma::pack4_prmt(r0, r1, r2, r3);
-                packed[j] = (ACT == ACT_RELU && ZMODE == 0) ? relu_s8x4(pk) : pk;
+                // RELU of the conv, or of the fused sum in its short form, on packed bytes
+                packed[j] = ((ACT == ACT_RELU && ZMODE == 0) || (ZMODE == 2 && ZFAST))
+                                    ? relu_s8x4(pk)
+                                    : pk;
                 continue;
             }
             float4 s = make_float4(e.s_flt, e.s_flt, e.s_flt, e.s_flt);
@@ -308,17 +350,31 @@ __device__ __forceinline__ void epilogue_store(
     }
     int8_t* out = dst + off;
     const bool pc = e.flt_scales != nullptr;
-    if (e.fast_mul != 0.f) {
+    if (e.fast_ops != 0) {
         // set by the host only together with `bounded`, per-tensor scales, IDENTITY / RELU
         const int8_t* zin = e.z_mode != 0 ? e.z + off : nullptr;
-        if (e.z_mode == 1)
-            epilogue_store_t<NV, ACT_IDENTITY, false, true, 1, true>(v, e, out, zin, ch0);
-        else if (e.z_mode == 2)
-            epilogue_store_t<NV, ACT_IDENTITY, false, true, 2, true>(v, e, out, zin, ch0);
-        else if (e.act == ACT_RELU)
-            epilogue_store_t<NV, ACT_RELU, false, true, 0, true>(v, e, out, nullptr, ch0);
-        else
-            epilogue_store_t<NV, ACT_IDENTITY, false, true, 0, true>(v, e, out, nullptr, ch0);
+        const bool zfast = e.z_mode != 0 && e.z_fast_a != 0.f;
+#define MB200_FAST_CASE(OPS)                                                                      \
+    if (zfast && e.z_mode == 1)                                                                   \
+        epilogue_store_t<NV, ACT_IDENTITY, false, true, 1, OPS, true>(v, e, out, zin, ch0);       \
+    else if (zfast)                                                                               \
+        epilogue_store_t<NV, ACT_IDENTITY, false, true, 2, OPS, true>(v, e, out, zin, ch0);       \
+    else if (e.z_mode == 1)                                                                       \
+        epilogue_store_t<NV, ACT_IDENTITY, false, true, 1, OPS>(v, e, out, zin, ch0);             \
+    else if (e.z_mode == 2)                                                                       \
+        epilogue_store_t<NV, ACT_IDENTITY, false, true, 2, OPS>(v, e, out, zin, ch0);             \
+    else if (e.act == ACT_RELU)                                                                   \
+        epilogue_store_t<NV, ACT_RELU, false, true, 0, OPS>(v, e, out, nullptr, ch0);             \
+    else                                                                                          \
+        epilogue_store_t<NV, ACT_IDENTITY, false, true, 0, OPS>(v, e, out, nullptr, ch0);
+        if (e.fast_ops == 1) {
+            MB200_FAST_CASE(1)
+        } else if (e.fast_ops == 2) {
+            MB200_FAST_CASE(2)
+        } else {
+            MB200_FAST_CASE(3)
+        }
+#undef MB200_FAST_CASE
         return;
     }
     if (e.z_mode != 0) {

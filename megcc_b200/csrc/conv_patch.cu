@@ -568,16 +568,27 @@ int launch_conv_patch(
     p.ep.s_dst = a.s_dst;
     p.ep.inv_dst = 1.0f / a.s_dst;  // correctly rounded on the host
     // a fused step follows a ConvBias without activation
-    p.ep.fast_mul = (p.ep.bounded && !flt_scales)
-                            ? requant_fast_constant(a.s_src, a.s_flt, a.s_dst,
-                                                    (a.z && a.z_mode) ? ACT_IDENTITY : a.act)
-                            : 0.f;
+    p.ep.fast_mul = p.ep.fast_add = 0.f;
+    p.ep.fast_ops = 0;
+    if (p.ep.bounded && !flt_scales)
+        p.ep.fast_ops = requant_fast_constants(a.s_src, a.s_flt, a.s_dst,
+                                               (a.z && a.z_mode) ? ACT_IDENTITY : a.act,
+                                               &p.ep.fast_mul, &p.ep.fast_add);
     p.ep.bias = bias;
     p.ep.flt_scales = flt_scales;
     p.ep.z = a.z;
     p.ep.z_mode = a.z ? a.z_mode : 0;
     p.ep.z_scale = a.z_scale;
     p.ep.z_div = 1.0f / a.z_out_scale;  // the reference's scale_div = 1.f / scale_dst
+    p.ep.z_fast_a = p.ep.z_fast_b = 0.f;
+    if (p.ep.z_mode != 0 && p.ep.fast_ops != 0)
+        residual_fast_constants(a.s_dst, a.z_scale, a.z_out_scale, p.ep.z_mode, &p.ep.z_fast_a,
+                                &p.ep.z_fast_b);
+    if (getenv("MB200_DEBUG"))
+        fprintf(stderr, "%s: scales %g %g %g act %d z_mode %d verified requant: %d ops, %g + %.9g, short residual %g %g\n", "conv_patch",
+                a.s_src, a.s_flt, a.s_dst, a.act, p.ep.z_mode, p.ep.fast_ops, p.ep.fast_mul, p.ep.fast_add,
+                p.ep.z_fast_a,
+                p.ep.z_fast_b);
     p.ep.acc_out = a.acc_out;
     p.dst = dst;
     p.status = device_status_word();

@@ -57,9 +57,17 @@ bool conv_dw_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt, 
 int launch_conv_dw(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
         const float* flt_scales, int8_t* dst, cudaStream_t st);
-// requant_verify.cu: the multiplier c for which clamp_s8(roundf(act((float)acc * c))) equals the
-// reference's three-step requantisation for EVERY int32 acc (checked value by value), or 0
-float requant_fast_constant(float s_src, float s_flt, float s_dst, int act);
+// requant_verify.cu: the shortest form clamp_s8(trunc(fma(f, mul, +-add))), f = (float)acc
+// [* s_src [* s_flt]], that equals the reference's three-step requantisation for EVERY int32
+// acc (checked on both sides of every step of the reference's staircase). Returns the number
+// of float operations (1..3), or 0 and zeros when none passed
+int requant_fast_constants(
+        float s_src, float s_flt, float s_dst, int act, float* mul_out, float* add_out);
+// the same idea for the fused residual step (mode 1 QADD, 2 QFUSE_ADD_RELU): a and b with
+// trunc(fma(z, b, conv * a) +- 0.49999997) equal to the reference's five float operations on
+// all 65536 (conv, z) pairs; false (and zeros) when no candidate passes
+bool residual_fast_constants(
+        float s_conv, float s_z, float out_scale, int mode, float* a_out, float* b_out);
 
 // tensor-core implicit GEMM; conv_umma_supported() says whether the shape qualifies
 bool conv_umma_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst);

@@ -49,8 +49,8 @@ def test_missing_library_fails_loudly(monkeypatch):
         _lib.lib()
 
 
-def test_verified_requant_constant_agrees_with_the_reference_chain():
-    """mb200_requant_fast_constant (host only): the one-FMA requantisation it licenses must
+def test_verified_requant_constants_agree_with_the_reference_chain():
+    """mb200_requant_fast_constants (host only): the one-FMA requantisation it licenses must
     give the reference's int8 on every accumulator; checked here independently, with exact
     rational arithmetic for the fused multiply-add, on all near-tie accumulators (those whose
     scaled value lies within 1e-4 of a half-integer), a dense band around zero, and the
@@ -61,18 +61,26 @@ def test_verified_requant_constant_agrees_with_the_reference_chain():
     from megcc_b200._lib import lib
     f32 = np.float32
 
-    def to_f32(fr):  # correctly rounded Fraction -> float32 (via float64 is exact enough here:
-        # the values are sums of a 48-bit product and a 24-bit constant, far from float64 ties)
-        return f32(float(fr))
+    def constants(s_src, s_flt, s_dst, act):
+        m, d = ctypes.c_float(), ctypes.c_float()
+        ok = lib().mb200_requant_fast_constants(s_src, s_flt, s_dst, act, ctypes.byref(m),
+                                                ctypes.byref(d))
+        return ok, m.value, d.value
 
     found = 0
-    for s_src, s_flt, s_dst, act in [(0.05, 0.01, 2.0, 1), (0.05, 0.01, 5.0, 1),
-                                     (0.0473, 0.00731, 0.1931, 1), (0.02, 0.01, 0.5, 0),
-                                     (0.05, 0.01, 0.77, 0), (0.3, 0.2, 0.01, 1)]:
-        c = lib().mb200_requant_fast_constant(s_src, s_flt, s_dst, act)
-        if c == 0.0:
+    rng = np.random.default_rng(7)
+    triples = [(0.05, 0.01, 2.0, 1), (0.05, 0.01, 5.0, 1), (0.0473, 0.00731, 0.1931, 1),
+               (0.02, 0.01, 0.5, 0), (0.05, 0.01, 0.77, 0), (0.3, 0.2, 0.01, 1)]
+    triples += [(float(rng.uniform(0.01, 0.1)), float(rng.uniform(0.002, 0.02)),
+                 float(rng.uniform(0.05, 3.0)), int(rng.integers(0, 2))) for _ in range(12)]
+    for s_src, s_flt, s_dst, act in triples:
+        ops, c, d = constants(s_src, s_flt, s_dst, act)
+        if not ops:
+            assert c == 0.0 and d == 0.0
             continue
+        assert ops in (1, 2, 3)
         found += 1
+        assert 0.0 < d < 1.0
         ratio = float(f32(s_src)) * float(f32(s_flt)) / float(f32(s_dst))
         r = int(130 / ratio) + 4
         acc = np.arange(-r, r + 1, dtype=np.int64)
@@ -85,15 +93,23 @@ def test_verified_requant_constant_agrees_with_the_reference_chain():
         if act == 1:
             x = np.maximum(x, f32(0))
         want = np.clip(np.sign(x) * np.floor(np.abs(x.astype(np.float64)) + 0.5), -128, 127)
-        half = Fraction(float(f32(0.49999997)))
+        off = Fraction(float(f32(d)))
         got = []
-        for v in a:
-            h = half if (act == 1 or v >= 0) else -half
-            y = to_f32(Fraction(float(v)) * Fraction(float(f32(c))) + h)
+        lead = a
+        if ops >= 2:
+            lead = (lead * f32(s_src)).astype(np.float32)
+        if ops >= 3:
+            lead = (lead * f32(s_flt)).astype(np.float32)
+        for v in lead:
+            h = off if (act == 1 or not np.signbit(v)) else -off
+            # exact sum, then one rounding to float32 (float64 in between is harmless: the
+            # exact value has at most 48 + 24 significant bits and is nowhere near a float64 tie
+            # that is also a float32 tie)
+            y = f32(float(Fraction(float(v)) * Fraction(float(f32(c))) + h))
             q = int(np.clip(np.trunc(y), -128, 127))
             got.append(max(q, 0) if act == 1 else q)
         assert (np.array(got) == want).all(), (s_src, s_flt, s_dst, act)
-    assert found >= 3
+    assert found >= 6
     # no licence without positive scales, nor for H_SWISH
-    assert lib().mb200_requant_fast_constant(0.05, -0.01, 2.0, 1) == 0.0
-    assert lib().mb200_requant_fast_constant(0.05, 0.01, 2.0, 2) == 0.0
+    assert constants(0.05, -0.01, 2.0, 1)[0] == 0
+    assert constants(0.05, 0.01, 2.0, 2)[0] == 0
