@@ -98,6 +98,26 @@ def test_conv_umma_matches_oracle(ops, oracle, case):
     assert (np.abs(want.astype(int)) < 127).mean() > 0.3
 
 
+@pytest.mark.parametrize("algo", ["umma", "patch"])
+@pytest.mark.parametrize("act", ["RELU", "IDENTITY"])
+def test_conv_reference_operation_order_without_verified_forms(ops, oracle, algo, act,
+                                                               monkeypatch):
+    """The epilogue with the reference's own six float operations (the verified short forms
+    switched off), and the same case with them on: both bit-exact."""
+    c = dict(name="exact_chain_" + act, n=2, ic=64, oc=64, h=40, w=40, k=3, stride=1, pad=1,
+             groups=1, act=act, range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.9))
+    s0, s1, s2 = c["scales"]
+    src, flt, bias = cases.conv_inputs(c)
+    want = oracle.conv_bias_qs8(src, flt, bias, 1, 1, s0, s1, s2, act)
+    out, _ = run_conv_nchw(ops, c, algo=algo)
+    assert (out == want).all()
+    monkeypatch.setenv("MB200_NO_FAST_REQUANT", "1")
+    out, _ = run_conv_nchw(ops, c, algo=algo)
+    assert (out == want).all()
+    assert ops.device_status() == 0
+
+
 BN256_CASES = [
     # name, n, ic, oc, h, w, k, stride, pad, act, forced
     ("s1_256", 4, 256, 256, 14, 14, 3, 1, 1, "RELU", True),
