@@ -221,7 +221,14 @@ __device__ __forceinline__ void epilogue_store_t(
         for (int j = 0; j < NV / 4; ++j)
             zw[j] = 0;
         if (ZMODE != 0) {
-            if (wide) {
+            if (NV == 32 && (e.oc % 32) == 0 && ((uintptr_t)zin & 31) == 0) {
+                // one 256-bit load of the sector that the store below will mirror
+                asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                             : "=r"(zw[0]), "=r"(zw[1]), "=r"(zw[2]), "=r"(zw[3]),
+                               "=r"(zw[NV / 4 - 4]), "=r"(zw[NV / 4 - 3]), "=r"(zw[NV / 4 - 2]),
+                               "=r"(zw[NV / 4 - 1])
+                             : "l"(zin));
+            } else if (wide) {
 #pragma unroll
                 for (int h = 0; h < NV / 16; ++h) {
                     const uint4 z0 = __ldg(reinterpret_cast<const uint4*>(zin) + h);
@@ -295,7 +302,15 @@ __device__ __forceinline__ void epilogue_store_t(
             }
             packed[j] = umma::pack4_prmt(r0, r1, r2, r3);
         }
-        if (wide) {
+        if (NV == 32 && (e.oc % 32) == 0 && ((uintptr_t)out & 31) == 0) {
+            // the chunk's 32 bytes are one whole, aligned sector: one 256-bit store (two
+            // 16-byte stores would each touch half a sector of 32 different lines per warp)
+            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(out),
+                         "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]),
+                         "r"(packed[NV / 4 - 4]), "r"(packed[NV / 4 - 3]), "r"(packed[NV / 4 - 2]),
+                         "r"(packed[NV / 4 - 1])
+                         : "memory");
+        } else if (wide) {
 #pragma unroll
             for (int h = 0; h < NV / 16; ++h)
                 reinterpret_cast<uint4*>(out)[h] = make_uint4(
