@@ -320,14 +320,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) conv_pa
                 break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kBN);
-            // the four warps of one lane quarter interleave over its eight 32-column chunks
             const int first = (warp - 2) >> 2;
-            constexpr int kChunkStep = kEpilogueWarps / 4;
+            // each warp takes a run of adjacent chunks: its thread's bytes are contiguous
+            constexpr int kChunksPerWarp = (kBN / 32) / (kEpilogueWarps / 4);
 #pragma unroll 1
-            for (int c = first; c < kBN / 32; c += kChunkStep) {
+            for (int c = first * kChunksPerWarp; c < (first + 1) * kChunksPerWarp; ++c) {
                 uint32_t v[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), v);
-                if (c + kChunkStep >= kBN / 32) {
+                if (c + 1 == (first + 1) * kChunksPerWarp) {
                     // this warp's accumulators are in registers: release the buffer (one
                     // arrival per warp, on the leader's barrier)
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -321,14 +321,16 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
             const uint32_t pixel = ((uint32_t)at.img * p.oh + oy) * p.ow + ox;
             const size_t px_off = (size_t)pixel * p.oc;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-            // the warps of one lane quarter interleave over its 32-column chunks
             const int half = (warp - 2) >> 2;
-            constexpr int kChunkStep = kEpilogueWarps / 4;
+            // each warp takes a run of adjacent chunks: its thread's bytes are contiguous
+            constexpr int kChunksPerWarp = (BN / 32) / (kEpilogueWarps / 4);
+            static_assert(kChunksPerWarp >= 1, "every epilogue warp must own a chunk: it is "
+                                               "counted on the accumulator-drained barrier");
 #pragma unroll 1
-            for (int c = half; c < BN / 32; c += kChunkStep) {
+            for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; ++c) {
                 uint32_t v[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), v);
-                if (c + kChunkStep >= BN / 32) {
+                if (c + 1 == (half + 1) * kChunksPerWarp) {
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     mbar_arrive(&acc_empty[buf]);
                 }
@@ -611,8 +613,8 @@ int launch_conv_patch(
     else if (pl.bn == 128 && a.kh == 3 && a.kw == 3 && a.ic == 128 && alone)
         rc = launch_patch<128, 3, 3, 8, 16>(map_a, map_b, p, pl.smem_bytes, grid, st);
     else if (pl.bn == 64)
-        rc = alone ? launch_patch<64, 0, 0, 0, 16>(map_a, map_b, p, pl.smem_bytes, grid, st)
-                   : launch_patch<64, 0, 0, 0, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);
+        // two 32-column chunks per lane quarter: eight epilogue warps at most
+        rc = launch_patch<64, 0, 0, 0, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);
     else
         rc = alone ? launch_patch<128, 0, 0, 0, 16>(map_a, map_b, p, pl.smem_bytes, grid, st)
                    : launch_patch<128, 0, 0, 0, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);

@@ -288,14 +288,15 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                 break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-            // the warps of one lane quarter interleave over its 32-column chunks
             const int half = (warp - 2) >> 2;
-            constexpr int kChunkStep = kEpilogueWarps / 4;
+            // each warp takes a run of adjacent chunks: its thread's bytes are contiguous
+            constexpr int kChunksPerWarp = (BN / 32) / (kEpilogueWarps / 4);
+            static_assert(kChunksPerWarp >= 1, "every epilogue warp must own a chunk");
 #pragma unroll 1
-            for (int c = half; c < BN / 32; c += kChunkStep) {
+            for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; ++c) {
                 uint32_t v[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), v);
-                if (c + kChunkStep >= BN / 32) {
+                if (c + 1 == (half + 1) * kChunksPerWarp) {
                     // all of this thread's accumulators are in registers: hand the buffer back
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     mbar_arrive(&acc_empty[buf]);

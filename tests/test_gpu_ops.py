@@ -257,6 +257,8 @@ PATCH_CASES = [
     ("c64_oc128", 2, 64, 128, 40, 40, 3, 1, "RELU"),
     ("c128_oc64", 2, 128, 64, 28, 28, 3, 1, "RELU"),
     ("c128_28", 2, 128, 128, 28, 28, 3, 1, "RELU"),
+    ("c128_28_many_tiles", 80, 128, 128, 28, 28, 3, 1, "RELU"),   # 640 patches: 4-5 per CTA
+    ("c128_oc64_many_tiles", 80, 128, 64, 28, 28, 3, 1, "IDENTITY"),
     ("c96_oc128_k3", 2, 96, 128, 30, 30, 3, 1, "IDENTITY"),
     ("c32_k5", 2, 32, 72, 50, 50, 5, 2, "H_SWISH"),
     ("c16_k2x4", 8, 16, 64, 40, 40, 4, 2, "RELU"),
