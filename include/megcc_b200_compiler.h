@@ -45,6 +45,15 @@ MB200C_API int mb200c_add_conv_bias(
         int groups, const char* nonline, const int8_t* flt, float flt_scale,
         const int32_t* bias, const float* channel_scales, float dst_scale);
 
+/* MatrixMul + TypeCvt: C[batch][n] = requant(A[batch][K] x B[K][n]); A = tensor src with
+ * h = w = 1 (K = its channels), b: [K][n] int8 row-major with per-tensor scale. The int32
+ * product has scale src.scale * b_scale (one float multiplication, as MegEngine records it)
+ * and is converted to qint8 at dst_scale by the TypeCvt rule
+ * (compiler/lib/KernelGen/BareMetal/Typecvt.cpp:91-96). */
+MB200C_API int mb200c_add_matmul(
+        mb200c_graph* g, const char* name, int src, int n, const int8_t* b, float b_scale,
+        float dst_scale);
+
 /* mode: "MAX" | "AVERAGE" | "AVERAGE_COUNT_EXCLUDE_PADDING" */
 MB200C_API int mb200c_add_pooling(
         mb200c_graph* g, const char* name, int src, const char* mode, int window, int stride,

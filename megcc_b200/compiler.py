@@ -16,6 +16,7 @@ SIGNATURES = {
     "mb200c_add_input": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_float]),
     "mb200c_add_conv_bias": (C.c_int, [_P, C.c_char_p] + [C.c_int] * 7 + [
         C.c_char_p, _P, C.c_float, _P, _P, C.c_float]),
+    "mb200c_add_matmul": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int, _P, C.c_float, C.c_float]),
     "mb200c_add_pooling": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_char_p] + [C.c_int] * 3),
     "mb200c_add_qelemwise": (C.c_int, [_P, C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_float]),
     "mb200c_mark_output": (C.c_int, [_P, C.c_int]),
@@ -83,6 +84,12 @@ class Graph:
             self._g, name.encode(), src, oc, kh, kw, stride, pad, groups, nonline.encode(),
             flt.ctypes.data, flt_scale, None if b is None else b.ctypes.data,
             None if cs is None else cs.ctypes.data, dst_scale))
+
+    def matmul(self, name, src, b, b_scale, dst_scale):
+        """MatrixMul + TypeCvt: src is a [batch][K] tensor (h = w = 1), b a [K, N] int8 array."""
+        b = np.ascontiguousarray(b, dtype=np.int8)
+        return _check(lib().mb200c_add_matmul(self._g, name.encode(), src, b.shape[1],
+                                              b.ctypes.data, b_scale, dst_scale))
 
     def pooling(self, name, src, mode, window, stride, pad):
         return _check(lib().mb200c_add_pooling(self._g, name.encode(), src, mode.encode(), window,

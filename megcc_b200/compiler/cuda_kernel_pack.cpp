@@ -444,6 +444,78 @@ TinyNNStatus ${signature} {
 }
 
 // ------------------------------------------------------------------------------------------
+// MatrixMul (+ TypeCvt)
+// ------------------------------------------------------------------------------------------
+bool MatMulQS8::IsAvailable(TContext* ctx) const {
+    if (!ctx->haveAttr("fused_typecvt") || ctx->getAttrStr("format") != "DEFAULT" ||
+        ctx->getAttrStr("compute_mode") != "DEFAULT")
+        return false;
+    if (ctx->getAttrBool("transposeA") || ctx->getAttrBool("transposeB"))
+        return false;
+    const CCOperand a = ctx->getAttrOprand("operand:0");
+    const CCOperand b = ctx->getAttrOprand("operand:1");
+    const CCOperand c = ctx->getAttrOprand("operand:2");
+    return is_quant(a.dtype, 8) && is_quant(b.dtype, 8) && is_quant(c.dtype, 8) && a.scale > 0 &&
+           b.scale > 0 && c.scale > 0;
+}
+
+std::string MatMulQS8::GetKernelSymbol(TContext*) const {
+    // kernel_matmul_<n|t><n|t>_<dtype> in the reference; the requantisation is spelled out
+    return "cuda_sm100_matmul_nn_qsi8qsi8qsi32_typecvt_qsi8";
+}
+
+std::string MatMulQS8::GetKernelBody(TContext* ctx) const {
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    const Tensor* a = inputs[0];
+    const Tensor* b = inputs[1]; /* re-laid to [N][K] by the init function */
+    Tensor* c = outputs[0];
+    const int m = a->layout.dims[0];
+    int k = 1;
+    for (int i = 1; i < a->layout.nr_dim; ++i) k *= a->layout.dims[i];
+    const int n = c->layout.dims[1];
+    /* scale of the qint32 product as MegEngine records it: one float multiplication */
+    const float acc_scale = a->dtype.param.scale * b->dtype.param.scale;
+    return (TinyNNStatus)mb200_matmul_s8_qs8(
+            m, n, k, (const int8_t*)a->ptr, (const int8_t*)b->ptr, (int8_t*)c->ptr, acc_scale,
+            c->dtype.param.scale, mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue()).set("signature", GetKernelSignature(ctx));
+    return s.text;
+}
+
+std::string MatMulQS8::GetInitBody(TContext* ctx) const {
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    /* three-phase init (runtime/src/data_struct.h:135-142): B [K][N] -> [N][K] on the device */
+    Tensor* b = inputs[1];
+    const int k = b->layout.dims[0], n = b->layout.dims[1];
+    if (out_weights == NULL && nr_out_weight != NULL) {
+        *nr_out_weight = 1;
+        return TinyNN_SUCCESS;
+    }
+    if (out_weights != NULL && nr_out_weight == NULL) {
+        out_weights[0].layout.nr_dim = 2;
+        out_weights[0].layout.dims[0] = n;
+        out_weights[0].layout.dims[1] = k;
+        out_weights[0].layout.stride[0] = k;
+        out_weights[0].layout.stride[1] = 1;
+        out_weights[0].dtype = b->dtype;
+        out_weights[0].name = b->name;
+        return TinyNN_SUCCESS;
+    }
+    return (TinyNNStatus)mb200_matmul_pack_b(
+            k, n, (const int8_t*)b->ptr, (int8_t*)out_weights[0].ptr, mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue()).set("signature", GetInitSignature(ctx));
+    return s.text;
+}
+
+// ------------------------------------------------------------------------------------------
 // Relayout
 // ------------------------------------------------------------------------------------------
 bool RelayoutQS8::IsAvailable(TContext* ctx) const {
@@ -483,7 +555,10 @@ std::vector<const KernelFunc*> ArchKernelPack::GetKernel(KernelPack::KernType ke
     static ElemwiseMultiTypeQS8 qelem;
     static TypeCvtQS32QS8 typecvt;
     static RelayoutQS8 relayout;
+    static MatMulQS8 matmul;
     switch (kernel_type) {
+        case KernelPack::KernType::MatrixMulKernel:
+            return {&matmul};
         case KernelPack::KernType::ConvKernel:
             return {&conv};
         case KernelPack::KernType::PoolingKernel:

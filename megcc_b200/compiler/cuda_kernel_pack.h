@@ -48,6 +48,20 @@ public:
     std::string GetKernelBody(TContext* ctx) const override;
 };
 
+// qint8 x qint8 -> qint32 MatrixMul with the TypeCvt to qint8 that follows it folded in
+// (attribute "fused_typecvt"), operand:0 A [M][K], operand:1 B [K][N] (a weight),
+// operand:2 C [M][N] qint8. The reference has an int8 MatrixMul only for Arm
+// (compiler/lib/KernelGen/Arm/Arm64/MatMulKernel/Int8DotMatMulM8N12K4.cpp:20-31); attribute
+// names are those of BareMetal::MatrixMulKernel (compiler/lib/KernelGen/BareMetal/
+// MatrixMul.cpp:13-43).
+class MatMulQS8 : public KernelFunc {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+    std::string GetInitBody(TContext* ctx) const override;
+};
+
 // NCHW <-> NHWC at the model boundary
 class RelayoutQS8 : public KernelFunc {
 public:

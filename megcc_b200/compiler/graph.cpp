@@ -47,7 +47,7 @@ struct GWeight {
     int use_count = 0;
 };
 
-enum class OpType { CONV, POOL, QELEM, RELAYOUT };
+enum class OpType { CONV, POOL, QELEM, RELAYOUT, MATMUL };
 
 struct GOp {
     OpType type;
@@ -210,6 +210,25 @@ struct mb200c_graph {
                 set_i32(*ctx, "nr_operands", k);
                 break;
             }
+            case OpType::MATMUL: {
+                // MatrixMul qsi8 x qsi8 -> qsi32 with the TypeCvt behind it folded in
+                // (attribute names of BareMetal/MatrixMul.cpp:13-43)
+                const GTensor& a = tensors[op.inputs[0]];
+                const GTensor& c = tensors[op.output];
+                const GWeight& b = weights[op.weights[0]];
+                set_u32(*ctx, "transposeA", 0);
+                set_u32(*ctx, "transposeB", 0);
+                set_str(*ctx, "format", "DEFAULT");
+                set_str(*ctx, "compute_mode", "DEFAULT");
+                set_str(*ctx, "fused_typecvt", "qsi8");
+                set_opr(*ctx, "operand:0",
+                        operand("qsi8", {(size_t)batch, (size_t)(a.c * a.h * a.w)}, a.scale));
+                set_opr(*ctx, "operand:1",
+                        operand("qsi8", {(size_t)b.dims[0], (size_t)b.dims[1]}, b.scale));
+                set_opr(*ctx, "operand:2", operand("qsi8", {(size_t)batch, (size_t)c.c}, c.scale));
+                set_i32(*ctx, "nr_operands", 3);
+                break;
+            }
             case OpType::RELAYOUT: {
                 set_str(*ctx, "relayout_mode", op.mode);
                 set_opr(*ctx, "operand:0",
@@ -227,6 +246,7 @@ struct mb200c_graph {
             case OpType::CONV: return KernType::ConvKernel;
             case OpType::POOL: return KernType::PoolingKernel;
             case OpType::QELEM: return KernType::ElemwiseMultiKernel;
+            case OpType::MATMUL: return KernType::MatrixMulKernel;
             default: return KernType::RelayoutKernel;
         }
     }
@@ -435,6 +455,34 @@ int mb200c_add_conv_bias(
         op.weights.push_back((int)g->weights.size() - 1);
     }
     op.output = g->add_tensor(std::string(name) + ":out", oc, oh, ow, dst_scale);
+    g->ops.push_back(op);
+    return op.output;
+}
+
+int mb200c_add_matmul(
+        mb200c_graph* g, const char* name, int src, int n, const int8_t* b, float b_scale,
+        float dst_scale) {
+    if (!g || !name || !b || !g->valid(src) || n <= 0)
+        return err("add_matmul: bad argument");
+    const GTensor s = g->tensors[src];
+    const int k = s.c * s.h * s.w;
+    if (s.h != 1 || s.w != 1)
+        return err("add_matmul %s: the input must be a [batch][K] matrix (h = w = 1)", name);
+    GOp op;
+    op.type = OpType::MATMUL;
+    op.name = name;
+    op.inputs = {src};
+    op.flt_scale = b_scale;
+    GWeight wb;
+    wb.name = std::string(name) + ":B";
+    wb.dtype = fb::QInt8;
+    wb.scale = b_scale;
+    wb.dims = {k, n};
+    wb.data.assign((const uint8_t*)b, (const uint8_t*)b + (size_t)k * n);
+    wb.use_count = 1;
+    g->weights.push_back(std::move(wb));
+    op.weights.push_back((int)g->weights.size() - 1);
+    op.output = g->add_tensor(std::string(name) + ":out", n, 1, 1, dst_scale);
     g->ops.push_back(op);
     return op.output;
 }
@@ -698,7 +746,12 @@ int mb200c_compile(
             const GOp& op = work.ops[k];
             std::vector<int32_t> in;
             std::vector<int8_t> in_t;
-            if (op.type == OpType::CONV) {
+            if (op.type == OpType::MATMUL) {
+                in.push_back(op.inputs[0]);
+                in_t.push_back(fb::TENSOR);
+                in.push_back(op.weights[0]);
+                in_t.push_back(fb::WEIGHT);
+            } else if (op.type == OpType::CONV) {
                 // operand order src, filter, [bias], [channel scales], [z, mid scale]
                 in.push_back(op.inputs[0]);
                 in_t.push_back(fb::TENSOR);

@@ -60,7 +60,9 @@ size_t tensor_bytes(const Tensor& t) {
     return n * dtype_bytes(t.dtype.type_enum);
 }
 
-enum OpKind { OP_CONV, OP_POOL, OP_QELEM, OP_TYPECVT, OP_RELAYOUT_TO_NHWC, OP_RELAYOUT_TO_NCHW };
+enum OpKind {
+    OP_CONV, OP_POOL, OP_QELEM, OP_TYPECVT, OP_RELAYOUT_TO_NHWC, OP_RELAYOUT_TO_NCHW, OP_MATMUL
+};
 
 struct OpPlan {
     OpKind kind;
@@ -233,6 +235,11 @@ bool parse_symbol(const std::string& sym, OpPlan* op) {
         op->kind = OP_QELEM;
         return op->mode >= 0;
     }
+    if (sym == "cuda_sm100_matmul_nn_qsi8qsi8qsi32_typecvt_qsi8") {
+        op->kind = OP_MATMUL;
+        op->needs_init = true;  // B [K][N] is re-laid to [N][K]
+        return true;
+    }
     if (sym == "cuda_sm100_typecvt_qsi32qsi8") {
         op->kind = OP_TYPECVT;
         return true;
@@ -329,6 +336,18 @@ int run_op(const OpPlan& op, cudaStream_t st) {
                     (const int8_t*)a->ptr, (const int8_t*)b->ptr, (int8_t*)op.outputs[0]->ptr,
                     op.mode, nr_elems(a), a->dtype.param.scale, b->dtype.param.scale,
                     op.outputs[0]->dtype.param.scale, st);
+        }
+        case OP_MATMUL: {
+            const Tensor* a = op.inputs[0];
+            const Tensor* b = op.inputs[1];  // re-laid to [N][K] at load
+            const Tensor* c = op.outputs[0];
+            const int m = a->layout.dims[0];
+            const int k = (int)(nr_elems(a) / (size_t)m);
+            const int n = c->layout.dims[1];
+            // scale of the qint32 product: one float multiplication, as MegEngine records it
+            const float acc_scale = a->dtype.param.scale * b->dtype.param.scale;
+            return mb200_matmul_s8_qs8(m, n, k, (const int8_t*)a->ptr, (const int8_t*)b->ptr,
+                                       (int8_t*)c->ptr, acc_scale, c->dtype.param.scale, st);
         }
         case OP_TYPECVT: {
             const Tensor* s = op.inputs[0];
@@ -610,8 +629,10 @@ int upload_weights(Network* net) {
     std::vector<int> pack_mode;  // per entry of `packs`
     for (auto& pk : packs) {
         mb200_conv_param cp;
-        fill_conv_param(*pk.first, &cp);
-        const bool s2d = !pk.first->z_mode && mb200_conv_s2d_supported(&cp) &&
+        if (pk.first->kind == OP_CONV)
+            fill_conv_param(*pk.first, &cp);
+        const bool s2d = pk.first->kind == OP_CONV && !pk.first->z_mode &&
+                         mb200_conv_s2d_supported(&cp) &&
                          pk.first->ws.size >= mb200_conv_s2d_workspace_bytes(&cp);
         pk.first->use_s2d = s2d;
         pack_mode.push_back(s2d ? 1 : 0);
@@ -652,6 +673,17 @@ int upload_weights(Network* net) {
         const int pi = packed_of[(size_t)wi * 2 + pack_mode[k]];
         Tensor* src = &net->weights[wi];
         Tensor* dst = &net->processed[pi];
+        if (!done[pi] && op->kind == OP_MATMUL) {
+            const Layout& l = src->layout;
+            if (l.nr_dim != 2)
+                return fail(TinyNN_ERROR_INVALID_LAYOUT, "MatrixMul weight must have 2 dims");
+            const int rc = mb200_matmul_pack_b((int)l.dims[0], (int)l.dims[1],
+                                               (const int8_t*)src->ptr, (int8_t*)dst->ptr,
+                                               net->stream);
+            if (rc)
+                return fail(rc, "re-laying matrix '%s': %s", src->name, mb200_last_error());
+            done[pi] = 1;
+        }
         if (!done[pi]) {
             const Layout& l = src->layout;
             if (l.nr_dim != 4 && l.nr_dim != 5)

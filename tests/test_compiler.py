@@ -185,6 +185,42 @@ def test_exported_stubs_compile_against_public_headers(tmp_path):
     assert all(tab[i] for i in range(len(syms)))
 
 
+def _matmul_graph():
+    from megcc_b200.compiler import Graph
+    rng = np.random.default_rng(11)
+    g = Graph("gap_matmul")
+    x = g.input("data", 64, 8, 8, 0.05)
+    f = rng.integers(-127, 128, (64, 64, 3, 3), dtype=np.int8)
+    y = g.conv_bias("conv", x, f, None, 1, 1, 0.01, 0.9, "RELU")
+    y = g.pooling("gap", y, "AVERAGE", 8, 8, 0)
+    b = rng.integers(-127, 128, (64, 200), dtype=np.int8)
+    y = g.matmul("fc", y, b, 0.01, 0.3)
+    g.mark_output(y)
+    return g, f, b
+
+
+def test_matmul_kernel_func_symbol_stub_and_model(tmp_path):
+    """MatrixMul + TypeCvt as an operator of a compiled model: the symbol follows the
+    reference's kernel_matmul_<n|t><n|t>_<dtype> scheme, the exported kernel and init stubs
+    compile as C99 against the public headers, and this repository's loader lists the
+    instruction with its weight."""
+    from megcc_b200 import _lib
+    g, _, _ = _matmul_graph()
+    model = g.compile([4])
+    syms = g.kernel_symbols()
+    assert "cuda_sm100_matmul_nn_qsi8qsi8qsi32_typecvt_qsi8" in syms
+    g.export_kernels(str(tmp_path))
+    srcs = [str(tmp_path / f) for f in sorted(os.listdir(tmp_path)) if f.endswith(".c")]
+    so = str(tmp_path / "libkernels.so")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-shared", "-fPIC",
+                    "-I" + os.path.join(ROOT, "include"), "-I" + str(tmp_path), "-o", so] + srcs
+                   + [_lib.LIB_PATH], check=True)
+    out = C.create_string_buffer(1 << 16)
+    assert _lib.lib().mb200_tinynn_describe(model, len(model), out, len(out)) == 0
+    text = out.value.decode()
+    assert "cuda_sm100_matmul_nn_qsi8qsi8qsi32_typecvt_qsi8" in text and "fc:B" in text
+
+
 def test_compile_side_builds_inside_the_reference_kernelgen(tmp_path):
     """The CUDA kernel pack and graph compiler, compiled against the reference's own
     KernelGen.h / TContext.h and linked with its registry (oracle/Makefile), emit byte for
