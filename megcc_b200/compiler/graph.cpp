@@ -91,11 +91,13 @@ void set_u32(CodeGenContext& c, const char* k, uint32_t v) { c.setAttr(k, CCAttr
 void set_i32(CodeGenContext& c, const char* k, int32_t v) { c.setAttr(k, CCAttr(v)); }
 void set_str(CodeGenContext& c, const char* k, const std::string& v) { c.setAttr(k, CCAttr(v)); }
 void set_opr(CodeGenContext& c, const std::string& k, const CCOperand& v) { c.setAttr(k, CCAttr(v)); }
+void set_bool(CodeGenContext& c, const char* k, bool v) { c.setAttr(k, CCAttr(v)); }
 #else
 void set_u32(CodeGenContext& c, const char* k, uint32_t v) { c.setInt(k, v); }
 void set_i32(CodeGenContext& c, const char* k, int32_t v) { c.setInt(k, v); }
 void set_str(CodeGenContext& c, const char* k, const std::string& v) { c.setStr(k, v); }
 void set_opr(CodeGenContext& c, const std::string& k, const CCOperand& v) { c.setOperand(k, v); }
+void set_bool(CodeGenContext& c, const char* k, bool v) { c.setInt(k, v ? 1 : 0); }
 #endif
 
 int out_extent(int in, int k, int s, int p) {
@@ -216,8 +218,8 @@ struct mb200c_graph {
                 const GTensor& a = tensors[op.inputs[0]];
                 const GTensor& c = tensors[op.output];
                 const GWeight& b = weights[op.weights[0]];
-                set_u32(*ctx, "transposeA", 0);
-                set_u32(*ctx, "transposeB", 0);
+                set_bool(*ctx, "transposeA", false);
+                set_bool(*ctx, "transposeB", false);
                 set_str(*ctx, "format", "DEFAULT");
                 set_str(*ctx, "compute_mode", "DEFAULT");
                 set_str(*ctx, "fused_typecvt", "qsi8");
