@@ -102,14 +102,14 @@ def test_matmul_instruction_in_a_model_matches_oracle(lite, oracle):
     y = g.conv_bias("conv", x, f, None, 1, 1, 0.01, 0.9, "RELU")
     y = g.pooling("gap", y, "AVERAGE", 8, 8, 0)
     b = rng.integers(-127, 128, (64, 200), dtype=np.int8)
-    y = g.matmul("fc", y, b, 0.01, 0.3)
+    y = g.matmul("fc", y, b, 0.01, 25.0)
     g.mark_output(y)
     model = g.compile([n])
     src = rng.integers(-128, 128, (n, 64, 8, 8), dtype=np.int8)
     conv = oracle.conv_bias_qs8(src, f, None, 1, 1, 0.05, 0.01, 0.9, "RELU")
     pooled = oracle.pooling_qs8(conv, "AVERAGE", 8, 8, 0).reshape(n, 64)
     acc = oracle.matmul_s8_s32(pooled, b)
-    want = oracle.typecvt_qs32_qs8(acc, float(np.float32(0.9) * np.float32(0.01)), 0.3)
+    want = oracle.typecvt_qs32_qs8(acc, float(np.float32(0.9) * np.float32(0.01)), 25.0)
     for out in run_model(lite, model, src, (n, 200), forwards=3):
         assert (out == want).all()
     assert (np.abs(want.astype(int)) < 127).mean() > 0.3
