@@ -115,6 +115,35 @@ def test_matmul_instruction_in_a_model_matches_oracle(lite, oracle):
     assert (np.abs(want.astype(int)) < 127).mean() > 0.3
 
 
+def test_three_networks_in_flight_with_large_host_inputs(lite, oracle):
+    """Three networks of one model on one GPU, each given a different 9.6 MB host input
+    (large enough to be copied in four pieces on the side streams), forwards enqueued before
+    any wait and collected out of order, twice: every network's output must be its own
+    input's result. Exercises the split copy and the one-after-the-other ordering of the
+    networks' kernel sequences."""
+    from megcc_b200 import zoo
+    n = 64
+    spec = zoo.single_conv(ic=3, oc=64, hw=224, k=7, stride=2, pad=3, s_src=0.02, s_flt=0.01,
+                           s_dst=0.5)
+    flt, bias = spec.layers[0]["flt"], spec.layers[0]["bias"]
+    model = spec.to_graph().compile([n])
+    rng = np.random.default_rng(5)
+    nets = [lite.Network(model) for _ in range(3)]
+    name_in, name_out = nets[0].input_names()[0], nets[0].output_names()[0]
+    for rnd in range(2):
+        xs = [rng.integers(-128, 128, (n, 3, 224, 224), dtype=np.int8) for _ in nets]
+        for net, x in zip(nets, xs):
+            net.set_input(name_in, x)
+            net.forward()
+        for i in (2, 0, 1):
+            nets[i].wait()
+            out = nets[i].output(name_out).reshape(n, 64, 112, 112)
+            want = oracle.conv_bias_qs8(xs[i], flt, bias, 2, 3, 0.02, 0.01, 0.5, "RELU")
+            assert (out == want).all(), (rnd, i)
+    for net in nets:
+        net.close()
+
+
 def test_batch_variants_and_device_io(lite, oracle):
     from megcc_b200 import zoo
     spec = zoo.resnet18(hw=64, classes=100)
