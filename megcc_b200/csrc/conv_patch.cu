@@ -164,12 +164,40 @@ __device__ __forceinline__ void issue_tile_mmas(
     }
 }
 
-template <int BN, int KH, int KW, int CHUNKS, int EW>
+// The row form (ROWS = 1; 64 input channels): the patch is stored as [patch row][16 columns]
+// [64 bytes] with the 64-byte swizzle, one TMA request whose rows are a pixel's 64 channels.
+// The plain form above needs C/16 rows of 16 bytes per pixel, and the TMA unit's cost is per
+// row: 720 rows per tile against 288 here. A patch row is padded to 16 columns so that the
+// 8-row groups of a tap lie a multiple of the swizzle pattern (512 bytes) apart; the
+// swizzle is a function of the shared-memory address, so a tap's shifted start needs
+// nothing else. `a0` / `b0` are 64-byte-swizzle descriptors of the stage / filter base.
+constexpr int kRowCols = 16;
+template <int BN, int KH, int KW>
+__device__ __forceinline__ void issue_tile_mmas_rows64(uint64_t a0, uint64_t b0, uint32_t tmem_d) {
+    constexpr uint32_t idesc = umma_idesc_s8(128, BN);
+    constexpr uint32_t pix16 = 64 / 16;  // one pixel in descriptor address units
+#pragma unroll
+    for (int fy = 0; fy < KH; ++fy) {
+#pragma unroll
+        for (int fx = 0; fx < KW; ++fx) {
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {  // two K steps of 32 bytes inside the 64-byte row
+                const uint64_t ad = a0 + (uint32_t)((fy * kRowCols + fx) * pix16 + 2 * k);
+                const uint64_t bd = b0 + (uint32_t)((fy * KW + fx) * BN * pix16 + 2 * k);
+                if ((fy | fx | k) == 0)
+                    umma_s8_c<false>(tmem_d, ad, bd, idesc);
+                else
+                    umma_s8_c<true>(tmem_d, ad, bd, idesc);
+            }
+        }
+    }
+}
+
+template <int BN, int KH, int KW, int CHUNKS, int EW, int ROWS = 0>
 __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const PatchParams p) {
     constexpr int kEpilogueWarps = EW;
-    constexpr int kEpilogueThreads = 32 * EW;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_b = smem;
@@ -198,7 +226,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], kEpilogueThreads);
+            mbar_init(&acc_empty[b], 32 * kEpilogueWarps);  // every epilogue thread arrives
         }
         mbar_init(b_full, 1);
         mbar_init(drain_bar, 1);
@@ -224,7 +252,11 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
             // the filter slice, once: one [BN][16-byte] block per 16 bytes of K
             const int kchunks = p.kh * p.kw * p.chunks;
             mbar_expect_tx(b_full, (uint32_t)p.b_bytes);
-            if (p.b_single_load) {
+            if (ROWS) {
+                // one swizzled [BN][64-byte] tile per filter tap
+                for (int t = 0; t < p.kh * p.kw; ++t)
+                    tma_load_2d(smem_b + t * (BN * 64), &map_b, b_full, t * 64, n0);
+            } else if (p.b_single_load) {
                 // 3-D view {16 bytes, rows, K/16}: one request lays down every block
                 tma_load_3d(smem_b, &map_b, b_full, 0, n0, 0);
             } else {
@@ -245,8 +277,13 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
                 const int img = at.img;
                 const int x0 = at.tx * kTW - p.pw, y0 = at.ty * kTH - p.ph;
                 mbar_expect_tx(&a_full[s], (uint32_t)p.a_tx_bytes);
-                // one request: box {16 B, patch columns, patch rows, 1 image, all chunks}
-                tma_load_5d(smem_a + s * p.a_stage_bytes, &map_a, &a_full[s], 0, x0, y0, img, 0);
+                if (ROWS) {
+                    // one request: box {64 B, 16 columns, patch rows, 1 image}
+                    tma_load_4d(smem_a + s * p.a_stage_bytes, &map_a, &a_full[s], 0, x0, y0, img);
+                } else {
+                    // one request: box {16 B, patch columns, patch rows, 1 image, all chunks}
+                    tma_load_5d(smem_a + s * p.a_stage_bytes, &map_a, &a_full[s], 0, x0, y0, img, 0);
+                }
                 if (++s == p.stages) {
                     s = 0;
                     phase ^= 1u;
@@ -262,7 +299,8 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
                 atomicExch(p.status, ERR_MMA_WAIT);
             }
             const uint32_t sbo_a = (uint32_t)p.ppw * 16;  // the next patch row
-            const uint64_t b0 = umma_smem_desc(smem_u32(smem_b), BN * 16, 128, 0);
+            const uint64_t b0 = ROWS ? umma_smem_desc(smem_u32(smem_b), 16, 512, 4)
+                                     : umma_smem_desc(smem_u32(smem_b), BN * 16, 128, 0);
             int local = 0, s = 0;
             uint32_t phase = 0;
             for (int mt = m_first; mt < p.m_tiles && ok; mt += m_step, ++local) {
@@ -285,8 +323,14 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_addr = smem_u32(smem_a + s * p.a_stage_bytes);
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                const uint64_t a0 = umma_smem_desc(a_addr, (uint32_t)p.a_lbo, sbo_a, 0);
-                issue_tile_mmas<BN, KH, KW, CHUNKS>(p, a0, b0, tmem_d);
+                if constexpr (ROWS != 0) {
+                    // 8-row groups (patch rows) are 16 pixels x 64 bytes apart
+                    const uint64_t a0 = umma_smem_desc(a_addr, 16, kRowCols * 64, 4);
+                    issue_tile_mmas_rows64<BN, KH, KW>(a0, b0, tmem_d);
+                } else {
+                    const uint64_t a0 = umma_smem_desc(a_addr, (uint32_t)p.a_lbo, sbo_a, 0);
+                    issue_tile_mmas<BN, KH, KW, CHUNKS>(p, a0, b0, tmem_d);
+                }
                 umma_commit(&a_empty[s]);
                 umma_commit(&acc_full[buf]);
                 if (++s == p.stages) {
@@ -326,17 +370,31 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
             constexpr int kChunksPerWarp = (BN / 32) / (kEpilogueWarps / 4);
             static_assert(kChunksPerWarp >= 1, "every epilogue warp must own a chunk: it is "
                                                "counted on the accumulator-drained barrier");
-#pragma unroll 1
-            for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; ++c) {
+            // one 32-column chunk: registers <- TMEM, buffer released after the warp's last
+            // load, requantisation, store
+            auto do_chunk = [&](int c, bool last) {
                 uint32_t v[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), v);
-                if (c + 1 == (half + 1) * kChunksPerWarp) {
+                if (last) {
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     mbar_arrive(&acc_empty[buf]);
                 }
                 const int ch0 = n0 + c * 32;
                 if (valid && ch0 < p.oc)
                     epilogue_store<32>(v, p.ep, p.dst, px_off + ch0, ch0);
+            };
+            if constexpr (kChunksPerWarp == 1) {
+                // Written as a strided loop of (at run time) one trip: with the chunk's code
+                // inlined straight into the tile loop the compiler spills 2 KB per thread
+                // per tile at 64 registers, and the 64-channel kernels run 5 % slower.
+                constexpr int kChunkStep = kEpilogueWarps / 4;
+#pragma unroll 1
+                for (int c = half; c < BN / 32; c += kChunkStep)
+                    do_chunk(c, c + kChunkStep >= BN / 32);
+            } else {
+#pragma unroll 1
+                for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; ++c)
+                    do_chunk(c, c + 1 == (half + 1) * kChunksPerWarp);
             }
         }
     }
@@ -370,6 +428,7 @@ struct PatchPlan {
     bool ok;
     int bn, stages, ctas_per_sm;
     int a_stage_bytes, b_bytes, smem_bytes, plane_stride;
+    bool rows64;  // 64-channel 3x3: pixel rows of 64 bytes, 64-byte swizzle
 };
 
 // CTAs per SM to try first; MB200_PATCH_CTAS overrides (performance experiments)
@@ -393,9 +452,12 @@ PatchPlan plan_patch(const ConvArgs& a) {
     if (pph > 256 || ppw > 256)
         return pl;
     pl.bn = a.oc <= 64 ? 64 : 128;
+    pl.rows64 = a.ic == 64 && a.kh == 3 && a.kw == 3 && pl.bn == 64 && !getenv("MB200_PATCH_PLAIN");
     pl.plane_stride = pph * ppw * 16;
     // a TMA destination in shared memory must be 128-byte aligned: pad the stage
     pl.a_stage_bytes = ((a.ic / 16) * pl.plane_stride + 127) / 128 * 128;
+    if (pl.rows64)
+        pl.a_stage_bytes = pph * kRowCols * 64;  // a multiple of 1024
     pl.b_bytes = pl.bn * a.kh * a.kw * a.ic;
     const int fixed = pl.b_bytes + (2 * kMaxStages + 6) * 8 + 64 + 1024;
     const int budget = 227 * 1024;
@@ -418,18 +480,18 @@ PatchPlan plan_patch(const ConvArgs& a) {
     return pl;
 }
 
-template <int BN, int KH, int KW, int CHUNKS, int EW>
+template <int BN, int KH, int KW, int CHUNKS, int EW, int ROWS = 0>
 int launch_patch(
         const CUtensorMap& ma, const CUtensorMap& mb, const PatchParams& p, int smem, int grid,
         cudaStream_t st) {
     constexpr int kThreads = 64 + 32 * EW;
     if (cudaFuncSetAttribute(
-                conv_patch_kernel<BN, KH, KW, CHUNKS, EW>,
+                conv_patch_kernel<BN, KH, KW, CHUNKS, EW, ROWS>,
                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return check_launch("conv_patch smem attribute");
     // never more CTAs than are resident at once: a persistent CTA that starts late would
     // leave its share of the patches to the end
-    const int per_sm = resident_ctas_per_sm(conv_patch_kernel<BN, KH, KW, CHUNKS, EW>, kThreads, smem, 2 * BN);
+    const int per_sm = resident_ctas_per_sm(conv_patch_kernel<BN, KH, KW, CHUNKS, EW, ROWS>, kThreads, smem, 2 * BN);
     {
         int cap = sm_count() * per_sm / p.n_tiles * p.n_tiles;
         if (cap >= p.n_tiles && grid > cap)
@@ -439,7 +501,7 @@ int launch_patch(
         fprintf(stderr, "conv_patch<%d,%d,%d,%d,%d>: per_sm %d grid %d m_tiles %d n_tiles %d smem %d "
                 "stages %d b_single_load %d\n", BN, KH, KW, CHUNKS, EW, per_sm, grid, p.m_tiles,
                 p.n_tiles, smem, p.stages, p.b_single_load);
-    conv_patch_kernel<BN, KH, KW, CHUNKS, EW><<<grid, kThreads, smem, st>>>(ma, mb, p);
+    conv_patch_kernel<BN, KH, KW, CHUNKS, EW, ROWS><<<grid, kThreads, smem, st>>>(ma, mb, p);
     return check_launch("conv_patch");
 }
 
@@ -490,7 +552,31 @@ int launch_conv_patch(
 
     const int pph = kTH + a.kh - 1, ppw = kTW + a.kw - 1;
     CUtensorMap map_a, map_b;
-    {
+    if (pl.rows64) {
+        cuuint64_t dims[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw, (cuuint64_t)a.ih,
+                              (cuuint64_t)a.n};
+        cuuint64_t strides[3] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw * a.ic,
+                                 (cuuint64_t)a.ih * a.iw * a.ic};
+        cuuint32_t box[4] = {64, (cuuint32_t)kRowCols, (cuuint32_t)pph, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = api.tiled(
+                &map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)src, dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(activation) failed: %d", (int)r);
+        const cuuint64_t k_total = (cuuint64_t)a.kh * a.kw * a.ic;
+        cuuint64_t bdims[2] = {k_total, (cuuint64_t)a.oc};
+        cuuint64_t bstrides[1] = {k_total};
+        cuuint32_t bbox[2] = {64, (cuuint32_t)pl.bn};
+        cuuint32_t bestr[2] = {1, 1};
+        r = api.tiled(
+                &map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)flt, bdims, bstrides, bbox, bestr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(filter) failed: %d", (int)r);
+    } else {
         // NHWC seen as {16 channel bytes, W, H, N, C/16}: a box over all chunks arrives as
         // [chunk][row][column][16 bytes]
         cuuint64_t dims[5] = {16, (cuuint64_t)a.iw, (cuuint64_t)a.ih, (cuuint64_t)a.n,
@@ -507,7 +593,7 @@ int launch_conv_patch(
             return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(activation) failed: %d", (int)r);
     }
     int b_single_load = 0;
-    {
+    if (!pl.rows64) {
         const cuuint64_t k_total = (cuuint64_t)a.kh * a.kw * a.ic;
         const cuuint64_t kchunks = k_total / 16;
         CUresult r = CUDA_ERROR_INVALID_VALUE;
@@ -557,7 +643,7 @@ int launch_conv_patch(
     p.stages = pl.stages;
     p.a_stage_bytes = pl.a_stage_bytes;
     p.plane_stride = pl.plane_stride;
-    p.a_tx_bytes = p.chunks * pl.plane_stride;
+    p.a_tx_bytes = pl.rows64 ? pl.a_stage_bytes : p.chunks * pl.plane_stride;
     p.b_bytes = pl.b_bytes;
     p.b_single_load = b_single_load;
     p.mma_per_tap = a.ic == 16 ? 0 : a.ic / 32;
@@ -606,7 +692,9 @@ int launch_conv_patch(
         grid = (int)total;
     int rc;
     const bool alone = pl.ctas_per_sm == 1;  // one CTA per SM: sixteen epilogue warps
-    if (pl.bn == 64 && a.kh == 3 && a.kw == 3 && a.ic == 64 && !alone)
+    if (pl.rows64)
+        rc = launch_patch<64, 3, 3, 4, 8, 1>(map_a, map_b, p, pl.smem_bytes, grid, st);
+    else if (pl.bn == 64 && a.kh == 3 && a.kw == 3 && a.ic == 64 && !alone)
         rc = launch_patch<64, 3, 3, 4, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);
     else if (pl.bn == 64 && a.kh == 4 && a.kw == 4 && a.ic == 16 && !alone)
         rc = launch_patch<64, 4, 4, 1, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);

@@ -96,7 +96,6 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
     constexpr int kBKc = Geom<BN, GEOM>::kBKg;
     constexpr int kSt = Geom<BN, GEOM>::kStagesG;
     constexpr int kEpilogueWarps = Shape<BN>::kEpilogueWarps;
-    constexpr int kEpilogueThreads = Shape<BN>::kEpilogueThreads;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles_a = smem;
@@ -119,7 +118,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], kEpilogueThreads);
+            mbar_init(&acc_empty[b], 32 * kEpilogueWarps);  // every epilogue thread arrives
         }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;

