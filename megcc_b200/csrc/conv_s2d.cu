@@ -99,6 +99,57 @@ __global__ void __launch_bounds__(256) space_to_depth_nchw2_kernel(
     }
 }
 
+// Three channels, NCHW, width a multiple of 8, 8-byte aligned base: one thread makes FOUR
+// adjacent half-resolution pixels from six 8-byte loads (two source rows of three channel
+// planes) and writes 64 contiguous bytes. The twelve bytes of a pixel are put in place by
+// seven byte permutes instead of a shift, a mask and an OR each: the general kernels above
+// execute some 380 instructions per pixel and are bound by instruction issue (measured: 46 us
+// for a 256 x 3 x 224 x 224 input, 80 % issue-active, 12 % of the DRAM bandwidth).
+// Slot order: (dy*2 + dx)*3 + ch, so word 0 = [c0 c1 c2 | c0'] of the upper row's left and
+// right byte, word 1 = [c1' c2' | lower row c0 c1], word 2 = [c2 | c0' c1' c2'], word 3 = 0.
+__global__ void __launch_bounds__(256) space_to_depth_nchw3_x4_kernel(
+        const int8_t* __restrict__ src, uint4* __restrict__ dst, int n, int h, int w, int h2) {
+    const unsigned w8 = (unsigned)w / 8;  // groups of four half-resolution pixels per row
+    const unsigned total = (unsigned)n * h2 * w8;
+    const size_t plane = (size_t)h * w;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += gridDim.x * blockDim.x) {
+        const unsigned xg = idx % w8;
+        const unsigned t = idx / w8;
+        const unsigned y2 = t % h2, b = t / h2;
+        const int8_t* row = src + ((size_t)b * 3 * h + 2 * y2) * w + 8 * xg;
+        uint2 r[2][3];
+#pragma unroll
+        for (int dy = 0; dy < 2; ++dy) {
+#pragma unroll
+            for (int ch = 0; ch < 3; ++ch) {
+                r[dy][ch] = make_uint2(0, 0);
+                if ((int)(2 * y2) + dy < h)
+                    r[dy][ch] = __ldg(reinterpret_cast<const uint2*>(row + ch * plane + (size_t)dy * w));
+            }
+        }
+        uint4* out = dst + (size_t)idx * 4;  // half-resolution pixels are w/2 = 4*w8 per row
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            // source bytes 2p (left) and 2p + 1 (right) of every row: byte o / o + 1 of a word
+            constexpr unsigned kFromY = 4;
+            const unsigned o = (unsigned)(p & 1) * 2;
+            const uint32_t a0 = p < 2 ? r[0][0].x : r[0][0].y, a1 = p < 2 ? r[0][1].x : r[0][1].y,
+                           a2 = p < 2 ? r[0][2].x : r[0][2].y;
+            const uint32_t b0 = p < 2 ? r[1][0].x : r[1][0].y, b1 = p < 2 ? r[1][1].x : r[1][1].y,
+                           b2 = p < 2 ? r[1][2].x : r[1][2].y;
+            const uint32_t t0 = __byte_perm(a0, a1, o | (kFromY + o) << 4 | (o + 1) << 12);
+            const uint32_t w0 = __byte_perm(t0, a2, 0x3010u | (kFromY + o) << 8);
+            const uint32_t t1 = __byte_perm(a1, a2, (o + 1) | (kFromY + o + 1) << 4);
+            const uint32_t t2 = __byte_perm(b0, b1, o | (kFromY + o) << 4);
+            const uint32_t w1 = __byte_perm(t1, t2, 0x5410u);
+            const uint32_t t3 = __byte_perm(b2, b0, o | (kFromY + o + 1) << 4 | (o + 1) << 12);
+            const uint32_t w2 = __byte_perm(t3, b1, 0x3010u | (kFromY + o + 1) << 8);
+            out[p] = make_uint4(w0, w1, w2, 0u);
+        }
+    }
+}
+
 // OIHW -> [OC][kh2][kw2][16]
 __global__ void __launch_bounds__(256) s2d_pack_filter_kernel(
         const int8_t* __restrict__ src, int8_t* __restrict__ dst, int oc, int ic, int kh, int kw,
@@ -172,8 +223,12 @@ int launch_conv_s2d(
         sy = (long long)a.iw * a.ic;
         sn = sy * a.ih;
     }
-    if (a.src_is_nchw && a.iw % 2 == 0 && ((uintptr_t)src & 1) == 0 && g.w2 == a.iw / 2 &&
-        (size_t)a.n * g.h2 * g.w2 < (1u << 31)) {
+    if (a.src_is_nchw && a.ic == 3 && a.iw % 8 == 0 && ((uintptr_t)src & 7) == 0 &&
+        g.w2 == a.iw / 2 && (size_t)a.n * g.h2 * g.w2 < (1u << 31)) {
+        space_to_depth_nchw3_x4_kernel<<<grid_for((size_t)a.n * g.h2 * (a.iw / 8)), 256, 0, st>>>(
+                src, (uint4*)workspace, a.n, a.ih, a.iw, g.h2);
+    } else if (a.src_is_nchw && a.iw % 2 == 0 && ((uintptr_t)src & 1) == 0 && g.w2 == a.iw / 2 &&
+               (size_t)a.n * g.h2 * g.w2 < (1u << 31)) {
         space_to_depth_nchw2_kernel<<<grid_for((size_t)a.n * g.h2 * g.w2), 256, 0, st>>>(
                 src, (uint4*)workspace, a.n, a.ic, a.ih, a.iw, g.h2, g.w2);
     } else {

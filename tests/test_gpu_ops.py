@@ -287,6 +287,8 @@ S2D_CASES = [
     ("r18_stem", 2, 3, 64, 224, 224, 7, 3, "RELU"),
     ("mbv1_stem", 2, 3, 32, 224, 224, 3, 1, "RELU"),
     ("odd_hw", 3, 3, 64, 225, 223, 7, 3, "IDENTITY"),
+    ("odd_h_w8", 4, 3, 48, 97, 104, 3, 1, "RELU"),
+    ("odd_h_w8_k7", 8, 3, 64, 61, 72, 7, 3, "IDENTITY"),
     ("ic1_k5", 4, 1, 40, 120, 120, 5, 2, "RELU"),
     ("ic4_k3_nopad", 4, 4, 136, 96, 100, 3, 0, "H_SWISH"),
     ("ic2_k2", 4, 2, 64, 128, 128, 2, 0, "RELU"),
