@@ -266,6 +266,60 @@ __global__ void __launch_bounds__(64) pooling_global_avg_vec16_kernel(
     }
 }
 
+// The same with the pixels of one image split over the four warps of a CTA: a classifier's
+// global pool has few outputs (batch x C/16 vectors) but 49 loads and 800 additions behind
+// each, and one thread per output leaves most SMs with a single busy warp (21 us for
+// 256 x 7 x 7 x 512). A CTA takes 32 consecutive 16-channel vectors of one image; warp g sums
+// pixels g, g+4, ...; the partial sums meet in shared memory and every thread finishes four
+// channels. The integer sum is exact in any order, the division is the one of
+// pooling_kernel.
+__global__ void __launch_bounds__(128) pooling_global_avg_split_kernel(
+        const uint4* __restrict__ src, uint32_t* __restrict__ dst, int c16, int pixels,
+        int blocks_per_image) {
+    __shared__ int part[4][16][32];
+    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int b = blockIdx.x / blocks_per_image;
+    const int cv = (blockIdx.x - b * blocks_per_image) * 32 + lane;
+    const bool live = cv < c16;
+    int sum[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        sum[i] = 0;
+    if (live) {
+        const uint4* p = src + (size_t)b * pixels * c16 + cv;
+        for (int px0 = g; px0 < pixels; px0 += 4 * 7) {
+            uint4 v[7];
+#pragma unroll
+            for (int k = 0; k < 7; ++k)
+                v[k] = px0 + 4 * k < pixels ? __ldg(p + (size_t)(px0 + 4 * k) * c16)
+                                            : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int k = 0; k < 7; ++k) {
+                const uint32_t w[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    sum[i] += (int)(int8_t)(w[i >> 2] >> (8 * (i & 3)));
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        part[g][i][lane] = sum[i];
+    __syncthreads();
+    if (!live)
+        return;
+    // thread (g, lane): channels 4g .. 4g+3 of vector `cv`
+    const float d = (float)pixels;
+    int r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int s = part[0][4 * g + i][lane] + part[1][4 * g + i][lane] +
+                      part[2][4 * g + i][lane] + part[3][4 * g + i][lane];
+        r[i] = f32_to_i32_x86(roundf(__fdiv_rn(__int2float_rn(s), d)));
+    }
+    dst[((size_t)b * c16 + cv) * 4 + g] = pack4(r[0], r[1], r[2], r[3]);
+}
+
 // ------------------------------------------------------------------------------------------
 // quantised elementwise, same-shape operands, 16 bytes per thread
 // ------------------------------------------------------------------------------------------
@@ -404,6 +458,12 @@ int launch_pooling(
         ww == iw && ph == 0 && pw == 0 && (size_t)n * (c / 16) < (1u << 31)) {
         // one window per image and no padding: both AVERAGE modes divide by wh * ww
         const size_t work = (size_t)n * (c / 16);
+        const int per_image = (c / 16 + 31) / 32;
+        if (ih * iw >= 8 && (size_t)n * per_image < (1u << 30)) {
+            pooling_global_avg_split_kernel<<<n * per_image, 128, 0, st>>>(
+                    (const uint4*)src, (uint32_t*)dst, c / 16, ih * iw, per_image);
+            return check_launch("pooling_global_avg_split");
+        }
         pooling_global_avg_vec16_kernel<<<grid_for(work, 64), 64, 0, st>>>(
                 (const uint4*)src, (uint4*)dst, n, c / 16, ih * iw);
         return check_launch("pooling_global_avg_vec16");

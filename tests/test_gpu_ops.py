@@ -436,6 +436,21 @@ def test_global_average_pool_matches_oracle(ops, oracle, mode):
     assert (out == oracle.pooling_qs8(x, mode, 5, 5, 0)).all()
 
 
+@pytest.mark.parametrize("shape", [(16, 512, 7, 7), (3, 1040, 5, 5), (2, 16, 3, 3), (4, 32, 2, 2),
+                                   (2, 528, 14, 14)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_global_average_pool_shapes(ops, oracle, shape):
+    """The CTA-per-image kernel (pixels split over four warps, partial sums in shared memory):
+    fewer and more than 32 channel vectors per image, pixel counts that are no multiple of
+    four, and a 2x2 image that stays on the one-thread-per-output kernel."""
+    n, c, h, w = shape
+    x = cases.rng_for("gap_shape_%d_%d_%d_%d" % shape).integers(-128, 128, shape, dtype=np.int8)
+    x[0, : c // 2] = 127
+    y = ops.pooling_qs8_nhwc(ops.nchw_to_nhwc(dev(x)), "AVERAGE", h, h, 0)
+    out = ops.nhwc_to_nchw(y).cpu().numpy()
+    assert (out == oracle.pooling_qs8(x, "AVERAGE", h, h, 0)).all()
+
+
 def test_qelemwise_golden(ops):
     for c in cases.qelem_catalogue():
         if c["a"] != c["b"]:
