@@ -214,14 +214,37 @@ __global__ void __launch_bounds__(256) pooling_max_3x3s2_vec16_kernel(
                                                                      : lowest;
             }
         }
-        uint4 col[5];
+        // Column maxima, then the two windows. Signed bytes are compared as the HIGH bytes of
+        // signed 16-bit lanes (one three-input s16x2 maximum per lane pair; the byte-wise
+        // intrinsic is emulated with a dozen instructions and made this kernel ALU-bound at
+        // 53 % of the DRAM bandwidth): odd bytes already are high bytes, even bytes after a
+        // shift by 8; what sits in a lane's low byte only breaks ties between equal high
+        // bytes and is dropped when the two halves are merged.
+        uint32_t odd[5][4], even[5][4];
 #pragma unroll
-        for (int fx = 0; fx < 5; ++fx)
-            col[fx] = vmax16(vmax16(v[0][fx], v[1][fx]), v[2][fx]);
+        for (int fx = 0; fx < 5; ++fx) {
+            const uint32_t r0[4] = {v[0][fx].x, v[0][fx].y, v[0][fx].z, v[0][fx].w};
+            const uint32_t r1[4] = {v[1][fx].x, v[1][fx].y, v[1][fx].z, v[1][fx].w};
+            const uint32_t r2[4] = {v[2][fx].x, v[2][fx].y, v[2][fx].z, v[2][fx].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                odd[fx][k] = __vimax3_s16x2(r0[k], r1[k], r2[k]);
+                even[fx][k] = __vimax3_s16x2(r0[k] << 8, r1[k] << 8, r2[k] << 8);
+            }
+        }
+        uint32_t o0[4], o1[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            // bytes 1 and 3 of both halves -> bytes (even, odd, even, odd)
+            o0[k] = __byte_perm(__vimax3_s16x2(even[0][k], even[1][k], even[2][k]),
+                                __vimax3_s16x2(odd[0][k], odd[1][k], odd[2][k]), 0x7351);
+            o1[k] = __byte_perm(__vimax3_s16x2(even[2][k], even[3][k], even[4][k]),
+                                __vimax3_s16x2(odd[2][k], odd[3][k], odd[4][k]), 0x7351);
+        }
         uint4* out = dst + ((size_t)((unsigned)b * oh + y) * ow + x0) * c16 + cv;
-        out[0] = vmax16(vmax16(col[0], col[1]), col[2]);
+        out[0] = make_uint4(o0[0], o0[1], o0[2], o0[3]);
         if (x0 + 1 < ow)
-            out[c16] = vmax16(vmax16(col[2], col[3]), col[4]);
+            out[c16] = make_uint4(o1[0], o1[1], o1[2], o1[3]);
     }
 }
 
