@@ -24,6 +24,10 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "conv_epilogue.cuh"
 #include "internal.h"
 #include "umma_ptx.cuh"
@@ -75,20 +79,51 @@ struct UmmaConvParams {
     EpilogueParams ep;
     int8_t* dst;
     int* status;
+    // split-K (SPLITK kernels only): work items below `full_tiles` are whole tiles, the
+    // tiles after them are cut into `split` parts of `k_per_part` pipeline steps each
+    int full_tiles, split, k_per_part, total_items;
+    int4* slabs;          // [split item][chunk][16-byte group][row]: one part's accumulators
+    unsigned* counters;   // [split tile] parts finished; zero between launches
 };
+
+// One unit of work of a persistent CTA: a whole tile, or one K range of a split tile.
+struct WorkItem {
+    int tile, k0, k1;
+    int slot;  // index of the split item (its slab), -1 for a whole tile
+};
+
+template <bool SPLITK>
+__device__ __forceinline__ WorkItem decode_item(const UmmaConvParams& p, int item) {
+    WorkItem w;
+    if (!SPLITK || item < p.full_tiles) {
+        w.tile = item;
+        w.k0 = 0;
+        w.k1 = p.k_iters;
+        w.slot = -1;
+    } else {
+        const int idx = item - p.full_tiles;
+        const int t = idx / p.split, part = idx - t * p.split;
+        w.tile = p.full_tiles + t;
+        w.k0 = part * p.k_per_part;
+        w.k1 = min(w.k0 + p.k_per_part, p.k_iters);
+        w.slot = idx;
+    }
+    return w;
+}
 
 template <int BN, int GEOM>
 struct SmemLayout {
     static constexpr int kABytes = kBM * Geom<BN, GEOM>::kBKg;
     static constexpr int kBBytes = BN * Geom<BN, GEOM>::kBKg;
     static constexpr int kTiles = Geom<BN, GEOM>::kStagesG * (kABytes + kBBytes);
-    // after the tiles: full[kStages], empty[kStages], acc_full[2], acc_empty[2], drain
+    // after the tiles: full[kStages], empty[kStages], acc_full[2], acc_empty[2], drain,
+    // the epilogue's own rendezvous (split-K), then three words
     static constexpr int kBarOff = kTiles;
-    static constexpr int kTotal = kBarOff + (2 * kStages + 5) * 8 + 16;
+    static constexpr int kTotal = kBarOff + (2 * kStages + 6) * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;  // room to align the tiles to 1024 bytes
 };
 
-template <int BN, int GEOM>
+template <int BN, int GEOM, bool SPLITK = false>
 __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv_umma_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const UmmaConvParams p) {
@@ -105,11 +140,13 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
     uint64_t* acc_full = empty_bar + kStages;  // [2]
     uint64_t* acc_empty = acc_full + 2;        // [2]
     uint64_t* drain_bar = acc_empty + 2;
-    uint32_t* tmem_slot = (uint32_t*)(drain_bar + 1);
+    uint64_t* ep_bar = drain_bar + 1;
+    uint32_t* tmem_slot = (uint32_t*)(ep_bar + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    volatile int* last_flag = (volatile int*)(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int total_tiles = SPLITK ? p.total_items : p.m_tiles * p.n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -121,6 +158,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
             mbar_init(&acc_empty[b], 32 * kEpilogueWarps);  // every epilogue thread arrives
         }
         mbar_init(drain_bar, 1);
+        mbar_init(ep_bar, 32 * kEpilogueWarps);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -145,7 +183,9 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+                const WorkItem w = decode_item<SPLITK>(p, item);
+                const int tile = w.tile;
                 const int tile_n = tile % p.n_tiles, tile_m = tile / p.n_tiles;
                 const int m0 = tile_m * kBM, n0 = tile_n * BN;
                 const int img = m0 / (p.oh * p.ow);
@@ -153,7 +193,14 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                 const int oy = rem / p.ow, ox = rem - oy * p.ow;
                 const int base_w = ox * p.sw + p.base_w, base_h = oy * p.sh + p.base_h;
                 int cb = 0, fx = 0, fy = 0;
-                for (int it = 0; it < p.k_iters; ++it) {
+                if (SPLITK && w.k0 != 0) {
+                    // a later part of a split tile starts in the middle of the filter
+                    cb = w.k0 % p.cblocks;
+                    const int tap = w.k0 / p.cblocks;
+                    fy = tap / p.taps_w;
+                    fx = tap - fy * p.taps_w;
+                }
+                for (int it = w.k0; it < w.k1; ++it) {
                     if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) {
                         if (!*abort_flag) {
                             *abort_flag = 1;
@@ -206,7 +253,8 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
             int local = 0, s = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++local) {
+                const WorkItem w = decode_item<SPLITK>(p, item);
                 const int buf = local & 1;
                 const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
                 // the epilogue must have drained this accumulator buffer
@@ -220,7 +268,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                for (int it = 0; it < p.k_iters; ++it) {
+                for (int it = w.k0; it < w.k1; ++it) {
                     if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
                         if (!*abort_flag) {
                             *abort_flag = 1;
@@ -252,7 +300,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                         a_step = 2 * (kBM * 16) / 16;
                         b_step = 2 * (BN * 16) / 16;
                     }
-                    umma_s8(tmem_d, adesc, bdesc, idesc, it != 0 ? 1u : 0u);
+                    umma_s8(tmem_d, adesc, bdesc, idesc, it != w.k0 ? 1u : 0u);
 #pragma unroll
                     for (int k = 1; k < kBKc / kUmmaK; ++k)
                         umma_s8_c<true>(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc);
@@ -272,7 +320,10 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
         const int row = q * 32 + lane;
         int local = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        uint32_t ep_phase = 0;  // parity of the epilogue's own rendezvous (split-K)
+        for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++local) {
+            const WorkItem w = decode_item<SPLITK>(p, item);
+            const int tile = w.tile;
             const int buf = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             const int tile_n = tile % p.n_tiles, tile_m = tile / p.n_tiles;
@@ -291,6 +342,80 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
             // each warp takes a run of adjacent chunks: its thread's bytes are contiguous
             constexpr int kChunksPerWarp = (BN / 32) / (kEpilogueWarps / 4);
             static_assert(kChunksPerWarp >= 1, "every epilogue warp must own a chunk");
+            if (SPLITK && w.slot >= 0) {
+                // One K range of a split tile. Its raw accumulators go to this item's slab;
+                // a slab is laid out [chunk][16-byte group][row], so a warp's 16-byte stores
+                // (and the loads of the CTA that finishes the tile, whose threads own the same
+                // rows and chunks) are 512 contiguous bytes. The CTA that finds the tile's
+                // other parts already counted sums all slabs and requantises; nobody waits
+                // for another CTA.
+                constexpr int kSlabVecs = (BN / 32) * 8 * kBM;
+                int4* slab = p.slabs + (size_t)w.slot * kSlabVecs;
+#pragma unroll 1
+                for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + (uint32_t)(c * 32), v);
+                    if (c + 1 == (half + 1) * kChunksPerWarp) {
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        mbar_arrive(&acc_empty[buf]);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        __stcg(slab + (c * 8 + k) * kBM + row,
+                               make_int4((int)v[4 * k], (int)v[4 * k + 1], (int)v[4 * k + 2],
+                                         (int)v[4 * k + 3]));
+                }
+                __threadfence();  // the slab is visible device-wide before the part is counted
+                mbar_arrive(ep_bar);
+                ok = mbar_wait(ep_bar, ep_phase, abort_flag);
+                ep_phase ^= 1u;
+                if (ok && threadIdx.x == 64) {
+                    unsigned* counter = p.counters + (w.tile - p.full_tiles);
+                    const unsigned before = atomicAdd(counter, 1u);
+                    const bool last = before + 1u == (unsigned)p.split;
+                    if (last)
+                        *counter = 0;  // every part has been counted: ready for the next launch
+                    *last_flag = last ? 1 : 0;
+                }
+                if (ok) {
+                    mbar_arrive(ep_bar);
+                    ok = mbar_wait(ep_bar, ep_phase, abort_flag);
+                    ep_phase ^= 1u;
+                }
+                if (!ok && !*abort_flag) {
+                    *abort_flag = 1;
+                    atomicExch(p.status, ERR_EPILOGUE_WAIT);
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+                if (*last_flag) {
+                    __threadfence();
+                    const int4* first = p.slabs + (size_t)(w.slot - w.slot % p.split) * kSlabVecs;
+#pragma unroll 1
+                    for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; ++c) {
+                        uint32_t v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            v[j] = 0;
+                        for (int part = 0; part < p.split; ++part) {
+                            const int4* s4 = first + (size_t)part * kSlabVecs + (c * 8) * kBM + row;
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) {
+                                const int4 t = __ldcg(s4 + k * kBM);
+                                v[4 * k] += (uint32_t)t.x;
+                                v[4 * k + 1] += (uint32_t)t.y;
+                                v[4 * k + 2] += (uint32_t)t.z;
+                                v[4 * k + 3] += (uint32_t)t.w;
+                            }
+                        }
+                        const int ch0 = n0 + c * 32;
+                        if (m < p.m_total && ch0 < p.oc)
+                            epilogue_store<32>(v, p.ep, p.dst, (size_t)m * p.oc + ch0, ch0);
+                    }
+                }
+                continue;
+            }
 #pragma unroll 1
             for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; ++c) {
                 uint32_t v[32];
@@ -337,26 +462,110 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
 // ------------------------------------------------------------------------------------------
 // host side: tensor maps and launch
 // ------------------------------------------------------------------------------------------
-template <int BN, int GEOM>
+template <int BN, int GEOM, bool SPLITK = false>
 int launch_kernel(
         const CUtensorMap& ma, const CUtensorMap& mb, const UmmaConvParams& p, cudaStream_t st) {
     if (cudaFuncSetAttribute(
-                conv_umma_kernel<BN, GEOM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                conv_umma_kernel<BN, GEOM, SPLITK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                 SmemLayout<BN, GEOM>::kDynamic) != cudaSuccess)
         return check_launch("conv_umma smem attribute");
     // persistent CTAs: as many as the SM holds at once
     constexpr int kThreads = Shape<BN>::kThreads;
     const int per_sm = resident_ctas_per_sm(
-            conv_umma_kernel<BN, GEOM>, kThreads, SmemLayout<BN, GEOM>::kDynamic, 2 * BN);
-    const int total = p.m_tiles * p.n_tiles;
+            conv_umma_kernel<BN, GEOM, SPLITK>, kThreads, SmemLayout<BN, GEOM>::kDynamic, 2 * BN);
+    const int total = SPLITK ? p.total_items : p.m_tiles * p.n_tiles;
     int grid = sm_count() * per_sm;
     if (grid > total)
         grid = total;
     if (getenv("MB200_DEBUG"))
-        fprintf(stderr, "conv_umma<%d,%d>: per_sm %d grid %d tiles %d smem %d\n", BN, GEOM, per_sm, grid,
-                total, SmemLayout<BN, GEOM>::kDynamic);
-    conv_umma_kernel<BN, GEOM><<<grid, kThreads, SmemLayout<BN, GEOM>::kDynamic, st>>>(ma, mb, p);
+        fprintf(stderr, "conv_umma<%d,%d,%d>: per_sm %d grid %d items %d (whole tiles %d, split %d) smem %d\n",
+                BN, GEOM, (int)SPLITK, per_sm, grid, total, SPLITK ? p.full_tiles : total,
+                SPLITK ? p.split : 1, SmemLayout<BN, GEOM>::kDynamic);
+    conv_umma_kernel<BN, GEOM, SPLITK>
+            <<<grid, kThreads, SmemLayout<BN, GEOM>::kDynamic, st>>>(ma, mb, p);
     return check_launch("conv_umma");
+}
+
+// ------------------------------------------------------------------------------------------
+// split-K for the last, partly filled wave of 128 x 256 tiles
+// ------------------------------------------------------------------------------------------
+// 196 tiles on 148 SMs take two waves with the second a third full. The tiles of that last
+// wave can be cut along K into `split` parts, each a work item of its own, so that the wave
+// takes 1/split of a tile's MMA time when the parts fit the SMs. Parts leave their int32
+// accumulators in scratch slabs; the last part of a tile to finish sums them and runs the
+// usual epilogue (integer sums: the result does not depend on the order).
+//
+// OFF unless MB200_CONV_SPLITK=2..4 asks for it: bit-exact, but measured SLOWER on the
+// ResNet-18 layers at batch 256 (512->512 7x7: 30.5 -> 32.6 us; 256->256 14x14: 26.7 ->
+// 41.4 us). A part of 6-12 pipeline steps is 2-5 us of MMAs, while its epilogue writes a
+// 128 KB slab (four times the int8 tile) and the finisher reads `split` slabs back from L2
+// with eight 16-byte loads in flight per thread: about 64 KB in flight per SM, some 6 us for
+// 384 KB, all of it after the last MMA of the kernel with nothing left to overlap it.
+constexpr int kMaxSplitItems = 2 * 148;
+constexpr size_t kSlabBytes = (size_t)kBM * 256 * 4;
+constexpr size_t kCounterBytes = 4096;  // one word per split tile (fewer than 148)
+constexpr size_t kSplitScratchBytes = kCounterBytes + kMaxSplitItems * kSlabBytes;
+
+struct SplitPlan {
+    int full_tiles, split, k_per_part, total_items;
+};
+
+SplitPlan plan_split_k(int tiles, int k_iters, int ctas) {
+    SplitPlan sp{tiles, 1, k_iters, tiles};
+    const char* e = getenv("MB200_CONV_SPLITK");  // 2..4: that split wherever it fits
+    const int forced = e ? atoi(e) : 0;
+    if (forced < 2 || ctas <= 0)
+        return sp;
+    const int rem = tiles % ctas;
+    if (rem == 0)
+        return sp;
+    int best = 1;
+    for (int s = 2; s <= 4; ++s) {
+        const int per_part = (k_iters + s - 1) / s;
+        if (k_iters / s < 4 || (s - 1) * per_part >= k_iters ||  // no short or empty part
+            rem * s > kMaxSplitItems || rem > (int)(kCounterBytes / 4))
+            continue;
+        if (forced == s)
+            best = s;
+    }
+    if (best > 1) {
+        sp.full_tiles = tiles - rem;
+        sp.split = best;
+        sp.k_per_part = (k_iters + best - 1) / best;
+        sp.total_items = sp.full_tiles + rem * best;
+    }
+    return sp;
+}
+
+// Scratch for the slabs: one buffer per (device, stream), so that launches on different
+// streams cannot meet in it; allocated at first use, never while the stream is capturing
+// (the caller then runs unsplit). The counters at its start are zeroed once: every launch
+// leaves them at zero.
+void* split_scratch(cudaStream_t st) {
+    static std::mutex mu;
+    static std::map<std::pair<int, cudaStream_t>, void*> pool;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess)
+        return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = pool.find(std::make_pair(dev, st));
+    if (it != pool.end())
+        return it->second;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    void* ptr = nullptr;
+    if (cudaMalloc(&ptr, kSplitScratchBytes) != cudaSuccess ||
+        cudaMemset(ptr, 0, kCounterBytes) != cudaSuccess) {
+        cudaGetLastError();
+        if (ptr)
+            cudaFree(ptr);
+        ptr = nullptr;
+    }
+    pool[std::make_pair(dev, st)] = ptr;
+    return ptr;
 }
 
 }  // namespace
@@ -531,9 +740,26 @@ int launch_conv_umma_geom(
     p.status = device_status_word();
     if (!p.status)
         return ST_MALLOC;
+    p.full_tiles = p.total_items = p.m_tiles * p.n_tiles;
+    p.split = 1;
+    p.k_per_part = p.k_iters;
+    p.slabs = nullptr;
+    p.counters = nullptr;
     if (geom == GEOM_WIDE128) {
-        if (bn == 256)
+        if (bn == 256) {
+            const SplitPlan sp = plan_split_k(p.m_tiles * p.n_tiles, p.k_iters, sm_count());
+            void* scratch = sp.split > 1 ? split_scratch(st) : nullptr;
+            if (scratch) {
+                p.full_tiles = sp.full_tiles;
+                p.split = sp.split;
+                p.k_per_part = sp.k_per_part;
+                p.total_items = sp.total_items;
+                p.counters = (unsigned*)scratch;
+                p.slabs = (int4*)((uint8_t*)scratch + kCounterBytes);
+                return launch_kernel<256, GEOM_WIDE128, true>(map_a, map_b, p, st);
+            }
             return launch_kernel<256, GEOM_WIDE128>(map_a, map_b, p, st);
+        }
         return bn == 64 ? launch_kernel<64, GEOM_WIDE128>(map_a, map_b, p, st)
                         : launch_kernel<128, GEOM_WIDE128>(map_a, map_b, p, st);
     }

@@ -147,6 +147,69 @@ def test_conv_umma_256_wide_tiles_match_oracle(ops, oracle, case, monkeypatch):
     assert ops.device_status() == 0
 
 
+SPLITK_CASES = [
+    # name, n, ic, oc, h, w, k, stride, pad, act, split
+    ("s1_256_x2", 4, 256, 256, 14, 14, 3, 1, 1, "RELU", 2),
+    ("s1_256_x3", 4, 256, 256, 14, 14, 3, 1, 1, "IDENTITY", 3),
+    ("s1_256_x4", 4, 256, 256, 14, 14, 3, 1, 1, "RELU", 4),
+    ("s1_512_x3", 6, 512, 512, 7, 7, 3, 1, 1, "RELU", 3),          # two channel tiles
+    ("s2_128_256_x2", 2, 128, 256, 28, 28, 3, 2, 1, "IDENTITY", 2),  # 9 K steps: 5 + 4
+    ("ragged_oc320_x3", 4, 128, 320, 20, 20, 3, 1, 1, "RELU", 3),
+    ("pw_1024_x2", 3, 1024, 1024, 7, 7, 1, 1, 0, "H_SWISH", 2),     # tiled A map
+]
+
+
+@pytest.mark.parametrize("case", SPLITK_CASES, ids=[c[0] for c in SPLITK_CASES])
+def test_conv_umma_split_k_matches_oracle(ops, oracle, case, monkeypatch):
+    """128 x 256 tiles cut along K: every part leaves its accumulators in scratch and the last
+    one to finish sums and requantises. Forced on small shapes (all tiles split), run twice:
+    the second launch finds the counters as the first one left them."""
+    name, n, ic, oc, h, w, k, stride, pad, act, split = case
+    monkeypatch.setenv("MB200_CONV_BN", "256")
+    monkeypatch.setenv("MB200_CONV_SPLITK", str(split))
+    c = dict(name="splitk_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=stride, pad=pad,
+             groups=1, act=act, range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.37 * (ic * k * k / 576.0) ** 0.5 + 0.4))
+    s0, s1, s2 = c["scales"]
+    want = None
+    for _ in range(2):
+        out, (src, flt, bias) = run_conv_nchw(ops, c, algo="umma")
+        if want is None:
+            want = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, s1, s2, act)
+        bad = int((out != want).sum())
+        assert bad == 0, f"{bad}/{want.size} differ; first at {np.argwhere(out != want)[:4].tolist()}"
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("mode", [None, "QFUSE_ADD_RELU"])
+def test_conv_umma_split_k_last_wave_equals_unsplit(ops, mode, monkeypatch):
+    """A ResNet stage-4 shape at batch 256 (196 tiles on 148 SMs: 148 whole tiles, 48 tiles
+    in three parts each), with and without the fused residual step, against the same kernel
+    without the split (itself checked against the oracle on smaller shapes)."""
+    n, ic, oc, hw = 256, 512, 512, 7
+    rng = cases.rng_for("splitk_auto_%s" % mode)
+    src = dev(rng.integers(-128, 128, (n, hw, hw, ic), dtype=np.int8))
+    flt = rng.integers(-127, 128, (oc, ic, 3, 3), dtype=np.int8)
+    bias = dev(rng.integers(-1000, 1000, (oc,), dtype=np.int32))
+    z = dev(rng.integers(-128, 128, (n, hw, hw, oc), dtype=np.int8))
+    p = ops.conv_param(n, ic, hw, hw, oc, 3, 3, 1, 1, 1, "IDENTITY" if mode else "RELU",
+                       0.05, 0.01, 1.6)
+    packed = ops.pack_filter(p, dev(flt))
+
+    def run():
+        if mode:
+            return ops.conv_bias_qs8_nhwc_fused(p, src, packed, bias, z, mode, 0.7, 1.3,
+                                                algo="umma").cpu().numpy()
+        return ops.conv_bias_qs8_nhwc(p, src, packed, bias, algo="umma").cpu().numpy()
+
+    whole = run()
+    assert (np.abs(whole.astype(int)) < 127).mean() > 0.3
+    monkeypatch.setenv("MB200_CONV_SPLITK", "3")
+    for _ in range(2):
+        assert (run() == whole).all()
+    assert ops.device_status() == 0
+
+
 PAIR_CASES = [
     # name, n, ic, oc, h, w, k, stride, pad, act
     ("s1_256", 4, 256, 256, 14, 14, 3, 1, 1, "RELU"),            # 784 pixels: 3 full pairs + tail
