@@ -152,6 +152,63 @@ def cpu_reference_run(spec, steps, warmup, threads):
     return threads * steps / dt, dt / steps, kind
 
 
+def other_configs(local_rank):
+    """The figures BASELINE's metric names besides the headline: batch-1 latency (p50 / p95 of
+    50 CUDA-graph forwards after 10 warm-ups, input resident in HBM, one event pair per
+    forward; `e2e_p50_ms` = wall clock of LITE_forward + LITE_wait from a pinned host input,
+    logits back on the host), MobileNetV1 at batch 64, and ResNet-18 at batch 256 with one
+    filter scale per output channel (the reference has one per tensor, so that variant has
+    no reference arm). Short runs on rank 0 only; none of them is the `value`."""
+    import numpy as np
+    import torch
+
+    from megcc_b200 import lite, zoo
+    dev = torch.device("cuda", local_rank)
+
+    def forwards(spec, batch, host_input):
+        model = spec.to_graph().compile([batch])
+        rng = np.random.default_rng(7)
+        x = torch.from_numpy(rng.integers(-128, 128, (batch, 3, 224, 224), dtype=np.int8))
+        x = x.pin_memory() if host_input else x.to(dev)
+        net = (lite.Network(model, device_id=local_rank) if host_input else
+               lite.Network(model, device_id=local_rank, device_io=("fc:out",)))
+        net.set_input_ptr("data", x.data_ptr(), x.numel())
+        stream = torch.cuda.ExternalStream(net.stream())
+        for _ in range(10):
+            net.forward()
+        net.wait()
+        times = []
+        for _ in range(50):
+            if host_input:
+                t0 = time.perf_counter()
+                net.forward()
+                net.wait()
+                times.append((time.perf_counter() - t0) * 1e3)
+            else:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                net.forward()
+                e1.record(stream)
+                net.wait()
+                times.append(e0.elapsed_time(e1))
+        net.close()
+        times.sort()
+        return times[len(times) // 2], times[int(len(times) * 0.95)]
+
+    out = {}
+    for name, make in (("resnet18", zoo.resnet18), ("mobilenetv1", zoo.mobilenet_v1)):
+        p50, p95 = forwards(make(), 1, False)
+        e2e50, _ = forwards(make(), 1, True)
+        out[name + "_b1"] = dict(p50_ms=round(p50, 4), p95_ms=round(p95, 4),
+                                 e2e_p50_ms=round(e2e50, 4))
+    p50, _ = forwards(zoo.mobilenet_v1(), 64, False)
+    out["mobilenetv1_b64"] = dict(ms_per_forward=round(p50, 4), img_s=round(64 / (p50 * 1e-3)))
+    p50, _ = forwards(zoo.resnet18(per_channel=True), BATCH, False)
+    out["resnet18_b256_per_channel_scales"] = dict(ms_per_forward=round(p50, 4),
+                                                   img_s=round(BATCH / (p50 * 1e-3)))
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -309,6 +366,7 @@ def main():
     # ---- per-kernel pass for the roofline of the dominant kernel ----
     roofline = None
     cpu_baseline = None
+    extra = None
     if rank == 0:
         peaks = load_peaks()
         net.set_profile(True)
@@ -343,6 +401,10 @@ def main():
             peak_note=f"2 x bf16 sustained ({peaks['source']}); int8 dense peak is not in "
                       "MEASURED_PEAKS.json",
             per_kernel_ms={n: round(ms, 4) for n, s, ms, c in rows})
+        try:
+            extra = other_configs(local_rank)
+        except Exception as e:  # never lose the headline line to a side measurement
+            extra = dict(error=repr(e))
         if affinity_before is not None:
             os.sched_setaffinity(0, affinity_before)  # the CPU leg uses every host core
         ips_cpu, sec, kind = cpu_reference_run(spec, 2, 1, threads)
@@ -364,7 +426,7 @@ def main():
         clocks=clocks, gpu_launches=ops_per_step * args.steps,
         e2e=dict(value=images / (ms_e2e * 1e-3), unit=UNIT, ms_per_step=ms_e2e / args.steps,
                  h2d_bytes_per_step=in_bytes, d2h_bytes_per_step=out_bytes),
-        roofline=roofline, cpu_baseline=cpu_baseline)
+        roofline=roofline, cpu_baseline=cpu_baseline, other_configs=extra)
     print(json.dumps(line))
 
 

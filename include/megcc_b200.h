@@ -66,6 +66,16 @@ MB200_API const char* mb200_last_error(void);
  * (0 = healthy). Synchronises `stream`. */
 MB200_API int mb200_device_status(void* stream, int* status_host);
 
+/* Tells the library that [base, base + bytes) is device memory the caller owns and that may
+ * be READ anywhere inside (an arena). The tensor-core ConvBias kernels describe activations to
+ * the TMA unit as tensors of at least 128 KiB; a smaller activation (batch 1 of a late layer)
+ * takes them only when it lies in a registered range with enough bytes behind it, and the
+ * general CUDA-core kernel otherwise. What is loaded from behind the activation is never
+ * used. The runtime (LITE_*) registers its arenas itself (runtime/src/init.c:437-487 is where
+ * the reference lays out its arena). Unregister before freeing the memory. */
+MB200_API int mb200_register_readable_range(const void* base, size_t bytes);
+MB200_API int mb200_unregister_readable_range(const void* base);
+
 /* Parses a tinynn model (root table MegCC.Model, runtime/schema/model.fbs) the way the
  * runtime's loader does, without using a GPU, and writes a text summary into out.
  * Returns TinyNN_ERROR_MODEL_PARSE (7) for a truncated or malformed buffer. */

@@ -4,6 +4,9 @@
 #include <string.h>
 
 #include "../../include/megcc_b200.h"
+#include <map>
+#include <mutex>
+
 #include "internal.h"
 
 namespace mb200 {
@@ -103,7 +106,49 @@ static size_t align_up(size_t v, size_t a) {
 
 using namespace mb200;
 
+namespace mb200 {
+
+namespace {
+std::mutex g_ranges_mu;
+std::map<uintptr_t, size_t> g_ranges;  // base -> bytes
+}  // namespace
+
+bool readable_through(const void* p, size_t bytes) {
+    std::lock_guard<std::mutex> lock(g_ranges_mu);
+    auto it = g_ranges.upper_bound((uintptr_t)p);
+    if (it == g_ranges.begin())
+        return false;
+    --it;
+    return (uintptr_t)p + bytes <= it->first + it->second;
+}
+
+int descriptor_images(const ConvArgs& a, const int8_t* src) {
+    constexpr size_t kMinMapBytes = 131072;
+    const size_t image = (size_t)a.ih * a.iw * a.ic;
+    if ((size_t)a.n * image >= kMinMapBytes)
+        return a.n;
+    const size_t images = (kMinMapBytes + image - 1) / image;
+    return readable_through(src, images * image) ? (int)images : 0;
+}
+
+}  // namespace mb200
+
 extern "C" {
+
+int mb200_register_readable_range(const void* base, size_t bytes) {
+    if (!base || !bytes)
+        return mb200::set_error(mb200::ST_NULL_PTR, "register_readable_range: empty range");
+    std::lock_guard<std::mutex> lock(mb200::g_ranges_mu);
+    mb200::g_ranges[(uintptr_t)base] = bytes;
+    return 0;
+}
+
+int mb200_unregister_readable_range(const void* base) {
+    std::lock_guard<std::mutex> lock(mb200::g_ranges_mu);
+    mb200::g_ranges.erase((uintptr_t)base);
+    return 0;
+}
+
 
 const char* mb200_version(void) {
     return "megcc_b200 0.1 (sm_100a)";

@@ -527,7 +527,7 @@ bool conv_patch_supported(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst) {
     if (!plan_patch(a).ok)
         return false;
-    if ((size_t)a.n * a.ih * a.iw * a.ic < 131072)
+    if (descriptor_images(a, src) == 0)  // maps are built over at least 128 KiB
         return false;
     if ((size_t)a.n * a.oh * a.ow >= (1ull << 31))
         return false;
@@ -551,10 +551,14 @@ int launch_conv_patch(
         return set_error(ST_INVALID_LAYOUT, "bias and channel scales must be 16-byte aligned");
 
     const int pph = kTH + a.kh - 1, ppw = kTW + a.kw - 1;
+    // (a small activation is described with the images of readable memory behind it)
+    const int images = descriptor_images(a, src);
+    if (images == 0)
+        return set_error(ST_INVALID_LAYOUT, "activation below 128 KiB outside a registered range");
     CUtensorMap map_a, map_b;
     if (pl.rows64) {
         cuuint64_t dims[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw, (cuuint64_t)a.ih,
-                              (cuuint64_t)a.n};
+                              (cuuint64_t)images};
         cuuint64_t strides[3] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw * a.ic,
                                  (cuuint64_t)a.ih * a.iw * a.ic};
         cuuint32_t box[4] = {64, (cuuint32_t)kRowCols, (cuuint32_t)pph, 1};
@@ -579,7 +583,7 @@ int launch_conv_patch(
     } else {
         // NHWC seen as {16 channel bytes, W, H, N, C/16}: a box over all chunks arrives as
         // [chunk][row][column][16 bytes]
-        cuuint64_t dims[5] = {16, (cuuint64_t)a.iw, (cuuint64_t)a.ih, (cuuint64_t)a.n,
+        cuuint64_t dims[5] = {16, (cuuint64_t)a.iw, (cuuint64_t)a.ih, (cuuint64_t)images,
                               (cuuint64_t)(a.ic / 16)};
         cuuint64_t strides[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw * a.ic,
                                  (cuuint64_t)a.ih * a.iw * a.ic, 16};

@@ -588,9 +588,9 @@ bool conv_umma_supported(
     // im2col bounding-box corners and tap offsets are 8-bit fields for a 4-D map
     if (a.ph > 64 || a.pw > 64 || a.kh > 64 || a.kw > 64 || a.sh > 8 || a.sw > 8)
         return false;
-    // the driver mis-encodes im2col maps of very small tensors; keep those on the
-    // general kernel (a pointwise convolution uses a tiled map and has no such limit)
-    if ((size_t)a.n * a.ih * a.iw * a.ic < 131072 && !conv_is_plain_matrix(a))
+    // im2col maps are built over at least 128 KiB (descriptor_images); a pointwise
+    // convolution uses a tiled map over the plain matrix and has no such limit
+    if (!conv_is_plain_matrix(a) && descriptor_images(a, src) == 0)
         return false;
     if (((uintptr_t)src | (uintptr_t)flt | (uintptr_t)dst) & 15)
         return false;
@@ -660,8 +660,12 @@ int launch_conv_umma_geom(
         if (r != CUDA_SUCCESS)
             return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(activation) failed: %d", (int)r);
     } else {
+        // (a small activation is described with the images of readable memory behind it)
+        const int images = descriptor_images(a, src);
+        if (images == 0)
+            return set_error(ST_INVALID_LAYOUT, "activation below 128 KiB outside a registered range");
         cuuint64_t dims[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw, (cuuint64_t)a.ih,
-                              (cuuint64_t)a.n};
+                              (cuuint64_t)images};
         cuuint64_t strides[3] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw * a.ic,
                                  (cuuint64_t)a.ih * a.iw * a.ic};
         // bounding box of the first-tap positions: from -pad to the last output's position

@@ -69,6 +69,15 @@ int requant_fast_constants(
 bool residual_fast_constants(
         float s_conv, float s_z, float out_scale, int mode, float* a_out, float* b_out);
 
+// Images the activation's tensor map describes. TMA maps are only built over at least
+// 128 KiB (smaller tensors need a descriptor fix-up on current drivers that this library does
+// not apply). A smaller activation is described with more images than it has, as many as
+// reach 128 KiB, when the bytes behind it are known to be readable (a registered range,
+// mb200_register_readable_range): the kernels never use what they load from there. 0 = the
+// tensor is too small and nothing is known about the memory behind it.
+int descriptor_images(const ConvArgs& a, const int8_t* src);
+bool readable_through(const void* p, size_t bytes);
+
 // tensor-core implicit GEMM; conv_umma_supported() says whether the shape qualifies
 bool conv_umma_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst);
 // the same implicit GEMM on a pair of SMs (cta_group::2), 256 x 256 tiles: wide layers

@@ -94,12 +94,15 @@ struct Instr {
     MemForwardPlan mf;
 };
 
+constexpr size_t kArenaSlack = 131072 + 4096;
+
 struct Arena {
     void* ptr = nullptr;
     size_t bytes = 0;
     int device = 0;
     ~Arena() {
         if (ptr) {
+            mb200_unregister_readable_range(ptr);
             cudaSetDevice(device);
             cudaFree(ptr);
         }
@@ -795,10 +798,17 @@ int init_model_memory(Network* net) {
     if (a.bytes < net->arena_need)
         a.bytes = net->arena_need;
     if (!a.ptr) {
-        // one allocation for every tensor and workspace of the model
+        // one allocation for every tensor and workspace of the model, with 128 KiB behind
+        // the last tensor: the tensor-core ConvBias describes a small activation (batch 1 of a
+        // late layer) to the TMA unit as 128 KiB starting at it, and the whole arena is
+        // declared readable for that
         a.device = net->device_id;
-        if ((e = cudaMalloc(&a.ptr, a.bytes ? a.bytes : 256)) != cudaSuccess)
+        const size_t total = (a.bytes ? a.bytes : 256) + kArenaSlack;
+        if ((e = cudaMalloc(&a.ptr, total)) != cudaSuccess)
             return cuda_fail(e, "cudaMalloc(arena)");
+        if ((e = cudaMemset((uint8_t*)a.ptr + total - kArenaSlack, 0, kArenaSlack)) != cudaSuccess)
+            return cuda_fail(e, "cudaMemset(arena slack)");
+        mb200_register_readable_range(a.ptr, total);
     }
     for (auto& t : m.tensors)
         t.ptr = (uint8_t*)a.ptr + t.offset;

@@ -147,6 +147,60 @@ def test_conv_umma_256_wide_tiles_match_oracle(ops, oracle, case, monkeypatch):
     assert ops.device_status() == 0
 
 
+SMALL_CASES = [
+    # name, n, ic, oc, h, w, k, stride, pad, act, algo: activations below 128 KiB
+    ("b1_128_28", 1, 128, 128, 28, 28, 3, 1, 1, "RELU", "umma"),
+    ("b1_256_14", 1, 256, 256, 14, 14, 3, 1, 1, "RELU", "umma"),
+    ("b1_512_7", 1, 512, 512, 7, 7, 3, 1, 1, "IDENTITY", "umma"),
+    ("b1_256_512_s2", 1, 256, 512, 14, 14, 3, 2, 1, "RELU", "umma"),
+    ("b1_proj_s2", 1, 128, 256, 28, 28, 1, 2, 0, "IDENTITY", "umma"),
+    ("b3_512_7", 3, 512, 512, 7, 7, 3, 1, 1, "RELU", "umma"),
+    ("b1_128_28_patch", 1, 128, 128, 28, 28, 3, 1, 1, "RELU", "patch"),
+    ("b1_64_20_patch", 1, 64, 64, 20, 20, 3, 1, 1, "RELU", "patch"),
+]
+
+
+@pytest.mark.parametrize("case", SMALL_CASES, ids=[c[0] for c in SMALL_CASES])
+def test_conv_small_activation_in_registered_range(ops, oracle, case):
+    """Batch 1 of the late ResNet layers: the activation is smaller than the 128 KiB a TMA map
+    is built over. Inside a registered readable range (what the runtime does with its arena)
+    the tensor-core kernels take it; the same call outside such a range is refused by the
+    forced algorithm and served by the general kernel under "auto"."""
+    import ctypes
+    from megcc_b200._lib import check, lib
+    name, n, ic, oc, h, w, k, stride, pad, act, algo = case
+    c = dict(name="small_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=stride, pad=pad,
+             groups=1, act=act, range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.37 * (ic * k * k / 576.0) ** 0.5 + 0.4))
+    s0, s1, s2 = c["scales"]
+    src, flt, bias = cases.conv_inputs(c)
+    want = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, s1, s2, act)
+    p = ops.conv_param(n, ic, h, w, oc, k, k, stride, pad, 1, act, s0, s1, s2)
+    packed = ops.pack_filter(p, dev(flt))
+    nhwc = np.ascontiguousarray(src.transpose(0, 2, 3, 1))
+    assert nhwc.size < 131072
+    # an "arena": the activation sits at an odd 256-byte offset, 192 KiB of bytes follow it
+    arena = torch.randint(-128, 128, (nhwc.size + 256 * 3 + 192 * 1024,), dtype=torch.int8,
+                          device="cuda")
+    view = arena[768:768 + nhwc.size].view(n, h, w, ic)
+    view.copy_(torch.from_numpy(nhwc))
+    check(lib().mb200_register_readable_range(ctypes.c_void_p(arena.data_ptr()), arena.numel()))
+    try:
+        out = ops.conv_bias_qs8_nhwc(p, view, packed, dev(bias), algo=algo)
+        torch.cuda.synchronize()
+    finally:
+        check(lib().mb200_unregister_readable_range(ctypes.c_void_p(arena.data_ptr())))
+    got = out.cpu().numpy().transpose(0, 3, 1, 2)
+    bad = int((got != want).sum())
+    assert bad == 0, f"{bad}/{want.size} differ; first at {np.argwhere(got != want)[:4].tolist()}"
+    assert ops.device_status() == 0
+    # not registered any more: the tensor-core kernels decline, "auto" still answers
+    with pytest.raises(Exception):
+        ops.conv_bias_qs8_nhwc(p, view, packed, dev(bias), algo=algo)
+    out = ops.conv_bias_qs8_nhwc(p, view, packed, dev(bias), algo="auto")
+    assert (out.cpu().numpy().transpose(0, 3, 1, 2) == want).all()
+
+
 SPLITK_CASES = [
     # name, n, ic, oc, h, w, k, stride, pad, act, split
     ("s1_256_x2", 4, 256, 256, 14, 14, 3, 1, 1, "RELU", 2),
