@@ -27,6 +27,10 @@ struct DwParams {
     ConvArgs a;
     int c16;    // channels / 16
     float inv_dst, z_div;
+    // the verified one-FMA requantisation (requant_verify.cu), per-tensor scales only:
+    // fast_ops == 1 -> trunc(fma((float)acc, fast_mul, +-fast_add)) saturated
+    int fast_ops;
+    float fast_mul, fast_add;
 };
 
 // four words, byte i = channel i of taps a..d  ->  four words, byte j = tap j of one channel
@@ -123,8 +127,18 @@ __global__ void __launch_bounds__(256) conv_dw_kernel(
             int r[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                r[i] = requant_conv_fast(acc[q * 4 + i] + bb[i], a.s_src, ss[i], a.s_dst, p.inv_dst,
-                                         a.act);
+                if (p.fast_ops == 1) {
+                    const float f = __int2float_rn(acc[q * 4 + i] + bb[i]);
+                    const float y = __fmaf_rn(
+                            f, p.fast_mul,
+                            a.act == ACT_RELU ? p.fast_add : copysignf(p.fast_add, f));
+                    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(r[i]) : "f"(y));
+                    if (a.act == ACT_RELU)
+                        r[i] = max(r[i], 0);
+                } else {
+                    r[i] = requant_conv_fast(acc[q * 4 + i] + bb[i], a.s_src, ss[i], a.s_dst,
+                                             p.inv_dst, a.act);
+                }
                 if (a.z_mode != 0 && a.z) {
                     // fused ElemwiseMultiType step (ElemwiseMultiType.cpp:38-46,158)
                     const int zi = (int)(int8_t)(zw[q] >> (8 * i));
@@ -170,6 +184,15 @@ int launch_conv_dw(
     p.c16 = a.ic / 16;
     p.inv_dst = 1.0f / a.s_dst;         // RN(1/d), as the division by a constant needs
     p.z_div = 1.0f / a.z_out_scale;     // the reference's scale_div = 1.f / scale_dst
+    p.fast_ops = 0;
+    p.fast_mul = p.fast_add = 0.f;
+    if (!flt_scales) {
+        // (the search itself refuses scales whose results could leave the int range)
+        p.fast_ops = requant_fast_constants(a.s_src, a.s_flt, a.s_dst, a.act, &p.fast_mul,
+                                            &p.fast_add);
+        if (p.fast_ops != 1)
+            p.fast_ops = 0;
+    }
     const size_t work = (size_t)a.m * p.c16;
     size_t grid = (work + 255) / 256;
     const size_t cap = (size_t)148 * 8;
