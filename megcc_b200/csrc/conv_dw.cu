@@ -15,6 +15,8 @@
 // Arithmetic: the reference's order (compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:305-344,
 // Activation.cpp:105-113), per-tensor or per-channel filter scales, optional fused residual
 // step as in the other ConvBias kernels.
+#include <stdlib.h>
+
 #include "internal.h"
 
 namespace mb200 {
@@ -155,6 +157,128 @@ __global__ void __launch_bounds__(256) conv_dw_kernel(
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// OUT (2 or 4) horizontally adjacent outputs per thread (3x3, stride 1 or 2, no fused residual step)
+// ------------------------------------------------------------------------------------------
+// The kernel above spends 41 instructions per output and is bound by instruction issue.
+// Here a thread walks the (OUT - 1) S + 3 input columns its outputs touch. A column is loaded
+// once (three vectors: the three filter rows), transposed once into one word per channel
+// holding (top, middle, bottom, 0), and every output that uses the column adds one dp4a per
+// channel with the word of its filter column (w(0,dx), w(1,dx), w(2,dx), 0). Against one
+// output per thread: half the vector loads, two thirds of the permutes at stride 1, a quarter
+// of the index arithmetic. Filter columns live in shared memory as [dx][channel quad of the
+// vector][16-channel vector][4 channels] words.
+__device__ __forceinline__ uint32_t quad_word(const uint4& v, int q) {
+    return q == 0 ? v.x : q == 1 ? v.y : q == 2 ? v.z : v.w;
+}
+
+template <int S, int OUT>
+__global__ void __launch_bounds__(128, OUT == 4 ? 4 : 6) conv_dw3x3_row_kernel(
+        const DwParams p, const uint4* __restrict__ src, const int8_t* __restrict__ flt,
+        const int32_t* __restrict__ bias, const float* __restrict__ flt_scales,
+        uint4* __restrict__ dst) {
+    extern __shared__ uint4 w_smem[];  // [3 dx][4 quads][c16] vectors of 4 channel words
+    const ConvArgs& a = p.a;
+    constexpr int kOut = OUT, kCols = (kOut - 1) * S + 3;
+    for (int c = threadIdx.x; c < a.ic; c += blockDim.x) {
+        const int cvv = c >> 4, q = (c >> 2) & 3, i = c & 3;
+#pragma unroll
+        for (int dx = 0; dx < 3; ++dx) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int fy = 0; fy < 3; ++fy)
+                w |= (uint32_t)(uint8_t)flt[(size_t)c * 9 + fy * 3 + dx] << (8 * fy);
+            reinterpret_cast<uint32_t*>(w_smem)[((dx * 4 + q) * p.c16 + cvv) * 4 + i] = w;
+        }
+    }
+    __syncthreads();
+
+    const unsigned groups = (unsigned)(a.ow + kOut - 1) / kOut;
+    const unsigned total = (unsigned)a.n * a.oh * groups * p.c16;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += gridDim.x * blockDim.x) {
+        const unsigned cv = idx % p.c16;
+        unsigned t = idx / p.c16;
+        const int ox0 = (int)(t % groups) * kOut;
+        t /= groups;
+        const int oy = (int)(t % a.oh);
+        const int n = (int)(t / a.oh);
+        const int iy0 = oy * S - a.ph, ix0 = ox0 * S - a.pw;
+        int acc[kOut][16];
+#pragma unroll
+        for (int o = 0; o < kOut; ++o)
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                acc[o][i] = 0;
+        const uint4* base = src + (size_t)((unsigned)n * a.ih) * a.iw * p.c16 + cv;
+#pragma unroll
+        for (int j = 0; j < kCols; ++j) {
+            const int ix = ix0 + j;
+            uint4 r[3];
+#pragma unroll
+            for (int fy = 0; fy < 3; ++fy) {
+                const int iy = iy0 + fy;
+                r[fy] = make_uint4(0, 0, 0, 0);
+                if ((unsigned)iy < (unsigned)a.ih && (unsigned)ix < (unsigned)a.iw)
+                    r[fy] = __ldg(base + ((size_t)iy * a.iw + ix) * p.c16);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t ch[4];  // channel 4q + i: bytes (top, middle, bottom, 0)
+                transpose4x4(quad_word(r[0], q), quad_word(r[1], q), quad_word(r[2], q), 0u, ch);
+#pragma unroll
+                for (int o = 0; o < kOut; ++o) {
+                    const int dx = j - o * S;  // this column's place in output o's window
+                    if (dx < 0 || dx > 2)
+                        continue;
+                    const uint4 w = w_smem[(dx * 4 + q) * p.c16 + cv];
+                    acc[o][q * 4 + 0] = __dp4a((int)ch[0], (int)w.x, acc[o][q * 4 + 0]);
+                    acc[o][q * 4 + 1] = __dp4a((int)ch[1], (int)w.y, acc[o][q * 4 + 1]);
+                    acc[o][q * 4 + 2] = __dp4a((int)ch[2], (int)w.z, acc[o][q * 4 + 2]);
+                    acc[o][q * 4 + 3] = __dp4a((int)ch[3], (int)w.w, acc[o][q * 4 + 3]);
+                }
+            }
+        }
+        const int c0 = (int)cv * 16;
+        uint4* out = dst + ((size_t)((unsigned)n * a.oh + oy) * a.ow + ox0) * p.c16 + cv;
+#pragma unroll
+        for (int o = 0; o < kOut; ++o) {
+            if (ox0 + o >= a.ow)
+                break;
+            uint32_t packed[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                int4 b = make_int4(0, 0, 0, 0);
+                if (bias)
+                    b = __ldg(reinterpret_cast<const int4*>(bias + c0) + q);
+                float4 s = make_float4(a.s_flt, a.s_flt, a.s_flt, a.s_flt);
+                if (flt_scales)
+                    s = __ldg(reinterpret_cast<const float4*>(flt_scales + c0) + q);
+                const int bb[4] = {b.x, b.y, b.z, b.w};
+                const float ss[4] = {s.x, s.y, s.z, s.w};
+                int r4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int x = acc[o][q * 4 + i] + bb[i];
+                    if (p.fast_ops == 1) {
+                        const float f = __int2float_rn(x);
+                        const float y = __fmaf_rn(
+                                f, p.fast_mul,
+                                a.act == ACT_RELU ? p.fast_add : copysignf(p.fast_add, f));
+                        asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(r4[i]) : "f"(y));
+                        if (a.act == ACT_RELU)
+                            r4[i] = max(r4[i], 0);
+                    } else {
+                        r4[i] = requant_conv_fast(x, a.s_src, ss[i], a.s_dst, p.inv_dst, a.act);
+                    }
+                }
+                packed[q] = pack4(r4[0], r4[1], r4[2], r4[3]);
+            }
+            out[(size_t)o * p.c16] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+    }
+}
+
 }  // namespace
 
 bool conv_dw_supported(
@@ -201,6 +325,34 @@ int launch_conv_dw(
     if (grid < 1)
         grid = 1;
     const int smem = a.ic * kTapWords * 4;
+    // Several outputs per thread. Measured on the MobileNetV1 layers at batch 64: two outputs
+    // per thread are 10-20 % faster than one at stride 1 (40 against 49 us for 32 channels
+    // at 112x112) and four are no better than two (130 registers, 18 % of the warp slots,
+    // latency-bound); at stride 2 adjacent outputs share one input column only and the
+    // one-output kernel stays ahead. MB200_DW_OUT=2|4 forces a form at either stride,
+    // MB200_DW_ONE_OUTPUT=1 the one-output kernel (tests and experiments).
+    const char* e = getenv("MB200_DW_OUT");
+    const int forced = e ? atoi(e) : 0;
+    if (a.sh == a.sw && (a.sh == 1 || (a.sh == 2 && forced != 0)) && !(a.z_mode != 0 && a.z) &&
+        !getenv("MB200_DW_ONE_OUTPUT")) {
+        const int outs = forced == 4 ? 4 : 2;
+        const size_t items = (size_t)a.n * a.oh * ((a.ow + outs - 1) / outs) * p.c16;
+        size_t blocks = (items + 127) / 128;
+        const size_t most = (size_t)148 * 16;
+        if (blocks > most)
+            blocks = most;
+        if (blocks < 1)
+            blocks = 1;
+        auto kernel = outs == 4 ? (a.sh == 1 ? conv_dw3x3_row_kernel<1, 4> : conv_dw3x3_row_kernel<2, 4>)
+                                : (a.sh == 1 ? conv_dw3x3_row_kernel<1, 2> : conv_dw3x3_row_kernel<2, 2>);
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+                    cudaSuccess)
+            return check_launch("conv_dw smem attribute");
+        kernel<<<(int)blocks, 128, smem, st>>>(p, (const uint4*)src, flt, bias, flt_scales,
+                                               (uint4*)dst);
+        return check_launch("conv_dw_row");
+    }
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(conv_dw_kernel<3, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smem) != cudaSuccess)

@@ -302,6 +302,31 @@ DW_CASES = [
 ]
 
 
+@pytest.mark.parametrize("form", ["one", "2", "4"])
+@pytest.mark.parametrize("case", [DW_CASES[1], DW_CASES[4], DW_CASES[5]],
+                         ids=["c64_s2", "odd_hw_nopad", "odd_hw_s2_pad2"])
+def test_depthwise_kernel_forms(ops, oracle, case, form, monkeypatch):
+    """Every form of the depthwise kernel at both strides, chosen by its tuning variable: one
+    output per thread (it also serves the fused residual step), two and four outputs."""
+    if form == "one":
+        monkeypatch.setenv("MB200_DW_ONE_OUTPUT", "1")
+    else:
+        monkeypatch.setenv("MB200_DW_OUT", form)
+    name, n, ch, h, w, stride, pad, act, per_channel = case
+    c = dict(name="dw_" + name, n=n, ic=ch, oc=ch, h=h, w=w, k=3, stride=stride, pad=pad,
+             groups=ch, act=act, range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.06))
+    src, flt, bias = cases.conv_inputs(c)
+    s0, s1, s2 = c["scales"]
+    scales = None
+    if per_channel:
+        scales = cases.rng_for("dw_scales_" + name).uniform(0.005, 0.02, ch).astype(np.float32)
+    out, _ = run_conv_nchw(ops, c, algo="auto", flt_scales=scales)
+    want = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, scales if per_channel else s1,
+                                s2, act, groups=ch)
+    assert (out == want).all()
+
+
 @pytest.mark.parametrize("case", DW_CASES, ids=[c[0] for c in DW_CASES])
 def test_depthwise_3x3_matches_oracle(ops, oracle, case):
     """The vectorised depthwise kernel (auto) against the oracle, and against the general
