@@ -1,20 +1,21 @@
 // qint8 depthwise ConvBias (groups == channels, one filter per channel), NHWC, 3x3 filter,
-// any stride and padding: a bandwidth-bound operator, so no tensor cores.
+// any stride and padding: no reduction over channels, so no tensor cores.
 //
-// One thread = one output pixel x 16 channels. Its taps are 16-byte vector loads (the 16
-// channels of one input pixel); a tap outside the image contributes zeros. int8 products
-// have no reduction over channels, so dp4a is used the other way round: the bytes of four
-// taps are transposed (8 PRMTs per 4 taps x 4 channels) into one word per channel holding
-// that channel's four taps, and one dp4a per channel multiplies them with the channel's four
-// weights: 0.75 instructions per multiply-add instead of 3 for extract-extract-multiply.
-// The filter, packed [C][KH*KW] like every group filter, is re-laid once per CTA into shared
-// memory as words of four taps each (zero beyond the ninth tap), ordered [tap group][channel
-// quad within 16][16-channel group][4 channels] so that a warp's 16-byte reads are
-// consecutive.
+// Two kernels. conv_dw_kernel: one thread = one output pixel x 16 channels. Its taps are
+// 16-byte vector loads (the 16 channels of one input pixel); a tap outside the image
+// contributes zeros. dp4a is used the other way round: the bytes of four taps are transposed
+// (8 PRMTs per 4 taps x 4 channels) into one word per channel holding that channel's four
+// taps, and one dp4a per channel multiplies them with the channel's four weights: 0.75
+// instructions per multiply-add instead of 3 for extract-extract-multiply. The filter, packed
+// [C][KH*KW] like every group filter, is re-laid once per CTA into shared memory as words of
+// four taps each (zero beyond the ninth tap), ordered [tap group][channel quad within 16]
+// [16-channel group][4 channels] so that a warp's 16-byte reads are consecutive. It serves
+// stride 2 and the fused residual step. conv_dw3x3_row_kernel (further down): two or four
+// adjacent outputs per thread, the default at stride 1.
 //
 // Arithmetic: the reference's order (compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:305-344,
-// Activation.cpp:105-113), per-tensor or per-channel filter scales, optional fused residual
-// step as in the other ConvBias kernels.
+// Activation.cpp:105-113) or its verified one-FMA form for per-tensor scales, per-tensor or
+// per-channel filter scales, optional fused residual step as in the other ConvBias kernels.
 #include <stdlib.h>
 
 #include "internal.h"
