@@ -185,7 +185,7 @@ __device__ __forceinline__ uint4 vmax16(uint4 a, uint4 b) {
                       __vmaxs4(a.w, b.w));
 }
 
-__global__ void __launch_bounds__(256) pooling_max_3x3s2_vec16_kernel(
+__global__ void __launch_bounds__(256, 4) pooling_max_3x3s2_vec16_kernel(
         const uint4* __restrict__ src, uint4* __restrict__ dst, int n, int c16, int ih, int iw,
         int oh, int ow, int ph, int pw) {
     const int owp = (ow + 1) / 2;  // output pairs per row
