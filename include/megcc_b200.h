@@ -11,6 +11,23 @@
  * channels are one contiguous TMA row; the model-visible layout stays the reference's
  * NCHW (compiler/lib/KernelGen/BareMetal/FormatHelper.cpp:18-22) and the *_nchw entry
  * points convert on the way in and out.
+ *
+ * Alignment contract. int8 tensors (activations, filters, z) may start at ANY byte: a
+ * tensor that is not 16-byte aligned (a slice of a larger buffer) is computed by the general
+ * CUDA-core kernels with byte loads, never by a vector or TMA path, and the results are the
+ * same. int32 and float operands (bias, channel scales, int32 accumulators / products,
+ * TypeCvt sources) must be 4-byte aligned as their type demands; a misaligned one is refused
+ * with TinyNN_ERROR_INVALID_LAYOUT (12). Entry points that name a stricter rule (workspaces,
+ * the fused operand z: 16 bytes) say so at their declaration. The tensor-core kernels
+ * additionally want bias and channel scales 16-byte aligned and refuse them otherwise when
+ * they were asked for by name (MB200_ALGO_UMMA / _PATCH); MB200_ALGO_AUTO falls back.
+ *
+ * Scale range. Results are bit-identical to the reference's x86 kernels for every finite
+ * positive scale triple. The vector and tensor-core kernels divide by dst_scale with a
+ * three-instruction sequence that is exact for 2^-100 <= src_scale * flt_scale <= 2^69 and
+ * 2^-60 <= dst_scale <= 2^60; outside that range MB200_ALGO_AUTO runs the general kernel
+ * with the true division. One scale per output channel (flt_scales) must lie inside the
+ * range by contract: the array is device memory and is not inspected by the host.
  */
 #ifndef MEGCC_B200_H_
 #define MEGCC_B200_H_

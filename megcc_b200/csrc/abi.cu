@@ -47,11 +47,11 @@ int* device_status_word() {
     return words[dev];
 }
 
-static int out_extent(int in, int k, int s, int p, int d) {
+int out_extent(int in, int k, int s, int p, int d) {
     return (in + 2 * p - d * (k - 1) - 1) / s + 1;
 }
 
-static int make_args(const mb200_conv_param* p, int src_is_nchw, ConvArgs* a) {
+int make_args(const mb200_conv_param* p, int src_is_nchw, ConvArgs* a) {
     if (!p)
         return set_error(ST_NULL_PTR, "conv param is NULL");
     if (p->n <= 0 || p->ic <= 0 || p->oc <= 0 || p->ih <= 0 || p->iw <= 0 || p->kh <= 0 ||
@@ -95,10 +95,11 @@ static int make_args(const mb200_conv_param* p, int src_is_nchw, ConvArgs* a) {
     a->z_scale = 1.f;
     a->z_out_scale = 1.f;
     a->acc_out = nullptr;
+    a->true_division = division_range_ok(p->src_scale, p->flt_scale, p->dst_scale) ? 0 : 1;
     return ST_SUCCESS;
 }
 
-static size_t align_up(size_t v, size_t a) {
+size_t align_up(size_t v, size_t a) {
     return (v + a - 1) / a * a;
 }
 
@@ -225,8 +226,14 @@ int mb200_conv_bias_qs8_nhwc_fused(
     }
     if (!src || !flt_packed || !dst)
         return set_error(ST_NULL_PTR, "conv tensor pointer is NULL");
+    if (((uintptr_t)bias | (uintptr_t)flt_scales) & 3)
+        return set_error(ST_INVALID_LAYOUT, "bias and channel scales must be 4-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
-    const bool patch_ok = conv_patch_supported(a, src, flt_packed, dst);
+    // the vector kernels load bias and channel scales 16 bytes at a time
+    // ... and divide by a constant in three instructions, which is exact inside a scale range
+    const bool side_ok =
+            ((((uintptr_t)bias | (uintptr_t)flt_scales) & 15) == 0) && !a.true_division;
+    const bool patch_ok = side_ok && conv_patch_supported(a, src, flt_packed, dst);
     if (algo == MB200_ALGO_PATCH && !patch_ok)
         return set_error(ST_NO_IMPLEMENT,
                          "halo-patch ConvBias needs dense, stride 1, NHWC, ic in {16, 32k <= 128}, "
@@ -235,7 +242,7 @@ int mb200_conv_bias_qs8_nhwc_fused(
     if (algo == MB200_ALGO_PATCH ||
         (algo == MB200_ALGO_AUTO && patch_ok && conv_patch_efficiency(a) >= 0.75f))
         return launch_conv_patch(a, src, flt_packed, bias, flt_scales, dst, st);
-    const bool umma_ok = conv_umma_supported(a, src, flt_packed, dst);
+    const bool umma_ok = side_ok && conv_umma_supported(a, src, flt_packed, dst);
     if (algo == MB200_ALGO_UMMA && !umma_ok)
         return set_error(ST_NO_IMPLEMENT,
                          "tensor-core ConvBias needs dense, NHWC, ic %% 64 == 0, oc %% 8 == 0, "
@@ -245,7 +252,7 @@ int mb200_conv_bias_qs8_nhwc_fused(
     if (algo != MB200_ALGO_AUTO && algo != MB200_ALGO_DIRECT)
         return set_error(ST_OUT_OF_RANGE, "unknown algo %d", algo);
     // depthwise 3x3: bandwidth-bound, vector loads and dp4a over taps
-    if (algo == MB200_ALGO_AUTO && conv_dw_supported(a, src, flt_packed, dst))
+    if (algo == MB200_ALGO_AUTO && side_ok && conv_dw_supported(a, src, flt_packed, dst))
         return launch_conv_dw(a, src, flt_packed, bias, flt_scales, dst, st);
     return launch_conv_direct(a, src, flt_packed, bias, flt_scales, dst, nullptr, st);
 }
@@ -259,6 +266,8 @@ int mb200_conv_acc_qs8_nhwc(
         return rc;
     if (!src || !flt_packed || !acc)
         return set_error(ST_NULL_PTR, "conv tensor pointer is NULL");
+    if (((uintptr_t)bias | (uintptr_t)acc) & 3)
+        return set_error(ST_INVALID_LAYOUT, "bias and acc must be 4-byte aligned");
     return launch_conv_direct(
             a, src, flt_packed, bias, nullptr, nullptr, acc, (cudaStream_t)stream);
 }
@@ -309,6 +318,10 @@ int mb200_conv_bias_qs8_s2d(
         return set_error(ST_NULL_PTR, "conv tensor or workspace pointer is NULL");
     if (!conv_s2d_supported(a))
         return set_error(ST_NO_IMPLEMENT, "the space-to-depth path does not apply to this conv");
+    if (a.true_division)
+        return set_error(ST_OUT_OF_RANGE, "scales %g * %g / %g are outside the range of the "
+                         "tensor-core epilogue: use mb200_conv_bias_qs8_nhwc", p->src_scale,
+                         p->flt_scale, p->dst_scale);
     if (workspace_bytes < conv_s2d_workspace_bytes(a))
         return set_error(ST_OUT_OF_RANGE, "workspace of %zu bytes is too small", workspace_bytes);
     if (((uintptr_t)workspace | (uintptr_t)flt_s2d | (uintptr_t)dst) & 15)
@@ -343,7 +356,7 @@ int mb200_conv_bias_qs8_nchw(
     if ((uintptr_t)workspace & 255)
         return set_error(ST_INVALID_LAYOUT, "workspace must be 256-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
-    if (conv_s2d_supported(a) && algo != MB200_ALGO_DIRECT) {
+    if (conv_s2d_supported(a) && algo != MB200_ALGO_DIRECT && !a.true_division) {
         // first-layer form: the input is read in place, only the output needs a transpose
         int8_t* ws_dst = (int8_t*)workspace;
         int8_t* ws_flt = ws_dst + align_up((size_t)a.m * a.oc, 256);
@@ -423,6 +436,8 @@ int mb200_matmul_s8_s32(
         return rc;
     if (!a || !b_packed || !c)
         return set_error(ST_NULL_PTR, "matmul operand pointer is NULL");
+    if ((uintptr_t)c & 3)
+        return set_error(ST_INVALID_LAYOUT, "the int32 product must be 4-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     if (conv_umma_supported(args, a, b_packed, (const int8_t*)c)) {
         args.acc_out = c;
@@ -446,8 +461,9 @@ int mb200_matmul_s8_qs8(
     args.s_src = acc_scale;
     args.s_flt = 1.f;
     args.s_dst = dst_scale;
+    args.true_division = division_range_ok(acc_scale, 1.f, dst_scale) ? 0 : 1;
     cudaStream_t st = (cudaStream_t)stream;
-    if (conv_umma_supported(args, a, b_packed, c))
+    if (!args.true_division && conv_umma_supported(args, a, b_packed, c))
         return launch_conv_umma(args, a, b_packed, nullptr, nullptr, c, st);
     return launch_conv_direct(args, a, b_packed, nullptr, nullptr, c, nullptr, st);
 }
@@ -487,6 +503,8 @@ int mb200_typecvt_qs32_qs8(
         void* stream) {
     if (!src || !dst)
         return set_error(ST_NULL_PTR, "typecvt tensor pointer is NULL");
+    if ((uintptr_t)src & 3)
+        return set_error(ST_INVALID_LAYOUT, "typecvt source must be 4-byte aligned");
     if (nr_elem == 0)
         return ST_SUCCESS;
     return launch_typecvt_qs32_qs8(

@@ -50,9 +50,19 @@ __device__ __forceinline__ int requant_conv(
 // ---- the same arithmetic in fewer instructions, still bit-exact ----
 //
 // Division: with r = RN(1/d) (computed on the host), q0 = RN(t*r), rem = t - q0*d (exact in
-// one FMA) and q = RN(q0 + rem*r) equals RN(t/d) for every normal t; checked exhaustively
-// over all numerators for the divisors in tests/requant_math_check.c. Three instructions
-// instead of the general division routine.
+// one FMA) and q = RN(q0 + rem*r) equals RN(t/d) as long as no intermediate leaves the normal
+// range. tests/requant_math_check.c checks it on the host for every mantissa of t, a list of
+// divisors that includes the range ends below, and around every int8 step of the accumulator
+// chain. Three instructions instead of the general division routine.
+//
+// Precondition (division_range_ok): 2^-100 <= |s_src * s_flt| <= 2^69 (so that t, for any
+// non-zero int32 accumulator, and rem = t * 2^-24 stay normal) and 2^-60 <= |s_dst| <= 2^60.
+// The launchers check it for per-tensor scales and send anything else to the general kernel
+// with the true division; one scale per output channel must satisfy it by contract.
+__host__ __device__ inline bool division_range_ok(float s_src, float s_flt, float s_dst) {
+    const float prod = fabsf(s_src * s_flt), d = fabsf(s_dst);
+    return prod >= 0x1p-100f && prod <= 0x1p69f && d >= 0x1p-60f && d <= 0x1p60f;
+}
 __device__ __forceinline__ float div_rn_by_const(float t, float d, float r) {
     const float q0 = __fmul_rn(t, r);
     const float rem = __fmaf_rn(-q0, d, t);

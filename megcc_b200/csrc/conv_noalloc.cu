@@ -10,6 +10,8 @@
 // the process exits, which is why it is kept modest and why larger problems are refused.
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/megcc_b200.h"
 #include "internal.h"
 
@@ -21,16 +23,10 @@ constexpr size_t kScratchBytes = MB200_NOALLOC_SCRATCH_BYTES;
 // a kernel can use comes from cudaGetSymbolAddress below.
 static __device__ __align__(256) uint8_t g_scratch[kScratchBytes];
 
-// device address of g_scratch per CUDA ordinal, resolved on the first call on that device
-uint8_t* g_scratch_addr[64] = {nullptr};
-
-size_t align_up(size_t v, size_t a) {
-    return (v + a - 1) / a * a;
-}
-
-int out_extent(int in, int k, int s, int p, int d) {
-    return (in + 2 * p - d * (k - 1) - 1) / s + 1;
-}
+// device address of g_scratch per CUDA ordinal, resolved on the first call on that device.
+// Atomic: several host threads may make their first call at once; each would store the same
+// address.
+std::atomic<uint8_t*> g_scratch_addr[64];
 
 }  // namespace
 
@@ -45,46 +41,15 @@ size_t mb200_conv_bias_qs8_nchw_noalloc_max_scratch(void) {
 int mb200_conv_bias_qs8_nchw_noalloc(
         const mb200_conv_param* p, const int8_t* src, const int8_t* flt_oihw,
         const int32_t* bias, const float* flt_scales, int8_t* dst, void* stream) {
-    if (!p)
-        return set_error(ST_NULL_PTR, "conv param is NULL");
+    // the same validation and argument block as every other ConvBias entry point
+    ConvArgs a{};
+    int rc = make_args(p, 0, &a);
+    if (rc)
+        return rc;
     if (!src || !flt_oihw || !dst)
         return set_error(ST_NULL_PTR, "conv tensor pointer is NULL");
-    if (p->n <= 0 || p->ic <= 0 || p->oc <= 0 || p->ih <= 0 || p->iw <= 0 || p->kh <= 0 ||
-        p->kw <= 0 || p->stride_h <= 0 || p->stride_w <= 0 || p->pad_h < 0 || p->pad_w < 0 ||
-        p->dilate_h <= 0 || p->dilate_w <= 0 || p->groups <= 0 || p->ic % p->groups ||
-        p->oc % p->groups)
-        return set_error(ST_INVALID_LAYOUT, "conv param has an invalid extent");
-    if (p->nonline < 0 || p->nonline > 2)
-        return set_error(ST_NO_IMPLEMENT, "nonlineMode %d not supported", p->nonline);
-
-    ConvArgs a{};
-    a.n = p->n;
-    a.ic = p->ic;
-    a.ih = p->ih;
-    a.iw = p->iw;
-    a.oc = p->oc;
-    a.kh = p->kh;
-    a.kw = p->kw;
-    a.sh = p->stride_h;
-    a.sw = p->stride_w;
-    a.ph = p->pad_h;
-    a.pw = p->pad_w;
-    a.dh = p->dilate_h;
-    a.dw = p->dilate_w;
-    a.groups = p->groups;
-    a.oh = out_extent(p->ih, p->kh, p->stride_h, p->pad_h, p->dilate_h);
-    a.ow = out_extent(p->iw, p->kw, p->stride_w, p->pad_w, p->dilate_w);
-    if (a.oh <= 0 || a.ow <= 0)
-        return set_error(ST_INVALID_LAYOUT, "filter larger than the padded input");
-    const long long m = (long long)p->n * a.oh * a.ow;
-    if (m > 0x7fffffffLL)
-        return set_error(ST_OUT_OF_RANGE, "too many output pixels");
-    a.m = (int)m;
-    a.act = p->nonline;
-    a.src_is_nchw = 0;
-    a.s_src = p->src_scale;
-    a.s_flt = p->flt_scale;
-    a.s_dst = p->dst_scale;
+    if (((uintptr_t)bias | (uintptr_t)flt_scales) & 3)
+        return set_error(ST_INVALID_LAYOUT, "bias and channel scales must be 4-byte aligned");
 
     // scratch layout: [src as NHWC][dst as NHWC][filter packed K-major], 256-byte aligned
     const size_t src_bytes = align_up((size_t)a.n * a.ih * a.iw * a.ic, 256);
@@ -102,15 +67,16 @@ int mb200_conv_bias_qs8_nchw_noalloc(
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 64)
         return set_error(ST_RUNTIME, "no usable current CUDA device");
-    if (!g_scratch_addr[dev]) {
+    uint8_t* scratch = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!scratch) {
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, g_scratch);
         if (e != cudaSuccess || !ptr)
             return set_error(ST_RUNTIME, "cudaGetSymbolAddress(scratch): %s",
                              cudaGetErrorString(e));
-        g_scratch_addr[dev] = (uint8_t*)ptr;
+        scratch = (uint8_t*)ptr;
+        g_scratch_addr[dev].store(scratch, std::memory_order_release);
     }
-    uint8_t* scratch = g_scratch_addr[dev];
 
     cudaStream_t st = (cudaStream_t)stream;
     int8_t* ws_src = (int8_t*)scratch;
@@ -118,7 +84,7 @@ int mb200_conv_bias_qs8_nchw_noalloc(
     int8_t* ws_flt = ws_dst + dst_bytes;
     // Nothing in the scratch has to start at zero: every byte a kernel reads below is written
     // earlier in this same call, so whatever the previous call left behind is never seen.
-    int rc = launch_transpose_s8(src, ws_src, a.n, a.ic, a.ih * a.iw, st);
+    rc = launch_transpose_s8(src, ws_src, a.n, a.ic, a.ih * a.iw, st);
     if (rc)
         return rc;
     if ((rc = launch_pack_filter(a, flt_oihw, ws_flt, st)))

@@ -39,7 +39,18 @@ struct ConvArgs {
     float z_scale, z_out_scale;
     // tensor-core kernels only: store the int32 accumulators here instead of int8 results
     int32_t* acc_out;
+    // general kernel only: divide by s_dst with the true division (scales outside the range
+    // in which the three-instruction division by a constant is exact, see common.cuh)
+    int true_division;
 };
+
+}  // namespace mb200
+struct mb200_conv_param;
+namespace mb200 {
+// validates the public parameter block and fills the kernels' argument block (abi.cu)
+int make_args(const mb200_conv_param* p, int src_is_nchw, ConvArgs* a);
+int out_extent(int in, int k, int s, int p, int d);
+size_t align_up(size_t v, size_t a);
 
 // records a message for mb200_last_error() and returns `code`
 int set_error(int code, const char* fmt, ...);

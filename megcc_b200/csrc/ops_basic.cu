@@ -36,7 +36,11 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
         int8_t* __restrict__ dst, int32_t* __restrict__ acc_out) {
     const size_t total = (size_t)a.m * a.oc;
     const int icpg = a.ic / a.groups, ocpg = a.oc / a.groups;
-    const bool vec4 = !a.src_is_nchw && (icpg % 4 == 0);
+    // 4-byte loads only where every (pixel, group) run and every filter tap starts on a
+    // 4-byte boundary: icpg % 4 == 0 keeps the strides aligned, the base pointers are the
+    // caller's (a tensor sliced at an odd byte takes the byte loop)
+    const bool vec4 = !a.src_is_nchw && (icpg % 4 == 0) &&
+                      ((((uintptr_t)src) | ((uintptr_t)flt)) & 3) == 0;
     const float inv_dst = __fdiv_rn(1.f, a.s_dst);  // RN(1/d), as the fast division needs
     const float z_div = __fdiv_rn(1.f, a.z_out_scale);
     for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
@@ -84,7 +88,9 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
             acc += bias[o];
         if (kRequant) {
             const float sf = flt_scales ? flt_scales[o] : a.s_flt;
-            int q = requant_conv_fast(acc, a.s_src, sf, a.s_dst, inv_dst, a.act);
+            int q = a.true_division
+                            ? requant_conv(acc, a.s_src, sf, a.s_dst, a.act)
+                            : requant_conv_fast(acc, a.s_src, sf, a.s_dst, inv_dst, a.act);
             if (a.z_mode != 0 && a.z) {
                 // fused ElemwiseMultiType step (ElemwiseMultiType.cpp:38-46,158)
                 float t = __fadd_rn(__fmul_rn(a.s_dst, __int2float_rn(q)),

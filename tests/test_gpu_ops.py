@@ -480,6 +480,49 @@ def test_conv_accumulators_match_oracle(ops, oracle):
     assert (acc.cpu().numpy().transpose(0, 3, 1, 2) == want).all()
 
 
+@pytest.mark.parametrize("ic,oc,groups", [(64, 64, 1), (20, 12, 1), (32, 32, 32), (6, 6, 1)])
+def test_conv_on_tensors_that_start_at_an_odd_byte(ops, oracle, ic, oc, groups):
+    """int8 tensors sliced out of a larger buffer at byte offset 1: no vector or TMA path may
+    take them, and the byte-wise kernel gives the same result."""
+    c = dict(name=f"odd_offset_{ic}_{oc}_{groups}", n=2, ic=ic, oc=oc, h=19, w=17, k=3, stride=1,
+             pad=1, groups=groups, act="RELU", range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.4))
+    src, flt, bias = cases.conv_inputs(c)
+    p = ops.conv_param(2, ic, 19, 17, oc, 3, 3, 1, 1, groups, "RELU", 0.05, 0.01, 0.4)
+
+    def at_offset_one(t):
+        buf = torch.empty(t.numel() + 64, dtype=torch.int8, device="cuda")
+        off = 1 + (-buf.data_ptr()) % 16  # one past a 16-byte boundary
+        view = buf[off:off + t.numel()].view(t.shape)
+        view.copy_(t)
+        assert view.data_ptr() % 16 == 1
+        return view
+
+    nhwc = at_offset_one(ops.nchw_to_nhwc(dev(src)))
+    packed = at_offset_one(ops.pack_filter(p, dev(flt)))
+    dst = at_offset_one(torch.zeros((2, 19, 17, oc), dtype=torch.int8, device="cuda"))
+    ops.conv_bias_qs8_nhwc(p, nhwc, packed, dev(bias), dst=dst)
+    torch.cuda.synchronize()
+    want = oracle.conv_bias_qs8(src, flt, bias, 1, 1, 0.05, 0.01, 0.4, "RELU", groups=groups)
+    assert (dst.cpu().numpy().transpose(0, 3, 1, 2) == want).all()
+    acc = ops.conv_acc_qs8_nhwc(p, nhwc, packed, dev(bias))
+    want_acc = oracle.conv_bias_qs8(src, flt, bias, 1, 1, 0.05, 0.01, 0.4, "RELU", groups=groups,
+                                    return_acc=True)[1]
+    assert (acc.cpu().numpy().transpose(0, 3, 1, 2) == want_acc).all()
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("scales", [(1e-18, 1e-18, 1e-32), (3e12, 2e12, 6e28), (0.05, 0.01, 1e-21)])
+def test_conv_with_scales_outside_the_fast_division_range(ops, oracle, scales):
+    """Scale triples for which the three-instruction division is not proven exact take the
+    general kernel with the true division: still bit-exact."""
+    c = dict(name="extreme_scales", n=2, ic=64, oc=64, h=24, w=24, k=3, stride=1, pad=1, groups=1,
+             act="IDENTITY", range=(-128, 127), bias_range=(-1000, 1000), scales=scales)
+    out, (src, flt, bias) = run_conv_nchw(ops, c)
+    want = oracle.conv_bias_qs8(src, flt, bias, 1, 1, *scales, "IDENTITY")
+    assert (out == want).all()
+
+
 def test_first_layer_reads_nchw_in_place(ops, oracle):
     c = dict(name="stem_nchw", n=2, ic=3, oc=64, h=64, w=64, k=7, stride=2, pad=3, groups=1,
              act="RELU", range=(-128, 127), bias_range=(-1000, 1000), scales=(0.05, 0.01, 0.9))
