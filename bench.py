@@ -123,8 +123,7 @@ def cpu_reference_run(spec, steps, warmup, threads):
     """The reference's own x86 kernels on the host: each step walks the network once per
     thread on one image, all threads in parallel. Returns (img/s, seconds per step)."""
     import numpy as np
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import netwalk
+    from oracle import netwalk
     from oracle import oracle as O
 
     if O.ref_lib() is None:

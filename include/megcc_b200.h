@@ -79,9 +79,34 @@ typedef struct mb200_conv_fuse {
 MB200_API const char* mb200_version(void);
 /* text of the last error raised on the calling thread ("" if none) */
 MB200_API const char* mb200_last_error(void);
-/* Reads and clears the device status word that kernels set when a bounded wait ran out
- * (0 = healthy). Synchronises `stream`. */
+/* Kernel-selection switches for experiments and tests (the library's own choices are the
+ * defaults): "conv_bn" 0|128|256, "conv_pair" 0|1, "conv_splitk" 0|2..4, "wide128" 1|0,
+ * "patch_ctas" 0|1..3, "patch_alone" 0|1, "patch_plain" 0|1, "dw_out" 0|2|4,
+ * "dw_one_output" 0|1, "fast_requant" 1|0, "debug" 0|1. Their initial values come from the
+ * environment variables of the same meaning (MB200_CONV_BN, ...), read ONCE per process; no
+ * launch consults the environment. Every setting yields bit-identical results. Process-wide,
+ * not thread-safe against concurrent launches. */
+MB200_API int mb200_set_option(const char* name, int value);
+MB200_API int mb200_get_option(const char* name, int* value);
+/* Reads and clears the status word that kernels launched on `stream` set when a bounded wait
+ * ran out (0 = healthy; one word per device and stream). Synchronises `stream`. */
 MB200_API int mb200_device_status(void* stream, int* status_host);
+
+/* Self-test of the bounded device waits. Every wait inside the tensor-core kernels (on an
+ * mbarrier that a TMA load or an MMA completes) has a time limit; when it runs out the kernel
+ * records a code in the status word of its stream, lets the loads and MMAs it started
+ * finish, frees its tensor memory and returns, so that the context stays usable and
+ * LITE_wait can report TinyNN_ERROR_RUNTIME instead of hanging. This entry point makes that
+ * happen on purpose without faulting anything: it launches the tensor-core ConvBias of `p`
+ * (no bias, a shape the tensor-core kernel takes, >= 3 pipeline steps) with the limit
+ * shortened to limit_cycles GPU clock cycles and with one pipeline stage per tile left
+ * unfilled, so the MMA thread's wait for that stage expires. dst receives no defined result.
+ * Afterwards mb200_device_status(stream) reports 0x102 (and clears it). The reference has no
+ * counterpart (its runtime has no device and LITE_wait is a no-op,
+ * runtime/src/lite/network.c:229-232). */
+MB200_API int mb200_selftest_wait_expiry(
+        const mb200_conv_param* p, const int8_t* src, const int8_t* flt_packed, int8_t* dst,
+        long long limit_cycles, void* stream);
 
 /* Tells the library that [base, base + bytes) is device memory the caller owns and that may
  * be READ anywhere inside (an arena). The tensor-core ConvBias kernels describe activations to

@@ -171,6 +171,11 @@ LITE_API int LITE_get_tensor_device_type(const LiteTensor tensor, LiteDeviceType
  * The CUDA stream (cudaStream_t) all work of the network is issued on, for callers that
  * time or order their own work against it. */
 LITE_API int mb200_lite_stream(const LiteNetwork network, void** stream);
+/* Per-network switches. "use_graph" (default 1): replay the instruction list as one CUDA
+ * graph; 0 issues the kernels one by one on every forward. "profile": as
+ * mb200_lite_set_profile. New networks take their defaults from the environment once per
+ * process (MB200_NO_GRAPH=1, MB200_PROFILE=1); nothing reads the environment afterwards. */
+LITE_API int mb200_lite_set_option(LiteNetwork network, const char* name, int value);
 /* Per-instruction timing (the reference's compile-time TINYNN_PROFILE_KERNEL,
  * runtime/src/lite/network.c:187-224, as a run-time switch): while enabled every forward
  * runs instruction by instruction with a CUDA event pair around each one. */

@@ -1,6 +1,7 @@
 // extern "C" operator-level entry points declared in include/megcc_b200.h.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "../../include/megcc_b200.h"
@@ -8,6 +9,7 @@
 #include <mutex>
 
 #include "internal.h"
+#include "tuning.h"
 
 namespace mb200 {
 
@@ -28,23 +30,92 @@ int check_launch(const char* what) {
     return ST_SUCCESS;
 }
 
-int* device_status_word() {
-    // one word per device, allocated on first use and kept for the life of the process
-    static int* words[64] = {nullptr};
+// One status word per (device, stream): a kernel whose bounded wait runs out records its
+// code in the word of the stream it was launched on, so that a network waiting on its own
+// stream never consumes another network's error. The words of a device come from one small
+// allocation made at first use; a stream first seen while it is capturing (no set-up may
+// happen then) and streams beyond the pool's capacity share word 0.
+int* device_status_word(cudaStream_t st) {
+    constexpr int kWords = 4096;
+    struct Pool {
+        int* base = nullptr;
+        std::map<cudaStream_t, int> index;
+        int next = 1;
+    };
+    static Pool pools[64];
+    static std::mutex mu;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
         set_error(ST_RUNTIME, "no current CUDA device");
         return nullptr;
     }
-    if (!words[dev]) {
-        int* p = nullptr;
-        if (cudaMalloc(&p, 256) != cudaSuccess || cudaMemset(p, 0, 256) != cudaSuccess) {
-            set_error(ST_MALLOC, "cannot allocate the device status word");
+    std::lock_guard<std::mutex> lock(mu);
+    Pool& pool = pools[dev];
+    if (!pool.base) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (st && cudaStreamIsCapturing(st, &cap) == cudaSuccess &&
+            cap != cudaStreamCaptureStatusNone) {
+            set_error(ST_RUNTIME, "first use of the library on this device during stream capture");
             return nullptr;
         }
-        words[dev] = p;
+        int* p = nullptr;
+        if (cudaMalloc(&p, kWords * sizeof(int)) != cudaSuccess ||
+            cudaMemset(p, 0, kWords * sizeof(int)) != cudaSuccess) {
+            cudaGetLastError();
+            set_error(ST_MALLOC, "cannot allocate the device status words");
+            return nullptr;
+        }
+        pool.base = p;
     }
-    return words[dev];
+    auto it = pool.index.find(st);
+    if (it != pool.index.end())
+        return pool.base + it->second;
+    if (pool.next >= kWords)
+        return pool.base;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (st && cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+        return pool.base;
+    cudaGetLastError();
+    const int idx = pool.next++;
+    pool.index[st] = idx;
+    return pool.base + idx;
+}
+
+namespace {
+struct TuningField {
+    const char* name;
+    const char* env;
+    int Tuning::*field;
+    bool env_negates;  // the variable switches the feature OFF
+};
+const TuningField kTuningFields[] = {
+        {"conv_bn", "MB200_CONV_BN", &Tuning::conv_bn, false},
+        {"conv_pair", "MB200_CONV_PAIR", &Tuning::conv_pair, false},
+        {"conv_splitk", "MB200_CONV_SPLITK", &Tuning::conv_splitk, false},
+        {"wide128", "MB200_NO_WIDE128", &Tuning::wide128, true},
+        {"patch_ctas", "MB200_PATCH_CTAS", &Tuning::patch_ctas, false},
+        {"patch_alone", "MB200_PATCH_ALONE", &Tuning::patch_alone, false},
+        {"patch_plain", "MB200_PATCH_PLAIN", &Tuning::patch_plain, false},
+        {"dw_out", "MB200_DW_OUT", &Tuning::dw_out, false},
+        {"dw_one_output", "MB200_DW_ONE_OUTPUT", &Tuning::dw_one_output, false},
+        {"fast_requant", "MB200_NO_FAST_REQUANT", &Tuning::fast_requant, true},
+        {"debug", "MB200_DEBUG", &Tuning::debug, false},
+};
+}  // namespace
+
+Tuning& tuning() {
+    static Tuning t = [] {
+        Tuning v;
+        for (const TuningField& f : kTuningFields) {
+            const char* e = getenv(f.env);
+            if (!e || !*e)
+                continue;
+            const int n = atoi(e);
+            v.*(f.field) = f.env_negates ? (n != 0 ? 0 : 1) : n;
+        }
+        return v;
+    }();
+    return t;
 }
 
 int out_extent(int in, int k, int s, int p, int d) {
@@ -151,6 +222,28 @@ int mb200_unregister_readable_range(const void* base) {
 }
 
 
+int mb200_set_option(const char* name, int value) {
+    if (!name)
+        return set_error(ST_NULL_PTR, "option name is NULL");
+    for (const TuningField& f : kTuningFields)
+        if (strcmp(name, f.name) == 0) {
+            tuning().*(f.field) = value;
+            return ST_SUCCESS;
+        }
+    return set_error(ST_OUT_OF_RANGE, "unknown option '%s'", name);
+}
+
+int mb200_get_option(const char* name, int* value) {
+    if (!name || !value)
+        return set_error(ST_NULL_PTR, "option name or value pointer is NULL");
+    for (const TuningField& f : kTuningFields)
+        if (strcmp(name, f.name) == 0) {
+            *value = tuning().*(f.field);
+            return ST_SUCCESS;
+        }
+    return set_error(ST_OUT_OF_RANGE, "unknown option '%s'", name);
+}
+
 const char* mb200_version(void) {
     return "megcc_b200 0.1 (sm_100a)";
 }
@@ -162,10 +255,10 @@ const char* mb200_last_error(void) {
 int mb200_device_status(void* stream, int* status_host) {
     if (!status_host)
         return set_error(ST_NULL_PTR, "status_host is NULL");
-    int* w = device_status_word();
+    cudaStream_t st = (cudaStream_t)stream;
+    int* w = device_status_word(st);
     if (!w)
         return ST_MALLOC;
-    cudaStream_t st = (cudaStream_t)stream;
     int v = 0;
     if (cudaMemcpyAsync(&v, w, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
         cudaStreamSynchronize(st) != cudaSuccess)
@@ -255,6 +348,26 @@ int mb200_conv_bias_qs8_nhwc_fused(
     if (algo == MB200_ALGO_AUTO && side_ok && conv_dw_supported(a, src, flt_packed, dst))
         return launch_conv_dw(a, src, flt_packed, bias, flt_scales, dst, st);
     return launch_conv_direct(a, src, flt_packed, bias, flt_scales, dst, nullptr, st);
+}
+
+int mb200_selftest_wait_expiry(
+        const mb200_conv_param* p, const int8_t* src, const int8_t* flt_packed, int8_t* dst,
+        long long limit_cycles, void* stream) {
+    ConvArgs a{};
+    int rc = make_args(p, 0, &a);
+    if (rc)
+        return rc;
+    if (!src || !flt_packed || !dst)
+        return set_error(ST_NULL_PTR, "conv tensor pointer is NULL");
+    if (limit_cycles < 1000 || limit_cycles > (1LL << 31))
+        return set_error(ST_OUT_OF_RANGE, "limit of %lld cycles is outside [1000, 2^31]",
+                         limit_cycles);
+    if (!conv_umma_supported(a, src, flt_packed, dst) || a.kh * a.kw * (a.ic / 64) < 3)
+        return set_error(ST_NO_IMPLEMENT, "the self-test needs a shape of the tensor-core "
+                                          "ConvBias with at least three pipeline steps");
+    a.test_wait_cycles = limit_cycles;
+    a.test_skip_step = 1;
+    return launch_conv_umma(a, src, flt_packed, nullptr, nullptr, dst, (cudaStream_t)stream);
 }
 
 int mb200_conv_acc_qs8_nhwc(

@@ -19,6 +19,7 @@
 #include <stdlib.h>
 
 #include "internal.h"
+#include "tuning.h"
 
 namespace mb200 {
 
@@ -332,10 +333,9 @@ int launch_conv_dw(
     // latency-bound); at stride 2 adjacent outputs share one input column only and the
     // one-output kernel stays ahead. MB200_DW_OUT=2|4 forces a form at either stride,
     // MB200_DW_ONE_OUTPUT=1 the one-output kernel (tests and experiments).
-    const char* e = getenv("MB200_DW_OUT");
-    const int forced = e ? atoi(e) : 0;
+    const int forced = tuning().dw_out;
     if (a.sh == a.sw && (a.sh == 1 || (a.sh == 2 && forced != 0)) && !(a.z_mode != 0 && a.z) &&
-        !getenv("MB200_DW_ONE_OUTPUT")) {
+        !tuning().dw_one_output) {
         const int outs = forced == 4 ? 4 : 2;
         const size_t items = (size_t)a.n * a.oh * ((a.ow + outs - 1) / outs) * p.c16;
         size_t blocks = (items + 127) / 128;

@@ -21,6 +21,7 @@
 
 #include "conv_epilogue.cuh"
 #include "internal.h"
+#include "tuning.h"
 #include "umma_ptx.cuh"
 
 namespace mb200 {
@@ -496,7 +497,7 @@ int launch_conv_pair(
                                 &p.ep.z_fast_b);
     p.ep.acc_out = a.acc_out;
     p.dst = dst;
-    p.status = device_status_word();
+    p.status = device_status_word(st);
     if (!p.status)
         return ST_MALLOC;
     if (cudaFuncSetAttribute(conv_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -506,7 +507,7 @@ int launch_conv_pair(
     int clusters = pair_clusters_resident();
     if (clusters > total)
         clusters = total;
-    if (getenv("MB200_DEBUG"))
+    if (tuning().debug)
         fprintf(stderr, "conv_pair: clusters %d tiles %d k_iters %d smem %d\n", clusters, total,
                 p.k_iters, kDynamic);
     conv_pair_kernel<<<2 * clusters, kThreads, kDynamic, st>>>(map_a, map_b, p);

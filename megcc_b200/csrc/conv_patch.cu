@@ -26,6 +26,7 @@
 
 #include "conv_epilogue.cuh"
 #include "internal.h"
+#include "tuning.h"
 #include "umma_ptx.cuh"
 
 namespace mb200 {
@@ -433,8 +434,7 @@ struct PatchPlan {
 
 // CTAs per SM to try first; MB200_PATCH_CTAS overrides (performance experiments)
 int patch_first_ctas() {
-    const char* e = getenv("MB200_PATCH_CTAS");
-    const int v = e ? atoi(e) : 0;
+    const int v = tuning().patch_ctas;
     return v >= 1 && v <= 3 ? v : 3;
 }
 
@@ -452,7 +452,7 @@ PatchPlan plan_patch(const ConvArgs& a) {
     if (pph > 256 || ppw > 256)
         return pl;
     pl.bn = a.oc <= 64 ? 64 : 128;
-    pl.rows64 = a.ic == 64 && a.kh == 3 && a.kw == 3 && pl.bn == 64 && !getenv("MB200_PATCH_PLAIN");
+    pl.rows64 = a.ic == 64 && a.kh == 3 && a.kw == 3 && pl.bn == 64 && !tuning().patch_plain;
     pl.plane_stride = pph * ppw * 16;
     // a TMA destination in shared memory must be 128-byte aligned: pad the stage
     pl.a_stage_bytes = ((a.ic / 16) * pl.plane_stride + 127) / 128 * 128;
@@ -497,7 +497,7 @@ int launch_patch(
         if (cap >= p.n_tiles && grid > cap)
             grid = cap;
     }
-    if (getenv("MB200_DEBUG"))
+    if (tuning().debug)
         fprintf(stderr, "conv_patch<%d,%d,%d,%d,%d>: per_sm %d grid %d m_tiles %d n_tiles %d smem %d "
                 "stages %d b_single_load %d\n", BN, KH, KW, CHUNKS, EW, per_sm, grid, p.m_tiles,
                 p.n_tiles, smem, p.stages, p.b_single_load);
@@ -515,8 +515,7 @@ float conv_patch_efficiency(const ConvArgs& a) {
     // shares its scheduler with epilogue warps, is the limit: the im2col kernel with two CTAs
     // per SM measured faster. MB200_PATCH_ALONE=1 uses the patch kernel all the same.
     if (plan_patch(a).ctas_per_sm < 2) {
-        const char* alone = getenv("MB200_PATCH_ALONE");
-        if (!(alone && atoi(alone) != 0))
+        if (!tuning().patch_alone)
             return 0.f;
     }
     const int ty = (a.oh + kTH - 1) / kTH, tx = (a.ow + kTW - 1) / kTW;
@@ -676,14 +675,14 @@ int launch_conv_patch(
     if (p.ep.z_mode != 0 && p.ep.fast_ops != 0)
         residual_fast_constants(a.s_dst, a.z_scale, a.z_out_scale, p.ep.z_mode, &p.ep.z_fast_a,
                                 &p.ep.z_fast_b);
-    if (getenv("MB200_DEBUG"))
+    if (tuning().debug)
         fprintf(stderr, "%s: scales %g %g %g act %d z_mode %d verified requant: %d ops, %g + %.9g, short residual %g %g\n", "conv_patch",
                 a.s_src, a.s_flt, a.s_dst, a.act, p.ep.z_mode, p.ep.fast_ops, p.ep.fast_mul, p.ep.fast_add,
                 p.ep.z_fast_a,
                 p.ep.z_fast_b);
     p.ep.acc_out = a.acc_out;
     p.dst = dst;
-    p.status = device_status_word();
+    p.status = device_status_word(st);
     if (!p.status)
         return ST_MALLOC;
     // persistent grid: a multiple of the channel-slice count, at most what fits on the GPU

@@ -30,6 +30,7 @@
 
 #include "conv_epilogue.cuh"
 #include "internal.h"
+#include "tuning.h"
 #include "umma_ptx.cuh"
 
 namespace mb200 {
@@ -79,6 +80,10 @@ struct UmmaConvParams {
     EpilogueParams ep;
     int8_t* dst;
     int* status;
+    // cycles a bounded wait may take (kWaitCycles unless a self-test shortens it), and the
+    // pipeline step of every tile that the producer leaves out (-1: none; self-test only)
+    long long wait_cycles;
+    int skip_step;
     // split-K (SPLITK kernels only): work items below `full_tiles` are whole tiles, the
     // tiles after them are cut into `split` parts of `k_per_part` pipeline steps each
     int full_tiles, split, k_per_part, total_items;
@@ -201,13 +206,23 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                     fx = tap - fy * p.taps_w;
                 }
                 for (int it = w.k0; it < w.k1; ++it) {
-                    if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) {
+                    if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag, p.wait_cycles)) {
                         if (!*abort_flag) {
                             *abort_flag = 1;
                             atomicExch(p.status, ERR_PRODUCER_WAIT);
                         }
                         ok = false;
                         break;
+                    }
+                    if (it == p.skip_step) {
+                        // self-test of the bounded waits: this stage is never filled (neither
+                        // the byte count is announced nor a load issued), so the MMA thread's
+                        // wait for it runs out and the kernel takes its give-up path
+                        if (++s == kSt) {
+                            s = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
                     }
                     mbar_expect_tx(&full_bar[s], (uint32_t)(L::kABytes + L::kBBytes));
                     uint8_t* sa = tiles_a + s * L::kABytes;
@@ -258,7 +273,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                 const int buf = local & 1;
                 const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
                 // the epilogue must have drained this accumulator buffer
-                if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
+                if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag, p.wait_cycles)) {
                     if (!*abort_flag) {
                         *abort_flag = 1;
                         atomicExch(p.status, ERR_MMA_ACC_WAIT);
@@ -269,7 +284,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
                 for (int it = w.k0; it < w.k1; ++it) {
-                    if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
+                    if (!mbar_wait(&full_bar[s], phase, abort_flag, p.wait_cycles)) {
                         if (!*abort_flag) {
                             *abort_flag = 1;
                             atomicExch(p.status, ERR_MMA_WAIT);
@@ -328,7 +343,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             const int tile_n = tile % p.n_tiles, tile_m = tile / p.n_tiles;
             const int m = tile_m * kBM + row, n0 = tile_n * BN;
-            ok = mbar_wait(&acc_full[buf], acc_phase, abort_flag);
+            ok = mbar_wait(&acc_full[buf], acc_phase, abort_flag, p.wait_cycles);
             if (!ok && !*abort_flag) {
                 *abort_flag = 1;
                 atomicExch(p.status, ERR_EPILOGUE_WAIT);
@@ -367,7 +382,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                 }
                 __threadfence();  // the slab is visible device-wide before the part is counted
                 mbar_arrive(ep_bar);
-                ok = mbar_wait(ep_bar, ep_phase, abort_flag);
+                ok = mbar_wait(ep_bar, ep_phase, abort_flag, p.wait_cycles);
                 ep_phase ^= 1u;
                 if (ok && threadIdx.x == 64) {
                     unsigned* counter = p.counters + (w.tile - p.full_tiles);
@@ -379,7 +394,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
                 }
                 if (ok) {
                     mbar_arrive(ep_bar);
-                    ok = mbar_wait(ep_bar, ep_phase, abort_flag);
+                    ok = mbar_wait(ep_bar, ep_phase, abort_flag, p.wait_cycles);
                     ep_phase ^= 1u;
                 }
                 if (!ok && !*abort_flag) {
@@ -442,7 +457,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
             umma_commit(drain_bar);
             const long long t0 = clock64();
             while (!mbar_try_wait(drain_bar, 0)) {
-                if (clock64() - t0 > kWaitCycles) {
+                if (clock64() - t0 > p.wait_cycles) {
                     atomicExch(p.status, ERR_DRAIN_WAIT);
                     break;
                 }
@@ -477,7 +492,7 @@ int launch_kernel(
     int grid = sm_count() * per_sm;
     if (grid > total)
         grid = total;
-    if (getenv("MB200_DEBUG"))
+    if (tuning().debug)
         fprintf(stderr, "conv_umma<%d,%d,%d>: per_sm %d grid %d items %d (whole tiles %d, split %d) smem %d\n",
                 BN, GEOM, (int)SPLITK, per_sm, grid, total, SPLITK ? p.full_tiles : total,
                 SPLITK ? p.split : 1, SmemLayout<BN, GEOM>::kDynamic);
@@ -512,8 +527,7 @@ struct SplitPlan {
 
 SplitPlan plan_split_k(int tiles, int k_iters, int ctas) {
     SplitPlan sp{tiles, 1, k_iters, tiles};
-    const char* e = getenv("MB200_CONV_SPLITK");  // 2..4: that split wherever it fits
-    const int forced = e ? atoi(e) : 0;
+    const int forced = tuning().conv_splitk;  // 2..4: that split wherever it fits
     if (forced < 2 || ctas <= 0)
         return sp;
     const int rem = tiles % ctas;
@@ -615,15 +629,14 @@ int launch_conv_umma_geom(
         return set_error(ST_INVALID_LAYOUT, "bias and channel scales must be 16-byte aligned");
 
     // 128-channel rows whenever the channel count allows: fewer, larger TMA requests
-    if (geom == GEOM_WIDE && a.ic % 128 == 0 && !getenv("MB200_NO_WIDE128"))
+    if (geom == GEOM_WIDE && a.ic % 128 == 0 && tuning().wide128)
         geom = GEOM_WIDE128;
     // MB200_CONV_PAIR=1: one 256 x 256 tile per pair of SMs (conv_pair.cu) wherever it applies.
     // Off by default: both kernels are bound by shared-memory bandwidth (operand reads of
     // the MMAs plus the TMA writes), and on the ResNet layers the pair measured no faster
     // than the 128 x 256 tile of a single SM.
     if (geom == GEOM_WIDE128 && conv_pair_supported(a, src, flt, dst)) {
-        const char* pair = getenv("MB200_CONV_PAIR");
-        if (pair && atoi(pair) != 0)
+        if (tuning().conv_pair != 0)
             return launch_conv_pair(a, src, flt, bias, flt_scales, dst, st);
     }
     const int chans = geom == GEOM_WIDE128 ? 128 : geom == GEOM_WIDE ? kBK : 16;
@@ -633,12 +646,12 @@ int launch_conv_umma_geom(
         // of a single CTA per SM and there are tiles for every SM
         const long long k_bytes = (long long)taps * a.ic;
         const long long tiles256 = (long long)((a.m + kBM - 1) / kBM) * ((a.oc + 255) / 256);
-        const char* force = getenv("MB200_CONV_BN");
+        const int force = tuning().conv_bn;
         if (geom == GEOM_WIDE128 && a.oc > 128 && k_bytes >= 1024 && tiles256 >= sm_count())
             bn = 256;
-        if (force && geom == GEOM_WIDE128 && atoi(force) == 256 && a.oc > 128)
+        if (force == 256 && geom == GEOM_WIDE128 && a.oc > 128)
             bn = 256;
-        if (force && atoi(force) == 128 && a.oc > 64)
+        if (force == 128 && a.oc > 64)
             bn = 128;
     }
     const CUtensorMapSwizzle swz = geom == GEOM_WIDE128 ? CU_TENSOR_MAP_SWIZZLE_128B
@@ -734,14 +747,16 @@ int launch_conv_umma_geom(
     if (p.ep.z_mode != 0 && p.ep.fast_ops != 0)
         residual_fast_constants(a.s_dst, a.z_scale, a.z_out_scale, p.ep.z_mode, &p.ep.z_fast_a,
                                 &p.ep.z_fast_b);
-    if (getenv("MB200_DEBUG"))
+    if (tuning().debug)
         fprintf(stderr, "%s: scales %g %g %g act %d z_mode %d verified requant: %d ops, %g + %.9g, short residual %g %g\n", "conv_umma",
                 a.s_src, a.s_flt, a.s_dst, a.act, p.ep.z_mode, p.ep.fast_ops, p.ep.fast_mul, p.ep.fast_add,
                 p.ep.z_fast_a,
                 p.ep.z_fast_b);
     p.ep.acc_out = a.acc_out;
     p.dst = dst;
-    p.status = device_status_word();
+    p.status = device_status_word(st);
+    p.wait_cycles = a.test_wait_cycles > 0 ? a.test_wait_cycles : kWaitCycles;
+    p.skip_step = a.test_wait_cycles > 0 ? a.test_skip_step : -1;
     if (!p.status)
         return ST_MALLOC;
     p.full_tiles = p.total_items = p.m_tiles * p.n_tiles;

@@ -42,6 +42,11 @@ struct ConvArgs {
     // general kernel only: divide by s_dst with the true division (scales outside the range
     // in which the three-instruction division by a constant is exact, see common.cuh)
     int true_division;
+    // self-test of the bounded device waits (conv_umma only): when test_wait_cycles > 0 the
+    // waits give up after that many clock cycles and the producer leaves out pipeline step
+    // test_skip_step of every tile
+    long long test_wait_cycles;
+    int test_skip_step;
 };
 
 }  // namespace mb200
@@ -56,8 +61,9 @@ size_t align_up(size_t v, size_t a);
 int set_error(int code, const char* fmt, ...);
 // cudaGetLastError() after a launch -> status
 int check_launch(const char* what);
-// the per-device int that kernels set when a bounded wait runs out
-int* device_status_word();
+// the int that kernels launched on `st` set when a bounded wait runs out (one per device
+// and stream, see abi.cu)
+int* device_status_word(cudaStream_t st);
 
 int launch_pack_filter(const ConvArgs& a, const int8_t* src, int8_t* dst, cudaStream_t st);
 int launch_conv_direct(

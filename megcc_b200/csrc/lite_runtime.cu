@@ -176,12 +176,29 @@ struct ComputeLane {
     cudaEvent_t done = nullptr;
     bool recorded = false;
 };
+// Defaults of a new network, taken from the environment once per process
+// (MB200_NO_GRAPH=1, MB200_PROFILE=1, MB200_LITE_SERIAL_COMPUTE=0); a network's own settings
+// change through mb200_lite_set_option afterwards.
+struct RuntimeDefaults {
+    bool use_graph = true, profile = false, serial_compute = true;
+};
+const RuntimeDefaults& runtime_defaults() {
+    static const RuntimeDefaults d = [] {
+        RuntimeDefaults v;
+        const char* e = getenv("MB200_NO_GRAPH");
+        v.use_graph = !(e && e[0] == '1');
+        e = getenv("MB200_PROFILE");
+        v.profile = e && e[0] == '1';
+        e = getenv("MB200_LITE_SERIAL_COMPUTE");
+        v.serial_compute = !(e && atoi(e) == 0);
+        return v;
+    }();
+    return d;
+}
+
 ComputeLane* compute_lane(int device) {
     static ComputeLane lanes[64];
-    static const bool enabled = [] {
-        const char* e = getenv("MB200_LITE_SERIAL_COMPUTE");
-        return !(e && atoi(e) == 0);
-    }();
+    const bool enabled = runtime_defaults().serial_compute;
     if (!enabled || device < 0 || device >= 64)
         return nullptr;
     return &lanes[device];
@@ -778,7 +795,7 @@ int upload_weights(Network* net) {
     }
     if ((e = cudaStreamSynchronize(net->stream)) != cudaSuccess)
         return cuda_fail(e, "weight upload");
-    if (!mb200::device_status_word())
+    if (!mb200::device_status_word(net->stream))
         return fail(TinyNN_ERROR_MEMORY_MALLOC, "%s", mb200_last_error());
     net->loaded = true;
     return TinyNN_SUCCESS;
@@ -1084,10 +1101,8 @@ int LITE_make_network(LiteNetwork* network, const LiteConfig config, const LiteN
     for (size_t i = 0; i < io.output_size; ++i)
         if (io.outputs && io.outputs[i].name && !io.outputs[i].is_host)
             net->io_device_names.push_back(io.outputs[i].name);
-    const char* ng = getenv("MB200_NO_GRAPH");
-    net->use_graph = !(ng && ng[0] == '1');
-    const char* pf = getenv("MB200_PROFILE");
-    net->profile = pf && pf[0] == '1';
+    net->use_graph = runtime_defaults().use_graph;
+    net->profile = runtime_defaults().profile;
     *network = net;
     return TinyNN_SUCCESS;
 }
@@ -1380,6 +1395,23 @@ int mb200_lite_stream(const LiteNetwork network, void** stream) {
         return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
     *stream = as_net(network)->stream;
     return TinyNN_SUCCESS;
+}
+
+int mb200_lite_set_option(LiteNetwork network, const char* name, int value) {
+    if (!network || !name)
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    Network* net = as_net(network);
+    if (strcmp(name, "use_graph") == 0) {
+        if (wait(net))
+            return TinyNN_ERROR_RUNTIME;
+        net->use_graph = value != 0;
+        return TinyNN_SUCCESS;
+    }
+    if (strcmp(name, "profile") == 0) {
+        net->profile = value != 0;
+        return TinyNN_SUCCESS;
+    }
+    return fail(TinyNN_ERROR_OUT_OF_RANGE, "unknown option '%s'", name);
 }
 
 int mb200_lite_set_profile(LiteNetwork network, int enable) {

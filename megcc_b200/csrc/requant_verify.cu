@@ -25,6 +25,7 @@
 
 #include "common.cuh"
 #include "internal.h"
+#include "tuning.h"
 
 namespace mb200 {
 
@@ -217,7 +218,7 @@ inline int fast_residual(int q, int z, float a, float b, bool relu) {
 bool residual_fast_constants(
         float s_conv, float s_z, float out_scale, int mode, float* a_out, float* b_out) {
     *a_out = *b_out = 0.f;
-    if (getenv("MB200_NO_FAST_REQUANT") || (mode != 1 && mode != 2))
+    if (!tuning().fast_requant || (mode != 1 && mode != 2))
         return false;
     if (!(s_conv > 0.f) || !(s_z > 0.f) || !(out_scale > 0.f))
         return false;
@@ -280,7 +281,7 @@ int requant_fast_constants(
     *mul_out = *add_out = 0.f;
     if (act != ACT_IDENTITY && act != ACT_RELU)
         return 0;
-    if (getenv("MB200_NO_FAST_REQUANT"))
+    if (!tuning().fast_requant)
         return 0;
     struct Verdict {
         int ops;

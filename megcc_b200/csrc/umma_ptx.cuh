@@ -53,7 +53,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. Returns false when the limit ran out or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(
-        uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+        uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+        long long limit = kWaitCycles) {
     // A few immediate polls, then short sleeps (20 ns doubling to 160 ns): roles that wait
     // for most of a kernel (producer and MMA thread of an epilogue-bound layer) should not
     // take issue slots from the warps that work. Measured against polling without sleeps on
@@ -73,7 +74,7 @@ __device__ __forceinline__ bool mbar_wait(
         if ((spin & 63) == 63) {
             if (*abort_flag)
                 return false;
-            if (clock64() - t0 > kWaitCycles)
+            if (clock64() - t0 > limit)
                 return false;
         }
     }

@@ -72,6 +72,7 @@ SIGNATURES = {
     "LITE_get_tensor_device_type": (C.c_int, [_P, C.POINTER(C.c_int)]),
     "mb200_lite_stream": (C.c_int, [_P, C.POINTER(_P)]),
     "mb200_lite_set_profile": (C.c_int, [_P, C.c_int]),
+    "mb200_lite_set_option": (C.c_int, [_P, C.c_char_p, C.c_int]),
     "mb200_lite_profile": (C.c_int, [_P, C.c_char_p, C.c_size_t]),
 }
 
@@ -189,6 +190,9 @@ class Network:
         p = _P()
         check(lib().mb200_lite_stream(self._net, C.byref(p)))
         return p.value or 0
+
+    def set_option(self, name, value):
+        check(lib().mb200_lite_set_option(self._net, name.encode(), int(value)))
 
     def set_profile(self, enable):
         check(lib().mb200_lite_set_profile(self._net, int(enable)))

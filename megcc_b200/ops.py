@@ -156,6 +156,14 @@ def nhwc_to_nchw(src):
     return dst
 
 
+def set_option(name, value):
+    """Kernel-selection switch (see mb200_set_option); returns the previous value."""
+    old = C.c_int(0)
+    check(lib().mb200_get_option(name.encode(), C.byref(old)))
+    check(lib().mb200_set_option(name.encode(), int(value)))
+    return old.value
+
+
 def device_status():
     s = C.c_int(0)
     check(lib().mb200_device_status(_stream(), C.byref(s)))

@@ -20,6 +20,8 @@ import subprocess
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+# the one place that names where the reference tree is expected (override: MEGCC_REFERENCE_DIR)
+DEFAULT_REFERENCE_DIR = "/root/reference"
 ACT = {"IDENTITY": 0, "RELU": 1, "H_SWISH": 2}
 POOL = {"MAX": 0, "AVERAGE": 1, "AVERAGE_COUNT_EXCLUDE_PADDING": 2}
 QELEM = {"QADD": 0, "QFUSE_ADD_RELU": 1, "QMUL": 2, "QRELU": 3}
@@ -29,10 +31,21 @@ _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
 _f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 
 
+def reference_tree():
+    """Where the reference's source tree lies: $MEGCC_REFERENCE_DIR, else the default the
+    Makefile also uses. None when its KernelGen sources are not there."""
+    root = os.environ.get("MEGCC_REFERENCE_DIR", DEFAULT_REFERENCE_DIR)
+    return root if os.path.isdir(os.path.join(root, "compiler", "lib", "KernelGen")) else None
+
+
 def build(with_reference=True):
     """Compile the checker (and, when the reference tree is present, oracle/_ref)."""
-    targets = ["oracle"] + (["ref"] if with_reference else [])
-    subprocess.run(["make", "-s", "-j8", "-C", HERE] + targets, check=True)
+    targets = ["oracle"]
+    args = []
+    if with_reference and reference_tree():
+        targets.append("ref")
+        args.append("REF=" + reference_tree())
+    subprocess.run(["make", "-s", "-j8", "-C", HERE] + args + targets, check=True)
 
 
 _lib = None

@@ -5,7 +5,7 @@ import pytest
 
 import cases
 import golden_util as G
-import netwalk
+from oracle import netwalk
 
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu

@@ -17,6 +17,19 @@ def ops():
     return O
 
 
+@pytest.fixture
+def tune(ops):
+    """Sets kernel-selection switches for one test and puts the old values back."""
+    saved = []
+
+    def set_(name, value):
+        saved.append((name, ops.set_option(name, value)))
+
+    yield set_
+    for name, old in reversed(saved):
+        ops.set_option(name, old)
+
+
 def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
@@ -101,7 +114,7 @@ def test_conv_umma_matches_oracle(ops, oracle, case):
 @pytest.mark.parametrize("algo", ["umma", "patch"])
 @pytest.mark.parametrize("act", ["RELU", "IDENTITY"])
 def test_conv_reference_operation_order_without_verified_forms(ops, oracle, algo, act,
-                                                               monkeypatch):
+                                                               tune):
     """The epilogue with the reference's own six float operations (the verified short forms
     switched off), and the same case with them on: both bit-exact."""
     c = dict(name="exact_chain_" + act, n=2, ic=64, oc=64, h=40, w=40, k=3, stride=1, pad=1,
@@ -112,7 +125,7 @@ def test_conv_reference_operation_order_without_verified_forms(ops, oracle, algo
     want = oracle.conv_bias_qs8(src, flt, bias, 1, 1, s0, s1, s2, act)
     out, _ = run_conv_nchw(ops, c, algo=algo)
     assert (out == want).all()
-    monkeypatch.setenv("MB200_NO_FAST_REQUANT", "1")
+    tune("fast_requant", 0)
     out, _ = run_conv_nchw(ops, c, algo=algo)
     assert (out == want).all()
     assert ops.device_status() == 0
@@ -130,12 +143,12 @@ BN256_CASES = [
 
 
 @pytest.mark.parametrize("case", BN256_CASES, ids=[c[0] for c in BN256_CASES])
-def test_conv_umma_256_wide_tiles_match_oracle(ops, oracle, case, monkeypatch):
+def test_conv_umma_256_wide_tiles_match_oracle(ops, oracle, case, tune):
     """The 128 x 256 output tile (one CTA per SM, sixteen epilogue warps): forced through the
     tuning variable on small shapes, and chosen by the launcher itself on one large enough."""
     name, n, ic, oc, h, w, k, stride, pad, act, forced = case
     if forced:
-        monkeypatch.setenv("MB200_CONV_BN", "256")
+        tune("conv_bn", 256)
     c = dict(name="bn256_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=stride, pad=pad,
              groups=1, act=act, range=(-128, 127), bias_range=(-1000, 1000),
              scales=(0.05, 0.01, 0.37 * (ic * k * k / 576.0) ** 0.5 + 0.4))
@@ -214,13 +227,13 @@ SPLITK_CASES = [
 
 
 @pytest.mark.parametrize("case", SPLITK_CASES, ids=[c[0] for c in SPLITK_CASES])
-def test_conv_umma_split_k_matches_oracle(ops, oracle, case, monkeypatch):
+def test_conv_umma_split_k_matches_oracle(ops, oracle, case, tune):
     """128 x 256 tiles cut along K: every part leaves its accumulators in scratch and the last
     one to finish sums and requantises. Forced on small shapes (all tiles split), run twice:
     the second launch finds the counters as the first one left them."""
     name, n, ic, oc, h, w, k, stride, pad, act, split = case
-    monkeypatch.setenv("MB200_CONV_BN", "256")
-    monkeypatch.setenv("MB200_CONV_SPLITK", str(split))
+    tune("conv_bn", 256)
+    tune("conv_splitk", split)
     c = dict(name="splitk_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=stride, pad=pad,
              groups=1, act=act, range=(-128, 127), bias_range=(-1000, 1000),
              scales=(0.05, 0.01, 0.37 * (ic * k * k / 576.0) ** 0.5 + 0.4))
@@ -236,7 +249,7 @@ def test_conv_umma_split_k_matches_oracle(ops, oracle, case, monkeypatch):
 
 
 @pytest.mark.parametrize("mode", [None, "QFUSE_ADD_RELU"])
-def test_conv_umma_split_k_last_wave_equals_unsplit(ops, mode, monkeypatch):
+def test_conv_umma_split_k_last_wave_equals_unsplit(ops, mode, tune):
     """A ResNet stage-4 shape at batch 256 (196 tiles on 148 SMs: 148 whole tiles, 48 tiles
     in three parts each), with and without the fused residual step, against the same kernel
     without the split (itself checked against the oracle on smaller shapes)."""
@@ -258,7 +271,7 @@ def test_conv_umma_split_k_last_wave_equals_unsplit(ops, mode, monkeypatch):
 
     whole = run()
     assert (np.abs(whole.astype(int)) < 127).mean() > 0.3
-    monkeypatch.setenv("MB200_CONV_SPLITK", "3")
+    tune("conv_splitk", 3)
     for _ in range(2):
         assert (run() == whole).all()
     assert ops.device_status() == 0
@@ -276,10 +289,10 @@ PAIR_CASES = [
 
 
 @pytest.mark.parametrize("case", PAIR_CASES, ids=[c[0] for c in PAIR_CASES])
-def test_conv_pair_of_sms_matches_oracle(ops, oracle, case, monkeypatch):
+def test_conv_pair_of_sms_matches_oracle(ops, oracle, case, tune):
     """256 x 256 tiles computed by two CTAs on two SMs (tcgen05 cta_group::2)."""
     name, n, ic, oc, h, w, k, stride, pad, act = case
-    monkeypatch.setenv("MB200_CONV_PAIR", "1")
+    tune("conv_pair", 1)
     c = dict(name="pair_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=stride, pad=pad,
              groups=1, act=act, range=(-128, 127), bias_range=(-1000, 1000),
              scales=(0.05, 0.01, 0.37 * (ic * k * k / 576.0) ** 0.5 + 0.4))
@@ -305,13 +318,13 @@ DW_CASES = [
 @pytest.mark.parametrize("form", ["one", "2", "4"])
 @pytest.mark.parametrize("case", [DW_CASES[1], DW_CASES[4], DW_CASES[5]],
                          ids=["c64_s2", "odd_hw_nopad", "odd_hw_s2_pad2"])
-def test_depthwise_kernel_forms(ops, oracle, case, form, monkeypatch):
+def test_depthwise_kernel_forms(ops, oracle, case, form, tune):
     """Every form of the depthwise kernel at both strides, chosen by its tuning variable: one
     output per thread (it also serves the fused residual step), two and four outputs."""
     if form == "one":
-        monkeypatch.setenv("MB200_DW_ONE_OUTPUT", "1")
+        tune("dw_one_output", 1)
     else:
-        monkeypatch.setenv("MB200_DW_OUT", form)
+        tune("dw_out", int(form))
     name, n, ch, h, w, stride, pad, act, per_channel = case
     c = dict(name="dw_" + name, n=n, ic=ch, oc=ch, h=h, w=w, k=3, stride=stride, pad=pad,
              groups=ch, act=act, range=(-128, 127), bias_range=(-1000, 1000),
@@ -364,12 +377,12 @@ FUSED_CASES = [
 @pytest.mark.parametrize("mode", ["QADD", "QFUSE_ADD_RELU"])
 @pytest.mark.parametrize("case", FUSED_CASES, ids=[c[0] for c in FUSED_CASES])
 def test_conv_with_fused_residual_step_matches_two_oracle_kernels(ops, oracle, case, mode,
-                                                                  monkeypatch):
+                                                                  tune):
     """ConvBias + QADD / QFUSE_ADD_RELU in one launch == the reference's two kernels run one
     after the other (ConvBias to int8 at its own scale, then ElemwiseMultiType)."""
     name, n, ic, oc, h, w, k, stride, pad, algo = case
     if name == "umma_256_wide":
-        monkeypatch.setenv("MB200_CONV_BN", "256")
+        tune("conv_bn", 256)
     groups = ic if name == "direct_dw" else 1
     c = dict(name="fused_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=stride, pad=pad,
              groups=groups, act="IDENTITY", range=(-128, 127), bias_range=(-1000, 1000),

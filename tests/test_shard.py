@@ -15,7 +15,7 @@ sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "t
 import numpy as np
 from megcc_b200 import shard, zoo
 from oracle import oracle as O
-import netwalk
+from oracle import netwalk
 g = shard.Group("gloo")
 spec = zoo.resnet18(hw=32, classes=16)
 x = np.random.default_rng(5).integers(-128, 128, (5, 3, 32, 32), dtype=np.int8)
