@@ -245,6 +245,104 @@ MB200_API int mb200_relayout_nchw_to_nhwc_s8(
 MB200_API int mb200_relayout_nhwc_to_nchw_s8(
         const int8_t* src, int8_t* dst, int n, int c, int h, int w, void* stream);
 
+/* ======================================================================================
+ * fp32 path (the detector configuration and the fp32 MatrixMul sweep). NHWC fp32 tensors,
+ * 4-byte aligned at least; the vector and tensor-core paths want 16 bytes and fall back to
+ * scalar kernels otherwise. Results agree with the reference's x86 kernels within 1e-4
+ * relative / 1e-5 absolute (fp32 sums in a different order), not bit for bit.
+ * ====================================================================================== */
+
+/* nonlineMode of an fp32 ConvBias. The reference's fp32 ConvBias kernels take IDENTITY / RELU /
+ * SIGMOID / H_SWISH (compiler/lib/KernelGen/GeneralIntrinsic/ConvKernel/Fp32Im2col.cpp:130-134);
+ * SILU is the Elemwise kernel that follows a ConvBias in a YOLOX-style graph
+ * (BareMetal/ElemwiseKernel.cpp:52-53), folded into the epilogue here. */
+enum { MB200_F32_IDENTITY = 0, MB200_F32_RELU = 1, MB200_F32_H_SWISH = 2, MB200_F32_SIGMOID = 3,
+       MB200_F32_SILU = 4 };
+/* Elemwise modes (compiler/lib/KernelGen/BareMetal/ElemwiseKernel.cpp:20-120); unary below 16 */
+enum { MB200_ELEM_RELU = 0, MB200_ELEM_SIGMOID = 1, MB200_ELEM_SILU = 2, MB200_ELEM_H_SWISH = 3,
+       MB200_ELEM_EXP = 4, MB200_ELEM_ADD = 16, MB200_ELEM_SUB = 17, MB200_ELEM_MUL = 18,
+       MB200_ELEM_MAX = 19, MB200_ELEM_FUSE_ADD_RELU = 20 };
+
+typedef struct mb200_conv_f32_param {
+    int n, ic, ih, iw;
+    int oc, kh, kw;
+    int stride_h, stride_w, pad_h, pad_w;
+    int groups;  /* 1 = DENSE */
+    int nonline; /* MB200_F32_* */
+} mb200_conv_f32_param;
+
+/* ---- ConvBias fp32 (replaces GI_kernel_conv2d_im2col_<k>x<k>_NCHW_DENSE_..._f32,
+ * compiler/lib/KernelGen/GeneralIntrinsic/ConvKernel/Fp32Im2col.cpp:88-120, body :198-217).
+ * The Init step (mb200_conv_f32_pack_filter) turns the OIHW filter into the K-major form
+ * [OC][KH][KW][ICpg] followed, for dense filters whose channel count fills whole TMA rows (16
+ * or a multiple of 32), by its two tf32 planes for the tensor cores. The ConvBias itself needs
+ * mb200_conv_f32_workspace_bytes(p) bytes of 256-byte aligned device scratch (the tf32 planes
+ * of the activation; 0 when the general kernel runs).
+ *   bias   [OC] floats or NULL
+ *   z      optional NHWC tensor of the output's shape added AFTER the activation (the shortcut
+ *          of a bottleneck block: an Elemwise ADD folded into the epilogue), or NULL
+ *   dst_pitch  floats between consecutive output pixels; 0 = oc. A larger pitch lets the
+ *          ConvBias write its channel slice of a wider buffer (a Concat without a copy).
+ *   algo   MB200_ALGO_AUTO / MB200_ALGO_DIRECT (CUDA cores) / MB200_ALGO_UMMA (tensor cores) */
+MB200_API size_t mb200_conv_f32_packed_filter_bytes(const mb200_conv_f32_param* p);
+MB200_API int mb200_conv_f32_pack_filter(
+        const mb200_conv_f32_param* p, const float* flt_oihw, float* flt_packed, void* stream);
+MB200_API size_t mb200_conv_f32_workspace_bytes(const mb200_conv_f32_param* p);
+MB200_API int mb200_conv_bias_f32_nhwc(
+        const mb200_conv_f32_param* p, const float* src, const float* flt_packed,
+        const float* bias, const float* z, float* dst, long long dst_pitch, void* workspace,
+        size_t workspace_bytes, int algo, void* stream);
+
+/* ---- MatrixMul fp32, C[M][N] = A[M][K] * B[K][N], row-major (replaces
+ * GI_kernel_fp32_matmul_4x12_nn, compiler/lib/KernelGen/GeneralIntrinsic/MatMulKernel/
+ * Fp32MatMulM4N12.cpp:8-160). B is prepared once by mb200_matmul_f32_pack_b into
+ * mb200_matmul_f32_packed_b_bytes(k, n) bytes; the product needs
+ * mb200_matmul_f32_workspace_bytes(m, k) bytes of scratch. Tensor cores (three tf32 passes)
+ * when k % 32 == 0 (or k == 16) and A holds at least 128 KiB. */
+MB200_API size_t mb200_matmul_f32_packed_b_bytes(int k, int n);
+MB200_API int mb200_matmul_f32_pack_b(int k, int n, const float* b, float* b_packed, void* stream);
+MB200_API size_t mb200_matmul_f32_workspace_bytes(int m, int k);
+MB200_API int mb200_matmul_f32(
+        int m, int n, int k, const float* a, const float* b_packed, float* c, void* workspace,
+        size_t workspace_bytes, void* stream);
+
+/* ---- Elemwise fp32, same-shape operands (b ignored for unary modes) ---- */
+MB200_API int mb200_elemwise_f32(
+        int mode, const float* a, const float* b, float* dst, size_t nr_elem, void* stream);
+
+/* ---- Concat along channels of NHWC tensors with the same pixel count (kernel_concat_*,
+ * compiler/lib/KernelGen/BareMetal/Concat.cpp:23-78); at most 8 inputs ---- */
+MB200_API int mb200_concat_f32_nhwc(
+        const float* const* srcs_host_array, const int* channels_host_array, int nr_inputs,
+        float* dst, size_t pixels, void* stream);
+
+/* ---- Resize NEAREST (kernel_resize_linear_NCHW_NEAREST_f32: ih = min((int)(oh / scale),
+ * IH - 1), compiler/lib/KernelGen/Common/Resize.h:155-156), NHWC ---- */
+MB200_API int mb200_resize_nearest_f32_nhwc(
+        const float* src, float* dst, int n, int c, int ih, int iw, int oh, int ow, void* stream);
+
+/* ---- Pooling fp32 (kernel_pooling_<MODE>_NCHW_..._f32f32,
+ * compiler/lib/KernelGen/BareMetal/Pooling.cpp:166-273), NHWC, modes as MB200_POOL_* ---- */
+MB200_API int mb200_pooling_f32_nhwc(
+        const float* src, float* dst, int mode, int n, int c, int ih, int iw, int window_h,
+        int window_w, int stride_h, int stride_w, int pad_h, int pad_w, void* stream);
+
+/* ---- Focus stem: the four stride-2 slices of an NCHW image concatenated along channels in
+ * the order (even rows, even cols), (odd, even), (even, odd), (odd, odd), written as an NHWC
+ * tensor [N][H/2][W/2][c_out] with c_out >= 4 * c (extra channels zero, so that the first
+ * ConvBias reads whole TMA rows). In the reference these are four Subtensor views turned into
+ * zero-copy MemForward instructions (compiler/lib/Dialect/Kernel/Transforms/
+ * MemoryForwarding.cpp:36-85, runtime/src/vm/memforward.c:41-51) feeding a Concat. ---- */
+MB200_API int mb200_focus_f32(
+        const float* src_nchw, float* dst_nhwc, int n, int c, int h, int w, int c_out,
+        void* stream);
+
+/* ---- model-boundary layout transforms, fp32 ---- */
+MB200_API int mb200_relayout_nchw_to_nhwc_f32(
+        const float* src, float* dst, int n, int c, int h, int w, void* stream);
+MB200_API int mb200_relayout_nhwc_to_nchw_f32(
+        const float* src, float* dst, int n, int c, int h, int w, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

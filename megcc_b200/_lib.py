@@ -15,6 +15,13 @@ class ConvParam(C.Structure):
         ("src_scale", C.c_float), ("flt_scale", C.c_float), ("dst_scale", C.c_float)]
 
 
+class ConvF32Param(C.Structure):
+    """Mirror of ``mb200_conv_f32_param``."""
+    _fields_ = [(k, C.c_int) for k in (
+        "n", "ic", "ih", "iw", "oc", "kh", "kw", "stride_h", "stride_w", "pad_h", "pad_w",
+        "groups", "nonline")]
+
+
 class ConvFuse(C.Structure):
     """Mirror of ``mb200_conv_fuse``."""
     _fields_ = [("z", C.c_void_p), ("mode", C.c_int), ("z_scale", C.c_float),
@@ -65,6 +72,24 @@ SIGNATURES = {
     "mb200_typecvt_qs32_qs8": (C.c_int, [_P, _P, C.c_size_t, C.c_float, C.c_float, _P]),
     "mb200_relayout_nchw_to_nhwc_s8": (C.c_int, [_P, _P] + [C.c_int] * 4 + [_P]),
     "mb200_relayout_nhwc_to_nchw_s8": (C.c_int, [_P, _P] + [C.c_int] * 4 + [_P]),
+    # fp32 path
+    "mb200_conv_f32_packed_filter_bytes": (C.c_size_t, [C.POINTER(ConvF32Param)]),
+    "mb200_conv_f32_pack_filter": (C.c_int, [C.POINTER(ConvF32Param), _P, _P, _P]),
+    "mb200_conv_f32_workspace_bytes": (C.c_size_t, [C.POINTER(ConvF32Param)]),
+    "mb200_conv_bias_f32_nhwc": (C.c_int, [C.POINTER(ConvF32Param), _P, _P, _P, _P, _P,
+                                           C.c_longlong, _P, C.c_size_t, C.c_int, _P]),
+    "mb200_matmul_f32_packed_b_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "mb200_matmul_f32_pack_b": (C.c_int, [C.c_int, C.c_int, _P, _P, _P]),
+    "mb200_matmul_f32_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "mb200_matmul_f32": (C.c_int, [C.c_int, C.c_int, C.c_int, _P, _P, _P, _P, C.c_size_t, _P]),
+    "mb200_elemwise_f32": (C.c_int, [C.c_int, _P, _P, _P, C.c_size_t, _P]),
+    "mb200_concat_f32_nhwc": (C.c_int, [C.POINTER(_P), C.POINTER(C.c_int), C.c_int, _P,
+                                        C.c_size_t, _P]),
+    "mb200_resize_nearest_f32_nhwc": (C.c_int, [_P, _P] + [C.c_int] * 6 + [_P]),
+    "mb200_pooling_f32_nhwc": (C.c_int, [_P, _P] + [C.c_int] * 11 + [_P]),
+    "mb200_focus_f32": (C.c_int, [_P, _P] + [C.c_int] * 5 + [_P]),
+    "mb200_relayout_nchw_to_nhwc_f32": (C.c_int, [_P, _P] + [C.c_int] * 4 + [_P]),
+    "mb200_relayout_nhwc_to_nchw_f32": (C.c_int, [_P, _P] + [C.c_int] * 4 + [_P]),
 }
 
 

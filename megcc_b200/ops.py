@@ -168,3 +168,122 @@ def device_status():
     s = C.c_int(0)
     check(lib().mb200_device_status(_stream(), C.byref(s)))
     return s.value
+
+
+# ----------------------------------------------------------------------------------------
+# fp32 path (NHWC float32 device tensors)
+# ----------------------------------------------------------------------------------------
+F32_ACT = {"IDENTITY": 0, "RELU": 1, "H_SWISH": 2, "SIGMOID": 3, "SILU": 4}
+ELEM = {"RELU": 0, "SIGMOID": 1, "SILU": 2, "H_SWISH": 3, "EXP": 4, "ADD": 16, "SUB": 17,
+        "MUL": 18, "MAX": 19, "FUSE_ADD_RELU": 20}
+
+
+def conv_f32_param(n, ic, ih, iw, oc, kh, kw, stride, pad, groups=1, act="IDENTITY"):
+    from ._lib import ConvF32Param
+    p = ConvF32Param()
+    p.n, p.ic, p.ih, p.iw, p.oc, p.kh, p.kw = n, ic, ih, iw, oc, kh, kw
+    p.stride_h = p.stride_w = stride
+    p.pad_h = p.pad_w = pad
+    p.groups = groups
+    p.nonline = F32_ACT[act]
+    return p
+
+
+def _scratch(nbytes, device):
+    """256-byte aligned device scratch of at least nbytes (None when nbytes == 0)."""
+    if nbytes == 0:
+        return None, None
+    buf = torch.empty(nbytes + 256, dtype=torch.int8, device=device)
+    return buf, buf.data_ptr() + (-buf.data_ptr()) % 256
+
+
+def pack_filter_f32(p, flt_oihw):
+    nbytes = lib().mb200_conv_f32_packed_filter_bytes(C.byref(p))
+    packed = torch.empty(nbytes // 4, dtype=torch.float32, device=flt_oihw.device)
+    check(lib().mb200_conv_f32_pack_filter(C.byref(p), _ptr(flt_oihw), _ptr(packed), _stream()))
+    return packed
+
+
+def conv_bias_f32_nhwc(p, src, flt_packed, bias=None, z=None, dst=None, dst_pitch=0,
+                       algo="auto"):
+    oh = (p.ih + 2 * p.pad_h - p.kh) // p.stride_h + 1
+    ow = (p.iw + 2 * p.pad_w - p.kw) // p.stride_w + 1
+    if dst is None:
+        dst = torch.empty((p.n, oh, ow, p.oc), dtype=torch.float32, device=src.device)
+    nbytes = lib().mb200_conv_f32_workspace_bytes(C.byref(p))
+    keep, ws = _scratch(nbytes, src.device)
+    check(lib().mb200_conv_bias_f32_nhwc(
+        C.byref(p), _ptr(src), _ptr(flt_packed), _ptr(bias), _ptr(z), _ptr(dst), dst_pitch,
+        None if ws is None else C.c_void_p(ws), nbytes, ALGO[algo], _stream()))
+    torch.cuda.current_stream().synchronize()  # the scratch must outlive the kernels
+    return dst
+
+
+def matmul_f32(a, b):
+    """C = A[M, K] @ B[K, N] (fp32 device tensors) through pack + product."""
+    m, k = a.shape
+    n = b.shape[1]
+    packed = torch.empty(lib().mb200_matmul_f32_packed_b_bytes(k, n) // 4, dtype=torch.float32,
+                         device=a.device)
+    check(lib().mb200_matmul_f32_pack_b(k, n, _ptr(b), _ptr(packed), _stream()))
+    c = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    nbytes = lib().mb200_matmul_f32_workspace_bytes(m, k)
+    keep, ws = _scratch(nbytes, a.device)
+    check(lib().mb200_matmul_f32(m, n, k, _ptr(a), _ptr(packed), _ptr(c),
+                                 None if ws is None else C.c_void_p(ws), nbytes, _stream()))
+    torch.cuda.current_stream().synchronize()
+    return c
+
+
+def elemwise_f32(mode, a, b=None):
+    dst = torch.empty_like(a)
+    check(lib().mb200_elemwise_f32(ELEM[mode], _ptr(a), _ptr(b), _ptr(dst), a.numel(), _stream()))
+    return dst
+
+
+def concat_f32_nhwc(tensors):
+    n, h, w = tensors[0].shape[:3]
+    chans = [t.shape[3] for t in tensors]
+    dst = torch.empty((n, h, w, sum(chans)), dtype=torch.float32, device=tensors[0].device)
+    ptrs = (C.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+    cs = (C.c_int * len(tensors))(*chans)
+    check(lib().mb200_concat_f32_nhwc(ptrs, cs, len(tensors), _ptr(dst), n * h * w, _stream()))
+    return dst
+
+
+def resize_nearest_f32_nhwc(src, oh, ow):
+    n, ih, iw, c = src.shape
+    dst = torch.empty((n, oh, ow, c), dtype=torch.float32, device=src.device)
+    check(lib().mb200_resize_nearest_f32_nhwc(_ptr(src), _ptr(dst), n, c, ih, iw, oh, ow,
+                                              _stream()))
+    return dst
+
+
+def pooling_f32_nhwc(src, mode, window, stride, pad):
+    n, ih, iw, c = src.shape
+    oh, ow = (ih + 2 * pad - window) // stride + 1, (iw + 2 * pad - window) // stride + 1
+    dst = torch.empty((n, oh, ow, c), dtype=torch.float32, device=src.device)
+    check(lib().mb200_pooling_f32_nhwc(_ptr(src), _ptr(dst), POOL[mode], n, c, ih, iw, window,
+                                       window, stride, stride, pad, pad, _stream()))
+    return dst
+
+
+def focus_f32(src_nchw, c_out):
+    n, c, h, w = src_nchw.shape
+    dst = torch.empty((n, h // 2, w // 2, c_out), dtype=torch.float32, device=src_nchw.device)
+    check(lib().mb200_focus_f32(_ptr(src_nchw), _ptr(dst), n, c, h, w, c_out, _stream()))
+    return dst
+
+
+def nchw_to_nhwc_f32(x):
+    n, c, h, w = x.shape
+    y = torch.empty((n, h, w, c), dtype=torch.float32, device=x.device)
+    check(lib().mb200_relayout_nchw_to_nhwc_f32(_ptr(x), _ptr(y), n, c, h, w, _stream()))
+    return y
+
+
+def nhwc_to_nchw_f32(x):
+    n, h, w, c = x.shape
+    y = torch.empty((n, c, h, w), dtype=torch.float32, device=x.device)
+    check(lib().mb200_relayout_nhwc_to_nchw_f32(_ptr(x), _ptr(y), n, c, h, w, _stream()))
+    return y

@@ -254,3 +254,171 @@ void oracle_matmul_s8_s32(
         }
     }
 }
+
+/* ==========================================================================================
+ * fp32 path. Parity status: pinned within tolerance, not bit for bit: the functions below
+ * are compared with the reference's own fp32 kernels (GI im2col ConvBias, GI 4x12 MatrixMul,
+ * GI / BareMetal Elemwise, BareMetal Pooling / Resize / Concat) in
+ * tests/test_oracle_vs_reference.py at 1e-5 relative; fp32 sums in a different order cannot
+ * agree to the last bit. The GPU is then held to 1e-4 relative / 1e-5 absolute against these.
+ * ========================================================================================== */
+enum { F32_IDENTITY = 0, F32_RELU = 1, F32_H_SWISH = 2, F32_SIGMOID = 3, F32_SILU = 4 };
+
+/* BareMetal/Activation.cpp:9-42 (RELU, H_SWISH, SIGMOID) and
+ * BareMetal/ElemwiseKernel.cpp:52-53 (SILU: val / (1 + expf(-val))) */
+static inline float act_f32(int act, float x) {
+    switch (act) {
+        case F32_RELU:
+            return x > 0 ? x : 0;
+        case F32_H_SWISH: {
+            float t = x + 3;
+            t = t > 0.f ? t : 0.f;
+            t = t > 6.f ? 6.f : t;
+            return x * t * (1.f / 6.f);
+        }
+        case F32_SIGMOID:
+            return 1.f / (1.f + expf(-x));
+        case F32_SILU:
+            return x / (1.f + expf(-x));
+        default:
+            return x;
+    }
+}
+
+/* fp32 ConvBias, NCHW / OIHW ([G][OCpg][ICpg][KH][KW] when grouped), then the activation,
+ * then an optional tensor z of the output's shape added (the bottleneck shortcut). The sum
+ * runs in double and is rounded once: the tightest statement of "the fp32 result" that both
+ * the reference's SIMD GEMM order and the GPU's tensor-core order are compared with. */
+void oracle_conv_bias_f32(
+        const float* src, const float* flt, const float* bias, const float* z, float* dst,
+        int n, int ic, int ih, int iw, int oc, int kh, int kw, int sh, int sw, int ph, int pw,
+        int groups, int act) {
+    const int oh = out_extent(ih, kh, sh, ph, 1), ow = out_extent(iw, kw, sw, pw, 1);
+    const int icpg = ic / groups, ocpg = oc / groups;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int b = 0; b < n; ++b) {
+        for (int o = 0; o < oc; ++o) {
+            const int g = o / ocpg;
+            double* a = (double*)calloc((size_t)oh * ow, sizeof(double));
+            for (int c = 0; c < icpg; ++c) {
+                const float* s = src + ((size_t)b * ic + g * icpg + c) * ih * iw;
+                const float* f = flt + ((size_t)o * icpg + c) * kh * kw;
+                for (int fy = 0; fy < kh; ++fy)
+                    for (int fx = 0; fx < kw; ++fx) {
+                        const double w = f[fy * kw + fx];
+                        for (int y = 0; y < oh; ++y) {
+                            const int iy = y * sh + fy - ph;
+                            if (iy < 0 || iy >= ih)
+                                continue;
+                            for (int x = 0; x < ow; ++x) {
+                                const int ix = x * sw + fx - pw;
+                                if (ix < 0 || ix >= iw)
+                                    continue;
+                                a[(size_t)y * ow + x] += (double)s[(size_t)iy * iw + ix] * w;
+                            }
+                        }
+                    }
+            }
+            float* d = dst + ((size_t)b * oc + o) * oh * ow;
+            const float* zz = z ? z + ((size_t)b * oc + o) * oh * ow : NULL;
+            for (int i = 0; i < oh * ow; ++i) {
+                float r = act_f32(act, (float)(a[i] + (bias ? (double)bias[o] : 0.0)));
+                if (zz)
+                    r += zz[i];
+                d[i] = r;
+            }
+            free(a);
+        }
+    }
+}
+
+/* C[M][N] = A[M][K] * B[K][N], row-major; double sum, one rounding */
+void oracle_matmul_f32(const float* a, const float* b, float* c, int m, int n, int k) {
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < m; ++i) {
+        double* row = (double*)calloc((size_t)n, sizeof(double));
+        for (int kk = 0; kk < k; ++kk) {
+            const double av = a[(size_t)i * k + kk];
+            const float* br = b + (size_t)kk * n;
+            for (int j = 0; j < n; ++j)
+                row[j] += av * (double)br[j];
+        }
+        for (int j = 0; j < n; ++j)
+            c[(size_t)i * n + j] = (float)row[j];
+        free(row);
+    }
+}
+
+/* Elemwise modes of BareMetal/ElemwiseKernel.cpp:20-120 (codes as in include/megcc_b200.h) */
+void oracle_elemwise_f32(int mode, const float* a, const float* b, float* dst, size_t n) {
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) {
+        const float x = a[i];
+        float r;
+        switch (mode) {
+            case 0: r = x > 0 ? x : 0; break;
+            case 1: r = 1.f / (1.f + expf(-x)); break;
+            case 2: r = x / (1.f + expf(-x)); break;
+            case 3: r = act_f32(F32_H_SWISH, x); break;
+            case 4: r = expf(x); break;
+            case 16: r = x + b[i]; break;
+            case 17: r = x - b[i]; break;
+            case 18: r = x * b[i]; break;
+            case 19: r = x > b[i] ? x : b[i]; break;
+            case 20: r = x + b[i]; r = r > 0 ? r : 0; break;
+            default: r = x; break;
+        }
+        dst[i] = r;
+    }
+}
+
+/* fp32 pooling, NCHW (BareMetal/Pooling.cpp:66-150,166-273): MAX starts from -FLT_MAX and
+ * skips padding; AVERAGE divides by the window, AVERAGE_COUNT_EXCLUDE_PADDING by the taps */
+void oracle_pooling_f32(
+        const float* src, float* dst, int mode, int n, int c, int ih, int iw, int wh, int ww,
+        int sh, int sw, int ph, int pw) {
+    const int oh = (ih + 2 * ph - wh) / sh + 1, ow = (iw + 2 * pw - ww) / sw + 1;
+#pragma omp parallel for schedule(static)
+    for (int bc = 0; bc < n * c; ++bc) {
+        const float* s = src + (size_t)bc * ih * iw;
+        float* d = dst + (size_t)bc * oh * ow;
+        for (int y = 0; y < oh; ++y)
+            for (int x = 0; x < ow; ++x) {
+                float mx = -3.402823466e38f, sum = 0.f;
+                int count = 0;
+                for (int fy = 0; fy < wh; ++fy) {
+                    const int iy = y * sh + fy - ph;
+                    if (iy < 0 || iy >= ih)
+                        continue;
+                    for (int fx = 0; fx < ww; ++fx) {
+                        const int ix = x * sw + fx - pw;
+                        if (ix < 0 || ix >= iw)
+                            continue;
+                        const float v = s[(size_t)iy * iw + ix];
+                        mx = v > mx ? v : mx;
+                        sum += v;
+                        ++count;
+                    }
+                }
+                d[(size_t)y * ow + x] =
+                        mode == 0 ? mx : sum / (mode == 1 ? (float)(wh * ww) : (float)count);
+            }
+    }
+}
+
+/* Resize NEAREST, NCHW (compiler/lib/KernelGen/Common/Resize.h:155-156 with
+ * scale = (float)out / in as BareMetal/Resize.cpp computes it) */
+void oracle_resize_nearest_f32(
+        const float* src, float* dst, int n, int c, int ih, int iw, int oh, int ow) {
+    const float scale_h = (float)oh / ih, scale_w = (float)ow / iw;
+    for (int bc = 0; bc < n * c; ++bc)
+        for (int y = 0; y < oh; ++y) {
+            int sy = (int)(y / scale_h);
+            sy = sy < ih - 1 ? sy : ih - 1;
+            for (int x = 0; x < ow; ++x) {
+                int sx = (int)(x / scale_w);
+                sx = sx < iw - 1 ? sx : iw - 1;
+                dst[((size_t)bc * oh + y) * ow + x] = src[((size_t)bc * ih + sy) * iw + sx];
+            }
+        }
+}

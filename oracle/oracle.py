@@ -72,6 +72,16 @@ def lib():
         L.oracle_typecvt_qs32_qs8.argtypes = [_i32p, _i8p, C.c_size_t, C.c_float, C.c_float]
         L.oracle_matmul_s8_s32.restype = None
         L.oracle_matmul_s8_s32.argtypes = [_i8p, _i8p, _i32p, C.c_int, C.c_int, C.c_int]
+        L.oracle_conv_bias_f32.restype = None
+        L.oracle_conv_bias_f32.argtypes = [_f32p, _f32p, C.c_void_p, C.c_void_p, _f32p] + [C.c_int] * 13
+        L.oracle_matmul_f32.restype = None
+        L.oracle_matmul_f32.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
+        L.oracle_elemwise_f32.restype = None
+        L.oracle_elemwise_f32.argtypes = [C.c_int, _f32p, C.c_void_p, _f32p, C.c_size_t]
+        L.oracle_pooling_f32.restype = None
+        L.oracle_pooling_f32.argtypes = [_f32p, _f32p] + [C.c_int] * 11
+        L.oracle_resize_nearest_f32.restype = None
+        L.oracle_resize_nearest_f32.argtypes = [_f32p, _f32p] + [C.c_int] * 6
         _lib = L
     return _lib
 
@@ -150,6 +160,83 @@ def matmul_s8_s32(a, b):
     c = np.empty((m, n), np.int32)
     lib().oracle_matmul_s8_s32(a, b, c, m, n, k)
     return c
+
+
+# ----------------------------------------------------------------------------------------
+# fp32 path (restated)
+# ----------------------------------------------------------------------------------------
+F32_ACT = {"IDENTITY": 0, "RELU": 1, "H_SWISH": 2, "SIGMOID": 3, "SILU": 4}
+ELEM = {"RELU": 0, "SIGMOID": 1, "SILU": 2, "H_SWISH": 3, "EXP": 4, "ADD": 16, "SUB": 17,
+        "MUL": 18, "MAX": 19, "FUSE_ADD_RELU": 20}
+
+
+def conv_bias_f32(src, flt, bias, stride, pad, act="IDENTITY", groups=1, z=None):
+    """fp32 ConvBias (NCHW, OIHW), activation, then optionally + z."""
+    src, flt = _c(src, np.float32), _c(flt, np.float32)
+    n, ic, ih, iw = src.shape
+    kh, kw = flt.shape[-2:]
+    oc = flt.shape[0] if flt.ndim == 4 else flt.shape[0] * flt.shape[1]
+    oh, ow = out_extent(ih, kh, stride, pad), out_extent(iw, kw, stride, pad)
+    dst = np.empty((n, oc, oh, ow), np.float32)
+    b = None if bias is None else _c(np.asarray(bias).reshape(-1), np.float32)
+    zz = None if z is None else _c(z, np.float32)
+    lib().oracle_conv_bias_f32(src, flt, None if b is None else b.ctypes.data,
+                               None if zz is None else zz.ctypes.data, dst, n, ic, ih, iw, oc,
+                               kh, kw, stride, stride, pad, pad, groups, F32_ACT[act])
+    return dst
+
+
+def matmul_f32(a, b):
+    a, b = _c(a, np.float32), _c(b, np.float32)
+    m, k = a.shape
+    k2, n = b.shape
+    assert k == k2
+    c = np.empty((m, n), np.float32)
+    lib().oracle_matmul_f32(a, b, c, m, n, k)
+    return c
+
+
+def elemwise_f32(mode, a, b=None):
+    a = _c(a, np.float32)
+    bb = None if b is None else _c(b, np.float32)
+    dst = np.empty(a.shape, np.float32)
+    lib().oracle_elemwise_f32(ELEM[mode], a, None if bb is None else bb.ctypes.data, dst, a.size)
+    return dst
+
+
+def pooling_f32(src, mode, window, stride, pad):
+    src = _c(src, np.float32)
+    n, c, ih, iw = src.shape
+    oh, ow = (ih + 2 * pad - window) // stride + 1, (iw + 2 * pad - window) // stride + 1
+    dst = np.empty((n, c, oh, ow), np.float32)
+    lib().oracle_pooling_f32(src, dst, POOL[mode], n, c, ih, iw, window, window, stride, stride,
+                             pad, pad)
+    return dst
+
+
+def resize_nearest_f32(src, oh, ow):
+    src = _c(src, np.float32)
+    n, c, ih, iw = src.shape
+    dst = np.empty((n, c, oh, ow), np.float32)
+    lib().oracle_resize_nearest_f32(src, dst, n, c, ih, iw, oh, ow)
+    return dst
+
+
+def concat_f32(tensors):
+    """Concat along channels, NCHW (BareMetal/Concat.cpp:23-78 with axis 1)."""
+    return np.concatenate([_c(t, np.float32) for t in tensors], axis=1)
+
+
+def focus_f32(src, c_out=None):
+    """The Focus stem's four stride-2 slices concatenated along channels (optionally padded
+    with zero channels up to c_out)."""
+    x = _c(src, np.float32)
+    parts = [x[:, :, 0::2, 0::2], x[:, :, 1::2, 0::2], x[:, :, 0::2, 1::2], x[:, :, 1::2, 1::2]]
+    out = np.concatenate(parts, axis=1)
+    if c_out is not None and c_out > out.shape[1]:
+        pad = np.zeros((out.shape[0], c_out - out.shape[1]) + out.shape[2:], np.float32)
+        out = np.concatenate([out, pad], axis=1)
+    return np.ascontiguousarray(out)
 
 
 # ----------------------------------------------------------------------------------------
