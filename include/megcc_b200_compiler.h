@@ -54,7 +54,7 @@ MB200C_API int mb200c_add_matmul(
         mb200c_graph* g, const char* name, int src, int n, const int8_t* b, float b_scale,
         float dst_scale);
 
-/* mode: "MAX" | "AVERAGE" | "AVERAGE_COUNT_EXCLUDE_PADDING" */
+/* mode: "MAX" | "AVERAGE" | "AVERAGE_COUNT_EXCLUDE_PADDING"; qint8 or fp32 by its input */
 MB200C_API int mb200c_add_pooling(
         mb200c_graph* g, const char* name, int src, const char* mode, int window, int stride,
         int pad);
@@ -62,6 +62,34 @@ MB200C_API int mb200c_add_pooling(
 /* mode: "QADD" | "QFUSE_ADD_RELU" | "QMUL" | "QRELU" (b < 0 for QRELU) */
 MB200C_API int mb200c_add_qelemwise(
         mb200c_graph* g, const char* name, const char* mode, int a, int b, float dst_scale);
+
+/* ---- fp32 operators (the detector configuration). Tensors are fp32, model-visible layout
+ * NCHW, NHWC inside the model. ---- */
+MB200C_API int mb200c_add_input_f32(mb200c_graph* g, const char* name, int c, int h, int w);
+/* ConvBias fp32: flt OIHW / [G][OCpg][ICpg][KH][KW] floats, bias [OC] floats or NULL.
+ * nonline: "IDENTITY" | "RELU" | "SIGMOID" | "H_SWISH" (the reference's fp32 ConvBias modes,
+ * compiler/lib/KernelGen/GeneralIntrinsic/ConvKernel/Fp32Im2col.cpp:130-134) or "SILU" (the
+ * Elemwise SILU that follows a ConvBias in a YOLOX-style graph, folded in). z >= 0: a tensor
+ * of the output's shape added after the activation (Elemwise ADD folded in), else -1. */
+MB200C_API int mb200c_add_conv_f32(
+        mb200c_graph* g, const char* name, int src, int oc, int kh, int kw, int stride, int pad,
+        int groups, const char* nonline, const float* flt, const float* bias, int z);
+/* MatrixMul fp32: C[batch][n] = A[batch][K] x B[K][n]; src has h = w = 1 */
+MB200C_API int mb200c_add_matmul_f32(
+        mb200c_graph* g, const char* name, int src, int n, const float* b);
+/* Elemwise fp32, mode "RELU" | "SIGMOID" | "SILU" | "H_SWISH" | "EXP" (b = -1) or
+ * "ADD" | "SUB" | "MUL" | "MAX" | "FUSE_ADD_RELU" (same-shape b) */
+MB200C_API int mb200c_add_elemwise_f32(
+        mb200c_graph* g, const char* name, const char* mode, int a, int b);
+/* Concat along channels, 1..8 fp32 tensors of equal spatial extent */
+MB200C_API int mb200c_add_concat(mb200c_graph* g, const char* name, const int* srcs, int nr);
+/* Focus stem: the four stride-2 slices of the NCHW model input concatenated along channels
+ * (in the reference: Subtensor views forwarded without a copy,
+ * compiler/lib/Dialect/Kernel/Transforms/MemoryForwarding.cpp:36-85, plus a Concat); c_out >=
+ * 4 * c, the extra channels are zeros */
+MB200C_API int mb200c_add_focus(mb200c_graph* g, const char* name, int src, int c_out);
+/* Resize NEAREST to oh x ow */
+MB200C_API int mb200c_add_resize_nearest(mb200c_graph* g, const char* name, int src, int oh, int ow);
 
 MB200C_API int mb200c_mark_output(mb200c_graph* g, int tensor);
 

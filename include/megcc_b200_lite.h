@@ -171,6 +171,16 @@ LITE_API int LITE_get_tensor_device_type(const LiteTensor tensor, LiteDeviceType
  * The CUDA stream (cudaStream_t) all work of the network is issued on, for callers that
  * time or order their own work against it. */
 LITE_API int mb200_lite_stream(const LiteNetwork network, void** stream);
+/* Registers the function tables of a generated kernels.c (what load_kernel_init_function
+ * fills in the reference, compiler/lib/Target/TinyNN/KernelExporter.cpp:15-66) before a model
+ * is loaded: kernels[kernel_id] and init_kernels[init_id] then execute the model's Oprs as
+ * runtime/src/vm/op.c:161-163 and runtime/src/init.c:29-131 do. NULL entries, and ids beyond
+ * the tables, fall to the library's own implementation of the Opr's symbol; an Opr whose
+ * symbol the library does not know runs only through a registered entry. The function types
+ * are those of include/megcc_b200_runtime.h (void* here to keep this header free of it). */
+LITE_API int mb200_lite_set_kernel_tables(
+        LiteNetwork network, const void* kernels, int nr_kernels, const void* init_kernels,
+        int nr_init);
 /* Per-network switches. "use_graph" (default 1): replay the instruction list as one CUDA
  * graph; 0 issues the kernels one by one on every forward. "profile": as
  * mb200_lite_set_profile. New networks take their defaults from the environment once per

@@ -120,6 +120,9 @@ typedef struct RuntimeOpt {
     /* ---- additions ---- */
     void* stream;  /* cudaStream_t every kernel of the model is issued on */
     int device_id; /* CUDA ordinal */
+    /* the Opr being executed, for the runtime's own kernel implementations (one function
+     * serves every symbol there); generated stubs have their attributes baked in and ignore it */
+    const void* opr;
 } RuntimeOpt;
 
 static inline void* mb200_opt_stream(const RuntimeOpt* opt) {

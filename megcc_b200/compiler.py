@@ -19,6 +19,14 @@ SIGNATURES = {
     "mb200c_add_matmul": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int, _P, C.c_float, C.c_float]),
     "mb200c_add_pooling": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_char_p] + [C.c_int] * 3),
     "mb200c_add_qelemwise": (C.c_int, [_P, C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_float]),
+    "mb200c_add_input_f32": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int, C.c_int]),
+    "mb200c_add_conv_f32": (C.c_int, [_P, C.c_char_p] + [C.c_int] * 7 + [C.c_char_p, _P, _P,
+                                                                        C.c_int]),
+    "mb200c_add_matmul_f32": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int, _P]),
+    "mb200c_add_elemwise_f32": (C.c_int, [_P, C.c_char_p, C.c_char_p, C.c_int, C.c_int]),
+    "mb200c_add_concat": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_int), C.c_int]),
+    "mb200c_add_focus": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int]),
+    "mb200c_add_resize_nearest": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int, C.c_int]),
     "mb200c_mark_output": (C.c_int, [_P, C.c_int]),
     "mb200c_set_option": (C.c_int, [_P, C.c_char_p, C.c_int]),
     "mb200c_compile": (C.c_int, [_P, C.POINTER(C.c_int), C.c_int, C.POINTER(_P),
@@ -90,6 +98,39 @@ class Graph:
         b = np.ascontiguousarray(b, dtype=np.int8)
         return _check(lib().mb200c_add_matmul(self._g, name.encode(), src, b.shape[1],
                                               b.ctypes.data, b_scale, dst_scale))
+
+    # ---- fp32 operators ----
+    def input_f32(self, name, c, h, w):
+        return _check(lib().mb200c_add_input_f32(self._g, name.encode(), c, h, w))
+
+    def conv_f32(self, name, src, flt, bias, stride, pad, nonline="IDENTITY", groups=1, z=None):
+        flt = np.ascontiguousarray(flt, np.float32)
+        kh, kw = flt.shape[-2:]
+        oc = flt.shape[0] if flt.ndim == 4 else flt.shape[0] * flt.shape[1]
+        b = None if bias is None else np.ascontiguousarray(np.asarray(bias).reshape(-1),
+                                                           np.float32)
+        return _check(lib().mb200c_add_conv_f32(
+            self._g, name.encode(), src, oc, kh, kw, stride, pad, groups, nonline.encode(),
+            flt.ctypes.data, None if b is None else b.ctypes.data, -1 if z is None else z))
+
+    def matmul_f32(self, name, src, b):
+        b = np.ascontiguousarray(b, np.float32)
+        return _check(lib().mb200c_add_matmul_f32(self._g, name.encode(), src, b.shape[1],
+                                                  b.ctypes.data))
+
+    def elemwise_f32(self, name, mode, a, b=None):
+        return _check(lib().mb200c_add_elemwise_f32(self._g, name.encode(), mode.encode(), a,
+                                                    -1 if b is None else b))
+
+    def concat(self, name, srcs):
+        arr = (C.c_int * len(srcs))(*srcs)
+        return _check(lib().mb200c_add_concat(self._g, name.encode(), arr, len(srcs)))
+
+    def focus(self, name, src, c_out):
+        return _check(lib().mb200c_add_focus(self._g, name.encode(), src, c_out))
+
+    def resize_nearest(self, name, src, oh, ow):
+        return _check(lib().mb200c_add_resize_nearest(self._g, name.encode(), src, oh, ow))
 
     def pooling(self, name, src, mode, window, stride, pad):
         return _check(lib().mb200c_add_pooling(self._g, name.encode(), src, mode.encode(), window,

@@ -524,7 +524,7 @@ bool RelayoutQS8::IsAvailable(TContext* ctx) const {
     const std::string m = ctx->getAttrStr("relayout_mode");
     const CCOperand src = ctx->getAttrOprand("operand:0");
     return (m == "NCHW_NHWC" || m == "NHWC_NCHW") && src.shape.size() == 4 &&
-           (is_quant(src.dtype, 8) || src.dtype == "si8");
+           (is_quant(src.dtype, 8) || src.dtype == "si8" || src.dtype == "f32");
 }
 
 std::string RelayoutQS8::GetKernelSymbol(TContext* ctx) const {
@@ -538,13 +538,458 @@ ${prologue}
 TinyNNStatus ${signature} {
     const Tensor* src = inputs[0];
     return (TinyNNStatus)${fn}(
-            (const int8_t*)src->ptr, (int8_t*)outputs[0]->ptr, src->layout.dims[0],
+            (const ${ctype}*)src->ptr, (${ctype}*)outputs[0]->ptr, src->layout.dims[0],
             src->layout.dims[1], src->layout.dims[2], src->layout.dims[3], mb200_opt_stream(opt));
+}
+)"};
+    const bool f32 = ctx->getAttrOprand("operand:0").dtype == "f32";
+    s.set("prologue", GenStubPrologue())
+            .set("signature", GetKernelSignature(ctx))
+            .set("ctype", f32 ? "float" : "int8_t")
+            .set("fn", std::string(to_nhwc ? "mb200_relayout_nchw_to_nhwc_" : "mb200_relayout_nhwc_to_nchw_") +
+                               (f32 ? "f32" : "s8"));
+    return s.text;
+}
+
+// ==========================================================================================
+// fp32 path
+// ==========================================================================================
+namespace {
+
+bool all_f32(TContext* ctx) {
+    const int n = ctx->getAttrInt("nr_operands");
+    for (int i = 0; i < n; ++i) {
+        const CCOperand o = ctx->getAttrOprand("operand:" + std::to_string(i));
+        // an absent bias is an operand without a shape (Common/ConvKernel.h:10-21)
+        if (o.dtype != "f32" && !(o.shape.empty() && i == 2))
+            return false;
+    }
+    return true;
+}
+
+int f32_act_code(const std::string& m) {
+    return m == "RELU" ? 1 : m == "H_SWISH" ? 2 : m == "SIGMOID" ? 3 : m == "SILU" ? 4 : 0;
+}
+
+int elem_code(const std::string& m) {
+    static const char* names[] = {"RELU", "SIGMOID", "SILU", "H_SWISH", "EXP"};
+    for (int i = 0; i < 5; ++i)
+        if (m == names[i])
+            return i;
+    static const char* bin[] = {"ADD", "SUB", "MUL", "MAX", "FUSE_ADD_RELU"};
+    for (int i = 0; i < 5; ++i)
+        if (m == bin[i])
+            return 16 + i;
+    return -1;
+}
+
+// the C text that fills an mb200_conv_f32_param from the Tensors of a ConvBias
+const char* kConvF32ParamFn = R"(
+static void ${symbol}_param(Tensor** inputs, mb200_conv_f32_param* p) {
+    const Tensor* src = inputs[0];
+    p->n = src->layout.dims[0];
+    p->ic = src->layout.dims[1];
+    p->ih = src->layout.dims[2];
+    p->iw = src->layout.dims[3];
+    p->groups = ${dense} ? 1 : p->ic / ${icpg};
+    p->oc = ${oc};
+    p->kh = ${kh}; p->kw = ${kw};
+    p->stride_h = ${sh}; p->stride_w = ${sw};
+    p->pad_h = ${ph}; p->pad_w = ${pw};
+    p->nonline = ${nonline};
+}
+)";
+
+Subst conv_f32_common(TContext* ctx, const KernelFunc* self, const char* text) {
+    Subst s{text};
+    const CCOperand dst = last_operand(ctx);
+    s.set("prologue", GenStubPrologue())
+            .set("symbol", self->GetKernelSymbol(ctx))
+            .set("oc", (long long)dst.shape[1])
+            .set("kh", ctx->getAttrUInt("kernel_h"))
+            .set("kw", ctx->getAttrUInt("kernel_w"))
+            .set("sh", ctx->getAttrUInt("stride_h"))
+            .set("sw", ctx->getAttrUInt("stride_w"))
+            .set("ph", ctx->getAttrUInt("pad_h"))
+            .set("pw", ctx->getAttrUInt("pad_w"))
+            .set("dense", ctx->getAttrStr("sparse") == "DENSE" ? 1 : 0)
+            .set("icpg", ctx->getAttrStr("sparse") == "DENSE"
+                                 ? 1LL
+                                 : (long long)ctx->getAttrOprand("operand:1").shape[2])
+            .set("nonline", f32_act_code(nonline(ctx)));
+    return s;
+}
+
+}  // namespace
+
+bool ConvBiasF32::IsAvailable(TContext* ctx) const {
+    if (ctx->getAttrStr("format") != "NCHW" || ctx->getAttrStr("mode") != "CROSS_CORRELATION")
+        return false;
+    const int n = ctx->getAttrInt("nr_operands");
+    if (n < 4 || n > 5 || !all_f32(ctx))
+        return false;
+    if (ctx->getAttrUInt("dilate_h") != 1 || ctx->getAttrUInt("dilate_w") != 1)
+        return false;
+    const CCOperand src = ctx->getAttrOprand("operand:0");
+    const CCOperand dst = last_operand(ctx);
+    if (src.shape.size() != 4 || dst.shape.size() != 4)
+        return false;
+    const std::string sparse = ctx->getAttrStr("sparse");
+    if (sparse != "DENSE" && sparse != "GROUP")
+        return false;
+    const std::string act = nonline(ctx);
+    if (act != "IDENTITY" && act != "RELU" && act != "SIGMOID" && act != "H_SWISH" &&
+        act != "SILU")
+        return false;
+    if (has_bias(ctx) && !channel_broadcast_bias(ctx))
+        return false;
+    const std::string fm = fuse_mode(ctx);
+    if (n == 5) {
+        if (fm != "ADD" || ctx->getAttrOprand("operand:3").shape != dst.shape)
+            return false;
+    } else if (!fm.empty()) {
+        return false;
+    }
+    return true;
+}
+
+std::string ConvBiasF32::GetKernelSymbol(TContext* ctx) const {
+    if (!ctx)
+        return "cuda_sm100_conv2d_f32";
+    std::stringstream ss;
+    ss << "cuda_sm100_conv2d_" << ctx->getAttrUInt("kernel_h") << "x"
+       << ctx->getAttrUInt("kernel_w") << "_NHWC_" << ctx->getAttrStr("sparse") << "_p"
+       << ctx->getAttrUInt("pad_h") << "x" << ctx->getAttrUInt("pad_w") << "_s"
+       << ctx->getAttrUInt("stride_h") << "x" << ctx->getAttrUInt("stride_w") << "_d1x1_oc"
+       << last_operand(ctx).shape[1];
+    // the processed filter is a flat buffer, so a grouped filter's channels per group are
+    // spelled out ([G][OCpg][ICpg][KH][KW])
+    if (ctx->getAttrStr("sparse") == "GROUP")
+        ss << "_icpg" << ctx->getAttrOprand("operand:1").shape[2];
+    ss << "_f32";
+    if (has_bias(ctx))
+        ss << "_bias";
+    if (nonline(ctx) != "IDENTITY")
+        ss << "_" << nonline(ctx);
+    if (!fuse_mode(ctx).empty())
+        ss << "_z_" << fuse_mode(ctx);
+    return ss.str();
+}
+
+std::string ConvBiasF32::GetKernelBody(TContext* ctx) const {
+    std::string text = std::string("${prologue}") + kConvF32ParamFn + R"(
+/* dims are the logical NCHW extents; strides say the buffers are NHWC. The pixel pitch of
+ * the output (stride of W) may exceed its channel count: the output is then a channel slice
+ * of a wider buffer, which is how a Concat of ConvBias results needs no copy. */
+TinyNNStatus ${signature} {
+    const Tensor* src = inputs[0];
+    Tensor* dst = outputs[0];
+    mb200_conv_f32_param p;
+    ${symbol}_param(inputs, &p);
+    const float* bias = ${has_bias} ? (const float*)inputs[2]->ptr : 0;
+    const float* z = ${fused} ? (const float*)inputs[nr_input - 1]->ptr : 0;
+    return (TinyNNStatus)mb200_conv_bias_f32_nhwc(
+            &p, (const float*)src->ptr, (const float*)inputs[1]->ptr, bias, z, (float*)dst->ptr,
+            (long long)dst->layout.stride[3], workspace->ptr, workspace->size, MB200_ALGO_AUTO,
+            mb200_opt_stream(opt));
+}
+)";
+    Subst s = conv_f32_common(ctx, this, text.c_str());
+    s.set("signature", GetKernelSignature(ctx))
+            .set("has_bias", has_bias(ctx) ? 1 : 0)
+            .set("fused", fuse_mode(ctx).empty() ? 0 : 1);
+    return s.text;
+}
+
+std::string ConvBiasF32::GetInitBody(TContext* ctx) const {
+    Subst s = conv_f32_common(ctx, this, R"(
+TinyNNStatus ${signature} {
+    /* three-phase init (runtime/src/data_struct.h:135-142): the OIHW filter becomes the K-major
+     * filter followed by its two tf32 planes, a flat float buffer */
+    Tensor* in_weights = inputs[1];
+    mb200_conv_f32_param p;
+    ${symbol}_param(inputs, &p);
+    if (out_weights == 0 && nr_out_weight != 0) {
+        *nr_out_weight = 1;
+        return TinyNN_SUCCESS;
+    }
+    if (out_weights != 0 && nr_out_weight == 0) {
+        out_weights->layout.nr_dim = 1;
+        out_weights->layout.dims[0] = (uint32_t)(mb200_conv_f32_packed_filter_bytes(&p) / 4);
+        out_weights->layout.stride[0] = 1;
+        out_weights->layout.format = in_weights->layout.format;
+        out_weights->dtype = in_weights->dtype;
+        out_weights->name = in_weights->name;
+        return TinyNN_SUCCESS;
+    }
+    return (TinyNNStatus)mb200_conv_f32_pack_filter(
+            &p, (const float*)in_weights->ptr, (float*)out_weights->ptr, mb200_opt_stream(opt));
+}
+)");
+    s.set("signature", GetInitSignature(ctx));
+    return s.text;
+}
+
+std::string ConvBiasF32::GetWorkspaceBody(TContext* ctx) const {
+    Subst s = conv_f32_common(ctx, this, R"(
+TinyNNStatus ${signature} {
+    mb200_conv_f32_param p;
+    ${symbol}_param(inputs, &p);
+    *workspace = mb200_conv_f32_workspace_bytes(&p);
+    return TinyNN_SUCCESS;
+}
+)");
+    s.set("signature", GetWorkspaceSignature(ctx));
+    return s.text;
+}
+
+// must agree with mb200_conv_f32_workspace_bytes (megcc_b200/csrc/f32_abi.cu): the two tf32
+// planes of the activation when the filter is dense and its channels fill whole TMA rows
+size_t ConvBiasF32::WorkspaceBytes(TContext* ctx) const {
+    const CCOperand src = ctx->getAttrOprand("operand:0");
+    if (ctx->getAttrStr("sparse") != "DENSE" || src.shape.size() != 4)
+        return 0;
+    const size_t ic = src.shape[1];
+    if (!(ic == 16 || ic % 32 == 0))
+        return 0;
+    const size_t bytes = 2 * src.shape[0] * src.shape[1] * src.shape[2] * src.shape[3] * 4;
+    return (bytes + 255) / 256 * 256;
+}
+
+// ---- MatrixMul fp32 ----
+bool MatMulF32::IsAvailable(TContext* ctx) const {
+    if (ctx->haveAttr("fused_typecvt") || ctx->getAttrStr("format") != "DEFAULT")
+        return false;
+    if (ctx->getAttrBool("transposeA") || ctx->getAttrBool("transposeB"))
+        return false;
+    return ctx->getAttrInt("nr_operands") == 3 && all_f32(ctx);
+}
+
+std::string MatMulF32::GetKernelSymbol(TContext*) const {
+    return "cuda_sm100_matmul_nn_f32f32f32";
+}
+
+std::string MatMulF32::GetKernelBody(TContext* ctx) const {
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    const Tensor* a = inputs[0];
+    const Tensor* b = inputs[1]; /* prepared by the init function */
+    Tensor* c = outputs[0];
+    const int m = a->layout.dims[0];
+    int k = 1;
+    for (int i = 1; i < a->layout.nr_dim; ++i) k *= a->layout.dims[i];
+    const int n = c->layout.dims[1];
+    return (TinyNNStatus)mb200_matmul_f32(
+            m, n, k, (const float*)a->ptr, (const float*)b->ptr, (float*)c->ptr, workspace->ptr,
+            workspace->size, mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue()).set("signature", GetKernelSignature(ctx));
+    return s.text;
+}
+
+std::string MatMulF32::GetInitBody(TContext* ctx) const {
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    Tensor* b = inputs[1];
+    const int k = b->layout.dims[0], n = b->layout.dims[1];
+    if (out_weights == NULL && nr_out_weight != NULL) {
+        *nr_out_weight = 1;
+        return TinyNN_SUCCESS;
+    }
+    if (out_weights != NULL && nr_out_weight == NULL) {
+        out_weights[0].layout.nr_dim = 1;
+        out_weights[0].layout.dims[0] = (uint32_t)(mb200_matmul_f32_packed_b_bytes(k, n) / 4);
+        out_weights[0].layout.stride[0] = 1;
+        out_weights[0].dtype = b->dtype;
+        out_weights[0].name = b->name;
+        return TinyNN_SUCCESS;
+    }
+    return (TinyNNStatus)mb200_matmul_f32_pack_b(
+            k, n, (const float*)b->ptr, (float*)out_weights[0].ptr, mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue()).set("signature", GetInitSignature(ctx));
+    return s.text;
+}
+
+std::string MatMulF32::GetWorkspaceBody(TContext* ctx) const {
+    Subst s{R"(
+TinyNNStatus ${signature} {
+    const Tensor* a = inputs[0];
+    int k = 1;
+    for (int i = 1; i < a->layout.nr_dim; ++i) k *= a->layout.dims[i];
+    *workspace = mb200_matmul_f32_workspace_bytes((int)a->layout.dims[0], k);
+    return TinyNN_SUCCESS;
+}
+)"};
+    s.set("signature", GetWorkspaceSignature(ctx));
+    return s.text;
+}
+
+size_t MatMulF32::WorkspaceBytes(TContext* ctx) const {
+    const CCOperand a = ctx->getAttrOprand("operand:0");
+    const size_t m = a.shape[0], k = a.shape[1];
+    if (!(k == 16 || k % 32 == 0))
+        return 0;
+    return (2 * m * k * 4 + 255) / 256 * 256;
+}
+
+// ---- Elemwise fp32 ----
+bool ElemwiseF32::IsAvailable(TContext* ctx) const {
+    const int code = elem_code(ctx->getAttrStr("mode"));
+    const int n = ctx->getAttrInt("nr_operands");
+    if (code < 0 || !all_f32(ctx))
+        return false;
+    if ((code < 16) != (n == 2) || (n != 2 && n != 3))
+        return false;
+    // same-shape operands only
+    return n == 2 || ctx->getAttrOprand("operand:0").shape == ctx->getAttrOprand("operand:1").shape;
+}
+
+std::string ElemwiseF32::GetKernelSymbol(TContext* ctx) const {
+    return "cuda_sm100_elementwise_" + ctx->getAttrStr("mode") + "_" + io_str(ctx);
+}
+
+std::string ElemwiseF32::GetKernelBody(TContext* ctx) const {
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    const Tensor* a = inputs[0];
+    const Tensor* b = nr_input > 1 ? inputs[1] : inputs[0];
+    size_t nr_elem = 1;
+    for (int i = 0; i < a->layout.nr_dim; ++i) nr_elem *= a->layout.dims[i];
+    return (TinyNNStatus)mb200_elemwise_f32(
+            ${mode}, (const float*)a->ptr, (const float*)b->ptr, (float*)outputs[0]->ptr, nr_elem,
+            mb200_opt_stream(opt));
 }
 )"};
     s.set("prologue", GenStubPrologue())
             .set("signature", GetKernelSignature(ctx))
-            .set("fn", to_nhwc ? "mb200_relayout_nchw_to_nhwc_s8" : "mb200_relayout_nhwc_to_nchw_s8");
+            .set("mode", elem_code(ctx->getAttrStr("mode")));
+    return s.text;
+}
+
+// ---- Concat / Focus ----
+bool ConcatF32::IsAvailable(TContext* ctx) const {
+    if (ctx->getAttrInt("axis") != 1 || !all_f32(ctx))
+        return false;
+    const int n = ctx->getAttrInt("nr_operands");
+    if (ctx->haveAttr("focus"))
+        return n == 2 && ctx->getAttrOprand("operand:0").shape.size() == 4;
+    return n >= 2 && n <= 9;
+}
+
+std::string ConcatF32::GetKernelSymbol(TContext* ctx) const {
+    if (ctx->haveAttr("focus"))
+        return "cuda_sm100_concat_focus_f32";
+    return "cuda_sm100_concat_NHWC_axis_1_f32";
+}
+
+std::string ConcatF32::GetKernelBody(TContext* ctx) const {
+    if (ctx->haveAttr("focus")) {
+        Subst s{R"(
+${prologue}
+/* the four stride-2 slices of the NCHW input, concatenated along channels, as NHWC */
+TinyNNStatus ${signature} {
+    const Tensor* src = inputs[0];
+    return (TinyNNStatus)mb200_focus_f32(
+            (const float*)src->ptr, (float*)outputs[0]->ptr, src->layout.dims[0],
+            src->layout.dims[1], src->layout.dims[2], src->layout.dims[3],
+            outputs[0]->layout.dims[1], mb200_opt_stream(opt));
+}
+)"};
+        s.set("prologue", GenStubPrologue()).set("signature", GetKernelSignature(ctx));
+        return s.text;
+    }
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    const float* srcs[8];
+    int channels[8];
+    if (nr_input > 8) return TinyNN_ERROR_OUT_OF_RANGE;
+    for (int i = 0; i < nr_input; ++i) {
+        srcs[i] = (const float*)inputs[i]->ptr;
+        channels[i] = inputs[i]->layout.dims[1];
+    }
+    const Tensor* dst = outputs[0];
+    return (TinyNNStatus)mb200_concat_f32_nhwc(
+            srcs, channels, nr_input, (float*)dst->ptr,
+            (size_t)dst->layout.dims[0] * dst->layout.dims[2] * dst->layout.dims[3],
+            mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue()).set("signature", GetKernelSignature(ctx));
+    return s.text;
+}
+
+// ---- Resize ----
+bool ResizeF32::IsAvailable(TContext* ctx) const {
+    return ctx->getAttrStr("imode") == "NEAREST" && ctx->getAttrStr("format") == "NCHW" &&
+           ctx->getAttrOprand("operand:0").dtype == "f32" &&
+           ctx->getAttrOprand("operand:0").shape.size() == 4;
+}
+
+std::string ResizeF32::GetKernelSymbol(TContext*) const {
+    return "cuda_sm100_resize_NHWC_NEAREST_f32";
+}
+
+std::string ResizeF32::GetKernelBody(TContext* ctx) const {
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    const Tensor* src = inputs[0];
+    const Tensor* dst = outputs[0];
+    return (TinyNNStatus)mb200_resize_nearest_f32_nhwc(
+            (const float*)src->ptr, (float*)dst->ptr, src->layout.dims[0], src->layout.dims[1],
+            src->layout.dims[2], src->layout.dims[3], dst->layout.dims[2], dst->layout.dims[3],
+            mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue()).set("signature", GetKernelSignature(ctx));
+    return s.text;
+}
+
+// ---- Pooling fp32 ----
+bool PoolingF32::IsAvailable(TContext* ctx) const {
+    if (ctx->getAttrStr("format") != "NCHW" || !all_f32(ctx))
+        return false;
+    const std::string mode = ctx->getAttrStr("mode");
+    return mode == "MAX" || mode == "AVERAGE" || mode == "AVERAGE_COUNT_EXCLUDE_PADDING";
+}
+
+std::string PoolingF32::GetKernelSymbol(TContext* ctx) const {
+    std::stringstream ss;
+    ss << "cuda_sm100_pooling_" << ctx->getAttrStr("mode") << "_NHWC_p" << ctx->getAttrInt("pad_h")
+       << "x" << ctx->getAttrInt("pad_w") << "_s" << ctx->getAttrInt("stride_h") << "x"
+       << ctx->getAttrInt("stride_w") << "_w" << ctx->getAttrInt("window_h") << "x"
+       << ctx->getAttrInt("window_w") << "_" << io_str(ctx);
+    return ss.str();
+}
+
+std::string PoolingF32::GetKernelBody(TContext* ctx) const {
+    const std::string mode = ctx->getAttrStr("mode");
+    Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    const Tensor* src = inputs[0];
+    return (TinyNNStatus)mb200_pooling_f32_nhwc(
+            (const float*)src->ptr, (float*)outputs[0]->ptr, ${mode}, src->layout.dims[0],
+            src->layout.dims[1], src->layout.dims[2], src->layout.dims[3], ${wh}, ${ww}, ${sh},
+            ${sw}, ${ph}, ${pw}, mb200_opt_stream(opt));
+}
+)"};
+    s.set("prologue", GenStubPrologue())
+            .set("signature", GetKernelSignature(ctx))
+            .set("mode", mode == "MAX" ? 0 : mode == "AVERAGE" ? 1 : 2)
+            .set("wh", ctx->getAttrInt("window_h"))
+            .set("ww", ctx->getAttrInt("window_w"))
+            .set("sh", ctx->getAttrInt("stride_h"))
+            .set("sw", ctx->getAttrInt("stride_w"))
+            .set("ph", ctx->getAttrInt("pad_h"))
+            .set("pw", ctx->getAttrInt("pad_w"));
     return s.text;
 }
 
@@ -556,13 +1001,25 @@ std::vector<const KernelFunc*> ArchKernelPack::GetKernel(KernelPack::KernType ke
     static TypeCvtQS32QS8 typecvt;
     static RelayoutQS8 relayout;
     static MatMulQS8 matmul;
+    static ConvBiasF32 conv_f32;
+    static MatMulF32 matmul_f32;
+    static ElemwiseF32 elem_f32;
+    static ConcatF32 concat_f32;
+    static ResizeF32 resize_f32;
+    static PoolingF32 pooling_f32;
     switch (kernel_type) {
         case KernelPack::KernType::MatrixMulKernel:
-            return {&matmul};
+            return {&matmul, &matmul_f32};
         case KernelPack::KernType::ConvKernel:
-            return {&conv};
+            return {&conv, &conv_f32};
         case KernelPack::KernType::PoolingKernel:
-            return {&pooling};
+            return {&pooling, &pooling_f32};
+        case KernelPack::KernType::ElemwiseKernel:
+            return {&elem_f32};
+        case KernelPack::KernType::ConcatKernel:
+            return {&concat_f32};
+        case KernelPack::KernType::ResizeKernel:
+            return {&resize_f32};
         case KernelPack::KernType::ElemwiseMultiKernel:
             return {&qelem};
         case KernelPack::KernType::TypeCvtKernel:

@@ -14,19 +14,6 @@ namespace megcc {
 namespace KernelGen {
 namespace Cuda {
 
-// qint8 ConvBias, activations NHWC. Admits a subset of what BareMetal::ConvGeneral admits
-// (compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:16-46).
-class ConvBiasQS8 : public KernelFunc {
-public:
-    bool IsAvailable(TContext* ctx) const override;
-    std::string GetKernelSymbol(TContext* ctx) const override;
-    std::string GetKernelBody(TContext* ctx) const override;
-    std::string GetInitBody(TContext* ctx) const override;
-    std::string GetWorkspaceBody(TContext* ctx) const override;
-    // bytes of device scratch the kernel needs for the operator `ctx` describes
-    size_t WorkspaceBytes(TContext* ctx) const;
-};
-
 class PoolingQS8 : public KernelFunc {
 public:
     bool IsAvailable(TContext* ctx) const override;
@@ -64,6 +51,91 @@ public:
 
 // NCHW <-> NHWC at the model boundary
 class RelayoutQS8 : public KernelFunc {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+};
+
+// Bytes of device scratch an operator needs, answered directly (the reference sizes
+// workspaces by running the generated *_workspace function through a JIT at compile time,
+// compiler/lib/Dialect/Kernel/Transforms/KernelTemplate.cpp:18-35). Kernels of this pack that
+// need scratch derive from it.
+class WithWorkspace {
+public:
+    virtual ~WithWorkspace() = default;
+    virtual size_t WorkspaceBytes(TContext* ctx) const = 0;
+};
+
+// qint8 ConvBias, activations NHWC. Admits a subset of what BareMetal::ConvGeneral admits
+// (compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:16-46).
+class ConvBiasQS8 : public KernelFunc, public WithWorkspace {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+    std::string GetInitBody(TContext* ctx) const override;
+    std::string GetWorkspaceBody(TContext* ctx) const override;
+    // bytes of device scratch the kernel needs for the operator `ctx` describes
+    size_t WorkspaceBytes(TContext* ctx) const override;
+};
+
+// ---- fp32 path (the detector configuration and the fp32 MatrixMul sweep) ----
+
+// fp32 ConvBias, activations NHWC. nonlineMode IDENTITY / RELU / SIGMOID / H_SWISH as the
+// reference's fp32 kernels take it (compiler/lib/KernelGen/GeneralIntrinsic/ConvKernel/
+// Fp32Im2col.cpp:122-156), plus SILU: the Elemwise kernel that follows the ConvBias in a
+// YOLOX-style graph, folded into the epilogue. An optional z operand (attribute
+// fuse_elemwise_mode = "ADD") is added after the activation (the bottleneck shortcut).
+class ConvBiasF32 : public KernelFunc, public WithWorkspace {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+    std::string GetInitBody(TContext* ctx) const override;
+    std::string GetWorkspaceBody(TContext* ctx) const override;
+    size_t WorkspaceBytes(TContext* ctx) const override;
+};
+
+// C[M][N] = A[M][K] x B[K][N], all fp32, B a weight
+// (compiler/lib/KernelGen/GeneralIntrinsic/MatMulKernel/Fp32MatMulM4N12.cpp:8-160)
+class MatMulF32 : public KernelFunc, public WithWorkspace {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+    std::string GetInitBody(TContext* ctx) const override;
+    std::string GetWorkspaceBody(TContext* ctx) const override;
+    size_t WorkspaceBytes(TContext* ctx) const override;
+};
+
+// Elemwise fp32, same-shape operands (compiler/lib/KernelGen/BareMetal/ElemwiseKernel.cpp:413-431)
+class ElemwiseF32 : public KernelFunc {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+};
+
+// Concat along channels (compiler/lib/KernelGen/BareMetal/Concat.cpp:10-78, axis 1); with the
+// attribute "focus" the single NCHW input is read through its four stride-2 slices
+class ConcatF32 : public KernelFunc {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+};
+
+// Resize NEAREST fp32 (compiler/lib/KernelGen/BareMetal/Resize.cpp:13-33)
+class ResizeF32 : public KernelFunc {
+public:
+    bool IsAvailable(TContext* ctx) const override;
+    std::string GetKernelSymbol(TContext* ctx) const override;
+    std::string GetKernelBody(TContext* ctx) const override;
+};
+
+// Pooling fp32 (compiler/lib/KernelGen/BareMetal/Pooling.cpp:15-29)
+class PoolingF32 : public KernelFunc {
 public:
     bool IsAvailable(TContext* ctx) const override;
     std::string GetKernelSymbol(TContext* ctx) const override;

@@ -36,6 +36,7 @@ struct GTensor {
     float scale = 1.f;
     bool nchw = false;  // physical layout of the buffer (model input / 1x1 outputs)
     bool is_input = false, is_output = false;
+    bool f32 = false;   // fp32 tensor (else qint8)
 };
 
 struct GWeight {
@@ -47,7 +48,7 @@ struct GWeight {
     int use_count = 0;
 };
 
-enum class OpType { CONV, POOL, QELEM, RELAYOUT, MATMUL };
+enum class OpType { CONV, POOL, QELEM, RELAYOUT, MATMUL, ELEM_F32, CONCAT, FOCUS, RESIZE };
 
 struct GOp {
     OpType type;
@@ -64,6 +65,7 @@ struct GOp {
     std::string fuse_mode;  // "" | "QADD" | "QFUSE_ADD_RELU"
     float mid_scale = 1.f;  // scale of the ConvBias result that the fused step consumes
     int mid_weight = -1;    // 1-element float weight carrying mid_scale to the runtime
+    bool f32 = false;       // fp32 operator (CONV / MATMUL / POOL / RELAYOUT)
 };
 
 struct Compiled {
@@ -83,6 +85,14 @@ CCOperand operand(const char* base, std::vector<size_t> shape, float scale) {
     o.shape = std::move(shape);
     o.dtype = qdtype(base, scale);
     o.scale = scale;
+    return o;
+}
+
+CCOperand operand_f32(std::vector<size_t> shape) {
+    CCOperand o;
+    o.shape = std::move(shape);
+    o.dtype = "f32";
+    o.scale = 1.f;
     return o;
 }
 
@@ -140,7 +150,40 @@ struct mb200c_graph {
             const GTensor& t = tensors[id];
             return std::vector<size_t>{(size_t)batch, (size_t)t.c, (size_t)t.h, (size_t)t.w};
         };
+        auto topr = [&](int id) {
+            const GTensor& t = tensors[id];
+            return t.f32 ? operand_f32(shape(id)) : operand("qsi8", shape(id), t.scale);
+        };
         switch (op.type) {
+            case OpType::ELEM_F32: {
+                set_str(*ctx, "mode", op.mode);
+                int k = 0;
+                for (int id : op.inputs)
+                    set_opr(*ctx, "operand:" + std::to_string(k++), topr(id));
+                set_opr(*ctx, "operand:" + std::to_string(k++), topr(op.output));
+                set_i32(*ctx, "nr_operands", k);
+                break;
+            }
+            case OpType::CONCAT:
+            case OpType::FOCUS: {
+                set_i32(*ctx, "axis", 1);
+                if (op.type == OpType::FOCUS)
+                    set_i32(*ctx, "focus", 1);
+                int k = 0;
+                for (int id : op.inputs)
+                    set_opr(*ctx, "operand:" + std::to_string(k++), topr(id));
+                set_opr(*ctx, "operand:" + std::to_string(k++), topr(op.output));
+                set_i32(*ctx, "nr_operands", k);
+                break;
+            }
+            case OpType::RESIZE: {
+                set_str(*ctx, "imode", "NEAREST");
+                set_str(*ctx, "format", "NCHW");
+                set_opr(*ctx, "operand:0", topr(op.inputs[0]));
+                set_opr(*ctx, "operand:1", topr(op.output));
+                set_i32(*ctx, "nr_operands", 2);
+                break;
+            }
             case OpType::CONV: {
                 const GTensor& src = tensors[op.inputs[0]];
                 const GTensor& dst = tensors[op.output];
@@ -157,6 +200,25 @@ struct mb200c_graph {
                 set_str(*ctx, "mode", "CROSS_CORRELATION");
                 set_str(*ctx, "nonlineMode", op.mode);
                 set_str(*ctx, "compute_mode", "DEFAULT");
+                if (op.f32) {
+                    std::vector<size_t> fshape;
+                    for (int d : weights[op.weights[0]].dims)
+                        fshape.push_back(d);
+                    set_opr(*ctx, "operand:0", topr(op.inputs[0]));
+                    set_opr(*ctx, "operand:1", operand_f32(fshape));
+                    set_opr(*ctx, "operand:2", op.has_bias ? operand_f32({1, (size_t)dst.c, 1, 1})
+                                                           : operand_f32({}));
+                    if (op.inputs.size() > 1) {
+                        set_opr(*ctx, "operand:3", topr(op.inputs[1]));
+                        set_opr(*ctx, "operand:4", topr(op.output));
+                        set_i32(*ctx, "nr_operands", 5);
+                        set_str(*ctx, "fuse_elemwise_mode", "ADD");
+                    } else {
+                        set_opr(*ctx, "operand:3", topr(op.output));
+                        set_i32(*ctx, "nr_operands", 4);
+                    }
+                    break;
+                }
                 set_opr(*ctx, "operand:0", operand("qsi8", shape(op.inputs[0]), src.scale));
                 std::vector<size_t> fs;
                 for (int d : weights[op.weights[0]].dims)
@@ -195,9 +257,8 @@ struct mb200c_graph {
                 set_i32(*ctx, "stride_w", op.stride);
                 set_i32(*ctx, "pad_h", op.pad);
                 set_i32(*ctx, "pad_w", op.pad);
-                set_opr(*ctx, "operand:0",
-                        operand("qsi8", shape(op.inputs[0]), tensors[op.inputs[0]].scale));
-                set_opr(*ctx, "operand:1", operand("qsi8", shape(op.output), tensors[op.output].scale));
+                set_opr(*ctx, "operand:0", topr(op.inputs[0]));
+                set_opr(*ctx, "operand:1", topr(op.output));
                 set_i32(*ctx, "nr_operands", 2);
                 break;
             }
@@ -222,6 +283,15 @@ struct mb200c_graph {
                 set_bool(*ctx, "transposeB", false);
                 set_str(*ctx, "format", "DEFAULT");
                 set_str(*ctx, "compute_mode", "DEFAULT");
+                if (op.f32) {
+                    set_opr(*ctx, "operand:0",
+                            operand_f32({(size_t)batch, (size_t)(a.c * a.h * a.w)}));
+                    set_opr(*ctx, "operand:1",
+                            operand_f32({(size_t)b.dims[0], (size_t)b.dims[1]}));
+                    set_opr(*ctx, "operand:2", operand_f32({(size_t)batch, (size_t)c.c}));
+                    set_i32(*ctx, "nr_operands", 3);
+                    break;
+                }
                 set_str(*ctx, "fused_typecvt", "qsi8");
                 set_opr(*ctx, "operand:0",
                         operand("qsi8", {(size_t)batch, (size_t)(a.c * a.h * a.w)}, a.scale));
@@ -233,9 +303,8 @@ struct mb200c_graph {
             }
             case OpType::RELAYOUT: {
                 set_str(*ctx, "relayout_mode", op.mode);
-                set_opr(*ctx, "operand:0",
-                        operand("qsi8", shape(op.inputs[0]), tensors[op.inputs[0]].scale));
-                set_opr(*ctx, "operand:1", operand("qsi8", shape(op.output), tensors[op.output].scale));
+                set_opr(*ctx, "operand:0", topr(op.inputs[0]));
+                set_opr(*ctx, "operand:1", topr(op.output));
                 set_i32(*ctx, "nr_operands", 2);
                 break;
             }
@@ -249,6 +318,10 @@ struct mb200c_graph {
             case OpType::POOL: return KernType::PoolingKernel;
             case OpType::QELEM: return KernType::ElemwiseMultiKernel;
             case OpType::MATMUL: return KernType::MatrixMulKernel;
+            case OpType::ELEM_F32: return KernType::ElemwiseKernel;
+            case OpType::CONCAT:
+            case OpType::FOCUS: return KernType::ConcatKernel;
+            case OpType::RESIZE: return KernType::ResizeKernel;
             default: return KernType::RelayoutKernel;
         }
     }
@@ -257,7 +330,7 @@ struct mb200c_graph {
 namespace {
 
 size_t tensor_bytes(const GTensor& t, int batch) {
-    return (size_t)batch * t.c * t.h * t.w;
+    return (size_t)batch * t.c * t.h * t.w * (t.f32 ? 4 : 1);
 }
 
 size_t align256(size_t v) {
@@ -402,7 +475,7 @@ int mb200c_add_conv_bias(
         mb200c_graph* g, const char* name, int src, int oc, int kh, int kw, int stride, int pad,
         int groups, const char* nonline, const int8_t* flt, float flt_scale, const int32_t* bias,
         const float* channel_scales, float dst_scale) {
-    if (!g || !name || !nonline || !flt || !g->valid(src))
+    if (!g || !name || !nonline || !flt || !g->valid(src) || g->tensors[src].f32)
         return err("add_conv_bias: bad argument");
     const GTensor s = g->tensors[src];
     if (oc <= 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0 || groups <= 0 ||
@@ -489,6 +562,175 @@ int mb200c_add_matmul(
     return op.output;
 }
 
+int mb200c_add_input_f32(mb200c_graph* g, const char* name, int c, int h, int w) {
+    const int id = mb200c_add_input(g, name, c, h, w, 1.f);
+    if (id >= 0)
+        g->tensors[id].f32 = true;
+    return id;
+}
+
+int mb200c_add_conv_f32(
+        mb200c_graph* g, const char* name, int src, int oc, int kh, int kw, int stride, int pad,
+        int groups, const char* nonline, const float* flt, const float* bias, int z) {
+    if (!g || !name || !nonline || !flt || !g->valid(src) || !g->tensors[src].f32)
+        return err("add_conv_f32: bad argument");
+    const GTensor s = g->tensors[src];
+    if (oc <= 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0 || groups <= 0 ||
+        s.c % groups || oc % groups)
+        return err("add_conv_f32 %s: bad extents", name);
+    const int oh = out_extent(s.h, kh, stride, pad), ow = out_extent(s.w, kw, stride, pad);
+    if (oh <= 0 || ow <= 0)
+        return err("add_conv_f32 %s: filter larger than padded input", name);
+    if (z >= 0) {
+        if (!g->valid(z) || !g->tensors[z].f32 || g->tensors[z].c != oc ||
+            g->tensors[z].h != oh || g->tensors[z].w != ow)
+            return err("add_conv_f32 %s: z does not have the output's shape", name);
+    }
+    GOp op;
+    op.type = OpType::CONV;
+    op.f32 = true;
+    op.name = name;
+    op.inputs = z >= 0 ? std::vector<int>{src, z} : std::vector<int>{src};
+    op.kh = kh;
+    op.kw = kw;
+    op.stride = stride;
+    op.pad = pad;
+    op.groups = groups;
+    op.mode = nonline;
+    const int icpg = s.c / groups;
+    GWeight wf;
+    wf.name = std::string(name) + ":filter";
+    wf.dtype = fb::Float32;
+    wf.scale = 1.f;
+    wf.dims = groups == 1 ? std::vector<int>{oc, s.c, kh, kw}
+                          : std::vector<int>{groups, oc / groups, icpg, kh, kw};
+    wf.data.assign((const uint8_t*)flt, (const uint8_t*)flt + (size_t)oc * icpg * kh * kw * 4);
+    wf.use_count = 1;
+    g->weights.push_back(std::move(wf));
+    op.weights.push_back((int)g->weights.size() - 1);
+    if (bias) {
+        GWeight wb;
+        wb.name = std::string(name) + ":bias";
+        wb.dtype = fb::Float32;
+        wb.scale = 1.f;
+        wb.dims = {1, oc, 1, 1};
+        wb.data.assign((const uint8_t*)bias, (const uint8_t*)bias + (size_t)oc * 4);
+        wb.use_count = 1;
+        g->weights.push_back(std::move(wb));
+        op.weights.push_back((int)g->weights.size() - 1);
+        op.has_bias = true;
+    }
+    op.output = g->add_tensor(std::string(name) + ":out", oc, oh, ow, 1.f);
+    g->tensors[op.output].f32 = true;
+    g->ops.push_back(op);
+    return op.output;
+}
+
+int mb200c_add_matmul_f32(mb200c_graph* g, const char* name, int src, int n, const float* b) {
+    if (!g || !name || !b || !g->valid(src) || n <= 0 || !g->tensors[src].f32)
+        return err("add_matmul_f32: bad argument");
+    const GTensor s = g->tensors[src];
+    if (s.h != 1 || s.w != 1)
+        return err("add_matmul_f32 %s: the input must be a [batch][K] matrix (h = w = 1)", name);
+    GOp op;
+    op.type = OpType::MATMUL;
+    op.f32 = true;
+    op.name = name;
+    op.inputs = {src};
+    GWeight wb;
+    wb.name = std::string(name) + ":B";
+    wb.dtype = fb::Float32;
+    wb.scale = 1.f;
+    wb.dims = {s.c, n};
+    wb.data.assign((const uint8_t*)b, (const uint8_t*)b + (size_t)s.c * n * 4);
+    wb.use_count = 1;
+    g->weights.push_back(std::move(wb));
+    op.weights.push_back((int)g->weights.size() - 1);
+    op.output = g->add_tensor(std::string(name) + ":out", n, 1, 1, 1.f);
+    g->tensors[op.output].f32 = true;
+    g->ops.push_back(op);
+    return op.output;
+}
+
+int mb200c_add_elemwise_f32(mb200c_graph* g, const char* name, const char* mode, int a, int b) {
+    if (!g || !name || !mode || !g->valid(a) || !g->tensors[a].f32)
+        return err("add_elemwise_f32: bad argument");
+    const GTensor s = g->tensors[a];
+    GOp op;
+    op.type = OpType::ELEM_F32;
+    op.f32 = true;
+    op.name = name;
+    op.mode = mode;
+    op.inputs = {a};
+    if (b >= 0) {
+        if (!g->valid(b) || !g->tensors[b].f32 || g->tensors[b].c != s.c ||
+            g->tensors[b].h != s.h || g->tensors[b].w != s.w)
+            return err("add_elemwise_f32 %s: operand shapes differ", name);
+        op.inputs.push_back(b);
+    }
+    op.output = g->add_tensor(std::string(name) + ":out", s.c, s.h, s.w, 1.f);
+    g->tensors[op.output].f32 = true;
+    g->ops.push_back(op);
+    return op.output;
+}
+
+int mb200c_add_concat(mb200c_graph* g, const char* name, const int* srcs, int nr) {
+    if (!g || !name || !srcs || nr < 1 || nr > 8)
+        return err("add_concat: 1..8 inputs");
+    GOp op;
+    op.type = OpType::CONCAT;
+    op.f32 = true;
+    op.name = name;
+    int c = 0;
+    for (int i = 0; i < nr; ++i) {
+        if (!g->valid(srcs[i]) || !g->tensors[srcs[i]].f32)
+            return err("add_concat %s: input %d is not an fp32 tensor", name, i);
+        const GTensor& t = g->tensors[srcs[i]];
+        if (t.h != g->tensors[srcs[0]].h || t.w != g->tensors[srcs[0]].w)
+            return err("add_concat %s: spatial extents differ", name);
+        c += t.c;
+        op.inputs.push_back(srcs[i]);
+    }
+    const GTensor s = g->tensors[srcs[0]];
+    op.output = g->add_tensor(std::string(name) + ":out", c, s.h, s.w, 1.f);
+    g->tensors[op.output].f32 = true;
+    g->ops.push_back(op);
+    return op.output;
+}
+
+int mb200c_add_focus(mb200c_graph* g, const char* name, int src, int c_out) {
+    if (!g || !name || !g->valid(src) || !g->tensors[src].f32)
+        return err("add_focus: bad argument");
+    const GTensor s = g->tensors[src];
+    if (!s.nchw || (s.h & 1) || (s.w & 1) || c_out < 4 * s.c)
+        return err("add_focus %s: needs the NCHW model input with even extents and "
+                   "c_out >= 4 * c", name);
+    GOp op;
+    op.type = OpType::FOCUS;
+    op.f32 = true;
+    op.name = name;
+    op.inputs = {src};
+    op.output = g->add_tensor(std::string(name) + ":out", c_out, s.h / 2, s.w / 2, 1.f);
+    g->tensors[op.output].f32 = true;
+    g->ops.push_back(op);
+    return op.output;
+}
+
+int mb200c_add_resize_nearest(mb200c_graph* g, const char* name, int src, int oh, int ow) {
+    if (!g || !name || !g->valid(src) || !g->tensors[src].f32 || oh <= 0 || ow <= 0)
+        return err("add_resize_nearest: bad argument");
+    const GTensor s = g->tensors[src];
+    GOp op;
+    op.type = OpType::RESIZE;
+    op.f32 = true;
+    op.name = name;
+    op.inputs = {src};
+    op.output = g->add_tensor(std::string(name) + ":out", s.c, oh, ow, 1.f);
+    g->tensors[op.output].f32 = true;
+    g->ops.push_back(op);
+    return op.output;
+}
+
 int mb200c_add_pooling(
         mb200c_graph* g, const char* name, int src, const char* mode, int window, int stride,
         int pad) {
@@ -506,7 +748,9 @@ int mb200c_add_pooling(
     op.stride = stride;
     op.pad = pad;
     op.mode = mode;
+    op.f32 = s.f32;
     op.output = g->add_tensor(std::string(name) + ":out", s.c, oh, ow, s.scale);
+    g->tensors[op.output].f32 = s.f32;
     g->ops.push_back(op);
     return op.output;
 }
@@ -515,6 +759,8 @@ int mb200c_add_qelemwise(
         mb200c_graph* g, const char* name, const char* mode, int a, int b, float dst_scale) {
     if (!g || !name || !mode || !g->valid(a))
         return err("add_qelemwise: bad argument");
+    if (g->tensors[a].f32)
+        return err("add_qelemwise %s: fp32 tensors take add_elemwise_f32", name);
     const bool unary = strcmp(mode, "QRELU") == 0;
     if (!unary && !g->valid(b))
         return err("add_qelemwise %s: second operand missing", name);
@@ -572,14 +818,16 @@ int mb200c_compile(
                 const int id = op.inputs[k];
                 if (!work.tensors[id].nchw)
                     continue;
-                if (op.type == OpType::CONV && k == 0)
-                    continue;  // ConvBias reads NCHW directly
+                if ((op.type == OpType::CONV && !op.f32 && k == 0) || op.type == OpType::FOCUS)
+                    continue;  // the qint8 ConvBias and Focus read NCHW directly
                 if (work.tensors[id].h == 1 && work.tensors[id].w == 1)
                     continue;  // NCHW == NHWC
                 if (!nhwc_of.count(id)) {
                     const GTensor t = work.tensors[id];
                     const int nid = work.add_tensor(t.name + ":nhwc", t.c, t.h, t.w, t.scale);
+                    work.tensors[nid].f32 = t.f32;
                     GOp r;
+                    r.f32 = t.f32;
                     r.type = OpType::RELAYOUT;
                     r.name = t.name + ":to_nhwc";
                     r.inputs = {id};
@@ -606,8 +854,10 @@ int mb200c_compile(
             const int nid = work.add_tensor(copy.name + ":nchw", copy.c, copy.h, copy.w, copy.scale);
             work.tensors[nid].is_output = true;
             work.tensors[nid].nchw = true;
+            work.tensors[nid].f32 = copy.f32;
             std::swap(work.tensors[id].name, work.tensors[nid].name);  // keep the visible name
             GOp r;
+            r.f32 = copy.f32;
             r.type = OpType::RELAYOUT;
             r.name = copy.name + ":to_nchw";
             r.inputs = {(int)id};
@@ -712,12 +962,12 @@ int mb200c_compile(
         // workspace bytes per operator, as the kernel that was selected reports them
         std::vector<size_t> ws_bytes(work.ops.size(), 0), ws_offsets;
         for (size_t k = 0; k < work.ops.size(); ++k) {
-            if (work.ops[k].type != OpType::CONV)
+            auto* with_ws =
+                    dynamic_cast<const KernelGen::Cuda::WithWorkspace*>(g->kernel_of[op_symbol[k]]);
+            if (!with_ws)
                 continue;
             auto ctx = work.context_for(work.ops[k], batch);
-            auto* conv = dynamic_cast<const KernelGen::Cuda::ConvBiasQS8*>(g->kernel_of[op_symbol[k]]);
-            if (conv)
-                ws_bytes[k] = conv->WorkspaceBytes(ctx.get());
+            ws_bytes[k] = with_ws->WorkspaceBytes(ctx.get());
         }
         std::vector<size_t> offsets;
         Compiled c;
@@ -735,7 +985,7 @@ int mb200c_compile(
             const std::vector<int> stride =
                     t.nchw ? contiguous(dims) : std::vector<int>{t.h * t.w * t.c, 1, t.w * t.c, t.c};
             auto n = fb::make_table();
-            n->add_ref(fb::field::T_dtype, dtype_node(fb::QInt8, t.scale));
+            n->add_ref(fb::field::T_dtype, dtype_node(t.f32 ? fb::Float32 : fb::QInt8, t.scale));
             n->add_ref(fb::field::T_layout, layout_node(dims, stride, t.nchw ? fb::NCHW : fb::NHWC));
             n->add<int64_t>(fb::field::T_offset, (int64_t)offsets[i]);
             n->add<int32_t>(fb::field::T_use_count, use_count[i]);
@@ -766,6 +1016,9 @@ int mb200c_compile(
                     in_t.push_back(fb::TENSOR);
                     in.push_back(op.mid_weight);
                     in_t.push_back(fb::WEIGHT);
+                } else if (op.f32 && op.inputs.size() > 1) {
+                    in.push_back(op.inputs[1]);  // z: added after the activation
+                    in_t.push_back(fb::TENSOR);
                 }
             } else {
                 for (int id : op.inputs) {

@@ -183,6 +183,8 @@ struct KernelPack {
         MatrixMulKernel = 5,
         RelayoutKernel = 7,
         TypeCvtKernel = 13,
+        ResizeKernel = 19,
+        ConcatKernel = 25,
     };
 };
 

@@ -11,12 +11,19 @@
 // tensor core treats the low 13 bits of its inputs.
 //
 // The tensor core adds each MMA's products into the TMEM accumulator with truncation, not
-// round-to-nearest: a long chain of MMAs drifts toward zero by about half an ulp per
-// instruction (measured: 384 MMAs over K = 1024 left errors of 3e-6 relative to the running
-// sum, ten times what fp32 summation gives). The K loop is therefore cut into segments of at
-// most 48 MMAs; each segment starts a fresh TMEM accumulator (the two buffers alternate) and
-// the epilogue warps add the finished segment into fp32 registers with round-to-nearest
-// while the tensor core works on the next one.
+// round-to-nearest: every instruction pulls the running sum toward zero by about half an ulp.
+// Over a long chain that is a SYSTEMATIC shrink of the result (measured: K = 1152 in one
+// chain scaled outputs by 1 - 4e-6; through the 60 ConvBias layers between a detector's input
+// and its heads that compounded to -3.6e-4, against a tolerance of 1e-4). Two measures keep
+// the drift at the level of fp32 rounding:
+//   * short chains: the K loop is cut into segments of four K = 8 steps; every segment starts
+//     fresh TMEM accumulators (two sets alternate) and the epilogue warps add the finished
+//     segment into fp32 registers with round-to-nearest while the tensor core works on the
+//     next one. A short partial sum is small against the final one and nearly uncorrelated
+//     with its sign, so what is left of the drift largely cancels;
+//   * the two correction passes (lo*hi, hi*lo) go to an accumulator of their own: they are
+//     2^-11 of the main pass, so their truncation does not matter, and they no longer cause
+//     two extra truncations of the main sum per step.
 //
 //   * filter: split once at load time (the Init step) into two K-major planes
 //     [2][OC][KH][KW][IC];
@@ -287,7 +294,7 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
         asm volatile(
                 "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                         smem_u32(tmem_slot)),
-                "r"(2 * BN)
+                "r"(4 * BN)
                 : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -373,7 +380,9 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                    // main sum (hi * hi) and correction sum (lo * hi + hi * lo) of this set
+                    const uint32_t tmem_d = tmem_base + (uint32_t)(buf * 2 * BN);
+                    const uint32_t tmem_c = tmem_d + (uint32_t)BN;
                     for (int it = k0; it < k1; ++it) {
                         if (!mbar_wait(&full_bar[s], phase, abort_flag, p.wait_cycles)) {
                             if (!*abort_flag) {
@@ -394,13 +403,14 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
                                 a_addr + 2 * L::kABytes + L::kBBytes, 16, kSbo, kLayout);
                         // a K step of 8 floats is 32 bytes inside the swizzled row: +2 in the
                         // descriptor's 16-byte address units
-                        umma_tf32(tmem_d, a_lo, b_hi, idesc, it != k0 ? 1u : 0u);
-                        umma_tf32_c<true>(tmem_d, a_hi, b_lo, idesc);
-                        umma_tf32_c<true>(tmem_d, a_hi, b_hi, idesc);
+                        const uint32_t acc = it != k0 ? 1u : 0u;
+                        umma_tf32(tmem_c, a_lo, b_hi, idesc, acc);
+                        umma_tf32_c<true>(tmem_c, a_hi, b_lo, idesc);
+                        umma_tf32(tmem_d, a_hi, b_hi, idesc, acc);
 #pragma unroll
                         for (int k = 1; k < ROWB / 32; ++k) {
-                            umma_tf32_c<true>(tmem_d, a_lo + 2 * k, b_hi + 2 * k, idesc);
-                            umma_tf32_c<true>(tmem_d, a_hi + 2 * k, b_lo + 2 * k, idesc);
+                            umma_tf32_c<true>(tmem_c, a_lo + 2 * k, b_hi + 2 * k, idesc);
+                            umma_tf32_c<true>(tmem_c, a_hi + 2 * k, b_lo + 2 * k, idesc);
                             umma_tf32_c<true>(tmem_d, a_hi + 2 * k, b_hi + 2 * k, idesc);
                         }
                         umma_commit(&empty_bar[s]);
@@ -441,16 +451,12 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
                     break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t taddr =
-                        tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+                        tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 2 * BN);
 #pragma unroll
                 for (int cc = 0; cc < kChunksPerWarp; ++cc) {
+                    const uint32_t col = (uint32_t)((half * kChunksPerWarp + cc) * 32);
                     uint32_t v[32];
-                    tmem_ld32(taddr + (uint32_t)((half * kChunksPerWarp + cc) * 32), v);
-                    if (cc + 1 == kChunksPerWarp) {
-                        // this thread's accumulators are in registers: hand the buffer back
-                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        mbar_arrive(&acc_empty[buf]);
-                    }
+                    tmem_ld32(taddr + col, v);  // main sum
                     if (k0 == 0) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
@@ -460,6 +466,15 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
                         for (int j = 0; j < 32; ++j)
                             sum[cc][j] = __fadd_rn(sum[cc][j], __uint_as_float(v[j]));
                     }
+                    tmem_ld32(taddr + (uint32_t)BN + col, v);  // correction sum
+                    if (cc + 1 == kChunksPerWarp) {
+                        // this thread's accumulators are in registers: hand the set back
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        mbar_arrive(&acc_empty[buf]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        sum[cc][j] = __fadd_rn(sum[cc][j], __uint_as_float(v[j]));
                 }
             }
             if (!ok)
@@ -493,7 +508,7 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
     }
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                     "r"(2 * BN)
+                     "r"(4 * BN)
                      : "memory");
     }
 }
@@ -573,7 +588,7 @@ int launch_f32_kernel(
                              L::kDynamic) != cudaSuccess)
         return check_launch("conv_f32_umma smem attribute");
     const int per_sm = resident_ctas_per_sm(conv_f32_umma_kernel<BN, ROWB>, kF32Threads,
-                                            L::kDynamic, 2 * BN);
+                                            L::kDynamic, 4 * BN);
     const int total = p.m_tiles * p.n_tiles;
     int grid = sm_count() * per_sm;
     if (grid > total)
@@ -725,8 +740,8 @@ int launch_conv_f32_umma(
     p.cblocks = a.ic / chans;
     p.taps_w = a.kw;
     p.k_iters = taps * p.cblocks;
-    // at most 48 MMAs (a pipeline step issues 3 per 32 bytes of row) per TMEM accumulation
-    p.seg_iters = 48 / (3 * (rowb / 32));
+    // four K = 8 steps per TMEM accumulation chain
+    p.seg_iters = 4 / (rowb / 32);
     p.sh = a.sh;
     p.sw = a.sw;
     p.base_h = -a.ph;

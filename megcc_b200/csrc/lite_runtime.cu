@@ -4,8 +4,14 @@
 //
 // It takes the place of the reference's parse.c / init.c / vm.c / vm/op.c / lite/*.c
 // (runtime/src): same model format, same structs handed to kernels, same status codes.
-// An Opr's `type` string is the kernel symbol chosen by KernelGen; the symbol selects the
-// pre-built sm_100a kernel here exactly as the generated stub of that symbol would.
+//
+// Dispatch follows the reference (runtime/src/vm/op.c:161-163): every Opr is executed as
+// kernels[opr->kernel_id](inputs, nr_input, outputs, nr_output, &workspace, &opt) through a
+// table of the reference's uniform KernelFunc type, and its weights are preprocessed through
+// init_kernels[opr->init_id] with the three-phase protocol of runtime/src/init.c:29-131.
+// The tables come from the generated kernels.c of the compile side when the caller registered
+// one (mb200_lite_set_kernel_tables); entries nobody registered are filled once at load time
+// with the library's own implementations, selected by the Opr's symbol.
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -54,15 +60,25 @@ size_t dtype_bytes(TinyNNDType t) {
     }
 }
 
+// bytes of a tensor, or SIZE_MAX when the product of its extents does not fit a size_t
 size_t tensor_bytes(const Tensor& t) {
-    size_t n = 1;
-    for (int i = 0; i < t.layout.nr_dim; ++i)
-        n *= t.layout.dims[i];
-    return n * dtype_bytes(t.dtype.type_enum);
+    size_t n = dtype_bytes(t.dtype.type_enum);
+    for (int i = 0; i < t.layout.nr_dim; ++i) {
+        const size_t d = t.layout.dims[i];
+        if (d != 0 && n > (SIZE_MAX / 4) / d)
+            return SIZE_MAX;
+        n *= d;
+    }
+    return n;
 }
 
 enum OpKind {
-    OP_CONV, OP_POOL, OP_QELEM, OP_TYPECVT, OP_RELAYOUT_TO_NHWC, OP_RELAYOUT_TO_NCHW, OP_MATMUL
+    OP_CONV, OP_POOL, OP_QELEM, OP_TYPECVT, OP_RELAYOUT_TO_NHWC, OP_RELAYOUT_TO_NCHW, OP_MATMUL,
+    // fp32 path
+    OP_CONV_F32, OP_MATMUL_F32, OP_ELEM_F32, OP_CONCAT_F32, OP_FOCUS_F32, OP_RESIZE_F32,
+    OP_POOL_F32, OP_RELAYOUT_F32_TO_NHWC, OP_RELAYOUT_F32_TO_NCHW,
+    // a symbol this library has no implementation for: runs only through a registered table
+    OP_EXTERNAL
 };
 
 struct OpPlan {
@@ -76,8 +92,13 @@ struct OpPlan {
     std::vector<int> weight_inputs;  // indices (into inputs) that are weights
     Workspace ws{nullptr, 0, 0};
     bool needs_init = false;
-    bool use_s2d = false;  // first-layer form: space-to-depth + tensor cores
     int z_mode = 0;        // fused elemwise step: 0 none, else MB200_QADD + 1 / MB200_QFUSE_ADD_RELU + 1
+    bool f32_z = false;    // fp32 ConvBias with a tensor added after the activation
+    int oc = 0, icpg = 0;  // fp32 ConvBias: output channels, input channels per group (symbol)
+    // table indices from the model file and the functions they resolved to
+    int kernel_id = -1, init_id = -1;
+    KernelFunc kernel_fn = nullptr;
+    InitFunc init_fn = nullptr;
     float ms_total = 0;
     int ms_count = 0;
 };
@@ -144,12 +165,15 @@ struct Network {
     int device_id = 0;
     cudaStream_t stream = nullptr;
     Device device{256, TinyNN_CUDA_SM100, nullptr, nullptr};
-    RuntimeOpt opt{nullptr, nullptr, 0};
+    RuntimeOpt opt{nullptr, nullptr, 0, nullptr};
     std::vector<uint8_t> owned_model;  // LITE_load_model_from_path
     std::vector<Tensor> weights;       // device-resident
     std::vector<std::string> weight_names;
     std::vector<const uint8_t*> weight_host;  // into the model buffer, until uploaded
     std::vector<Tensor> processed;     // packed filters
+    // function tables of a generated kernels.c, when the caller registered one
+    std::vector<KernelFunc> ext_kernels;
+    std::vector<InitFunc> ext_inits;
     void* weight_arena = nullptr;
     std::vector<DevModel> models;
     int active = 0;
@@ -279,11 +303,32 @@ bool parse_symbol(const std::string& sym, OpPlan* op) {
                    &op->dw, &used) != 9 ||
             used == 0)
             return false;
-        op->kind = OP_CONV;
         op->dense = strcmp(sparse, "DENSE") == 0;
         if (!op->dense && strcmp(sparse, "GROUP") != 0)
             return false;
         std::string rest = sym.substr(used);
+        int oc = 0, icpg = 0, used2 = 0;
+        if ((sscanf(rest.c_str(), "oc%d_icpg%d_f32%n", &oc, &icpg, &used2) == 2 && used2 > 0) ||
+            (icpg = 0, sscanf(rest.c_str(), "oc%d_f32%n", &oc, &used2) == 1 && used2 > 0)) {
+            // fp32 ConvBias: ..._oc<N>[_icpg<M>]_f32[_bias][_ACT][_z_ADD]
+            op->kind = OP_CONV_F32;
+            op->oc = oc;
+            op->icpg = icpg;
+            rest = rest.substr(used2);
+            if (ends_with(rest, "_z_ADD")) {
+                op->f32_z = true;
+                rest.resize(rest.size() - strlen("_z_ADD"));
+            }
+            op->has_bias = rest.find("_bias") != std::string::npos;
+            op->mode = ends_with(rest, "_H_SWISH")  ? MB200_F32_H_SWISH
+                       : ends_with(rest, "_RELU")   ? MB200_F32_RELU
+                       : ends_with(rest, "_SIGMOID") ? MB200_F32_SIGMOID
+                       : ends_with(rest, "_SILU")   ? MB200_F32_SILU
+                                                    : MB200_F32_IDENTITY;
+            op->needs_init = true;
+            return true;
+        }
+        op->kind = OP_CONV;
         if (rest.compare(0, 8, "qsi8qsi8") != 0)
             return false;
         // a fused elemwise step is spelled last: ..._z_QADD / ..._z_QFUSE_ADD_RELU
@@ -313,7 +358,7 @@ bool parse_symbol(const std::string& sym, OpPlan* op) {
         if (sscanf(sym.c_str() + p, "_NHWC_p%dx%d_s%dx%d_w%dx%d_", &op->ph, &op->pw, &op->sh,
                    &op->sw, &op->kh, &op->kw) != 6)
             return false;
-        op->kind = OP_POOL;
+        op->kind = ends_with(sym, "_f32f32") ? OP_POOL_F32 : OP_POOL;
         return true;
     }
     if (sym.compare(0, 33, "cuda_sm100_elementwise_multitype_") == 0) {
@@ -326,9 +371,44 @@ bool parse_symbol(const std::string& sym, OpPlan* op) {
         op->kind = OP_QELEM;
         return op->mode >= 0;
     }
+    if (sym.compare(0, 23, "cuda_sm100_elementwise_") == 0) {
+        const size_t p = sym.find("_f32");
+        if (p == std::string::npos)
+            return false;
+        const std::string mode = sym.substr(23, p - 23);
+        static const struct { const char* name; int code; } kModes[] = {
+                {"RELU", MB200_ELEM_RELU}, {"SIGMOID", MB200_ELEM_SIGMOID},
+                {"SILU", MB200_ELEM_SILU}, {"H_SWISH", MB200_ELEM_H_SWISH},
+                {"EXP", MB200_ELEM_EXP}, {"ADD", MB200_ELEM_ADD}, {"SUB", MB200_ELEM_SUB},
+                {"MUL", MB200_ELEM_MUL}, {"MAX", MB200_ELEM_MAX},
+                {"FUSE_ADD_RELU", MB200_ELEM_FUSE_ADD_RELU}};
+        op->mode = -1;
+        for (auto& m : kModes)
+            if (mode == m.name)
+                op->mode = m.code;
+        op->kind = OP_ELEM_F32;
+        return op->mode >= 0;
+    }
+    if (sym == "cuda_sm100_concat_NHWC_axis_1_f32") {
+        op->kind = OP_CONCAT_F32;
+        return true;
+    }
+    if (sym == "cuda_sm100_concat_focus_f32") {
+        op->kind = OP_FOCUS_F32;
+        return true;
+    }
+    if (sym == "cuda_sm100_resize_NHWC_NEAREST_f32") {
+        op->kind = OP_RESIZE_F32;
+        return true;
+    }
     if (sym == "cuda_sm100_matmul_nn_qsi8qsi8qsi32_typecvt_qsi8") {
         op->kind = OP_MATMUL;
         op->needs_init = true;  // B [K][N] is re-laid to [N][K]
+        return true;
+    }
+    if (sym == "cuda_sm100_matmul_nn_f32f32f32") {
+        op->kind = OP_MATMUL_F32;
+        op->needs_init = true;
         return true;
     }
     if (sym == "cuda_sm100_typecvt_qsi32qsi8") {
@@ -336,11 +416,11 @@ bool parse_symbol(const std::string& sym, OpPlan* op) {
         return true;
     }
     if (sym.compare(0, 30, "cuda_sm100_relayout_NCHW_NHWC_") == 0) {
-        op->kind = OP_RELAYOUT_TO_NHWC;
+        op->kind = ends_with(sym, "f32f32") ? OP_RELAYOUT_F32_TO_NHWC : OP_RELAYOUT_TO_NHWC;
         return true;
     }
     if (sym.compare(0, 30, "cuda_sm100_relayout_NHWC_NCHW_") == 0) {
-        op->kind = OP_RELAYOUT_TO_NCHW;
+        op->kind = ends_with(sym, "f32f32") ? OP_RELAYOUT_F32_TO_NCHW : OP_RELAYOUT_TO_NCHW;
         return true;
     }
     return false;
@@ -353,15 +433,15 @@ size_t nr_elems(const Tensor* t) {
     return n;
 }
 
-void fill_conv_param(const OpPlan& op, mb200_conv_param* p) {
-    const Tensor* src = op.inputs[0];
-    const Tensor* flt = op.inputs[1];
-    const Tensor* dst = op.outputs[0];
+void fill_conv_param(const OpPlan& op, Tensor* const* inputs, const Tensor* dst,
+                     mb200_conv_param* p) {
+    const Tensor* src = inputs[0];
+    const Tensor* flt = inputs[1];
+    memset(p, 0, sizeof(*p));
     p->n = src->layout.dims[0];
     p->ic = src->layout.dims[1];
     p->ih = src->layout.dims[2];
     p->iw = src->layout.dims[3];
-    p->oc = dst->layout.dims[1];
     p->kh = op.kh;
     p->kw = op.kw;
     p->stride_h = op.sh;
@@ -370,92 +450,408 @@ void fill_conv_param(const OpPlan& op, mb200_conv_param* p) {
     p->pad_w = op.pw;
     p->dilate_h = op.dh;
     p->dilate_w = op.dw;
-    p->groups = op.dense ? 1 : (int)flt->layout.dims[0];
+    // the original filter is [OC][IC][KH][KW] or [G][OCpg][ICpg][KH][KW]
+    const Layout& l = flt->layout;
+    p->groups = op.dense ? 1 : (int)l.dims[0];
+    p->oc = dst ? (int)dst->layout.dims[1]
+                : (op.dense ? (int)l.dims[0] : (int)(l.dims[0] * l.dims[1]));
     p->nonline = op.mode;
     p->src_scale = src->dtype.param.scale;
     p->flt_scale = flt->dtype.param.scale;
-    p->dst_scale = dst->dtype.param.scale;
+    p->dst_scale = dst ? dst->dtype.param.scale : 1.f;
 }
 
-// what the generated stub of op.symbol does (megcc_b200/compiler/cuda_kernel_pack.cpp)
-int run_op(const OpPlan& op, cudaStream_t st) {
+void fill_conv_f32_param(const OpPlan& op, Tensor* const* inputs, mb200_conv_f32_param* p) {
+    const Tensor* src = inputs[0];
+    const Layout& l = inputs[1]->layout;
+    memset(p, 0, sizeof(*p));
+    p->n = src->layout.dims[0];
+    p->ic = src->layout.dims[1];
+    p->ih = src->layout.dims[2];
+    p->iw = src->layout.dims[3];
+    p->oc = op.oc;
+    p->kh = op.kh;
+    p->kw = op.kw;
+    p->stride_h = op.sh;
+    p->stride_w = op.sw;
+    p->pad_h = op.ph;
+    p->pad_w = op.pw;
+    // the processed filter is a flat buffer: a grouped filter's channels per group are part
+    // of the symbol
+    (void)l;
+    p->groups = op.dense || op.icpg <= 0 ? 1 : p->ic / op.icpg;
+    p->nonline = op.mode;
+}
+
+int matrix_k(const Tensor* a) {
+    return (int)(nr_elems(a) / (size_t)a->layout.dims[0]);
+}
+
+// The library's own KernelFunc: what the generated stub of op.symbol does
+// (megcc_b200/compiler/cuda_kernel_pack.cpp). One function serves every symbol; the
+// attributes a stub has baked in come from the Opr's parsed symbol, which the VM passes in
+// RuntimeOpt::opr.
+TinyNNStatus builtin_kernel(
+        Tensor** inputs, int nr_input, Tensor** outputs, int nr_output, const Workspace* ws,
+        const RuntimeOpt* opt) {
+    if (!opt || !opt->opr || nr_input < 1 || nr_output < 1)
+        return TinyNN_ERROR_NULL_PTR;
+    const OpPlan& op = *(const OpPlan*)opt->opr;
+    void* st = opt->stream;
+    Tensor* dst = outputs[0];
     switch (op.kind) {
         case OP_CONV: {
             mb200_conv_param p;
-            fill_conv_param(op, &p);
-            const Tensor* src = op.inputs[0];
+            fill_conv_param(op, inputs, dst, &p);
+            const Tensor* src = inputs[0];
             // inputs: src, filter, [bias], [channel scales], [z, mid scale]
-            const size_t scale_idx = op.has_bias ? 3 : 2;
-            const size_t nr_plain = op.inputs.size() - (op.z_mode ? 2 : 0);
-            const int32_t* bias = op.has_bias ? (const int32_t*)op.inputs[2]->ptr : nullptr;
-            const float* ch =
-                    nr_plain > scale_idx ? (const float*)op.inputs[scale_idx]->ptr : nullptr;
+            const int scale_idx = op.has_bias ? 3 : 2;
+            const int nr_plain = nr_input - (op.z_mode ? 2 : 0);
+            const int32_t* bias = op.has_bias ? (const int32_t*)inputs[2]->ptr : nullptr;
+            const float* ch = nr_plain > scale_idx ? (const float*)inputs[scale_idx]->ptr : nullptr;
             if (op.z_mode) {
-                const Tensor* z = op.inputs[op.inputs.size() - 2];
+                const Tensor* z = inputs[nr_input - 2];
                 mb200_conv_fuse fuse;
                 fuse.z = (const int8_t*)z->ptr;
                 fuse.mode = op.z_mode - 1;
                 fuse.z_scale = z->dtype.param.scale;
-                fuse.out_scale = op.outputs[0]->dtype.param.scale;
-                p.dst_scale = op.inputs.back()->dtype.param.scale;  // scale of the ConvBias result
-                return mb200_conv_bias_qs8_nhwc_fused(
+                fuse.out_scale = dst->dtype.param.scale;
+                p.dst_scale = inputs[nr_input - 1]->dtype.param.scale;  // scale of the ConvBias result
+                return (TinyNNStatus)mb200_conv_bias_qs8_nhwc_fused(
                         &p, (const int8_t*)src->ptr, src->layout.format == TinyNN_NCHW,
-                        (const int8_t*)op.inputs[1]->ptr, bias, ch, &fuse,
-                        (int8_t*)op.outputs[0]->ptr, MB200_ALGO_AUTO, st);
+                        (const int8_t*)inputs[1]->ptr, bias, ch, &fuse, (int8_t*)dst->ptr,
+                        MB200_ALGO_AUTO, st);
             }
-            if (op.use_s2d)
-                return mb200_conv_bias_qs8_s2d(
+            if (mb200_conv_s2d_supported(&p))
+                return (TinyNNStatus)mb200_conv_bias_qs8_s2d(
                         &p, (const int8_t*)src->ptr, src->layout.format == TinyNN_NCHW,
-                        (const int8_t*)op.inputs[1]->ptr, bias, ch, (int8_t*)op.outputs[0]->ptr,
-                        op.ws.ptr, op.ws.size, st);
-            return mb200_conv_bias_qs8_nhwc(
+                        (const int8_t*)inputs[1]->ptr, bias, ch, (int8_t*)dst->ptr, ws->ptr,
+                        ws->size, st);
+            return (TinyNNStatus)mb200_conv_bias_qs8_nhwc(
                     &p, (const int8_t*)src->ptr, src->layout.format == TinyNN_NCHW,
-                    (const int8_t*)op.inputs[1]->ptr, bias, ch, (int8_t*)op.outputs[0]->ptr,
-                    MB200_ALGO_AUTO, st);
+                    (const int8_t*)inputs[1]->ptr, bias, ch, (int8_t*)dst->ptr, MB200_ALGO_AUTO, st);
         }
         case OP_POOL: {
-            const Tensor* s = op.inputs[0];
-            return mb200_pooling_qs8_nhwc(
-                    (const int8_t*)s->ptr, (int8_t*)op.outputs[0]->ptr, op.mode, s->layout.dims[0],
+            const Tensor* s = inputs[0];
+            return (TinyNNStatus)mb200_pooling_qs8_nhwc(
+                    (const int8_t*)s->ptr, (int8_t*)dst->ptr, op.mode, s->layout.dims[0],
                     s->layout.dims[1], s->layout.dims[2], s->layout.dims[3], op.kh, op.kw, op.sh,
                     op.sw, op.ph, op.pw, st);
         }
         case OP_QELEM: {
-            const Tensor* a = op.inputs[0];
-            const Tensor* b = op.inputs.size() > 1 ? op.inputs[1] : op.inputs[0];
-            return mb200_qelemwise_qs8(
-                    (const int8_t*)a->ptr, (const int8_t*)b->ptr, (int8_t*)op.outputs[0]->ptr,
-                    op.mode, nr_elems(a), a->dtype.param.scale, b->dtype.param.scale,
-                    op.outputs[0]->dtype.param.scale, st);
+            const Tensor* a = inputs[0];
+            const Tensor* b = nr_input > 1 ? inputs[1] : inputs[0];
+            return (TinyNNStatus)mb200_qelemwise_qs8(
+                    (const int8_t*)a->ptr, (const int8_t*)b->ptr, (int8_t*)dst->ptr, op.mode,
+                    nr_elems(a), a->dtype.param.scale, b->dtype.param.scale,
+                    dst->dtype.param.scale, st);
         }
         case OP_MATMUL: {
-            const Tensor* a = op.inputs[0];
-            const Tensor* b = op.inputs[1];  // re-laid to [N][K] at load
-            const Tensor* c = op.outputs[0];
-            const int m = a->layout.dims[0];
-            const int k = (int)(nr_elems(a) / (size_t)m);
-            const int n = c->layout.dims[1];
+            const Tensor* a = inputs[0];
+            const Tensor* b = inputs[1];  // re-laid to [N][K] at load
             // scale of the qint32 product: one float multiplication, as MegEngine records it
             const float acc_scale = a->dtype.param.scale * b->dtype.param.scale;
-            return mb200_matmul_s8_qs8(m, n, k, (const int8_t*)a->ptr, (const int8_t*)b->ptr,
-                                       (int8_t*)c->ptr, acc_scale, c->dtype.param.scale, st);
+            return (TinyNNStatus)mb200_matmul_s8_qs8(
+                    a->layout.dims[0], dst->layout.dims[1], matrix_k(a), (const int8_t*)a->ptr,
+                    (const int8_t*)b->ptr, (int8_t*)dst->ptr, acc_scale, dst->dtype.param.scale, st);
         }
         case OP_TYPECVT: {
-            const Tensor* s = op.inputs[0];
-            return mb200_typecvt_qs32_qs8(
-                    (const int32_t*)s->ptr, (int8_t*)op.outputs[0]->ptr, nr_elems(s),
-                    s->dtype.param.scale, op.outputs[0]->dtype.param.scale, st);
+            const Tensor* s = inputs[0];
+            return (TinyNNStatus)mb200_typecvt_qs32_qs8(
+                    (const int32_t*)s->ptr, (int8_t*)dst->ptr, nr_elems(s), s->dtype.param.scale,
+                    dst->dtype.param.scale, st);
         }
         case OP_RELAYOUT_TO_NHWC:
         case OP_RELAYOUT_TO_NCHW: {
-            const Tensor* s = op.inputs[0];
+            const Tensor* s = inputs[0];
             auto fn = op.kind == OP_RELAYOUT_TO_NHWC ? mb200_relayout_nchw_to_nhwc_s8
                                                      : mb200_relayout_nhwc_to_nchw_s8;
-            return fn((const int8_t*)s->ptr, (int8_t*)op.outputs[0]->ptr, s->layout.dims[0],
-                      s->layout.dims[1], s->layout.dims[2], s->layout.dims[3], st);
+            return (TinyNNStatus)fn((const int8_t*)s->ptr, (int8_t*)dst->ptr, s->layout.dims[0],
+                                    s->layout.dims[1], s->layout.dims[2], s->layout.dims[3], st);
         }
+        case OP_RELAYOUT_F32_TO_NHWC:
+        case OP_RELAYOUT_F32_TO_NCHW: {
+            const Tensor* s = inputs[0];
+            auto fn = op.kind == OP_RELAYOUT_F32_TO_NHWC ? mb200_relayout_nchw_to_nhwc_f32
+                                                         : mb200_relayout_nhwc_to_nchw_f32;
+            return (TinyNNStatus)fn((const float*)s->ptr, (float*)dst->ptr, s->layout.dims[0],
+                                    s->layout.dims[1], s->layout.dims[2], s->layout.dims[3], st);
+        }
+        case OP_CONV_F32: {
+            mb200_conv_f32_param p;
+            fill_conv_f32_param(op, inputs, &p);
+            const float* bias = op.has_bias ? (const float*)inputs[2]->ptr : nullptr;
+            const float* z = op.f32_z ? (const float*)inputs[nr_input - 1]->ptr : nullptr;
+            return (TinyNNStatus)mb200_conv_bias_f32_nhwc(
+                    &p, (const float*)inputs[0]->ptr, (const float*)inputs[1]->ptr, bias, z,
+                    (float*)dst->ptr, (long long)dst->layout.stride[3], ws->ptr, ws->size,
+                    MB200_ALGO_AUTO, st);
+        }
+        case OP_MATMUL_F32: {
+            const Tensor* a = inputs[0];
+            return (TinyNNStatus)mb200_matmul_f32(
+                    a->layout.dims[0], dst->layout.dims[1], matrix_k(a), (const float*)a->ptr,
+                    (const float*)inputs[1]->ptr, (float*)dst->ptr, ws->ptr, ws->size, st);
+        }
+        case OP_ELEM_F32: {
+            const Tensor* a = inputs[0];
+            const Tensor* b = nr_input > 1 ? inputs[1] : inputs[0];
+            return (TinyNNStatus)mb200_elemwise_f32(op.mode, (const float*)a->ptr,
+                                                    (const float*)b->ptr, (float*)dst->ptr,
+                                                    nr_elems(a), st);
+        }
+        case OP_CONCAT_F32: {
+            const float* srcs[8];
+            int channels[8];
+            if (nr_input > 8)
+                return TinyNN_ERROR_OUT_OF_RANGE;
+            for (int i = 0; i < nr_input; ++i) {
+                srcs[i] = (const float*)inputs[i]->ptr;
+                channels[i] = inputs[i]->layout.dims[1];
+            }
+            return (TinyNNStatus)mb200_concat_f32_nhwc(
+                    srcs, channels, nr_input, (float*)dst->ptr,
+                    (size_t)dst->layout.dims[0] * dst->layout.dims[2] * dst->layout.dims[3], st);
+        }
+        case OP_FOCUS_F32: {
+            const Tensor* s = inputs[0];
+            return (TinyNNStatus)mb200_focus_f32(
+                    (const float*)s->ptr, (float*)dst->ptr, s->layout.dims[0], s->layout.dims[1],
+                    s->layout.dims[2], s->layout.dims[3], dst->layout.dims[1], st);
+        }
+        case OP_RESIZE_F32: {
+            const Tensor* s = inputs[0];
+            return (TinyNNStatus)mb200_resize_nearest_f32_nhwc(
+                    (const float*)s->ptr, (float*)dst->ptr, s->layout.dims[0], s->layout.dims[1],
+                    s->layout.dims[2], s->layout.dims[3], dst->layout.dims[2], dst->layout.dims[3],
+                    st);
+        }
+        case OP_POOL_F32: {
+            const Tensor* s = inputs[0];
+            return (TinyNNStatus)mb200_pooling_f32_nhwc(
+                    (const float*)s->ptr, (float*)dst->ptr, op.mode, s->layout.dims[0],
+                    s->layout.dims[1], s->layout.dims[2], s->layout.dims[3], op.kh, op.kw, op.sh,
+                    op.sw, op.ph, op.pw, st);
+        }
+        case OP_EXTERNAL:
+            break;
     }
     return TinyNN_ERROR_NO_IMPLEMENT;
+}
+
+// The library's own InitFunc, in the three-phase protocol of runtime/src/data_struct.h
+// :135-142 (count -> describe -> fill): ConvBias filters are re-laid K-major (or into the
+// space-to-depth / tf32-plane forms), MatrixMul's B is transposed.
+TinyNNStatus builtin_init(
+        Tensor** inputs, int nr_input, Tensor* out_weights, int* nr_out_weight,
+        const RuntimeOpt* opt) {
+    if (!opt || !opt->opr || nr_input < 2)
+        return TinyNN_ERROR_NULL_PTR;
+    const OpPlan& op = *(const OpPlan*)opt->opr;
+    if (!op.needs_init) {
+        if (nr_out_weight)
+            *nr_out_weight = 0;
+        return TinyNN_SUCCESS;
+    }
+    if (!out_weights && nr_out_weight) {
+        *nr_out_weight = 1;
+        return TinyNN_SUCCESS;
+    }
+    Tensor* w = inputs[1];
+    const bool describe = out_weights && !nr_out_weight;
+    auto flat = [&](size_t elems) {
+        out_weights->layout.nr_dim = 1;
+        out_weights->layout.dims[0] = (uint32_t)elems;
+        out_weights->layout.stride[0] = 1;
+        out_weights->layout.format = w->layout.format;
+        out_weights->dtype = w->dtype;
+        out_weights->name = w->name;
+    };
+    switch (op.kind) {
+        case OP_CONV: {
+            if (w->layout.nr_dim != 4 && w->layout.nr_dim != 5)
+                return TinyNN_ERROR_INVALID_LAYOUT;
+            mb200_conv_param p;
+            fill_conv_param(op, inputs, nullptr, &p);
+            const bool s2d = !op.z_mode && mb200_conv_s2d_supported(&p);
+            if (describe) {
+                // the K-major filter keeps the layout (the kernel reads the group count from
+                // it); the space-to-depth packing is a flat byte buffer
+                if (s2d) {
+                    flat(mb200_conv_s2d_filter_bytes(&p));
+                } else {
+                    out_weights->layout = w->layout;
+                    out_weights->dtype = w->dtype;
+                    out_weights->name = w->name;
+                }
+                return TinyNN_SUCCESS;
+            }
+            return (TinyNNStatus)(
+                    s2d ? mb200_conv_s2d_pack_filter(&p, (const int8_t*)w->ptr,
+                                                     (int8_t*)out_weights->ptr, opt->stream)
+                        : mb200_conv_pack_filter(&p, (const int8_t*)w->ptr,
+                                                 (int8_t*)out_weights->ptr, opt->stream));
+        }
+        case OP_MATMUL: {
+            if (w->layout.nr_dim != 2)
+                return TinyNN_ERROR_INVALID_LAYOUT;
+            const int k = w->layout.dims[0], n = w->layout.dims[1];
+            if (describe) {
+                flat((size_t)k * n);
+                return TinyNN_SUCCESS;
+            }
+            return (TinyNNStatus)mb200_matmul_pack_b(k, n, (const int8_t*)w->ptr,
+                                                     (int8_t*)out_weights->ptr, opt->stream);
+        }
+        case OP_CONV_F32: {
+            if (w->layout.nr_dim != 4 && w->layout.nr_dim != 5)
+                return TinyNN_ERROR_INVALID_LAYOUT;
+            mb200_conv_f32_param p;
+            fill_conv_f32_param(op, inputs, &p);
+            if (describe) {
+                flat(mb200_conv_f32_packed_filter_bytes(&p) / 4);
+                return TinyNN_SUCCESS;
+            }
+            return (TinyNNStatus)mb200_conv_f32_pack_filter(
+                    &p, (const float*)w->ptr, (float*)out_weights->ptr, opt->stream);
+        }
+        case OP_MATMUL_F32: {
+            if (w->layout.nr_dim != 2)
+                return TinyNN_ERROR_INVALID_LAYOUT;
+            const int k = w->layout.dims[0], n = w->layout.dims[1];
+            if (describe) {
+                flat(mb200_matmul_f32_packed_b_bytes(k, n) / 4);
+                return TinyNN_SUCCESS;
+            }
+            return (TinyNNStatus)mb200_matmul_f32_pack_b(k, n, (const float*)w->ptr,
+                                                         (float*)out_weights->ptr, opt->stream);
+        }
+        default:
+            break;
+    }
+    return TinyNN_ERROR_NO_IMPLEMENT;
+}
+
+// Operand ranks and extents of an instruction against what its kernel will compute, so that a
+// truncated or hand-edited model cannot make a kernel read or write outside its tensors.
+// Returns a description of the first inconsistency, or nullptr.
+const char* check_operands(const OpPlan& op) {
+    auto rank4 = [](const Tensor* t) { return t->layout.nr_dim == 4; };
+    auto extent = [](int in, int k, int s, int p) { return (in + 2 * p - k) / s + 1; };
+    const Tensor* in0 = op.inputs[0];
+    const Tensor* out = op.outputs[0];
+    switch (op.kind) {
+        case OP_CONV:
+        case OP_CONV_F32: {
+            const Tensor* flt = op.inputs[1];
+            if (!rank4(in0) || !rank4(out))
+                return "ConvBias operands must have 4 dims";
+            if (!flt->is_weight || (flt->layout.nr_dim != 4 && flt->layout.nr_dim != 5))
+                return "ConvBias filter must be a weight with 4 or 5 dims";
+            if (op.kh <= 0 || op.kw <= 0 || op.sh <= 0 || op.sw <= 0)
+                return "ConvBias attributes";
+            const Layout& l = flt->layout;
+            const size_t oc = l.nr_dim == 4 ? l.dims[0] : (size_t)l.dims[0] * l.dims[1];
+            const size_t icpg = l.nr_dim == 4 ? l.dims[1] : l.dims[2];
+            const size_t groups = l.nr_dim == 4 ? 1 : l.dims[0];
+            if (l.dims[l.nr_dim - 2] != (uint32_t)op.kh || l.dims[l.nr_dim - 1] != (uint32_t)op.kw)
+                return "filter extent differs from the symbol";
+            if (icpg * groups != in0->layout.dims[1] || oc != out->layout.dims[1] ||
+                (op.dense != (l.nr_dim == 4)))
+                return "filter channels do not match the tensors";
+            if (out->layout.dims[0] != in0->layout.dims[0] ||
+                (int)out->layout.dims[2] != extent(in0->layout.dims[2], op.kh, op.sh, op.ph) ||
+                (int)out->layout.dims[3] != extent(in0->layout.dims[3], op.kw, op.sw, op.pw))
+                return "output extent differs from what the ConvBias computes";
+            const size_t extra = op.inputs.size() - 2;
+            size_t idx = 2;
+            if (op.has_bias) {
+                if (extra < 1 || nr_elems(op.inputs[2]) != oc || !op.inputs[2]->is_weight)
+                    return "bias must be a weight with one value per output channel";
+                ++idx;
+            }
+            if (op.kind == OP_CONV_F32) {
+                if (op.oc != (int)oc)
+                    return "output channels differ from the symbol";
+                if (op.f32_z && (op.inputs.size() <= idx || op.inputs.back()->size != out->size))
+                    return "z does not match the output";
+            } else if (op.inputs.size() - (op.z_mode ? 2 : 0) > idx &&
+                       nr_elems(op.inputs[idx]) != oc) {
+                return "channel scales must hold one value per output channel";
+            }
+            return nullptr;
+        }
+        case OP_POOL:
+        case OP_POOL_F32:
+            if (!rank4(in0) || !rank4(out))
+                return "Pooling operands must have 4 dims";
+            if (op.kh <= 0 || op.kw <= 0 || op.sh <= 0 || op.sw <= 0 ||
+                out->layout.dims[0] != in0->layout.dims[0] ||
+                out->layout.dims[1] != in0->layout.dims[1] ||
+                (int)out->layout.dims[2] != extent(in0->layout.dims[2], op.kh, op.sh, op.ph) ||
+                (int)out->layout.dims[3] != extent(in0->layout.dims[3], op.kw, op.sw, op.pw))
+                return "output extent differs from what the Pooling computes";
+            return nullptr;
+        case OP_MATMUL:
+        case OP_MATMUL_F32: {
+            const Tensor* b = op.inputs[1];
+            if (!b->is_weight || b->layout.nr_dim != 2 || in0->layout.nr_dim < 2 ||
+                out->layout.nr_dim < 2)
+                return "MatrixMul operands";
+            if (nr_elems(in0) != (size_t)in0->layout.dims[0] * b->layout.dims[0] ||
+                nr_elems(out) != (size_t)in0->layout.dims[0] * b->layout.dims[1] ||
+                out->layout.dims[0] != in0->layout.dims[0] || out->layout.dims[1] != b->layout.dims[1])
+                return "MatrixMul extents do not match";
+            return nullptr;
+        }
+        case OP_RELAYOUT_TO_NHWC:
+        case OP_RELAYOUT_TO_NCHW:
+        case OP_RELAYOUT_F32_TO_NHWC:
+        case OP_RELAYOUT_F32_TO_NCHW:
+            if (!rank4(in0) || !rank4(out) || in0->size != out->size)
+                return "Relayout operands must be 4-dim tensors of one size";
+            for (int d = 0; d < 4; ++d)
+                if (in0->layout.dims[d] != out->layout.dims[d])
+                    return "Relayout keeps the logical extents";
+            return nullptr;
+        case OP_QELEM:
+        case OP_ELEM_F32:
+            for (auto* t : op.inputs)
+                if (t->size != out->size)
+                    return "elementwise operands must have the output's size";
+            return nullptr;
+        case OP_TYPECVT:
+            return nr_elems(in0) == nr_elems(out) ? nullptr : "TypeCvt element counts differ";
+        case OP_CONCAT_F32: {
+            if (!rank4(out) || op.inputs.size() > 8)
+                return "Concat takes up to 8 inputs and a 4-dim output";
+            size_t c = 0;
+            for (auto* t : op.inputs) {
+                if (!rank4(t) || t->layout.dims[0] != out->layout.dims[0] ||
+                    t->layout.dims[2] != out->layout.dims[2] ||
+                    t->layout.dims[3] != out->layout.dims[3])
+                    return "Concat inputs must share the output's batch and spatial extents";
+                c += t->layout.dims[1];
+            }
+            return c == out->layout.dims[1] ? nullptr : "Concat channel counts do not add up";
+        }
+        case OP_FOCUS_F32:
+            if (!rank4(in0) || !rank4(out) || (in0->layout.dims[2] & 1) ||
+                (in0->layout.dims[3] & 1) || out->layout.dims[0] != in0->layout.dims[0] ||
+                out->layout.dims[1] < 4 * in0->layout.dims[1] ||
+                out->layout.dims[2] * 2 != in0->layout.dims[2] ||
+                out->layout.dims[3] * 2 != in0->layout.dims[3])
+                return "Focus extents do not match";
+            return nullptr;
+        case OP_RESIZE_F32:
+            if (!rank4(in0) || !rank4(out) || out->layout.dims[0] != in0->layout.dims[0] ||
+                out->layout.dims[1] != in0->layout.dims[1])
+                return "Resize keeps batch and channels";
+            return nullptr;
+        case OP_EXTERNAL:
+            return nullptr;
+    }
+    return nullptr;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -526,6 +922,8 @@ int parse_model(Network* net, const void* mem, size_t size) {
             return fail(TinyNN_ERROR_NO_IMPLEMENT, "compressed weights are not supported");
         const fb::Vec data = w.vec(fb::field::W_data, 1);
         t.size = tensor_bytes(t);
+        if (t.size == SIZE_MAX)
+            return fail(TinyNN_ERROR_MODEL_PARSE, "weight %u: extents overflow", i);
         if (!data || data.len != t.size)
             return fail(TinyNN_ERROR_MODEL_PARSE, "weight %u: %u data bytes for a %zu byte layout",
                         i, data ? data.len : 0, t.size);
@@ -566,7 +964,9 @@ int parse_model(Network* net, const void* mem, size_t size) {
                 return fail(TinyNN_ERROR_NO_IMPLEMENT, "dynamic-shape tensors are not supported");
             const int64_t off = tt.scalar<int64_t>(fb::field::T_offset, 0);
             t.size = tensor_bytes(t);
-            if (off < 0 || (size_t)off + t.size > m.tensor_memory)
+            if (t.size == SIZE_MAX)
+                return fail(TinyNN_ERROR_MODEL_PARSE, "tensor %u: extents overflow", i);
+            if (off < 0 || (size_t)off > m.tensor_memory || t.size > m.tensor_memory - (size_t)off)
                 return fail(TinyNN_ERROR_MODEL_PARSE,
                             "tensor %u at offset %lld (+%zu) lies outside the %zu byte arena", i,
                             (long long)off, t.size, m.tensor_memory);
@@ -615,10 +1015,37 @@ int parse_model(Network* net, const void* mem, size_t size) {
             if (tag == fb::INST_OPR) {
                 ins.is_opr = true;
                 std::string type;
-                if (!it.str(fb::field::O_type, &type) || !parse_symbol(type, &ins.op))
+                if (!it.str(fb::field::O_type, &type))
+                    return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u has no type", i);
+                // Dispatch goes through the function tables by kernel_id / init_id
+                // (runtime/src/vm/op.c:161-163): a registered table entry wins, else the
+                // library's own implementation of the symbol fills the slot.
+                const bool known = parse_symbol(type, &ins.op);
+                ins.op.kernel_id = it.scalar<int32_t>(fb::field::O_kernel_id, -1);
+                ins.op.init_id = it.scalar<int32_t>(fb::field::O_init_id, -1);
+                KernelFunc ext = ins.op.kernel_id >= 0 &&
+                                                 (size_t)ins.op.kernel_id < net->ext_kernels.size()
+                                         ? net->ext_kernels[ins.op.kernel_id]
+                                         : nullptr;
+                if (ext) {
+                    ins.op.kernel_fn = ext;
+                    ins.op.init_fn = ins.op.init_id >= 0 &&
+                                                     (size_t)ins.op.init_id < net->ext_inits.size()
+                                             ? net->ext_inits[ins.op.init_id]
+                                             : nullptr;
+                    if (!known) {
+                        ins.op.kind = OP_EXTERNAL;
+                        ins.op.symbol = type;
+                    }
+                } else if (known) {
+                    ins.op.kernel_fn = builtin_kernel;
+                    ins.op.init_fn = ins.op.needs_init ? builtin_init : nullptr;
+                } else {
                     return fail(TinyNN_ERROR_NO_FOUND,
-                                "instruction %u: no sm_100a kernel for symbol '%s'", i,
-                                type.c_str());
+                                "instruction %u: no sm_100a kernel for symbol '%s' and no "
+                                "registered kernel table entry %d", i, type.c_str(),
+                                ins.op.kernel_id);
+                }
                 it.str(fb::field::O_name, &ins.op.name);
                 const fb::Vec in = it.vec(fb::field::O_inputs, 4);
                 const fb::Vec in_t = it.vec(fb::field::O_input_types, 1);
@@ -650,9 +1077,15 @@ int parse_model(Network* net, const void* mem, size_t size) {
                 if (ins.op.ws.size && ins.op.ws.offset + ins.op.ws.size > m.tensor_memory)
                     return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: workspace outside arena",
                                 i);
-                const size_t need_in = ins.op.kind == OP_CONV ? 2 : 1;
+                const size_t need_in = (ins.op.kind == OP_CONV || ins.op.kind == OP_CONV_F32 ||
+                                        ins.op.kind == OP_MATMUL || ins.op.kind == OP_MATMUL_F32)
+                                               ? 2
+                                               : 1;
                 if (ins.op.inputs.size() < need_in || ins.op.outputs.empty())
                     return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: too few operands", i);
+                if (const char* why = check_operands(ins.op))
+                    return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u (%s): %s", i,
+                                type.c_str(), why);
                 if (ins.op.kind == OP_CONV &&
                     ins.op.inputs.size() < (size_t)(ins.op.has_bias ? 3 : 2) + (ins.op.z_mode ? 2 : 0))
                     return fail(TinyNN_ERROR_MODEL_PARSE, "instruction %u: conv operand missing", i);
@@ -688,7 +1121,14 @@ int parse_model(Network* net, const void* mem, size_t size) {
     return TinyNN_SUCCESS;
 }
 
-// weights -> one device allocation, then the Init step of every ConvBias
+// weights -> one device allocation, then the Init step of every Opr that has one, through
+// its InitFunc in the reference's three-phase protocol (runtime/src/init.c:29-131):
+//   init(inputs, n, NULL, &count)   how many processed weights (at most one)
+//   init(inputs, n, &w, NULL)       layout / dtype / name of the processed weight
+//   init(inputs, n, &w, &count)     fill w.ptr (device memory here)
+// after which the Opr's input whose name pointer equals the processed weight's is swapped for
+// it (runtime/src/init.c:59-92). Oprs that preprocess the same weight in the same way share
+// the result.
 int upload_weights(Network* net) {
     std::vector<const uint8_t*>& host_data = net->weight_host;
     cudaError_t e = cudaSetDevice(net->device_id);
@@ -699,44 +1139,82 @@ int upload_weights(Network* net) {
     net->opt.device = &net->device;
     net->opt.stream = net->stream;
     net->opt.device_id = net->device_id;
+    net->opt.opr = nullptr;
 
     auto up = [](size_t v) { return (v + 255) / 256 * 256; };
     size_t total = 0;
     for (auto& w : net->weights)
         total += up(w.size);
-    // packed copies of the conv filters (the Init step)
-    std::vector<std::pair<OpPlan*, int>> packs;  // op, filter index in weights
-    for (auto& m : net->models)
-        for (auto& ins : m.instrs)
-            if (ins.is_opr && ins.op.needs_init) {
-                Tensor* f = ins.op.inputs[1];
-                if (!f->is_weight)
-                    return fail(TinyNN_ERROR_NO_IMPLEMENT, "conv filter must be a weight");
-                packs.push_back({&ins.op, (int)(f - net->weights.data())});
-            }
-    // one processed copy per (filter, packing): the standard K-major packing, or the
-    // space-to-depth packing when the Opr qualifies and the compiler gave it a workspace
-    std::vector<int> packed_of(net->weights.size() * 2, -1);
-    std::vector<int> pack_mode;  // per entry of `packs`
-    for (auto& pk : packs) {
-        mb200_conv_param cp;
-        if (pk.first->kind == OP_CONV)
-            fill_conv_param(*pk.first, &cp);
-        const bool s2d = pk.first->kind == OP_CONV && !pk.first->z_mode &&
-                         mb200_conv_s2d_supported(&cp) &&
-                         pk.first->ws.size >= mb200_conv_s2d_workspace_bytes(&cp);
-        pk.first->use_s2d = s2d;
-        pack_mode.push_back(s2d ? 1 : 0);
-        const size_t key = (size_t)pk.second * 2 + (s2d ? 1 : 0);
-        if (packed_of[key] < 0) {
-            packed_of[key] = (int)net->processed.size();
-            Tensor t = net->weights[pk.second];
-            if (s2d)
-                t.size = mb200_conv_s2d_filter_bytes(&cp);
-            net->processed.push_back(t);
-            total += up(t.size);
+
+    struct Job {
+        OpPlan* op;
+        int input;      // which input the processed weight replaces
+        int processed;  // index into net->processed
+        bool fill;      // this job runs phase three (the others reuse its result)
+    };
+    std::vector<Job> jobs;
+    struct Key {
+        const Tensor* weight;
+        void* fn;
+        std::string symbol;
+        size_t bytes;
+        bool operator==(const Key& o) const {
+            return weight == o.weight && fn == o.fn && symbol == o.symbol && bytes == o.bytes;
         }
-    }
+    };
+    std::vector<std::pair<Key, int>> seen;
+    std::vector<Tensor> described;
+    for (auto& m : net->models)
+        for (auto& ins : m.instrs) {
+            if (!ins.is_opr || !ins.op.init_fn)
+                continue;
+            OpPlan& op = ins.op;
+            RuntimeOpt opt = net->opt;
+            opt.opr = &op;
+            int count = 0;
+            int rc = op.init_fn(op.inputs.data(), (int)op.inputs.size(), nullptr, &count, &opt);
+            if (rc)
+                return fail(rc, "init of %s: %s", op.symbol.c_str(), mb200_last_error());
+            if (count == 0)
+                continue;
+            if (count != 1)
+                return fail(TinyNN_ERROR_NO_IMPLEMENT,
+                            "init of %s wants %d processed weights; one is supported",
+                            op.symbol.c_str(), count);
+            Tensor w;
+            memset(&w, 0, sizeof(w));
+            rc = op.init_fn(op.inputs.data(), (int)op.inputs.size(), &w, nullptr, &opt);
+            if (rc)
+                return fail(rc, "init of %s: %s", op.symbol.c_str(), mb200_last_error());
+            int input = -1;
+            for (size_t j = 0; j < op.inputs.size(); ++j)
+                if (op.inputs[j]->is_weight && op.inputs[j]->name == w.name)
+                    input = (int)j;
+            if (input < 0)
+                return fail(TinyNN_ERROR_NO_FOUND,
+                            "init of %s names a processed weight that matches no input",
+                            op.symbol.c_str());
+            w.size = tensor_bytes(w);
+            if (w.size == SIZE_MAX || w.size == 0)
+                return fail(TinyNN_ERROR_INVALID_LAYOUT, "init of %s: bad processed layout",
+                            op.symbol.c_str());
+            w.is_weight = 1;
+            const Key key{op.inputs[input], (void*)op.init_fn, op.symbol, w.size};
+            int idx = -1;
+            for (auto& sk : seen)
+                if (sk.first == key)
+                    idx = sk.second;
+            const bool fresh = idx < 0;
+            if (fresh) {
+                idx = (int)described.size();
+                described.push_back(w);
+                seen.push_back({key, idx});
+                total += up(w.size);
+            }
+            jobs.push_back({&op, input, idx, fresh});
+        }
+    net->processed = described;  // no growth from here on: jobs point into it
+
     if (total == 0)
         total = 256;
     if ((e = cudaMalloc(&net->weight_arena, total)) != cudaSuccess)
@@ -755,44 +1233,22 @@ int upload_weights(Network* net) {
         pw.ptr = (uint8_t*)net->weight_arena + off;
         off += up(pw.size);
     }
-    // Init: pack each filter once, then point the Oprs at the processed weight
-    // (the swap the reference performs in runtime/src/init.c:59-92)
-    std::vector<char> done(net->processed.size(), 0);
-    for (size_t k = 0; k < packs.size(); ++k) {
-        OpPlan* op = packs[k].first;
-        const int wi = packs[k].second;
-        const int pi = packed_of[(size_t)wi * 2 + pack_mode[k]];
-        Tensor* src = &net->weights[wi];
-        Tensor* dst = &net->processed[pi];
-        if (!done[pi] && op->kind == OP_MATMUL) {
-            const Layout& l = src->layout;
-            if (l.nr_dim != 2)
-                return fail(TinyNN_ERROR_INVALID_LAYOUT, "MatrixMul weight must have 2 dims");
-            const int rc = mb200_matmul_pack_b((int)l.dims[0], (int)l.dims[1],
-                                               (const int8_t*)src->ptr, (int8_t*)dst->ptr,
-                                               net->stream);
-            if (rc)
-                return fail(rc, "re-laying matrix '%s': %s", src->name, mb200_last_error());
-            done[pi] = 1;
-        }
-        if (!done[pi]) {
-            const Layout& l = src->layout;
-            if (l.nr_dim != 4 && l.nr_dim != 5)
-                return fail(TinyNN_ERROR_INVALID_LAYOUT, "conv filter must have 4 or 5 dims");
-            mb200_conv_param p;
-            fill_conv_param(*op, &p);
-            const int rc =
-                    pack_mode[k]
-                            ? mb200_conv_s2d_pack_filter(&p, (const int8_t*)src->ptr,
-                                                         (int8_t*)dst->ptr, net->stream)
-                            : mb200_conv_pack_filter(&p, (const int8_t*)src->ptr,
-                                                     (int8_t*)dst->ptr, net->stream);
-            if (rc)
-                return fail(rc, "packing filter '%s': %s", src->name, mb200_last_error());
-            done[pi] = 1;
-        }
-        op->inputs[1] = dst;
+    // phase three with the original weights in place, then the swap
+    for (auto& job : jobs) {
+        if (!job.fill)
+            continue;
+        RuntimeOpt opt = net->opt;
+        opt.opr = job.op;
+        int count = 1;
+        const int rc = job.op->init_fn(job.op->inputs.data(), (int)job.op->inputs.size(),
+                                       &net->processed[job.processed], &count, &opt);
+        if (rc)
+            return fail(rc, "preprocessing weight '%s' for %s: %s",
+                        job.op->inputs[job.input]->name, job.op->symbol.c_str(),
+                        mb200_last_error());
     }
+    for (auto& job : jobs)
+        job.op->inputs[job.input] = &net->processed[job.processed];
     if ((e = cudaStreamSynchronize(net->stream)) != cudaSuccess)
         return cuda_fail(e, "weight upload");
     if (!mb200::device_status_word(net->stream))
@@ -855,7 +1311,12 @@ int issue_instructions(Network* net, DevModel& m, bool timed) {
             continue;  // memforward is resolved when the arena is laid out
         if (timed)
             cudaEventRecord(ev0, net->stream);
-        const int rc = run_op(ins.op, net->stream);
+        // kernels[opr->kernel_id](inputs, nr_input, outputs, nr_output, &workspace, &opt)
+        RuntimeOpt opt = net->opt;
+        opt.opr = &ins.op;
+        const int rc = ins.op.kernel_fn(ins.op.inputs.data(), (int)ins.op.inputs.size(),
+                                        ins.op.outputs.data(), (int)ins.op.outputs.size(),
+                                        &ins.op.ws, &opt);
         if (rc)
             return fail(rc, "kernel %s: %s", ins.op.symbol.c_str(), mb200_last_error());
         if (timed) {
@@ -1394,6 +1855,21 @@ int mb200_lite_stream(const LiteNetwork network, void** stream) {
     if (!network || !stream)
         return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
     *stream = as_net(network)->stream;
+    return TinyNN_SUCCESS;
+}
+
+int mb200_lite_set_kernel_tables(
+        LiteNetwork network, const void* kernel_table, int nr_kernels, const void* init_table,
+        int nr_init) {
+    const KernelFunc* kernels = (const KernelFunc*)kernel_table;
+    const InitFunc* init_kernels = (const InitFunc*)init_table;
+    if (!network || (nr_kernels > 0 && !kernels) || (nr_init > 0 && !init_kernels))
+        return fail(TinyNN_ERROR_NULL_PTR, "input pointer is NULL");
+    Network* net = as_net(network);
+    if (net->loaded)
+        return fail(TinyNN_ERROR, "kernel tables must be registered before the model is loaded");
+    net->ext_kernels.assign(kernels, kernels + (nr_kernels > 0 ? nr_kernels : 0));
+    net->ext_inits.assign(init_kernels, init_kernels + (nr_init > 0 ? nr_init : 0));
     return TinyNN_SUCCESS;
 }
 

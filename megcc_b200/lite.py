@@ -73,6 +73,7 @@ SIGNATURES = {
     "mb200_lite_stream": (C.c_int, [_P, C.POINTER(_P)]),
     "mb200_lite_set_profile": (C.c_int, [_P, C.c_int]),
     "mb200_lite_set_option": (C.c_int, [_P, C.c_char_p, C.c_int]),
+    "mb200_lite_set_kernel_tables": (C.c_int, [_P, _P, C.c_int, _P, C.c_int]),
     "mb200_lite_profile": (C.c_int, [_P, C.c_char_p, C.c_size_t]),
 }
 
@@ -107,7 +108,9 @@ class Network:
     """One LiteNetwork. ``device_outputs``/``device_inputs`` name the I/O tensors that stay
     in device memory (LiteIO.is_host = 0)."""
 
-    def __init__(self, model_bytes, device_id=0, device_io=()):
+    def __init__(self, model_bytes, device_id=0, device_io=(), kernel_tables=None):
+        """kernel_tables: (address of kernels[], count, address of init_kernels[], count) of a
+        generated kernels.c that was compiled and loaded by the caller, or None."""
         L = lib()
         cfg = L.default_config().contents
         cfg = LiteConfig.from_buffer_copy(cfg)
@@ -122,6 +125,9 @@ class Network:
             io.output_size = len(self._io_keep)
         self._net = _P()
         check(L.LITE_make_network(C.byref(self._net), cfg, io))
+        if kernel_tables is not None:
+            k, nk, i, ni = kernel_tables
+            check(L.mb200_lite_set_kernel_tables(self._net, _P(k), nk, _P(i), ni))
         # the runtime borrows the buffer for the life of the network
         self._model = C.create_string_buffer(model_bytes, len(model_bytes))
         try:

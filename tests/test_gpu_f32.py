@@ -144,3 +144,67 @@ def test_concat_resize_pool_focus_relayout_are_exact(ops, oracle):
     assert (to_nchw(got) == oracle.focus_f32(img, 16)).all()
     y = ops.nchw_to_nhwc_f32(dev(x))
     assert (ops.nhwc_to_nchw_f32(y).cpu().numpy() == x).all()
+
+
+# ---- whole fp32 models through the compiler and the LITE_* runtime -------------------------
+def run_f32_model(spec, x, forwards=3):
+    from megcc_b200 import lite
+    from oracle import netwalk, oracle as O
+    want = netwalk.run_f32(spec, x, O)
+    net = lite.Network(spec.to_graph().compile([x.shape[0]]))
+    outs = []
+    for _ in range(forwards):  # eager, capture, replay
+        net.set_input("data", x)
+        net.forward()
+        net.wait()
+        outs.append([net.output(n, dtype=np.float32).reshape(w.shape)
+                     for n, w in zip(net.output_names(), want)])
+    net.close()
+    return outs, want
+
+
+@pytest.mark.parametrize("hw,batch", [(128, 4), (64, 2), (224, 1)])
+def test_yolox_s_matches_oracle(ops, hw, batch):
+    """YOLOX-s-style detector (83 ConvBias layers, SPP, PAFPN, three decoupled heads) against
+    the CPU checker walking the same layer list. 128 x 128 at batch 4 runs nearly every
+    ConvBias on the tensor cores; 64 x 64 at batch 2 leaves the deep, small maps to the
+    general kernel."""
+    from megcc_b200 import zoo
+    spec = zoo.yolox_s(hw=hw)
+    x = cases.rng_for(f"yolox_{hw}").uniform(0, 1, (batch, 3, hw, hw)).astype(np.float32)
+    outs, want = run_f32_model(spec, x)
+    for i, got in enumerate(outs):
+        for g, w in zip(got, want):
+            close(g, w)
+    # the outputs must exercise the arithmetic: regressions and scores spread, nothing
+    # collapsed to a constant or saturated
+    assert all(w[:, :4].std() > 0.1 and 0.02 < w[:, 5:].std() < 0.45 for w in want)
+    assert ops.device_status() == 0
+
+
+def test_fp32_matmul_model_matches_oracle(ops, oracle):
+    """conv -> global average pool -> MatrixMul (fp32) through the compiler and the runtime."""
+    from megcc_b200 import lite
+    from megcc_b200.compiler import Graph
+    r = cases.rng_for("f32_gap_matmul")
+    n = 256
+    g = Graph("gap_matmul_f32")
+    x = g.input_f32("data", 32, 8, 8)
+    f = (r.standard_normal((64, 32, 3, 3)) / 17).astype(np.float32)
+    y = g.conv_f32("conv", x, f, None, 1, 1, "RELU")
+    y = g.pooling("gap", y, "AVERAGE", 8, 8, 0)
+    b = r.standard_normal((64, 200)).astype(np.float32)
+    y = g.matmul_f32("fc", y, b)
+    g.mark_output(y)
+    src = r.standard_normal((n, 32, 8, 8)).astype(np.float32)
+    conv = oracle.conv_bias_f32(src, f, None, 1, 1, "RELU")
+    pooled = oracle.pooling_f32(conv, "AVERAGE", 8, 8, 0).reshape(n, 64)
+    want = oracle.matmul_f32(pooled, b)
+    net = lite.Network(g.compile([n]))
+    for _ in range(3):
+        net.set_input("data", src)
+        net.forward()
+        net.wait()
+        got = net.output(net.output_names()[0], dtype=np.float32).reshape(n, 200)
+        close(got, want, RTOL, 3 * ATOL)
+    net.close()
