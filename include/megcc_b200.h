@@ -24,8 +24,8 @@
  *
  * Scale range. Results are bit-identical to the reference's x86 kernels for every finite
  * positive scale triple. The vector and tensor-core kernels divide by dst_scale with a
- * three-instruction sequence that is exact for 2^-100 <= src_scale * flt_scale <= 2^69 and
- * 2^-60 <= dst_scale <= 2^60; outside that range MB200_ALGO_AUTO runs the general kernel
+ * three-instruction sequence that is exact for 2^-100 <= src_scale * flt_scale <= 2^69,
+ * 2^-100 <= dst_scale <= 2^100 and a ratio of the two within 2^-60 .. 2^60; outside that range MB200_ALGO_AUTO runs the general kernel
  * with the true division. One scale per output channel (flt_scales) must lie inside the
  * range by contract: the array is device memory and is not inspected by the host.
  */
@@ -107,6 +107,13 @@ MB200_API int mb200_device_status(void* stream, int* status_host);
 MB200_API int mb200_selftest_wait_expiry(
         const mb200_conv_param* p, const int8_t* src, const int8_t* flt_packed, int8_t* dst,
         long long limit_cycles, void* stream);
+
+/* Measures the rate the tensor pipe of the current GPU sustains for tcgen05.mma kind::i8
+ * (kind 0) or kind::tf32 (kind 1): one CTA per SM issues 40 000 MMAs of 128 x 256 x 32 bytes
+ * on operands resident in shared memory. Result in tera-operations per second (2 per
+ * multiply-accumulate). About 50 ms. Benchmarks use it as the roofline denominator where
+ * no measured peak of that kind exists for the machine. */
+MB200_API int mb200_measure_mma_rate(int kind, void* stream, double* tera_ops_per_second);
 
 /* Tells the library that [base, base + bytes) is device memory the caller owns and that may
  * be READ anywhere inside (an arena). The tensor-core ConvBias kernels describe activations to

@@ -38,6 +38,7 @@ SIGNATURES = {
     "mb200_device_status": (C.c_int, [_P, C.POINTER(C.c_int)]),
     "mb200_set_option": (C.c_int, [C.c_char_p, C.c_int]),
     "mb200_get_option": (C.c_int, [C.c_char_p, C.POINTER(C.c_int)]),
+    "mb200_measure_mma_rate": (C.c_int, [C.c_int, _P, C.POINTER(C.c_double)]),
     "mb200_selftest_wait_expiry": (C.c_int, [C.POINTER(ConvParam), _P, _P, _P, C.c_longlong, _P]),
     "mb200_register_readable_range": (C.c_int, [_P, C.c_size_t]),
     "mb200_unregister_readable_range": (C.c_int, [_P]),

@@ -55,13 +55,19 @@ __device__ __forceinline__ int requant_conv(
 // divisors that includes the range ends below, and around every int8 step of the accumulator
 // chain. Three instructions instead of the general division routine.
 //
-// Precondition (division_range_ok): 2^-100 <= |s_src * s_flt| <= 2^69 (so that t, for any
-// non-zero int32 accumulator, and rem = t * 2^-24 stay normal) and 2^-60 <= |s_dst| <= 2^60.
-// The launchers check it for per-tensor scales and send anything else to the general kernel
-// with the true division; one scale per output channel must satisfy it by contract.
+// Precondition (division_range_ok): no intermediate may leave the normal range. With t the
+// product acc * s_src * s_flt of a non-zero int32 accumulator: 2^-100 <= |s_src * s_flt| <=
+// 2^69 keeps t and rem = t * 2^-24 normal, 2^-100 <= |s_dst| <= 2^100 keeps d and 1 / d normal,
+// and 2^-60 <= |s_src * s_flt / s_dst| <= 2^60 keeps the quotient normal. (Activation scales
+// of a deep network with large accumulators legitimately reach 1e20 and beyond.) The launchers
+// check it for per-tensor scales and send anything else to the general kernel with the true
+// division; one scale per output channel must satisfy it by contract.
 __host__ __device__ inline bool division_range_ok(float s_src, float s_flt, float s_dst) {
     const float prod = fabsf(s_src * s_flt), d = fabsf(s_dst);
-    return prod >= 0x1p-100f && prod <= 0x1p69f && d >= 0x1p-60f && d <= 0x1p60f;
+    if (!(prod >= 0x1p-100f && prod <= 0x1p69f && d >= 0x1p-100f && d <= 0x1p100f))
+        return false;
+    const float ratio = prod / d;
+    return ratio >= 0x1p-60f && ratio <= 0x1p60f;
 }
 __device__ __forceinline__ float div_rn_by_const(float t, float d, float r) {
     const float q0 = __fmul_rn(t, r);

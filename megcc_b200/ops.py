@@ -164,6 +164,13 @@ def set_option(name, value):
     return old.value
 
 
+def measure_mma_rate(kind="i8"):
+    """Sustained tcgen05.mma rate of the current GPU in TOP/s ("i8") or TFLOP/s ("tf32")."""
+    v = C.c_double(0)
+    check(lib().mb200_measure_mma_rate(0 if kind == "i8" else 1, _stream(), C.byref(v)))
+    return v.value
+
+
 def device_status():
     s = C.c_int(0)
     check(lib().mb200_device_status(_stream(), C.byref(s)))

@@ -12,7 +12,8 @@
  *             the edges of the int8 staircase. The identity is a property of the mantissas
  *             as long as no intermediate leaves the normal range, so the exponent sample
  *             includes the ends of the range the library admits (see `division_range_ok`
- *             in megcc_b200/csrc/common.cuh): 2^-100 <= |t| <= 2^100, 2^-60 <= d <= 2^60.
+ *             in megcc_b200/csrc/common.cuh): 2^-100 <= |t| <= 2^100, 2^-100 <= d <= 2^100,
+ *             2^-60 <= |t / d| <= 2^91.
  *
  * Usage: requant_math_check roundf | division <first> <count>
  * Prints "ok <checked>" or "FAIL ..." and exits non-zero.
@@ -67,7 +68,8 @@ static const float kDivisors[] = {
         /* mantissa extremes */
         1.9999999f, 1.0000001f, 1.5f, 1.25f, 0.99999994f, 3.9999998f,
         /* range ends the library admits */
-        0x1p-60f, 0x1.fffffep-60f, 0x1p60f, 0x1.fffffep59f, 0x1.555556p-40f, 0x1.aaaaaap37f,
+        0x1p-100f, 0x1.fffffep-100f, 0x1p100f, 0x1.fffffep99f, 0x1p-60f, 0x1p60f,
+        0x1.555556p-40f, 0x1.aaaaaap37f, 0x1.8p66f, 0x1.2p-77f,
 };
 
 static int check_division(int first, int count) {
@@ -88,11 +90,12 @@ static int check_division(int first, int count) {
         }
         volatile float rv = 1.0f / d;
         const float r = rv;
-        static const int exps[] = {-100, -37, -1, 0, 24, 54, 99};
+        static const int exps[] = {-100, -77, -37, -1, 0, 24, 54, 66, 99};
         for (unsigned ei = 0; ei < sizeof(exps) / sizeof(exps[0]); ++ei) {
-            /* keep t / d inside the normal range too */
+            /* the quotient's range the library admits: |t / d| from 2^-60 (one accumulator
+             * count at the smallest scale ratio) to 2^91 (2^31 counts at the largest) */
             const float lim = fabsf(ldexpf(1.f, exps[ei]) / d);
-            if (!(lim > 0x1p-120f && lim < 0x1p120f))
+            if (!(lim >= 0x1p-61f && lim <= 0x1p92f))
                 continue;
             for (uint32_t m = 0; m < (1u << 23); ++m) {
                 const float t = from_bits(((uint32_t)(127 + exps[ei]) << 23) | m);

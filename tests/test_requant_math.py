@@ -35,7 +35,7 @@ def test_roundf_identity_holds_for_every_float(checker):
 
 
 def test_division_by_constant_is_correctly_rounded(checker):
-    """The three-instruction division equals RN(t / d) for the divisor list (30 fixed, 18
-    pseudo-random), every mantissa of t at seven exponents, and around every int8 step."""
+    """The three-instruction division equals RN(t / d) for the divisor list (34 fixed, 14
+    pseudo-random), every mantissa of t at nine exponents, and around every int8 step."""
     out = _run_slices(checker, [("division", i * 4, 4) for i in range(12)])
     assert all(rc == 0 and text.startswith("ok") for rc, text in out), out
