@@ -82,7 +82,8 @@ MB200_API const char* mb200_last_error(void);
 /* Kernel-selection switches for experiments and tests (the library's own choices are the
  * defaults): "conv_bn" 0|128|256, "conv_pair" 0|1, "conv_splitk" 0|2..4, "wide128" 1|0,
  * "patch_ctas" 0|1..3, "patch_alone" 0|1, "patch_plain" 0|1, "dw_out" 0|2|4,
- * "dw_one_output" 0|1, "fast_requant" 1|0, "debug" 0|1. Their initial values come from the
+ * "dw_one_output" 0|1, "fast_requant" 1|0, "debug" 0|1, "pdl" 1|0 (programmatic dependent
+ * launch of consecutive kernels). Their initial values come from the
  * environment variables of the same meaning (MB200_CONV_BN, ...), read ONCE per process; no
  * launch consults the environment. Every setting yields bit-identical results. Process-wide,
  * not thread-safe against concurrent launches. */

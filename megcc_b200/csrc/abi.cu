@@ -100,6 +100,7 @@ const TuningField kTuningFields[] = {
         {"dw_one_output", "MB200_DW_ONE_OUTPUT", &Tuning::dw_one_output, false},
         {"fast_requant", "MB200_NO_FAST_REQUANT", &Tuning::fast_requant, true},
         {"debug", "MB200_DEBUG", &Tuning::debug, false},
+        {"pdl", "MB200_NO_PDL", &Tuning::pdl, true},
 };
 }  // namespace
 

@@ -44,6 +44,7 @@
 #include <stdio.h>
 
 #include "f32_internal.h"
+#include "pdl.h"
 #include "tuning.h"
 #include "umma_ptx.cuh"
 
@@ -99,6 +100,7 @@ __host__ __device__ inline float round_tf32(float v) {
 __global__ void __launch_bounds__(256) split_tf32_kernel(
         const float4* __restrict__ src, float4* __restrict__ hi, float4* __restrict__ lo,
         size_t vecs) {
+    pdl_start();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < vecs;
          i += (size_t)gridDim.x * blockDim.x) {
         const float4 v = __ldg(src + i);
@@ -302,6 +304,7 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    pdl_start();  // set-up done: from here on the kernel touches global memory
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -519,6 +522,7 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
 __global__ void __launch_bounds__(256) conv_f32_direct_kernel(
         ConvF32Args a, const float* __restrict__ src, const float* __restrict__ flt,
         const float* __restrict__ bias, const float* __restrict__ z, float* __restrict__ dst) {
+    pdl_start();
     // flt: the unsplit K-major filter [OC][KH][KW][ICpg]
     const size_t total = (size_t)a.m * a.oc;
     const int icpg = a.ic / a.groups, ocpg = a.oc / a.groups;
@@ -596,7 +600,8 @@ int launch_f32_kernel(
     if (tuning().debug)
         fprintf(stderr, "conv_f32_umma<%d,%d>: per_sm %d grid %d tiles %d k_iters %d smem %d\n", BN,
                 ROWB, per_sm, grid, total, p.k_iters, L::kDynamic);
-    conv_f32_umma_kernel<BN, ROWB><<<grid, kF32Threads, L::kDynamic, st>>>(ma, mb, p);
+    launch_pdl(conv_f32_umma_kernel<BN, ROWB>, dim3(grid), dim3(kF32Threads), (size_t)L::kDynamic, st,
+               ma, mb, p);
     return check_launch("conv_f32_umma");
 }
 
@@ -663,8 +668,8 @@ int launch_conv_f32_pack_filter_plain(
 int launch_conv_f32_direct(
         const ConvF32Args& a, const float* src, const float* flt_plain, const float* bias,
         const float* z, float* dst, cudaStream_t st) {
-    conv_f32_direct_kernel<<<grid_1d((size_t)a.m * a.oc, 256), 256, 0, st>>>(a, src, flt_plain,
-                                                                             bias, z, dst);
+    launch_pdl(conv_f32_direct_kernel, dim3(grid_1d((size_t)a.m * a.oc, 256)), dim3(256), 0, st, a,
+               src, flt_plain, bias, z, dst);
     return check_launch("conv_f32_direct");
 }
 
@@ -679,8 +684,8 @@ int launch_conv_f32_umma(
     const size_t elems = (size_t)a.n * a.ih * a.iw * a.ic;
     float* hi = (float*)workspace;
     float* lo = hi + elems;
-    split_tf32_kernel<<<grid_1d(elems / 4, 256), 256, 0, st>>>(
-            (const float4*)src, (float4*)hi, (float4*)lo, elems / 4);
+    launch_pdl(split_tf32_kernel, dim3(grid_1d(elems / 4, 256)), dim3(256), 0, st,
+               (const float4*)src, (float4*)hi, (float4*)lo, elems / 4);
     int rc = check_launch("split_tf32");
     if (rc)
         return rc;

@@ -26,6 +26,7 @@
 
 #include "conv_epilogue.cuh"
 #include "internal.h"
+#include "pdl.h"
 #include "tuning.h"
 #include "umma_ptx.cuh"
 
@@ -246,11 +247,13 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    pdl_release();  // the next kernel may be scheduled onto SMs this one leaves
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            // the filter slice, once: one [BN][16-byte] block per 16 bytes of K
+            // the filter slice, once: one [BN][16-byte] block per 16 bytes of K (weights: they
+            // do not depend on the kernel before this one, so they are fetched before the wait)
             const int kchunks = p.kh * p.kw * p.chunks;
             mbar_expect_tx(b_full, (uint32_t)p.b_bytes);
             if (ROWS) {
@@ -264,6 +267,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
                 for (int kc = 0; kc < kchunks; ++kc)
                     tma_load_2d(smem_b + kc * (BN * 16), &map_b, b_full, kc * 16, n0);
             }
+            pdl_wait();  // activations: only once the previous kernel has completed
             int s = 0;
             uint32_t phase = 0;
             PatchWalker at(m_first, m_step, p.tiles_y, p.tiles_x);
@@ -342,6 +346,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
         }
     } else {
         // ---------------- epilogue ----------------
+        pdl_wait();  // before the first read of z and the first store over memory in use
         const int q = warp & 3;
         const int row = q * 32 + lane;
         const int py = row >> 3, px = row & 7;
@@ -501,7 +506,8 @@ int launch_patch(
         fprintf(stderr, "conv_patch<%d,%d,%d,%d,%d>: per_sm %d grid %d m_tiles %d n_tiles %d smem %d "
                 "stages %d b_single_load %d\n", BN, KH, KW, CHUNKS, EW, per_sm, grid, p.m_tiles,
                 p.n_tiles, smem, p.stages, p.b_single_load);
-    conv_patch_kernel<BN, KH, KW, CHUNKS, EW, ROWS><<<grid, kThreads, smem, st>>>(ma, mb, p);
+    launch_pdl(conv_patch_kernel<BN, KH, KW, CHUNKS, EW, ROWS>, dim3(grid), dim3(kThreads),
+               (size_t)smem, st, ma, mb, p);
     return check_launch("conv_patch");
 }
 

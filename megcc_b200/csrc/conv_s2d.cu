@@ -13,6 +13,7 @@
 // the caller provides (the Opr workspace).
 #include "conv_s2d_geom.h"
 #include "internal.h"
+#include "pdl.h"
 
 namespace mb200 {
 
@@ -27,6 +28,7 @@ S2dGeom s2d_geom(const ConvArgs& a) {
 __global__ void __launch_bounds__(256) space_to_depth_kernel(
         const int8_t* __restrict__ src, uint4* __restrict__ dst, int n, int c, int h, int w,
         int h2, int w2, long long sn, long long sc, long long sy, long long sx) {
+    pdl_start();
     const size_t total = (size_t)n * h2 * w2;
     for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -61,6 +63,7 @@ __global__ void __launch_bounds__(256) space_to_depth_kernel(
 __global__ void __launch_bounds__(256) space_to_depth_nchw2_kernel(
         const int8_t* __restrict__ src, uint4* __restrict__ dst, int n, int c, int h, int w,
         int h2, int w2) {
+    pdl_start();
     const unsigned total = (unsigned)n * h2 * w2;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += gridDim.x * blockDim.x) {
@@ -109,6 +112,7 @@ __global__ void __launch_bounds__(256) space_to_depth_nchw2_kernel(
 // right byte, word 1 = [c1' c2' | lower row c0 c1], word 2 = [c2 | c0' c1' c2'], word 3 = 0.
 __global__ void __launch_bounds__(256) space_to_depth_nchw3_x4_kernel(
         const int8_t* __restrict__ src, uint4* __restrict__ dst, int n, int h, int w, int h2) {
+    pdl_start();
     const unsigned w8 = (unsigned)w / 8;  // groups of four half-resolution pixels per row
     const unsigned total = (unsigned)n * h2 * w8;
     const size_t plane = (size_t)h * w;
@@ -225,15 +229,15 @@ int launch_conv_s2d(
     }
     if (a.src_is_nchw && a.ic == 3 && a.iw % 8 == 0 && ((uintptr_t)src & 7) == 0 &&
         g.w2 == a.iw / 2 && (size_t)a.n * g.h2 * g.w2 < (1u << 31)) {
-        space_to_depth_nchw3_x4_kernel<<<grid_for((size_t)a.n * g.h2 * (a.iw / 8)), 256, 0, st>>>(
-                src, (uint4*)workspace, a.n, a.ih, a.iw, g.h2);
+        launch_pdl(space_to_depth_nchw3_x4_kernel, dim3(grid_for((size_t)a.n * g.h2 * (a.iw / 8))),
+                   dim3(256), 0, st, src, (uint4*)workspace, a.n, a.ih, a.iw, g.h2);
     } else if (a.src_is_nchw && a.iw % 2 == 0 && ((uintptr_t)src & 1) == 0 && g.w2 == a.iw / 2 &&
                (size_t)a.n * g.h2 * g.w2 < (1u << 31)) {
-        space_to_depth_nchw2_kernel<<<grid_for((size_t)a.n * g.h2 * g.w2), 256, 0, st>>>(
-                src, (uint4*)workspace, a.n, a.ic, a.ih, a.iw, g.h2, g.w2);
+        launch_pdl(space_to_depth_nchw2_kernel, dim3(grid_for((size_t)a.n * g.h2 * g.w2)), dim3(256),
+                   0, st, src, (uint4*)workspace, a.n, a.ic, a.ih, a.iw, g.h2, g.w2);
     } else {
-        space_to_depth_kernel<<<grid_for((size_t)a.n * g.h2 * g.w2), 256, 0, st>>>(
-                src, (uint4*)workspace, a.n, a.ic, a.ih, a.iw, g.h2, g.w2, sn, sc, sy, sx);
+        launch_pdl(space_to_depth_kernel, dim3(grid_for((size_t)a.n * g.h2 * g.w2)), dim3(256), 0, st,
+                   src, (uint4*)workspace, a.n, a.ic, a.ih, a.iw, g.h2, g.w2, sn, sc, sy, sx);
     }
     int rc = check_launch("space_to_depth");
     if (rc)

@@ -30,6 +30,7 @@
 
 #include "conv_epilogue.cuh"
 #include "internal.h"
+#include "pdl.h"
 #include "tuning.h"
 #include "umma_ptx.cuh"
 
@@ -179,6 +180,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    pdl_start();  // set-up done: from here on the kernel touches global memory
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -496,8 +498,8 @@ int launch_kernel(
         fprintf(stderr, "conv_umma<%d,%d,%d>: per_sm %d grid %d items %d (whole tiles %d, split %d) smem %d\n",
                 BN, GEOM, (int)SPLITK, per_sm, grid, total, SPLITK ? p.full_tiles : total,
                 SPLITK ? p.split : 1, SmemLayout<BN, GEOM>::kDynamic);
-    conv_umma_kernel<BN, GEOM, SPLITK>
-            <<<grid, kThreads, SmemLayout<BN, GEOM>::kDynamic, st>>>(ma, mb, p);
+    launch_pdl(conv_umma_kernel<BN, GEOM, SPLITK>, dim3(grid), dim3(kThreads),
+               (size_t)SmemLayout<BN, GEOM>::kDynamic, st, ma, mb, p);
     return check_launch("conv_umma");
 }
 

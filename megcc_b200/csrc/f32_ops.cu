@@ -10,6 +10,7 @@
 //                 runtime/src/vm/memforward.c:41-51) feeding a Concat
 //   transpose     model-boundary NCHW <-> NHWC
 #include "f32_internal.h"
+#include "pdl.h"
 #include "umma_ptx.cuh"
 
 namespace mb200 {
@@ -67,6 +68,7 @@ __device__ __forceinline__ float binary_f32(int mode, float x, float y) {
 __global__ void __launch_bounds__(256) elemwise_f32_kernel(
         int mode, const float* __restrict__ a, const float* __restrict__ b,
         float* __restrict__ dst, size_t nr_elem, int vec_ok) {
+    pdl_start();
     const bool binary = mode >= MB200_ELEM_ADD;
     const size_t vecs = vec_ok ? nr_elem / 4 : 0;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < vecs;
@@ -104,6 +106,7 @@ struct ConcatArgs {
 // one thread per (pixel, 4 output channels) when every channel count is a multiple of 4
 __global__ void __launch_bounds__(256) concat_f32_kernel(ConcatArgs a, float* __restrict__ dst,
                                                          size_t pixels) {
+    pdl_start();
     const int step = a.vec ? 4 : 1;
     const int per_pixel = a.c_out / step;
     const size_t total = pixels * (size_t)per_pixel;
@@ -128,6 +131,7 @@ __global__ void __launch_bounds__(256) concat_f32_kernel(ConcatArgs a, float* __
 __global__ void __launch_bounds__(256) resize_nearest_f32_kernel(
         const float* __restrict__ src, float* __restrict__ dst, int n, int c, int ih, int iw,
         int oh, int ow, float scale_h, float scale_w, int vec) {
+    pdl_start();
     const int step = vec ? 4 : 1;
     const int cv = c / step;
     const size_t total = (size_t)n * oh * ow * cv;
@@ -158,6 +162,7 @@ __global__ void __launch_bounds__(256) resize_nearest_f32_kernel(
 __global__ void __launch_bounds__(256) pooling_f32_kernel(
         const float* __restrict__ src, float* __restrict__ dst, int mode, int n, int c, int ih,
         int iw, int oh, int ow, int wh, int ww, int sh, int sw, int ph, int pw, int vec) {
+    pdl_start();
     const int step = vec ? 4 : 1;
     const int cv = c / step;
     const size_t total = (size_t)n * oh * ow * cv;
@@ -215,6 +220,7 @@ __global__ void __launch_bounds__(256) pooling_f32_kernel(
 __global__ void __launch_bounds__(256) focus_f32_kernel(
         const float* __restrict__ src, float* __restrict__ dst, int n, int c, int h, int w,
         int c_out) {
+    pdl_start();
     const int h2 = h / 2, w2 = w / 2;
     const size_t total = (size_t)n * h2 * w2;
     for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
@@ -237,6 +243,7 @@ __global__ void __launch_bounds__(256) focus_f32_kernel(
 
 __global__ void __launch_bounds__(256) transpose_f32_kernel(
         const float* __restrict__ src, float* __restrict__ dst, int rows, int cols) {
+    pdl_start();
     __shared__ float tile[32][33];
     const size_t base = (size_t)blockIdx.z * rows * cols;
     const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
@@ -258,8 +265,8 @@ __global__ void __launch_bounds__(256) transpose_f32_kernel(
 int launch_elemwise_f32(
         int mode, const float* a, const float* b, float* dst, size_t nr_elem, cudaStream_t st) {
     const int vec_ok = ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)dst) & 15) == 0) ? 1 : 0;
-    elemwise_f32_kernel<<<grid_for_f32(nr_elem / 4 + 1, 256), 256, 0, st>>>(mode, a, b, dst,
-                                                                           nr_elem, vec_ok);
+    launch_pdl(elemwise_f32_kernel, dim3(grid_for_f32(nr_elem / 4 + 1, 256)), dim3(256), 0, st, mode,
+               a, b, dst, nr_elem, vec_ok);
     return check_launch("elemwise_f32");
 }
 
@@ -285,7 +292,7 @@ int launch_concat_f32(
         }
     }
     const size_t work = pixels * (size_t)(a.c_out / (a.vec ? 4 : 1));
-    concat_f32_kernel<<<grid_for_f32(work, 256), 256, 0, st>>>(a, dst, pixels);
+    launch_pdl(concat_f32_kernel, dim3(grid_for_f32(work, 256)), dim3(256), 0, st, a, dst, pixels);
     return check_launch("concat_f32");
 }
 
@@ -296,8 +303,8 @@ int launch_resize_nearest_f32(
     // scale = (float)out / in, the reference's own float expression
     const float scale_h = (float)oh / ih, scale_w = (float)ow / iw;
     const size_t work = (size_t)n * oh * ow * (c / (vec ? 4 : 1));
-    resize_nearest_f32_kernel<<<grid_for_f32(work, 256), 256, 0, st>>>(src, dst, n, c, ih, iw, oh,
-                                                                       ow, scale_h, scale_w, vec);
+    launch_pdl(resize_nearest_f32_kernel, dim3(grid_for_f32(work, 256)), dim3(256), 0, st, src, dst,
+               n, c, ih, iw, oh, ow, scale_h, scale_w, vec);
     return check_launch("resize_nearest_f32");
 }
 
@@ -307,8 +314,8 @@ int launch_pooling_f32(
     const int oh = (ih + 2 * ph - wh) / sh + 1, ow = (iw + 2 * pw - ww) / sw + 1;
     const int vec = (c % 4 == 0 && ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0)) ? 1 : 0;
     const size_t work = (size_t)n * oh * ow * (c / (vec ? 4 : 1));
-    pooling_f32_kernel<<<grid_for_f32(work, 256), 256, 0, st>>>(
-            src, dst, mode, n, c, ih, iw, oh, ow, wh, ww, sh, sw, ph, pw, vec);
+    launch_pdl(pooling_f32_kernel, dim3(grid_for_f32(work, 256)), dim3(256), 0, st, src, dst, mode, n,
+               c, ih, iw, oh, ow, wh, ww, sh, sw, ph, pw, vec);
     return check_launch("pooling_f32");
 }
 
@@ -316,8 +323,8 @@ int launch_focus_f32(
         const float* src_nchw, float* dst_nhwc, int n, int c, int h, int w, int c_out,
         cudaStream_t st) {
     const size_t work = (size_t)n * (h / 2) * (w / 2);
-    focus_f32_kernel<<<grid_for_f32(work, 256), 256, 0, st>>>(src_nchw, dst_nhwc, n, c, h, w,
-                                                              c_out);
+    launch_pdl(focus_f32_kernel, dim3(grid_for_f32(work, 256)), dim3(256), 0, st, src_nchw, dst_nhwc,
+               n, c, h, w, c_out);
     return check_launch("focus_f32");
 }
 
@@ -328,7 +335,7 @@ int launch_transpose_f32(
     if (batch > 65535)
         return set_error(ST_OUT_OF_RANGE, "transpose: batch %d exceeds the grid z limit", batch);
     dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch), block(32, 8);
-    transpose_f32_kernel<<<grid, block, 0, st>>>(src, dst, rows, cols);
+    launch_pdl(transpose_f32_kernel, grid, block, 0, st, src, dst, rows, cols);
     return check_launch("transpose_f32");
 }
 

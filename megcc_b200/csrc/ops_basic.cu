@@ -2,6 +2,7 @@
 // pooling, quantised elementwise, type conversion and layout transforms. The tensor-core
 // ConvBias lives in conv_umma.cu; everything here is bandwidth- or latency-bound work.
 #include "internal.h"
+#include "pdl.h"
 
 namespace mb200 {
 
@@ -112,6 +113,7 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
 __global__ void __launch_bounds__(256) pooling_kernel(
         const int8_t* __restrict__ src, int8_t* __restrict__ dst, int mode, int n, int c, int ih,
         int iw, int oh, int ow, int wh, int ww, int sh, int sw, int ph, int pw) {
+    pdl_start();
     const size_t total = (size_t)n * oh * ow * c;
     for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -152,6 +154,7 @@ __global__ void __launch_bounds__(256) pooling_kernel(
 __global__ void __launch_bounds__(256) pooling_max_vec16_kernel(
         const uint4* __restrict__ src, uint4* __restrict__ dst, int n, int c16, int ih, int iw,
         int oh, int ow, int wh, int ww, int sh, int sw, int ph, int pw) {
+    pdl_start();
     const size_t total = (size_t)n * oh * ow * c16;
     for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -194,6 +197,7 @@ __device__ __forceinline__ uint4 vmax16(uint4 a, uint4 b) {
 __global__ void __launch_bounds__(256, 4) pooling_max_3x3s2_vec16_kernel(
         const uint4* __restrict__ src, uint4* __restrict__ dst, int n, int c16, int ih, int iw,
         int oh, int ow, int ph, int pw) {
+    pdl_start();
     const int owp = (ow + 1) / 2;  // output pairs per row
     const unsigned total = (unsigned)n * oh * owp * c16;
     const uint4 lowest = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // -128
@@ -258,6 +262,7 @@ __global__ void __launch_bounds__(256, 4) pooling_max_3x3s2_vec16_kernel(
 // wh * ww vector loads, sixteen int sums, then roundf((float)sum / count) as pooling_kernel.
 __global__ void __launch_bounds__(64) pooling_global_avg_vec16_kernel(
         const uint4* __restrict__ src, uint4* __restrict__ dst, int n, int c16, int pixels) {
+    pdl_start();
     const unsigned total = (unsigned)n * c16;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += gridDim.x * blockDim.x) {
@@ -305,6 +310,7 @@ __global__ void __launch_bounds__(64) pooling_global_avg_vec16_kernel(
 __global__ void __launch_bounds__(128) pooling_global_avg_split_kernel(
         const uint4* __restrict__ src, uint32_t* __restrict__ dst, int c16, int pixels,
         int blocks_per_image) {
+    pdl_start();
     __shared__ int part[4][16][32];
     const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int b = blockIdx.x / blocks_per_image;
@@ -376,6 +382,7 @@ __global__ void __launch_bounds__(256) qelemwise_kernel(
         const int8_t* __restrict__ a, const int8_t* __restrict__ b, int8_t* __restrict__ dst,
         int mode, size_t nr_elem, float s0, float s1, float scale_div, float scale_mul,
         int vec_ok) {
+    pdl_start();
     const size_t nvec = vec_ok ? nr_elem / 16 : 0;
     const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
     const size_t nthr = (size_t)gridDim.x * blockDim.x;
@@ -424,6 +431,7 @@ __global__ void __launch_bounds__(256) typecvt_qs32_qs8_kernel(
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) transpose_s8_kernel(
         const int8_t* __restrict__ src, int8_t* __restrict__ dst, int rows, int cols) {
+    pdl_start();
     __shared__ int8_t tile[32][33];
     const size_t base = (size_t)blockIdx.z * rows * cols;
     const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
@@ -479,8 +487,8 @@ int launch_pooling(
         (size_t)n * ih * iw * (c / 16) < (1u << 30) && oh > 0 && ow > 0) {
         // a window with no valid element cannot occur: padding is below the window size
         const size_t pairs = (size_t)n * oh * ((ow + 1) / 2) * (c / 16);
-        pooling_max_3x3s2_vec16_kernel<<<grid_for(pairs, 256), 256, 0, st>>>(
-                (const uint4*)src, (uint4*)dst, n, c / 16, ih, iw, oh, ow, ph, pw);
+        launch_pdl(pooling_max_3x3s2_vec16_kernel, dim3(grid_for(pairs, 256)), dim3(256), 0, st,
+                   (const uint4*)src, (uint4*)dst, n, c / 16, ih, iw, oh, ow, ph, pw);
         return check_launch("pooling_max_3x3s2_vec16");
     }
     if (mode != 0 && c % 16 == 0 && ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0) && wh == ih &&
@@ -489,21 +497,21 @@ int launch_pooling(
         const size_t work = (size_t)n * (c / 16);
         const int per_image = (c / 16 + 31) / 32;
         if (ih * iw >= 8 && (size_t)n * per_image < (1u << 30)) {
-            pooling_global_avg_split_kernel<<<n * per_image, 128, 0, st>>>(
-                    (const uint4*)src, (uint32_t*)dst, c / 16, ih * iw, per_image);
+            launch_pdl(pooling_global_avg_split_kernel, dim3(n * per_image), dim3(128), 0, st,
+                       (const uint4*)src, (uint32_t*)dst, c / 16, ih * iw, per_image);
             return check_launch("pooling_global_avg_split");
         }
-        pooling_global_avg_vec16_kernel<<<grid_for(work, 64), 64, 0, st>>>(
-                (const uint4*)src, (uint4*)dst, n, c / 16, ih * iw);
+        launch_pdl(pooling_global_avg_vec16_kernel, dim3(grid_for(work, 64)), dim3(64), 0, st,
+                   (const uint4*)src, (uint4*)dst, n, c / 16, ih * iw);
         return check_launch("pooling_global_avg_vec16");
     }
     if (vec16) {
-        pooling_max_vec16_kernel<<<grid_for(total / 16, 256), 256, 0, st>>>(
-                (const uint4*)src, (uint4*)dst, n, c / 16, ih, iw, oh, ow, wh, ww, sh, sw, ph, pw);
+        launch_pdl(pooling_max_vec16_kernel, dim3(grid_for(total / 16, 256)), dim3(256), 0, st,
+                   (const uint4*)src, (uint4*)dst, n, c / 16, ih, iw, oh, ow, wh, ww, sh, sw, ph, pw);
         return check_launch("pooling_max_vec16");
     }
-    pooling_kernel<<<grid_for(total, 256), 256, 0, st>>>(
-            src, dst, mode, n, c, ih, iw, oh, ow, wh, ww, sh, sw, ph, pw);
+    launch_pdl(pooling_kernel, dim3(grid_for(total, 256)), dim3(256), 0, st, src, dst, mode, n, c, ih,
+               iw, oh, ow, wh, ww, sh, sw, ph, pw);
     return check_launch("pooling");
 }
 
@@ -517,8 +525,8 @@ int launch_qelemwise(
     volatile float scale_mul = t * scale_div;
     const int vec_ok = (((uintptr_t)a | (uintptr_t)b | (uintptr_t)dst) & 15) == 0;
     const size_t work = nr_elem / 16 + 1;
-    qelemwise_kernel<<<grid_for(work, 256), 256, 0, st>>>(
-            a, b, dst, mode, nr_elem, s0, s1, scale_div, scale_mul, vec_ok);
+    launch_pdl(qelemwise_kernel, dim3(grid_for(work, 256)), dim3(256), 0, st,
+               a, b, dst, mode, nr_elem, s0, s1, scale_div, scale_mul, vec_ok);
     return check_launch("qelemwise");
 }
 
@@ -537,7 +545,7 @@ int launch_transpose_s8(
     if (batch > 65535)
         return set_error(4, "transpose: batch %d exceeds the grid z limit", batch);
     dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch), block(32, 8);
-    transpose_s8_kernel<<<grid, block, 0, st>>>(src, dst, rows, cols);
+    launch_pdl(transpose_s8_kernel, grid, block, 0, st, src, dst, rows, cols);
     return check_launch("transpose_s8");
 }
 

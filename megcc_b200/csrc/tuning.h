@@ -17,6 +17,7 @@ struct Tuning {
     int dw_one_output = 0;  // MB200_DW_ONE_OUTPUT  1 = one output per thread
     int fast_requant = 1;   // MB200_NO_FAST_REQUANT  0 = always the reference's float operations
     int debug = 0;          // MB200_DEBUG          1 = one line per launch on stderr
+    int pdl = 1;            // MB200_NO_PDL         0 = plain stream-ordered launches
 };
 
 Tuning& tuning();
