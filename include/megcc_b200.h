@@ -240,6 +240,28 @@ MB200_API int mb200_qelemwise_qs8(
         const int8_t* a, const int8_t* b, int8_t* dst, int mode, size_t nr_elem, float scale_a,
         float scale_b, float scale_dst, void* stream);
 
+/* The broadcast forms of the same kernel (the reference's fixture catalogue has a {2,3,4,5}
+ * operand combined with {1,3,1,1} and with a scalar, compiler/test/kernel/opr/naive/
+ * elemwise_multitype.cpp:33-62): element i of a meets b[(i / inner) % b_channels], or b[0]
+ * when b_channels == 0. For an NCHW tensor and one value per channel inner = H * W; for NHWC
+ * inner = 1. Modes QADD / QFUSE_ADD_RELU / QMUL. */
+MB200_API int mb200_qelemwise_qs8_bcast(
+        const int8_t* a, const int8_t* b, int8_t* dst, int mode, size_t nr_elem,
+        size_t b_channels, size_t inner, float scale_a, float scale_b, float scale_dst,
+        void* stream);
+
+/* ---- TypeCvt between fp32 and qsi8, the rule of the reference's x86 build: these dtype pairs
+ * resolve to GI_kernel_typecvt_* there (compiler/lib/KernelGen/GeneralIntrinsic/Typecvt.cpp
+ * :176-190,258-267), which multiplies by scale = src_scale / dst_scale (one float division on
+ * the host; the scale of the FLOAT side counts as 1 whatever is passed, :56-69) and stores
+ * clamp(round(v * scale)), half away from zero; qsi8 -> fp32 is v * scale. ---- */
+MB200_API int mb200_typecvt_f32_qs8(
+        const float* src, int8_t* dst, size_t nr_elem, float src_scale, float dst_scale,
+        void* stream);
+MB200_API int mb200_typecvt_qs8_f32(
+        const int8_t* src, float* dst, size_t nr_elem, float src_scale, float dst_scale,
+        void* stream);
+
 /* ---- TypeCvt qsi32 -> qsi8 (kernel_typecvt_qsi32qsi8,
  * compiler/lib/KernelGen/BareMetal/Typecvt.cpp:43-106) ---- */
 MB200_API int mb200_typecvt_qs32_qs8(

@@ -71,6 +71,10 @@ SIGNATURES = {
     "mb200_qelemwise_qs8": (C.c_int, [_P, _P, _P, C.c_int, C.c_size_t, C.c_float, C.c_float,
                                       C.c_float, _P]),
     "mb200_typecvt_qs32_qs8": (C.c_int, [_P, _P, C.c_size_t, C.c_float, C.c_float, _P]),
+    "mb200_typecvt_f32_qs8": (C.c_int, [_P, _P, C.c_size_t, C.c_float, C.c_float, _P]),
+    "mb200_typecvt_qs8_f32": (C.c_int, [_P, _P, C.c_size_t, C.c_float, C.c_float, _P]),
+    "mb200_qelemwise_qs8_bcast": (C.c_int, [_P, _P, _P, C.c_int, C.c_size_t, C.c_size_t, C.c_size_t,
+                                            C.c_float, C.c_float, C.c_float, _P]),
     "mb200_relayout_nchw_to_nhwc_s8": (C.c_int, [_P, _P] + [C.c_int] * 4 + [_P]),
     "mb200_relayout_nhwc_to_nchw_s8": (C.c_int, [_P, _P] + [C.c_int] * 4 + [_P]),
     # fp32 path

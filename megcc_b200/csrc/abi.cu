@@ -612,6 +612,47 @@ int mb200_qelemwise_qs8(
             (cudaStream_t)stream);
 }
 
+int mb200_qelemwise_qs8_bcast(
+        const int8_t* a, const int8_t* b, int8_t* dst, int mode, size_t nr_elem,
+        size_t b_channels, size_t inner, float scale_a, float scale_b, float scale_dst,
+        void* stream) {
+    if (mode < 0 || mode > 2)
+        return set_error(ST_NO_IMPLEMENT, "elemwise mode %d takes no second operand to broadcast",
+                         mode);
+    if (!a || !b || !dst)
+        return set_error(ST_NULL_PTR, "elemwise tensor pointer is NULL");
+    if (b_channels > 0xffffffffull || inner > 0xffffffffull || (b_channels && !inner))
+        return set_error(ST_INVALID_LAYOUT, "broadcast extents are invalid");
+    if (nr_elem == 0)
+        return ST_SUCCESS;
+    return launch_qelemwise_bcast(a, b, dst, mode, nr_elem, (unsigned)b_channels, (unsigned)inner,
+                                  scale_a, scale_b, scale_dst, (cudaStream_t)stream);
+}
+
+int mb200_typecvt_f32_qs8(
+        const float* src, int8_t* dst, size_t nr_elem, float src_scale, float dst_scale,
+        void* stream) {
+    if (!src || !dst)
+        return set_error(ST_NULL_PTR, "typecvt tensor pointer is NULL");
+    if ((uintptr_t)src & 3)
+        return set_error(ST_INVALID_LAYOUT, "typecvt source must be 4-byte aligned");
+    if (nr_elem == 0)
+        return ST_SUCCESS;
+    return launch_typecvt_f32_qs8(src, dst, nr_elem, src_scale, dst_scale, (cudaStream_t)stream);
+}
+
+int mb200_typecvt_qs8_f32(
+        const int8_t* src, float* dst, size_t nr_elem, float src_scale, float dst_scale,
+        void* stream) {
+    if (!src || !dst)
+        return set_error(ST_NULL_PTR, "typecvt tensor pointer is NULL");
+    if ((uintptr_t)dst & 3)
+        return set_error(ST_INVALID_LAYOUT, "typecvt destination must be 4-byte aligned");
+    if (nr_elem == 0)
+        return ST_SUCCESS;
+    return launch_typecvt_qs8_f32(src, dst, nr_elem, src_scale, dst_scale, (cudaStream_t)stream);
+}
+
 int mb200_typecvt_qs32_qs8(
         const int32_t* src, int8_t* dst, size_t nr_elem, float src_scale, float dst_scale,
         void* stream) {

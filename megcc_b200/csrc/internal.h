@@ -126,6 +126,13 @@ int launch_pooling(
 int launch_qelemwise(
         const int8_t* a, const int8_t* b, int8_t* dst, int mode, size_t nr_elem, float s0,
         float s1, float s_dst, cudaStream_t st);
+int launch_qelemwise_bcast(
+        const int8_t* a, const int8_t* b, int8_t* dst, int mode, size_t nr_elem, unsigned channels,
+        unsigned inner, float s0, float s1, float s_dst, cudaStream_t st);
+int launch_typecvt_f32_qs8(
+        const float* src, int8_t* dst, size_t nr_elem, float s_src, float s_dst, cudaStream_t st);
+int launch_typecvt_qs8_f32(
+        const int8_t* src, float* dst, size_t nr_elem, float s_src, float s_dst, cudaStream_t st);
 int launch_typecvt_qs32_qs8(
         const int32_t* src, int8_t* dst, size_t nr_elem, float s_src, float s_dst,
         cudaStream_t st);

@@ -413,6 +413,53 @@ __global__ void __launch_bounds__(256) qelemwise_kernel(
     }
 }
 
+// Broadcast forms of ElemwiseMultiType (compiler/test/kernel/opr/naive/elemwise_multitype.cpp
+// :33-62: a {2,3,4,5} operand combined with {1,3,1,1} or a scalar): element i of a meets
+// b[(i / inner) % channels], or b[0] when channels == 0.
+__global__ void __launch_bounds__(256) qelemwise_bcast_kernel(
+        const int8_t* __restrict__ a, const int8_t* __restrict__ b, int8_t* __restrict__ dst,
+        int mode, size_t nr_elem, unsigned channels, unsigned inner, float s0, float s1,
+        float scale_div, float scale_mul) {
+    pdl_start();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nr_elem;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t bi = channels ? (i / inner) % channels : 0;
+        dst[i] = (int8_t)qelem_one(mode, (int)a[i], (int)b[bi], s0, s1, scale_div, scale_mul);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// TypeCvt between fp32 and qsi8 as the reference's x86 build performs it: these dtype pairs
+// resolve to the GeneralIntrinsic kernel, whose rule is NOT the BareMetal one
+// (compiler/lib/KernelGen/GeneralIntrinsic/Typecvt.cpp:258-267 and :176-190): scale =
+// src_scale / dst_scale is computed once in float, with the scale of the float side taken as
+// 1 whatever the tensor says (:56-69), then every element is clamp(round(v * scale)), half
+// away from zero. With the flags of the reference's x86 builds (no -msse4.2,
+// compiler/script/compile_target_cmake.cmake:33) only GI_SSE2_INTRINSICS is defined and the
+// SIMD groups of 16 take the same round() as the trailing elements
+// (immigration/include/gi_int.h:1332-1340, gi_common.h:71-76); an SSE4.2 build would convert
+// the SIMD groups as trunc(v * scale +- 0.5) instead, which differs next to ties.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) typecvt_f32_qs8_kernel(
+        const float* __restrict__ src, int8_t* __restrict__ dst, size_t nr_elem, float scale) {
+    pdl_start();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nr_elem;
+         i += (size_t)gridDim.x * blockDim.x) {
+        float r = roundf(__fmul_rn(src[i], scale));
+        r = r >= 127.f ? 127.f : r;
+        r = r <= -128.f ? -128.f : r;
+        dst[i] = (int8_t)__float2int_rn(r);
+    }
+}
+
+__global__ void __launch_bounds__(256) typecvt_qs8_f32_kernel(
+        const int8_t* __restrict__ src, float* __restrict__ dst, size_t nr_elem, float scale) {
+    pdl_start();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nr_elem;
+         i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = __fmul_rn(__int2float_rn((int)src[i]), scale);
+}
+
 // ------------------------------------------------------------------------------------------
 // typecvt qsi32 -> qsi8: saturate(roundf(val * src_scale / dst_scale))
 // ------------------------------------------------------------------------------------------
@@ -528,6 +575,36 @@ int launch_qelemwise(
     launch_pdl(qelemwise_kernel, dim3(grid_for(work, 256)), dim3(256), 0, st,
                a, b, dst, mode, nr_elem, s0, s1, scale_div, scale_mul, vec_ok);
     return check_launch("qelemwise");
+}
+
+int launch_qelemwise_bcast(
+        const int8_t* a, const int8_t* b, int8_t* dst, int mode, size_t nr_elem, unsigned channels,
+        unsigned inner, float s0, float s1, float s_dst, cudaStream_t st) {
+    volatile float scale_div = 1.f / s_dst;
+    volatile float t = s0 * s1;
+    volatile float scale_mul = t * scale_div;
+    launch_pdl(qelemwise_bcast_kernel, dim3(grid_for(nr_elem, 256)), dim3(256), 0, st, a, b, dst,
+               mode, nr_elem, channels, inner ? inner : 1u, s0, s1, (float)scale_div,
+               (float)scale_mul);
+    return check_launch("qelemwise_bcast");
+}
+
+int launch_typecvt_f32_qs8(
+        const float* src, int8_t* dst, size_t nr_elem, float s_src, float s_dst, cudaStream_t st) {
+    (void)s_src;  // a float tensor's scale counts as 1 (GeneralIntrinsic/Typecvt.cpp:56-69)
+    volatile float scale = 1.f / s_dst;
+    launch_pdl(typecvt_f32_qs8_kernel, dim3(grid_for(nr_elem, 256)), dim3(256), 0, st, src, dst,
+               nr_elem, (float)scale);
+    return check_launch("typecvt_f32_qs8");
+}
+
+int launch_typecvt_qs8_f32(
+        const int8_t* src, float* dst, size_t nr_elem, float s_src, float s_dst, cudaStream_t st) {
+    (void)s_dst;  // a float tensor's scale counts as 1
+    volatile float scale = s_src / 1.f;
+    launch_pdl(typecvt_qs8_f32_kernel, dim3(grid_for(nr_elem, 256)), dim3(256), 0, st, src, dst,
+               nr_elem, (float)scale);
+    return check_launch("typecvt_qs8_f32");
 }
 
 int launch_typecvt_qs32_qs8(

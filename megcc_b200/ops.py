@@ -294,3 +294,23 @@ def nhwc_to_nchw_f32(x):
     y = torch.empty((n, c, h, w), dtype=torch.float32, device=x.device)
     check(lib().mb200_relayout_nhwc_to_nchw_f32(_ptr(x), _ptr(y), n, c, h, w, _stream()))
     return y
+
+
+def qelemwise_qs8_bcast(mode, a, b, s0, s1, s_dst, channels, inner):
+    """ElemwiseMultiType with b broadcast over a: b[(i / inner) % channels], or b[0]."""
+    dst = torch.empty_like(a)
+    check(lib().mb200_qelemwise_qs8_bcast(_ptr(a), _ptr(b), _ptr(dst), QELEM[mode], a.numel(),
+                                          channels, inner, s0, s1, s_dst, _stream()))
+    return dst
+
+
+def typecvt_f32_qs8(src, s_src, s_dst):
+    dst = torch.empty(src.shape, dtype=torch.int8, device=src.device)
+    check(lib().mb200_typecvt_f32_qs8(_ptr(src), _ptr(dst), src.numel(), s_src, s_dst, _stream()))
+    return dst
+
+
+def typecvt_qs8_f32(src, s_src, s_dst):
+    dst = torch.empty(src.shape, dtype=torch.float32, device=src.device)
+    check(lib().mb200_typecvt_qs8_f32(_ptr(src), _ptr(dst), src.numel(), s_src, s_dst, _stream()))
+    return dst

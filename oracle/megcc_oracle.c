@@ -422,3 +422,28 @@ void oracle_resize_nearest_f32(
             }
         }
 }
+
+/* fp32 <-> qsi8 TypeCvt as the reference's x86 build performs it: the GeneralIntrinsic kernel
+ * (compiler/lib/KernelGen/GeneralIntrinsic/Typecvt.cpp:258-267: scale = src_scale / dst_scale
+ * with the float side's scale forced to 1, :56-69). Built with the reference's x86 flags (no
+ * -msse4.2) its SIMD groups go through the plain round() of immigration/include/gi_int.h
+ * :1332-1340, the same rule as the trailing elements (Typecvt.cpp:176-183). */
+void oracle_typecvt_f32_qs8(
+        const float* src, int8_t* dst, size_t nr_elem, float s_src, float s_dst) {
+    (void)s_src;
+    const float scale = 1.f / s_dst;
+    for (size_t i = 0; i < nr_elem; ++i) {
+        float r = roundf(src[i] * scale);
+        r = r >= 127.f ? 127.f : r;
+        r = r <= -128.f ? -128.f : r;
+        dst[i] = (int8_t)(int)r;
+    }
+}
+
+void oracle_typecvt_qs8_f32(
+        const int8_t* src, float* dst, size_t nr_elem, float s_src, float s_dst) {
+    (void)s_dst;
+    const float scale = s_src / 1.f;
+    for (size_t i = 0; i < nr_elem; ++i)
+        dst[i] = (float)src[i] * scale;
+}

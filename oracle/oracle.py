@@ -72,6 +72,10 @@ def lib():
         L.oracle_typecvt_qs32_qs8.argtypes = [_i32p, _i8p, C.c_size_t, C.c_float, C.c_float]
         L.oracle_matmul_s8_s32.restype = None
         L.oracle_matmul_s8_s32.argtypes = [_i8p, _i8p, _i32p, C.c_int, C.c_int, C.c_int]
+        L.oracle_typecvt_f32_qs8.restype = None
+        L.oracle_typecvt_f32_qs8.argtypes = [_f32p, _i8p, C.c_size_t, C.c_float, C.c_float]
+        L.oracle_typecvt_qs8_f32.restype = None
+        L.oracle_typecvt_qs8_f32.argtypes = [_i8p, _f32p, C.c_size_t, C.c_float, C.c_float]
         L.oracle_conv_bias_f32.restype = None
         L.oracle_conv_bias_f32.argtypes = [_f32p, _f32p, C.c_void_p, C.c_void_p, _f32p] + [C.c_int] * 13
         L.oracle_matmul_f32.restype = None
@@ -149,6 +153,20 @@ def typecvt_qs32_qs8(src, s_src, s_dst):
     src = _c(src, np.int32)
     dst = np.empty(src.shape, np.int8)
     lib().oracle_typecvt_qs32_qs8(src, dst, src.size, np.float32(s_src), np.float32(s_dst))
+    return dst
+
+
+def typecvt_f32_qs8(src, s_src, s_dst):
+    src = _c(src, np.float32)
+    dst = np.empty(src.shape, np.int8)
+    lib().oracle_typecvt_f32_qs8(src, dst, src.size, np.float32(s_src), np.float32(s_dst))
+    return dst
+
+
+def typecvt_qs8_f32(src, s_src, s_dst):
+    src = _c(src, np.int8)
+    dst = np.empty(src.shape, np.float32)
+    lib().oracle_typecvt_qs8_f32(src, dst, src.size, np.float32(s_src), np.float32(s_dst))
     return dst
 
 
@@ -351,8 +369,89 @@ def ref_qelemwise(mode, a, b, s0, s1, s_dst):
     return dst
 
 
+def ref_typecvt_f32_qs8(src, s_src, s_dst):
+    src = _c(src, np.float32)
+    dst = np.empty(src.shape, np.int8)
+    ref_call("GI_kernel_typecvt_f32qsi8", [(src, s_src)], [(dst, s_dst)])
+    return dst
+
+
+def ref_typecvt_qs8_f32(src, s_src, s_dst):
+    src = _c(src, np.int8)
+    dst = np.empty(src.shape, np.float32)
+    ref_call("GI_kernel_typecvt_qsi8f32", [(src, s_src)], [(dst, s_dst)])
+    return dst
+
+
 def ref_typecvt_qs32_qs8(src, s_src, s_dst):
     src = _c(src, np.int32)
     dst = np.empty(src.shape, np.int8)
     ref_call("kernel_typecvt_qsi32qsi8", [(src, s_src)], [(dst, s_dst)])
+    return dst
+
+
+# ---- the reference's fp32 kernels (GeneralIntrinsic im2col ConvBias and 4x12 MatrixMul,
+# GI / BareMetal Elemwise, BareMetal Concat / Resize / Pooling) ----
+def ref_conv_bias_f32(src, flt, bias, stride, pad, act="IDENTITY"):
+    """ConvBias fp32 with the reference's own nonlinearities (IDENTITY / RELU / SIGMOID)."""
+    src, flt = _c(src, np.float32), _c(flt, np.float32)
+    n, ic, ih, iw = src.shape
+    oc, _, kh, kw = flt.shape
+    oh, ow = out_extent(ih, kh, stride, pad), out_extent(iw, kw, stride, pad)
+    dst = np.empty((n, oc, oh, ow), np.float32)
+    sym = f"GI_kernel_conv2d_im2col_{kh}x{kw}_NCHW_DENSE_p{pad}x{pad}_s{stride}x{stride}_d1x1"
+    if bias is not None:
+        sym += "_bias"
+        b = _c(np.asarray(bias).reshape(1, oc, 1, 1), np.float32)
+    else:
+        b = np.zeros((0,), np.float32)
+    if act != "IDENTITY":
+        sym += "_" + act
+    ref_call(sym + "f32", [(src, 1.0), (flt, 1.0), (b, 1.0)], [(dst, 1.0)])
+    return dst
+
+
+def ref_matmul_f32(a, b):
+    a, b = _c(a, np.float32), _c(b, np.float32)
+    c = np.empty((a.shape[0], b.shape[1]), np.float32)
+    ref_call("GI_kernel_fp32_matmul_4x12_nn", [(a, 1.0), (b, 1.0)], [(c, 1.0)])
+    return c
+
+
+def ref_elemwise_f32(mode, a, b=None):
+    a = _c(a, np.float32)
+    dst = np.empty(a.shape, np.float32)
+    if mode == "SILU":
+        ref_call("kernel_elementwise_SILU_f32f32", [(a, 1.0)], [(dst, 1.0)])
+    elif b is None:
+        ref_call(f"GI_kernel_elementwise_{mode}_f32_unary_vec_vec_f32f32", [(a, 1.0)], [(dst, 1.0)])
+    else:
+        ref_call(f"GI_kernel_elementwise_{mode}_f32_binary_VEC_VEC_f32f32f32",
+                 [(a, 1.0), (_c(b, np.float32), 1.0)], [(dst, 1.0)])
+    return dst
+
+
+def ref_concat_f32(tensors):
+    ts = [_c(t, np.float32) for t in tensors]
+    shape = list(ts[0].shape)
+    shape[1] = sum(t.shape[1] for t in ts)
+    dst = np.empty(shape, np.float32)
+    ref_call("kernel_concat_byte_4_axis_1", [(t, 1.0) for t in ts], [(dst, 1.0)])
+    return dst
+
+
+def ref_resize_nearest_f32(src, oh, ow):
+    src = _c(src, np.float32)
+    dst = np.empty(src.shape[:2] + (oh, ow), np.float32)
+    ref_call("kernel_resize_linear_NCHW_NEAREST_f32", [(src, 1.0)], [(dst, 1.0)])
+    return dst
+
+
+def ref_pooling_f32(src, mode, window, stride, pad):
+    src = _c(src, np.float32)
+    n, c, ih, iw = src.shape
+    oh, ow = (ih + 2 * pad - window) // stride + 1, (iw + 2 * pad - window) // stride + 1
+    dst = np.empty((n, c, oh, ow), np.float32)
+    ref_call(f"kernel_pooling_{mode}_NCHW_p{pad}x{pad}_s{stride}x{stride}_w{window}x{window}_f32f32",
+             [(src, 1.0)], [(dst, 1.0)])
     return dst

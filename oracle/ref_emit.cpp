@@ -53,7 +53,21 @@ static CCOperand make_operand(
 
 struct Emitted {
     std::string symbol, body;
+    // internal kernels the chosen kernel depends on (symbol -> C text), emitted once each as
+    // files of their own, as the reference's exporter does
+    std::vector<std::pair<std::string, std::string>> deps;
 };
+
+static void collect_deps(
+        const std::vector<KernelGen::KernelObj>& objs,
+        std::vector<std::pair<std::string, std::string>>& out) {
+    for (auto& d : objs) {
+        collect_deps(d.kernel_dep, out);
+        std::stringstream ss;
+        ss << KernelGen::GenCommonInclude() << "\n" << d.kernel_body << "\n";
+        out.push_back({d.kernel_symbol, ss.str()});
+    }
+}
 
 static bool pick(
         KernType type, std::unordered_map<std::string, CCAttr>& attrs, Emitted& out) {
@@ -62,12 +76,14 @@ static bool pick(
     for (auto* k : kerns) {
         if (k->IsAvailable(&ctx)) {
             out.symbol = k->GetKernelSymbol(&ctx);
+            collect_deps(k->GetDependInternalSymbol(&ctx), out.deps);
             std::stringstream ss;
             ss << KernelGen::GenCommonInclude() << "\n";
-            for (auto& dep : k->GetDependInternalSymbol(&ctx)) {
-                ss << dep.kernel_body << "\n";
-            }
             ss << k->GetKernelBody(&ctx) << "\n";
+            // the weight-preprocessing and workspace functions of the same kernel (the fp32
+            // GEMM-based kernels need both; for the others these are the trivial defaults)
+            ss << k->GetInitBody(&ctx) << "\n";
+            ss << k->GetWorkspaceBody(&ctx) << "\n";
             out.body = ss.str();
             return true;
         }
@@ -169,6 +185,97 @@ int main(int argc, char** argv) {
             attrs["operand:1"] = CCAttr(make_operand(d, {1, 8, 16, 16}));
             attrs["nr_operands"] = CCAttr((int)2);
             ok = pick(KernType::TypeCvtKernel, attrs, em);
+        } else if (kind == "convf32") {
+            // convf32 <kh> <kw> <sh> <sw> <ph> <pw> <nonline> <bias 0|1> <ic> <oc> <hw>
+            uint32_t kh, kw, sh, sw, ph, pw;
+            std::string nonline;
+            int bias;
+            size_t ic, oc, hw;
+            ls >> kh >> kw >> sh >> sw >> ph >> pw >> nonline >> bias >> ic >> oc >> hw;
+            attrs["kernel_h"] = CCAttr(kh);
+            attrs["kernel_w"] = CCAttr(kw);
+            attrs["stride_h"] = CCAttr(sh);
+            attrs["stride_w"] = CCAttr(sw);
+            attrs["pad_h"] = CCAttr(ph);
+            attrs["pad_w"] = CCAttr(pw);
+            attrs["dilate_h"] = CCAttr((uint32_t)1);
+            attrs["dilate_w"] = CCAttr((uint32_t)1);
+            attrs["sparse"] = CCAttr("DENSE");
+            attrs["format"] = CCAttr("NCHW");
+            attrs["mode"] = CCAttr("CROSS_CORRELATION");
+            attrs["nonlineMode"] = CCAttr(nonline);
+            attrs["compute_mode"] = CCAttr("DEFAULT");
+            const size_t oh = (hw + 2 * ph - kh) / sh + 1;
+            attrs["operand:0"] = CCAttr(make_operand("f32", {1, ic, hw, hw}));
+            attrs["operand:1"] = CCAttr(make_operand("f32", {oc, ic, kh, kw}));
+            attrs["operand:2"] = bias ? CCAttr(make_operand("f32", {1, oc, 1, 1}))
+                                      : CCAttr(make_operand("f32", {}));
+            attrs["operand:3"] = CCAttr(make_operand("f32", {1, oc, oh, oh}));
+            attrs["nr_operands"] = CCAttr((int)4);
+            ok = pick(KernType::ConvKernel, attrs, em);
+        } else if (kind == "matmulf32") {
+            // matmulf32 <m> <n> <k>
+            size_t m, n, k;
+            ls >> m >> n >> k;
+            attrs["transposeA"] = CCAttr(false);
+            attrs["transposeB"] = CCAttr(false);
+            attrs["format"] = CCAttr("DEFAULT");
+            attrs["compute_mode"] = CCAttr("DEFAULT");
+            attrs["operand:0"] = CCAttr(make_operand("f32", {m, k}));
+            attrs["operand:1"] = CCAttr(make_operand("f32", {k, n}));
+            attrs["operand:2"] = CCAttr(make_operand("f32", {m, n}));
+            attrs["nr_operands"] = CCAttr((int)3);
+            ok = pick(KernType::MatrixMulKernel, attrs, em);
+        } else if (kind == "elemf32") {
+            // elemf32 <MODE> <nr inputs>
+            std::string mode;
+            int n;
+            ls >> mode >> n;
+            attrs["mode"] = CCAttr(mode);
+            for (int i = 0; i <= n; ++i)
+                attrs["operand:" + std::to_string(i)] =
+                        CCAttr(make_operand("f32", {1, 8, 16, 16}));
+            attrs["nr_operands"] = CCAttr(n + 1);
+            ok = pick(KernType::ElemwiseKernel, attrs, em);
+        } else if (kind == "concatf32") {
+            // concatf32 <axis> <nr inputs>
+            int axis, n;
+            ls >> axis >> n;
+            attrs["axis"] = CCAttr(axis);
+            for (int i = 0; i < n; ++i)
+                attrs["operand:" + std::to_string(i)] =
+                        CCAttr(make_operand("f32", {1, 8, 16, 16}));
+            attrs["operand:" + std::to_string(n)] =
+                    CCAttr(make_operand("f32", {1, (size_t)(8 * n), 16, 16}));
+            attrs["nr_operands"] = CCAttr(n + 1);
+            ok = pick(KernType::ConcatKernel, attrs, em);
+        } else if (kind == "resizef32") {
+            // resizef32 <imode>
+            std::string imode;
+            ls >> imode;
+            attrs["imode"] = CCAttr(imode);
+            attrs["format"] = CCAttr("NCHW");
+            attrs["operand:0"] = CCAttr(make_operand("f32", {1, 8, 16, 16}));
+            attrs["operand:1"] = CCAttr(make_operand("f32", {1, 8, 32, 32}));
+            attrs["nr_operands"] = CCAttr((int)2);
+            ok = pick(KernType::ResizeKernel, attrs, em);
+        } else if (kind == "poolf32") {
+            // poolf32 <mode> <wh> <ww> <sh> <sw> <ph> <pw>
+            std::string mode;
+            uint32_t wh, ww, sh, sw, ph, pw;
+            ls >> mode >> wh >> ww >> sh >> sw >> ph >> pw;
+            attrs["mode"] = CCAttr(mode);
+            attrs["format"] = CCAttr("NCHW");
+            attrs["window_h"] = CCAttr(wh);
+            attrs["window_w"] = CCAttr(ww);
+            attrs["stride_h"] = CCAttr(sh);
+            attrs["stride_w"] = CCAttr(sw);
+            attrs["pad_h"] = CCAttr(ph);
+            attrs["pad_w"] = CCAttr(pw);
+            attrs["operand:0"] = CCAttr(make_operand("f32", {1, 8, 16, 16}));
+            attrs["operand:1"] = CCAttr(make_operand("f32", {1, 8, 16, 16}));
+            attrs["nr_operands"] = CCAttr((int)2);
+            ok = pick(KernType::PoolingKernel, attrs, em);
         } else {
             fprintf(stderr, "line %d: unknown kind '%s'\n", nline, kind.c_str());
             return 1;
@@ -183,6 +290,11 @@ int main(int argc, char** argv) {
             std::ofstream f(outdir + "/" + em.symbol + ".c");
             f << em.body;
         }
+        for (auto& d : em.deps)
+            if (done.insert(d.first).second) {
+                std::ofstream f(outdir + "/" + d.first + ".c");
+                f << d.second;
+            }
     }
     return 0;
 }

@@ -11,6 +11,7 @@
 #include <dlfcn.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "data_struct.h"
@@ -65,7 +66,11 @@ int megcc_ref_has(const char* symbol) {
     return h && dlsym(h, symbol) != NULL;
 }
 
-/* returns the kernel's TinyNNStatus, or -1 when the symbol was not pre-built */
+/* returns the kernel's TinyNNStatus, or -1 when the symbol was not pre-built.
+ * Follows the reference's own test harness (compiler/test/kernel/common/src/cc_proxy.cpp
+ * :125-255): <symbol>_workspace sizes the scratch, <symbol>_init preprocesses weights in its
+ * three phases (count, describe, fill) and the processed weight replaces the input of the
+ * same name, then the kernel runs. */
 int megcc_ref_call(
         const char* symbol, const RefOperand* ins, int n_in, const RefOperand* outs,
         int n_out) {
@@ -78,17 +83,55 @@ int megcc_ref_call(
     Tensor tin[8], tout[4];
     Tensor* pin[8];
     Tensor* pout[4];
+    static char names[8][8] = {"in0", "in1", "in2", "in3", "in4", "in5", "in6", "in7"};
     if (n_in > 8 || n_out > 4)
         return -2;
     for (int i = 0; i < n_in; ++i) {
         fill(&tin[i], &ins[i]);
+        tin[i].name = names[i];
         pin[i] = &tin[i];
     }
     for (int i = 0; i < n_out; ++i) {
         fill(&tout[i], &outs[i]);
         pout[i] = &tout[i];
     }
-    Workspace ws = {NULL, 0, 0};
+    char sym2[512];
+    size_t ws_bytes = 0;
+    snprintf(sym2, sizeof(sym2), "%s_workspace", symbol);
+    WorkspaceFunc wfn = (WorkspaceFunc)dlsym(h, sym2);
+    if (wfn && wfn(pin, n_in, 1, &ws_bytes) != TinyNN_SUCCESS)
+        return -3;
+    void* processed = NULL;
+    Tensor new_weight;
+    snprintf(sym2, sizeof(sym2), "%s_init", symbol);
+    InitFunc ifn = (InitFunc)dlsym(h, sym2);
+    if (ifn) {
+        int count = 0;
+        if (ifn(pin, n_in, NULL, &count, NULL) != TinyNN_SUCCESS || count > 1)
+            return -4;
+        if (count == 1) {
+            memset(&new_weight, 0, sizeof(new_weight));
+            if (ifn(pin, n_in, &new_weight, NULL, NULL) != TinyNN_SUCCESS)
+                return -4;
+            size_t bytes = new_weight.dtype.type_enum == TinyNN_FLOAT ? 4 : 1;
+            for (int d = 0; d < new_weight.layout.nr_dim; ++d)
+                bytes *= new_weight.layout.dims[d];
+            processed = malloc(bytes + 64);
+            new_weight.ptr = processed;
+            if (ifn(pin, n_in, &new_weight, &count, NULL) != TinyNN_SUCCESS) {
+                free(processed);
+                return -4;
+            }
+            for (int i = 0; i < n_in; ++i)
+                if (tin[i].name == new_weight.name)
+                    tin[i] = new_weight;
+        }
+    }
+    void* ws_mem = ws_bytes ? malloc(ws_bytes + 64) : NULL;
+    Workspace ws = {ws_mem, ws_bytes, 0};
     RuntimeOpt opt = {NULL};
-    return (int)fn(pin, n_in, pout, n_out, &ws, &opt);
+    const int rc = (int)fn(pin, n_in, pout, n_out, &ws, &opt);
+    free(ws_mem);
+    free(processed);
+    return rc;
 }

@@ -168,3 +168,36 @@ def typecvt_catalogue():
 def typecvt_input(c):
     lo, hi = c["range"]
     return rng_for(c["name"]).integers(lo, hi + 1, c["shape"], dtype=np.int32)
+
+
+def f32_conv_catalogue():
+    """fp32 ConvBias cases in the nonlinearities the reference's own fp32 kernels take."""
+    out = []
+    for k, stride, pad, act, bias in ((3, 1, 1, "IDENTITY", True), (3, 2, 1, "IDENTITY", True),
+                                      (1, 1, 0, "IDENTITY", True), (3, 1, 1, "RELU", True),
+                                      (1, 1, 0, "SIGMOID", True), (3, 1, 1, "IDENTITY", False)):
+        for n, ic, oc, h, w in ((2, 32, 64, 40, 40), (2, 64, 48, 24, 20), (3, 16, 32, 48, 48)):
+            out.append(dict(name=f"f32conv_k{k}_s{stride}_p{pad}_{act}_b{int(bias)}_{n}x{ic}x{oc}x{h}x{w}",
+                            k=k, stride=stride, pad=pad, act=act, bias=bias, n=n, ic=ic, oc=oc,
+                            h=h, w=w))
+    return out
+
+
+def f32_conv_inputs(c):
+    r = rng_for(c["name"])
+    src = r.standard_normal((c["n"], c["ic"], c["h"], c["w"])).astype(np.float32)
+    flt = (r.standard_normal((c["oc"], c["ic"], c["k"], c["k"]))
+           / np.sqrt(c["ic"] * c["k"] * c["k"])).astype(np.float32)
+    bias = r.standard_normal(c["oc"]).astype(np.float32) if c["bias"] else None
+    return src, flt, bias
+
+
+def f32_matmul_catalogue():
+    return [dict(name=f"f32mm_{m}x{n}x{k}", m=m, n=n, k=k)
+            for m, n, k in ((512, 512, 512), (300, 72, 640), (64, 15, 48), (1024, 1000, 2048))]
+
+
+def f32_matmul_inputs(c):
+    r = rng_for(c["name"])
+    return (r.standard_normal((c["m"], c["k"])).astype(np.float32),
+            r.standard_normal((c["k"], c["n"])).astype(np.float32))

@@ -45,6 +45,21 @@ def put(out, name, result, *inputs):
     out[name + "/crc"] = crc(*inputs)
 
 
+def put_f32(out, name, result, *inputs):
+    """fp32 results: 4096 elements at fixed pseudo-random positions (whole when smaller)."""
+    flat = result.reshape(-1)
+    if flat.size > 4096:
+        idx = np.random.Generator(np.random.PCG64(zlib.crc32(name.encode()))).choice(
+            flat.size, 4096, replace=False)
+        idx.sort()
+        out[name + "/idx"] = idx.astype(np.int64)
+        out[name] = flat[idx]
+    else:
+        out[name] = flat
+    out[name + "/shape"] = np.array(result.shape, np.int64)
+    out[name + "/crc"] = crc(*inputs)
+
+
 def main():
     O.build(with_reference=True)
     assert O.ref_lib() is not None, "needs the reference tree to build oracle/_ref"
@@ -79,6 +94,18 @@ def main():
         x = cases.typecvt_input(c)
         put(out, c["name"], O.ref_typecvt_qs32_qs8(x, c["s_src"], c["s_dst"]), x)
     np.savez_compressed(os.path.join(HERE, "typecvt_qs32_qs8.npz"), **out)
+    # fp32 path: outputs of the reference's GeneralIntrinsic ConvBias (im2col) and MatrixMul
+    # (4x12) kernels, stored as a checksum-free float digest: mean, standard deviation and 64
+    # sampled elements per case (the GPU is compared within 1e-4 / 1e-5, not bit for bit)
+    out = {}
+    for c in cases.f32_conv_catalogue():
+        src, flt, bias = cases.f32_conv_inputs(c)
+        put_f32(out, c["name"], O.ref_conv_bias_f32(src, flt, bias, c["stride"], c["pad"], c["act"]),
+                src, flt, bias)
+    for c in cases.f32_matmul_catalogue():
+        a, b = cases.f32_matmul_inputs(c)
+        put_f32(out, c["name"], O.ref_matmul_f32(a, b), a, b)
+    np.savez_compressed(os.path.join(HERE, "f32_ops.npz"), **out)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

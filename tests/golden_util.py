@@ -34,3 +34,18 @@ def check(family, name, result, *inputs):
     else:
         assert tuple(g[name + "/shape"]) == result.shape
         assert int(g[name + "/out_crc"]) == crc(result), f"{name}: output digest differs"
+
+
+def check_close(family, name, result, rtol, atol, *inputs):
+    """fp32 results against the stored reference outputs (sampled positions for large
+    tensors): |result - golden| <= atol + rtol * |golden| elementwise."""
+    g = _load(family)
+    assert int(g[name + "/crc"]) == crc(*inputs), f"{name}: seeded inputs differ from golden run"
+    assert tuple(g[name + "/shape"]) == result.shape, (name, result.shape)
+    flat = np.asarray(result, np.float64).reshape(-1)
+    if name + "/idx" in g.files:
+        flat = flat[g[name + "/idx"]]
+    want = g[name].astype(np.float64)
+    excess = np.abs(flat - want) - (atol + rtol * np.abs(want))
+    assert np.isfinite(flat).all() and excess.max() <= 0, \
+        f"{name}: worst excess {excess.max():.3e} over the tolerance"

@@ -4,6 +4,7 @@ import numpy as np
 import pytest
 
 import cases
+import golden_util as G
 
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
@@ -66,6 +67,24 @@ def test_conv_bias_f32_matches_oracle(ops, oracle, case):
     out = ops.conv_bias_f32_nhwc(p, ops.nchw_to_nhwc_f32(dev(src)), packed, dev(bias), algo=algo)
     want = oracle.conv_bias_f32(src, flt, bias, stride, pad, act, groups)
     close(to_nchw(out), want)
+    assert ops.device_status() == 0
+
+
+def test_conv_and_matmul_f32_against_reference_vectors(ops):
+    """Outputs of the reference's own fp32 kernels (GI im2col ConvBias, GI 4x12 MatrixMul),
+    committed under tests/golden/: 1e-4 relative / 1e-5 absolute."""
+    for c in cases.f32_conv_catalogue():
+        src, flt, bias = cases.f32_conv_inputs(c)
+        p = ops.conv_f32_param(c["n"], c["ic"], c["h"], c["w"], c["oc"], c["k"], c["k"], c["stride"],
+                               c["pad"], 1, c["act"])
+        out = ops.conv_bias_f32_nhwc(p, ops.nchw_to_nhwc_f32(dev(src)),
+                                     ops.pack_filter_f32(p, dev(flt)),
+                                     None if bias is None else dev(bias))
+        G.check_close("f32_ops", c["name"], to_nchw(out), RTOL, ATOL, src, flt, bias)
+    for c in cases.f32_matmul_catalogue():
+        a, b = cases.f32_matmul_inputs(c)
+        G.check_close("f32_ops", c["name"], ops.matmul_f32(dev(a), dev(b)).cpu().numpy(), RTOL,
+                      ATOL * np.sqrt(c["k"]), a, b)
     assert ops.device_status() == 0
 
 

@@ -650,13 +650,34 @@ def test_global_average_pool_shapes(ops, oracle, shape):
 
 
 def test_qelemwise_golden(ops):
+    """Same-shape operands and the broadcast forms of the reference's fixture catalogue
+    ({2,3,4,5} with {1,3,1,1}: one value per channel of an NCHW tensor; with a scalar)."""
     for c in cases.qelem_catalogue():
-        if c["a"] != c["b"]:
-            continue  # broadcast forms are not on the model path
         a, b = cases.qelem_inputs(c)
         s0, s1, s2 = c["scales"]
-        out = ops.qelemwise_qs8(c["mode"], dev(a), dev(b), s0, s1, s2).cpu().numpy()
-        G.check("qelemwise", c["name"], out, a, b)
+        if c["a"] == c["b"]:
+            out = ops.qelemwise_qs8(c["mode"], dev(a), dev(b), s0, s1, s2)
+        elif b.size == 1:
+            out = ops.qelemwise_qs8_bcast(c["mode"], dev(a), dev(b), s0, s1, s2, 0, 1)
+        else:
+            assert b.size == a.shape[1]
+            out = ops.qelemwise_qs8_bcast(c["mode"], dev(a), dev(b), s0, s1, s2, a.shape[1],
+                                          int(np.prod(a.shape[2:])))
+        G.check("qelemwise", c["name"], out.cpu().numpy(), a, b)
+
+
+def test_typecvt_between_fp32_and_qsi8_follows_the_gi_rule(ops, oracle):
+    r = cases.rng_for("typecvt_gi_gpu")
+    for n in (16, 37, 4099):
+        x = (r.standard_normal(n) * 60).astype(np.float32)
+        ties = (np.arange(-130, 131, dtype=np.float32) + np.float32(0.5)) * np.float32(0.7)
+        x[:min(n, ties.size)] = ties[:min(n, ties.size)]
+        x[-3:] = np.float32([0.49999997 * 0.7, -0.49999997 * 0.7, 0.35])
+        got = ops.typecvt_f32_qs8(dev(x), 0.3, 0.7).cpu().numpy()
+        assert (got == oracle.typecvt_f32_qs8(x, 0.3, 0.7)).all()
+        q = r.integers(-128, 128, n, dtype=np.int8)
+        got = ops.typecvt_qs8_f32(dev(q), 0.3, 0.7).cpu().numpy()
+        assert (got == oracle.typecvt_qs8_f32(q, 0.3, 0.7)).all()
 
 
 def test_qrelu_matches_oracle(ops, oracle):

@@ -63,3 +63,16 @@ def test_matmul_is_exact_integer_gemm(oracle):
         b = r.integers(-127, 128, (k, n), dtype=np.int8)
         want = a.astype(np.int64) @ b.astype(np.int64)
         assert (oracle.matmul_s8_s32(a, b) == want).all()
+
+
+def test_fp32_conv_and_matmul_against_reference_vectors(oracle):
+    """The fp32 restatement against outputs of the reference's GeneralIntrinsic kernels
+    (fp32 summation order differs: 2e-5 relative / 2e-6 absolute)."""
+    for c in cases.f32_conv_catalogue():
+        src, flt, bias = cases.f32_conv_inputs(c)
+        out = oracle.conv_bias_f32(src, flt, bias, c["stride"], c["pad"], c["act"])
+        G.check_close("f32_ops", c["name"], out, 2e-5, 2e-6, src, flt, bias)
+    for c in cases.f32_matmul_catalogue():
+        a, b = cases.f32_matmul_inputs(c)
+        G.check_close("f32_ops", c["name"], oracle.matmul_f32(a, b), 2e-5,
+                      2e-6 * np.sqrt(c["k"]), a, b)

@@ -76,3 +76,81 @@ def test_per_channel_scale_extension(oracle):
         one = oracle.conv_bias_qs8(src, flt[o:o + 1], bias[o:o + 1], 1, 1, 0.05, float(sf[o]),
                                    0.2, "RELU")
         assert (full[:, o] == one[:, 0]).all()
+
+
+# ---- fp32 path: the restated checker against the reference's own fp32 kernels ----------------
+def _close(a, b, rtol=2e-5, atol=2e-6):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    assert a.shape == b.shape
+    assert (np.abs(a - b) <= atol + rtol * np.abs(b)).all(), float(np.abs(a - b).max())
+
+
+def test_fp32_conv_matches_reference_im2col_kernel(reference):
+    """GI_kernel_conv2d_im2col_* (weight packing through its init function, workspace through
+    its workspace function) against the double-accumulating restatement: the two differ by
+    fp32 summation noise only."""
+    O = reference
+    r = cases.rng_for("f32_conv_ref")
+    for k, stride, pad, act, bias in ((3, 1, 1, "IDENTITY", True), (3, 2, 1, "IDENTITY", True),
+                                      (1, 1, 0, "IDENTITY", True), (3, 1, 1, "RELU", True),
+                                      (1, 1, 0, "SIGMOID", True), (3, 1, 1, "IDENTITY", False)):
+        for n, ic, oc, h, w in ((1, 16, 32, 16, 16), (2, 24, 40, 13, 17), (1, 64, 12, 9, 9)):
+            src = r.standard_normal((n, ic, h, w)).astype(np.float32)
+            flt = (r.standard_normal((oc, ic, k, k)) / np.sqrt(ic * k * k)).astype(np.float32)
+            b = r.standard_normal(oc).astype(np.float32) if bias else None
+            _close(O.conv_bias_f32(src, flt, b, stride, pad, act),
+                   O.ref_conv_bias_f32(src, flt, b, stride, pad, act))
+
+
+def test_fp32_matmul_matches_reference_4x12_kernel(reference):
+    O = reference
+    r = cases.rng_for("f32_matmul_ref")
+    for m, n, k in ((64, 64, 64), (37, 50, 129), (5, 12, 300), (128, 1, 64)):
+        a = r.standard_normal((m, k)).astype(np.float32)
+        b = r.standard_normal((k, n)).astype(np.float32)
+        _close(O.matmul_f32(a, b), O.ref_matmul_f32(a, b), 2e-5, 2e-6 * np.sqrt(k))
+
+
+@pytest.mark.parametrize("mode", ["SILU", "SIGMOID", "RELU", "H_SWISH", "EXP", "ADD", "SUB", "MUL",
+                                  "MAX", "FUSE_ADD_RELU"])
+def test_fp32_elemwise_matches_reference(reference, mode):
+    """SILU resolves to the BareMetal kernel (x / (1 + expf(-x))), the others to the
+    GeneralIntrinsic ones, whose exp is a polynomial: agreement to a few ulp."""
+    O = reference
+    r = cases.rng_for("f32_elem_ref_" + mode)
+    a = (3 * r.standard_normal((2, 5, 9, 13))).astype(np.float32)
+    b = (3 * r.standard_normal((2, 5, 9, 13))).astype(np.float32)
+    binary = mode in ("ADD", "SUB", "MUL", "MAX", "FUSE_ADD_RELU")
+    _close(O.elemwise_f32(mode, a, b if binary else None),
+           O.ref_elemwise_f32(mode, a, b if binary else None), 1e-5, 1e-6)
+
+
+def test_fp32_data_movement_and_pooling_match_reference_exactly(reference):
+    O = reference
+    r = cases.rng_for("f32_move_ref")
+    xs = [r.standard_normal((2, c, 7, 9)).astype(np.float32) for c in (8, 3, 16)]
+    assert (O.concat_f32(xs) == O.ref_concat_f32(xs)).all()
+    x = r.standard_normal((2, 6, 10, 13)).astype(np.float32)
+    for oh, ow in ((20, 26), (17, 31), (5, 7)):
+        assert (O.resize_nearest_f32(x, oh, ow) == O.ref_resize_nearest_f32(x, oh, ow)).all()
+    x = r.standard_normal((2, 8, 20, 20)).astype(np.float32)
+    for window in (5, 9, 13):
+        assert (O.pooling_f32(x, "MAX", window, 1, window // 2)
+                == O.ref_pooling_f32(x, "MAX", window, 1, window // 2)).all()
+    for mode in ("AVERAGE", "AVERAGE_COUNT_EXCLUDE_PADDING"):
+        _close(O.pooling_f32(x, mode, 3, 2, 1), O.ref_pooling_f32(x, mode, 3, 2, 1), 1e-6, 1e-7)
+
+
+def test_fp32_qsi8_typecvt_matches_reference_gi_kernel(reference):
+    """fp32 <-> qsi8 resolve to the GeneralIntrinsic TypeCvt on x86, not the BareMetal one:
+    values next to ties, in the SIMD groups and in the trailing elements alike."""
+    O = reference
+    r = cases.rng_for("typecvt_gi")
+    for n in (16, 37, 1000, 5, 4099):
+        x = (r.standard_normal(n) * 60).astype(np.float32)
+        ties = (np.arange(-130, 131, dtype=np.float32) + np.float32(0.5)) * np.float32(0.7)
+        x[:min(n, ties.size)] = ties[:min(n, ties.size)]
+        x[-3:] = np.float32([0.49999997 * 0.7, -0.49999997 * 0.7, 0.35])[:min(3, n)]
+        assert (O.typecvt_f32_qs8(x, 0.3, 0.7) == O.ref_typecvt_f32_qs8(x, 0.3, 0.7)).all()
+        q = r.integers(-128, 128, n, dtype=np.int8)
+        assert (O.typecvt_qs8_f32(q, 0.3, 0.7) == O.ref_typecvt_qs8_f32(q, 0.3, 0.7)).all()
