@@ -192,3 +192,43 @@ def test_api_errors(lite):
         net.tensor("nonexistent")
     assert e.value.status == 5
     net.close()
+
+
+def _sampled_parity(lite, oracle, spec, batch, name, samples=4, forwards=2):
+    """Runs `batch` images on the GPU and checks `samples` of them, spread over the batch,
+    against the CPU checker (images are independent, so a subset proves the rest of the
+    batch's code path: tile tails, wave boundaries, the kernel choice made for this batch)."""
+    x = cases.rng_for(name).integers(-128, 128, (batch, 3, 224, 224), dtype=np.int8)
+    idx = sorted({int(i) for i in np.linspace(0, batch - 1, min(samples, batch))})
+    want = netwalk.run(spec, x[idx], oracle).reshape(len(idx), -1)
+    outs = run_model(lite, spec.to_graph().compile([batch]), x, (batch, want.shape[1]),
+                     forwards=forwards)
+    for out in outs:
+        assert (out[idx] == want).all()
+    assert len(np.unique(want)) > 8
+
+
+@pytest.mark.parametrize("batch", [32, 64, 128, 256])
+def test_resnet18_at_the_benchmarked_and_sharded_batch_sizes(lite, oracle, batch):
+    """Batch 256 is the benchmark's; 128 / 64 / 32 are its shards over 2 / 4 / 8 GPUs. The
+    kernel selection changes with the batch (tile width, patch kernel, small-activation
+    path), so each size is a different set of launches."""
+    from megcc_b200 import zoo
+    _sampled_parity(lite, oracle, zoo.resnet18(), batch, f"resnet18_b{batch}")
+
+
+@pytest.mark.parametrize("batch", [1, 64])
+@pytest.mark.parametrize("per_channel", [False, True])
+def test_mobilenet_v1_at_the_benchmarked_batch_sizes(lite, oracle, batch, per_channel):
+    """MobileNetV1 at batch 1 (latency) and 64, with one filter scale per tensor and with one
+    per output channel (the form the configuration names; an extension over the reference,
+    checked against the same formula with flt_scale[oc])."""
+    from megcc_b200 import zoo
+    _sampled_parity(lite, oracle, zoo.mobilenet_v1(per_channel=per_channel), batch,
+                    f"mbv1_b{batch}_{per_channel}")
+
+
+def test_resnet18_per_channel_scales_at_batch_256(lite, oracle):
+    from megcc_b200 import zoo
+    _sampled_parity(lite, oracle, zoo.resnet18(per_channel=True), 256, "resnet18_pc_b256",
+                    samples=3)
