@@ -141,6 +141,19 @@ MB200_API size_t mb200_conv_packed_filter_bytes(const mb200_conv_param* p);
  * (the 3-phase init protocol of runtime/src/data_struct.h:135-142). */
 MB200_API int mb200_conv_pack_filter(
         const mb200_conv_param* p, const int8_t* flt_oihw, int8_t* flt_packed, void* stream);
+/* The same Init step for the filter of a model compiled with --enable_nchw44 (the layout
+ * transform MegEngine's optimize_for_inference applies, compiler/lib/Target/MGB/importer.cpp
+ * :1313-1367), layouts of compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:48-62,88-101:
+ *   form 0 dense        [OC/4][IC/4][KH][KW][4 ic][4 oc]
+ *   form 1 channel-wise [G/4][1][1][KH][KW][4]
+ *   form 2 first layer  [OC/4][KH][KW][IC][4 oc]   (NCHW input, NCHW44 output)
+ * The result is exactly what mb200_conv_pack_filter (or mb200_conv_s2d_pack_filter, where
+ * mb200_conv_s2d_supported(p)) gives for the same filter in OIHW, so the ConvBias entry
+ * points are shared. Load-time only: it allocates and frees a scratch buffer of the filter's
+ * size. */
+MB200_API int mb200_conv_pack_filter_nchw44(
+        const mb200_conv_param* p, int form, const int8_t* flt_nchw44, int8_t* flt_packed,
+        void* stream);
 /* src/dst NHWC. bias may be NULL. flt_scales: NULL = per-tensor p->flt_scale (all the
  * reference can express), else one float per output channel (extension).
  * src_is_nchw != 0 lets the first layer read the model input in place. */
@@ -372,6 +385,14 @@ MB200_API int mb200_relayout_nchw_to_nhwc_f32(
         const float* src, float* dst, int n, int c, int h, int w, void* stream);
 MB200_API int mb200_relayout_nhwc_to_nchw_f32(
         const float* src, float* dst, int n, int c, int h, int w, void* stream);
+
+/* ---- NCHW44 activations [N][C/4][H][W][4] (compiler/lib/KernelGen/BareMetal/FormatHelper.cpp
+ * :23-26) <-> the internal NHWC, at the boundary of a model compiled with --enable_nchw44;
+ * c % 4 == 0, 4-byte aligned tensors ---- */
+MB200_API int mb200_relayout_nchw44_to_nhwc_s8(
+        const int8_t* src, int8_t* dst, int n, int c, int h, int w, void* stream);
+MB200_API int mb200_relayout_nhwc_to_nchw44_s8(
+        const int8_t* src, int8_t* dst, int n, int c, int h, int w, void* stream);
 
 #ifdef __cplusplus
 }

@@ -45,6 +45,23 @@ MB200C_API int mb200c_add_conv_bias(
         int groups, const char* nonline, const int8_t* flt, float flt_scale,
         const int32_t* bias, const float* channel_scales, float dst_scale);
 
+/* A model compiled with --enable_nchw44 (compiler/tools/mgb-to-tinynn/mgb-to-tinynn.cpp:41-46;
+ * the transform itself is MegEngine's, compiler/lib/Target/MGB/importer.cpp:1313-1367):
+ * tensors are [N][C/4][H][W][4] and filters come in the layouts of
+ * compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:48-62,88-101. Such a model keeps its
+ * visible layout: an input added here is read as NCHW44, every output with c % 4 == 0 is
+ * handed back as NCHW44 (dims [N][C/4][H][W][4] in the model file), and the filters are
+ * repacked by the Init step at load time; inside, activations are NHWC as always. */
+MB200C_API int mb200c_add_input_nchw44(
+        mb200c_graph* g, const char* name, int c, int h, int w, float scale);
+/* flt44: dense [OC/4][IC/4][KH][KW][4][4] (groups == 1), channel-wise [G/4][1][1][KH][KW][4]
+ * (groups == ic == oc), or, when src is an NCHW model input, the first-layer form
+ * [OC/4][KH][KW][IC][4]. bias: [OC] in channel order (= [1][OC/4][1][1][4]). */
+MB200C_API int mb200c_add_conv_bias_nchw44(
+        mb200c_graph* g, const char* name, int src, int oc, int kh, int kw, int stride, int pad,
+        int groups, const char* nonline, const int8_t* flt44, float flt_scale,
+        const int32_t* bias, const float* channel_scales, float dst_scale);
+
 /* MatrixMul + TypeCvt: C[batch][n] = requant(A[batch][K] x B[K][n]); A = tensor src with
  * h = w = 1 (K = its channels), b: [K][n] int8 row-major with per-tensor scale. The int32
  * product has scale src.scale * b_scale (one float multiplication, as MegEngine records it)

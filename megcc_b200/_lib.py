@@ -45,6 +45,9 @@ SIGNATURES = {
     "mb200_tinynn_describe": (C.c_int, [_P, C.c_size_t, C.c_char_p, C.c_size_t]),
     "mb200_conv_packed_filter_bytes": (C.c_size_t, [C.POINTER(ConvParam)]),
     "mb200_conv_pack_filter": (C.c_int, [C.POINTER(ConvParam), _P, _P, _P]),
+    "mb200_conv_pack_filter_nchw44": (C.c_int, [C.POINTER(ConvParam), C.c_int, _P, _P, _P]),
+    "mb200_relayout_nchw44_to_nhwc_s8": (C.c_int, [_P, _P] + [C.c_int] * 4 + [_P]),
+    "mb200_relayout_nhwc_to_nchw44_s8": (C.c_int, [_P, _P] + [C.c_int] * 4 + [_P]),
     "mb200_conv_bias_qs8_nhwc": (C.c_int, [C.POINTER(ConvParam), _P, C.c_int, _P, _P, _P, _P,
                                            C.c_int, _P]),
     "mb200_conv_bias_qs8_nhwc_fused": (C.c_int, [C.POINTER(ConvParam), _P, C.c_int, _P, _P, _P, _P,

@@ -16,6 +16,9 @@ SIGNATURES = {
     "mb200c_add_input": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_float]),
     "mb200c_add_conv_bias": (C.c_int, [_P, C.c_char_p] + [C.c_int] * 7 + [
         C.c_char_p, _P, C.c_float, _P, _P, C.c_float]),
+    "mb200c_add_input_nchw44": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_float]),
+    "mb200c_add_conv_bias_nchw44": (C.c_int, [_P, C.c_char_p] + [C.c_int] * 7 + [
+        C.c_char_p, _P, C.c_float, _P, _P, C.c_float]),
     "mb200c_add_matmul": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int, _P, C.c_float, C.c_float]),
     "mb200c_add_pooling": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_char_p] + [C.c_int] * 3),
     "mb200c_add_qelemwise": (C.c_int, [_P, C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_float]),
@@ -91,6 +94,35 @@ class Graph:
         return _check(lib().mb200c_add_conv_bias(
             self._g, name.encode(), src, oc, kh, kw, stride, pad, groups, nonline.encode(),
             flt.ctypes.data, flt_scale, None if b is None else b.ctypes.data,
+            None if cs is None else cs.ctypes.data, dst_scale))
+
+    def input_nchw44(self, name, c, h, w, scale):
+        """Input of a model compiled with --enable_nchw44: the buffer is [N, C/4, H, W, 4]."""
+        return _check(lib().mb200c_add_input_nchw44(self._g, name.encode(), c, h, w, scale))
+
+    def conv_bias_nchw44(self, name, src, flt44, bias, stride, pad, flt_scale, dst_scale, form,
+                         nonline="IDENTITY", channel_scales=None):
+        """ConvBias whose filter comes in an NCHW44 layout; form names it: "dense"
+        [OC/4, IC/4, KH, KW, 4, 4], "channel_wise" [G/4, 1, 1, KH, KW, 4] or, on an NCHW model
+        input, "first_layer" [OC/4, KH, KW, IC, 4]."""
+        flt44 = np.ascontiguousarray(flt44, np.int8)
+        oc = flt44.shape[0] * 4
+        if form == "first_layer":
+            assert flt44.ndim == 5 and flt44.shape[4] == 4
+            kh, kw, groups = flt44.shape[1], flt44.shape[2], 1
+        elif form == "channel_wise":
+            assert flt44.ndim == 6 and flt44.shape[1:3] == (1, 1) and flt44.shape[5] == 4
+            kh, kw, groups = flt44.shape[3], flt44.shape[4], oc
+        elif form == "dense":
+            assert flt44.ndim == 6 and flt44.shape[4:] == (4, 4)
+            kh, kw, groups = flt44.shape[2], flt44.shape[3], 1
+        else:
+            raise ValueError(f"unknown NCHW44 filter form {form!r}")
+        b = None if bias is None else np.ascontiguousarray(np.asarray(bias).reshape(-1), np.int32)
+        cs = None if channel_scales is None else np.ascontiguousarray(channel_scales, np.float32)
+        return _check(lib().mb200c_add_conv_bias_nchw44(
+            self._g, name.encode(), src, oc, kh, kw, stride, pad, groups, nonline.encode(),
+            flt44.ctypes.data, flt_scale, None if b is None else b.ctypes.data,
             None if cs is None else cs.ctypes.data, dst_scale))
 
     def matmul(self, name, src, b, b_scale, dst_scale):

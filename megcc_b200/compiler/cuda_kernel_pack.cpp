@@ -48,7 +48,46 @@ bool channel_broadcast_bias(TContext* ctx) {
     const CCOperand b = ctx->getAttrOprand("operand:2");
     if (b.shape.size() == 1)
         return true;
+    if (b.shape.size() == 5)  // NCHW44: [1][C/4][1][1][4], the channels in order
+        return b.shape[0] == 1 && b.shape[2] == 1 && b.shape[3] == 1 && b.shape[4] == 4;
     return b.shape.size() == 4 && b.shape[0] == 1 && b.shape[2] == 1 && b.shape[3] == 1;
+}
+
+// Filter layout of a ConvBias: 0 OIHW / GOIHW; for format NCHW44 (the filters of a model
+// compiled with --enable_nchw44, compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:48-62,88-101)
+// 1 dense [OC/4][IC/4][KH][KW][4][4], 2 channel-wise [G/4][1][1][KH][KW][4], 3 first layer
+// [OC/4][KH][KW][IC][4] (NCHW input: FormatHelper.cpp's "NCHW_NCHW44"); -1 not one of them
+int filter_form(TContext* ctx) {
+    const std::string format = ctx->getAttrStr("format");
+    if (format == "NCHW")
+        return 0;
+    if (format != "NCHW44")
+        return -1;
+    const CCOperand src = ctx->getAttrOprand("operand:0");
+    const CCOperand flt = ctx->getAttrOprand("operand:1");
+    const size_t kh = ctx->getAttrUInt("kernel_h"), kw = ctx->getAttrUInt("kernel_w");
+    const bool dense = ctx->getAttrStr("sparse") == "DENSE";
+    if (src.shape.size() == 4)
+        return dense && flt.shape.size() == 5 && flt.shape[1] == kh && flt.shape[2] == kw &&
+                               flt.shape[3] == src.shape[1] && flt.shape[4] == 4
+                       ? 3
+                       : -1;
+    if (src.shape.size() != 5 || src.shape[4] != 4 || flt.shape.size() != 6 || flt.shape[5] != 4)
+        return -1;
+    if (dense)
+        return flt.shape[1] == src.shape[1] && flt.shape[2] == kh && flt.shape[3] == kw &&
+                               flt.shape[4] == 4
+                       ? 1
+                       : -1;
+    return flt.shape[0] == src.shape[1] && flt.shape[1] == 1 && flt.shape[2] == 1 &&
+                           flt.shape[3] == kh && flt.shape[4] == kw
+                   ? 2
+                   : -1;
+}
+
+const char* filter_form_token(int form) {
+    static const char* names[] = {"NHWC", "NHWC44D", "NHWC44C", "NHWC44H"};
+    return names[form];
 }
 
 // "" unless the operator carries a fused ElemwiseMultiType step (5 operands: src, filter,
@@ -86,7 +125,7 @@ std::string Cuda::GenStubPrologue() {
 // ConvBias
 // ------------------------------------------------------------------------------------------
 bool ConvBiasQS8::IsAvailable(TContext* ctx) const {
-    if (ctx->getAttrStr("format") != "NCHW" || ctx->getAttrStr("mode") != "CROSS_CORRELATION")
+    if (ctx->getAttrStr("mode") != "CROSS_CORRELATION")
         return false;
     if (ctx->getAttrInt("nr_operands") < 3)
         return false;
@@ -95,7 +134,10 @@ bool ConvBiasQS8::IsAvailable(TContext* ctx) const {
     const CCOperand dst = last_operand(ctx);
     if (!is_quant(src.dtype, 8) || !is_quant(flt.dtype, 8) || !is_quant(dst.dtype, 8))
         return false;
-    if (src.shape.size() != 4)
+    // NCHW, or NCHW44 with the filter repacked at load time (the tensors of such a model are
+    // converted to the internal NHWC at its boundary)
+    const int form = filter_form(ctx);
+    if (form < 0 || (form == 0 && src.shape.size() != 4))
         return false;
     const std::string sparse = ctx->getAttrStr("sparse");
     if (sparse != "DENSE" && sparse != "GROUP")
@@ -131,7 +173,8 @@ std::string ConvBiasQS8::GetKernelSymbol(TContext* ctx) const {
         return "cuda_sm100_conv2d";
     std::stringstream ss;
     ss << "cuda_sm100_conv2d_" << ctx->getAttrUInt("kernel_h") << "x"
-       << ctx->getAttrUInt("kernel_w") << "_NHWC_" << ctx->getAttrStr("sparse") << "_p"
+       << ctx->getAttrUInt("kernel_w") << "_" << filter_form_token(filter_form(ctx)) << "_"
+       << ctx->getAttrStr("sparse") << "_p"
        << ctx->getAttrUInt("pad_h") << "x" << ctx->getAttrUInt("pad_w") << "_s"
        << ctx->getAttrUInt("stride_h") << "x" << ctx->getAttrUInt("stride_w") << "_d"
        << ctx->getAttrUInt("dilate_h") << "x" << ctx->getAttrUInt("dilate_w") << "_"
@@ -163,7 +206,7 @@ TinyNNStatus ${signature} {
     p.stride_h = ${sh}; p.stride_w = ${sw};
     p.pad_h = ${ph}; p.pad_w = ${pw};
     p.dilate_h = ${dh}; p.dilate_w = ${dw};
-    p.groups = ${dense} ? 1 : (int)flt->layout.dims[0];
+    p.groups = ${dense} ? 1 : (int)flt->layout.dims[0] * ${group_block};
     p.nonline = ${nonline};
     p.src_scale = src->dtype.param.scale;
     p.flt_scale = flt->dtype.param.scale;
@@ -209,6 +252,7 @@ TinyNNStatus ${signature} {
             .set("dh", ctx->getAttrUInt("dilate_h"))
             .set("dw", ctx->getAttrUInt("dilate_w"))
             .set("dense", ctx->getAttrStr("sparse") == "DENSE" ? 1 : 0)
+            .set("group_block", filter_form(ctx) ? 4 : 1)
             .set("nonline", nonline_code(nonline(ctx)))
             .set("has_bias", bias ? 1 : 0)
             .set("scale_idx", bias ? 3 : 2);
@@ -227,13 +271,18 @@ ${prologue}
 static void ${symbol}_param(Tensor** inputs, mb200_conv_param* p) {
     const Tensor* src = inputs[0];
     const Layout* l = &inputs[1]->layout;
-    const int grouped = l->nr_dim == 5;
+    const int grouped = !${dense};
     p->n = src->layout.dims[0];
     p->ic = src->layout.dims[1];
     p->ih = src->layout.dims[2];
     p->iw = src->layout.dims[3];
-    p->groups = grouped ? (int)l->dims[0] : 1;
-    p->oc = grouped ? (int)(l->dims[0] * l->dims[1]) : (int)l->dims[0];
+    if (${form}) { /* NCHW44 layouts count blocks of four output channels (or groups) */
+        p->groups = grouped ? (int)l->dims[0] * 4 : 1;
+        p->oc = (int)l->dims[0] * 4;
+    } else {
+        p->groups = grouped ? (int)l->dims[0] : 1;
+        p->oc = grouped ? (int)(l->dims[0] * l->dims[1]) : (int)l->dims[0];
+    }
     p->kh = ${kh}; p->kw = ${kw};
     p->stride_h = ${sh}; p->stride_w = ${sw};
     p->pad_h = ${ph}; p->pad_w = ${pw};
@@ -261,6 +310,10 @@ TinyNNStatus ${signature} {
         out_weights->name = in_weights->name;
         return TinyNN_SUCCESS;
     }
+    if (${form}) /* from the NCHW44 layout straight to whichever packing the kernel reads */
+        return (TinyNNStatus)mb200_conv_pack_filter_nchw44(
+                &p, ${form} - 1, (const int8_t*)in_weights->ptr, (int8_t*)out_weights->ptr,
+                mb200_opt_stream(opt));
     if (s2d)
         return (TinyNNStatus)mb200_conv_s2d_pack_filter(
                 &p, (const int8_t*)in_weights->ptr, (int8_t*)out_weights->ptr,
@@ -272,6 +325,8 @@ TinyNNStatus ${signature} {
     s.set("prologue", GenStubPrologue())
             .set("signature", GetInitSignature(ctx))
             .set("symbol", GetKernelSymbol(ctx))
+            .set("form", filter_form(ctx))
+            .set("dense", ctx->getAttrStr("sparse") == "DENSE" ? 1 : 0)
             .set("kh", ctx->getAttrUInt("kernel_h"))
             .set("kw", ctx->getAttrUInt("kernel_w"))
             .set("sh", ctx->getAttrUInt("stride_h"))
@@ -303,12 +358,17 @@ size_t ConvBiasQS8::WorkspaceBytes(TContext* ctx) const {
     const CCOperand src = ctx->getAttrOprand("operand:0");
     const CCOperand flt = ctx->getAttrOprand("operand:1");
     const CCOperand dst = last_operand(ctx);
-    if (src.shape.size() != 4 || dst.shape.size() != 4)
+    const int form = filter_form(ctx);
+    if (form < 0 || (form == 0 && (src.shape.size() != 4 || dst.shape.size() != 4)))
         return 0;
-    const int groups = ctx->getAttrStr("sparse") == "DENSE" ? 1 : (int)flt.shape[0];
+    auto channels = [](const CCOperand& o) {
+        return (int)(o.shape.size() == 5 ? o.shape[1] * 4 : o.shape[1]);
+    };
+    const int groups = ctx->getAttrStr("sparse") == "DENSE" ? 1
+                                                            : (int)flt.shape[0] * (form ? 4 : 1);
     const mb200::S2dGeom g = mb200::s2d_geometry(
-            (int)src.shape[0], (int)src.shape[1], (int)src.shape[2], (int)src.shape[3],
-            (int)dst.shape[1], (int)ctx->getAttrUInt("kernel_h"), (int)ctx->getAttrUInt("kernel_w"),
+            (int)src.shape[0], channels(src), (int)src.shape[2], (int)src.shape[3],
+            channels(dst), (int)ctx->getAttrUInt("kernel_h"), (int)ctx->getAttrUInt("kernel_w"),
             (int)ctx->getAttrUInt("stride_h"), (int)ctx->getAttrUInt("stride_w"),
             (int)ctx->getAttrUInt("pad_h"), (int)ctx->getAttrUInt("pad_w"),
             (int)ctx->getAttrUInt("dilate_h"), (int)ctx->getAttrUInt("dilate_w"), groups);
@@ -523,6 +583,10 @@ bool RelayoutQS8::IsAvailable(TContext* ctx) const {
         return false;
     const std::string m = ctx->getAttrStr("relayout_mode");
     const CCOperand src = ctx->getAttrOprand("operand:0");
+    if (m == "NCHW44_NHWC")  // [N][C/4][H][W][4] in
+        return src.shape.size() == 5 && src.shape[4] == 4 && is_quant(src.dtype, 8);
+    if (m == "NHWC_NCHW44")
+        return src.shape.size() == 4 && src.shape[1] % 4 == 0 && is_quant(src.dtype, 8);
     return (m == "NCHW_NHWC" || m == "NHWC_NCHW") && src.shape.size() == 4 &&
            (is_quant(src.dtype, 8) || src.dtype == "si8" || src.dtype == "f32");
 }
@@ -532,7 +596,27 @@ std::string RelayoutQS8::GetKernelSymbol(TContext* ctx) const {
 }
 
 std::string RelayoutQS8::GetKernelBody(TContext* ctx) const {
-    const bool to_nhwc = ctx->getAttrStr("relayout_mode") == "NCHW_NHWC";
+    const std::string m = ctx->getAttrStr("relayout_mode");
+    if (m == "NCHW44_NHWC" || m == "NHWC_NCHW44") {
+        Subst s{R"(
+${prologue}
+TinyNNStatus ${signature} {
+    const Tensor* src = inputs[0];
+    return (TinyNNStatus)${fn}(
+            (const int8_t*)src->ptr, (int8_t*)outputs[0]->ptr, src->layout.dims[0],
+            src->layout.dims[1] * ${cblock}, src->layout.dims[2], src->layout.dims[3],
+            mb200_opt_stream(opt));
+}
+)"};
+        const bool from44 = m == "NCHW44_NHWC";
+        s.set("prologue", GenStubPrologue())
+                .set("signature", GetKernelSignature(ctx))
+                .set("cblock", from44 ? 4 : 1)
+                .set("fn", from44 ? "mb200_relayout_nchw44_to_nhwc_s8"
+                                  : "mb200_relayout_nhwc_to_nchw44_s8");
+        return s.text;
+    }
+    const bool to_nhwc = m == "NCHW_NHWC";
     Subst s{R"(
 ${prologue}
 TinyNNStatus ${signature} {

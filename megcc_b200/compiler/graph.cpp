@@ -37,6 +37,8 @@ struct GTensor {
     bool nchw = false;  // physical layout of the buffer (model input / 1x1 outputs)
     bool is_input = false, is_output = false;
     bool f32 = false;   // fp32 tensor (else qint8)
+    // model-visible tensor of an NCHW44 model: buffer [N][C/4][H][W][4]
+    bool nchw44 = false;
 };
 
 struct GWeight {
@@ -66,6 +68,9 @@ struct GOp {
     float mid_scale = 1.f;  // scale of the ConvBias result that the fused step consumes
     int mid_weight = -1;    // 1-element float weight carrying mid_scale to the runtime
     bool f32 = false;       // fp32 operator (CONV / MATMUL / POOL / RELAYOUT)
+    // ConvBias whose filter is given in an NCHW44 layout: 1 dense, 2 channel-wise, 3 first
+    // layer (NCHW input)
+    int flt44 = 0;
 };
 
 struct Compiled {
@@ -196,7 +201,7 @@ struct mb200c_graph {
                 set_u32(*ctx, "dilate_h", 1);
                 set_u32(*ctx, "dilate_w", 1);
                 set_str(*ctx, "sparse", op.groups == 1 ? "DENSE" : "GROUP");
-                set_str(*ctx, "format", "NCHW");
+                set_str(*ctx, "format", op.flt44 ? "NCHW44" : "NCHW");
                 set_str(*ctx, "mode", "CROSS_CORRELATION");
                 set_str(*ctx, "nonlineMode", op.mode);
                 set_str(*ctx, "compute_mode", "DEFAULT");
@@ -219,25 +224,43 @@ struct mb200c_graph {
                     }
                     break;
                 }
-                set_opr(*ctx, "operand:0", operand("qsi8", shape(op.inputs[0]), src.scale));
+                // what the operator looks like in an NCHW44 graph: 5-dim tensors, except the
+                // NCHW input of the first layer
+                auto shape_of = [&](int id, bool blocked) {
+                    const GTensor& t = tensors[id];
+                    if (!blocked)
+                        return shape(id);
+                    return std::vector<size_t>{(size_t)batch, (size_t)t.c / 4, (size_t)t.h,
+                                               (size_t)t.w, 4};
+                };
+                const bool b_src = op.flt44 == 1 || op.flt44 == 2, b_dst = op.flt44 != 0;
+                set_opr(*ctx, "operand:0",
+                        operand("qsi8", shape_of(op.inputs[0], b_src), src.scale));
                 std::vector<size_t> fs;
                 for (int d : weights[op.weights[0]].dims)
                     fs.push_back(d);
                 set_opr(*ctx, "operand:1", operand("qsi8", fs, op.flt_scale));
-                if (op.has_bias)
+                if (op.has_bias && b_dst)
+                    set_opr(*ctx, "operand:2",
+                            operand("qsi32", {1, (size_t)dst.c / 4, 1, 1, 4},
+                                    src.scale * op.flt_scale));
+                else if (op.has_bias)
                     set_opr(*ctx, "operand:2",
                             operand("qsi32", {1, (size_t)dst.c, 1, 1}, src.scale * op.flt_scale));
                 else
                     set_opr(*ctx, "operand:2", operand("qsi32", {}, src.scale * op.flt_scale));
                 if (op.fuse_mode.empty()) {
-                    set_opr(*ctx, "operand:3", operand("qsi8", shape(op.output), dst.scale));
+                    set_opr(*ctx, "operand:3",
+                            operand("qsi8", shape_of(op.output, b_dst), dst.scale));
                     set_i32(*ctx, "nr_operands", 4);
                 } else {
                     // operand order src, filter, bias, z, dst: the z slot of the reference's
                     // Conv2DKernel (include/compiler/Dialect/Kernel/IR/AbstractKernels.td:113-118)
                     set_opr(*ctx, "operand:3",
-                            operand("qsi8", shape(op.inputs[1]), tensors[op.inputs[1]].scale));
-                    set_opr(*ctx, "operand:4", operand("qsi8", shape(op.output), dst.scale));
+                            operand("qsi8", shape_of(op.inputs[1], b_dst),
+                                    tensors[op.inputs[1]].scale));
+                    set_opr(*ctx, "operand:4",
+                            operand("qsi8", shape_of(op.output, b_dst), dst.scale));
                     set_i32(*ctx, "nr_operands", 5);
                     set_str(*ctx, "fuse_elemwise_mode", op.fuse_mode);
 #ifdef MEGCC_B200_IN_MEGCC_TREE
@@ -303,8 +326,16 @@ struct mb200c_graph {
             }
             case OpType::RELAYOUT: {
                 set_str(*ctx, "relayout_mode", op.mode);
-                set_opr(*ctx, "operand:0", topr(op.inputs[0]));
-                set_opr(*ctx, "operand:1", topr(op.output));
+                auto side = [&](int id) {
+                    const GTensor& t = tensors[id];
+                    if (!t.nchw44)
+                        return topr(id);
+                    return operand("qsi8",
+                                   {(size_t)batch, (size_t)t.c / 4, (size_t)t.h, (size_t)t.w, 4},
+                                   t.scale);
+                };
+                set_opr(*ctx, "operand:0", side(op.inputs[0]));
+                set_opr(*ctx, "operand:1", side(op.output));
                 set_i32(*ctx, "nr_operands", 2);
                 break;
             }
@@ -469,6 +500,53 @@ int mb200c_add_input(mb200c_graph* g, const char* name, int c, int h, int w, flo
     g->tensors[id].is_input = true;
     g->tensors[id].nchw = true;
     return id;
+}
+
+int mb200c_add_input_nchw44(mb200c_graph* g, const char* name, int c, int h, int w, float scale) {
+    if (!g || !name || c <= 0 || c % 4 || h <= 0 || w <= 0 || !(scale > 0))
+        return err("add_input_nchw44: bad argument (channels must be a multiple of 4)");
+    const int id = g->add_tensor(name, c, h, w, scale);
+    g->tensors[id].is_input = true;
+    g->tensors[id].nchw44 = true;
+    return id;
+}
+
+int mb200c_add_conv_bias_nchw44(
+        mb200c_graph* g, const char* name, int src, int oc, int kh, int kw, int stride, int pad,
+        int groups, const char* nonline, const int8_t* flt44, float flt_scale,
+        const int32_t* bias, const float* channel_scales, float dst_scale) {
+    if (!g || !g->valid(src) || !name)
+        return err("add_conv_bias_nchw44: bad argument");
+    const GTensor s = g->tensors[src];
+    int form;
+    if (groups == 1 && s.is_input && s.nchw && !s.nchw44)
+        form = 3;  // NCHW model input -> NCHW44
+    else if (groups == 1)
+        form = 1;
+    else if (groups == s.c && oc == s.c)
+        form = 2;
+    else
+        return err("add_conv_bias_nchw44 %s: only dense and channel-wise filters have an NCHW44 "
+                   "layout here", name);
+    if (oc % 4 || (form != 3 && s.c % 4))
+        return err("add_conv_bias_nchw44 %s: channels must be multiples of 4", name);
+    // same operator; the filter bytes are taken as they are (the count is the same)
+    const int out = mb200c_add_conv_bias(g, name, src, oc, kh, kw, stride, pad, groups, nonline,
+                                         flt44, flt_scale, bias, channel_scales, dst_scale);
+    if (out < 0)
+        return out;
+    GOp& op = g->ops.back();
+    op.flt44 = form;
+    GWeight& wf = g->weights[op.weights[0]];
+    if (form == 1)
+        wf.dims = {oc / 4, s.c / 4, kh, kw, 4, 4};
+    else if (form == 2)
+        wf.dims = {oc / 4, 1, 1, kh, kw, 4};
+    else
+        wf.dims = {oc / 4, kh, kw, s.c, 4};
+    if (op.has_bias)
+        g->weights[op.weights[1]].dims = {1, oc / 4, 1, 1, 4};
+    return out;
 }
 
 int mb200c_add_conv_bias(
@@ -813,9 +891,31 @@ int mb200c_compile(
     {
         std::vector<GOp> ops;
         std::map<int, int> nhwc_of;  // NCHW input id -> converted tensor id
+        // a model with NCHW44 inputs or filters hands its outputs back in NCHW44 too
+        bool model44 = false;
+        for (auto& t : work.tensors)
+            model44 |= t.nchw44;
+        for (auto& op : work.ops)
+            model44 |= op.flt44 != 0;
         for (auto op : work.ops) {
             for (size_t k = 0; k < op.inputs.size(); ++k) {
                 const int id = op.inputs[k];
+                if (work.tensors[id].nchw44 && !nhwc_of.count(id)) {
+                    const GTensor t = work.tensors[id];
+                    const int nid = work.add_tensor(t.name + ":nhwc", t.c, t.h, t.w, t.scale);
+                    GOp r;
+                    r.type = OpType::RELAYOUT;
+                    r.name = t.name + ":to_nhwc";
+                    r.inputs = {id};
+                    r.mode = "NCHW44_NHWC";
+                    r.output = nid;
+                    ops.push_back(r);
+                    nhwc_of[id] = nid;
+                }
+                if (work.tensors[id].nchw44) {
+                    op.inputs[k] = nhwc_of[id];
+                    continue;
+                }
                 if (!work.tensors[id].nchw)
                     continue;
                 if ((op.type == OpType::CONV && !op.f32 && k == 0) || op.type == OpType::FOCUS)
@@ -843,10 +943,30 @@ int mb200c_compile(
         const size_t n_before = work.tensors.size();
         for (size_t id = 0; id < n_before; ++id) {
             GTensor& t = work.tensors[id];
-            if (!t.is_output || t.nchw)
+            if (!t.is_output || t.nchw || t.nchw44)
                 continue;
-            if (t.h == 1 && t.w == 1) {
+            const bool to44 = model44 && !t.f32 && t.c % 4 == 0;
+            if (t.h == 1 && t.w == 1 && !to44) {  // one pixel: NCHW is the channel vector
                 t.nchw = true;
+                continue;
+            }
+            if (to44) {
+                // (also for a single pixel: the visible tensor has five dims, the operator
+                // that produces it works on four)
+                const GTensor copy = t;
+                t.is_output = false;
+                const int nid = work.add_tensor(copy.name + ":nchw44", copy.c, copy.h, copy.w,
+                                                copy.scale);
+                work.tensors[nid].is_output = true;
+                work.tensors[nid].nchw44 = true;
+                std::swap(work.tensors[id].name, work.tensors[nid].name);
+                GOp r;
+                r.type = OpType::RELAYOUT;
+                r.name = copy.name + ":to_nchw44";
+                r.inputs = {(int)id};
+                r.mode = "NHWC_NCHW44";
+                r.output = nid;
+                ops.push_back(r);
                 continue;
             }
             const GTensor copy = t;
@@ -981,12 +1101,16 @@ int mb200c_compile(
                 use_count[id]++;
         for (size_t i = 0; i < work.tensors.size(); ++i) {
             const GTensor& t = work.tensors[i];
-            const std::vector<int> dims = {batch, t.c, t.h, t.w};
+            const std::vector<int> dims = t.nchw44 ? std::vector<int>{batch, t.c / 4, t.h, t.w, 4}
+                                                   : std::vector<int>{batch, t.c, t.h, t.w};
             const std::vector<int> stride =
-                    t.nchw ? contiguous(dims) : std::vector<int>{t.h * t.w * t.c, 1, t.w * t.c, t.c};
+                    t.nchw || t.nchw44 ? contiguous(dims)
+                                       : std::vector<int>{t.h * t.w * t.c, 1, t.w * t.c, t.c};
             auto n = fb::make_table();
             n->add_ref(fb::field::T_dtype, dtype_node(t.f32 ? fb::Float32 : fb::QInt8, t.scale));
-            n->add_ref(fb::field::T_layout, layout_node(dims, stride, t.nchw ? fb::NCHW : fb::NHWC));
+            n->add_ref(fb::field::T_layout,
+                       layout_node(dims, stride,
+                                   t.nchw44 ? fb::NCHW4 : t.nchw ? fb::NCHW : fb::NHWC));
             n->add<int64_t>(fb::field::T_offset, (int64_t)offsets[i]);
             n->add<int32_t>(fb::field::T_use_count, use_count[i]);
             n->add_ref(fb::field::T_name, fb::make_string(t.name));

@@ -288,6 +288,61 @@ int mb200_conv_pack_filter(
     return launch_pack_filter(a, flt_oihw, flt_packed, (cudaStream_t)stream);
 }
 
+int mb200_conv_pack_filter_nchw44(
+        const mb200_conv_param* p, int form, const int8_t* flt_nchw44, int8_t* flt_packed,
+        void* stream) {
+    ConvArgs a{};
+    int rc = make_args(p, 0, &a);
+    if (rc)
+        return rc;
+    if (!flt_nchw44 || !flt_packed)
+        return set_error(ST_NULL_PTR, "filter pointer is NULL");
+    const int icpg = a.ic / a.groups;
+    if (form < 0 || form > 2 || a.oc % 4 || (form == 0 && (a.groups != 1 || icpg % 4)) ||
+        (form == 1 && (a.groups != a.ic || a.oc != a.ic)) || (form == 2 && a.groups != 1))
+        return set_error(ST_INVALID_LAYOUT, "filter form %d does not fit %d -> %d channels in %d "
+                         "groups", form, a.ic, a.oc, a.groups);
+    cudaStream_t st = (cudaStream_t)stream;
+    // through OIHW in a scratch buffer of the filter's size: load-time work, so the
+    // allocation (and the synchronisation freeing it implies) is acceptable here
+    const size_t bytes = (size_t)a.oc * icpg * a.kh * a.kw;
+    int8_t* oihw = nullptr;
+    if (cudaMalloc(&oihw, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return set_error(ST_MALLOC, "cannot allocate %zu bytes of filter scratch", bytes);
+    }
+    rc = launch_filter_nchw44_to_oihw(a, form, flt_nchw44, oihw, st);
+    if (!rc)
+        rc = conv_s2d_supported(a) ? launch_conv_s2d_pack_filter(a, oihw, flt_packed, st)
+                                   : launch_pack_filter(a, oihw, flt_packed, st);
+    cudaStreamSynchronize(st);
+    cudaFree(oihw);
+    return rc;
+}
+
+int mb200_relayout_nchw44_to_nhwc_s8(
+        const int8_t* src, int8_t* dst, int n, int c, int h, int w, void* stream) {
+    if (!src || !dst)
+        return set_error(ST_NULL_PTR, "relayout tensor pointer is NULL");
+    if (c % 4 || (((uintptr_t)src | (uintptr_t)dst) & 3))
+        return set_error(ST_INVALID_LAYOUT, "NCHW44 needs channels %% 4 == 0 and 4-byte aligned "
+                                            "tensors");
+    // [N][C/4][HW] four-byte groups -> [N][HW][C/4]
+    return launch_transpose_f32((const float*)src, (float*)dst, n, c / 4, h * w,
+                                (cudaStream_t)stream);
+}
+
+int mb200_relayout_nhwc_to_nchw44_s8(
+        const int8_t* src, int8_t* dst, int n, int c, int h, int w, void* stream) {
+    if (!src || !dst)
+        return set_error(ST_NULL_PTR, "relayout tensor pointer is NULL");
+    if (c % 4 || (((uintptr_t)src | (uintptr_t)dst) & 3))
+        return set_error(ST_INVALID_LAYOUT, "NCHW44 needs channels %% 4 == 0 and 4-byte aligned "
+                                            "tensors");
+    return launch_transpose_f32((const float*)src, (float*)dst, n, h * w, c / 4,
+                                (cudaStream_t)stream);
+}
+
 int mb200_conv_bias_qs8_nhwc(
         const mb200_conv_param* p, const int8_t* src, int src_is_nchw, const int8_t* flt_packed,
         const int32_t* bias, const float* flt_scales, int8_t* dst, int algo, void* stream) {

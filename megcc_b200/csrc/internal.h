@@ -66,6 +66,10 @@ int check_launch(const char* what);
 int* device_status_word(cudaStream_t st);
 
 int launch_pack_filter(const ConvArgs& a, const int8_t* src, int8_t* dst, cudaStream_t st);
+int launch_filter_nchw44_to_oihw(
+        const ConvArgs& a, int form, const int8_t* src, int8_t* dst, cudaStream_t st);
+int launch_transpose_f32(
+        const float* src, float* dst, int batch, int rows, int cols, cudaStream_t st);
 int launch_conv_direct(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
         const float* flt_scales, int8_t* dst, int32_t* acc, cudaStream_t st);

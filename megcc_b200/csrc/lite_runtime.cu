@@ -76,7 +76,8 @@ enum OpKind {
     OP_CONV, OP_POOL, OP_QELEM, OP_TYPECVT, OP_RELAYOUT_TO_NHWC, OP_RELAYOUT_TO_NCHW, OP_MATMUL,
     // fp32 path
     OP_CONV_F32, OP_MATMUL_F32, OP_ELEM_F32, OP_CONCAT_F32, OP_FOCUS_F32, OP_RESIZE_F32,
-    OP_POOL_F32, OP_RELAYOUT_F32_TO_NHWC, OP_RELAYOUT_F32_TO_NCHW,
+    OP_POOL_F32, OP_RELAYOUT_F32_TO_NHWC, OP_RELAYOUT_F32_TO_NCHW, OP_RELAYOUT_44_TO_NHWC,
+    OP_RELAYOUT_NHWC_TO_44,
     // a symbol this library has no implementation for: runs only through a registered table
     OP_EXTERNAL
 };
@@ -92,6 +93,7 @@ struct OpPlan {
     std::vector<int> weight_inputs;  // indices (into inputs) that are weights
     Workspace ws{nullptr, 0, 0};
     bool needs_init = false;
+    int flt44 = 0;         // filter layout: 0 OIHW, 1 / 2 / 3 NCHW44 dense / channel-wise / first layer
     int z_mode = 0;        // fused elemwise step: 0 none, else MB200_QADD + 1 / MB200_QFUSE_ADD_RELU + 1
     bool f32_z = false;    // fp32 ConvBias with a tensor added after the activation
     int oc = 0, icpg = 0;  // fp32 ConvBias: output channels, input channels per group (symbol)
@@ -296,12 +298,22 @@ bool ends_with(const std::string& s, const char* suf) {
 bool parse_symbol(const std::string& sym, OpPlan* op) {
     op->symbol = sym;
     if (sym.compare(0, 18, "cuda_sm100_conv2d_") == 0) {
-        char sparse[16] = {0};
+        char sparse[16] = {0}, format[16] = {0};
         int used = 0;
-        if (sscanf(sym.c_str(), "cuda_sm100_conv2d_%dx%d_NHWC_%15[A-Z]_p%dx%d_s%dx%d_d%dx%d_%n",
-                   &op->kh, &op->kw, sparse, &op->ph, &op->pw, &op->sh, &op->sw, &op->dh,
-                   &op->dw, &used) != 9 ||
+        if (sscanf(sym.c_str(),
+                   "cuda_sm100_conv2d_%dx%d_%15[A-Z0-9]_%15[A-Z]_p%dx%d_s%dx%d_d%dx%d_%n", &op->kh,
+                   &op->kw, format, sparse, &op->ph, &op->pw, &op->sh, &op->sw, &op->dh, &op->dw,
+                   &used) != 10 ||
             used == 0)
+            return false;
+        // activations are NHWC; NHWC44D / NHWC44C / NHWC44H say the filter arrives in the
+        // dense / channel-wise / first-layer NCHW44 layout
+        static const char* kFormats[] = {"NHWC", "NHWC44D", "NHWC44C", "NHWC44H"};
+        op->flt44 = -1;
+        for (int f = 0; f < 4; ++f)
+            if (strcmp(format, kFormats[f]) == 0)
+                op->flt44 = f;
+        if (op->flt44 < 0)
             return false;
         op->dense = strcmp(sparse, "DENSE") == 0;
         if (!op->dense && strcmp(sparse, "GROUP") != 0)
@@ -311,6 +323,8 @@ bool parse_symbol(const std::string& sym, OpPlan* op) {
         if ((sscanf(rest.c_str(), "oc%d_icpg%d_f32%n", &oc, &icpg, &used2) == 2 && used2 > 0) ||
             (icpg = 0, sscanf(rest.c_str(), "oc%d_f32%n", &oc, &used2) == 1 && used2 > 0)) {
             // fp32 ConvBias: ..._oc<N>[_icpg<M>]_f32[_bias][_ACT][_z_ADD]
+            if (op->flt44)
+                return false;
             op->kind = OP_CONV_F32;
             op->oc = oc;
             op->icpg = icpg;
@@ -419,6 +433,14 @@ bool parse_symbol(const std::string& sym, OpPlan* op) {
         op->kind = ends_with(sym, "f32f32") ? OP_RELAYOUT_F32_TO_NHWC : OP_RELAYOUT_TO_NHWC;
         return true;
     }
+    if (sym.compare(0, 32, "cuda_sm100_relayout_NCHW44_NHWC_") == 0) {
+        op->kind = OP_RELAYOUT_44_TO_NHWC;
+        return true;
+    }
+    if (sym.compare(0, 32, "cuda_sm100_relayout_NHWC_NCHW44_") == 0) {
+        op->kind = OP_RELAYOUT_NHWC_TO_44;
+        return true;
+    }
     if (sym.compare(0, 30, "cuda_sm100_relayout_NHWC_NCHW_") == 0) {
         op->kind = ends_with(sym, "f32f32") ? OP_RELAYOUT_F32_TO_NCHW : OP_RELAYOUT_TO_NCHW;
         return true;
@@ -450,11 +472,19 @@ void fill_conv_param(const OpPlan& op, Tensor* const* inputs, const Tensor* dst,
     p->pad_w = op.pw;
     p->dilate_h = op.dh;
     p->dilate_w = op.dw;
-    // the original filter is [OC][IC][KH][KW] or [G][OCpg][ICpg][KH][KW]
+    // the original filter is [OC][IC][KH][KW] or [G][OCpg][ICpg][KH][KW]; in the NCHW44
+    // layouts the leading extent counts blocks of four output channels (or groups)
     const Layout& l = flt->layout;
-    p->groups = op.dense ? 1 : (int)l.dims[0];
-    p->oc = dst ? (int)dst->layout.dims[1]
-                : (op.dense ? (int)l.dims[0] : (int)(l.dims[0] * l.dims[1]));
+    if (op.flt44) {
+        // (after Init the first-layer filter may be a flat buffer: with dst given, the
+        // channel count comes from dst)
+        p->groups = op.dense ? 1 : (int)l.dims[0] * 4;
+        p->oc = dst ? (int)dst->layout.dims[1] : (int)l.dims[0] * 4;
+    } else {
+        p->groups = op.dense ? 1 : (int)l.dims[0];
+        p->oc = dst ? (int)dst->layout.dims[1]
+                    : (op.dense ? (int)l.dims[0] : (int)(l.dims[0] * l.dims[1]));
+    }
     p->nonline = op.mode;
     p->src_scale = src->dtype.param.scale;
     p->flt_scale = flt->dtype.param.scale;
@@ -569,6 +599,18 @@ TinyNNStatus builtin_kernel(
             return (TinyNNStatus)fn((const int8_t*)s->ptr, (int8_t*)dst->ptr, s->layout.dims[0],
                                     s->layout.dims[1], s->layout.dims[2], s->layout.dims[3], st);
         }
+        case OP_RELAYOUT_44_TO_NHWC: {  // src [N][C/4][H][W][4]
+            const Tensor* s = inputs[0];
+            return (TinyNNStatus)mb200_relayout_nchw44_to_nhwc_s8(
+                    (const int8_t*)s->ptr, (int8_t*)dst->ptr, s->layout.dims[0],
+                    s->layout.dims[1] * 4, s->layout.dims[2], s->layout.dims[3], st);
+        }
+        case OP_RELAYOUT_NHWC_TO_44: {
+            const Tensor* s = inputs[0];
+            return (TinyNNStatus)mb200_relayout_nhwc_to_nchw44_s8(
+                    (const int8_t*)s->ptr, (int8_t*)dst->ptr, s->layout.dims[0], s->layout.dims[1],
+                    s->layout.dims[2], s->layout.dims[3], st);
+        }
         case OP_RELAYOUT_F32_TO_NHWC:
         case OP_RELAYOUT_F32_TO_NCHW: {
             const Tensor* s = inputs[0];
@@ -669,7 +711,7 @@ TinyNNStatus builtin_init(
     };
     switch (op.kind) {
         case OP_CONV: {
-            if (w->layout.nr_dim != 4 && w->layout.nr_dim != 5)
+            if (w->layout.nr_dim < 4 || w->layout.nr_dim > 6)
                 return TinyNN_ERROR_INVALID_LAYOUT;
             mb200_conv_param p;
             fill_conv_param(op, inputs, nullptr, &p);
@@ -686,6 +728,10 @@ TinyNNStatus builtin_init(
                 }
                 return TinyNN_SUCCESS;
             }
+            if (op.flt44)
+                return (TinyNNStatus)mb200_conv_pack_filter_nchw44(
+                        &p, op.flt44 - 1, (const int8_t*)w->ptr, (int8_t*)out_weights->ptr,
+                        opt->stream);
             return (TinyNNStatus)(
                     s2d ? mb200_conv_s2d_pack_filter(&p, (const int8_t*)w->ptr,
                                                      (int8_t*)out_weights->ptr, opt->stream)
@@ -746,18 +792,44 @@ const char* check_operands(const OpPlan& op) {
             const Tensor* flt = op.inputs[1];
             if (!rank4(in0) || !rank4(out))
                 return "ConvBias operands must have 4 dims";
-            if (!flt->is_weight || (flt->layout.nr_dim != 4 && flt->layout.nr_dim != 5))
-                return "ConvBias filter must be a weight with 4 or 5 dims";
+            if (!flt->is_weight)
+                return "ConvBias filter must be a weight";
             if (op.kh <= 0 || op.kw <= 0 || op.sh <= 0 || op.sw <= 0)
                 return "ConvBias attributes";
             const Layout& l = flt->layout;
-            const size_t oc = l.nr_dim == 4 ? l.dims[0] : (size_t)l.dims[0] * l.dims[1];
-            const size_t icpg = l.nr_dim == 4 ? l.dims[1] : l.dims[2];
-            const size_t groups = l.nr_dim == 4 ? 1 : l.dims[0];
-            if (l.dims[l.nr_dim - 2] != (uint32_t)op.kh || l.dims[l.nr_dim - 1] != (uint32_t)op.kw)
-                return "filter extent differs from the symbol";
-            if (icpg * groups != in0->layout.dims[1] || oc != out->layout.dims[1] ||
-                (op.dense != (l.nr_dim == 4)))
+            size_t oc, icpg, groups;
+            if (op.flt44 == 1) {
+                // [OC/4][IC/4][KH][KW][4][4]
+                if (l.nr_dim != 6 || l.dims[2] != (uint32_t)op.kh || l.dims[3] != (uint32_t)op.kw ||
+                    l.dims[4] != 4 || l.dims[5] != 4 || !op.dense)
+                    return "dense NCHW44 filter must be [OC/4][IC/4][KH][KW][4][4]";
+                oc = (size_t)l.dims[0] * 4, icpg = (size_t)l.dims[1] * 4, groups = 1;
+            } else if (op.flt44 == 2) {
+                // [G/4][1][1][KH][KW][4]
+                if (l.nr_dim != 6 || l.dims[1] != 1 || l.dims[2] != 1 ||
+                    l.dims[3] != (uint32_t)op.kh || l.dims[4] != (uint32_t)op.kw ||
+                    l.dims[5] != 4 || op.dense)
+                    return "channel-wise NCHW44 filter must be [G/4][1][1][KH][KW][4]";
+                oc = groups = (size_t)l.dims[0] * 4, icpg = 1;
+            } else if (op.flt44 == 3) {
+                // [OC/4][KH][KW][IC][4]
+                if (l.nr_dim != 5 || l.dims[4] != 4 || l.dims[1] != (uint32_t)op.kh ||
+                    l.dims[2] != (uint32_t)op.kw || !op.dense)
+                    return "first-layer NCHW44 filter must be [OC/4][KH][KW][IC][4]";
+                oc = (size_t)l.dims[0] * 4, icpg = l.dims[3], groups = 1;
+            } else {
+                if (l.nr_dim != 4 && l.nr_dim != 5)
+                    return "ConvBias filter must have 4 or 5 dims";
+                oc = l.nr_dim == 4 ? l.dims[0] : (size_t)l.dims[0] * l.dims[1];
+                icpg = l.nr_dim == 4 ? l.dims[1] : l.dims[2];
+                groups = l.nr_dim == 4 ? 1 : l.dims[0];
+                if (l.dims[l.nr_dim - 2] != (uint32_t)op.kh ||
+                    l.dims[l.nr_dim - 1] != (uint32_t)op.kw)
+                    return "filter extent differs from the symbol";
+                if (op.dense != (l.nr_dim == 4))
+                    return "filter rank does not match the sparse mode";
+            }
+            if (icpg * groups != in0->layout.dims[1] || oc != out->layout.dims[1])
                 return "filter channels do not match the tensors";
             if (out->layout.dims[0] != in0->layout.dims[0] ||
                 (int)out->layout.dims[2] != extent(in0->layout.dims[2], op.kh, op.sh, op.ph) ||
@@ -814,6 +886,18 @@ const char* check_operands(const OpPlan& op) {
                 if (in0->layout.dims[d] != out->layout.dims[d])
                     return "Relayout keeps the logical extents";
             return nullptr;
+        case OP_RELAYOUT_44_TO_NHWC:
+        case OP_RELAYOUT_NHWC_TO_44: {
+            const Tensor* t44 = op.kind == OP_RELAYOUT_44_TO_NHWC ? in0 : out;
+            const Tensor* t4 = op.kind == OP_RELAYOUT_44_TO_NHWC ? out : in0;
+            if (t44->layout.nr_dim != 5 || t44->layout.dims[4] != 4 || !rank4(t4) ||
+                t44->layout.dims[0] != t4->layout.dims[0] ||
+                t44->layout.dims[1] * 4 != t4->layout.dims[1] ||
+                t44->layout.dims[2] != t4->layout.dims[2] ||
+                t44->layout.dims[3] != t4->layout.dims[3])
+                return "NCHW44 Relayout operands must be [N][C/4][H][W][4] and [N][C][H][W]";
+            return nullptr;
+        }
         case OP_QELEM:
         case OP_ELEM_F32:
             for (auto* t : op.inputs)

@@ -27,6 +27,41 @@ __global__ void pack_filter_kernel(
 }
 
 // ------------------------------------------------------------------------------------------
+// NCHW44 filters (what a model compiled with --enable_nchw44 carries) -> OIHW, after which
+// the usual packing applies. Index formulas of compiler/lib/KernelGen/BareMetal/ConvKernel.cpp
+// :48-62,88-101:
+//   form 0 dense        [OC/4][IC/4][KH][KW][4 ic][4 oc]
+//   form 1 channel-wise [G/4][1][1][KH][KW][4]            (one input channel per group)
+//   form 2 first layer  [OC/4][KH][KW][IC][4 oc]          (NCHW input, NCHW44 output)
+// dst: OIHW, or [G][1][1][KH][KW] for form 1
+// ------------------------------------------------------------------------------------------
+__global__ void filter_nchw44_to_oihw_kernel(
+        const int8_t* __restrict__ src, int8_t* __restrict__ dst, int form, int oc, int icpg,
+        int kh, int kw) {
+    const size_t total = (size_t)oc * icpg * kh * kw;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        // i indexes dst: [o][c][fy][fx]
+        const int fx = (int)(i % kw);
+        size_t t = i / kw;
+        const int fy = (int)(t % kh);
+        t /= kh;
+        const int c = (int)(t % icpg);
+        const int o = (int)(t / icpg);
+        size_t off;
+        if (form == 0)
+            off = (size_t)(o / 4) * ((size_t)icpg * kh * kw * 4) + (size_t)(c / 4) * (kh * kw * 16) +
+                  (size_t)fy * (kw * 16) + (size_t)fx * 16 + (c % 4) * 4 + (o % 4);
+        else if (form == 1)
+            off = (size_t)(o / 4) * (kh * kw * 4) + (size_t)fy * (kw * 4) + (size_t)fx * 4 + (o % 4);
+        else
+            off = (size_t)(o / 4) * ((size_t)4 * kh * kw * icpg) + (size_t)fy * (kw * icpg * 4) +
+                  (size_t)fx * (icpg * 4) + (size_t)c * 4 + (o % 4);
+        dst[i] = src[off];
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // general direct ConvBias. One thread per (output pixel, output channel), channel fastest,
 // so a warp shares one input window (broadcast loads) and writes 32 contiguous bytes.
 // ------------------------------------------------------------------------------------------
@@ -510,6 +545,15 @@ int launch_pack_filter(
     const size_t total = (size_t)a.oc * icpg * a.kh * a.kw;
     pack_filter_kernel<<<grid_for(total, 256), 256, 0, st>>>(src, dst, a.oc, icpg, a.kh, a.kw);
     return check_launch("pack_filter");
+}
+
+int launch_filter_nchw44_to_oihw(
+        const ConvArgs& a, int form, const int8_t* src, int8_t* dst, cudaStream_t st) {
+    const int icpg = a.ic / a.groups;
+    const size_t total = (size_t)a.oc * icpg * a.kh * a.kw;
+    filter_nchw44_to_oihw_kernel<<<grid_for(total, 256), 256, 0, st>>>(src, dst, form, a.oc, icpg,
+                                                                       a.kh, a.kw);
+    return check_launch("filter_nchw44_to_oihw");
 }
 
 int launch_conv_direct(

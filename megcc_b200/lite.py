@@ -172,6 +172,19 @@ class Network:
         check(lib().LITE_get_tensor_total_size_in_byte(self.tensor(name, phase), C.byref(n)))
         return n.value
 
+    def _shape(self, name, phase):
+        # quantised tensors have no lite data type: for them the call fails with
+        # TinyNN_ERROR_OUT_OF_RANGE, as the reference's does (runtime/src/lite/tensor.c:11-40)
+        lay = LiteLayout()
+        check(lib().LITE_get_tensor_layout(self.tensor(name, phase), C.byref(lay)))
+        return tuple(int(lay.shapes[i]) for i in range(lay.ndim))
+
+    def input_shape(self, name):
+        return self._shape(name, LITE_INPUT)
+
+    def output_shape(self, name):
+        return self._shape(name, LITE_OUTPUT)
+
     def set_input(self, name, array):
         """Host numpy array: borrowed until the next set_input / close."""
         a = np.ascontiguousarray(array)

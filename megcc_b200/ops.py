@@ -314,3 +314,54 @@ def typecvt_qs8_f32(src, s_src, s_dst):
     dst = torch.empty(src.shape, dtype=torch.float32, device=src.device)
     check(lib().mb200_typecvt_qs8_f32(_ptr(src), _ptr(dst), src.numel(), s_src, s_dst, _stream()))
     return dst
+
+
+def conv_s2d_supported(p):
+    return bool(lib().mb200_conv_s2d_supported(C.byref(p)))
+
+
+def conv_bias_qs8_s2d(p, src, flt_packed, bias, flt_scales=None, src_is_nchw=True):
+    """First-layer ConvBias (few input channels) through the space-to-depth form; flt_packed
+    from mb200_conv_s2d_pack_filter or pack_filter_nchw44."""
+    oh, ow = out_hw(p)
+    dst = torch.empty((p.n, oh, ow, p.oc), dtype=torch.int8, device=src.device)
+    nbytes = lib().mb200_conv_s2d_workspace_bytes(C.byref(p))
+    keep, ws = _scratch(nbytes, src.device)
+    check(lib().mb200_conv_bias_qs8_s2d(
+        C.byref(p), _ptr(src), int(src_is_nchw), _ptr(flt_packed), _ptr(bias), _ptr(flt_scales),
+        _ptr(dst), ws, nbytes, _stream()))
+    return dst
+
+
+# ---- NCHW44 (models compiled with --enable_nchw44) ----
+NCHW44_FORMS = {"dense": 0, "channel_wise": 1, "first_layer": 2}
+
+
+def pack_filter_nchw44(p, flt44, form):
+    """Filter in an NCHW44 layout (dense [OC/4,IC/4,KH,KW,4,4], channel_wise [G/4,1,1,KH,KW,4],
+    first_layer [OC/4,KH,KW,IC,4]) -> the packing the ConvBias entry points read: the
+    space-to-depth packing where conv_s2d_supported(p), the K-major one otherwise."""
+    s2d = bool(lib().mb200_conv_s2d_supported(C.byref(p)))
+    nbytes = (lib().mb200_conv_s2d_filter_bytes if s2d else lib().mb200_conv_packed_filter_bytes)(
+        C.byref(p))
+    packed = torch.empty(nbytes, dtype=torch.int8, device=flt44.device)
+    check(lib().mb200_conv_pack_filter_nchw44(C.byref(p), NCHW44_FORMS[form], _ptr(flt44),
+                                              _ptr(packed), _stream()))
+    return packed
+
+
+def nchw44_to_nhwc(src):
+    """[N, C/4, H, W, 4] int8 -> [N, H, W, C]"""
+    n, cb, h, w, four = src.shape
+    assert four == 4
+    dst = torch.empty((n, h, w, cb * 4), dtype=torch.int8, device=src.device)
+    check(lib().mb200_relayout_nchw44_to_nhwc_s8(_ptr(src), _ptr(dst), n, cb * 4, h, w, _stream()))
+    return dst
+
+
+def nhwc_to_nchw44(src):
+    """[N, H, W, C] int8 -> [N, C/4, H, W, 4]"""
+    n, h, w, c = src.shape
+    dst = torch.empty((n, c // 4, h, w, 4), dtype=torch.int8, device=src.device)
+    check(lib().mb200_relayout_nhwc_to_nchw44_s8(_ptr(src), _ptr(dst), n, c, h, w, _stream()))
+    return dst

@@ -83,17 +83,32 @@ class NetSpec:
                 total += oc * oh * ow * (ic // l["groups"]) * k * k
         return total
 
-    def to_graph(self):
-        g = Graph(self.name)
-        ids = {"data": g.input("data", self.input["c"], self.input["h"], self.input["w"],
-                               self.input["scale"])}
+    def to_graph(self, nchw44=False):
+        """nchw44: build the model as MegCC's --enable_nchw44 would hand it over: filters in
+        the NCHW44 layouts (first-layer form on the NCHW input, dense, channel-wise), outputs
+        handed back as [N, C/4, H, W, 4]. Operators whose channel counts are not multiples
+        of 4 (other than the first layer's input) have no NCHW44 form."""
+        g = Graph(self.name + ("_nchw44" if nchw44 else ""))
+        # an NCHW44 model's input is NCHW44 itself unless its channels do not fill blocks of
+        # four (the image input of a first layer)
+        in44 = nchw44 and self.input["c"] % 4 == 0
+        ids = {"data": (g.input_nchw44 if in44 else g.input)(
+            "data", self.input["c"], self.input["h"], self.input["w"], self.input["scale"])}
         for l in self.layers:
             if l["op"] == "conv":
                 pc = np.ndim(l["s_flt"]) > 0
+                s_flt = float(np.mean(l["s_flt"])) if pc else l["s_flt"]
+                if nchw44:
+                    form = ("first_layer" if l["src"] == "data" and not in44
+                            else "dense" if l["groups"] == 1 else "channel_wise")
+                    ids[l["name"]] = g.conv_bias_nchw44(
+                        l["name"], ids[l["src"]], filter_to_nchw44(l["flt"], form), l["bias"],
+                        l["stride"], l["pad"], s_flt, l["s_dst"], form, l["act"],
+                        l["s_flt"] if pc else None)
+                    continue
                 ids[l["name"]] = g.conv_bias(
                     l["name"], ids[l["src"]], l["flt"], l["bias"], l["stride"], l["pad"],
-                    float(np.mean(l["s_flt"])) if pc else l["s_flt"], l["s_dst"], l["act"],
-                    l["groups"], l["s_flt"] if pc else None)
+                    s_flt, l["s_dst"], l["act"], l["groups"], l["s_flt"] if pc else None)
             elif l["op"] == "pool":
                 ids[l["name"]] = g.pooling(l["name"], ids[l["src"]], l["mode"], l["window"],
                                            l["stride"], l["pad"])
@@ -102,6 +117,27 @@ class NetSpec:
                                              None if l["b"] is None else ids[l["b"]], l["s_dst"])
         g.mark_output(ids[self.output])
         return g
+
+
+def filter_to_nchw44(flt, form):
+    """OIHW or [G, 1, 1, KH, KW] int8 -> the NCHW44 filter layouts MegEngine's layout
+    transform produces (index formulas: compiler/lib/KernelGen/BareMetal/ConvKernel.cpp
+    :48-62,88-101): dense [OC/4, IC/4, KH, KW, 4 ic, 4 oc], channel_wise
+    [G/4, 1, 1, KH, KW, 4], first_layer [OC/4, KH, KW, IC, 4 oc]."""
+    flt = np.asarray(flt)
+    kh, kw = flt.shape[-2:]
+    if form == "dense":
+        oc, ic = flt.shape[:2]
+        return np.ascontiguousarray(
+            flt.reshape(oc // 4, 4, ic // 4, 4, kh, kw).transpose(0, 2, 4, 5, 3, 1))
+    if form == "channel_wise":
+        g = flt.shape[0]
+        return np.ascontiguousarray(
+            flt.reshape(g // 4, 4, kh, kw).transpose(0, 2, 3, 1).reshape(g // 4, 1, 1, kh, kw, 4))
+    if form == "first_layer":
+        oc, ic = flt.shape[:2]
+        return np.ascontiguousarray(flt.reshape(oc // 4, 4, ic, kh, kw).transpose(0, 3, 4, 2, 1))
+    raise ValueError(f"unknown NCHW44 filter form {form!r}")
 
 
 def resnet18(seed=0, classes=1000, hw=224, per_channel=False):

@@ -346,6 +346,99 @@ def ref_conv_bias_qs8(src, flt, bias, stride, pad, s_src, s_flt, s_dst, act="IDE
     return dst
 
 
+# ---- NCHW44: the layouts of a model compiled with --enable_nchw44 ----
+def nchw_to_nchw44(x):
+    """[N, C, H, W] -> [N, C/4, H, W, 4] (compiler/lib/KernelGen/BareMetal/FormatHelper.cpp:23-26:
+    offset = n*s0 + (c/4)*s1 + h*s2 + w*s3 + c%4)."""
+    n, c, h, w = x.shape
+    assert c % 4 == 0
+    return np.ascontiguousarray(x.reshape(n, c // 4, 4, h, w).transpose(0, 1, 3, 4, 2))
+
+
+def nchw44_to_nchw(x):
+    n, cb, h, w, four = x.shape
+    assert four == 4
+    return np.ascontiguousarray(x.transpose(0, 1, 4, 2, 3).reshape(n, cb * 4, h, w))
+
+
+def filter_to_nchw44(flt, form):
+    """OIHW (dense, first_layer) or [G, 1, 1, KH, KW] (channel_wise) -> the NCHW44 filter
+    layouts of compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:48-62,88-101."""
+    flt = np.asarray(flt)
+    if form == "dense":  # [OC/4][IC/4][KH][KW][4 ic][4 oc]
+        oc, ic, kh, kw = flt.shape
+        return np.ascontiguousarray(
+            flt.reshape(oc // 4, 4, ic // 4, 4, kh, kw).transpose(0, 2, 4, 5, 3, 1))
+    if form == "channel_wise":  # [G/4][1][1][KH][KW][4]
+        g = flt.shape[0]
+        kh, kw = flt.shape[-2:]
+        return np.ascontiguousarray(
+            flt.reshape(g // 4, 4, kh, kw).transpose(0, 2, 3, 1).reshape(g // 4, 1, 1, kh, kw, 4))
+    if form == "first_layer":  # [OC/4][KH][KW][IC][4 oc]
+        oc, ic, kh, kw = flt.shape
+        return np.ascontiguousarray(flt.reshape(oc // 4, 4, ic, kh, kw).transpose(0, 3, 4, 2, 1))
+    raise ValueError(form)
+
+
+def filter_from_nchw44(flt44, form):
+    """Inverse of filter_to_nchw44: back to OIHW, or [G, 1, 1, KH, KW] for channel_wise."""
+    flt44 = np.asarray(flt44)
+    if form == "dense":
+        ob, ib, kh, kw, _, _ = flt44.shape
+        return np.ascontiguousarray(
+            flt44.transpose(0, 5, 1, 4, 2, 3).reshape(ob * 4, ib * 4, kh, kw))
+    if form == "channel_wise":
+        gb, _, _, kh, kw, _ = flt44.shape
+        return np.ascontiguousarray(
+            flt44.reshape(gb, kh, kw, 4).transpose(0, 3, 1, 2).reshape(gb * 4, 1, 1, kh, kw))
+    if form == "first_layer":
+        ob, kh, kw, ic, _ = flt44.shape
+        return np.ascontiguousarray(flt44.transpose(0, 4, 3, 1, 2).reshape(ob * 4, ic, kh, kw))
+    raise ValueError(form)
+
+
+def conv_bias_qs8_nchw44(src, flt44, bias, stride, pad, s_src, s_flt, s_dst, form,
+                         act="IDENTITY"):
+    """ConvBias of an NCHW44 model, restated as layout conversions around the NCHW
+    restatement: src [N, C/4, H, W, 4] (NCHW for form "first_layer"), result [N, OC/4, OH, OW, 4].
+    Pinned to the reference's own NCHW44 kernels by tests/test_oracle_vs_reference.py."""
+    x = np.asarray(src) if form == "first_layer" else nchw44_to_nchw(np.asarray(src))
+    flt = filter_from_nchw44(flt44, form)
+    groups = flt.shape[0] if form == "channel_wise" else 1
+    out = conv_bias_qs8(x, flt, bias, stride, pad, s_src, s_flt, s_dst, act, groups=groups)
+    return nchw_to_nchw44(out)
+
+
+def ref_conv_bias_qs8_nchw44(src, flt44, bias, stride, pad, s_src, s_flt, s_dst, form,
+                             act="IDENTITY"):
+    """The reference's ConvGeneral generated for format NCHW44 (symbol naming of
+    compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:144-176 with get_format's NCHW_NCHW44)."""
+    src, flt44 = _c(src, np.int8), _c(flt44, np.int8)
+    oc = flt44.shape[0] * 4
+    if form == "first_layer":
+        kh, kw = flt44.shape[1:3]
+        fmt, sparse = "NCHW_NCHW44", "DENSE"
+    elif form == "channel_wise":
+        kh, kw = flt44.shape[3:5]
+        fmt, sparse = "NCHW44", "GROUP"
+    else:
+        kh, kw = flt44.shape[2:4]
+        fmt, sparse = "NCHW44", "DENSE"
+    ih, iw = src.shape[2], src.shape[3]
+    oh, ow = out_extent(ih, kh, stride, pad), out_extent(iw, kw, stride, pad)
+    dst = np.empty((src.shape[0], oc // 4, oh, ow, 4), np.int8)
+    b = (np.zeros((0,), np.int32) if bias is None
+         else _c(np.asarray(bias).reshape(1, oc // 4, 1, 1, 4), np.int32))
+    sym = (f"kernel_conv2d_{kh}x{kw}_{fmt}_{sparse}_p{pad}x{pad}_s{stride}x{stride}_d1x1_"
+           f"qsi8qsi8qsi32qsi8")
+    if bias is not None:
+        sym += "_bias"
+    if act != "IDENTITY":
+        sym += "_" + act
+    ref_call(sym, [(src, s_src), (flt44, s_flt), (b, s_src * s_flt)], [(dst, s_dst)])
+    return dst
+
+
 def ref_pooling_qs8(src, mode, window, stride, pad, scale=1.0):
     src = _c(src, np.int8)
     n, c, ih, iw = src.shape

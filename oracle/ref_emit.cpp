@@ -149,6 +149,44 @@ int main(int argc, char** argv) {
             attrs["operand:3"] = CCAttr(make_operand("qsi8", {1, c, 16, 16}));
             attrs["nr_operands"] = CCAttr((int)4);
             ok = pick(KernType::ConvKernel, attrs, em);
+        } else if (kind == "conv44") {
+            // conv44 <kh> <kw> <sh> <sw> <ph> <pw> <DENSE|GROUP|HYBRID> <nonline> <bias 0|1>
+            // format NCHW44: tensors [N][C/4][H][W][4]; GROUP is channel-wise; HYBRID is the
+            // first layer with an NCHW input, which the reference names NCHW_NCHW44
+            // (compiler/lib/KernelGen/BareMetal/ConvKernel.cpp:111-121)
+            uint32_t kh, kw, sh, sw, ph, pw;
+            std::string sparse, nonline;
+            int bias;
+            ls >> kh >> kw >> sh >> sw >> ph >> pw >> sparse >> nonline >> bias;
+            const bool hybrid = sparse == "HYBRID";
+            attrs["kernel_h"] = CCAttr(kh);
+            attrs["kernel_w"] = CCAttr(kw);
+            attrs["stride_h"] = CCAttr(sh);
+            attrs["stride_w"] = CCAttr(sw);
+            attrs["pad_h"] = CCAttr(ph);
+            attrs["pad_w"] = CCAttr(pw);
+            attrs["dilate_h"] = CCAttr((uint32_t)1);
+            attrs["dilate_w"] = CCAttr((uint32_t)1);
+            attrs["sparse"] = CCAttr(hybrid ? std::string("DENSE") : sparse);
+            attrs["format"] = CCAttr("NCHW44");
+            attrs["mode"] = CCAttr("CROSS_CORRELATION");
+            attrs["nonlineMode"] = CCAttr(nonline);
+            attrs["compute_mode"] = CCAttr("DEFAULT");
+            if (hybrid) {
+                attrs["operand:0"] = CCAttr(make_operand("qsi8", {1, 3, 16, 16}));
+                attrs["operand:1"] = CCAttr(make_operand("qsi8", {2, kh, kw, 3, 4}));
+            } else if (sparse == "DENSE") {
+                attrs["operand:0"] = CCAttr(make_operand("qsi8", {1, 2, 16, 16, 4}));
+                attrs["operand:1"] = CCAttr(make_operand("qsi8", {2, 2, kh, kw, 4, 4}));
+            } else {
+                attrs["operand:0"] = CCAttr(make_operand("qsi8", {1, 2, 16, 16, 4}));
+                attrs["operand:1"] = CCAttr(make_operand("qsi8", {2, 1, 1, kh, kw, 4}));
+            }
+            attrs["operand:2"] = bias ? CCAttr(make_operand("qsi32", {1, 2, 1, 1, 4}))
+                                      : CCAttr(make_operand("qsi32", {}));
+            attrs["operand:3"] = CCAttr(make_operand("qsi8", {1, 2, 16, 16, 4}));
+            attrs["nr_operands"] = CCAttr((int)4);
+            ok = pick(KernType::ConvKernel, attrs, em);
         } else if (kind == "pool") {
             // pool <mode> <wh> <ww> <sh> <sw> <ph> <pw>
             std::string mode;

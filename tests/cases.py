@@ -109,6 +109,59 @@ def conv_model_shapes():
     return out
 
 
+def conv_nchw44_catalogue():
+    """ConvBias as a model compiled with --enable_nchw44 carries it: dense, channel-wise and
+    first-layer (NCHW input) filters, each at a toy size and at one that reaches the
+    tensor-core kernels. `form` names the filter layout; inputs are built in NCHW / OIHW by
+    conv_inputs and converted by conv_nchw44_inputs."""
+    out = []
+    forms = [
+        ("dense", 1, 1, 0, "RELU", True), ("dense", 3, 1, 1, "RELU", True),
+        ("dense", 3, 2, 1, "IDENTITY", True), ("dense", 3, 1, 1, "H_SWISH", False),
+        ("channel_wise", 3, 1, 1, "RELU", True), ("channel_wise", 3, 2, 1, "IDENTITY", True),
+        ("channel_wise", 5, 1, 2, "H_SWISH", True),
+        ("first_layer", 3, 2, 1, "RELU", True), ("first_layer", 7, 2, 3, "RELU", True),
+        ("first_layer", 3, 1, 1, "IDENTITY", False),
+    ]
+    for form, k, stride, pad, act, bias in forms:
+        for size in ("toy", "wide"):
+            if form == "first_layer":
+                n, ic, oc, hw = (2, 3, 8, 13) if size == "toy" else (4, 3, 32, 64)
+            elif form == "dense":
+                n, ic, oc, hw = (2, 8, 12, 9) if size == "toy" else (4, 64, 128, 28)
+            else:
+                n, ic, oc, hw = (2, 8, 8, 9) if size == "toy" else (4, 96, 96, 28)
+            groups = ic if form == "channel_wise" else 1
+            name = f"nchw44_{form}_{size}_k{k}_s{stride}_p{pad}_{act}_b{int(bias)}"
+            out.append(_conv(name, n, ic, oc, hw, hw + 2, k, stride, pad, groups, act, (-128, 127),
+                             (0.05, 0.01, 0.3 if k > 1 else 0.1), bias=bias,
+                             bias_range=(-3000, 3000), form=form))
+    return out
+
+
+def conv_nchw44_inputs(c, O):
+    """(src, flt44, bias) in the layouts the NCHW44 model holds; O is the oracle module, whose
+    layout helpers restate the reference's index formulas."""
+    src, flt, bias = conv_inputs(c)
+    if c["form"] != "first_layer":
+        src = O.nchw_to_nchw44(src)
+    return src, O.filter_to_nchw44(flt, c["form"]), bias
+
+
+def nchw44_block_spec(seed=0):
+    """A block whose input and output are both spatial NCHW44 tensors: dense 3x3, channel-wise
+    3x3 / 2, dense 1x1, and a residual add around a second dense 3x3."""
+    from megcc_b200 import zoo
+    rng = np.random.Generator(np.random.PCG64(0x44440000 + seed))
+    n = zoo.NetSpec("nchw44_block", 16, 30, 34, 0.05)
+    a = n.conv(rng, "c1", "data", 64, 3, 1, 1)
+    b = n.conv(rng, "dw", a, 64, 3, 2, 1, groups=64)
+    c = n.conv(rng, "pw", b, 96, 1, 1, 0)
+    d = n.conv(rng, "c2", c, 96, 3, 1, 1, act="IDENTITY")
+    n.output = n.qelem("add", "QFUSE_ADD_RELU", d, c)
+    return n
+
+
 def pool_catalogue():
     """TEST(NAIVE, PoolingNCHWQuant): values U[-127,127], scale 0.7 both sides."""
     out = []

@@ -75,6 +75,16 @@ def main():
         put(out, c["name"], dst, src, flt, bias)
     np.savez_compressed(os.path.join(HERE, "conv_bias_qs8.npz"), **out)
 
+    # format NCHW44: outputs of the reference's ConvGeneral generated for NCHW44 / NCHW_NCHW44
+    out = {}
+    for c in cases.conv_nchw44_catalogue():
+        src, flt44, bias = cases.conv_nchw44_inputs(c, O)
+        s0, s1, s2 = c["scales"]
+        dst = O.ref_conv_bias_qs8_nchw44(src, flt44, bias, c["stride"], c["pad"], s0, s1, s2,
+                                         c["form"], c["act"])
+        put(out, c["name"], dst, src, flt44, bias)
+    np.savez_compressed(os.path.join(HERE, "conv_bias_nchw44.npz"), **out)
+
     out = {}
     for c in cases.pool_catalogue():
         x = cases.pool_input(c)

@@ -9,6 +9,8 @@ import subprocess
 import numpy as np
 import pytest
 
+import cases
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -28,8 +30,9 @@ def test_kernel_pack_symbols_follow_reference_naming():
     assert sym == "cuda_sm100_conv2d_3x3_NHWC_DENSE_p1x1_s1x1_d1x1_qsi8qsi8qsi32qsi8_bias_RELU"
     ok, sym = probe_conv_symbol(32, 32, 112, 112, 3, 2, 1, groups=32, nonline="H_SWISH", bias=False)
     assert ok and sym == "cuda_sm100_conv2d_3x3_NHWC_GROUP_p1x1_s2x2_d1x1_qsi8qsi8qsi32qsi8_H_SWISH"
-    # admission is a subset of BareMetal::ConvGeneral::IsAvailable: other formats and
-    # activations are refused, so the registry would fall through to the CPU kernels
+    # admission is a subset of BareMetal::ConvGeneral::IsAvailable: what it refuses falls
+    # through to the CPU kernels in the registry. NCHW44 is admitted with NCHW44 operands
+    # only, not with the NCHW shapes this probe passes.
     assert not probe_conv_symbol(64, 64, 56, 56, 3, 1, 1, fmt="NCHW44")[0]
     assert not probe_conv_symbol(64, 64, 56, 56, 3, 1, 1, nonline="SIGMOID")[0]
 
@@ -183,6 +186,37 @@ def test_exported_stubs_compile_against_public_headers(tmp_path):
     L.load_kernel_init_function()
     tab = (C.c_void_p * len(syms)).in_dll(L, "kernels")
     assert all(tab[i] for i in range(len(syms)))
+
+
+def test_nchw44_model_keeps_its_visible_layout_and_its_stubs_compile(tmp_path):
+    """A model handed over as --enable_nchw44 would: filters stay in their NCHW44 layouts in
+    the model file (the Init stub repacks them at load), the visible tensors are
+    [N, C/4, H, W, 4], Relayout instructions sit at the boundary, and the stubs are C99."""
+    from megcc_b200 import zoo, _lib
+    g = zoo.mobilenet_v1(hw=64).to_graph(nchw44=True)
+    model = g.compile([2])
+    rc, text = describe(model)
+    assert rc == 0
+    assert "weight stem:filter" in text and "dims=8x3x3x3x4" in text      # [OC/4][KH][KW][IC][4]
+    assert "dims=8x1x1x3x3x4" in text                                     # channel-wise
+    assert "dims=16x8x1x1x4x4" in text                                    # dense
+    syms = g.kernel_symbols()
+    assert "cuda_sm100_relayout_NHWC_NCHW44_qsi8qsi8" in syms
+    assert any("_NHWC44H_DENSE_" in s for s in syms)
+    assert any("_NHWC44C_GROUP_" in s for s in syms)
+    assert any("_NHWC44D_DENSE_" in s for s in syms)
+    g.export_kernels(str(tmp_path))
+    srcs = [str(tmp_path / f) for f in sorted(os.listdir(tmp_path)) if f.endswith(".c")]
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-shared", "-fPIC",
+                    "-I" + os.path.join(ROOT, "include"), "-I" + str(tmp_path), "-o",
+                    str(tmp_path / "libkernels.so")] + srcs + [_lib.LIB_PATH], check=True)
+    init = "".join((tmp_path / f).read_text() for f in os.listdir(tmp_path) if "NHWC44C" in f)
+    assert "mb200_conv_pack_filter_nchw44" in init
+    # an NCHW44 input is declared with five dims
+    rc, text = describe(cases.nchw44_block_spec().to_graph(nchw44=True).compile([1]))
+    assert rc == 0 and "cuda_sm100_relayout_NCHW44_NHWC_qsi8qsi8" in text
+    assert re.search(r"tensor data .*format=2 .*dims=1x4x30x34x4 stride=16320x4080x136x4x1", text)
+    assert re.search(r"tensor add:out .*format=2 .*dims=1x24x15x17x4 ", text)
 
 
 def _matmul_graph():

@@ -232,3 +232,50 @@ def test_resnet18_per_channel_scales_at_batch_256(lite, oracle):
     from megcc_b200 import zoo
     _sampled_parity(lite, oracle, zoo.resnet18(per_channel=True), 256, "resnet18_pc_b256",
                     samples=3)
+
+
+# ---- models as MegCC's --enable_nchw44 hands them over ----
+@pytest.mark.parametrize("which", ["resnet18", "mobilenet_v1"])
+def test_nchw44_models_match_oracle(lite, oracle, which):
+    """Filters in the NCHW44 layouts (first-layer form on the NCHW image, dense,
+    channel-wise), repacked by the Init step at load; the logits come back as
+    [N, C/4, 1, 1, 4], which for one pixel is the channel order."""
+    from megcc_b200 import zoo
+    spec = getattr(zoo, which)()
+    x = cases.rng_for(which + "_nchw44").integers(-128, 128, (4, 3, 224, 224), dtype=np.int8)
+    g = spec.to_graph(nchw44=True)
+    model = g.compile([4])
+    assert all("_NHWC44" in s for s in g.kernel_symbols() if "conv2d" in s)
+    want = netwalk.run(spec, x, oracle)
+    for out in run_model(lite, model, x, want.shape, forwards=3):
+        assert (out == want).all()
+
+
+@pytest.mark.parametrize("batch", [1, 5])
+def test_nchw44_input_and_spatial_output(lite, oracle, batch):
+    spec = cases.nchw44_block_spec()
+    x = cases.rng_for("nchw44_block").integers(-128, 128, (batch, 16, 30, 34), dtype=np.int8)
+    want = oracle.nchw_to_nchw44(netwalk.run(spec, x, oracle))
+    model = spec.to_graph(nchw44=True).compile([batch])
+    assert want.shape == (batch, 24, 15, 17, 4)
+    for out in run_model(lite, model, oracle.nchw_to_nchw44(x), want.shape, forwards=3):
+        assert (out == want).all()
+
+
+def test_nchw44_model_through_generated_kernel_tables(lite, oracle, tmp_path):
+    """The same block with every Opr run as kernels[kernel_id](...) from stubs compiled as C:
+    the NCHW44 Init stub repacks the filter, the Relayout stubs convert at the boundary."""
+    from test_gpu_kernel_tables import build_kernel_library, tables
+    spec = cases.nchw44_block_spec(seed=1)
+    x = cases.rng_for("nchw44_tables").integers(-128, 128, (3, 16, 30, 34), dtype=np.int8)
+    want = oracle.nchw_to_nchw44(netwalk.run(spec, x, oracle))
+    g = spec.to_graph(nchw44=True)
+    model = g.compile([3])
+    handle, n = build_kernel_library(g, str(tmp_path))
+    net = lite.Network(model, kernel_tables=tables(handle, n))
+    for _ in range(2):
+        net.set_input("data", oracle.nchw_to_nchw44(x))
+        net.forward()
+        net.wait()
+        assert (net.output(net.output_names()[0]).reshape(want.shape) == want).all()
+    net.close()

@@ -63,6 +63,37 @@ def test_conv_model_shapes_golden(ops):
         G.check("conv_bias_qs8", c["name"], out, *ins)
 
 
+def test_conv_nchw44_catalogue_golden(ops, oracle):
+    """Tensors and filters in the NCHW44 layouts: relayout to NHWC, filter repacked straight
+    from its NCHW44 form, ConvBias, relayout back; against the outputs of the reference's
+    NCHW44 kernels."""
+    for c in cases.conv_nchw44_catalogue():
+        src, flt44, bias = cases.conv_nchw44_inputs(c, oracle)
+        s0, s1, s2 = c["scales"]
+        p = ops.conv_param(c["n"], c["ic"], c["h"], c["w"], c["oc"], c["k"], c["k"], c["stride"],
+                           c["pad"], c["groups"], c["act"], s0, s1, s2)
+        first = c["form"] == "first_layer"
+        x = dev(src) if first else ops.nchw44_to_nhwc(dev(src))
+        packed = ops.pack_filter_nchw44(p, dev(flt44), c["form"])
+        b = None if bias is None else dev(bias)
+        if ops.conv_s2d_supported(p):
+            y = ops.conv_bias_qs8_s2d(p, x, packed, b, src_is_nchw=first)
+        else:
+            y = ops.conv_bias_qs8_nhwc(p, x, packed, b, src_is_nchw=first)
+        out = ops.nhwc_to_nchw44(y).cpu().numpy()
+        G.check("conv_bias_nchw44", c["name"], out, src, flt44, bias)
+
+
+def test_nchw44_relayouts_are_inverse_and_match_numpy(ops, oracle):
+    r = cases.rng_for("nchw44_relayout")
+    for n, c, h, w in [(1, 4, 1, 1), (3, 20, 7, 5), (2, 64, 33, 31), (5, 8, 1, 130)]:
+        x = r.integers(-128, 128, (n, c, h, w), dtype=np.int8)
+        x44 = oracle.nchw_to_nchw44(x)
+        nhwc = ops.nchw44_to_nhwc(dev(x44))
+        assert (nhwc.cpu().numpy() == x.transpose(0, 2, 3, 1)).all()
+        assert (ops.nhwc_to_nchw44(nhwc).cpu().numpy() == x44).all()
+
+
 @pytest.mark.parametrize("algo", ["direct", "umma"])
 @pytest.mark.parametrize("dst_scale", [0.1, 5.0])
 def test_conv_cfg1_golden(ops, algo, dst_scale):

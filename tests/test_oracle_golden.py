@@ -35,6 +35,17 @@ def test_conv_model_shapes(oracle):
         _conv(oracle, c)
 
 
+def test_conv_nchw44_catalogue(oracle):
+    """Dense, channel-wise and first-layer NCHW44 filters against the reference's NCHW44
+    kernels' outputs."""
+    for c in cases.conv_nchw44_catalogue():
+        src, flt44, bias = cases.conv_nchw44_inputs(c, oracle)
+        s0, s1, s2 = c["scales"]
+        dst = oracle.conv_bias_qs8_nchw44(src, flt44, bias, c["stride"], c["pad"], s0, s1, s2,
+                                          c["form"], c["act"])
+        G.check("conv_bias_nchw44", c["name"], dst, src, flt44, bias)
+
+
 def test_pooling(oracle):
     for c in cases.pool_catalogue():
         x = cases.pool_input(c)

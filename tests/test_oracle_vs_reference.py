@@ -31,6 +31,37 @@ def test_random_convs_match_reference(reference):
         assert (a == b).all(), (i, k, stride, pad, act, dw)
 
 
+def test_nchw44_convs_match_reference(reference):
+    """The NCHW44 restatement (layout conversions around the NCHW one) against the
+    reference's ConvGeneral generated for NCHW44 / NCHW_NCHW44, at odd sizes."""
+    O = reference
+    r = cases.rng_for("random_nchw44")
+    for form, k, stride, pad, act, with_bias in [
+            ("dense", 1, 1, 0, "RELU", True), ("dense", 3, 1, 1, "RELU", True),
+            ("dense", 3, 2, 1, "IDENTITY", True), ("dense", 3, 1, 1, "H_SWISH", False),
+            ("channel_wise", 3, 1, 1, "RELU", True), ("channel_wise", 3, 2, 1, "IDENTITY", True),
+            ("channel_wise", 5, 1, 2, "H_SWISH", True), ("first_layer", 3, 2, 1, "RELU", True),
+            ("first_layer", 7, 2, 3, "RELU", True), ("first_layer", 3, 1, 1, "IDENTITY", False)]:
+        for _ in range(3):
+            oc = 4 * int(r.integers(1, 6))
+            ic = (int(r.integers(1, 5)) if form == "first_layer"
+                  else oc if form == "channel_wise" else 4 * int(r.integers(1, 6)))
+            n, h, w = int(r.integers(1, 3)), int(r.integers(k, 20)), int(r.integers(k, 20))
+            src = r.integers(-128, 128, (n, ic, h, w), dtype=np.int8)
+            flt = (r.integers(-127, 128, (oc, 1, 1, k, k), dtype=np.int8)
+                   if form == "channel_wise"
+                   else r.integers(-127, 128, (oc, ic, k, k), dtype=np.int8))
+            bias = r.integers(-2000, 2001, (oc,), dtype=np.int32) if with_bias else None
+            if form != "first_layer":
+                src = O.nchw_to_nchw44(src)
+            flt44 = O.filter_to_nchw44(flt, form)
+            s = (float(r.uniform(0.01, 0.1)), float(r.uniform(0.005, 0.02)),
+                 float(r.uniform(0.05, 3)))
+            a = O.conv_bias_qs8_nchw44(src, flt44, bias, stride, pad, *s, form, act)
+            b = O.ref_conv_bias_qs8_nchw44(src, flt44, bias, stride, pad, *s, form, act)
+            assert (a == b).all(), (form, k, stride, act, oc, ic, h, w)
+
+
 def test_conv_without_bias_matches_reference(reference):
     O = reference
     r = cases.rng_for("nobias")
