@@ -181,6 +181,20 @@ MB200_API int mb200_conv_bias_qs8_s2d(
         const mb200_conv_param* p, const int8_t* src, int src_is_nchw, const int8_t* flt_s2d,
         const int32_t* bias, const float* flt_scales, int8_t* dst, void* workspace,
         size_t workspace_bytes, void* stream);
+/* The same first-layer ConvBias followed by Pooling MAX, window 3x3, stride 2, pad 1
+ * (compiler/lib/KernelGen/BareMetal/Pooling.cpp:66-150), as ONE kernel: dst is the pooled
+ * tensor [n][(oh-1)/2+1][(ow-1)/2+1][oc] (NHWC), the ConvBias result itself is never stored.
+ * Requantisation with positive scales and IDENTITY / RELU never decreases when the
+ * accumulator grows, so the window maximum is taken on the int32 accumulators and the
+ * result equals the two reference kernels run one after the other, bit for bit.
+ * mb200_conv_s2d_pool_supported(p) != 0 says the form applies (the first-layer path, at most
+ * 64 output channels in groups of 16, IDENTITY or RELU); all scales, per-channel ones
+ * included, must be positive. */
+MB200_API int mb200_conv_s2d_pool_supported(const mb200_conv_param* p);
+MB200_API int mb200_conv_bias_pool_qs8_s2d(
+        const mb200_conv_param* p, const int8_t* src, int src_is_nchw, const int8_t* flt_s2d,
+        const int32_t* bias, const float* flt_scales, int8_t* dst, void* workspace,
+        size_t workspace_bytes, void* stream);
 /* Same operator in the reference's own layouts: src/dst NCHW, filter OIHW. Needs
  * mb200_conv_bias_qs8_nchw_workspace(p) bytes of device scratch (256-byte aligned). */
 MB200_API size_t mb200_conv_bias_qs8_nchw_workspace(const mb200_conv_param* p);

@@ -110,12 +110,18 @@ MB200C_API int mb200c_add_resize_nearest(mb200c_graph* g, const char* name, int 
 
 MB200C_API int mb200c_mark_output(mb200c_graph* g, int tensor);
 
-/* Options (all on by default):
- *   "fuse_conv_elemwise"  a ConvBias without activation whose only consumer is a QADD /
- *                         QFUSE_ADD_RELU becomes one instruction (the z operand slot of the
- *                         reference's Conv2DKernel); results are bit-identical to the two
- *                         separate kernels (the MGB-level counterpart in the reference is
- *                         compiler/lib/Dialect/MGB/Transforms/KernelFuse.cpp:41-80). */
+/* Options:
+ *   "fuse_conv_elemwise"  (on by default) a ConvBias without activation whose only consumer
+ *                         is a QADD / QFUSE_ADD_RELU becomes one instruction (the z operand
+ *                         slot of the reference's Conv2DKernel); results are bit-identical
+ *                         to the two separate kernels (the MGB-level counterpart in the
+ *                         reference is compiler/lib/Dialect/MGB/Transforms/KernelFuse.cpp
+ *                         :41-80).
+ *   "fuse_conv_pooling"   (off by default) a first-layer ConvBias (IDENTITY / RELU, at most
+ *                         64 output channels) whose only consumer is a Pooling MAX 3x3 /
+ *                         stride 2 / pad 1 becomes one instruction that never stores the
+ *                         ConvBias result; bit-identical to the two kernels. Off because the
+ *                         fused kernel measured slower than the pair it replaces. */
 MB200C_API int mb200c_set_option(mb200c_graph* g, const char* name, int value);
 
 /* Compiles one DeviceModel (device CUDA_SM100) per batch size into a tinynn model.

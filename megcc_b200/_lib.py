@@ -58,6 +58,9 @@ SIGNATURES = {
     "mb200_conv_s2d_pack_filter": (C.c_int, [C.POINTER(ConvParam), _P, _P, _P]),
     "mb200_conv_bias_qs8_s2d": (C.c_int, [C.POINTER(ConvParam), _P, C.c_int, _P, _P, _P, _P, _P,
                                           C.c_size_t, _P]),
+    "mb200_conv_bias_pool_qs8_s2d": (C.c_int, [C.POINTER(ConvParam), _P, C.c_int, _P, _P, _P, _P, _P,
+                                          C.c_size_t, _P]),
+    "mb200_conv_s2d_pool_supported": (C.c_int, [C.POINTER(ConvParam)]),
     "mb200_conv_bias_qs8_nchw_workspace": (C.c_size_t, [C.POINTER(ConvParam)]),
     "mb200_conv_bias_qs8_nchw": (C.c_int, [C.POINTER(ConvParam), _P, _P, _P, _P, _P, _P,
                                            C.c_size_t, C.c_int, _P]),

@@ -96,6 +96,11 @@ std::string fuse_mode(TContext* ctx) {
     return ctx->haveAttr("fuse_elemwise_mode") ? ctx->getAttrStr("fuse_elemwise_mode") : "";
 }
 
+// "" unless the MAX pooling 3x3 / stride 2 / pad 1 behind the ConvBias is part of the operator
+std::string fuse_pool(TContext* ctx) {
+    return ctx->haveAttr("fuse_pooling") ? ctx->getAttrStr("fuse_pooling") : "";
+}
+
 std::string nonline(TContext* ctx) {
     return ctx->haveAttr("nonlineMode") ? ctx->getAttrStr("nonlineMode") : "IDENTITY";
 }
@@ -165,6 +170,25 @@ bool ConvBiasQS8::IsAvailable(TContext* ctx) const {
         if (std::fabs(src.scale * flt.scale - bias.scale) >= 1e-5)
             return false;
     }
+    const std::string fp = fuse_pool(ctx);
+    if (!fp.empty()) {
+        // ConvBias + MAX pooling: only the first-layer form (NCHW input, few channels,
+        // stride 2) with at most 64 output channels has the pooled epilogue, and taking the
+        // maximum before the requantisation needs that to be non-decreasing
+        if (fp != "MAX_3x3_s2x2_p1x1" || !fm.empty() || act == "H_SWISH" ||
+            src.shape.size() != 4 || sparse != "DENSE" || ctx->getAttrUInt("dilate_h") != 1 ||
+            ctx->getAttrUInt("dilate_w") != 1 || !(src.scale > 0) || !(flt.scale > 0) ||
+            !(dst.scale > 0))
+            return false;
+        const int oc = (int)(dst.shape.size() == 5 ? dst.shape[1] * 4 : dst.shape[1]);
+        const mb200::S2dGeom g = mb200::s2d_geometry(
+                (int)src.shape[0], (int)src.shape[1], (int)src.shape[2], (int)src.shape[3], oc,
+                (int)ctx->getAttrUInt("kernel_h"), (int)ctx->getAttrUInt("kernel_w"),
+                (int)ctx->getAttrUInt("stride_h"), (int)ctx->getAttrUInt("stride_w"),
+                (int)ctx->getAttrUInt("pad_h"), (int)ctx->getAttrUInt("pad_w"), 1, 1, 1);
+        if (!mb200::s2d_pool_fusable(g, oc))
+            return false;
+    }
     return true;
 }
 
@@ -185,6 +209,8 @@ std::string ConvBiasQS8::GetKernelSymbol(TContext* ctx) const {
         ss << "_" << nonline(ctx);
     if (!fuse_mode(ctx).empty())
         ss << "_z_" << fuse_mode(ctx);
+    if (!fuse_pool(ctx).empty())
+        ss << "_pool_MAX3x3s2p1";
     return ss.str();
 }
 
@@ -229,6 +255,12 @@ TinyNNStatus ${signature} {
                 &p, (const int8_t*)src->ptr, src_is_nchw, (const int8_t*)flt->ptr, bias, ch_scales,
                 &fuse, (int8_t*)dst->ptr, MB200_ALGO_AUTO, mb200_opt_stream(opt));
     }
+    if (${pooled}) {
+        /* dst is the tensor behind the MAX pooling 3x3 / 2 / pad 1 that follows */
+        return (TinyNNStatus)mb200_conv_bias_pool_qs8_s2d(
+                &p, (const int8_t*)src->ptr, src_is_nchw, (const int8_t*)flt->ptr, bias, ch_scales,
+                (int8_t*)dst->ptr, workspace->ptr, workspace->size, mb200_opt_stream(opt));
+    }
     if (mb200_conv_s2d_supported(&p)) {
         /* first-layer form; the filter was packed for it by the init function below */
         return (TinyNNStatus)mb200_conv_bias_qs8_s2d(
@@ -258,6 +290,7 @@ TinyNNStatus ${signature} {
             .set("scale_idx", bias ? 3 : 2);
     const std::string fm = fuse_mode(ctx);
     s.set("fused", fm.empty() ? 0 : 1).set("fuse_code", fm == "QADD" ? 0 : 1);
+    s.set("pooled", fuse_pool(ctx).empty() ? 0 : 1);
     return s.text;
 }
 

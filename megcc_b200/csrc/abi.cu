@@ -167,6 +167,7 @@ int make_args(const mb200_conv_param* p, int src_is_nchw, ConvArgs* a) {
     a->z_scale = 1.f;
     a->z_out_scale = 1.f;
     a->acc_out = nullptr;
+    a->pool = 0;
     a->true_division = division_range_ok(p->src_scale, p->flt_scale, p->dst_scale) ? 0 : 1;
     return ST_SUCCESS;
 }
@@ -495,6 +496,34 @@ int mb200_conv_bias_qs8_s2d(
         return set_error(ST_OUT_OF_RANGE, "workspace of %zu bytes is too small", workspace_bytes);
     if (((uintptr_t)workspace | (uintptr_t)flt_s2d | (uintptr_t)dst) & 15)
         return set_error(ST_INVALID_LAYOUT, "workspace, filter and dst must be 16-byte aligned");
+    return launch_conv_s2d(a, src, flt_s2d, bias, flt_scales, dst, workspace, (cudaStream_t)stream);
+}
+
+int mb200_conv_s2d_pool_supported(const mb200_conv_param* p) {
+    ConvArgs a{};
+    if (make_args(p, 0, &a))
+        return 0;
+    return conv_s2d_pool_supported(a) && !a.true_division ? 1 : 0;
+}
+
+int mb200_conv_bias_pool_qs8_s2d(
+        const mb200_conv_param* p, const int8_t* src, int src_is_nchw, const int8_t* flt_s2d,
+        const int32_t* bias, const float* flt_scales, int8_t* dst, void* workspace,
+        size_t workspace_bytes, void* stream) {
+    ConvArgs a{};
+    int rc = make_args(p, src_is_nchw, &a);
+    if (rc)
+        return rc;
+    if (!src || !flt_s2d || !dst || !workspace)
+        return set_error(ST_NULL_PTR, "conv tensor or workspace pointer is NULL");
+    if (!conv_s2d_pool_supported(a) || a.true_division)
+        return set_error(ST_NO_IMPLEMENT, "ConvBias + MAX pooling 3x3/2 does not apply to this "
+                                          "conv: see mb200_conv_s2d_pool_supported");
+    if (workspace_bytes < conv_s2d_workspace_bytes(a))
+        return set_error(ST_OUT_OF_RANGE, "workspace of %zu bytes is too small", workspace_bytes);
+    if (((uintptr_t)workspace | (uintptr_t)flt_s2d | (uintptr_t)dst) & 15)
+        return set_error(ST_INVALID_LAYOUT, "workspace, filter and dst must be 16-byte aligned");
+    a.pool = 1;
     return launch_conv_s2d(a, src, flt_s2d, bias, flt_scales, dst, workspace, (cudaStream_t)stream);
 }
 

@@ -337,6 +337,63 @@ __device__ __forceinline__ void epilogue_store_t(
     }
 }
 
+// Four consecutive channels (from ch0, a multiple of 4) of one output of a ConvBias without a
+// fused elementwise step: accumulators + bias `b` -> four packed int8, by the same
+// arithmetic and the same choice of form as epilogue_store() makes for whole chunks. `s` are
+// the channels' filter scales when e.flt_scales is set (else ignored). IDENTITY / RELU only.
+__device__ __forceinline__ uint32_t epilogue_word(
+        const uint32_t (&v)[4], const int4 b, const float4 s, const EpilogueParams& e) {
+    const int a0 = (int)v[0] + b.x, a1 = (int)v[1] + b.y, a2 = (int)v[2] + b.z,
+              a3 = (int)v[3] + b.w;
+    const bool relu = e.act == ACT_RELU;
+    int r0, r1, r2, r3;
+    if (e.fast_ops != 0) {
+#define MB200_WORD_FAST(OPS)                                             \
+    if (relu) {                                                          \
+        requant_pair_fast<ACT_RELU, OPS>(a0, a1, e, r0, r1);             \
+        requant_pair_fast<ACT_RELU, OPS>(a2, a3, e, r2, r3);             \
+    } else {                                                             \
+        requant_pair_fast<ACT_IDENTITY, OPS>(a0, a1, e, r0, r1);         \
+        requant_pair_fast<ACT_IDENTITY, OPS>(a2, a3, e, r2, r3);         \
+    }
+        if (e.fast_ops == 1) {
+            MB200_WORD_FAST(1)
+        } else if (e.fast_ops == 2) {
+            MB200_WORD_FAST(2)
+        } else {
+            MB200_WORD_FAST(3)
+        }
+#undef MB200_WORD_FAST
+        const uint32_t pk = umma::pack4_prmt(r0, r1, r2, r3);
+        return relu ? relu_s8x4(pk) : pk;
+    }
+    if (e.bounded && !e.flt_scales) {
+        const RequantPair rp(e);
+        if (relu) {
+            requant_pair<ACT_RELU>(a0, a1, rp, r0, r1);
+            requant_pair<ACT_RELU>(a2, a3, rp, r2, r3);
+        } else {
+            requant_pair<ACT_IDENTITY>(a0, a1, rp, r0, r1);
+            requant_pair<ACT_IDENTITY>(a2, a3, rp, r2, r3);
+        }
+        const uint32_t pk = umma::pack4_prmt(r0, r1, r2, r3);
+        return relu ? relu_s8x4(pk) : pk;
+    }
+    const float4 sc = e.flt_scales ? s : make_float4(e.s_flt, e.s_flt, e.s_flt, e.s_flt);
+    if (relu) {
+        r0 = requant_one<ACT_RELU, false>(a0, e.s_src, sc.x, e.s_dst, e.inv_dst);
+        r1 = requant_one<ACT_RELU, false>(a1, e.s_src, sc.y, e.s_dst, e.inv_dst);
+        r2 = requant_one<ACT_RELU, false>(a2, e.s_src, sc.z, e.s_dst, e.inv_dst);
+        r3 = requant_one<ACT_RELU, false>(a3, e.s_src, sc.w, e.s_dst, e.inv_dst);
+    } else {
+        r0 = requant_one<ACT_IDENTITY, false>(a0, e.s_src, sc.x, e.s_dst, e.inv_dst);
+        r1 = requant_one<ACT_IDENTITY, false>(a1, e.s_src, sc.y, e.s_dst, e.inv_dst);
+        r2 = requant_one<ACT_IDENTITY, false>(a2, e.s_src, sc.z, e.s_dst, e.inv_dst);
+        r3 = requant_one<ACT_IDENTITY, false>(a3, e.s_src, sc.w, e.s_dst, e.inv_dst);
+    }
+    return umma::pack4_prmt(r0, r1, r2, r3);
+}
+
 // run-time dispatch on (activation, per-channel scales, bounded, fused step); uniform across
 // the CTA. `off` is the element offset of the pixel's first channel of this chunk in the
 // output tensor (and in z, which has the same shape).

@@ -21,6 +21,16 @@
 //
 // Accumulators: int32 in TMEM, two buffers; epilogue identical in arithmetic to conv_umma.cu
 // (reference order of compiler/lib/KernelGen/BareMetal/Activation.cpp:105-113).
+//
+// POOL = 1 folds the MAX pooling 3x3 / stride 2 / pad 1 that follows the ConvBias into the
+// epilogue (a ResNet stem). Requantisation with positive scales and IDENTITY / RELU is a
+// non-decreasing function of the int32 accumulator, and the bias is one constant per channel,
+// so max over a window of requantised values == requantised max of the accumulators, bit for
+// bit: the window maximum is taken on the int32 accumulators (staged through shared memory)
+// and only one value in four is requantised and stored; the full-resolution tensor never
+// exists. A 16 x 8 patch of ConvBias outputs whose origin is the odd position (2P-1, 2Q-1)
+// holds every window of a 7 x 3 block of pooled outputs, so patches are laid 14 x 6 apart
+// and overlap by their last two rows / columns (0.66 of the MMA rows are distinct outputs).
 #include <stdio.h>
 #include <stdlib.h>
 
@@ -43,8 +53,13 @@ constexpr int kTH = 16, kTW = 8;  // output patch; kTW = 8 makes a patch row one
 // its own MMAs.
 constexpr int kMaxStages = 3;
 
+// pooled outputs per patch and the distance between patch origins (POOL form)
+constexpr int kPoolRows = 7, kPoolCols = 3;
+constexpr int kPoolBufBytes = 128 * 64 * 4;  // int32 accumulators of one 128 x 64 tile
+
 struct PatchParams {
     int n, oh, ow, oc;
+    int poh, pow;    // POOL form: extent of the pooled output
     int chunks;      // C / 16
     int kh, kw, ph, pw;
     int pph, ppw;    // input patch extent: kTH + kh - 1, kTW + kw - 1
@@ -53,6 +68,7 @@ struct PatchParams {
     int a_stage_bytes, a_tx_bytes, b_bytes;
     int plane_stride;  // one chunk plane: pph x ppw pixels of 16 bytes
     int b_single_load;  // the filter map is the 3-D view (one load) rather than 2-D blocks
+    int a_flat16;       // 16 input channels: the activation map is {W * 16 bytes, H, N}
     int mma_per_tap;  // k-steps per tap (C/32), or 0 when C == 16 (two taps per k-step)
     int a_lbo;        // distance between the two 16-byte K halves of one A operand
     EpilogueParams ep;
@@ -195,11 +211,15 @@ __device__ __forceinline__ void issue_tile_mmas_rows64(uint64_t a0, uint64_t b0,
     }
 }
 
-template <int BN, int KH, int KW, int CHUNKS, int EW, int ROWS = 0>
+template <int BN, int KH, int KW, int CHUNKS, int EW, int ROWS = 0, int POOL = 0>
 __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const PatchParams p) {
+    static_assert(POOL == 0 || (BN == 64 && EW == 8 && ROWS == 0), "pooled form: 64 channels");
     constexpr int kEpilogueWarps = EW;
+    // distance between patch origins and the origin's offset (see the POOL note above)
+    constexpr int kStepY = POOL ? 2 * kPoolRows : kTH, kStepX = POOL ? 2 * kPoolCols : kTW;
+    constexpr int kOrigin = POOL ? -1 : 0;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_b = smem;
@@ -213,6 +233,10 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
     uint64_t* drain_bar = b_full + 1;
     uint32_t* tmem_slot = (uint32_t*)(drain_bar + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    // POOL: the tile's int32 accumulators, [pixel][16 groups of 4 channels], the group index
+    // XORed with the pixel's column so that neither the row-wise writes nor the window reads
+    // collide on banks
+    uint8_t* pool_buf = (uint8_t*)(((uintptr_t)(abort_flag + 1) + 127) & ~(uintptr_t)127);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // each CTA owns one slice of output channels and walks the patches with a fixed stride
     const int tile_n = blockIdx.x % p.n_tiles;
@@ -280,11 +304,16 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
                     break;
                 }
                 const int img = at.img;
-                const int x0 = at.tx * kTW - p.pw, y0 = at.ty * kTH - p.ph;
+                const int x0 = at.tx * kStepX + kOrigin - p.pw, y0 = at.ty * kStepY + kOrigin - p.ph;
                 mbar_expect_tx(&a_full[s], (uint32_t)p.a_tx_bytes);
                 if (ROWS) {
                     // one request: box {64 B, 16 columns, patch rows, 1 image}
                     tma_load_4d(smem_a + s * p.a_stage_bytes, &map_a, &a_full[s], 0, x0, y0, img);
+                } else if (p.a_flat16) {
+                    // 16 channels: a patch row is contiguous in memory, one box row of
+                    // (patch columns x 16) bytes instead of one 16-byte row per pixel (the
+                    // TMA unit's cost is per row)
+                    tma_load_3d(smem_a + s * p.a_stage_bytes, &map_a, &a_full[s], x0 * 16, y0, img);
                 } else {
                     // one request: box {16 B, patch columns, patch rows, 1 image, all chunks}
                     tma_load_5d(smem_a + s * p.a_stage_bytes, &map_a, &a_full[s], 0, x0, y0, img, 0);
@@ -352,6 +381,18 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
         const int py = row >> 3, px = row & 7;
         int local = 0;
         bool ok = true;
+        // POOL: this thread's channel group (4 channels) and first pooled pixel of a patch;
+        // its bias and filter scales do not change from patch to patch
+        const int pool_g = (int)(threadIdx.x - 64) & 15, pool_pj = (int)(threadIdx.x - 64) >> 4;
+        const int pool_ch = n0 + pool_g * 4;
+        int4 pool_bias = make_int4(0, 0, 0, 0);
+        float4 pool_scales = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (POOL != 0 && pool_ch < p.oc) {
+            if (p.ep.bias)
+                pool_bias = __ldg(reinterpret_cast<const int4*>(p.ep.bias + pool_ch));
+            if (p.ep.flt_scales)
+                pool_scales = __ldg(reinterpret_cast<const float4*>(p.ep.flt_scales + pool_ch));
+        }
         PatchWalker at(m_first, m_step, p.tiles_y, p.tiles_x);
         for (int mt = m_first; mt < p.m_tiles && ok; mt += m_step, ++local, at.next()) {
             const int buf = local & 1;
@@ -361,10 +402,93 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
                 *abort_flag = 1;
                 atomicExch(p.status, ERR_EPILOGUE_WAIT);
             }
-            ok = __all_sync(0xffffffffu, ok);
+            if constexpr (POOL != 0) {
+                // The epilogue warps meet at barriers below, so they must leave the loop
+                // together: agree on the outcome of the (bounded) wait across all of them.
+                // Arriving here also says that this thread is through with the staging
+                // buffer of the previous tile.
+                int all;
+                asm volatile(
+                        "{\n\t.reg .pred p, r;\n\tsetp.ne.u32 p, %1, 0;\n\t"
+                        "bar.red.and.pred r, 1, %2, p;\n\tselp.u32 %0, 1, 0, r;\n\t}"
+                        : "=r"(all)
+                        : "r"((int)ok), "n"(32 * EW)
+                        : "memory");
+                ok = all != 0;
+            } else {
+                ok = __all_sync(0xffffffffu, ok);
+            }
             if (!ok)
                 break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if constexpr (POOL != 0) {
+                // (1) this thread's pixel: 32 accumulators TMEM -> registers -> shared memory
+                const int c = (warp - 2) >> 2;  // the warp's 32-column chunk
+                {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN) +
+                                      (uint32_t)(c * 32),
+                              v);
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbar_arrive(&acc_empty[buf]);
+                    // a position outside the ConvBias output (the rim of the first / last
+                    // patches) must never win a window: the smallest int32 in its place.
+                    // (Every window's centre is a real output, so that value never reaches
+                    // the bias addition.)
+                    const int oy = at.ty * kStepY + kOrigin + py, ox = at.tx * kStepX + kOrigin + px;
+                    if ((unsigned)oy >= (unsigned)p.oh || (unsigned)ox >= (unsigned)p.ow) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            v[j] = 0x80000000u;
+                    }
+                    uint8_t* mine = pool_buf + row * 256;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int g = c * 8 + (j ^ px);  // group c*8+j at slot (c*8+j) ^ px
+                        *reinterpret_cast<uint4*>(mine + g * 16) =
+                                make_uint4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
+                // (2) one pooled pixel x 4 channels per item, 21 x 16 items over the 256
+                // threads: 16 consecutive lanes read the 16 groups of one pixel (every slot of
+                // its 256 bytes once: no bank conflicts) and store its 64 bytes
+#pragma unroll 1
+                for (int pj = pool_pj; pj < kPoolRows * kPoolCols; pj += 16) {
+                    const int pyj = pj / kPoolCols, pxj = pj - pyj * kPoolCols;
+                    const int P = at.ty * kPoolRows + pyj, Q = at.tx * kPoolCols + pxj;
+                    if (P >= p.poh || Q >= p.pow)
+                        continue;
+                    // the window: 3 x 3 pixels from (2 pyj, 2 pxj); a pixel's group sits at
+                    // the slot XORed with the pixel's column
+                    const uint8_t* win = pool_buf + (2 * pyj * 8 + 2 * pxj) * 256;
+                    const uint8_t* col[3];
+#pragma unroll
+                    for (int wx = 0; wx < 3; ++wx)
+                        col[wx] = win + wx * 256 + ((pool_g ^ (2 * pxj + wx)) << 4);
+                    uint32_t m[4];
+#pragma unroll
+                    for (int wy = 0; wy < 3; ++wy) {
+#pragma unroll
+                        for (int wx = 0; wx < 3; ++wx) {
+                            const uint4 t = *reinterpret_cast<const uint4*>(col[wx] + wy * 8 * 256);
+                            if (wy == 0 && wx == 0) {
+                                m[0] = t.x, m[1] = t.y, m[2] = t.z, m[3] = t.w;
+                            } else {
+                                m[0] = (uint32_t)max((int)m[0], (int)t.x);
+                                m[1] = (uint32_t)max((int)m[1], (int)t.y);
+                                m[2] = (uint32_t)max((int)m[2], (int)t.z);
+                                m[3] = (uint32_t)max((int)m[3], (int)t.w);
+                            }
+                        }
+                    }
+                    const uint32_t pixel = ((uint32_t)at.img * p.poh + P) * p.pow + Q;
+                    if (pool_ch < p.oc)
+                        *reinterpret_cast<uint32_t*>(p.dst + (size_t)pixel * p.oc + pool_ch) =
+                                epilogue_word(m, pool_bias, pool_scales, p.ep);
+                }
+                continue;  // (the next tile's agreement barrier frees the staging buffer)
+            }
             const int oy = at.ty * kTH + py, ox = at.tx * kTW + px;
             const bool valid = oy < p.oh && ox < p.ow;
             // the pixel index fits 32 bits (the launcher checks); one wide multiply
@@ -457,14 +581,18 @@ PatchPlan plan_patch(const ConvArgs& a) {
     if (pph > 256 || ppw > 256)
         return pl;
     pl.bn = a.oc <= 64 ? 64 : 128;
-    pl.rows64 = a.ic == 64 && a.kh == 3 && a.kw == 3 && pl.bn == 64 && !tuning().patch_plain;
+    if (a.pool && (pl.bn != 64 || a.oc % 16 != 0))
+        return pl;
+    pl.rows64 = a.ic == 64 && a.kh == 3 && a.kw == 3 && pl.bn == 64 && !tuning().patch_plain &&
+                !a.pool;
     pl.plane_stride = pph * ppw * 16;
     // a TMA destination in shared memory must be 128-byte aligned: pad the stage
     pl.a_stage_bytes = ((a.ic / 16) * pl.plane_stride + 127) / 128 * 128;
     if (pl.rows64)
         pl.a_stage_bytes = pph * kRowCols * 64;  // a multiple of 1024
     pl.b_bytes = pl.bn * a.kh * a.kw * a.ic;
-    const int fixed = pl.b_bytes + (2 * kMaxStages + 6) * 8 + 64 + 1024;
+    const int fixed = pl.b_bytes + (2 * kMaxStages + 6) * 8 + 64 + 1024 +
+                      (a.pool ? kPoolBufBytes + 128 : 0);
     const int budget = 227 * 1024;
     // more CTAs per SM hide more latency; one stage is a whole tile, so two stages already
     // keep the loads a tile ahead
@@ -485,28 +613,29 @@ PatchPlan plan_patch(const ConvArgs& a) {
     return pl;
 }
 
-template <int BN, int KH, int KW, int CHUNKS, int EW, int ROWS = 0>
+template <int BN, int KH, int KW, int CHUNKS, int EW, int ROWS = 0, int POOL = 0>
 int launch_patch(
         const CUtensorMap& ma, const CUtensorMap& mb, const PatchParams& p, int smem, int grid,
         cudaStream_t st) {
     constexpr int kThreads = 64 + 32 * EW;
     if (cudaFuncSetAttribute(
-                conv_patch_kernel<BN, KH, KW, CHUNKS, EW, ROWS>,
+                conv_patch_kernel<BN, KH, KW, CHUNKS, EW, ROWS, POOL>,
                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return check_launch("conv_patch smem attribute");
     // never more CTAs than are resident at once: a persistent CTA that starts late would
     // leave its share of the patches to the end
-    const int per_sm = resident_ctas_per_sm(conv_patch_kernel<BN, KH, KW, CHUNKS, EW, ROWS>, kThreads, smem, 2 * BN);
+    const int per_sm = resident_ctas_per_sm(conv_patch_kernel<BN, KH, KW, CHUNKS, EW, ROWS, POOL>,
+                                            kThreads, smem, 2 * BN);
     {
         int cap = sm_count() * per_sm / p.n_tiles * p.n_tiles;
         if (cap >= p.n_tiles && grid > cap)
             grid = cap;
     }
     if (tuning().debug)
-        fprintf(stderr, "conv_patch<%d,%d,%d,%d,%d>: per_sm %d grid %d m_tiles %d n_tiles %d smem %d "
-                "stages %d b_single_load %d\n", BN, KH, KW, CHUNKS, EW, per_sm, grid, p.m_tiles,
-                p.n_tiles, smem, p.stages, p.b_single_load);
-    launch_pdl(conv_patch_kernel<BN, KH, KW, CHUNKS, EW, ROWS>, dim3(grid), dim3(kThreads),
+        fprintf(stderr, "conv_patch<%d,%d,%d,%d,%d,%d,%d>: per_sm %d grid %d m_tiles %d n_tiles %d "
+                "smem %d stages %d b_single_load %d\n", BN, KH, KW, CHUNKS, EW, ROWS, POOL, per_sm,
+                grid, p.m_tiles, p.n_tiles, smem, p.stages, p.b_single_load);
+    launch_pdl(conv_patch_kernel<BN, KH, KW, CHUNKS, EW, ROWS, POOL>, dim3(grid), dim3(kThreads),
                (size_t)smem, st, ma, mb, p);
     return check_launch("conv_patch");
 }
@@ -537,6 +666,10 @@ bool conv_patch_supported(
     if ((size_t)a.n * a.oh * a.ow >= (1ull << 31))
         return false;
     if (((uintptr_t)src | (uintptr_t)flt | (uintptr_t)dst) & 15)
+        return false;
+    // the fused pooling commutes with the requantisation only where that is non-decreasing
+    if (a.pool && (a.act == ACT_H_SWISH || a.z || a.acc_out || !(a.s_src > 0.f) ||
+                   !(a.s_flt > 0.f) || !(a.s_dst > 0.f)))
         return false;
     return true;
 }
@@ -585,6 +718,19 @@ int launch_conv_patch(
                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS)
             return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(filter) failed: %d", (int)r);
+    } else if (a.ic == 16) {
+        // one chunk: [row][column][16 bytes] is the tensor's own order, so a patch row is one
+        // contiguous box row of ppw * 16 bytes
+        cuuint64_t dims[3] = {(cuuint64_t)a.iw * 16, (cuuint64_t)a.ih, (cuuint64_t)images};
+        cuuint64_t strides[2] = {(cuuint64_t)a.iw * 16, (cuuint64_t)a.ih * a.iw * 16};
+        cuuint32_t box[3] = {(cuuint32_t)ppw * 16, (cuuint32_t)pph, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = api.tiled(
+                &map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, (void*)src, dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(activation) failed: %d", (int)r);
     } else {
         // NHWC seen as {16 channel bytes, W, H, N, C/16}: a box over all chunks arrives as
         // [chunk][row][column][16 bytes]
@@ -645,8 +791,16 @@ int launch_conv_patch(
     p.pw = a.pw;
     p.pph = pph;
     p.ppw = ppw;
-    p.tiles_y = (a.oh + kTH - 1) / kTH;
-    p.tiles_x = (a.ow + kTW - 1) / kTW;
+    // MAX pooling 3x3 / 2 / pad 1 behind the ConvBias
+    p.poh = (a.oh - 1) / 2 + 1;
+    p.pow = (a.ow - 1) / 2 + 1;
+    if (a.pool) {
+        p.tiles_y = (p.poh + kPoolRows - 1) / kPoolRows;
+        p.tiles_x = (p.pow + kPoolCols - 1) / kPoolCols;
+    } else {
+        p.tiles_y = (a.oh + kTH - 1) / kTH;
+        p.tiles_x = (a.ow + kTW - 1) / kTW;
+    }
     p.m_tiles = a.n * p.tiles_y * p.tiles_x;
     p.n_tiles = (a.oc + pl.bn - 1) / pl.bn;
     p.stages = pl.stages;
@@ -655,6 +809,7 @@ int launch_conv_patch(
     p.a_tx_bytes = pl.rows64 ? pl.a_stage_bytes : p.chunks * pl.plane_stride;
     p.b_bytes = pl.b_bytes;
     p.b_single_load = b_single_load;
+    p.a_flat16 = (!pl.rows64 && a.ic == 16) ? 1 : 0;
     p.mma_per_tap = a.ic == 16 ? 0 : a.ic / 32;
     p.a_lbo = a.ic == 16 ? 16 : p.plane_stride;
     p.ep.oc = a.oc;
@@ -701,7 +856,11 @@ int launch_conv_patch(
         grid = (int)total;
     int rc;
     const bool alone = pl.ctas_per_sm == 1;  // one CTA per SM: sixteen epilogue warps
-    if (pl.rows64)
+    if (a.pool && a.kh == 4 && a.kw == 4 && a.ic == 16)
+        rc = launch_patch<64, 4, 4, 1, 8, 0, 1>(map_a, map_b, p, pl.smem_bytes, grid, st);
+    else if (a.pool)
+        rc = launch_patch<64, 0, 0, 0, 8, 0, 1>(map_a, map_b, p, pl.smem_bytes, grid, st);
+    else if (pl.rows64)
         rc = launch_patch<64, 3, 3, 4, 8, 1>(map_a, map_b, p, pl.smem_bytes, grid, st);
     else if (pl.bn == 64 && a.kh == 3 && a.kw == 3 && a.ic == 64 && !alone)
         rc = launch_patch<64, 3, 3, 4, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);

@@ -195,6 +195,11 @@ bool conv_s2d_supported(const ConvArgs& a) {
     return s2d_geom(a).ok;
 }
 
+bool conv_s2d_pool_supported(const ConvArgs& a) {
+    return s2d_pool_fusable(s2d_geom(a), a.oc) && a.act != ACT_H_SWISH && !a.z && !a.acc_out &&
+           a.s_src > 0.f && a.s_flt > 0.f && a.s_dst > 0.f;
+}
+
 size_t conv_s2d_filter_bytes(const ConvArgs& a) {
     return s2d_geom(a).filter_bytes;
 }
@@ -255,6 +260,8 @@ int launch_conv_s2d(
     // oh / ow / m stay those of the original convolution
     if (conv_patch_supported(t, (const int8_t*)workspace, flt_s2d, dst))
         return launch_conv_patch(t, (const int8_t*)workspace, flt_s2d, bias, flt_scales, dst, st);
+    if (a.pool)  // only the halo-patch kernel has the pooled epilogue
+        return set_error(ST_NO_IMPLEMENT, "ConvBias + pooling does not apply to this shape");
     return launch_conv_umma_geom(t, 1, (const int8_t*)workspace, flt_s2d, bias, flt_scales, dst, st);
 }
 

@@ -47,4 +47,12 @@ inline S2dGeom s2d_geometry(
     return g;
 }
 
+// May the MAX pooling 3x3 / stride 2 / pad 1 that follows such a ConvBias be folded into it?
+// (64 output channels at most, in whole 16-channel groups: the pooled epilogue of the
+// halo-patch kernel works on one 64-column accumulator tile.) The activation must be
+// IDENTITY or RELU and the scales positive; the callers check those.
+inline bool s2d_pool_fusable(const S2dGeom& g, int oc) {
+    return g.ok && oc <= 64 && oc % 16 == 0 && g.kh2 <= 8 && g.kw2 <= 8;
+}
+
 }  // namespace mb200

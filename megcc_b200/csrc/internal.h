@@ -39,6 +39,10 @@ struct ConvArgs {
     float z_scale, z_out_scale;
     // tensor-core kernels only: store the int32 accumulators here instead of int8 results
     int32_t* acc_out;
+    // halo-patch kernel only (reached through the space-to-depth path): 1 = the MAX pooling
+    // 3x3 / stride 2 / pad 1 that follows the ConvBias is taken in its epilogue and dst is the
+    // pooled tensor [n][(oh-1)/2+1][(ow-1)/2+1][oc]
+    int pool;
     // general kernel only: divide by s_dst with the true division (scales outside the range
     // in which the three-instruction division by a constant is exact, see common.cuh)
     int true_division;
@@ -124,6 +128,8 @@ int launch_conv_s2d_pack_filter(
 int launch_conv_s2d(
         const ConvArgs& a, const int8_t* src, const int8_t* flt_s2d, const int32_t* bias,
         const float* flt_scales, int8_t* dst, void* workspace, cudaStream_t st);
+// may a.pool be set for this ConvBias (first-layer form on the halo-patch kernel)?
+bool conv_s2d_pool_supported(const ConvArgs& a);
 int launch_pooling(
         const int8_t* src, int8_t* dst, int mode, int n, int c, int ih, int iw, int wh, int ww,
         int sh, int sw, int ph, int pw, cudaStream_t st);

@@ -93,6 +93,7 @@ struct OpPlan {
     std::vector<int> weight_inputs;  // indices (into inputs) that are weights
     Workspace ws{nullptr, 0, 0};
     bool needs_init = false;
+    int pool = 0;          // ConvBias with the MAX pooling 3x3 / 2 / pad 1 behind it folded in
     int flt44 = 0;         // filter layout: 0 OIHW, 1 / 2 / 3 NCHW44 dense / channel-wise / first layer
     int z_mode = 0;        // fused elemwise step: 0 none, else MB200_QADD + 1 / MB200_QFUSE_ADD_RELU + 1
     bool f32_z = false;    // fp32 ConvBias with a tensor added after the activation
@@ -345,6 +346,11 @@ bool parse_symbol(const std::string& sym, OpPlan* op) {
         op->kind = OP_CONV;
         if (rest.compare(0, 8, "qsi8qsi8") != 0)
             return false;
+        // a MAX pooling 3x3 / 2 / pad 1 folded into the ConvBias is spelled last
+        if (ends_with(rest, "_pool_MAX3x3s2p1")) {
+            op->pool = 1;
+            rest.resize(rest.size() - strlen("_pool_MAX3x3s2p1"));
+        }
         // a fused elemwise step is spelled last: ..._z_QADD / ..._z_QFUSE_ADD_RELU
         if (ends_with(rest, "_z_QFUSE_ADD_RELU")) {
             op->z_mode = MB200_QFUSE_ADD_RELU + 1;
@@ -552,6 +558,11 @@ TinyNNStatus builtin_kernel(
                         (const int8_t*)inputs[1]->ptr, bias, ch, &fuse, (int8_t*)dst->ptr,
                         MB200_ALGO_AUTO, st);
             }
+            if (op.pool)
+                return (TinyNNStatus)mb200_conv_bias_pool_qs8_s2d(
+                        &p, (const int8_t*)src->ptr, src->layout.format == TinyNN_NCHW,
+                        (const int8_t*)inputs[1]->ptr, bias, ch, (int8_t*)dst->ptr, ws->ptr,
+                        ws->size, st);
             if (mb200_conv_s2d_supported(&p))
                 return (TinyNNStatus)mb200_conv_bias_qs8_s2d(
                         &p, (const int8_t*)src->ptr, src->layout.format == TinyNN_NCHW,
@@ -831,9 +842,16 @@ const char* check_operands(const OpPlan& op) {
             }
             if (icpg * groups != in0->layout.dims[1] || oc != out->layout.dims[1])
                 return "filter channels do not match the tensors";
-            if (out->layout.dims[0] != in0->layout.dims[0] ||
-                (int)out->layout.dims[2] != extent(in0->layout.dims[2], op.kh, op.sh, op.ph) ||
-                (int)out->layout.dims[3] != extent(in0->layout.dims[3], op.kw, op.sw, op.pw))
+            int oh = extent(in0->layout.dims[2], op.kh, op.sh, op.ph);
+            int ow = extent(in0->layout.dims[3], op.kw, op.sw, op.pw);
+            if (op.pool) {  // MAX pooling 3x3 / 2 / pad 1 behind the ConvBias
+                if (op.kind != OP_CONV || op.z_mode || oh < 1 || ow < 1)
+                    return "ConvBias + pooling operands";
+                oh = extent(oh, 3, 2, 1);
+                ow = extent(ow, 3, 2, 1);
+            }
+            if (out->layout.dims[0] != in0->layout.dims[0] || (int)out->layout.dims[2] != oh ||
+                (int)out->layout.dims[3] != ow)
                 return "output extent differs from what the ConvBias computes";
             const size_t extra = op.inputs.size() - 2;
             size_t idx = 2;

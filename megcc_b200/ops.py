@@ -333,6 +333,31 @@ def conv_bias_qs8_s2d(p, src, flt_packed, bias, flt_scales=None, src_is_nchw=Tru
     return dst
 
 
+def pack_filter_s2d(p, flt_oihw):
+    """OIHW int8 device tensor -> the space-to-depth packing of the first-layer form."""
+    packed = torch.empty(lib().mb200_conv_s2d_filter_bytes(C.byref(p)), dtype=torch.int8,
+                         device=flt_oihw.device)
+    check(lib().mb200_conv_s2d_pack_filter(C.byref(p), _ptr(flt_oihw), _ptr(packed), _stream()))
+    return packed
+
+
+def conv_s2d_pool_supported(p):
+    return bool(lib().mb200_conv_s2d_pool_supported(C.byref(p)))
+
+
+def conv_bias_pool_qs8_s2d(p, src, flt_packed, bias, flt_scales=None, src_is_nchw=True):
+    """First-layer ConvBias + MAX pooling 3x3 / 2 / pad 1 as one kernel; NHWC pooled result."""
+    oh, ow = out_hw(p)
+    dst = torch.empty((p.n, (oh - 1) // 2 + 1, (ow - 1) // 2 + 1, p.oc), dtype=torch.int8,
+                      device=src.device)
+    nbytes = lib().mb200_conv_s2d_workspace_bytes(C.byref(p))
+    keep, ws = _scratch(nbytes, src.device)
+    check(lib().mb200_conv_bias_pool_qs8_s2d(
+        C.byref(p), _ptr(src), int(src_is_nchw), _ptr(flt_packed), _ptr(bias), _ptr(flt_scales),
+        _ptr(dst), ws, nbytes, _stream()))
+    return dst
+
+
 # ---- NCHW44 (models compiled with --enable_nchw44) ----
 NCHW44_FORMS = {"dense": 0, "channel_wise": 1, "first_layer": 2}
 

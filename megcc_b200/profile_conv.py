@@ -7,6 +7,12 @@ Meant to be run under a profiler, capturing the first launches:
 
     ncu --set full --clock-control none -k regex:conv_ -c 3 \
         python -m megcc_b200.profile_conv 32
+
+A second argument keeps only the cases whose name contains it, e.g. the first layer with the
+max-pool behind it folded in:
+
+    ncu --set full --clock-control none -k regex:conv_patch -c 1 \
+        python -m megcc_b200.profile_conv 32 first_layer_pool
 """
 import ctypes
 import sys
@@ -18,7 +24,7 @@ from . import ops
 from ._lib import check, lib
 
 
-def main(batch=32):
+def main(batch=32, only=""):
     rng = np.random.default_rng(0)
     dev = lambda a: torch.from_numpy(a).cuda()
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -41,6 +47,15 @@ def main(batch=32):
                                             None, ptr(dst), ptr(ws), ws.numel(), st))
 
     cases.append(("first_layer_3_64_7x7s2", first_layer, 2.0 * batch * 64 * 112 * 112 * 147))
+    pooled = torch.empty((batch, 56, 56, 64), dtype=torch.int8, device="cuda")
+
+    def first_layer_pool():
+        check(lib().mb200_conv_bias_pool_qs8_s2d(
+            ctypes.byref(p), ptr(src), 1, ptr(packed), ptr(bias), None, ptr(pooled), ptr(ws),
+            ws.numel(), st))
+
+    cases.append(("first_layer_pool_3_64_7x7s2_max3x3s2", first_layer_pool,
+                  2.0 * batch * 64 * 112 * 112 * 147))
     for name, c, hw in (("conv_64_64_3x3_56", 64, 56), ("conv_128_128_3x3_28", 128, 28),
                         ("conv_256_256_3x3_14", 256, 14), ("conv_512_512_3x3_7", 512, 7)):
         pp = ops.conv_param(batch, c, hw, hw, c, 3, 3, 1, 1, 1, "RELU", 0.05, 0.01, 2.0)
@@ -50,6 +65,7 @@ def main(batch=32):
         d = torch.empty((batch, hw, hw, c), dtype=torch.int8, device="cuda")
         cases.append((name, (lambda pp=pp, s=s, f=f, b=b, d=d: ops.conv_bias_qs8_nhwc(
             pp, s, f, b, dst=d, algo="auto")), 2.0 * batch * c * hw * hw * c * 9))
+    cases = [c for c in cases if only in c[0]]
     for rnd in range(2):
         for name, fn, work in cases:
             e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
@@ -66,4 +82,4 @@ def main(batch=32):
 
 
 if __name__ == "__main__":
-    main(int(sys.argv[1]) if len(sys.argv) > 1 else 32)
+    main(int(sys.argv[1]) if len(sys.argv) > 1 else 32, sys.argv[2] if len(sys.argv) > 2 else "")

@@ -52,7 +52,9 @@ def test_resnet18_runs_through_the_generated_kernel_tables(oracle, tmp_path):
     spec = zoo.resnet18(hw=64, classes=64)
     x = cases.rng_for("kernel_tables_resnet").integers(-128, 128, (8, 3, 64, 64), dtype=np.int8)
     g = spec.to_graph()
+    g.set_option("fuse_conv_pooling", 1)  # the stem + max-pool stub as well
     model = g.compile([8])
+    assert any(s.endswith("_pool_MAX3x3s2p1") for s in g.kernel_symbols())
     handle, n = build_kernel_library(g, str(tmp_path))
     want = netwalk.run(spec, x, oracle).reshape(-1)
     net = lite.Network(model, kernel_tables=tables(handle, n))

@@ -65,9 +65,25 @@ def test_resnet18_without_fusion_matches_oracle(lite, oracle):
     x = cases.rng_for("resnet18_nofuse").integers(-128, 128, (4, 3, 224, 224), dtype=np.int8)
     g = spec.to_graph()
     g.set_option("fuse_conv_elemwise", 0)
+    g.set_option("fuse_conv_pooling", 0)
     want = netwalk.run(spec, x, oracle)
     out = run_model(lite, g.compile([4]), x, want.shape, forwards=2)[1]
     assert (out == want).all()
+
+
+def test_resnet18_with_stem_and_max_pool_as_one_instruction(lite, oracle):
+    """The opt-in ConvBias + MAX pooling fusion: the stem never stores its 112 x 112 result."""
+    from megcc_b200 import zoo
+    spec = zoo.resnet18(seed=3)
+    x = cases.rng_for("resnet18_poolfuse").integers(-128, 128, (4, 3, 224, 224), dtype=np.int8)
+    g = spec.to_graph()
+    g.set_option("fuse_conv_pooling", 1)
+    model = g.compile([4])
+    assert any(s.endswith("_pool_MAX3x3s2p1") for s in g.kernel_symbols())
+    assert not any("pooling_MAX" in s for s in g.kernel_symbols())
+    want = netwalk.run(spec, x, oracle)
+    for out in run_model(lite, model, x, want.shape, forwards=3):
+        assert (out == want).all()
 
 
 def test_resnet18_reference_kernels_agree(lite, reference):

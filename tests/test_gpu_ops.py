@@ -503,6 +503,57 @@ def test_conv_first_layer_space_to_depth_matches_oracle(ops, oracle, case):
     assert (direct == want).all()
 
 
+POOL_CASES = [
+    # name, n, ic, oc, h, w, k, pad, act, per_channel, bias  (stride 2, then MAX 3x3 / 2 / pad 1)
+    ("r18_stem", 2, 3, 64, 224, 224, 7, 3, "RELU", False, True),
+    ("odd_hw", 3, 3, 64, 225, 223, 7, 3, "IDENTITY", False, True),
+    ("k3_oc32", 4, 3, 32, 97, 104, 3, 1, "RELU", False, True),
+    ("k5_ic1_oc48", 4, 1, 48, 120, 120, 5, 2, "RELU", True, True),
+    ("k3_nopad_oc16", 4, 4, 16, 96, 100, 3, 0, "IDENTITY", False, False),
+    ("tiny_maps", 32, 3, 64, 33, 35, 7, 3, "RELU", False, True),
+    ("one_tile_row", 48, 2, 64, 26, 30, 3, 1, "RELU", True, True),
+]
+
+
+@pytest.mark.parametrize("case", POOL_CASES, ids=[c[0] for c in POOL_CASES])
+def test_first_layer_conv_with_fused_max_pool_matches_two_oracle_kernels(ops, oracle, case):
+    """ConvBias + Pooling MAX 3x3 / 2 / pad 1 as one kernel (the window maximum is taken on the
+    int32 accumulators, one output in four is requantised) against the two CPU kernels run one
+    after the other."""
+    name, n, ic, oc, h, w, k, pad, act, per_channel, with_bias = case
+    c = dict(name="pool_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=2, pad=pad, groups=1,
+             act=act, range=(-128, 127), bias_range=(-1000, 1000), bias=with_bias,
+             scales=(0.05, 0.01, 0.05 * (ic * k * k) ** 0.5 + 0.05))
+    src, flt, bias = cases.conv_inputs(c)
+    s0, s1, s2 = c["scales"]
+    sf = (cases.rng_for(c["name"] + "_pc").uniform(0.005, 0.02, oc).astype(np.float32)
+          if per_channel else None)
+    p = ops.conv_param(n, ic, h, w, oc, k, k, 2, pad, 1, act, s0, s1, s2)
+    assert ops.conv_s2d_pool_supported(p)
+    packed = ops.pack_filter_s2d(p, dev(flt))
+    got = ops.conv_bias_pool_qs8_s2d(p, dev(src), packed, None if bias is None else dev(bias),
+                                     None if sf is None else dev(sf))
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    conv = oracle.conv_bias_qs8(src, flt, bias, 2, pad, s0, s1 if sf is None else sf, s2, act)
+    want = oracle.pooling_qs8(conv, "MAX", 3, 2, 1)
+    out = got.cpu().numpy().transpose(0, 3, 1, 2)
+    assert out.shape == want.shape
+    bad = int((out != want).sum())
+    assert bad == 0, f"{bad}/{want.size} differ; first at {np.argwhere(out != want)[:4].tolist()}"
+    assert len(np.unique(want)) > 8
+
+
+def test_fused_max_pool_is_refused_where_it_does_not_commute(ops):
+    # H_SWISH is not monotonic; more than 64 output channels have no pooled epilogue
+    assert not ops.conv_s2d_pool_supported(
+        ops.conv_param(2, 3, 224, 224, 64, 7, 7, 2, 3, 1, "H_SWISH", 0.05, 0.01, 0.5))
+    assert not ops.conv_s2d_pool_supported(
+        ops.conv_param(2, 3, 224, 224, 128, 7, 7, 2, 3, 1, "RELU", 0.05, 0.01, 0.5))
+    assert not ops.conv_s2d_pool_supported(
+        ops.conv_param(2, 64, 56, 56, 64, 3, 3, 2, 1, 1, "RELU", 0.05, 0.01, 0.5))
+
+
 def test_conv_umma_per_channel_scales(ops, oracle):
     c = dict(name="umma_perchannel", n=2, ic=64, oc=128, h=32, w=32, k=3, stride=1, pad=1,
              groups=1, act="RELU", range=(-128, 127), bias_range=(-1000, 1000),
