@@ -41,6 +41,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 BATCH = 256
+# DRAM bytes moved by the tensor-core ConvBias launches of one batch-256 forward, measured
+# once under ncu (the capture cannot run inside a timed benchmark)
+CONV_DRAM_BYTES_PER_STEP = 934.4e6
 METRIC = "resnet18_int8_images_per_second"
 UNIT = "img/s"
 
@@ -547,7 +550,12 @@ def main():
         roofline = dict(
             bound="tensor",
             kernel="conv_umma_kernel / conv_patch_kernel (tcgen05 kind::i8 implicit GEMM)",
-            achieved=achieved, peak=peak, unit="TOP/s", frac=achieved / peak, traffic=None,
+            achieved=achieved, peak=peak, unit="TOP/s", frac=achieved / peak,
+            traffic=CONV_DRAM_BYTES_PER_STEP, traffic_unit="bytes per step",
+            traffic_note="dram__bytes_read.sum + dram__bytes_write.sum of the 21 tensor-core "
+                         "launches of one forward at batch 256, one ncu capture "
+                         "(profiles/resnet18_int8_b256_dram_traffic_per_kernel.md); below the "
+                         "1.4 GB of algorithmic bytes because L2 keeps the smaller feature maps",
             launches_per_step=len(umma), share_of_step=umma_ms / total_ms if total_ms else None,
             peak_note=f"2 x bf16 sustained ({peaks['source']}); MEASURED_PEAKS.json holds no int8 "
                       "figure, so the other denominators are listed beside it",

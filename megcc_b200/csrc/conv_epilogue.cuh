@@ -7,6 +7,10 @@
 
 namespace mb200 {
 
+// what an absent bias reads: the vector path then loads unconditionally instead of testing the
+// pointer and clearing four registers for each group of four channels
+__device__ __align__(32) const int32_t kZeroBias[32] = {};
+
 struct EpilogueParams {
     int oc;
     int act;
@@ -247,11 +251,10 @@ __device__ __forceinline__ void epilogue_store_t(
         static_assert(FAST == 0 || kPaired, "the verified form exists for the paired path only");
         static_assert(ZMODE == 0 || ACT == ACT_IDENTITY, "the fused step follows a plain ConvBias");
         const RequantPair rp(e);
+        const int4* bias4 = reinterpret_cast<const int4*>(e.bias ? e.bias + ch0 : kZeroBias);
 #pragma unroll
         for (int j = 0; j < NV / 4; ++j) {
-            int4 b = make_int4(0, 0, 0, 0);
-            if (e.bias)
-                b = __ldg(reinterpret_cast<const int4*>(e.bias + ch0) + j);
+            const int4 b = __ldg(bias4 + j);
             if (kPaired) {
                 int r0, r1, r2, r3;
                 if (FAST != 0) {
