@@ -137,6 +137,39 @@ def cpu_reference_run(steps, warmup, procs):
     walking the whole network on its own image (oracle/cpu_worker.py). All start at a common
     time after their warm-up. Returns (img/s, seconds per step, kind)."""
     cpus = sorted(os.sched_getaffinity(0))[:procs]
+    runner = os.path.join(ROOT, "oracle", "_ref", "ref_lite_runner")
+    if os.path.exists(runner):
+        # the reference's C runtime itself: the BARE_METAL DeviceModel of the same network,
+        # compiled by this repository's compile side, through the reference's LITE_forward
+        # with the reference's generated kernels (oracle/ref_lite_runner.c). The runner does
+        # one untimed forward, then `steps` timed ones, and reports its own mean.
+        import tempfile
+
+        import numpy as np
+
+        from megcc_b200 import zoo
+        g = zoo.resnet18().to_graph()
+        g.set_option("bare_metal_model", 2)
+        model = g.compile([1])
+        with tempfile.TemporaryDirectory() as d:
+            with open(os.path.join(d, "resnet18_b1.tiny"), "wb") as f:
+                f.write(model)
+            for c in cpus:
+                np.random.default_rng(1234 + c).integers(
+                    -128, 128, (1, 3, 224, 224), dtype=np.int8).tofile(
+                    os.path.join(d, f"in{c}.bin"))
+            ps = [subprocess.Popen(
+                [runner, os.path.join(d, "resnet18_b1.tiny"), os.path.join(d, f"in{c}.bin"),
+                 os.path.join(d, f"out{c}.bin"), str(steps), str(c)],
+                stdout=subprocess.PIPE, text=True) for c in cpus]
+            ms = []
+            for p in ps:
+                out, _ = p.communicate()
+                if p.returncode != 0 or "forward_ms" not in out:
+                    raise RuntimeError("a reference runtime process failed")
+                ms.append(float(out.split("forward_ms")[1].split()[0]))
+        span = max(ms) * 1e-3 * steps
+        return len(cpus) * steps / span, span / steps, "reference"
     start = time.time() + 8.0 + 2.5 * warmup  # imports + model construction + warm-up
     ps = [subprocess.Popen([sys.executable, "-m", "oracle.cpu_worker", str(c), str(steps),
                             str(warmup), repr(start)], stdout=subprocess.PIPE, text=True,
@@ -345,9 +378,10 @@ def main():
             return
         steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
         ips, sec, kind = cpu_reference_run(steps, warmup, threads)
-        sample = (f"{steps} steps x {threads} images (one pinned single-threaded process per "
-                  f"host core, one image each) of the same network, {warmup} warm-up; the "
-                  f"{BATCH}-image batch is not run in full on the CPU")
+        sample = (f"{steps} steps x {threads} images (one pinned process of the reference's "
+                  f"single-threaded C runtime per host core, LITE_forward on the BARE_METAL "
+                  f"DeviceModel of the same network at batch 1, one image each), 1 warm-up "
+                  f"forward; the {BATCH}-image batch is not run in full on the CPU")
         print(json.dumps(dict(
             impl="reference", metric=METRIC, value=ips, unit=UNIT, n_gpus=args.gpus,
             steps=steps, warmup=warmup, ms_per_step=sec * 1e3, higher_is_better=True,
@@ -608,8 +642,9 @@ def main():
             ips_cpu, sec, kind = cpu_reference_run(2, 1, threads)
             cpu_baseline = dict(
                 value=ips_cpu, unit=UNIT, cores=threads, kind=kind,
-                sample=f"2 steps x {threads} images (one pinned single-threaded process per host "
-                       "core, one image each), 1 warm-up step")
+                sample=f"2 steps x {threads} images (one pinned process of the reference's "
+                       "single-threaded C runtime per host core, LITE_forward on the BARE_METAL "
+                       "DeviceModel of the same network at batch 1), 1 warm-up forward")
     arms.close()
     group.close()
     if rank != 0:

@@ -121,7 +121,16 @@ MB200C_API int mb200c_mark_output(mb200c_graph* g, int tensor);
  *                         64 output channels) whose only consumer is a Pooling MAX 3x3 /
  *                         stride 2 / pad 1 becomes one instruction that never stores the
  *                         ConvBias result; bit-identical to the two kernels. Off because the
- *                         fused kernel measured slower than the pair it replaces. */
+ *                         fused kernel measured slower than the pair it replaces.
+ *   "bare_metal_model"    0 (default): CUDA_SM100 DeviceModels only. 1: a BARE_METAL
+ *                         DeviceModel per batch size beside them (runtime/schema/model.fbs
+ *                         :391 allows several), whose Oprs name the reference's own x86
+ *                         kernels, one per operator, over NCHW tensors and the same weight
+ *                         pool: the reference's C runtime and this runtime then execute one
+ *                         artefact. 2: the BARE_METAL DeviceModels alone (the unmodified
+ *                         reference runtime stops at a device value it does not know,
+ *                         runtime/src/parse.c:78-99). For graphs of qint8 ConvBias with
+ *                         per-tensor scales, Pooling and ElemwiseMultiType. */
 MB200C_API int mb200c_set_option(mb200c_graph* g, const char* name, int value);
 
 /* Compiles one DeviceModel (device CUDA_SM100) per batch size into a tinynn model.

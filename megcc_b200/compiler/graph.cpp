@@ -140,6 +140,10 @@ struct mb200c_graph {
     // ConvBias + MAX pooling as one instruction: off unless asked for (on a ResNet-18 stem
     // at batch 256 the fused kernel measured 217 us against 132 + 55 us for the pair)
     bool fuse_conv_pooling = false;
+    // 0: CUDA_SM100 DeviceModels only; 1: a BARE_METAL DeviceModel per batch beside them
+    // (the operators as the reference's own x86 kernels: one artefact for both runtimes);
+    // 2: the BARE_METAL DeviceModels alone
+    int bare_metal_model = 0;
 
     int add_tensor(const std::string& n, int c, int h, int w, float scale) {
         GTensor t;
@@ -869,6 +873,12 @@ int mb200c_add_qelemwise(
 int mb200c_set_option(mb200c_graph* g, const char* name, int value) {
     if (!g || !name)
         return err("set_option: bad argument");
+    if (strcmp(name, "bare_metal_model") == 0) {
+        if (value < 0 || value > 2)
+            return err("set_option: bare_metal_model is 0, 1 or 2");
+        g->bare_metal_model = value;
+        return 0;
+    }
     if (strcmp(name, "fuse_conv_pooling") == 0) {
         g->fuse_conv_pooling = value != 0;
         return 0;
@@ -1158,7 +1168,7 @@ int mb200c_compile(
 
     // ---- one DeviceModel per batch size ----
     std::vector<fb::NodeP> dmodels;
-    for (int bi = 0; bi < nr_batches; ++bi) {
+    for (int bi = 0; bi < nr_batches && g->bare_metal_model != 2; ++bi) {
         const int batch = batches[bi];
         if (batch <= 0)
             return err("compile: batch %d", batch);
@@ -1265,6 +1275,125 @@ int mb200c_compile(
         dm->add_ref(fb::field::D_instructions_type, fb::make_vec<uint8_t>(itags));
         dm->add_ref(fb::field::D_instructions, fb::make_table_vec(inodes));
         dm->add<uint64_t>(fb::field::D_tensor_memory, (uint64_t)c.arena);
+        dm->add_ref(fb::field::D_inputs, fb::make_vec<int32_t>(ins));
+        dm->add_ref(fb::field::D_outputs, fb::make_vec<int32_t>(outs));
+        dmodels.push_back(dm);
+    }
+    // ---- the same network for the reference's C runtime: a BARE_METAL DeviceModel per batch
+    // whose Oprs name the reference's own kernels (one operator each, NCHW tensors, the
+    // weights of the shared pool as they are). runtime/schema/model.fbs:391 allows several
+    // DeviceModels; runtime/src/parse.c:470-520 takes those of the devices it knows. ----
+    for (int bi = 0; bi < nr_batches && g->bare_metal_model != 0; ++bi) {
+        const int batch = batches[bi];
+        if (batch <= 0)
+            return err("compile: batch %d", batch);
+        mb200c_graph bm = *g;  // the operators as the user added them: no relayout, no fusion
+        for (auto& t : bm.tensors)
+            t.nchw = true;
+        std::vector<std::string> sym(bm.ops.size());
+        std::map<std::string, int> bm_id;
+        for (size_t k = 0; k < bm.ops.size(); ++k) {
+            const GOp& op = bm.ops[k];
+            const bool known = !op.f32 && !op.flt44 &&
+                               ((op.type == OpType::CONV && op.weights.size() <= 2 &&
+                                 (op.weights.size() == 1 || op.has_bias)) ||
+                                op.type == OpType::POOL || op.type == OpType::QELEM);
+            if (!known)
+                return err("operator '%s' has no BARE_METAL form here (qint8 ConvBias with "
+                           "per-tensor scales, Pooling and ElemwiseMultiType do)", op.name.c_str());
+            auto ctx = bm.context_for(op, batch);
+            const KernelGen::KernelFunc* kf = nullptr;
+            for (auto* c : KernelGen::Cuda::ArchKernelPack::GetKernel(mb200c_graph::kern_type(op.type)))
+                if (c->IsAvailable(ctx.get())) {
+                    kf = c;
+                    break;
+                }
+            if (!kf)
+                return err("operator '%s' is not admitted", op.name.c_str());
+            // the reference's symbol for the same operator: its own prefix and format name
+            std::string s = kf->GetKernelSymbol(ctx.get());
+            const std::string prefix = "cuda_sm100_";
+            if (s.compare(0, prefix.size(), prefix) != 0)
+                return err("unexpected symbol %s", s.c_str());
+            s = "kernel_" + s.substr(prefix.size());
+            const size_t at = s.find("_NHWC_");
+            if (at != std::string::npos)
+                s.replace(at, 6, "_NCHW_");
+            sym[k] = s;
+            if (!bm_id.count(s)) {
+                const int id = (int)bm_id.size();
+                bm_id[s] = id;
+            }
+        }
+        std::vector<size_t> no_ws(bm.ops.size(), 0), offsets, ws_offsets;
+        size_t unplanned = 0;
+        const size_t arena = plan_memory(bm, bm.ops, batch, no_ws, &offsets, &ws_offsets, &unplanned);
+        std::vector<int> use_count(bm.tensors.size(), 0);
+        for (auto& op : bm.ops)
+            for (int id : op.inputs)
+                use_count[id]++;
+        std::vector<fb::NodeP> tnodes, inodes;
+        std::vector<uint8_t> itags;
+        for (size_t i = 0; i < bm.tensors.size(); ++i) {
+            const GTensor& t = bm.tensors[i];
+            const std::vector<int> dims = {batch, t.c, t.h, t.w};
+            auto n = fb::make_table();
+            n->add_ref(fb::field::T_dtype, dtype_node(fb::QInt8, t.scale));
+            n->add_ref(fb::field::T_layout, layout_node(dims, contiguous(dims), fb::NCHW));
+            n->add<int64_t>(fb::field::T_offset, (int64_t)offsets[i]);
+            n->add<int32_t>(fb::field::T_use_count, use_count[i]);
+            n->add_ref(fb::field::T_name, fb::make_string(t.name));
+            tnodes.push_back(n);
+        }
+        for (size_t k = 0; k < bm.ops.size(); ++k) {
+            const GOp& op = bm.ops[k];
+            std::vector<int32_t> in;
+            std::vector<int8_t> in_t;
+            for (int id : op.inputs) {
+                in.push_back(id);
+                in_t.push_back(fb::TENSOR);
+            }
+            if (op.type == OpType::CONV) {
+                // src, filter, [bias]
+                in.resize(1);
+                in_t.resize(1);
+                for (int wid : op.weights) {
+                    in.push_back(wid);
+                    in_t.push_back(fb::WEIGHT);
+                }
+            }
+            auto ws = fb::make_table();
+            ws->add<int64_t>(fb::field::WS_size, 0);
+            ws->add<int64_t>(fb::field::WS_offset, 0);
+            auto n = fb::make_table();
+            n->add_ref(fb::field::O_name, fb::make_string(op.name));
+            n->add_ref(fb::field::O_type, fb::make_string(sym[k]));
+            n->add_ref(fb::field::O_inputs, fb::make_vec<int32_t>(in));
+            n->add_ref(fb::field::O_input_types, fb::make_vec<int8_t>(in_t));
+            n->add_ref(fb::field::O_outputs, fb::make_vec<int32_t>({op.output}));
+            n->add_ref(fb::field::O_workspace, ws);
+            n->add<int32_t>(fb::field::O_init_id, bm_id[sym[k]]);
+            n->add<int32_t>(fb::field::O_kernel_id, bm_id[sym[k]]);
+            n->add<int32_t>(fb::field::O_workspace_id, bm_id[sym[k]]);
+            n->add<int32_t>(fb::field::O_deduce_id, -1);
+            inodes.push_back(n);
+            itags.push_back(fb::INST_OPR);
+        }
+        std::vector<int32_t> ins, outs;
+        for (size_t i = 0; i < bm.tensors.size(); ++i) {
+            if (bm.tensors[i].is_input)
+                ins.push_back((int)i);
+            if (bm.tensors[i].is_output)
+                outs.push_back((int)i);
+        }
+        if (outs.empty())
+            return err("compile: the graph has no output");
+        auto dm = fb::make_table();
+        dm->add<int8_t>(fb::field::D_device, (int8_t)fb::BARE_METAL);
+        dm->add_ref(fb::field::D_tensor_pool, fb::make_table_vec(tnodes));
+        dm->add_ref(fb::field::D_instructions_type, fb::make_vec<uint8_t>(itags));
+        dm->add_ref(fb::field::D_instructions, fb::make_table_vec(inodes));
+        dm->add<uint64_t>(fb::field::D_tensor_memory, (uint64_t)arena);
         dm->add_ref(fb::field::D_inputs, fb::make_vec<int32_t>(ins));
         dm->add_ref(fb::field::D_outputs, fb::make_vec<int32_t>(outs));
         dmodels.push_back(dm);

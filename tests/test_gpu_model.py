@@ -295,3 +295,16 @@ def test_nchw44_model_through_generated_kernel_tables(lite, oracle, tmp_path):
         net.wait()
         assert (net.output(net.output_names()[0]).reshape(want.shape) == want).all()
     net.close()
+
+
+def test_model_with_a_bare_metal_device_model_beside_the_cuda_one(lite, oracle):
+    """One artefact for both runtimes (tests/test_bare_metal_model.py runs the other half on
+    the reference's C runtime): this runtime takes the CUDA DeviceModels of the file."""
+    from megcc_b200 import zoo
+    spec = zoo.resnet18(seed=5)
+    x = cases.rng_for("dual_model").integers(-128, 128, (2, 3, 224, 224), dtype=np.int8)
+    g = spec.to_graph()
+    g.set_option("bare_metal_model", 1)
+    want = netwalk.run(spec, x, oracle)
+    out = run_model(lite, g.compile([2]), x, want.shape, forwards=2)[1]
+    assert (out == want).all()
