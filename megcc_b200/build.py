@@ -84,7 +84,8 @@ def build(verbose=False, force=False):
             sys.stderr.write(out)
         if p.returncode:
             raise RuntimeError(f"nvcc failed on {s}")
-    cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-lcudart", "-ldl"]
+    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs + [
+        "-lcudart", "-ldl"]
     subprocess.run(cmd, check=True)
     return LIB
 

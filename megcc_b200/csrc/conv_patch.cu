@@ -494,6 +494,19 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_ker
             // the pixel index fits 32 bits (the launcher checks); one wide multiply
             const uint32_t pixel = ((uint32_t)at.img * p.oh + oy) * p.ow + ox;
             const size_t px_off = (size_t)pixel * p.oc;
+            if (p.ep.z_mode != 0) {
+                // The residual operand is the one read of this epilogue that nothing
+                // pipelines: ask for the bytes this thread will want one tile from now, so
+                // that they wait in L2 instead of DRAM when the chunk below loads them.
+                PatchWalker nx = at;
+                nx.next();
+                const int ny = nx.ty * kTH + py, nxx = nx.tx * kTW + px;
+                if (mt + m_step < p.m_tiles && ny < p.oh && nxx < p.ow) {
+                    const uint32_t npix = ((uint32_t)nx.img * p.oh + ny) * p.ow + nxx;
+                    const int8_t* zn = p.ep.z + (size_t)npix * p.oc + n0 + ((warp - 2) >> 2) * 32;
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(zn));
+                }
+            }
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             const int half = (warp - 2) >> 2;
             // each warp takes a run of adjacent chunks: its thread's bytes are contiguous

@@ -65,6 +65,15 @@ def main(batch=32, only=""):
         d = torch.empty((batch, hw, hw, c), dtype=torch.int8, device="cuda")
         cases.append((name, (lambda pp=pp, s=s, f=f, b=b, d=d: ops.conv_bias_qs8_nhwc(
             pp, s, f, b, dst=d, algo="auto")), 2.0 * batch * c * hw * hw * c * 9))
+    # the 1x1 / stride 2 projection of the first block of a ResNet stage (64 -> 128 at 56 x 56)
+    pp = ops.conv_param(batch, 64, 56, 56, 128, 1, 1, 2, 0, 1, "IDENTITY", 0.05, 0.01, 0.5)
+    s = dev(rng.integers(-128, 128, (batch, 56, 56, 64), dtype=np.int8))
+    f = ops.pack_filter(pp, dev(rng.integers(-127, 128, (128, 64, 1, 1), dtype=np.int8)))
+    b = dev(rng.integers(-1000, 1000, (128,), dtype=np.int32))
+    d = torch.empty((batch, 28, 28, 128), dtype=torch.int8, device="cuda")
+    cases.append(("proj_64_128_1x1s2_56", (lambda: ops.conv_bias_qs8_nhwc(pp, s, f, b, dst=d,
+                                                                         algo="auto")),
+                  2.0 * batch * 128 * 28 * 28 * 64))
     cases = [c for c in cases if only in c[0]]
     for rnd in range(2):
         for name, fn, work in cases:
