@@ -260,8 +260,8 @@ def other_configs(local_rank, rates):
         tf32_pass_tflops=round(3 * flops / (p50 * 1e-3) / 1e12, 1),
         frac_of_measured_tf32_mma_rate=round(3 * flops / (p50 * 1e-3) / 1e12 / rates["tf32"], 3),
         arena_gb=round(g.arena_bytes(0) / 1e9, 2), gmac_per_image=round(spec.macs_per_image() / 1e9, 2),
-        note="whole forward (83 ConvBias + concat / resize / pooling kernels + the operand-split "
-             "pre-passes); fp32_tflops counts 2 x MAC once, tf32_pass_tflops the three tensor-core "
+        note="whole forward (83 ConvBias + concat / resize / pooling kernels; operands are split "
+             "into their tf32 planes on chip); fp32_tflops counts 2 x MAC once, tf32_pass_tflops the three tensor-core "
              "passes that fp32 accuracy costs")
 
     def timed(fn, reps=10):

@@ -332,9 +332,10 @@ typedef struct mb200_conv_f32_param {
  * compiler/lib/KernelGen/GeneralIntrinsic/ConvKernel/Fp32Im2col.cpp:88-120, body :198-217).
  * The Init step (mb200_conv_f32_pack_filter) turns the OIHW filter into the K-major form
  * [OC][KH][KW][ICpg] followed, for dense filters whose channel count fills whole TMA rows (16
- * or a multiple of 32), by its two tf32 planes for the tensor cores. The ConvBias itself needs
- * mb200_conv_f32_workspace_bytes(p) bytes of 256-byte aligned device scratch (the tf32 planes
- * of the activation; 0 when the general kernel runs).
+ * or a multiple of 32), by its two tf32 planes for the tensor cores. The activation is split
+ * into its planes in shared memory, so the ConvBias needs no scratch:
+ * mb200_conv_f32_workspace_bytes(p) answers 0 and `workspace` may be NULL (both are kept so
+ * that callers written against earlier versions keep working).
  *   bias   [OC] floats or NULL
  *   z      optional NHWC tensor of the output's shape added AFTER the activation (the shortcut
  *          of a bottleneck block: an Elemwise ADD folded into the epilogue), or NULL
@@ -353,8 +354,8 @@ MB200_API int mb200_conv_bias_f32_nhwc(
 /* ---- MatrixMul fp32, C[M][N] = A[M][K] * B[K][N], row-major (replaces
  * GI_kernel_fp32_matmul_4x12_nn, compiler/lib/KernelGen/GeneralIntrinsic/MatMulKernel/
  * Fp32MatMulM4N12.cpp:8-160). B is prepared once by mb200_matmul_f32_pack_b into
- * mb200_matmul_f32_packed_b_bytes(k, n) bytes; the product needs
- * mb200_matmul_f32_workspace_bytes(m, k) bytes of scratch. Tensor cores (three tf32 passes)
+ * mb200_matmul_f32_packed_b_bytes(k, n) bytes; the product needs no scratch
+ * (mb200_matmul_f32_workspace_bytes answers 0). Tensor cores (three tf32 passes)
  * when k % 32 == 0 (or k == 16) and A holds at least 128 KiB. */
 MB200_API size_t mb200_matmul_f32_packed_b_bytes(int k, int n);
 MB200_API int mb200_matmul_f32_pack_b(int k, int n, const float* b, float* b_packed, void* stream);

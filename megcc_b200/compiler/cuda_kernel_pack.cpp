@@ -862,15 +862,8 @@ TinyNNStatus ${signature} {
 
 // must agree with mb200_conv_f32_workspace_bytes (megcc_b200/csrc/f32_abi.cu): the two tf32
 // planes of the activation when the filter is dense and its channels fill whole TMA rows
-size_t ConvBiasF32::WorkspaceBytes(TContext* ctx) const {
-    const CCOperand src = ctx->getAttrOprand("operand:0");
-    if (ctx->getAttrStr("sparse") != "DENSE" || src.shape.size() != 4)
-        return 0;
-    const size_t ic = src.shape[1];
-    if (!(ic == 16 || ic % 32 == 0))
-        return 0;
-    const size_t bytes = 2 * src.shape[0] * src.shape[1] * src.shape[2] * src.shape[3] * 4;
-    return (bytes + 255) / 256 * 256;
+size_t ConvBiasF32::WorkspaceBytes(TContext*) const {
+    return 0;  // the activation is split into its tf32 planes in shared memory
 }
 
 // ---- MatrixMul fp32 ----
@@ -946,12 +939,8 @@ TinyNNStatus ${signature} {
     return s.text;
 }
 
-size_t MatMulF32::WorkspaceBytes(TContext* ctx) const {
-    const CCOperand a = ctx->getAttrOprand("operand:0");
-    const size_t m = a.shape[0], k = a.shape[1];
-    if (!(k == 16 || k % 32 == 0))
-        return 0;
-    return (2 * m * k * 4 + 255) / 256 * 256;
+size_t MatMulF32::WorkspaceBytes(TContext*) const {
+    return 0;
 }
 
 // ---- Elemwise fp32 ----

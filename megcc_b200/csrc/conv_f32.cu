@@ -16,7 +16,9 @@
 // chain scaled outputs by 1 - 4e-6; through the 60 ConvBias layers between a detector's input
 // and its heads that compounded to -3.6e-4, against a tolerance of 1e-4). Two measures keep
 // the drift at the level of fp32 rounding:
-//   * short chains: the K loop is cut into segments of four K = 8 steps; every segment starts
+//   * short chains: the K loop is cut into segments of eight K = 8 steps (with four the worst
+//     error of a detector's heads is 0.15 of the tolerance and the kernel 10 % slower, with
+//     sixteen 0.35, with thirty-two 0.6; eight leaves 0.23); every segment starts
 //     fresh TMEM accumulators (two sets alternate) and the epilogue warps add the finished
 //     segment into fp32 registers with round-to-nearest while the tensor core works on the
 //     next one. A short partial sum is small against the final one and nearly uncorrelated
@@ -27,12 +29,16 @@
 //
 //   * filter: split once at load time (the Init step) into two K-major planes
 //     [2][OC][KH][KW][IC];
-//   * activation: split by a bandwidth-bound pre-pass into scratch memory the caller provides
-//     (planes [2][N][H][W][C]), then fetched by TMA (im2col, or tiled for a 1x1 filter) like the
-//     int8 kernel's operands;
+//   * activation: fetched as it is by TMA (im2col, or tiled for a 1x1 filter) and split ON
+//     CHIP: four converter warps turn each arrived fp32 tile into its hi plane in place and
+//     its lo plane in the neighbouring slot of the stage. The split is elementwise and the
+//     TMA swizzle is a function of the shared-memory address, so both planes keep the layout
+//     the MMA descriptors expect; no pre-pass over global memory, no scratch tensor, and the
+//     input is read once instead of five times (read, two plane writes, two plane reads);
 //   * structure of the kernel as in conv_umma.cu: persistent CTAs, warp 0 TMA producer, warp 1
 //     MMA issuer and TMEM owner, warps 2..9 epilogue (tcgen05.ld -> + bias -> activation ->
-//     optional residual add -> 16-byte NHWC stores), two accumulator buffers, bounded waits.
+//     optional residual add -> 16-byte NHWC stores), warps 10..13 converters, two accumulator
+//     buffers, bounded waits.
 //
 // Replaces, for the fp32 configurations, the reference's im2col + 4x12 SIMD GEMM
 // (compiler/lib/KernelGen/GeneralIntrinsic/ConvKernel/Fp32Im2col.cpp:122-217,
@@ -42,6 +48,7 @@
 // differs from the reference's, as it does between any two fp32 GEMMs: parity is held to
 // 1e-4 relative / 1e-5 absolute, not bit for bit.
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "f32_internal.h"
 #include "pdl.h"
@@ -95,46 +102,8 @@ __host__ __device__ inline float round_tf32(float v) {
 }
 
 // ------------------------------------------------------------------------------------------
-// operand splitting
+// filter packing (load time)
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) split_tf32_kernel(
-        const float4* __restrict__ src, float4* __restrict__ hi, float4* __restrict__ lo,
-        size_t vecs) {
-    pdl_start();
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < vecs;
-         i += (size_t)gridDim.x * blockDim.x) {
-        const float4 v = __ldg(src + i);
-        float4 h, l;
-        h.x = round_tf32(v.x); l.x = round_tf32(__fsub_rn(v.x, h.x));
-        h.y = round_tf32(v.y); l.y = round_tf32(__fsub_rn(v.y, h.y));
-        h.z = round_tf32(v.z); l.z = round_tf32(__fsub_rn(v.z, h.z));
-        h.w = round_tf32(v.w); l.w = round_tf32(__fsub_rn(v.w, h.w));
-        hi[i] = h;
-        lo[i] = l;
-    }
-}
-
-// the same over pixel rows of `c` floats that lie `pitch` floats apart (a channel slice of a
-// wider NHWC buffer), c % 4 == 0
-__global__ void __launch_bounds__(256) split_tf32_rows_kernel(
-        const float* __restrict__ src, float4* __restrict__ hi, float4* __restrict__ lo,
-        size_t rows, int c4, size_t pitch) {
-    const size_t vecs = rows * (size_t)c4;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < vecs;
-         i += (size_t)gridDim.x * blockDim.x) {
-        const size_t r = i / c4;
-        const int k = (int)(i - r * c4);
-        const float4 v = __ldg(reinterpret_cast<const float4*>(src + r * pitch) + k);
-        float4 h, l;
-        h.x = round_tf32(v.x); l.x = round_tf32(__fsub_rn(v.x, h.x));
-        h.y = round_tf32(v.y); l.y = round_tf32(__fsub_rn(v.y, h.y));
-        h.z = round_tf32(v.z); l.z = round_tf32(__fsub_rn(v.z, h.z));
-        h.w = round_tf32(v.w); l.w = round_tf32(__fsub_rn(v.w, h.w));
-        hi[i] = h;
-        lo[i] = l;
-    }
-}
-
 // OIHW fp32 -> two K-major planes [2][OC][KH][KW][ICp] (hi, lo), ICp >= IC zero-filled
 __global__ void __launch_bounds__(256) pack_filter_f32_kernel(
         const float* __restrict__ src, float* __restrict__ dst, int oc, int ic, int icp, int kh,
@@ -237,7 +206,6 @@ struct F32ConvParams {
     int sh, sw, base_h, base_w;
     int m_tiles, n_tiles;
     int a_tiled;      // 1x1, stride 1, no padding: A is the plain matrix [pixels][channels]
-    int a_lo_offset;  // images (im2col) or rows (tiled) from the hi plane to the lo plane
     int b_lo_offset;  // rows from the hi plane to the lo plane of the filter
     F32Epilogue ep;
     int* status;
@@ -252,12 +220,23 @@ struct F32Smem {
     static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
     static constexpr int kTiles = kStages * kStageBytes;
     static constexpr int kBarOff = kTiles;
-    static constexpr int kTotal = kBarOff + (2 * kMaxStages + 5) * 8 + 16;
+    static constexpr int kTotal = kBarOff + (3 * kMaxStages + 5) * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;
 };
 
 constexpr int kF32EpilogueWarps = 8;
-constexpr int kF32Threads = 64 + 32 * kF32EpilogueWarps;
+constexpr int kF32ConvertWarps = 4;
+constexpr int kF32Threads = 64 + 32 * kF32EpilogueWarps + 32 * kF32ConvertWarps;
+
+// v = hi + lo with both halves exact tf32 values (which way a tie rounds does not matter:
+// v - hi is exact, and lo is its nearest tf32)
+__device__ __forceinline__ void split_tf32(float v, float& hi, float& lo) {
+    uint32_t h, l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
+    hi = __uint_as_float(h);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(__fsub_rn(v, hi)));
+    lo = __uint_as_float(l);
+}
 
 template <int BN, int ROWB>
 __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
@@ -270,7 +249,8 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(smem + L::kBarOff);
     uint64_t* empty_bar = full_bar + kMaxStages;
-    uint64_t* acc_full = empty_bar + kMaxStages;  // [2]
+    uint64_t* conv_bar = empty_bar + kMaxStages;  // the stage's A tile is split: MMAs may read it
+    uint64_t* acc_full = conv_bar + kMaxStages;  // [2]
     uint64_t* acc_empty = acc_full + 2;           // [2]
     uint64_t* drain_bar = acc_empty + 2;
     uint32_t* tmem_slot = (uint32_t*)(drain_bar + 1);
@@ -283,6 +263,7 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
         for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
+            mbar_init(&conv_bar[s], 32 * kF32ConvertWarps);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
@@ -329,20 +310,17 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(&full_bar[s], (uint32_t)L::kStageBytes);
+                    // the fp32 A tile lands in the hi slot; the lo slot is filled on chip
+                    mbar_expect_tx(&full_bar[s], (uint32_t)(L::kABytes + 2 * L::kBBytes));
                     uint8_t* a_hi = smem + s * L::kStageBytes;
                     uint8_t* a_lo = a_hi + L::kABytes;
                     uint8_t* b_hi = a_lo + L::kABytes;
                     uint8_t* b_lo = b_hi + L::kBBytes;
-                    if (p.a_tiled) {
+                    if (p.a_tiled)
                         tma_load_2d(a_hi, &map_a, &full_bar[s], cb * kChans, m0);
-                        tma_load_2d(a_lo, &map_a, &full_bar[s], cb * kChans, m0 + p.a_lo_offset);
-                    } else {
+                    else
                         tma_load_im2col_4d(a_hi, &map_a, &full_bar[s], cb * kChans, base_w, base_h,
                                            img, (uint16_t)fx, (uint16_t)fy);
-                        tma_load_im2col_4d(a_lo, &map_a, &full_bar[s], cb * kChans, base_w, base_h,
-                                           img + p.a_lo_offset, (uint16_t)fx, (uint16_t)fy);
-                    }
                     tma_load_2d(b_hi, &map_b, &full_bar[s], it * kChans, n0);
                     tma_load_2d(b_lo, &map_b, &full_bar[s], it * kChans, n0 + p.b_lo_offset);
                     if (++cb == p.cblocks) {
@@ -387,7 +365,7 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
                     const uint32_t tmem_d = tmem_base + (uint32_t)(buf * 2 * BN);
                     const uint32_t tmem_c = tmem_d + (uint32_t)BN;
                     for (int it = k0; it < k1; ++it) {
-                        if (!mbar_wait(&full_bar[s], phase, abort_flag, p.wait_cycles)) {
+                        if (!mbar_wait(&conv_bar[s], phase, abort_flag, p.wait_cycles)) {
                             if (!*abort_flag) {
                                 *abort_flag = 1;
                                 atomicExch(p.status, ERR_MMA_WAIT);
@@ -424,6 +402,48 @@ __global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
                     }
                     if (ok)
                         umma_commit(&acc_full[buf]);
+                }
+            }
+        }
+    } else if (warp >= 2 + kF32EpilogueWarps) {
+        // ---------------- converters: fp32 A tile -> hi (in place) and lo planes ----------------
+        const int ct = (int)threadIdx.x - (64 + 32 * kF32EpilogueWarps);
+        constexpr int kVecs = L::kABytes / 16;
+        constexpr int kPerThread = kVecs / (32 * kF32ConvertWarps);
+        static_assert(kVecs % (32 * kF32ConvertWarps) == 0, "whole vectors per converter thread");
+        int s = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int it = 0; it < p.k_iters; ++it) {
+                ok = mbar_wait(&full_bar[s], phase, abort_flag, p.wait_cycles);
+                if (!ok && !*abort_flag) {
+                    *abort_flag = 1;
+                    atomicExch(p.status, ERR_PRODUCER_WAIT);
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+                float4* hi = reinterpret_cast<float4*>(smem + s * L::kStageBytes);
+                float4* lo = hi + kVecs;
+#pragma unroll
+                for (int j = 0; j < kPerThread; ++j) {
+                    const int idx = ct + j * 32 * kF32ConvertWarps;
+                    const float4 v = hi[idx];
+                    float4 h, l;
+                    split_tf32(v.x, h.x, l.x);
+                    split_tf32(v.y, h.y, l.y);
+                    split_tf32(v.z, h.z, l.z);
+                    split_tf32(v.w, h.w, l.w);
+                    hi[idx] = h;
+                    lo[idx] = l;
+                }
+                // generic-proxy writes, read next by the tensor core through the async proxy
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&conv_bar[s]);
+                if (++s == kSt) {
+                    s = 0;
+                    phase ^= 1u;
                 }
             }
         }
@@ -633,7 +653,7 @@ bool conv_f32_umma_supported(const ConvF32Args& a, const float* src, const float
         return false;
     if ((size_t)a.n * a.ih * a.iw * a.ic * 4 < 131072)
         return false;
-    if ((size_t)2 * a.n * a.ih * a.iw >= (1ull << 31) || (size_t)2 * a.m >= (1ull << 31))
+    if ((size_t)a.n * a.ih * a.iw >= (1ull << 31) || (size_t)a.m >= (1ull << 31))
         return false;
     if (((uintptr_t)src | (uintptr_t)dst) & 15)
         return false;
@@ -643,8 +663,8 @@ bool conv_f32_umma_supported(const ConvF32Args& a, const float* src, const float
 }
 
 size_t conv_f32_workspace_bytes(const ConvF32Args& a) {
-    // the two tf32 planes of the activation
-    return 2 * (size_t)a.n * a.ih * a.iw * a.ic * sizeof(float);
+    (void)a;  // the activation is split into its tf32 planes in shared memory
+    return 0;
 }
 
 int launch_conv_f32_pack_filter_split(
@@ -679,16 +699,9 @@ int launch_conv_f32_umma(
     const DriverApi& api = driver_api();
     if (!api.ok)
         return set_error(ST_RUNTIME, "cuTensorMapEncode* entry points not found in the driver");
-    if (((uintptr_t)workspace | (uintptr_t)flt_split) & 15)
-        return set_error(ST_INVALID_LAYOUT, "workspace and filter must be 16-byte aligned");
-    const size_t elems = (size_t)a.n * a.ih * a.iw * a.ic;
-    float* hi = (float*)workspace;
-    float* lo = hi + elems;
-    launch_pdl(split_tf32_kernel, dim3(grid_1d(elems / 4, 256)), dim3(256), 0, st,
-               (const float4*)src, (float4*)hi, (float4*)lo, elems / 4);
-    int rc = check_launch("split_tf32");
-    if (rc)
-        return rc;
+    (void)workspace;  // the operands are split in shared memory: no scratch tensor
+    if ((uintptr_t)flt_split & 15)
+        return set_error(ST_INVALID_LAYOUT, "the filter must be 16-byte aligned");
 
     const int rowb = a.ic == 16 ? 64 : 128;
     const int chans = rowb / 4;
@@ -699,11 +712,11 @@ int launch_conv_f32_umma(
     const bool a_tiled = plain_matrix(a);
     CUtensorMap map_a, map_b;
     if (a_tiled) {
-        cuuint64_t dims[2] = {(cuuint64_t)a.ic, (cuuint64_t)2 * a.m};
+        cuuint64_t dims[2] = {(cuuint64_t)a.ic, (cuuint64_t)a.m};
         cuuint64_t strides[1] = {(cuuint64_t)a.ic * 4};
         cuuint32_t box[2] = {(cuuint32_t)chans, (cuuint32_t)kBM};
         cuuint32_t estr[2] = {1, 1};
-        CUresult r = api.tiled(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)hi, dims, strides,
+        CUresult r = api.tiled(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)src, dims, strides,
                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -711,13 +724,13 @@ int launch_conv_f32_umma(
             return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(f32 activation) failed: %d", (int)r);
     } else {
         cuuint64_t dims[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw, (cuuint64_t)a.ih,
-                              (cuuint64_t)2 * a.n};
+                              (cuuint64_t)a.n};
         cuuint64_t strides[3] = {(cuuint64_t)a.ic * 4, (cuuint64_t)a.iw * a.ic * 4,
                                  (cuuint64_t)a.ih * a.iw * a.ic * 4};
         int lower[2] = {-a.pw, -a.ph};
         int upper[2] = {(a.ow - 1) * a.sw - a.pw - (a.iw - 1), (a.oh - 1) * a.sh - a.ph - (a.ih - 1)};
         cuuint32_t estr[4] = {1, (cuuint32_t)a.sw, (cuuint32_t)a.sh, 1};
-        CUresult r = api.im2col(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)hi, dims, strides,
+        CUresult r = api.im2col(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)src, dims, strides,
                                 lower, upper, chans, kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -745,8 +758,8 @@ int launch_conv_f32_umma(
     p.cblocks = a.ic / chans;
     p.taps_w = a.kw;
     p.k_iters = taps * p.cblocks;
-    // four K = 8 steps per TMEM accumulation chain
-    p.seg_iters = 4 / (rowb / 32);
+    // eight K = 8 steps per TMEM accumulation chain
+    p.seg_iters = 8 / (rowb / 32);
     p.sh = a.sh;
     p.sw = a.sw;
     p.base_h = -a.ph;
@@ -754,7 +767,6 @@ int launch_conv_f32_umma(
     p.m_tiles = (a.m + kBM - 1) / kBM;
     p.n_tiles = (a.oc + bn - 1) / bn;
     p.a_tiled = a_tiled ? 1 : 0;
-    p.a_lo_offset = a_tiled ? a.m : a.n;
     p.b_lo_offset = a.oc;
     p.ep.oc = a.oc;
     p.ep.act = a.act;

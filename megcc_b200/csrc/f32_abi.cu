@@ -114,14 +114,14 @@ int mb200_conv_bias_f32_nhwc(
          (uintptr_t)z) & 3)
         return set_error(ST_INVALID_LAYOUT, "fp32 operands must be 4-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
-    const bool umma_ok = split_eligible(a) && conv_f32_umma_supported(a, src, dst) && workspace &&
+    const bool umma_ok = split_eligible(a) && conv_f32_umma_supported(a, src, dst) &&
                          workspace_bytes >= conv_f32_workspace_bytes(a) &&
                          (((uintptr_t)workspace | (uintptr_t)flt_packed | (uintptr_t)bias |
                            (uintptr_t)z) & 15) == 0;
     if (algo == MB200_ALGO_UMMA && !umma_ok)
         return set_error(ST_NO_IMPLEMENT,
                          "tensor-core fp32 ConvBias needs a dense filter, ic == 16 or ic %% 32 == 0, "
-                         "16-byte aligned operands, >= 128 KiB of input and its workspace");
+                         "16-byte aligned operands and >= 128 KiB of input");
     if (algo == MB200_ALGO_UMMA || (algo == MB200_ALGO_AUTO && umma_ok))
         return launch_conv_f32_umma(
                 a, src, (const float*)((const uint8_t*)flt_packed + plain_filter_bytes(a)), bias, z,
