@@ -315,36 +315,70 @@ def other_configs(local_rank, rates):
     return out
 
 
+class HostBuffer:
+    """Page-locked host memory from cudaHostAlloc, optionally write-combined (the CPU writes it
+    once, the GPU's copy engine reads it without snooping the CPU caches)."""
+
+    def __init__(self, nbytes, write_combined):
+        import ctypes as C
+        self._rt = C.CDLL("libcudart.so.12")
+        self._rt.cudaHostAlloc.argtypes = [C.POINTER(C.c_void_p), C.c_size_t, C.c_uint]
+        self._rt.cudaFreeHost.argtypes = [C.c_void_p]
+        p = C.c_void_p()
+        rc = self._rt.cudaHostAlloc(C.byref(p), nbytes, 0x04 if write_combined else 0)
+        if rc != 0 or not p.value:
+            raise RuntimeError(f"cudaHostAlloc failed: {rc}")
+        self.ptr, self.nbytes = p.value, nbytes
+
+    def fill(self, array):
+        import ctypes as C
+        C.memmove(self.ptr, array.ctypes.data, min(self.nbytes, array.nbytes))
+
+    def close(self):
+        if self.ptr:
+            self._rt.cudaFreeHost(self.ptr)
+            self.ptr = None
+
+
 def h2d_probe(group, local_rank, nbytes):
-    """Host-to-device copy bandwidth of this rank's pinned staging buffer, every rank alone (the
+    """Host-to-device copy bandwidth of a rank's pinned staging buffer, every rank alone (the
     others idle) and all ranks together: the end-to-end arm is bound by it at 4 and 8 GPUs.
-    Also a write-combined pinned buffer on rank 0. GB/s per rank."""
+    The same with write-combined pinned memory. GB/s per rank."""
     import ctypes as C
 
     import torch
+    rt = C.CDLL("libcudart.so.12")
+    rt.cudaMemcpyAsync.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
     dst = torch.empty(nbytes, dtype=torch.int8, device=f"cuda:{local_rank}")
-    src = torch.empty(nbytes, dtype=torch.int8).pin_memory()
+    stream = torch.cuda.current_stream()
 
-    def rate(s):
+    def rate(buf):
+        def copy():
+            rt.cudaMemcpyAsync(dst.data_ptr(), buf.ptr, nbytes, 1, stream.cuda_stream)
         for _ in range(2):
-            dst.copy_(s, non_blocking=True)
+            copy()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(8):
-            dst.copy_(s, non_blocking=True)
+            copy()
         e1.record()
         torch.cuda.synchronize()
         return 8 * nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9
 
-    alone = 0.0
-    for r in range(group.world):
+    out = dict(bytes=nbytes)
+    for tag, wc in (("", False), ("wc_", True)):
+        buf = HostBuffer(nbytes, wc)
+        alone = 0.0
+        for r in range(group.world):
+            group.barrier()
+            if r == group.rank:
+                alone = rate(buf)
         group.barrier()
-        if r == group.rank:
-            alone = rate(src)
-    group.barrier()
-    together = rate(src)
-    out = dict(bytes=nbytes, alone_gbs_min=-group.max(-alone), alone_gbs_max=group.max(alone),
-               together_gbs_min=-group.max(-together), together_gbs_sum=group.sum(together))
+        together = rate(buf)
+        out.update({f"alone_{tag}gbs_min": -group.max(-alone), f"alone_{tag}gbs_max": group.max(alone),
+                    f"together_{tag}gbs_min": -group.max(-together),
+                    f"together_{tag}gbs_sum": group.sum(together)})
+        buf.close()
     return out
 
 
