@@ -224,9 +224,12 @@ struct F32Smem {
     static constexpr int kDynamic = kTotal + 1024;
 };
 
-constexpr int kF32EpilogueWarps = 8;
+// Eight epilogue warps (two 32-column chunks each for BN = 128). Sixteen, one chunk each,
+// halve a warp's chain of dependent TMEM loads per hand-over, but measured no faster on the
+// ConvBias layers and 10 % slower on the 4096^3 MatrixMul.
+__host__ __device__ constexpr int f32_epilogue_warps(int bn) { return bn >= 64 ? 8 : 8; }
 constexpr int kF32ConvertWarps = 4;
-constexpr int kF32Threads = 64 + 32 * kF32EpilogueWarps + 32 * kF32ConvertWarps;
+__host__ __device__ constexpr int f32_threads(int bn) { return 64 + 32 * f32_epilogue_warps(bn) + 32 * kF32ConvertWarps; }
 
 // v = hi + lo with both halves exact tf32 values (which way a tie rounds does not matter:
 // v - hi is exact, and lo is its nearest tf32)
@@ -239,12 +242,13 @@ __device__ __forceinline__ void split_tf32(float v, float& hi, float& lo) {
 }
 
 template <int BN, int ROWB>
-__global__ void __launch_bounds__(kF32Threads, 1) conv_f32_umma_kernel(
+__global__ void __launch_bounds__(f32_threads(BN), 1) conv_f32_umma_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const F32ConvParams p) {
     using L = F32Smem<BN, ROWB>;
     constexpr int kSt = L::kStages;
     constexpr int kChans = ROWB / 4;  // floats per row
+    constexpr int kF32EpilogueWarps = f32_epilogue_warps(BN);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(smem + L::kBarOff);
@@ -611,6 +615,7 @@ int launch_f32_kernel(
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              L::kDynamic) != cudaSuccess)
         return check_launch("conv_f32_umma smem attribute");
+    constexpr int kF32Threads = f32_threads(BN);
     const int per_sm = resident_ctas_per_sm(conv_f32_umma_kernel<BN, ROWB>, kF32Threads,
                                             L::kDynamic, 4 * BN);
     const int total = p.m_tiles * p.n_tiles;

@@ -6,6 +6,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#ifndef MB200_WAIT_SLEEP_CAP
+#define MB200_WAIT_SLEEP_CAP 160
+#endif
 namespace mb200 {
 namespace umma {
 
@@ -69,7 +72,7 @@ __device__ __forceinline__ bool mbar_wait(
         if (mbar_try_wait(bar, parity))
             return true;
         __nanosleep(ns);
-        if (ns < 160)
+        if (ns < MB200_WAIT_SLEEP_CAP)
             ns *= 2;
         if ((spin & 63) == 63) {
             if (*abort_flag)
