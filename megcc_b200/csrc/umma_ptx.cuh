@@ -6,6 +6,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#ifndef MB200_TRY_WAIT_HINT_NS
+#define MB200_TRY_WAIT_HINT_NS 2000
+#endif
 #ifndef MB200_WAIT_SLEEP_CAP
 #define MB200_WAIT_SLEEP_CAP 160
 #endif
@@ -49,7 +52,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)
+            : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)MB200_TRY_WAIT_HINT_NS)
             : "memory");
     return ok != 0;
 }
