@@ -655,6 +655,10 @@ int launch_conv_umma_geom(
             bn = 256;
         if (force == 128 && a.oc > 64)
             bn = 128;
+        // A short K loop leaves the kernel to its epilogue warps: 64-column tiles hold half
+        // the TMEM, so three CTAs (24 epilogue warps) fit an SM instead of two
+        if (force == 64 || (force == 0 && k_bytes <= 256 && bn == 128))
+            bn = 64;
     }
     const CUtensorMapSwizzle swz = geom == GEOM_WIDE128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                    : geom == GEOM_WIDE  ? CU_TENSOR_MAP_SWIZZLE_64B
