@@ -12,6 +12,7 @@
 // The tables come from the generated kernels.c of the compile side when the caller registered
 // one (mb200_lite_set_kernel_tables); entries nobody registered are filled once at load time
 // with the library's own implementations, selected by the Opr's symbol.
+#include <algorithm>
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -148,8 +149,15 @@ struct DevModel {
     std::vector<Instr> instrs;
     std::vector<IoSlot> inputs, outputs;
     size_t tensor_memory = 0;
-    cudaGraphExec_t exec = nullptr;
-    std::vector<void*> captured_inputs;
+    // instantiated graphs, one per set of input addresses (device pointers are baked into the
+    // captured kernels): a caller that cycles a few device buffers replays, it does not
+    // re-capture. Most recently used first, at most kMaxGraphs.
+    struct CapturedGraph {
+        std::vector<void*> inputs;
+        cudaGraphExec_t exec;
+    };
+    static constexpr size_t kMaxGraphs = 4;
+    std::vector<CapturedGraph> graphs;
     bool memory_ready = false;
     bool ran_eager = false;
 };
@@ -1487,11 +1495,20 @@ int forward(Network* net) {
                 return rc;
             m.ran_eager = true;
         } else {
-            if (m.exec && in_ptrs != m.captured_inputs) {
-                cudaGraphExecDestroy(m.exec);
-                m.exec = nullptr;
-            }
-            if (!m.exec) {
+            size_t hit = m.graphs.size();
+            for (size_t i = 0; i < m.graphs.size(); ++i)
+                if (m.graphs[i].inputs == in_ptrs) {
+                    hit = i;
+                    break;
+                }
+            if (hit < m.graphs.size()) {
+                if (hit != 0)
+                    std::rotate(m.graphs.begin(), m.graphs.begin() + hit, m.graphs.begin() + hit + 1);
+            } else {
+                if (m.graphs.size() >= DevModel::kMaxGraphs) {  // drop the least recently used
+                    cudaGraphExecDestroy(m.graphs.back().exec);
+                    m.graphs.pop_back();
+                }
                 cudaGraph_t graph = nullptr;
                 if ((e = cudaStreamBeginCapture(net->stream, cudaStreamCaptureModeThreadLocal)) !=
                     cudaSuccess)
@@ -1505,13 +1522,14 @@ int forward(Network* net) {
                 }
                 if (e != cudaSuccess)
                     return cuda_fail(e, "cudaStreamEndCapture");
-                e = cudaGraphInstantiate(&m.exec, graph, 0);
+                cudaGraphExec_t exec = nullptr;
+                e = cudaGraphInstantiate(&exec, graph, 0);
                 cudaGraphDestroy(graph);
                 if (e != cudaSuccess)
                     return cuda_fail(e, "cudaGraphInstantiate");
-                m.captured_inputs = in_ptrs;
+                m.graphs.insert(m.graphs.begin(), DevModel::CapturedGraph{in_ptrs, exec});
             }
-            if ((e = cudaGraphLaunch(m.exec, net->stream)) != cudaSuccess)
+            if ((e = cudaGraphLaunch(m.graphs.front().exec, net->stream)) != cudaSuccess)
                 return cuda_fail(e, "cudaGraphLaunch");
         }
     }
@@ -1930,8 +1948,9 @@ int LITE_destroy_network(LiteNetwork network) {
                 if (ins.is_opr && ins.op.ms_count)
                     log_at(LITE_WARN, "profile %-90s %8.4f ms\n", ins.op.symbol.c_str(),
                            ins.op.ms_total / ins.op.ms_count);
-        if (m.exec)
-            cudaGraphExecDestroy(m.exec);
+        for (auto& g : m.graphs)
+            cudaGraphExecDestroy(g.exec);
+        m.graphs.clear();
         for (auto& o : m.outputs)
             if (o.host_stage)
                 cudaFreeHost(o.host_stage);
