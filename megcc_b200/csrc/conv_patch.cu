@@ -212,7 +212,7 @@ __device__ __forceinline__ void issue_tile_mmas_rows64(uint64_t a0, uint64_t b0,
 }
 
 template <int BN, int KH, int KW, int CHUNKS, int EW, int ROWS = 0, int POOL = 0>
-__global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 3) conv_patch_kernel(
+__global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 2) conv_patch_kernel(
         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const PatchParams p) {
     static_assert(POOL == 0 || (BN == 64 && EW == 8 && ROWS == 0), "pooled form: 64 channels");
