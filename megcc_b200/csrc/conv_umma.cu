@@ -57,7 +57,7 @@ struct Shape {
     static constexpr int kEpilogueWarps = BN == 256 ? 16 : 8;
     static constexpr int kEpilogueThreads = 32 * kEpilogueWarps;
     static constexpr int kThreads = 64 + kEpilogueThreads;
-    static constexpr int kMinCtas = BN == 256 ? 1 : 3;
+    static constexpr int kMinCtas = BN == 256 ? 1 : 2;
 };
 
 // K bytes and pipeline depth per geometry. WIDE128 moves 128-channel rows (128-byte swizzle):
