@@ -96,6 +96,7 @@ const TuningField kTuningFields[] = {
         {"patch_ctas", "MB200_PATCH_CTAS", &Tuning::patch_ctas, false},
         {"patch_alone", "MB200_PATCH_ALONE", &Tuning::patch_alone, false},
         {"patch_plain", "MB200_PATCH_PLAIN", &Tuning::patch_plain, false},
+        {"dw_tensor", "MB200_DW_TENSOR", &Tuning::dw_tensor, false},
         {"dw_out", "MB200_DW_OUT", &Tuning::dw_out, false},
         {"dw_one_output", "MB200_DW_ONE_OUTPUT", &Tuning::dw_one_output, false},
         {"fast_requant", "MB200_NO_FAST_REQUANT", &Tuning::fast_requant, true},
@@ -198,7 +199,7 @@ bool readable_through(const void* p, size_t bytes) {
 
 int descriptor_images(const ConvArgs& a, const int8_t* src) {
     constexpr size_t kMinMapBytes = 131072;
-    const size_t image = (size_t)a.ih * a.iw * a.ic;
+    const size_t image = (size_t)a.ih * a.iw * (a.dw64 ? a.oc : a.ic);  // (dw64: a.ic is a slice)
     if ((size_t)a.n * image >= kMinMapBytes)
         return a.n;
     const size_t images = (kMinMapBytes + image - 1) / image;
@@ -401,7 +402,13 @@ int mb200_conv_bias_qs8_nhwc_fused(
         return launch_conv_umma(a, src, flt_packed, bias, flt_scales, dst, st);
     if (algo != MB200_ALGO_AUTO && algo != MB200_ALGO_DIRECT)
         return set_error(ST_OUT_OF_RANGE, "unknown algo %d", algo);
-    // depthwise 3x3: bandwidth-bound, vector loads and dp4a over taps
+    // depthwise 3x3 / stride 1 over whole 64-channel slices: the halo-patch tensor-core kernel
+    // with a block-diagonal filter (63 of 64 MACs multiply zeros, and it is still the faster
+    // form: the CUDA-core kernel below is bound by instruction issue)
+    if (algo == MB200_ALGO_AUTO && side_ok && tuning().dw_tensor &&
+        conv_patch_dw_supported(a, src, flt_packed, dst))
+        return launch_conv_patch_dw(a, src, flt_packed, bias, flt_scales, dst, st);
+    // depthwise 3x3: vector loads and dp4a over taps
     if (algo == MB200_ALGO_AUTO && side_ok && conv_dw_supported(a, src, flt_packed, dst))
         return launch_conv_dw(a, src, flt_packed, bias, flt_scales, dst, st);
     return launch_conv_direct(a, src, flt_packed, bias, flt_scales, dst, nullptr, st);

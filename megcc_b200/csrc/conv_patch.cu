@@ -71,6 +71,9 @@ struct PatchParams {
     int a_flat16;       // 16 input channels: the activation map is {W * 16 bytes, H, N}
     int mma_per_tap;  // k-steps per tap (C/32), or 0 when C == 16 (two taps per k-step)
     int a_lbo;        // distance between the two 16-byte K halves of one A operand
+    // Depthwise form (64-channel rows kernel only): the raw filter [C][3][3]. Each CTA then
+    // convolves input channels n0 .. n0+63 with the block-diagonal operand it builds itself.
+    const int8_t* dw_flt;
     EpilogueParams ep;
     int8_t* dst;
     int* status;
@@ -259,6 +262,26 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 2) conv_patch_ker
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if constexpr (ROWS != 0) {
+        if (p.dw_flt) {
+            // Depthwise 3x3 as a dense 64 -> 64 convolution of this CTA's channel slice with
+            // a block-diagonal filter: tap t is the [64 oc][64 ic] tile whose only non-zero
+            // bytes are w[n0 + c][t] at (c, c). Written here in the layout the TMA would have
+            // produced (rows of 64 bytes, 64-byte swizzle: 16-byte unit u of row r sits at
+            // unit u ^ ((r >> 1) & 3)), then handed to the tensor core's (async) proxy.
+            uint4* b16 = reinterpret_cast<uint4*>(smem_b);
+            for (int i = threadIdx.x; i < 9 * BN * 4; i += blockDim.x)
+                b16[i] = make_uint4(0, 0, 0, 0);
+            __syncthreads();
+            for (int i = threadIdx.x; i < 9 * BN; i += blockDim.x) {
+                const int t = i / BN, c = i - t * BN;
+                const int unit = (c >> 4) ^ ((c >> 1) & 3);
+                smem_b[t * (BN * 64) + c * 64 + unit * 16 + (c & 15)] =
+                        (uint8_t)p.dw_flt[(size_t)(n0 + c) * 9 + t];
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+    }
     if (warp == 1) {
         asm volatile(
                 "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -279,15 +302,19 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 2) conv_patch_ker
             // the filter slice, once: one [BN][16-byte] block per 16 bytes of K (weights: they
             // do not depend on the kernel before this one, so they are fetched before the wait)
             const int kchunks = p.kh * p.kw * p.chunks;
-            mbar_expect_tx(b_full, (uint32_t)p.b_bytes);
-            if (ROWS) {
+            if (ROWS && p.dw_flt) {
+                mbar_arrive(b_full);  // the operand was built in place before the roles split
+            } else if (ROWS) {
+                mbar_expect_tx(b_full, (uint32_t)p.b_bytes);
                 // one swizzled [BN][64-byte] tile per filter tap
                 for (int t = 0; t < p.kh * p.kw; ++t)
                     tma_load_2d(smem_b + t * (BN * 64), &map_b, b_full, t * 64, n0);
             } else if (p.b_single_load) {
                 // 3-D view {16 bytes, rows, K/16}: one request lays down every block
+                mbar_expect_tx(b_full, (uint32_t)p.b_bytes);
                 tma_load_3d(smem_b, &map_b, b_full, 0, n0, 0);
             } else {
+                mbar_expect_tx(b_full, (uint32_t)p.b_bytes);
                 for (int kc = 0; kc < kchunks; ++kc)
                     tma_load_2d(smem_b + kc * (BN * 16), &map_b, b_full, kc * 16, n0);
             }
@@ -307,8 +334,10 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 2) conv_patch_ker
                 const int x0 = at.tx * kStepX + kOrigin - p.pw, y0 = at.ty * kStepY + kOrigin - p.ph;
                 mbar_expect_tx(&a_full[s], (uint32_t)p.a_tx_bytes);
                 if (ROWS) {
-                    // one request: box {64 B, 16 columns, patch rows, 1 image}
-                    tma_load_4d(smem_a + s * p.a_stage_bytes, &map_a, &a_full[s], 0, x0, y0, img);
+                    // one request: box {64 B, 16 columns, patch rows, 1 image} (depthwise
+                    // form: this CTA's 64 input channels)
+                    tma_load_4d(smem_a + s * p.a_stage_bytes, &map_a, &a_full[s], p.dw_flt ? n0 : 0,
+                                x0, y0, img);
                 } else if (p.a_flat16) {
                     // 16 channels: a patch row is contiguous in memory, one box row of
                     // (patch columns x 16) bytes instead of one 16-byte row per pixel (the
@@ -593,11 +622,13 @@ PatchPlan plan_patch(const ConvArgs& a) {
     const int pph = kTH + a.kh - 1, ppw = kTW + a.kw - 1;
     if (pph > 256 || ppw > 256)
         return pl;
-    pl.bn = a.oc <= 64 ? 64 : 128;
+    pl.bn = (a.oc <= 64 || a.dw64) ? 64 : 128;
     if (a.pool && (pl.bn != 64 || a.oc % 16 != 0))
         return pl;
-    pl.rows64 = a.ic == 64 && a.kh == 3 && a.kw == 3 && pl.bn == 64 && !tuning().patch_plain &&
-                !a.pool;
+    pl.rows64 = a.ic == 64 && a.kh == 3 && a.kw == 3 && pl.bn == 64 &&
+                (!tuning().patch_plain || a.dw64) && !a.pool;
+    if (a.dw64 && (!pl.rows64 || a.oc % 64 != 0 || a.acc_out))
+        return pl;
     pl.plane_stride = pph * ppw * 16;
     // a TMA destination in shared memory must be 128-byte aligned: pad the stage
     pl.a_stage_bytes = ((a.ic / 16) * pl.plane_stride + 127) / 128 * 128;
@@ -708,10 +739,11 @@ int launch_conv_patch(
         return set_error(ST_INVALID_LAYOUT, "activation below 128 KiB outside a registered range");
     CUtensorMap map_a, map_b;
     if (pl.rows64) {
-        cuuint64_t dims[4] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw, (cuuint64_t)a.ih,
-                              (cuuint64_t)images};
-        cuuint64_t strides[3] = {(cuuint64_t)a.ic, (cuuint64_t)a.iw * a.ic,
-                                 (cuuint64_t)a.ih * a.iw * a.ic};
+        // (depthwise form: the tensor has a.oc channels, a box covers the CTA's 64)
+        const cuuint64_t src_c = a.dw64 ? (cuuint64_t)a.oc : (cuuint64_t)a.ic;
+        cuuint64_t dims[4] = {src_c, (cuuint64_t)a.iw, (cuuint64_t)a.ih, (cuuint64_t)images};
+        cuuint64_t strides[3] = {src_c, (cuuint64_t)a.iw * src_c,
+                                 (cuuint64_t)a.ih * a.iw * src_c};
         cuuint32_t box[4] = {64, (cuuint32_t)kRowCols, (cuuint32_t)pph, 1};
         cuuint32_t estr[4] = {1, 1, 1, 1};
         CUresult r = api.tiled(
@@ -720,6 +752,9 @@ int launch_conv_patch(
                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS)
             return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(activation) failed: %d", (int)r);
+        if (a.dw64) {
+            map_b = map_a;  // unused: the kernel builds the filter tile itself
+        } else {
         const cuuint64_t k_total = (cuuint64_t)a.kh * a.kw * a.ic;
         cuuint64_t bdims[2] = {k_total, (cuuint64_t)a.oc};
         cuuint64_t bstrides[1] = {k_total};
@@ -731,6 +766,7 @@ int launch_conv_patch(
                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS)
             return set_error(ST_RUNTIME, "cuTensorMapEncodeTiled(filter) failed: %d", (int)r);
+        }
     } else if (a.ic == 16) {
         // one chunk: [row][column][16 bytes] is the tensor's own order, so a patch row is one
         // contiguous box row of ppw * 16 bytes
@@ -855,6 +891,7 @@ int launch_conv_patch(
                 p.ep.z_fast_a,
                 p.ep.z_fast_b);
     p.ep.acc_out = a.acc_out;
+    p.dw_flt = a.dw64 ? flt : nullptr;
     p.dst = dst;
     p.status = device_status_word(st);
     if (!p.status)
@@ -888,6 +925,39 @@ int launch_conv_patch(
         rc = alone ? launch_patch<128, 0, 0, 0, 16>(map_a, map_b, p, pl.smem_bytes, grid, st)
                    : launch_patch<128, 0, 0, 0, 8>(map_a, map_b, p, pl.smem_bytes, grid, st);
     return rc;
+}
+
+// ---- depthwise 3x3 / stride 1 as 64-channel block-diagonal slices ----
+namespace {
+// the dense view the halo-patch kernel works on
+ConvArgs dw_dense_view(const ConvArgs& a) {
+    ConvArgs t = a;
+    t.groups = 1;
+    t.ic = 64;
+    t.dw64 = 1;
+    return t;
+}
+}  // namespace
+
+bool conv_patch_dw_supported(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst) {
+    if (a.groups != a.ic || a.oc != a.ic || a.ic % 64 != 0 || a.kh != 3 || a.kw != 3)
+        return false;
+    if (a.pool || a.acc_out)
+        return false;
+    const ConvArgs t = dw_dense_view(a);
+    // partial 16 x 8 patches are paid for in full
+    return conv_patch_supported(t, src, src, dst) && flt != nullptr &&
+           conv_patch_efficiency(t) >= 0.75f;
+}
+
+int launch_conv_patch_dw(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
+        const float* flt_scales, int8_t* dst, cudaStream_t st) {
+    if (!conv_patch_dw_supported(a, src, flt, dst))
+        return set_error(ST_NO_IMPLEMENT, "tensor-core depthwise ConvBias does not apply to this "
+                                          "shape");
+    return launch_conv_patch(dw_dense_view(a), src, flt, bias, flt_scales, dst, st);
 }
 
 }  // namespace mb200

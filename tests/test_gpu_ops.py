@@ -343,6 +343,11 @@ DW_CASES = [
     ("mbv1_7_c1024", 2, 1024, 7, 7, 1, 1, "IDENTITY", True),
     ("odd_hw_nopad", 2, 48, 13, 17, 1, 0, "H_SWISH", False),
     ("odd_hw_s2_pad2", 1, 16, 15, 11, 2, 2, "RELU", False),
+    # stride 1 over whole 64-channel slices: the tensor-core form (block-diagonal filter)
+    ("tc_56_c128", 2, 128, 56, 56, 1, 1, "RELU", False),
+    ("tc_28_c256_identity", 2, 256, 28, 28, 1, 1, "IDENTITY", False),
+    ("tc_30x24_c64_nopad", 3, 64, 30, 24, 1, 0, "H_SWISH", True),
+    ("tc_partial_patches_c192", 2, 192, 27, 23, 1, 1, "RELU", True),
 ]
 
 
@@ -392,6 +397,26 @@ def test_depthwise_3x3_matches_oracle(ops, oracle, case):
     ref, _ = run_conv_nchw(ops, c, algo="direct", flt_scales=scales)
     assert (ref == want).all()
     assert (np.abs(want.astype(int)) < 127).mean() > 0.3
+
+
+@pytest.mark.parametrize("case", [DW_CASES[2], DW_CASES[6]], ids=["c512_14", "c128_56"])
+def test_depthwise_stride1_on_cuda_cores(ops, oracle, case, tune):
+    """The shapes the tensor-core depthwise form takes by default, through the CUDA-core
+    kernel (dw_tensor = 0): both stay bit-exact against the oracle."""
+    tune("dw_tensor", 0)
+    name, n, ch, h, w, stride, pad, act, per_channel = case
+    c = dict(name="dw_" + name, n=n, ic=ch, oc=ch, h=h, w=w, k=3, stride=stride, pad=pad,
+             groups=ch, act=act, range=(-128, 127), bias_range=(-1000, 1000),
+             scales=(0.05, 0.01, 0.06))
+    src, flt, bias = cases.conv_inputs(c)
+    s0, s1, s2 = c["scales"]
+    scales = None
+    if per_channel:
+        scales = cases.rng_for("dw_scales_" + name).uniform(0.005, 0.02, ch).astype(np.float32)
+    out, _ = run_conv_nchw(ops, c, algo="auto", flt_scales=scales)
+    want = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, scales if per_channel else s1,
+                                s2, act, groups=ch)
+    assert (out == want).all()
 
 
 FUSED_CASES = [
