@@ -384,6 +384,14 @@ int mb200_conv_bias_qs8_nhwc_fused(
     // ... and divide by a constant in three instructions, which is exact inside a scale range
     const bool side_ok =
             ((((uintptr_t)bias | (uintptr_t)flt_scales) & 15) == 0) && !a.true_division;
+    if (algo == MB200_ALGO_PATCH && a.groups > 1) {
+        // a depthwise ConvBias asked onto the halo-patch kernel: its block-diagonal form
+        if (!side_ok || !conv_patch_dw_supported(a, src, flt_packed, dst, true))
+            return set_error(ST_NO_IMPLEMENT,
+                             "halo-patch depthwise ConvBias needs 3x3, stride 1, channels %% 64 "
+                             "== 0, NHWC, 16-byte aligned tensors and >= 128 KiB of input");
+        return launch_conv_patch_dw(a, src, flt_packed, bias, flt_scales, dst, st);
+    }
     const bool patch_ok = side_ok && conv_patch_supported(a, src, flt_packed, dst);
     if (algo == MB200_ALGO_PATCH && !patch_ok)
         return set_error(ST_NO_IMPLEMENT,

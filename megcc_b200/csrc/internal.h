@@ -121,8 +121,11 @@ int launch_conv_umma(
 bool conv_patch_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst);
 // Depthwise 3x3 / stride 1 over a multiple of 64 channels on the tensor cores: the halo-patch
 // kernel with a block-diagonal filter built on chip. `a` is the depthwise convolution itself
-// (groups == ic == oc), `flt` its packed filter [C][3][3].
-bool conv_patch_dw_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst);
+// (groups == ic == oc), `flt` its packed filter [C][3][3]. `whatever_the_size`: leave out the
+// two checks that only say whether it pays (enough patches per CTA, few partial patches).
+bool conv_patch_dw_supported(
+        const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst,
+        bool whatever_the_size = false);
 int launch_conv_patch_dw(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int32_t* bias,
         const float* flt_scales, int8_t* dst, cudaStream_t st);

@@ -348,6 +348,7 @@ DW_CASES = [
     ("tc_28_c256_identity", 2, 256, 28, 28, 1, 1, "IDENTITY", False),
     ("tc_30x24_c64_nopad", 3, 64, 30, 24, 1, 0, "H_SWISH", True),
     ("tc_partial_patches_c192", 2, 192, 27, 23, 1, 1, "RELU", True),
+    ("auto_tc_14_c512", 64, 512, 14, 14, 1, 1, "RELU", False),   # 1024 patches: "auto" takes it
 ]
 
 
@@ -389,7 +390,9 @@ def test_depthwise_3x3_matches_oracle(ops, oracle, case):
     scales = None
     if per_channel:
         scales = cases.rng_for("dw_scales_" + name).uniform(0.005, 0.02, ch).astype(np.float32)
-    out, _ = run_conv_nchw(ops, c, algo="auto", flt_scales=scales)
+    # "tc_" cases: the tensor-core form by name ("auto" takes it from 888 patches up only)
+    out, _ = run_conv_nchw(ops, c, algo="patch" if name.startswith("tc_") else "auto",
+                           flt_scales=scales)
     want = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, scales if per_channel else s1,
                                 s2, act, groups=ch)
     bad = int((out != want).sum())
