@@ -430,6 +430,7 @@ FUSED_CASES = [
     ("umma_oc76", 2, 64, 76, 40, 40, 3, 1, 1, "umma"),    # byte stores
     ("umma_256_wide", 4, 256, 256, 14, 14, 3, 1, 1, "umma"),
     ("direct_dw", 2, 32, 32, 20, 20, 3, 1, 1, "direct"),
+    ("patch_dw", 2, 128, 128, 40, 36, 3, 1, 1, "patch"),   # depthwise, block-diagonal form
 ]
 
 
@@ -442,7 +443,7 @@ def test_conv_with_fused_residual_step_matches_two_oracle_kernels(ops, oracle, c
     name, n, ic, oc, h, w, k, stride, pad, algo = case
     if name == "umma_256_wide":
         tune("conv_bn", 256)
-    groups = ic if name == "direct_dw" else 1
+    groups = ic if name.endswith("_dw") else 1
     c = dict(name="fused_" + name, n=n, ic=ic, oc=oc, h=h, w=w, k=k, stride=stride, pad=pad,
              groups=groups, act="IDENTITY", range=(-128, 127), bias_range=(-1000, 1000),
              scales=(0.05, 0.01, 0.3 * (ic // groups * k * k / 576.0) ** 0.5 + 0.1))
