@@ -233,12 +233,13 @@ def test_resnet18_at_the_benchmarked_and_sharded_batch_sizes(lite, oracle, batch
     _sampled_parity(lite, oracle, zoo.resnet18(), batch, f"resnet18_b{batch}")
 
 
-@pytest.mark.parametrize("batch", [1, 64])
+@pytest.mark.parametrize("batch", [1, 64, 256])
 @pytest.mark.parametrize("per_channel", [False, True])
 def test_mobilenet_v1_at_the_benchmarked_batch_sizes(lite, oracle, batch, per_channel):
-    """MobileNetV1 at batch 1 (latency) and 64, with one filter scale per tensor and with one
-    per output channel (the form the configuration names; an extension over the reference,
-    checked against the same formula with flt_scale[oc])."""
+    """MobileNetV1 at batch 1 (latency), 64 and 256, with one filter scale per tensor and with
+    one per output channel (the form the configuration names; an extension over the reference,
+    checked against the same formula with flt_scale[oc]). From batch 64 up the stride-1
+    depthwise layers over 128, 256 and 512 channels run on the tensor cores."""
     from megcc_b200 import zoo
     _sampled_parity(lite, oracle, zoo.mobilenet_v1(per_channel=per_channel), batch,
                     f"mbv1_b{batch}_{per_channel}")
