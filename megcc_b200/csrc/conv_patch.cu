@@ -74,6 +74,9 @@ struct PatchParams {
     // Depthwise form (64-channel rows kernel only): the raw filter [C][3][3]. Each CTA then
     // convolves input channels n0 .. n0+63 with the block-diagonal operand it builds itself.
     const int8_t* dw_flt;
+    // 1: the depthwise tensor has 32 channels and is seen as pixel PAIRS of 64 bytes
+    // ([N][H][W/2][2][32]); column 32 h + c of a row is channel c of the pair's pixel h
+    int dw_pairs;
     EpilogueParams ep;
     int8_t* dst;
     int* status;
@@ -274,10 +277,26 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 2) conv_patch_ker
                 b16[i] = make_uint4(0, 0, 0, 0);
             __syncthreads();
             for (int i = threadIdx.x; i < 9 * BN; i += blockDim.x) {
-                const int t = i / BN, c = i - t * BN;
-                const int unit = (c >> 4) ^ ((c >> 1) & 3);
-                smem_b[t * (BN * 64) + c * 64 + unit * 16 + (c & 15)] =
-                        (uint8_t)p.dw_flt[(size_t)(n0 + c) * 9 + t];
+                const int t = i / BN, c = i - t * BN;  // tap, output column (tile row)
+                uint8_t* row = smem_b + t * (BN * 64) + c * 64;
+                const int swz = (c >> 1) & 3;
+                if (!p.dw_pairs) {
+                    row[(((c >> 4) ^ swz) << 4) + (c & 15)] =
+                            (uint8_t)p.dw_flt[(size_t)(n0 + c) * 9 + t];
+                } else {
+                    // Pixel pairs: output pixel ho of pair x sees input pixel hi of pair
+                    // x + fx - 1 through filter column dx = 2 (fx - 1) + hi - ho + 1.
+                    const int fy = t / 3, fx = t - fy * 3, ho = c >> 5, ch = c & 31;
+#pragma unroll
+                    for (int hi = 0; hi < 2; ++hi) {
+                        const int dx = 2 * (fx - 1) + hi - ho + 1;
+                        if (dx >= 0 && dx <= 2) {
+                            const int k = hi * 32 + ch;  // input column
+                            row[(((k >> 4) ^ swz) << 4) + (k & 15)] =
+                                    (uint8_t)p.dw_flt[ch * 9 + fy * 3 + dx];
+                        }
+                    }
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
@@ -553,7 +572,9 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 2) conv_patch_ker
                 }
                 const int ch0 = n0 + c * 32;
                 if (valid && ch0 < p.oc)
-                    epilogue_store<32>(v, p.ep, p.dst, px_off + ch0, ch0);
+                    // (pixel pairs: bias and channel scales are those of channel column % 32)
+                    epilogue_store<32>(v, p.ep, p.dst, px_off + ch0,
+                                       (ROWS != 0 && p.dw_pairs) ? (ch0 & 31) : ch0);
             };
             if constexpr (kChunksPerWarp == 1) {
                 // Written as a strided loop of (at run time) one trip: with the chunk's code
@@ -892,6 +913,7 @@ int launch_conv_patch(
                 p.ep.z_fast_b);
     p.ep.acc_out = a.acc_out;
     p.dw_flt = a.dw64 ? flt : nullptr;
+    p.dw_pairs = a.dw64 == 2 ? 1 : 0;
     p.dst = dst;
     p.status = device_status_word(st);
     if (!p.status)
@@ -935,6 +957,15 @@ ConvArgs dw_dense_view(const ConvArgs& a) {
     t.groups = 1;
     t.ic = 64;
     t.dw64 = 1;
+    if (a.ic == 32) {
+        // 32 channels: two horizontally adjacent pixels make one 64-byte "pixel"; with one
+        // pixel of padding the pair x needs pairs x - 1 .. x + 1, a 3-wide filter again
+        t.oc = 64;
+        t.iw = a.iw / 2;
+        t.ow = a.ow / 2;
+        t.m = a.n * a.oh * t.ow;
+        t.dw64 = 2;
+    }
     return t;
 }
 }  // namespace
@@ -942,7 +973,10 @@ ConvArgs dw_dense_view(const ConvArgs& a) {
 bool conv_patch_dw_supported(
         const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst,
         bool whatever_the_size) {
-    if (a.groups != a.ic || a.oc != a.ic || a.ic % 64 != 0 || a.kh != 3 || a.kw != 3)
+    if (a.groups != a.ic || a.oc != a.ic || a.kh != 3 || a.kw != 3)
+        return false;
+    // whole 64-channel slices, or 32 channels as pixel pairs (even widths, one pixel of padding)
+    if (a.ic % 64 != 0 && !(a.ic == 32 && a.iw % 2 == 0 && a.ow == a.iw && a.pw == 1))
         return false;
     if (a.pool || a.acc_out)
         return false;
@@ -950,8 +984,8 @@ bool conv_patch_dw_supported(
     // A CTA builds its filter tile and sets up TMEM and barriers before its first patch: with
     // fewer than three patches per resident CTA the CUDA-core kernel measured faster
     // (MobileNetV1 at batch 16 against batch 64).
-    const long long tiles = (long long)a.n * ((a.oh + kTH - 1) / kTH) * ((a.ow + kTW - 1) / kTW) *
-                            (a.oc / 64);
+    const long long tiles = (long long)t.n * ((t.oh + kTH - 1) / kTH) * ((t.ow + kTW - 1) / kTW) *
+                            (t.oc / 64);
     if (tiles < 6LL * sm_count() && !whatever_the_size)
         return false;
     // partial 16 x 8 patches are paid for in full

@@ -348,6 +348,9 @@ DW_CASES = [
     ("tc_28_c256_identity", 2, 256, 28, 28, 1, 1, "IDENTITY", False),
     ("tc_30x24_c64_nopad", 3, 64, 30, 24, 1, 0, "H_SWISH", True),
     ("tc_partial_patches_c192", 2, 192, 27, 23, 1, 1, "RELU", True),
+    # 32 channels: pixel pairs as 64-byte rows, two diagonals in the filter tile
+    ("tc_pairs_112_c32", 2, 32, 112, 112, 1, 1, "RELU", True),
+    ("tc_pairs_c32_20x36_identity", 8, 32, 20, 36, 1, 1, "IDENTITY", False),
     ("auto_tc_14_c512", 64, 512, 14, 14, 1, 1, "RELU", False),   # 1024 patches: "auto" takes it
 ]
 
@@ -431,6 +434,7 @@ FUSED_CASES = [
     ("umma_256_wide", 4, 256, 256, 14, 14, 3, 1, 1, "umma"),
     ("direct_dw", 2, 32, 32, 20, 20, 3, 1, 1, "direct"),
     ("patch_dw", 2, 128, 128, 40, 36, 3, 1, 1, "patch"),   # depthwise, block-diagonal form
+    ("patch_pairs_dw", 4, 32, 32, 40, 36, 3, 1, 1, "patch"),   # ... 32 channels as pixel pairs
 ]
 
 
