@@ -49,8 +49,8 @@ enum { MB200_POOL_MAX = 0, MB200_POOL_AVERAGE = 1, MB200_POOL_AVERAGE_COUNT_EXCL
 enum { MB200_QADD = 0, MB200_QFUSE_ADD_RELU = 1, MB200_QMUL = 2, MB200_QRELU = 3 };
 /* kernel choice for ConvBias: AUTO picks; DIRECT is the general CUDA-core kernel; UMMA the
  * tcgen05 implicit GEMM with TMA im2col loads; PATCH the tcgen05 halo-patch kernel (dense,
- * stride 1, or a depthwise 3x3 / stride 1 over whole 64-channel slices, which it runs with a
- * block-diagonal filter). A named kernel that does not apply returns TinyNN_ERROR_NO_IMPLEMENT. */
+ * stride 1, or a depthwise 3x3 / stride 1 over whole 64-channel slices or over 32 channels,
+ * which it runs with a block-diagonal filter). A named kernel that does not apply returns TinyNN_ERROR_NO_IMPLEMENT. */
 enum { MB200_ALGO_AUTO = 0, MB200_ALGO_DIRECT = 1, MB200_ALGO_UMMA = 2, MB200_ALGO_PATCH = 3 };
 
 /* The attributes the reference passes through TContext for a ConvBias

@@ -389,7 +389,8 @@ int mb200_conv_bias_qs8_nhwc_fused(
         if (!side_ok || !conv_patch_dw_supported(a, src, flt_packed, dst, true))
             return set_error(ST_NO_IMPLEMENT,
                              "halo-patch depthwise ConvBias needs 3x3, stride 1, channels %% 64 "
-                             "== 0, NHWC, 16-byte aligned tensors and >= 128 KiB of input");
+                             "== 0 (or 32 channels, even width, padding 1), NHWC, 16-byte aligned "
+                             "tensors and >= 128 KiB of input");
         return launch_conv_patch_dw(a, src, flt_packed, bias, flt_scales, dst, st);
     }
     const bool patch_ok = side_ok && conv_patch_supported(a, src, flt_packed, dst);

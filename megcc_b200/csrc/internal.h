@@ -45,7 +45,8 @@ struct ConvArgs {
     int pool;
     // halo-patch kernel only: `a` is the dense view of a depthwise 3x3 convolution over
     // a.oc channels taken 64 at a time (a.ic == 64, a.groups == 1): every CTA reads its own
-    // 64 input channels and builds the block-diagonal filter tile from the raw [C][3][3] filter
+    // 64 input channels and builds the block-diagonal filter tile from the raw [C][3][3] filter.
+    // 2: 32 channels, a.iw / a.ow count pixel PAIRS (64-byte rows), a.oc == 64.
     int dw64;
     // general kernel only: divide by s_dst with the true division (scales outside the range
     // in which the three-instruction division by a constant is exact, see common.cuh)
@@ -119,8 +120,8 @@ int launch_conv_umma(
         const float* flt_scales, int8_t* dst, cudaStream_t st);
 // stride-1 tensor-core ConvBias with halo-patch tiles and a resident filter (conv_patch.cu)
 bool conv_patch_supported(const ConvArgs& a, const int8_t* src, const int8_t* flt, const int8_t* dst);
-// Depthwise 3x3 / stride 1 over a multiple of 64 channels on the tensor cores: the halo-patch
-// kernel with a block-diagonal filter built on chip. `a` is the depthwise convolution itself
+// Depthwise 3x3 / stride 1 over a multiple of 64 channels (or 32 channels as pixel pairs) on
+// the tensor cores: the halo-patch kernel with a block-diagonal filter built on chip. `a` is the depthwise convolution itself
 // (groups == ic == oc), `flt` its packed filter [C][3][3]. `whatever_the_size`: leave out the
 // two checks that only say whether it pays (enough patches per CTA, few partial patches).
 bool conv_patch_dw_supported(
