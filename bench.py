@@ -239,8 +239,9 @@ def other_configs(local_rank, rates):
         e2e50, _ = int8_net(make(), 1, True)
         out[name + "_b1"] = dict(p50_ms=round(p50, 4), p95_ms=round(p95, 4),
                                  e2e_p50_ms=round(e2e50, 4))
-    p50, _ = int8_net(zoo.mobilenet_v1(), 64, False)
-    out["mobilenetv1_b64"] = dict(ms_per_forward=round(p50, 4), img_s=round(64 / (p50 * 1e-3)))
+    for b in (64, BATCH):
+        p50, _ = int8_net(zoo.mobilenet_v1(), b, False)
+        out[f"mobilenetv1_b{b}"] = dict(ms_per_forward=round(p50, 4), img_s=round(b / (p50 * 1e-3)))
     p50, _ = int8_net(zoo.resnet18(per_channel=True), BATCH, False)
     out["resnet18_b256_per_channel_scales"] = dict(ms_per_forward=round(p50, 4),
                                                    img_s=round(BATCH / (p50 * 1e-3)))
