@@ -2,7 +2,7 @@
 runtime without a CUDA graph, so that a profiler lists every kernel of a forward as its own
 launch:
 
-    python -m megcc_b200.profile_net [batch=64] [resnet18|mobilenetv1] [times]
+    python -m megcc_b200.profile_net [batch=64] [resnet18|mobilenetv1|yolox_s] [times]
 
     ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum,gpu__time_duration.sum \
         --clock-control none -k regex:"conv_|pooling_|space_to_depth" -s 24 -c 24 --csv \
@@ -18,7 +18,7 @@ import numpy as np
 
 from . import lite, zoo
 
-MODELS = {"resnet18": zoo.resnet18, "mobilenetv1": zoo.mobilenet_v1}
+MODELS = {"resnet18": zoo.resnet18, "mobilenetv1": zoo.mobilenet_v1, "yolox_s": zoo.yolox_s}
 
 
 def main(batch=64, model_name="resnet18", times=False, forwards=3):
@@ -26,7 +26,10 @@ def main(batch=64, model_name="resnet18", times=False, forwards=3):
     model = spec.to_graph().compile([batch])
     net = lite.Network(model)
     net.set_option("use_graph", 0)
-    x = np.random.default_rng(0).integers(-128, 128, (batch, 3, 224, 224), dtype=np.int8)
+    if model_name == "yolox_s":  # the fp32 detector, 640 x 640
+        x = np.random.default_rng(0).uniform(0, 1, (batch, 3, 640, 640)).astype(np.float32)
+    else:
+        x = np.random.default_rng(0).integers(-128, 128, (batch, 3, 224, 224), dtype=np.int8)
     net.set_input("data", x)
     for _ in range(forwards):
         net.forward()
@@ -46,7 +49,7 @@ def main(batch=64, model_name="resnet18", times=False, forwards=3):
         total = sum(v[1] for v in acc.values())
         print(f"total {total:.4f} ms, {batch / total * 1e3:.0f} img/s (instructions timed one by one)")
     else:
-        print("logits", net.output(net.output_names()[0])[:8])
+        print("first outputs", net.output(net.output_names()[0], dtype=x.dtype)[:8])
     net.close()
 
 
