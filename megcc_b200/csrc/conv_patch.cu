@@ -981,16 +981,19 @@ bool conv_patch_dw_supported(
     if (a.pool || a.acc_out)
         return false;
     const ConvArgs t = dw_dense_view(a);
-    // A CTA builds its filter tile and sets up TMEM and barriers before its first patch: with
-    // fewer than three patches per resident CTA the CUDA-core kernel measured faster
-    // (MobileNetV1 at batch 16 against batch 64).
+    if (!conv_patch_supported(t, src, src, dst) || flt == nullptr)
+        return false;
+    if (whatever_the_size)
+        return true;
+    // A CTA builds its filter tile and sets up TMEM and barriers before its first patch, and a
+    // partial 16 x 8 patch is paid for in full: the form is taken from four patches' worth of
+    // real outputs per SM up. Measured against the CUDA-core kernel: 512 channels at 14 x 14
+    // (77 % of the patch rows are outputs) 14.0 against 16.9 us at batch 64 and 26 against
+    // 45 us at batch 256; 1024 channels at 7 x 7 (38 %) 14.7 against 14.4 us at batch 64 and
+    // 22 against 33 us at batch 256.
     const long long tiles = (long long)t.n * ((t.oh + kTH - 1) / kTH) * ((t.ow + kTW - 1) / kTW) *
                             (t.oc / 64);
-    if (tiles < 6LL * sm_count() && !whatever_the_size)
-        return false;
-    // partial 16 x 8 patches are paid for in full
-    return conv_patch_supported(t, src, src, dst) && flt != nullptr &&
-           (conv_patch_efficiency(t) >= 0.75f || whatever_the_size);
+    return (double)tiles * conv_patch_efficiency(t) >= 4.0 * sm_count();
 }
 
 int launch_conv_patch_dw(

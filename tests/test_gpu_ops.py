@@ -351,7 +351,7 @@ DW_CASES = [
     # 32 channels: pixel pairs as 64-byte rows, two diagonals in the filter tile
     ("tc_pairs_112_c32", 2, 32, 112, 112, 1, 1, "RELU", True),
     ("tc_pairs_c32_20x36_identity", 8, 32, 20, 36, 1, 1, "IDENTITY", False),
-    ("auto_tc_14_c512", 64, 512, 14, 14, 1, 1, "RELU", False),   # 1024 patches: "auto" takes it
+    ("auto_tc_14_c512", 64, 512, 14, 14, 1, 1, "RELU", False),   # 1024 patches on 148 SMs: "auto" takes it
 ]
 
 
@@ -393,7 +393,7 @@ def test_depthwise_3x3_matches_oracle(ops, oracle, case):
     scales = None
     if per_channel:
         scales = cases.rng_for("dw_scales_" + name).uniform(0.005, 0.02, ch).astype(np.float32)
-    # "tc_" cases: the tensor-core form by name ("auto" takes it from 888 patches up only)
+    # "tc_" cases: the tensor-core form by name ("auto" takes it only from four patches of real outputs per SM up)
     out, _ = run_conv_nchw(ops, c, algo="patch" if name.startswith("tc_") else "auto",
                            flt_scales=scales)
     want = oracle.conv_bias_qs8(src, flt, bias, stride, pad, s0, scales if per_channel else s1,
