@@ -96,6 +96,7 @@ const TuningField kTuningFields[] = {
         {"patch_ctas", "MB200_PATCH_CTAS", &Tuning::patch_ctas, false},
         {"patch_alone", "MB200_PATCH_ALONE", &Tuning::patch_alone, false},
         {"patch_plain", "MB200_PATCH_PLAIN", &Tuning::patch_plain, false},
+        {"overlap_loads", "MB200_OVERLAP_LOADS", &Tuning::overlap_loads, false},
         {"dw_tensor", "MB200_DW_TENSOR", &Tuning::dw_tensor, false},
         {"dw_out", "MB200_DW_OUT", &Tuning::dw_out, false},
         {"dw_one_output", "MB200_DW_ONE_OUTPUT", &Tuning::dw_one_output, false},

@@ -400,6 +400,99 @@ __device__ __forceinline__ uint32_t epilogue_word(
 // run-time dispatch on (activation, per-channel scales, bounded, fused step); uniform across
 // the CTA. `off` is the element offset of the pixel's first channel of this chunk in the
 // output tensor (and in z, which has the same shape).
+// ---- one 32-column chunk with its TMEM load split in two ----
+// The epilogue warps are bound by the latency of their own chain (wait, tcgen05.ld,
+// requantisation, store), so the chunk's accumulators are fetched as two 16-column loads and
+// the second is in flight while the first half is requantised (halo-patch kernel, batch 256,
+// same box: first layer 134 -> 117 us with its space-to-depth pass, 64 -> 64 layers 44 -> 40 us).
+// Written for the two commonest epilogues only, each with everything fixed at compile time:
+// RELU and QFUSE_ADD_RELU in the verified one-FMA form; everything else takes
+// epilogue_store(). How this is compiled decides whether it pays: twelve instantiations (every
+// verified form and activation) made the compiler spill the accumulators in the tile loop
+// (first layer 142 us), one instantiation per fused-step mode with the operation count and
+// the activation as run-time values was slower than no overlap at all (149 against 141 us),
+// and as functions of their own (__noinline__) the variants crash ptxas 12.9.
+//
+// Can the chunk at channel ch0 take this path? (Uniform over the warp.)
+__device__ __forceinline__ bool epilogue_chunk_overlappable(
+        const EpilogueParams& e, const int8_t* dst, int ch0) {
+    if (e.fast_ops != 1 || e.acc_out || e.flt_scales || (e.oc % 32) != 0 || ch0 + 32 > e.oc)
+        return false;
+    if (((uintptr_t)dst & 31) != 0)
+        return false;
+    // the two commonest epilogues only: RELU without a fused step, QFUSE_ADD_RELU
+    if (!(e.z_mode == 0 && e.act == ACT_RELU) && e.z_mode != 2)
+        return false;
+    if (e.z_mode != 0 && (e.z_fast_a == 0.f || ((uintptr_t)e.z & 31) != 0))
+        return false;
+    return true;
+}
+
+// ZMODE 0: ConvBias with RELU; 2: QFUSE_ADD_RELU behind an IDENTITY ConvBias. `release_bar` (or null): the accumulator buffer's "drained" barrier, on which the
+// thread arrives once all its accumulators are in registers. Every lane of the warp must
+// call (the loads are warp-wide); `valid` guards the reads of z and the store.
+template <int ZMODE>
+__device__ __forceinline__ void epilogue_chunk_overlapped_t(
+        uint32_t taddr, const EpilogueParams& e, int8_t* out, const int8_t* zin, int ch0,
+        bool valid, uint64_t* release_bar) {
+    uint32_t lo[16], hi[16], packed[8], zw[8];
+    umma::tmem_ld16_nowait(taddr, lo);
+    if (ZMODE != 0 && valid)
+        asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(zw[0]), "=r"(zw[1]), "=r"(zw[2]), "=r"(zw[3]), "=r"(zw[4]),
+                       "=r"(zw[5]), "=r"(zw[6]), "=r"(zw[7])
+                     : "l"(zin));
+    const int4* bias4 = reinterpret_cast<const int4*>(e.bias ? e.bias + ch0 : kZeroBias);
+    constexpr bool relu = ZMODE == 0;
+    umma::tmem_ld_wait16(lo);
+    umma::tmem_ld16_nowait(taddr + 16u, hi);
+    auto half = [&](const uint32_t (&v)[16], int base) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int4 b = __ldg(bias4 + base + j);
+            int r0, r1, r2, r3;
+            constexpr int kAct = ZMODE == 0 ? ACT_RELU : ACT_IDENTITY;
+            requant_pair_fast<kAct, 1>((int)v[4 * j] + b.x, (int)v[4 * j + 1] + b.y, e, r0, r1);
+            requant_pair_fast<kAct, 1>((int)v[4 * j + 2] + b.z, (int)v[4 * j + 3] + b.w, e, r2, r3);
+            if (ZMODE != 0) {
+                const uint32_t z = zw[base + j];
+                r0 = fuse_z_fast<ZMODE>(r0, (int)(int8_t)(z), e.z_fast_a, e.z_fast_b);
+                r1 = fuse_z_fast<ZMODE>(r1, (int)(int8_t)(z >> 8), e.z_fast_a, e.z_fast_b);
+                r2 = fuse_z_fast<ZMODE>(r2, (int)(int8_t)(z >> 16), e.z_fast_a, e.z_fast_b);
+                r3 = fuse_z_fast<ZMODE>(r3, (int)(int8_t)(z >> 24), e.z_fast_a, e.z_fast_b);
+            }
+            const uint32_t pk = umma::pack4_prmt(r0, r1, r2, r3);
+            // RELU of the ConvBias, or of the fused sum, on packed bytes
+            packed[base + j] = (relu || ZMODE == 2) ? relu_s8x4(pk) : pk;
+        }
+    };
+    half(lo, 0);
+    umma::tmem_ld_wait16(hi);
+    if (release_bar) {
+        // all of this thread's accumulators are in registers: hand the buffer back
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        umma::mbar_arrive(release_bar);
+    }
+    half(hi, 4);
+    if (valid)
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(out),
+                     "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]),
+                     "r"(packed[4]), "r"(packed[5]), "r"(packed[6]), "r"(packed[7])
+                     : "memory");
+}
+
+// `taddr`: the chunk's first TMEM column for this thread's lane; `off`: element offset of the
+// pixel's channel ch0 in dst (and z). The caller has checked epilogue_chunk_overlappable().
+__device__ __forceinline__ void epilogue_chunk_overlapped(
+        uint32_t taddr, const EpilogueParams& e, int8_t* dst, size_t off, int ch0, bool valid,
+        uint64_t* release_bar) {
+    int8_t* out = dst + off;
+    if (e.z_mode == 0)
+        epilogue_chunk_overlapped_t<0>(taddr, e, out, nullptr, ch0, valid, release_bar);
+    else
+        epilogue_chunk_overlapped_t<2>(taddr, e, out, e.z + off, ch0, valid, release_bar);
+}
+
 template <int NV>
 __device__ __forceinline__ void epilogue_store(
         const uint32_t (&v)[NV], const EpilogueParams& e, int8_t* dst, size_t off, int ch0) {

@@ -73,6 +73,7 @@ struct PatchParams {
     int a_lbo;        // distance between the two 16-byte K halves of one A operand
     // Depthwise form (64-channel rows kernel only): the raw filter [C][3][3]. Each CTA then
     // convolves input channels n0 .. n0+63 with the block-diagonal operand it builds itself.
+    int overlap;  // 1: chunks of the verified short forms load their accumulators in two halves
     const int8_t* dw_flt;
     // 1: the depthwise tensor has 32 channels and is seen as pixel PAIRS of 64 bytes
     // ([N][H][W/2][2][32]); column 32 h + c of a row is channel c of the pair's pixel h
@@ -441,6 +442,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 2) conv_patch_ker
             if (p.ep.flt_scales)
                 pool_scales = __ldg(reinterpret_cast<const float4*>(p.ep.flt_scales + pool_ch));
         }
+        const bool overlap_ok = POOL == 0 && p.overlap && epilogue_chunk_overlappable(p.ep, p.dst, 0);
         PatchWalker at(m_first, m_step, p.tiles_y, p.tiles_x);
         for (int mt = m_first; mt < p.m_tiles && ok; mt += m_step, ++local, at.next()) {
             const int buf = local & 1;
@@ -564,6 +566,16 @@ __global__ void __launch_bounds__(64 + 32 * EW, EW == 16 ? 1 : 2) conv_patch_ker
             // one 32-column chunk: registers <- TMEM, buffer released after the warp's last
             // load, requantisation, store
             auto do_chunk = [&](int c, bool last) {
+                if (overlap_ok && n0 + c * 32 + 32 <= p.oc) {
+                    // a verified short form: the chunk's second 16 columns are fetched while
+                    // the first are requantised
+                    const int ch0 = n0 + c * 32;
+                    epilogue_chunk_overlapped(
+                            taddr + (uint32_t)(c * 32), p.ep, p.dst, px_off + ch0,
+                            (ROWS != 0 && p.dw_pairs) ? (ch0 & 31) : ch0, valid,
+                            last ? &acc_empty[buf] : nullptr);
+                    return;
+                }
                 uint32_t v[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), v);
                 if (last) {
@@ -912,6 +924,7 @@ int launch_conv_patch(
                 p.ep.z_fast_a,
                 p.ep.z_fast_b);
     p.ep.acc_out = a.acc_out;
+    p.overlap = tuning().overlap_loads;
     p.dw_flt = a.dw64 ? flt : nullptr;
     p.dw_pairs = a.dw64 == 2 ? 1 : 0;
     p.dst = dst;

@@ -13,6 +13,7 @@ struct Tuning {
     int patch_ctas = 0;     // MB200_PATCH_CTAS     1..3 = resident CTAs the patch kernel tries first
     int patch_alone = 0;    // MB200_PATCH_ALONE    1 = patch kernel even with one CTA per SM
     int patch_plain = 0;    // MB200_PATCH_PLAIN    1 = 16-channel planes for 64-channel layers
+    int overlap_loads = 1;  // MB200_OVERLAP_LOADS  0 = one 32-column TMEM load per chunk in the halo-patch epilogue
     int dw_tensor = 1;      // MB200_DW_TENSOR      0 = depthwise 3x3/1 on the CUDA cores only
     int dw_out = 0;         // MB200_DW_OUT         2 | 4 = outputs per thread of the depthwise kernel
     int dw_one_output = 0;  // MB200_DW_ONE_OUTPUT  1 = one output per thread
