@@ -428,9 +428,10 @@ __device__ __forceinline__ bool epilogue_chunk_overlappable(
     return true;
 }
 
-// ZMODE 0: ConvBias with RELU; 2: QFUSE_ADD_RELU behind an IDENTITY ConvBias. `release_bar` (or null): the accumulator buffer's "drained" barrier, on which the
-// thread arrives once all its accumulators are in registers. Every lane of the warp must
-// call (the loads are warp-wide); `valid` guards the reads of z and the store.
+// ZMODE 0: ConvBias with RELU; 2: QFUSE_ADD_RELU behind an IDENTITY ConvBias. `release_bar`
+// (or null): the accumulator buffer's "drained" barrier, on which the thread arrives once all
+// its accumulators are in registers. Every lane of the warp must call (the loads are
+// warp-wide); `valid` guards the reads of z and the store.
 template <int ZMODE>
 __device__ __forceinline__ void epilogue_chunk_overlapped_t(
         uint32_t taddr, const EpilogueParams& e, int8_t* out, const int8_t* zin, int ch0,
