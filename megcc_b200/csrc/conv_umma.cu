@@ -88,6 +88,7 @@ struct UmmaConvParams {
     // split-K (SPLITK kernels only): work items below `full_tiles` are whole tiles, the
     // tiles after them are cut into `split` parts of `k_per_part` pipeline steps each
     int full_tiles, split, k_per_part, total_items;
+    int overlap;          // 1: chunks of the verified short forms load their accumulators in two halves
     int4* slabs;          // [split item][chunk][16-byte group][row]: one part's accumulators
     unsigned* counters;   // [split tile] parts finished; zero between launches
 };
@@ -338,6 +339,7 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
         int local = 0;
         bool ok = true;
         uint32_t ep_phase = 0;  // parity of the epilogue's own rendezvous (split-K)
+        const bool overlap_ok = p.overlap && epilogue_chunk_overlappable(p.ep, p.dst, 0);
         for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++local) {
             const WorkItem w = decode_item<SPLITK>(p, item);
             const int tile = w.tile;
@@ -435,6 +437,16 @@ __global__ void __launch_bounds__(Shape<BN>::kThreads, Shape<BN>::kMinCtas) conv
             }
 #pragma unroll 1
             for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; ++c) {
+                if (overlap_ok && n0 + c * 32 + 32 <= p.oc) {
+                    // a verified short form: the chunk's second 16 columns are fetched while
+                    // the first are requantised (conv_epilogue.cuh)
+                    const int ch0 = n0 + c * 32;
+                    epilogue_chunk_overlapped(
+                            taddr + (uint32_t)(c * 32), p.ep, p.dst, (size_t)m * p.oc + ch0, ch0,
+                            m < p.m_total,
+                            c + 1 == (half + 1) * kChunksPerWarp ? &acc_empty[buf] : nullptr);
+                    continue;
+                }
                 uint32_t v[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), v);
                 if (c + 1 == (half + 1) * kChunksPerWarp) {
@@ -769,6 +781,7 @@ int launch_conv_umma_geom(
     p.split = 1;
     p.k_per_part = p.k_iters;
     p.slabs = nullptr;
+    p.overlap = tuning().overlap_loads;
     p.counters = nullptr;
     if (geom == GEOM_WIDE128) {
         if (bn == 256) {
